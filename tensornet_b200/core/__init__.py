@@ -1,0 +1,165 @@
+"""``tn.core``: the control API of the runtime.
+
+Same twenty entry points as the reference's pybind module
+(core/main/py_wrapper.cc:61-263, re-exported by tensornet/core/__init__.py:15-34), backed by
+GPU-resident tables when a CUDA device is present and by the plain C++ tables otherwise.
+Table handles are small integers handed out in creation order; every rank builds the same
+model, so handles agree across ranks (core/ps/table/sparse_table.cc:151-158).
+"""
+from __future__ import annotations
+
+from typing import Dict, List
+
+from .config import Config, config
+from .optimizers import AdaGrad, Adam, Ftrl, OptimizerBase
+from .runtime import DeviceError, runtime
+
+_sparse_tables: List[object] = []
+_sparse_groups: Dict[str, int] = {}
+_dense_tables: List[object] = []
+_bn_tables: List[object] = []
+
+
+def init() -> bool:
+    """Bind this process to its GPU (or the CPU path) and set up the process groups."""
+    return runtime().init()
+
+
+def shutdown():
+    """Tear down process groups and forget all tables (used by tests)."""
+    _sparse_tables.clear()
+    _sparse_groups.clear()
+    _dense_tables.clear()
+    _bn_tables.clear()
+    runtime().shutdown()
+
+
+def get_opt_learning_rate(opt: OptimizerBase):
+    return opt.schedule if opt.schedule is not None else opt.learning_rate
+
+
+def set_sparse_init_mode(opt: OptimizerBase, is_training: bool):
+    opt.sparse_zero_init = not is_training
+
+
+# ----------------------------------------------------------------------------- sparse
+def create_sparse_table(opt: OptimizerBase, name: str, dimension: int, use_cvm: bool = False,
+                        embedding_group: str = "", rows: int = None) -> int:
+    """Create (or, with a non-empty ``embedding_group`` seen before, share) a sparse table."""
+    rt = runtime()
+    if embedding_group:
+        if embedding_group in _sparse_groups:
+            h = _sparse_groups[embedding_group]
+            t = _sparse_tables[h]
+            assert t.dim == dimension, "tables of one embedding_group must share the dimension"
+            return h
+    if rt.on_gpu:
+        from ..ops.sparse_table_gpu import GpuSparseTable
+
+        table = GpuSparseTable(opt, dimension, use_cvm, name=name, rows=rows)
+    else:
+        from ..ops.sparse_table_cpu import CpuSparseTable
+
+        table = CpuSparseTable(opt, dimension, use_cvm, name=name)
+    _sparse_tables.append(table)
+    h = len(_sparse_tables) - 1
+    table.handle = h
+    if embedding_group:
+        _sparse_groups[embedding_group] = h
+    return h
+
+
+def sparse_table(handle: int):
+    return _sparse_tables[handle]
+
+
+def save_sparse_table(handle: int, path: str, mode: str = "txt"):
+    from ..utils import checkpoint
+
+    checkpoint.save_sparse_table(_sparse_tables[handle], path, mode)
+
+
+def load_sparse_table(handle: int, path: str, mode: str = "txt"):
+    from ..utils import checkpoint
+
+    checkpoint.load_sparse_table(_sparse_tables[handle], path, mode)
+
+
+def show_decay(handle: int, delta_days: int):
+    _sparse_tables[handle].show_decay(delta_days)
+
+
+# ----------------------------------------------------------------------------- dense
+def create_dense_table(opt: OptimizerBase) -> int:
+    from ..ops.dense_table import DenseTable
+
+    _dense_tables.append(DenseTable(opt))
+    return len(_dense_tables) - 1
+
+
+def dense_table(handle: int):
+    return _dense_tables[handle]
+
+
+def save_dense_table(handle: int, path: str):
+    from ..utils import checkpoint
+
+    checkpoint.save_dense_table(_dense_tables[handle], path)
+
+
+def load_dense_table(handle: int, path: str):
+    from ..utils import checkpoint
+
+    checkpoint.load_dense_table(_dense_tables[handle], path)
+
+
+# ----------------------------------------------------------------------------- batch norm
+def create_bn_table(name: str, bn_size: int, sync: bool, moment: float, max_count: int, use_pctr_dnn_bn: bool = False) -> int:
+    from ..ops.bn_table import BnTable
+
+    _bn_tables.append(BnTable(name, bn_size, sync, moment, max_count, use_pctr_dnn_bn))
+    return len(_bn_tables) - 1
+
+
+def bn_table(handle: int):
+    return _bn_tables[handle]
+
+
+def save_bn_table(handle: int, path: str):
+    from ..utils import checkpoint
+
+    checkpoint.save_bn_table(_bn_tables[handle], path)
+
+
+def load_bn_table(handle: int, path: str):
+    from ..utils import checkpoint
+
+    checkpoint.load_bn_table(_bn_tables[handle], path)
+
+
+# ----------------------------------------------------------------------------- cluster
+def shard_num() -> int:
+    return runtime().world
+
+
+def self_shard_id() -> int:
+    return runtime().rank
+
+
+def barrier():
+    runtime().barrier()
+
+
+def reset_balance_dataset():
+    from ..data import dataset
+
+    dataset.reset_balance_dataset()
+
+
+__all__ = [
+    "init", "shutdown", "AdaGrad", "Adam", "Ftrl", "get_opt_learning_rate", "set_sparse_init_mode",
+    "create_sparse_table", "create_dense_table", "create_bn_table", "save_sparse_table", "load_sparse_table",
+    "save_dense_table", "load_dense_table", "save_bn_table", "load_bn_table", "shard_num", "self_shard_id",
+    "barrier", "reset_balance_dataset", "show_decay", "config", "Config", "DeviceError", "runtime",
+    "sparse_table", "dense_table", "bn_table",
+]

@@ -1,0 +1,55 @@
+"""Runtime knobs of the framework, overridable by ``TN_*`` environment variables.
+
+The reference has no flag system: its sizes are compile-time constants
+(core/ps/optimizer/optimizer_kernel.h:42-43,257-266, core/ps/ps_cluster.cc:78-79).
+Here they are one dataclass so a job can size the GPU tables for its data.
+"""
+from __future__ import annotations
+
+import dataclasses
+import os
+
+
+def _env(name: str, default, cast):
+    v = os.environ.get(name)
+    if v is None or v == "":
+        return default
+    if cast is bool:
+        return v.lower() not in ("0", "false", "no", "off")
+    return cast(v)
+
+
+@dataclasses.dataclass
+class Config:
+    #: rows each GPU's shard of a sparse table can hold (row slab capacity)
+    table_rows_per_gpu: int = 1 << 22
+    #: key-array load factor target; the key array is the next power of two >= rows / load_factor
+    table_load_factor: float = 0.5
+    #: head-room factor of one (sender, owner) segment over the even split unique/world
+    owner_segment_slack: float = 1.3
+    #: wall-time budget of every device-side wait, in seconds
+    wait_budget_s: float = 2.0
+    #: seed of the deterministic row initialiser
+    seed: int = 0x7E50A
+    #: use NVSwitch multicast (multimem) in the dense path when the mapping exists
+    use_multimem: bool = True
+    #: capture the train step in a CUDA graph
+    cuda_graph: bool = True
+    #: force the CPU oracle path even when a GPU is visible
+    force_cpu: bool = False
+
+    @classmethod
+    def from_env(cls) -> "Config":
+        c = cls()
+        c.table_rows_per_gpu = _env("TN_TABLE_ROWS", c.table_rows_per_gpu, int)
+        c.table_load_factor = _env("TN_TABLE_LOAD_FACTOR", c.table_load_factor, float)
+        c.owner_segment_slack = _env("TN_SEGMENT_SLACK", c.owner_segment_slack, float)
+        c.wait_budget_s = _env("TN_WAIT_BUDGET_S", c.wait_budget_s, float)
+        c.seed = _env("TN_SEED", c.seed, int)
+        c.use_multimem = _env("TN_USE_MULTIMEM", c.use_multimem, bool)
+        c.cuda_graph = _env("TN_CUDA_GRAPH", c.cuda_graph, bool)
+        c.force_cpu = _env("TN_FORCE_CPU", c.force_cpu, bool)
+        return c
+
+
+config = Config.from_env()

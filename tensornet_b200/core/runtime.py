@@ -1,0 +1,140 @@
+"""Process-wide runtime: device binding, process groups, status words.
+
+Replaces the reference's PsCluster / MpiManager bootstrap
+(core/ps/ps_cluster.cc:33-67, core/utility/mpi_manager.cc:46-97): one process per GPU
+started by ``torchrun``; ``torch.distributed`` carries the control plane (gloo for host
+barriers and object exchange, NCCL for symmetric-memory rendezvous and the baseline
+collectives); the data plane is peer memory written by this library's own kernels.
+"""
+from __future__ import annotations
+
+import datetime
+import os
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .config import config
+
+STATUS_NAMES = {
+    0: "ok",
+    1: "per-batch dedup scratch overflow",
+    2: "owner segment overflow (raise bucket_size or TN_SEGMENT_SLACK)",
+    3: "sparse table full (raise TN_TABLE_ROWS)",
+    4: "grid barrier timed out",
+    5: "wait on a peer GPU timed out",
+    6: "tensor-core pipeline wait timed out",
+    7: "sign missing from the table",
+    8: "bad argument",
+}
+
+
+class DeviceError(RuntimeError):
+    """A kernel recorded an error in the status words."""
+
+    def __init__(self, code: int, phase: int, aux: int):
+        self.code, self.phase, self.aux = code, phase, aux
+        super().__init__(f"device status {code} ({STATUS_NAMES.get(code, '?')}), phase {phase}, peer/aux {aux}")
+
+
+class Runtime:
+    def __init__(self):
+        self.initialized = False
+        self.rank = 0
+        self.world = 1
+        self.local_rank = 0
+        self.device = torch.device("cpu")
+        self.on_gpu = False
+        self.host_group = None      # gloo group: barriers, object exchange
+        self.device_group = None    # nccl group: symmetric memory rendezvous, baseline collectives
+        self._status = None
+        self._owns_pg = False
+
+    # ------------------------------------------------------------------
+    def init(self) -> bool:
+        if self.initialized:
+            return True
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", str(self.rank)))
+        self.on_gpu = torch.cuda.is_available() and not config.force_cpu
+        if self.on_gpu:
+            self.device = torch.device("cuda", self.local_rank % torch.cuda.device_count())
+            torch.cuda.set_device(self.device)
+        else:
+            self.device = torch.device("cpu")
+        if self.world > 1:
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            os.environ.setdefault("MASTER_PORT", "29511")
+            timeout = datetime.timedelta(seconds=int(os.environ.get("TN_PG_TIMEOUT_S", "600")))
+            if not dist.is_initialized():
+                backend = "nccl" if self.on_gpu else "gloo"
+                kwargs = {}
+                if self.on_gpu:
+                    kwargs["device_id"] = self.device
+                dist.init_process_group(backend, rank=self.rank, world_size=self.world, timeout=timeout, **kwargs)
+                self._owns_pg = True
+            if self.on_gpu:
+                self.device_group = dist.group.WORLD
+                self.host_group = dist.new_group(backend="gloo", timeout=timeout)
+            else:
+                self.host_group = dist.group.WORLD
+        if self.on_gpu:
+            self._status = torch.zeros(8, dtype=torch.int32, device=self.device)
+        self.initialized = True
+        return True
+
+    def shutdown(self):
+        if self._owns_pg and dist.is_initialized():
+            dist.destroy_process_group()
+        self.__init__()
+
+    # ------------------------------------------------------------------
+    @property
+    def status(self) -> torch.Tensor:
+        if self._status is None:
+            self._status = torch.zeros(8, dtype=torch.int32, device=self.device)
+        return self._status
+
+    def check_status(self):
+        """Raise DeviceError if any kernel reported a problem (synchronises the stream)."""
+        if not self.on_gpu:
+            return
+        s = self.status.tolist()
+        if s[0] != 0:
+            self._status.zero_()
+            raise DeviceError(s[0], s[1], s[2])
+
+    @property
+    def wait_ns(self) -> int:
+        return int(config.wait_budget_s * 1e9)
+
+    def barrier(self):
+        if self.world > 1:
+            if self.on_gpu:
+                torch.cuda.synchronize()
+            dist.barrier(group=self.host_group)
+
+    def all_gather_object(self, obj):
+        if self.world == 1:
+            return [obj]
+        out = [None] * self.world
+        dist.all_gather_object(out, obj, group=self.host_group)
+        return out
+
+    def broadcast_object(self, obj, src: int = 0):
+        if self.world == 1:
+            return obj
+        lst = [obj]
+        dist.broadcast_object_list(lst, src=src, group=self.host_group)
+        return lst[0]
+
+
+_RT = Runtime()
+
+
+def runtime() -> Runtime:
+    if not _RT.initialized:
+        _RT.init()
+    return _RT

@@ -1,0 +1,332 @@
+// Python bindings of the sm_100a kernels (module tensornet_b200._ext._tn_cuda).
+// Storage is owned by torch tensors created on the Python side; the objects here only keep
+// raw device pointers (plus a reference to the tensors) so a kernel launch costs one call.
+#include <torch/extension.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <cuda_runtime.h>
+#include <atomic>
+#include <string>
+#include <vector>
+
+#include "gemm_tcgen05.h"
+#include "tn_ops.h"
+#include "tn_types.h"
+
+namespace py = pybind11;
+
+namespace {
+
+template <typename T>
+T* ptr_of(const at::Tensor& t) { return reinterpret_cast<T*>(t.data_ptr()); }
+template <typename T>
+T* ptr_of(int64_t p) { return reinterpret_cast<T*>(static_cast<uintptr_t>(p)); }
+
+// Every binding that launches a kernel fetches the stream exactly once, so this doubles as the
+// count of kernels this library has launched (or recorded into a CUDA graph).
+std::atomic<long long> g_launches{0};
+cudaStream_t cur_stream() {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return at::cuda::getCurrentCUDAStream().stream();
+}
+
+void check(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+tn::SparseOptParams opt_from_dict(const py::dict& d) {
+  tn::SparseOptParams o{};
+  o.kind = d["kind"].cast<int>();
+  o.lr = d["lr"].cast<float>();
+  o.eps = d["eps"].cast<float>();
+  o.beta1 = d["beta1"].cast<float>();
+  o.beta2 = d["beta2"].cast<float>();
+  o.initial_g2sum = d["initial_g2sum"].cast<float>();
+  o.initial_scale = d["initial_scale"].cast<float>();
+  o.ftrl_beta = d["ftrl_beta"].cast<float>();
+  o.lambda1 = d["lambda1"].cast<float>();
+  o.lambda2 = d["lambda2"].cast<float>();
+  o.zero_init = d["zero_init"].cast<int>();
+  o.seed = d["seed"].cast<uint64_t>();
+  return o;
+}
+
+tn::TableView table_from_dict(const py::dict& d) {
+  tn::TableView t{};
+  t.keys = ptr_of<unsigned long long>(d["keys"].cast<at::Tensor>());
+  t.slots = ptr_of<int>(d["slots"].cast<at::Tensor>());
+  t.rows = ptr_of<float>(d["rows"].cast<at::Tensor>());
+  t.row_keys = ptr_of<unsigned long long>(d["row_keys"].cast<at::Tensor>());
+  t.row_tag = ptr_of<unsigned long long>(d["row_tag"].cast<at::Tensor>());
+  t.n_rows = ptr_of<int>(d["n_rows"].cast<at::Tensor>());
+  int64_t cap = d["keys"].cast<at::Tensor>().numel();
+  TORCH_CHECK(cap > 0 && (cap & (cap - 1)) == 0, "table capacity must be a power of two");
+  t.cap_mask = (unsigned)(cap - 1);
+  t.row_cap = (int)d["row_keys"].cast<at::Tensor>().numel();
+  t.dim = d["dim"].cast<int>();
+  t.stride = d["stride"].cast<int>();
+  t.use_cvm = d["use_cvm"].cast<int>();
+  return t;
+}
+
+// One embedding table + its exchange buffers.
+struct SparseCtx {
+  tn::SparseCommView c{};
+  tn::TableView t{};
+  tn::SparseOptParams o{};
+  int pull_lanes = 1, push_lanes = 1;
+  py::dict keep;   // keeps the tensors alive
+
+  SparseCtx(py::dict table, py::dict comm, py::dict opt) {
+    keep["table"] = table; keep["comm"] = comm;
+    t = table_from_dict(table);
+    o = opt_from_dict(opt);
+    c.world = comm["world"].cast<int>();
+    c.rank = comm["rank"].cast<int>();
+    c.capo = comm["capo"].cast<int>();
+    c.gstride = comm["gstride"].cast<int>();
+    c.ustride = comm["ustride"].cast<int>();
+    TORCH_CHECK(c.world >= 1 && c.world <= tn::kMaxWorld, "world must be 1..8");
+    TORCH_CHECK(c.capo % 4 == 0, "segment capacity must be a multiple of 4");
+    auto inbox = comm["inbox_ids"].cast<std::vector<int64_t>>();
+    auto ginbox = comm["ginbox"].cast<std::vector<int64_t>>();
+    auto U = comm["U"].cast<std::vector<int64_t>>();
+    auto sig = comm["sig"].cast<std::vector<int64_t>>();
+    TORCH_CHECK((int)inbox.size() == c.world && (int)ginbox.size() == c.world && (int)U.size() == c.world &&
+                    (int)sig.size() == c.world, "peer pointer tables must have `world` entries");
+    for (int p = 0; p < c.world; ++p) {
+      c.inbox_ids[p] = ptr_of<unsigned long long>(inbox[p]);
+      c.ginbox[p] = ptr_of<float>(ginbox[p]);
+      c.U[p] = ptr_of<float>(U[p]);
+      c.sig[p] = ptr_of<unsigned long long>(sig[p]);
+    }
+    c.stage_ids = ptr_of<unsigned long long>(comm["stage_ids"].cast<at::Tensor>());
+    c.gU = ptr_of<float>(comm["gU"].cast<at::Tensor>());
+    c.cnt = ptr_of<int>(comm["cnt"].cast<at::Tensor>());
+    c.cnt_saved = ptr_of<int>(comm["cnt_saved"].cast<at::Tensor>());
+    c.req_n = ptr_of<int>(comm["req_n"].cast<at::Tensor>());
+    c.req_row = ptr_of<int>(comm["req_row"].cast<at::Tensor>());
+    c.req_ou = ptr_of<int>(comm["req_ou"].cast<at::Tensor>());
+    c.ou_row = ptr_of<int>(comm["ou_row"].cast<at::Tensor>());
+    c.ocount = ptr_of<int>(comm["ocount"].cast<at::Tensor>());
+    c.acc = ptr_of<float>(comm["acc"].cast<at::Tensor>());
+    at::Tensor ddk = comm["dd_keys"].cast<at::Tensor>();
+    int64_t ddcap = ddk.numel();
+    TORCH_CHECK(ddcap >= 2 && (ddcap & (ddcap - 1)) == 0, "dedup scratch must be a power of two");
+    c.dd_keys = ptr_of<unsigned long long>(ddk);
+    c.dd_vals = ptr_of<int>(comm["dd_vals"].cast<at::Tensor>());
+    c.dd_mask = (unsigned)(ddcap - 1);
+    c.epoch = ptr_of<unsigned long long>(comm["epoch"].cast<at::Tensor>());
+    c.bar = ptr_of<unsigned>(comm["bar"].cast<at::Tensor>());
+    c.status = ptr_of<int>(comm["status"].cast<at::Tensor>());
+    c.wait_ns = comm["wait_ns"].cast<uint64_t>();
+    pull_lanes = tn::lanes_for_width_host(c.ustride);
+    push_lanes = tn::lanes_for_width_host(t.dim);
+  }
+
+  void set_opt(py::dict opt) { o = opt_from_dict(opt); }
+  void set_table(py::dict table) { keep["table"] = table; t = table_from_dict(table); }
+
+  void pull(at::Tensor ids, at::Tensor inverse, c10::optional<at::Tensor> labels, int label_mod, bool training) {
+    TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous(), "ids: contiguous int64 CUDA tensor");
+    TORCH_CHECK(inverse.scalar_type() == at::kInt && inverse.numel() >= ids.numel(), "inverse: int32, one per id");
+    c10::cuda::CUDAGuard guard(ids.device());
+    tn::PullArgs a{};
+    a.c = c; a.tbl = t; a.opt = o;
+    a.ids = ptr_of<const long long>(ids);
+    a.n_ids = (int)ids.numel();
+    a.inverse = ptr_of<int>(inverse);
+    a.labels = labels.has_value() ? ptr_of<const float>(*labels) : nullptr;
+    a.label_mod = label_mod;
+    a.training = training ? 1 : 0;
+    a.lanes = pull_lanes;
+    long long work = (long long)a.n_ids * (pull_lanes > 4 ? pull_lanes / 2 : 2);
+    if (work > (1ll << 30)) work = 1ll << 30;
+    check(tn::launch_sparse_pull(a, (int)work, cur_stream()), "sparse_pull_fused launch");
+  }
+
+  void push(int64_t work_hint) {
+    tn::PushArgs a{};
+    a.c = c; a.tbl = t; a.opt = o; a.lanes = push_lanes;
+    long long work = work_hint * push_lanes;
+    if (work > (1ll << 30)) work = 1ll << 30;
+    check(tn::launch_sparse_push(a, (int)work, cur_stream()), "sparse_push_fused launch");
+  }
+};
+
+struct DenseCtx {
+  tn::DenseStepArgs a{};
+  py::dict keep;
+  DenseCtx(py::dict d) {
+    keep = d;
+    a.opt.kind = d["kind"].cast<int>();
+    a.opt.beta1 = d["beta1"].cast<float>();
+    a.opt.beta2 = d["beta2"].cast<float>();
+    a.opt.eps = d["eps"].cast<float>();
+    a.opt.grad_decay = d["grad_decay"].cast<float>();
+    a.opt.mom_decay = d["mom_decay"].cast<float>();
+    a.opt.state = ptr_of<float>(d["state"].cast<at::Tensor>());
+    a.n = d["n"].cast<long long>();
+    a.chunk = d["chunk"].cast<long long>();
+    a.world = d["world"].cast<int>();
+    a.rank = d["rank"].cast<int>();
+    a.grad_scale = d["grad_scale"].cast<float>();
+    auto W = d["W"].cast<std::vector<int64_t>>();
+    auto G = d["G"].cast<std::vector<int64_t>>();
+    auto Wb = d["Wb"].cast<std::vector<int64_t>>();
+    auto sig = d["sig"].cast<std::vector<int64_t>>();
+    TORCH_CHECK((int)W.size() == a.world && (int)G.size() == a.world && (int)Wb.size() == a.world, "peer tables");
+    for (int p = 0; p < a.world; ++p) {
+      a.W[p] = ptr_of<float>(W[p]); a.G[p] = ptr_of<float>(G[p]); a.Wb[p] = ptr_of<void>(Wb[p]);
+      a.sig[p] = p < (int)sig.size() ? ptr_of<unsigned long long>(sig[p]) : nullptr;
+    }
+    a.W_mc = ptr_of<float>(d["W_mc"].cast<int64_t>());
+    a.G_mc = ptr_of<float>(d["G_mc"].cast<int64_t>());
+    a.Wb_mc = ptr_of<void>(d["Wb_mc"].cast<int64_t>());
+    a.s0 = ptr_of<float>(d["s0"].cast<at::Tensor>());
+    a.s1 = ptr_of<float>(d["s1"].cast<at::Tensor>());
+    a.s2 = d.contains("s2") && !d["s2"].is_none() ? ptr_of<float>(d["s2"].cast<at::Tensor>()) : nullptr;
+    a.epoch = ptr_of<unsigned long long>(d["epoch"].cast<at::Tensor>());
+    a.bar = ptr_of<unsigned>(d["bar"].cast<at::Tensor>());
+    a.status = ptr_of<int>(d["status"].cast<at::Tensor>());
+    a.wait_ns = d["wait_ns"].cast<uint64_t>();
+  }
+  void step() { check(tn::launch_dense_step(a, cur_stream()), "dense step launch"); }
+};
+
+void gemm(at::Tensor A, at::Tensor B, at::Tensor C, int M, int N, int K, int lda, int ldb, int ldc, bool a_mn, bool b_mn,
+          bool accumulate, bool relu, c10::optional<at::Tensor> bias, c10::optional<at::Tensor> mask_aux,
+          c10::optional<at::Tensor> had_x0, c10::optional<at::Tensor> had_xl, int ld_aux, int ones_col, int n_store,
+          int split_k, int BN, at::Tensor status) {
+  TORCH_CHECK(A.is_cuda() && B.is_cuda() && C.is_cuda(), "gemm: CUDA tensors");
+  TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16, "gemm: bf16 operands");
+  c10::cuda::CUDAGuard guard(A.device());
+  tn::GemmDesc d;
+  d.M = M; d.N = N; d.K = K; d.A = A.data_ptr(); d.B = B.data_ptr(); d.lda = lda; d.ldb = ldb;
+  d.a_mn = a_mn; d.b_mn = b_mn; d.C = C.data_ptr(); d.ldc = ldc;
+  d.out_f32 = C.scalar_type() == at::kFloat;
+  TORCH_CHECK(d.out_f32 || C.scalar_type() == at::kBFloat16, "gemm: C must be fp32 or bf16");
+  d.accumulate = accumulate; d.relu = relu;
+  d.bias = bias.has_value() ? ptr_of<const float>(*bias) : nullptr;
+  d.mask_aux = mask_aux.has_value() ? mask_aux->data_ptr() : nullptr;
+  d.had_x0 = had_x0.has_value() ? had_x0->data_ptr() : nullptr;
+  d.had_xl = had_xl.has_value() ? had_xl->data_ptr() : nullptr;
+  d.ld_aux = ld_aux; d.ones_col = ones_col; d.n_store = n_store; d.split_k = split_k; d.BN = BN;
+  d.status = ptr_of<int>(status);
+  const char* err = tn::gemm_bf16(d, cur_stream());
+  if (err) throw std::runtime_error(err);
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  py::class_<SparseCtx>(m, "SparseCtx")
+      .def(py::init<py::dict, py::dict, py::dict>())
+      .def("set_opt", &SparseCtx::set_opt)
+      .def("set_table", &SparseCtx::set_table)
+      .def("pull", &SparseCtx::pull)
+      .def("push", &SparseCtx::push);
+  py::class_<DenseCtx>(m, "DenseCtx").def(py::init<py::dict>()).def("step", &DenseCtx::step);
+  m.def("gemm", &gemm);
+  m.def("launch_count", []() { return g_launches.load(); });
+
+  m.def("pool_fwd", [](at::Tensor U, int ustride, at::Tensor inverse, c10::optional<at::Tensor> offsets, int B, int S, int pd,
+                       int combiner, at::Tensor out, int out_ld) {
+    c10::cuda::CUDAGuard guard(U.device());
+    tn::launch_pool_fwd(ptr_of<float>(U), ustride, ptr_of<int>(inverse), offsets ? ptr_of<int>(*offsets) : nullptr, B, S, pd,
+                        combiner, ptr_of<float>(out), out_ld, cur_stream());
+  });
+  m.def("pool_bwd", [](at::Tensor gU, int gstride, at::Tensor inverse, c10::optional<at::Tensor> offsets, int B, int S, int pd,
+                       int dim, int combiner, at::Tensor gout, int gout_ld) {
+    c10::cuda::CUDAGuard guard(gU.device());
+    tn::launch_pool_bwd(ptr_of<float>(gU), gstride, ptr_of<int>(inverse), offsets ? ptr_of<int>(*offsets) : nullptr, B, S, pd,
+                        dim, combiner, ptr_of<float>(gout), gout_ld, cur_stream());
+  });
+  m.def("seq_fwd", [](at::Tensor U, int ustride, at::Tensor inverse, at::Tensor offsets, int B, int T, int pd, at::Tensor out,
+                      at::Tensor lengths) {
+    c10::cuda::CUDAGuard guard(U.device());
+    tn::launch_seq_fwd(ptr_of<float>(U), ustride, ptr_of<int>(inverse), ptr_of<int>(offsets), B, T, pd, ptr_of<float>(out),
+                       ptr_of<int>(lengths), cur_stream());
+  });
+  m.def("seq_bwd", [](at::Tensor gU, int gstride, at::Tensor inverse, at::Tensor offsets, int B, int T, int pd, int dim,
+                      at::Tensor gout) {
+    c10::cuda::CUDAGuard guard(gU.device());
+    tn::launch_seq_bwd(ptr_of<float>(gU), gstride, ptr_of<int>(inverse), ptr_of<int>(offsets), B, T, pd, dim,
+                       ptr_of<float>(gout), cur_stream());
+  });
+  m.def("table_insert_keys", [](py::dict table, at::Tensor keys, at::Tensor out_rows, at::Tensor status) {
+    c10::cuda::CUDAGuard guard(keys.device());
+    tn::launch_table_insert_keys(table_from_dict(table), ptr_of<long long>(keys), (int)keys.numel(), ptr_of<int>(out_rows),
+                                 ptr_of<int>(status), cur_stream());
+  });
+  m.def("table_lookup", [](py::dict table, at::Tensor keys, at::Tensor out_rows) {
+    c10::cuda::CUDAGuard guard(keys.device());
+    tn::launch_table_lookup(table_from_dict(table), ptr_of<long long>(keys), (int)keys.numel(), ptr_of<int>(out_rows), cur_stream());
+  });
+  m.def("table_decay", [](py::dict table, int kind, float rate, int delta_days) {
+    tn::launch_table_decay(table_from_dict(table), kind, rate, delta_days, cur_stream());
+  });
+  m.def("fm_fwd", [](at::Tensor E, int ld, int B, int F, int D, at::Tensor out) {
+    c10::cuda::CUDAGuard guard(E.device());
+    tn::launch_fm_fwd(ptr_of<float>(E), ld, B, F, D, ptr_of<float>(out), cur_stream());
+  });
+  m.def("fm_bwd", [](at::Tensor E, int ld, int B, int F, int D, at::Tensor gout, at::Tensor gE, int gld, bool accumulate) {
+    c10::cuda::CUDAGuard guard(E.device());
+    tn::launch_fm_bwd(ptr_of<float>(E), ld, B, F, D, ptr_of<float>(gout), ptr_of<float>(gE), gld, accumulate, cur_stream());
+  });
+  auto concat_like = [](bool split) {
+    return [split](std::vector<c10::optional<at::Tensor>> pieces, std::vector<int> widths, std::vector<int> lds, at::Tensor out,
+                   int B, int ld_out, int ones_col) {
+      TORCH_CHECK(pieces.size() <= (size_t)tn::kMaxPieces && pieces.size() == widths.size() && lds.size() == widths.size(),
+                  "concat: at most 6 pieces");
+      c10::cuda::CUDAGuard guard(out.device());
+      tn::ConcatArgs a{};
+      a.B = B; a.n_pieces = (int)pieces.size(); a.out = out.data_ptr(); a.ld_out = ld_out; a.ones_col = ones_col;
+      for (size_t p = 0; p < pieces.size(); ++p) {
+        a.width[p] = widths[p]; a.ld[p] = lds[p];
+        if (pieces[p].has_value()) {
+          a.ptr[p] = pieces[p]->data_ptr();
+          a.is_bf16[p] = pieces[p]->scalar_type() == at::kBFloat16;
+          TORCH_CHECK(a.is_bf16[p] || pieces[p]->scalar_type() == at::kFloat, "concat: fp32 or bf16 pieces");
+        } else {
+          a.ptr[p] = nullptr; a.is_bf16[p] = 0;
+        }
+      }
+      if (split) tn::launch_split_cast(a, cur_stream()); else tn::launch_concat_cast(a, cur_stream());
+    };
+  };
+  m.def("concat_cast", concat_like(false));
+  m.def("split_cast", concat_like(true));
+  m.def("gemv_fwd", [](at::Tensor Z, int ld, int B, int K, at::Tensor w, at::Tensor y) {
+    c10::cuda::CUDAGuard guard(Z.device());
+    tn::launch_gemv_fwd(Z.data_ptr(), ld, B, K, ptr_of<float>(w), ptr_of<float>(y), cur_stream());
+  });
+  m.def("gemv_bwd", [](at::Tensor Z, int ld, int B, int K, at::Tensor w, at::Tensor dy, at::Tensor dZ, at::Tensor gw, int relu_cols) {
+    c10::cuda::CUDAGuard guard(Z.device());
+    tn::launch_gemv_bwd(Z.data_ptr(), ld, B, K, ptr_of<float>(w), ptr_of<float>(dy), dZ.data_ptr(), ptr_of<float>(gw), relu_cols,
+                        cur_stream());
+  });
+  m.def("bce", [](at::Tensor logit, at::Tensor label, c10::optional<at::Tensor> pred, c10::optional<at::Tensor> dlogit,
+                  float grad_scale, at::Tensor sums) {
+    c10::cuda::CUDAGuard guard(logit.device());
+    tn::launch_bce(ptr_of<float>(logit), ptr_of<float>(label), (int)logit.numel(), pred ? ptr_of<float>(*pred) : nullptr,
+                   dlogit ? ptr_of<float>(*dlogit) : nullptr, grad_scale, ptr_of<float>(sums), cur_stream());
+  });
+  m.def("relu_mask", [](at::Tensor g, at::Tensor y) {
+    c10::cuda::CUDAGuard guard(g.device());
+    TORCH_CHECK(g.numel() % 8 == 0 && g.numel() == y.numel(), "relu_mask: numel must be a multiple of 8");
+    tn::launch_relu_mask(g.data_ptr(), y.data_ptr(), g.numel(), cur_stream());
+  });
+  m.def("cross_v1_fwd", [](at::Tensor x0, at::Tensor xl, at::Tensor w, at::Tensor bias, at::Tensor y, at::Tensor dot) {
+    c10::cuda::CUDAGuard guard(x0.device());
+    tn::launch_cross_v1_fwd(ptr_of<float>(x0), ptr_of<float>(xl), ptr_of<float>(w), ptr_of<float>(bias), (int)x0.size(0),
+                            (int)x0.size(1), ptr_of<float>(y), ptr_of<float>(dot), cur_stream());
+  });
+  m.def("cross_v1_bwd", [](at::Tensor x0, at::Tensor xl, at::Tensor w, at::Tensor dot, at::Tensor gy, at::Tensor gx0,
+                           at::Tensor gxl, at::Tensor gw, at::Tensor gb) {
+    c10::cuda::CUDAGuard guard(x0.device());
+    tn::launch_cross_v1_bwd(ptr_of<float>(x0), ptr_of<float>(xl), ptr_of<float>(w), ptr_of<float>(dot), ptr_of<float>(gy),
+                            (int)x0.size(0), (int)x0.size(1), ptr_of<float>(gx0), ptr_of<float>(gxl), ptr_of<float>(gw),
+                            ptr_of<float>(gb), cur_stream());
+  });
+}

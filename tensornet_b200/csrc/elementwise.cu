@@ -1,0 +1,271 @@
+// Memory-bound pieces of the dense towers, each fused as far as the data flow allows:
+//   fm_fwd / fm_bwd            second-order FM term   (examples/common/layers.py:91-100)
+//   concat_cast / split_cast   fp32/bf16 pieces -> one padded bf16 GEMM operand with the
+//                              constant-one bias column, and the reverse for gradients
+//   gemv_fwd / gemv_bwd        the final Dense(1) head (examples/models/deepfm.py:52-57)
+//   bce_fwd_bwd                sigmoid + binary cross-entropy + dlogit + CTR/PCTR sums
+//                              (examples/main.py:63-74, tensornet/metric/metrics.py:31-104)
+//   cross_v1_fwd / bwd         DCN-v1 rank-1 cross layer (examples/common/layers.py:53-59)
+#include <cuda_bf16.h>
+#include "tn_device.cuh"
+#include "tn_ops.h"
+
+namespace tn {
+
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// ---- FM -------------------------------------------------------------------------------
+// E: [B, F, D] (row stride ld).  One warp per example; lane d handles component d (D <= 32)
+// or strides over D.
+__global__ void fm_fwd_kernel(const float* __restrict__ E, int ld, int B, int F, int D, float* __restrict__ out) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  for (int b = warp; b < B; b += nwarps) {
+    const float* e = E + (size_t)b * ld;
+    float acc = 0.f;
+    for (int d = lane; d < D; d += 32) {
+      float s = 0.f, sq = 0.f;
+      for (int f = 0; f < F; ++f) { float x = e[f * D + d]; s += x; sq += x * x; }
+      acc += s * s - sq;
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) out[b] = 0.5f * acc;
+  }
+}
+// gE[b,f,d] = gout[b] * (sum_f E[b,:,d] - E[b,f,d])
+__global__ void fm_bwd_kernel(const float* __restrict__ E, int ld, int B, int F, int D, const float* __restrict__ gout,
+                              float* __restrict__ gE, int gld, int accumulate) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  for (int b = warp; b < B; b += nwarps) {
+    const float* e = E + (size_t)b * ld;
+    float* g = gE + (size_t)b * gld;
+    const float go = gout[b];
+    for (int d = lane; d < D; d += 32) {
+      float s = 0.f;
+      for (int f = 0; f < F; ++f) s += e[f * D + d];
+      for (int f = 0; f < F; ++f) {
+        float v = go * (s - e[f * D + d]);
+        if (accumulate) g[f * D + d] += v; else g[f * D + d] = v;
+      }
+    }
+  }
+}
+
+// ---- concat + cast ----------------------------------------------------------------------
+__global__ void concat_cast_kernel(const ConcatArgs a) {
+  const long long total = (long long)a.B * a.ld_out;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int b = (int)(i / a.ld_out), c = (int)(i - (long long)b * a.ld_out);
+    float v = 0.f;
+    if (c == a.ones_col) {
+      v = 1.f;
+    } else {
+      int off = 0;
+#pragma unroll
+      for (int p = 0; p < kMaxPieces; ++p) {
+        if (p < a.n_pieces) {
+          const int w = a.width[p];
+          if (c >= off && c < off + w) {
+            const size_t idx = (size_t)b * a.ld[p] + (c - off);
+            v = a.is_bf16[p] ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.ptr[p])[idx])
+                             : reinterpret_cast<const float*>(a.ptr[p])[idx];
+          }
+          off += w;
+        }
+      }
+    }
+    reinterpret_cast<__nv_bfloat16*>(a.out)[i] = __float2bfloat16(v);
+  }
+}
+// reverse: bf16 [B, ld_out] -> fp32 pieces (each piece written densely with its own ld)
+__global__ void split_cast_kernel(const ConcatArgs a) {
+  int total_w = 0;
+  for (int p = 0; p < a.n_pieces; ++p) total_w += a.width[p];
+  const long long total = (long long)a.B * total_w;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int b = (int)(i / total_w), c = (int)(i - (long long)b * total_w);
+    const float v = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.out)[(size_t)b * a.ld_out + c]);
+    int off = 0;
+    for (int p = 0; p < a.n_pieces; ++p) {
+      const int w = a.width[p];
+      if (c >= off && c < off + w) {
+        if (a.ptr[p]) {
+          const size_t idx = (size_t)b * a.ld[p] + (c - off);
+          if (a.is_bf16[p]) reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(a.ptr[p]))[idx] = __float2bfloat16(v);
+          else reinterpret_cast<float*>(const_cast<void*>(a.ptr[p]))[idx] = v;
+        }
+        break;
+      }
+      off += w;
+    }
+  }
+}
+
+// ---- Dense(1) head -------------------------------------------------------------------------
+// y[b] = sum_k Z[b,k] * w[k]   (Z bf16 [B, ld], w fp32 [K]; the bias rides on Z's ones column)
+__global__ void gemv_fwd_kernel(const __nv_bfloat16* __restrict__ Z, int ld, int B, int K, const float* __restrict__ w,
+                                float* __restrict__ y) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  for (int b = warp; b < B; b += nwarps) {
+    const __nv_bfloat16* z = Z + (size_t)b * ld;
+    float acc = 0.f;
+    for (int k = lane; k < K; k += 32) acc += __bfloat162float(z[k]) * __ldg(w + k);
+    acc = warp_sum(acc);
+    if (lane == 0) y[b] = acc;
+  }
+}
+// dZ[b,k] = dy[b] * w[k] (bf16, masked where relu_cols > k and Z <= 0);  gw[k] += sum_b dy[b] * Z[b,k]
+__global__ void gemv_bwd_kernel(const __nv_bfloat16* __restrict__ Z, int ld, int B, int K, const float* __restrict__ w,
+                                const float* __restrict__ dy, __nv_bfloat16* __restrict__ dZ, float* __restrict__ gw,
+                                int relu_cols) {
+  extern __shared__ float s_gw[];   // [K]
+  for (int k = threadIdx.x; k < K; k += blockDim.x) s_gw[k] = 0.f;
+  __syncthreads();
+  const int rows_per_block = (B + gridDim.x - 1) / gridDim.x;
+  const int b0 = blockIdx.x * rows_per_block;
+  const int b1 = min(B, b0 + rows_per_block);
+  // thread k-strided over columns, loop over the block's rows: coalesced along k
+  for (int k = threadIdx.x; k < ld; k += blockDim.x) {
+    const float wk = k < K ? __ldg(w + k) : 0.f;
+    float acc = 0.f;
+    for (int b = b0; b < b1; ++b) {
+      const float z = __bfloat162float(Z[(size_t)b * ld + k]);
+      const float d = dy[b];
+      float g = d * wk;
+      if (k < relu_cols && !(z > 0.f)) g = 0.f;
+      dZ[(size_t)b * ld + k] = __float2bfloat16(k < K ? g : 0.f);
+      acc += d * z;
+    }
+    if (k < K) s_gw[k] = acc;
+  }
+  __syncthreads();
+  for (int k = threadIdx.x; k < K; k += blockDim.x) atomicAdd(gw + k, s_gw[k]);
+}
+
+// ---- sigmoid BCE ---------------------------------------------------------------------------
+// loss = mean(softplus(l) - y*l) ; dlogit = (sigmoid(l) - y) * scale ; pred = sigmoid(l)
+// sums[0] += loss_sum/B, sums[1] += sum(y), sums[2] += sum(pred), sums[3] += B
+__global__ void bce_kernel(const float* __restrict__ logit, const float* __restrict__ label, int B, float* __restrict__ pred,
+                           float* __restrict__ dlogit, float grad_scale, float* __restrict__ sums) {
+  float ls = 0.f, ys = 0.f, ps = 0.f;
+  for (int b = blockIdx.x * blockDim.x + threadIdx.x; b < B; b += gridDim.x * blockDim.x) {
+    const float l = logit[b], y = label[b];
+    const float p = 1.f / (1.f + expf(-l));
+    const float sp = fmaxf(l, 0.f) + log1pf(expf(-fabsf(l)));
+    ls += sp - y * l;
+    ys += y;
+    ps += p;
+    if (pred) pred[b] = p;
+    if (dlogit) dlogit[b] = (p - y) * grad_scale;
+  }
+  ls = warp_sum(ls); ys = warp_sum(ys); ps = warp_sum(ps);
+  if ((threadIdx.x & 31) == 0) {
+    atomicAdd(&sums[0], ls / (float)B);
+    atomicAdd(&sums[1], ys);
+    atomicAdd(&sums[2], ps);
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&sums[3], (float)B);
+}
+
+// ---- DCN-v1 cross layer: y = x0 * (xl . w) + b + xl ---------------------------------------------
+__global__ void cross_v1_fwd_kernel(const float* __restrict__ x0, const float* __restrict__ xl, const float* __restrict__ w,
+                                    const float* __restrict__ bias, int B, int D, float* __restrict__ y, float* __restrict__ dot) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  for (int b = warp; b < B; b += nwarps) {
+    const float* a = x0 + (size_t)b * D; const float* c = xl + (size_t)b * D;
+    float s = 0.f;
+    for (int d = lane; d < D; d += 32) s += c[d] * w[d];
+    s = warp_sum(s);
+    if (lane == 0) dot[b] = s;
+    for (int d = lane; d < D; d += 32) y[(size_t)b * D + d] = a[d] * s + bias[d] + c[d];
+  }
+}
+// gx0 += gy * s ; gxl = gy + w * (gy . x0) ; gw += xl * (gy . x0) ; gb += gy
+__global__ void cross_v1_bwd_kernel(const float* __restrict__ x0, const float* __restrict__ xl, const float* __restrict__ w,
+                                    const float* __restrict__ dot, const float* __restrict__ gy, int B, int D,
+                                    float* __restrict__ gx0, float* __restrict__ gxl, float* __restrict__ gw, float* __restrict__ gb) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  for (int b = warp; b < B; b += nwarps) {
+    const float* a = x0 + (size_t)b * D; const float* c = xl + (size_t)b * D; const float* g = gy + (size_t)b * D;
+    float t = 0.f;
+    for (int d = lane; d < D; d += 32) t += g[d] * a[d];
+    t = warp_sum(t);
+    const float s = dot[b];
+    for (int d = lane; d < D; d += 32) {
+      gx0[(size_t)b * D + d] = g[d] * s;
+      gxl[(size_t)b * D + d] = g[d] + w[d] * t;
+      atomicAdd(gw + d, c[d] * t);
+      atomicAdd(gb + d, g[d]);
+    }
+  }
+}
+
+// g[i] = y[i] > 0 ? g[i] : 0   (bf16, 8 elements per thread)
+__global__ void relu_mask_kernel(uint4* __restrict__ g, const uint4* __restrict__ y, long long n8) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    uint4 gv = g[i]; const uint4 yv = y[i];
+    __nv_bfloat16* gp = reinterpret_cast<__nv_bfloat16*>(&gv);
+    const __nv_bfloat16* yp = reinterpret_cast<const __nv_bfloat16*>(&yv);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) if (!(__bfloat162float(yp[k]) > 0.f)) gp[k] = __float2bfloat16(0.f);
+    g[i] = gv;
+  }
+}
+
+inline int blocks_for(long long work, int per_block) {
+  long long b = (work + per_block - 1) / per_block;
+  if (b < 1) b = 1;
+  if (b > 148 * 8) b = 148 * 8;
+  return (int)b;
+}
+
+}  // namespace
+
+void launch_fm_fwd(const float* E, int ld, int B, int F, int D, float* out, cudaStream_t st) {
+  fm_fwd_kernel<<<blocks_for(B, 8), 256, 0, st>>>(E, ld, B, F, D, out);
+}
+void launch_fm_bwd(const float* E, int ld, int B, int F, int D, const float* gout, float* gE, int gld, int accumulate, cudaStream_t st) {
+  fm_bwd_kernel<<<blocks_for(B, 8), 256, 0, st>>>(E, ld, B, F, D, gout, gE, gld, accumulate);
+}
+void launch_concat_cast(const ConcatArgs& a, cudaStream_t st) {
+  concat_cast_kernel<<<blocks_for((long long)a.B * a.ld_out, 256), 256, 0, st>>>(a);
+}
+void launch_split_cast(const ConcatArgs& a, cudaStream_t st) {
+  split_cast_kernel<<<blocks_for((long long)a.B * a.ld_out, 256), 256, 0, st>>>(a);
+}
+void launch_gemv_fwd(const void* Z, int ld, int B, int K, const float* w, float* y, cudaStream_t st) {
+  gemv_fwd_kernel<<<blocks_for(B, 8), 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(Z), ld, B, K, w, y);
+}
+void launch_gemv_bwd(const void* Z, int ld, int B, int K, const float* w, const float* dy, void* dZ, float* gw, int relu_cols,
+                     cudaStream_t st) {
+  int blocks = B / 32; if (blocks < 1) blocks = 1; if (blocks > 296) blocks = 296;
+  gemv_bwd_kernel<<<blocks, 256, K * sizeof(float), st>>>(reinterpret_cast<const __nv_bfloat16*>(Z), ld, B, K, w, dy,
+                                                          reinterpret_cast<__nv_bfloat16*>(dZ), gw, relu_cols);
+}
+void launch_bce(const float* logit, const float* label, int B, float* pred, float* dlogit, float grad_scale, float* sums,
+                cudaStream_t st) {
+  bce_kernel<<<blocks_for(B, 256), 256, 0, st>>>(logit, label, B, pred, dlogit, grad_scale, sums);
+}
+void launch_relu_mask(void* g, const void* y, long long n, cudaStream_t st) {
+  relu_mask_kernel<<<blocks_for(n / 8, 256), 256, 0, st>>>(reinterpret_cast<uint4*>(g), reinterpret_cast<const uint4*>(y), n / 8);
+}
+void launch_cross_v1_fwd(const float* x0, const float* xl, const float* w, const float* bias, int B, int D, float* y, float* dot,
+                         cudaStream_t st) {
+  cross_v1_fwd_kernel<<<blocks_for(B, 8), 256, 0, st>>>(x0, xl, w, bias, B, D, y, dot);
+}
+void launch_cross_v1_bwd(const float* x0, const float* xl, const float* w, const float* dot, const float* gy, int B, int D,
+                         float* gx0, float* gxl, float* gw, float* gb, cudaStream_t st) {
+  cross_v1_bwd_kernel<<<blocks_for(B, 8), 256, 0, st>>>(x0, xl, w, dot, gy, B, D, gx0, gxl, gw, gb);
+}
+
+}  // namespace tn

@@ -1,0 +1,431 @@
+// bf16 GEMM family for the dense towers (MLP forward, dgrad, wgrad and the DCN-v2 cross
+// layers) written directly against the Blackwell tensor-core path:
+//   * operand tiles are fetched by TMA (cp.async.bulk.tensor, no multicast) into a
+//     128B-swizzled shared-memory ring guarded by mbarriers,
+//   * one elected thread issues tcgen05.mma (kind::f16, bf16 in / fp32 accumulate) with
+//     the accumulator tile living in tensor memory (TMEM),
+//   * four epilogue warps read the accumulator back with tcgen05.ld and apply the fused
+//     epilogue (bias, ReLU, ReLU-mask of the backward pass, "ones" bias column,
+//     Hadamard-residual of DCN-v2, fp32 accumulate with split-K reduction).
+// The reference runs these layers as Keras Dense / tf.matmul on CPU
+// (examples/models/deepfm.py:43-44, examples/common/layers.py:53-59).
+//
+// C[M,N] = sum_k A(m,k) * B(n,k).  Each operand may be stored contraction-major
+// ("K-major": [rows, k] row-major) or output-major ("MN-major": [k, rows] row-major), which
+// covers forward (K,K), dgrad (K,MN) and wgrad (MN,MN) without any transposed copies.
+//
+// Every mbarrier wait is bounded; on expiry the CTA records an error, lets its TMA copies
+// land, frees its TMEM columns and returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <cstdio>
+#include <mutex>
+#include <unordered_map>
+#include "gemm_tcgen05.h"
+#include "tn_device.cuh"
+
+namespace tn {
+
+namespace {
+
+constexpr int kBM = 128;        // tile rows (UMMA M)
+constexpr int kBK = 64;         // contraction elements per stage = one 128-byte swizzle row of bf16
+constexpr int kUmmaK = 16;
+constexpr int kABytes = kBM * kBK * 2;   // 16 KiB
+constexpr int kGemmThreads = 192;        // warp0 TMA, warp1 MMA + TMEM owner, warps 2..5 epilogue
+constexpr unsigned kWaitSpins = 20u * 1000u * 1000u;   // ~ a second with the nanosleep below
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait; false on expiry or when another role of this CTA already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* s_abort) {
+  for (unsigned spins = 0; spins < kWaitSpins; ++spins) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spins & 255u) == 255u && *s_abort) return false;
+    if (spins > 64) __nanosleep(40);
+  }
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle, sm_100 version field set.
+//   K-major : rows of 128 B, 8-row groups 1024 B apart (SBO); LBO unused.
+//   MN-major: 64-element chunks along MN are 128 B rows indexed by k; 8-k groups 1024 B apart
+//             (SBO); the next 64-wide MN chunk starts `lbo_bytes` further (LBO).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;   // descriptor version for sm_100
+  d |= (uint64_t)2 << 61;   // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int kStages>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t s_full[kStages];
+  __shared__ __align__(8) uint64_t s_empty[kStages];
+  __shared__ __align__(8) uint64_t s_accum;
+  __shared__ uint32_t s_tmem;
+  __shared__ int s_abort_i;
+  volatile int* s_abort = &s_abort_i;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int BN = p.BN;
+  const uint32_t b_bytes = (uint32_t)BN * kBK * 2;
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t a_smem = base;
+  const uint32_t b_smem = base + kStages * kABytes;
+
+  const int n0 = blockIdx.x * BN;
+  const int m0 = blockIdx.y * kBM;
+  const int kt_total = (p.K + kBK - 1) / kBK;
+  const int kt0 = blockIdx.z * p.k_tiles_per_split;
+  int nk = kt_total - kt0;
+  if (nk > p.k_tiles_per_split) nk = p.k_tiles_per_split;
+
+  uint32_t tmem_cols = 32;
+  while ((int)tmem_cols < BN) tmem_cols <<= 1;
+
+  if (threadIdx.x == 0) {
+    *s_abort = 0;
+    for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&s_full[s]), 1); mbar_init(smem_u32(&s_empty[s]), 1); }
+    mbar_init(smem_u32(&s_accum), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmA)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmB)) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s_tmem;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer ---------------------------------------
+    if (lane == 0) {
+      for (int i = 0; i < nk; ++i) {
+        const int s = i % kStages;
+        const uint32_t ph = (uint32_t)(i / kStages) & 1u;
+        if (!mbar_wait(smem_u32(&s_empty[s]), ph ^ 1u, s_abort)) { *s_abort = 1; break; }
+        const uint32_t full = smem_u32(&s_full[s]);
+        mbar_expect_tx(full, kABytes + b_bytes);
+        const int kc = (kt0 + i) * kBK;
+        const uint32_t a_dst = a_smem + s * kABytes;
+        const uint32_t b_dst = b_smem + s * b_bytes;
+        if (!p.a_mn) {
+          tma_load_2d(a_dst, &tmA, kc, m0, full);
+        } else {
+          tma_load_2d(a_dst, &tmA, m0, kc, full);
+          tma_load_2d(a_dst + 8192, &tmA, m0 + 64, kc, full);
+        }
+        if (!p.b_mn) {
+          tma_load_2d(b_dst, &tmB, kc, n0, full);
+        } else {
+          for (int c = 0; c < BN / 64; ++c) tma_load_2d(b_dst + c * 8192, &tmB, n0 + 64 * c, kc, full);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -----------------------------------------
+    if (lane == 0) {
+      // instruction descriptor: D=f32, A=B=bf16, majors, N>>3, M>>4
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.a_mn ? 1 : 0) << 15) |
+                             ((uint32_t)(p.b_mn ? 1 : 0) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+      const uint32_t a_lbo = p.a_mn ? 8192u : 16u, b_lbo = p.b_mn ? 8192u : 16u;
+      const uint32_t a_kstep = p.a_mn ? 2048u : 32u, b_kstep = p.b_mn ? 2048u : 32u;
+      bool ok = true;
+      for (int i = 0; i < nk && ok; ++i) {
+        const int s = i % kStages;
+        const uint32_t ph = (uint32_t)(i / kStages) & 1u;
+        if (!mbar_wait(smem_u32(&s_full[s]), ph, s_abort)) { *s_abort = 1; ok = false; break; }
+        tc_fence_after();
+        const uint32_t a_base = a_smem + s * kABytes;
+        const uint32_t b_base = b_smem + s * b_bytes;
+#pragma unroll
+        for (int k = 0; k < kBK / kUmmaK; ++k) {
+          const uint64_t ad = make_smem_desc(a_base + k * a_kstep, a_lbo, 1024u);
+          const uint64_t bd = make_smem_desc(b_base + k * b_kstep, b_lbo, 1024u);
+          umma_f16(tmem, ad, bd, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&s_empty[s]));   // frees the stage once the MMAs have read it
+      }
+      if (ok) umma_commit(smem_u32(&s_accum));
+    }
+  } else {
+    // ------------------------------- epilogue (warps 2..5) ------------------------------
+    const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    const int row = m0 + q * 32 + lane;
+    bool ok = nk > 0;
+    if (ok && !mbar_wait(smem_u32(&s_accum), 0u, s_abort)) { *s_abort = 1; ok = false; }
+    tc_fence_after();
+    if (ok) {
+      const int n_store = p.n_store;
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        const int nb = n0 + c0;
+        if (nb >= n_store) break;           // warp-uniform
+        uint32_t r[16];
+        tmem_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+        if (row >= p.M) continue;
+        float v[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+        if (p.bias) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) if (nb + j < p.N) v[j] += __ldg(p.bias + nb + j);
+        }
+        if (p.relu) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = fmaxf(v[j], 0.f);
+        }
+        if (p.mask_aux) {   // backward of ReLU: keep the gradient where the forward activation was positive
+          const __nv_bfloat16* mrow = p.mask_aux + (size_t)row * p.ld_aux + nb;
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (nb + j < n_store && !(__bfloat162float(mrow[j]) > 0.f)) v[j] = 0.f;
+        }
+        if (p.had_x0) {     // DCN-v2: x0 * (acc + bias) + xl
+          const __nv_bfloat16* x0 = p.had_x0 + (size_t)row * p.ld_aux + nb;
+          const __nv_bfloat16* xl = p.had_xl + (size_t)row * p.ld_aux + nb;
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (nb + j < p.N) v[j] = __bfloat162float(x0[j]) * v[j] + __bfloat162float(xl[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int n = nb + j;
+          if (n >= p.N) v[j] = (n == p.ones_col) ? 1.f : 0.f;
+        }
+        if (p.out_f32) {
+          float* crow = reinterpret_cast<float*>(p.C) + (size_t)row * p.ldc + nb;
+          if (nb + 16 <= n_store && p.accumulate) {
+#pragma unroll
+            for (int j = 0; j < 16; j += 4) red_add_f32x4(crow + j, make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]));
+          } else if (nb + 16 <= n_store) {
+#pragma unroll
+            for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(crow + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          } else {
+            for (int j = 0; j < 16 && nb + j < n_store; ++j) {
+              if (p.accumulate) atomicAdd(crow + j, v[j]); else crow[j] = v[j];
+            }
+          }
+        } else {
+          __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)row * p.ldc + nb;
+          if (nb + 16 <= n_store) {
+            uint4 lo = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+            uint4 hi = make_uint4(pack_bf16(v[8], v[9]), pack_bf16(v[10], v[11]), pack_bf16(v[12], v[13]), pack_bf16(v[14], v[15]));
+            *reinterpret_cast<uint4*>(crow) = lo;
+            *reinterpret_cast<uint4*>(crow + 8) = hi;
+          } else {
+            for (int j = 0; j < 16 && nb + j < n_store; ++j) crow[j] = __float2bfloat16(v[j]);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*s_abort) {
+    // a wait ran out: report, give copies in flight time to land, then release TMEM
+    if (threadIdx.x == 0) set_status(p.status, kMbarTimeout, 30, (int)blockIdx.x);
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// host side: tensor-map cache + launch
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr; long long rows, cols, ld; int box_rows;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    uint64_t h = mix64((uint64_t)k.ptr);
+    h = mix64(h ^ (uint64_t)k.rows * 0x9E3779B97F4A7C15ull);
+    h = mix64(h ^ (uint64_t)k.cols * 0xC2B2AE3D27D4EB4Full);
+    h = mix64(h ^ (uint64_t)k.ld ^ ((uint64_t)k.box_rows << 48));
+    return (size_t)h;
+  }
+};
+
+// 2-D bf16 row-major tensor [rows, cols] with leading dimension `ld` elements; box = 64 x box_rows.
+bool get_tensor_map(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out) {
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  static std::mutex mu;
+  MapKey key{ptr, rows, cols, ld, box_rows};
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *out = it->second; return true; }
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, m);
+  *out = m;
+  return true;
+}
+
+}  // namespace
+
+const char* gemm_bf16(const GemmDesc& d, cudaStream_t stream) {
+  if (d.M <= 0 || d.N <= 0 || d.K <= 0) return "gemm_bf16: empty problem";
+  if ((reinterpret_cast<uintptr_t>(d.A) & 15) || (reinterpret_cast<uintptr_t>(d.B) & 15)) return "gemm_bf16: operands must be 16-byte aligned";
+  if ((d.lda % 8) || (d.ldb % 8)) return "gemm_bf16: leading dimensions must be multiples of 8 elements";
+  if (d.out_f32 ? (d.ldc % 4) : (d.ldc % 8)) return "gemm_bf16: ldc alignment";
+  if (reinterpret_cast<uintptr_t>(d.C) & 15) return "gemm_bf16: C must be 16-byte aligned";
+
+  // tile N: multiple of 16 (64 when B is MN-major), chosen to keep the grid near one wave
+  int n_cover = d.n_store > d.N ? d.n_store : d.N;
+  int BN = d.BN;
+  if (BN <= 0) {
+    const int gran = d.b_mn ? 64 : 16;
+    const int m_tiles = (d.M + kBM - 1) / kBM;
+    int best = 0; double best_cost = 1e30;
+    for (int cand = gran; cand <= 256; cand += gran) {
+      int n_tiles = (n_cover + cand - 1) / cand;
+      long long ctas = (long long)m_tiles * n_tiles;
+      long long waves = (ctas + 147) / 148;
+      double cost = (double)waves * (cand + 48);   // per-tile time ~ BN plus fixed overhead
+      if (cost < best_cost - 1e-9) { best_cost = cost; best = cand; }
+    }
+    BN = best;
+  }
+  if (BN % 16 || BN < 16 || BN > 256 || (d.b_mn && BN % 64)) return "gemm_bf16: bad tile N";
+
+  const int kt_total = (d.K + kBK - 1) / kBK;
+  int splits = d.split_k > 0 ? d.split_k : 1;
+  if (splits > kt_total) splits = kt_total;
+  if (splits > 1 && !(d.out_f32 && d.accumulate)) return "gemm_bf16: split-K needs an fp32 accumulate epilogue";
+  int ktps = (kt_total + splits - 1) / splits;
+  splits = (kt_total + ktps - 1) / ktps;
+
+  CUtensorMap tmA, tmB;
+  bool ok;
+  if (!d.a_mn) ok = get_tensor_map(d.A, d.M, d.K, d.lda, kBM, &tmA);          // [M, K]
+  else         ok = get_tensor_map(d.A, d.K, d.M, d.lda, kBK, &tmA);          // [K, M]
+  if (!ok) return "gemm_bf16: cuTensorMapEncodeTiled failed for A";
+  if (!d.b_mn) ok = get_tensor_map(d.B, d.N, d.K, d.ldb, BN, &tmB);           // [N, K]
+  else         ok = get_tensor_map(d.B, d.K, d.N, d.ldb, kBK, &tmB);          // [K, N]
+  if (!ok) return "gemm_bf16: cuTensorMapEncodeTiled failed for B";
+
+  GemmParams p;
+  p.M = d.M; p.N = d.N; p.K = d.K; p.BN = BN; p.a_mn = d.a_mn; p.b_mn = d.b_mn; p.k_tiles_per_split = ktps;
+  p.C = d.C; p.ldc = d.ldc; p.out_f32 = d.out_f32; p.accumulate = d.accumulate; p.relu = d.relu;
+  p.mask_aux = reinterpret_cast<const __nv_bfloat16*>(d.mask_aux);
+  p.had_x0 = reinterpret_cast<const __nv_bfloat16*>(d.had_x0);
+  p.had_xl = reinterpret_cast<const __nv_bfloat16*>(d.had_xl);
+  p.ld_aux = d.ld_aux; p.ones_col = d.ones_col; p.n_store = n_cover; p.bias = d.bias; p.status = d.status;
+
+  dim3 grid((n_cover + BN - 1) / BN, (d.M + kBM - 1) / kBM, splits);
+  const size_t b_bytes = (size_t)BN * kBK * 2;
+  size_t smem4 = 4 * (kABytes + b_bytes) + 1024, smem3 = 3 * (kABytes + b_bytes) + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    attr_set = true;
+  }
+  if (smem4 <= 200 * 1024)
+    gemm_bf16_tcgen05_kernel<4><<<grid, kGemmThreads, smem4, stream>>>(tmA, tmB, p);
+  else
+    gemm_bf16_tcgen05_kernel<3><<<grid, kGemmThreads, smem3, stream>>>(tmA, tmB, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
+}
+
+}  // namespace tn

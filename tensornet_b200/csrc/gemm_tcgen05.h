@@ -1,0 +1,48 @@
+// Host interface of the tcgen05 bf16 GEMM family (gemm_tcgen05.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+
+namespace tn {
+
+// Problem description: C[M,N] (+)= epilogue( sum_k A(m,k) * B(n,k) ).
+struct GemmDesc {
+  int M = 0, N = 0, K = 0;
+  const void* A = nullptr;   // bf16.  a_mn == 0: [M, K] row-major (lda >= K);  a_mn == 1: [K, M] row-major (lda >= M)
+  const void* B = nullptr;   // bf16.  b_mn == 0: [N, K] row-major (ldb >= K);  b_mn == 1: [K, N] row-major (ldb >= N)
+  int lda = 0, ldb = 0;
+  int a_mn = 0, b_mn = 0;
+  void* C = nullptr;         // bf16 or fp32 [M, ldc]
+  int ldc = 0;
+  int out_f32 = 0;
+  int accumulate = 0;        // fp32 only: C += result (atomic vector adds, required for split_k > 1)
+  int relu = 0;
+  const float* bias = nullptr;      // optional fp32 [N], added before ReLU
+  const void* mask_aux = nullptr;   // optional bf16 [M, ld_aux]: result is zeroed where mask_aux <= 0
+  const void* had_x0 = nullptr;     // optional bf16 [M, ld_aux]: result = had_x0 * result + had_xl
+  const void* had_xl = nullptr;
+  int ld_aux = 0;
+  int ones_col = -1;         // column (>= N) that is written as 1.0: the bias input of the next layer
+  int n_store = 0;           // columns written per row (>= N; columns past N get 0, or 1 at ones_col)
+  int split_k = 1;
+  int BN = 0;                // tile N override (0 = choose)
+  int* status = nullptr;     // device error words
+};
+
+// Kernel-side parameter block.
+struct GemmParams {
+  int M, N, K, BN, a_mn, b_mn, k_tiles_per_split;
+  void* C;
+  int ldc, out_f32, accumulate, relu;
+  const __nv_bfloat16* mask_aux;
+  const __nv_bfloat16* had_x0;
+  const __nv_bfloat16* had_xl;
+  int ld_aux, ones_col, n_store;
+  const float* bias;
+  int* status;
+};
+
+// Returns nullptr on success, otherwise a static error string.
+const char* gemm_bf16(const GemmDesc& d, cudaStream_t stream);
+
+}  // namespace tn

@@ -1,0 +1,525 @@
+// Fused sparse pull and push: the per-batch id dedup / virtual-index assignment, the
+// all-to-all exchange with the owning GPUs over NVLink peer memory, the owner-side hash
+// probe (insert on miss) and the optimizer update each run as ONE persistent cooperative
+// kernel per direction.  Peer traffic is plain ld/st to symmetric-heap addresses with
+// release/acquire flags at system scope; no collective library is involved.
+//
+// What these kernels replace in the reference:
+//   pull : SparsePullVarInfo dedup + per-shard RPC fan-out + SparseTable::Pull + scatter back
+//          (core/kernels/sparse_table_ops.cc:113-270, core/ps/table/sparse_table.cc:52-66)
+//   push : SparsePushVarInfo show/click counting + per-shard RPC + SparseTable::Push + Value::Apply
+//          (core/kernels/sparse_table_ops.cc:274-373, core/ps/table/sparse_table.cc:68-83,
+//           core/ps/optimizer/{ada_grad,adam,ftrl}_kernel.cc)
+//
+// Semantics that differ on purpose: the step is synchronous, and gradients of one sign
+// arriving from several GPUs (or several columns) are summed and applied once.
+#include "sparse_table.cuh"
+
+namespace tn {
+
+namespace {
+
+constexpr int kThreads = 256;
+enum SigKind { kSigPullReq = 0, kSigPullDone = 1, kSigPushReq = 2 };
+__device__ __forceinline__ unsigned long long* sig_word(unsigned long long* base, int kind, int src) {
+  return base + kind * kMaxWorld + src;
+}
+
+__device__ __forceinline__ unsigned group_mask(int G) {
+  if (G >= 32) return 0xffffffffu;
+  unsigned lane = threadIdx.x & 31;
+  return ((1u << G) - 1u) << (lane & ~(unsigned)(G - 1));
+}
+
+// Default value of stored-row element `e` (e < stride) for a brand-new row.
+__device__ __forceinline__ float new_row_elem(const SparseOptParams& o, unsigned long long key, int e, int dim) {
+  if (e < dim) return o.zero_init ? 0.f : init_weight(o.seed, key, e, dim, o.initial_scale);
+  if (o.kind == kAdaGrad && e == dim) return o.initial_g2sum;
+  return 0.f;  // slots, show, click; int fields are bit-zero
+}
+
+// Claim (or read) this step's owner-unique index of an existing row.
+__device__ __forceinline__ int claim_ou(const SparseCommView& c, unsigned long long* tag, int r, unsigned long long epoch,
+                                        bool* is_new_this_step) {
+  unsigned long long t = *((volatile unsigned long long*)tag);
+  *is_new_this_step = false;
+  if ((t >> 32) == epoch) {
+    *is_new_this_step = (t & kTagNew) != 0;
+    return (int)(t & 0x7fffffffull);
+  }
+  int ou = atomicAdd(c.ocount, 1);
+  unsigned long long old = atomicCAS(tag, t, (epoch << 32) | (unsigned long long)ou);
+  if (old == t) {
+    c.ou_row[ou] = r;
+    return ou;
+  }
+  c.ou_row[ou] = -1;  // hole: someone else claimed the row first
+  return (int)(old & 0x7fffffffull);
+}
+
+}  // namespace
+
+// =======================================================================================
+// sparse_pull_fused
+// =======================================================================================
+__global__ void __launch_bounds__(kThreads) sparse_pull_fused_kernel(const __grid_constant__ PullArgs a) {
+  const SparseCommView& c = a.c;
+  const TableView& t = a.tbl;
+  GridSync gs;
+  gs.init(c.bar, c.status, c.wait_ns);
+  __shared__ unsigned long long s_flag;
+  __shared__ int s_n[kMaxWorld];
+
+  const int tid = blockIdx.x * blockDim.x + threadIdx.x;
+  const int nth = gridDim.x * blockDim.x;
+  const int W = c.world, R = c.rank, capo = c.capo;
+  const unsigned long long epoch = __ldcg(c.epoch) + 1ull;
+  const int dim = t.dim;
+
+  if (tid == 0) *c.ocount = 0;
+  const bool need_ou = a.training && W > 1;
+
+  // ---- phase A: dedup; first occurrence of a sign allocates a slot in its owner's segment --------
+  for (int i = tid; i < a.n_ids; i += nth) {
+    unsigned long long key = canon_key((unsigned long long)a.ids[i]);
+    unsigned h = (unsigned)mix64(key ^ 0x2545F4914F6CDD1Dull) & c.dd_mask;
+    bool done = false;
+    for (unsigned probes = 0; probes <= c.dd_mask; ++probes) {
+      unsigned long long old = atomicCAS(&c.dd_keys[h], kEmptyKey, key);
+      if (old == kEmptyKey) {
+        int owner = owner_of(key, W);
+        int pos = atomicAdd(&c.cnt[owner], 1);
+        if (pos >= capo) {
+          set_status(c.status, kOwnerSegOverflow, 1, owner);
+          c.dd_vals[h] = -1;
+        } else {
+          c.stage_ids[owner * capo + pos] = key;
+          c.dd_vals[h] = owner * capo + pos;
+        }
+        done = true;
+        break;
+      }
+      if (old == key) { done = true; break; }
+      h = (h + 1) & c.dd_mask;
+    }
+    if (!done) set_status(c.status, kDedupOverflow, 1, 0);
+  }
+  if (!gs.sync(1, false)) goto done;
+
+  // ---- phase A2: inverse map, show/click counts; ship id segments to the owners -------------------
+  for (int i = tid; i < a.n_ids; i += nth) {
+    unsigned long long key = canon_key((unsigned long long)a.ids[i]);
+    unsigned h = (unsigned)mix64(key ^ 0x2545F4914F6CDD1Dull) & c.dd_mask;
+    int v = -1;
+    for (unsigned probes = 0; probes <= c.dd_mask; ++probes) {
+      unsigned long long k = __ldcg(&c.dd_keys[h]);
+      if (k == key) { v = __ldcg(&c.dd_vals[h]); break; }
+      if (k == kEmptyKey) break;
+      h = (h + 1) & c.dd_mask;
+    }
+    a.inverse[i] = v;
+    if (a.training && v >= 0) {
+      float* rec = c.gU + (size_t)v * c.gstride + dim;
+      atomicAdd(rec, 1.0f);
+      if (a.labels != nullptr) {
+        float y = a.label_mod > 0 ? a.labels[i % a.label_mod] : a.labels[i];
+        if (y != 0.f) atomicAdd(rec + 1, y);
+      }
+    }
+  }
+  if (W > 1) {
+    // coalesced 16-byte peer stores of each owner's id segment
+    for (int p = 0; p < W; ++p) {
+      if (p == R) continue;
+      int n = __ldcg(&c.cnt[p]);
+      if (n > capo) n = capo;
+      const ulonglong2* src = reinterpret_cast<const ulonglong2*>(c.stage_ids + (size_t)p * capo);
+      ulonglong2* dst = reinterpret_cast<ulonglong2*>(c.inbox_ids[p] + (size_t)R * capo);
+      int n2 = (n + 1) >> 1;
+      for (int j = tid; j < n2; j += nth) dst[j] = __ldcg(&src[j]);
+    }
+    if (!gs.sync(2, true)) goto done;
+    if (blockIdx.x == 0 && threadIdx.x < W && threadIdx.x != R) {
+      int p = threadIdx.x;
+      int n = min(__ldcg(&c.cnt[p]), capo);
+      st_release_sys_u64(sig_word(c.sig[p], kSigPullReq, R), (epoch << 32) | (unsigned long long)n);
+    }
+  }
+
+  // ---- phase B1: as owner, probe / insert every requested sign ------------------------------------
+  for (int si = 0; si < W; ++si) {
+    const int s = (R + si) % W;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      unsigned long long v = 0;
+      if (s == R) {
+        v = (unsigned long long)min(__ldcg(&c.cnt[R]), capo);
+      } else if (!wait_flag_ge(sig_word(c.sig[R], kSigPullReq, s), epoch, &v, c.wait_ns, c.status, 3, s)) {
+        v = ~0ull;
+      }
+      s_flag = v;
+    }
+    __syncthreads();
+    if (s_flag == ~0ull) { gs.failed = true; break; }
+    const int n_s = (int)(s_flag & 0xffffffffull);
+    if (threadIdx.x == 0) s_n[s] = n_s;
+    if (tid == 0) c.req_n[s] = n_s;
+    const unsigned long long* src = (s == R) ? c.stage_ids + (size_t)R * capo : c.inbox_ids[R] + (size_t)s * capo;
+    for (int j = tid; j < n_s; j += nth) {
+      const unsigned long long key = __ldcg(&src[j]);
+      const int q = s * capo + j;
+      unsigned h = table_home(t, key);
+      int rr = kReqNone, ou = -1;
+      bool placed = false;
+      for (unsigned probes = 0; probes <= t.cap_mask && !placed; ++probes) {
+        unsigned long long k = __ldcg(&t.keys[h]);
+        if (k == kEmptyKey) {
+          k = atomicCAS(&t.keys[h], kEmptyKey, key);
+          if (k == kEmptyKey) {  // this thread owns the new key
+            int r = atomicAdd(t.n_rows, 1);
+            if (r >= t.row_cap) {
+              atomicSub(t.n_rows, 1);
+              set_status(c.status, kTableFull, 3, s);
+              t.slots[h] = -3;
+            } else {
+              t.row_keys[r] = key;
+              unsigned long long tag = (epoch << 32) | kTagNew;
+              if (need_ou) {
+                ou = atomicAdd(c.ocount, 1);
+                c.ou_row[ou] = r;
+                tag |= (unsigned long long)ou;
+              }
+              t.row_tag[r] = tag;
+              __threadfence();
+              *((volatile int*)&t.slots[h]) = r;
+              rr = r | kReqNewOwner;
+            }
+            placed = true;
+            break;
+          }
+        }
+        if (k == key) {
+          int r = ld_volatile_s32(&t.slots[h]);
+          if (r == -1) {          // inserter has not published the row yet: resolve after the barrier
+            rr = kReqPending;
+            ou = (int)h;
+          } else if (r >= 0) {
+            bool fresh = false;
+            if (need_ou) {
+              ou = claim_ou(c, &t.row_tag[r], r, epoch, &fresh);
+            } else if (W > 1) {
+              unsigned long long tg = *((volatile unsigned long long*)&t.row_tag[r]);
+              fresh = (tg >> 32) == epoch && (tg & kTagNew);
+            }
+            rr = fresh ? (r | kReqNewCopy) : r;
+          }
+          placed = true;
+          break;
+        }
+        h = (h + 1) & t.cap_mask;
+      }
+      if (!placed) set_status(c.status, kTableFull, 3, s);
+      c.req_row[q] = rr;
+      c.req_ou[q] = ou;
+    }
+  }
+  if (gs.failed) goto done;
+  if (!gs.sync(4, false)) goto done;
+
+  if (blockIdx.x == 0 && threadIdx.x < W) {  // counts of this step for pooling / push, then re-arm
+    c.cnt_saved[threadIdx.x] = min(c.cnt[threadIdx.x], capo);
+    c.cnt[threadIdx.x] = 0;
+  }
+
+  // ---- phase B2: initialise new rows, write rows straight into each requester's matrix -----------
+  {
+    const int G = a.lanes;
+    const int lane = threadIdx.x % G;
+    const int gid = tid / G, ngroups = nth / G;
+    const int ustride = c.ustride, stride = t.stride;
+    const int uchunks = ustride >> 2, rchunks = stride >> 2;
+    const SparseOptParams& o = a.opt;
+    for (int s = 0; s < W; ++s) {
+      const int n_s = s_n[s];
+      const unsigned long long* src = (s == R) ? c.stage_ids + (size_t)R * capo : c.inbox_ids[R] + (size_t)s * capo;
+      float* dst_base = c.U[s] + (size_t)R * capo * ustride;
+      for (int j = gid; j < n_s; j += ngroups) {
+        const int q = s * capo + j;
+        int rr = __ldcg(&c.req_row[q]);
+        float* dst = dst_base + (size_t)j * ustride;
+        if (rr == kReqPending) {
+          int h = __ldcg(&c.req_ou[q]);
+          int r = ld_volatile_s32(&t.slots[h]);
+          if (r >= 0) {
+            unsigned long long tg = __ldcg(&t.row_tag[r]);
+            bool fresh = (tg >> 32) == epoch && (tg & kTagNew);
+            rr = fresh ? (r | kReqNewCopy) : r;
+            if (lane == 0) {
+              c.req_row[q] = rr;
+              c.req_ou[q] = need_ou ? (int)(tg & 0x7fffffffull) : -1;
+            }
+          } else {
+            rr = kReqNone;
+            if (lane == 0) { c.req_row[q] = kReqNone; c.req_ou[q] = -1; }
+          }
+        }
+        if (rr == kReqNone) {
+          for (int ch = lane; ch < uchunks; ch += G)
+            *reinterpret_cast<float4*>(dst + 4 * ch) = make_float4(0.f, 0.f, 0.f, 0.f);
+          continue;
+        }
+        const int r = rr & kReqRowMask;
+        float* row = t.rows + (size_t)r * stride;
+        if (rr & (kReqNewOwner | kReqNewCopy)) {
+          const unsigned long long key = __ldcg(&src[j]);
+          const bool write_row = (rr & kReqNewOwner) != 0;
+          const int nch = write_row ? max(rchunks, uchunks) : uchunks;
+          for (int ch = lane; ch < nch; ch += G) {
+            float4 v;
+            v.x = new_row_elem(o, key, 4 * ch + 0, dim);
+            v.y = new_row_elem(o, key, 4 * ch + 1, dim);
+            v.z = new_row_elem(o, key, 4 * ch + 2, dim);
+            v.w = new_row_elem(o, key, 4 * ch + 3, dim);
+            if (write_row && ch < rchunks) *reinterpret_cast<float4*>(row + 4 * ch) = v;
+            if (ch < uchunks) {
+              // pulled row = w[dim] (+ two zero CVM columns for a new row), zero padding
+              float4 u;
+              u.x = 4 * ch + 0 < dim ? v.x : 0.f;
+              u.y = 4 * ch + 1 < dim ? v.y : 0.f;
+              u.z = 4 * ch + 2 < dim ? v.z : 0.f;
+              u.w = 4 * ch + 3 < dim ? v.w : 0.f;
+              *reinterpret_cast<float4*>(dst + 4 * ch) = u;
+            }
+          }
+        } else {
+          float show = 0.f, click = 0.f;
+          if (t.use_cvm && o.kind == kAdaGrad) { show = row[dim + 1]; click = row[dim + 2]; }
+          for (int ch = lane; ch < uchunks; ch += G) {
+            float4 v = *reinterpret_cast<const float4*>(row + 4 * ch);  // stride >= ustride - 2 is guaranteed by layout
+            float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              int idx = 4 * ch + k;
+              if (idx >= dim) {
+                float x = 0.f;
+                if (t.use_cvm && o.kind == kAdaGrad) {
+                  if (idx == dim) x = show;
+                  else if (idx == dim + 1) x = logf(click + 1.f) - logf(show + 1.f);
+                }
+                e[k] = x;
+              }
+            }
+            *reinterpret_cast<float4*>(dst + 4 * ch) = make_float4(e[0], e[1], e[2], e[3]);
+          }
+        }
+      }
+    }
+  }
+
+  if (W > 1) {
+    if (!gs.sync(5, true)) goto done;
+    if (blockIdx.x == 0 && threadIdx.x < W && threadIdx.x != R)
+      st_release_sys_u64(sig_word(c.sig[threadIdx.x], kSigPullDone, R), epoch << 32);
+  } else {
+    if (!gs.sync(5, false)) goto done;
+  }
+
+  // ---- phase C: clear the dedup scratch while the owners' rows arrive ----------------------------
+  {
+    ulonglong2* kk = reinterpret_cast<ulonglong2*>(c.dd_keys);
+    const int n2 = (int)((c.dd_mask + 1u) >> 1);
+    for (int i = tid; i < n2; i += nth) kk[i] = make_ulonglong2(kEmptyKey, kEmptyKey);
+  }
+  if (W > 1 && blockIdx.x == 0 && threadIdx.x < W && threadIdx.x != R) {
+    unsigned long long v;
+    wait_flag_ge(sig_word(c.sig[R], kSigPullDone, threadIdx.x), epoch, &v, c.wait_ns, c.status, 6, threadIdx.x);
+  }
+  __syncthreads();
+  if (tid == 0) *c.epoch = epoch;
+
+done:
+  gs.leave();
+}
+
+// =======================================================================================
+// sparse_push_fused
+// =======================================================================================
+namespace {
+
+// One optimizer step on one row by a group of G lanes.  `g` points at the gradient record:
+// grad[dim] | show | click.   Math as in the reference's Sparse*Value::Apply.
+__device__ __forceinline__ void apply_row(const SparseOptParams& o, float* row, const float* g, int dim, int lane, int G,
+                                          unsigned gmask) {
+  const float bshow = g[dim], bclick = g[dim + 1];
+  if (o.kind == kAdaGrad) {
+    float ss = 0.f;
+    for (int e = lane; e < dim; e += G) { float x = g[e]; ss += x * x; }
+    for (int off = G >> 1; off > 0; off >>= 1) ss += __shfl_xor_sync(gmask, ss, off);
+    float g2 = row[dim] + ss / (float)dim;
+    float scale = o.lr / (o.eps + sqrtf(g2));
+    for (int e = lane; e < dim; e += G) row[e] -= scale * g[e];
+    __syncwarp(gmask);
+    if (lane == 0) {
+      row[dim] = g2;
+      row[dim + 1] += bshow;
+      row[dim + 2] += bclick;
+      reinterpret_cast<int*>(row)[dim + 3] = 0;
+    }
+  } else if (o.kind == kAdam) {
+    float* m = row + dim;
+    float* v = row + 2 * dim;
+    for (int e = lane; e < dim; e += G) {
+      float x = g[e];
+      float mm = o.beta1 * m[e] + (1.f - o.beta1) * x;
+      float vv = o.beta2 * v[e] + (1.f - o.beta2) * x * x;
+      m[e] = mm; v[e] = vv;
+      row[e] -= o.lr * mm / (o.eps + sqrtf(vv));
+    }
+    if (lane == 0) reinterpret_cast<int*>(row)[3 * dim + 1] += (int)bshow;
+  } else {
+    float* z = row + dim;
+    float* n = row + 2 * dim;
+    for (int e = lane; e < dim; e += G) {
+      float x = g[e], w = row[e], nn = n[e];
+      float g2 = x * x;
+      float zz = z[e] + x - o.lr * (sqrtf(nn + g2) - sqrtf(nn)) * w;
+      nn += g2;
+      float nw = 0.f;
+      if (fabsf(zz) > o.lambda1) {
+        nw = -1.f / ((o.ftrl_beta + sqrtf(nn)) * o.lr + o.lambda2);
+        nw *= zz > 0.f ? zz - o.lambda1 : zz + o.lambda1;
+      }
+      z[e] = zz; n[e] = nn; row[e] = nw;
+    }
+    if (lane == 0) reinterpret_cast<int*>(row)[3 * dim + 1] += (int)bshow;
+  }
+}
+
+}  // namespace
+
+__global__ void __launch_bounds__(kThreads) sparse_push_fused_kernel(const __grid_constant__ PushArgs a) {
+  const SparseCommView& c = a.c;
+  const TableView& t = a.tbl;
+  GridSync gs;
+  gs.init(c.bar, c.status, c.wait_ns);
+  __shared__ unsigned long long s_flag;
+
+  const int tid = blockIdx.x * blockDim.x + threadIdx.x;
+  const int nth = gridDim.x * blockDim.x;
+  const int W = c.world, R = c.rank, capo = c.capo;
+  const unsigned long long epoch = __ldcg(c.epoch);
+  const int dim = t.dim, gstride = c.gstride, gch = gstride >> 2;
+  const int G = a.lanes;
+  const int lane = threadIdx.x % G;
+  const int gid = tid / G, ngroups = nth / G;
+  const unsigned gmask = group_mask(G);
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+
+  if (W == 1) {
+    // single GPU: every unique sign of the batch maps to exactly one row; update in place
+    const int n = __ldcg(&c.cnt_saved[0]);
+    for (int j = gid; j < n; j += ngroups) {
+      int rr = __ldcg(&c.req_row[j]);
+      float* g = c.gU + (size_t)j * gstride;
+      if (rr != kReqNone && rr != kReqPending)
+        apply_row(a.opt, t.rows + (size_t)(rr & kReqRowMask) * t.stride, g, dim, lane, G, gmask);
+      __syncwarp(gmask);
+      for (int ch = lane; ch < gch; ch += G) *reinterpret_cast<float4*>(g + 4 * ch) = zero4;
+    }
+    goto done;
+  }
+
+  // ---- phase A: ship gradient records (grad | show | click) to the owners, re-zero local rows ------
+  for (int p = 0; p < W; ++p) {
+    const int n = __ldcg(&c.cnt_saved[p]);
+    float* src = c.gU + (size_t)p * capo * gstride;
+    float* dst = c.ginbox[p] + (size_t)R * capo * gstride;
+    const int total = n * gch;
+    for (int i = tid; i < total; i += nth) {
+      float4 v = *reinterpret_cast<const float4*>(src + 4 * (size_t)i);
+      *reinterpret_cast<float4*>(dst + 4 * (size_t)i) = v;
+      *reinterpret_cast<float4*>(src + 4 * (size_t)i) = zero4;
+    }
+  }
+  if (!gs.sync(11, true)) goto done;
+  if (blockIdx.x == 0 && threadIdx.x < W && threadIdx.x != R)
+    st_release_sys_u64(sig_word(c.sig[threadIdx.x], kSigPushReq, R), epoch << 32);
+
+  // ---- phase B: as owner, sum records of equal sign coming from different GPUs --------------------
+  for (int si = 0; si < W; ++si) {
+    const int s = (R + si) % W;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      unsigned long long v = 0;
+      if (s != R && !wait_flag_ge(sig_word(c.sig[R], kSigPushReq, s), epoch, &v, c.wait_ns, c.status, 12, s)) v = ~0ull;
+      s_flag = v;
+    }
+    __syncthreads();
+    if (s_flag == ~0ull) { gs.failed = true; break; }
+    const int n_s = __ldcg(&c.req_n[s]);
+    const float* src = c.ginbox[R] + (size_t)s * capo * gstride;
+    const int total = n_s * gch;
+    for (int i = tid; i < total; i += nth) {
+      const int j = i / gch, ch = i - j * gch;
+      const int ou = __ldcg(&c.req_ou[s * capo + j]);
+      if (ou < 0) continue;
+      float4 v = ldcg_f4(src + 4 * (size_t)i);
+      red_add_f32x4(c.acc + (size_t)ou * gstride + 4 * ch, v);
+    }
+  }
+  if (gs.failed) goto done;
+  if (!gs.sync(13, false)) goto done;
+
+  // ---- phase C: one optimizer update per touched row ----------------------------------------------
+  {
+    const int n_ou = __ldcg(c.ocount);
+    for (int ou = gid; ou < n_ou; ou += ngroups) {
+      const int r = __ldcg(&c.ou_row[ou]);
+      float* g = c.acc + (size_t)ou * gstride;
+      if (r >= 0) apply_row(a.opt, t.rows + (size_t)r * t.stride, g, dim, lane, G, gmask);
+      __syncwarp(gmask);
+      for (int ch = lane; ch < gch; ch += G) *reinterpret_cast<float4*>(g + 4 * ch) = zero4;
+    }
+  }
+
+done:
+  gs.leave();
+}
+
+// =======================================================================================
+// host launchers
+// =======================================================================================
+static int coop_grid(const void* fn, int device) {
+  int per_sm = 0, sms = 0;
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kThreads, 0);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  if (per_sm < 1) per_sm = 1;
+  if (per_sm > 2) per_sm = 2;
+  return per_sm * sms;
+}
+
+cudaError_t launch_sparse_pull(const PullArgs& args, int work_items, cudaStream_t stream) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  static int grid_max[64] = {0};
+  if (grid_max[dev] == 0) grid_max[dev] = coop_grid((const void*)sparse_pull_fused_kernel, dev);
+  int grid = (work_items + kThreads - 1) / kThreads;
+  if (grid < 1) grid = 1;
+  if (grid > grid_max[dev]) grid = grid_max[dev];
+  void* params[] = {(void*)&args};
+  return cudaLaunchCooperativeKernel((const void*)sparse_pull_fused_kernel, dim3(grid), dim3(kThreads), params, 0, stream);
+}
+
+cudaError_t launch_sparse_push(const PushArgs& args, int work_items, cudaStream_t stream) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  static int grid_max[64] = {0};
+  if (grid_max[dev] == 0) grid_max[dev] = coop_grid((const void*)sparse_push_fused_kernel, dev);
+  int grid = (work_items + kThreads - 1) / kThreads;
+  if (grid < 1) grid = 1;
+  if (grid > grid_max[dev]) grid = grid_max[dev];
+  void* params[] = {(void*)&args};
+  return cudaLaunchCooperativeKernel((const void*)sparse_push_fused_kernel, dim3(grid), dim3(kThreads), params, 0, stream);
+}
+
+}  // namespace tn

@@ -1,0 +1,52 @@
+// Host-callable launchers of the non-fused kernels.  All take raw device pointers and a
+// stream so the translation units that define them do not need the PyTorch headers.
+#pragma once
+#include <cuda_runtime.h>
+#include "tn_types.h"
+
+namespace tn {
+
+// pooling.cu
+void launch_pool_fwd(const float* U, int ustride, const int* inverse, const int* offsets, int B, int S, int pd,
+                     int combiner, float* out, int out_ld, cudaStream_t st);
+void launch_pool_bwd(float* gU, int gstride, const int* inverse, const int* offsets, int B, int S, int pd, int dim,
+                     int combiner, const float* gout, int gout_ld, cudaStream_t st);
+void launch_seq_fwd(const float* U, int ustride, const int* inverse, const int* offsets, int B, int T, int pd,
+                    float* out, int* lengths, cudaStream_t st);
+void launch_seq_bwd(float* gU, int gstride, const int* inverse, const int* offsets, int B, int T, int pd, int dim,
+                    const float* gout, cudaStream_t st);
+
+// table_ops.cu
+void launch_table_insert_keys(const TableView& t, const long long* keys, int n, int* out_rows, int* status, cudaStream_t st);
+void launch_table_lookup(const TableView& t, const long long* keys, int n, int* out_rows, cudaStream_t st);
+void launch_table_decay(const TableView& t, int kind, float rate, int delta_days, cudaStream_t st);
+
+// elementwise.cu
+constexpr int kMaxPieces = 6;
+struct ConcatArgs {
+  int B;
+  int n_pieces;
+  const void* ptr[kMaxPieces];   // piece p: [B, width[p]] with row stride ld[p], fp32 or bf16
+  int width[kMaxPieces];
+  int ld[kMaxPieces];
+  int is_bf16[kMaxPieces];
+  void* out;                     // bf16 [B, ld_out]; columns past the pieces are 0, ones_col is 1
+  int ld_out;
+  int ones_col;                  // -1 for none
+};
+void launch_fm_fwd(const float* E, int ld, int B, int F, int D, float* out, cudaStream_t st);
+void launch_fm_bwd(const float* E, int ld, int B, int F, int D, const float* gout, float* gE, int gld, int accumulate, cudaStream_t st);
+void launch_concat_cast(const ConcatArgs& a, cudaStream_t st);
+void launch_split_cast(const ConcatArgs& a, cudaStream_t st);
+void launch_gemv_fwd(const void* Z, int ld, int B, int K, const float* w, float* y, cudaStream_t st);
+void launch_gemv_bwd(const void* Z, int ld, int B, int K, const float* w, const float* dy, void* dZ, float* gw, int relu_cols,
+                     cudaStream_t st);
+void launch_bce(const float* logit, const float* label, int B, float* pred, float* dlogit, float grad_scale, float* sums,
+                cudaStream_t st);
+void launch_cross_v1_fwd(const float* x0, const float* xl, const float* w, const float* bias, int B, int D, float* y, float* dot,
+                         cudaStream_t st);
+void launch_cross_v1_bwd(const float* x0, const float* xl, const float* w, const float* dot, const float* gy, int B, int D,
+                         float* gx0, float* gxl, float* gw, float* gb, cudaStream_t st);
+void launch_relu_mask(void* g, const void* y, long long n, cudaStream_t st);
+
+}  // namespace tn

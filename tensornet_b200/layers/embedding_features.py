@@ -1,0 +1,104 @@
+"""``tn.layers.EmbeddingFeatures``: the first layer of every model.
+
+Creates one sparse table for the layer (or shares one through ``embedding_share``), and on
+every call dedups the batch's signs, pulls their rows from the owning shards into the small
+per-batch matrix and pools them per example - the reference's EmbeddingFeatures /
+StateManagerImpl (tensornet/layers/embedding_features.py:36-177,180-406).  ``backwards()``
+pushes the gradient of that per-batch matrix to the owners, where the sparse optimizer runs.
+
+With ``target_columns`` the table counts show / click per sign and every embedding gets two
+extra, gradient-free columns ``show`` and ``ln(click+1) - ln(show+1)`` (the CVM plug-in,
+embedding_features.py:288-295, core/ps/optimizer/ada_grad_kernel.cc:121-128).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+from torch import nn
+
+from .. import core
+from ..data.features import gather_columns
+from ..feature_column import EmbeddingColumn
+from ..ops.embedding import pull_pool
+
+
+class EmbeddingFeatures(nn.Module):
+    def __init__(self, feature_columns: Sequence[EmbeddingColumn], sparse_opt, trainable: bool = True,
+                 name: Optional[str] = None, is_concat: bool = False, target_columns: Optional[Sequence[str]] = None,
+                 embedding_share: Optional[str] = None, rows: Optional[int] = None):
+        super().__init__()
+        assert len(feature_columns) != 0, "feature_columns must not empty"
+        dim = feature_columns[0].dimension
+        combiner = feature_columns[0].combiner
+        for c in feature_columns:
+            if not isinstance(c, EmbeddingColumn):
+                raise ValueError(f"Items of feature_columns must be a {EmbeddingColumn}. Given: {c}")
+            assert c.dimension == dim, "currently we only support feature_columns with same dimension in EmbeddingFeatures"
+            assert c.combiner == combiner, "all columns of one EmbeddingFeatures layer must use the same combiner"
+        if target_columns and len(target_columns) > 1:
+            raise ValueError(f"For now cvm plugin only support one column, Given: {target_columns}")
+        self.layer_name = name or ""
+        self.trainable = trainable
+        self.is_concat = is_concat
+        self._sparse_opt = sparse_opt
+        self._feature_columns = list(feature_columns)
+        self._target_columns = list(target_columns) if target_columns else None
+        self._keys = [c.categorical_column.name for c in feature_columns]
+        self.dim = dim
+        self.combiner = combiner
+        self.use_cvm = bool(target_columns)
+        self.embedding_share = embedding_share
+        self.sparse_table_handle = core.create_sparse_table(sparse_opt, self.layer_name, dim, self.use_cvm,
+                                                            embedding_share or "", rows=rows)
+        self.table = core.sparse_table(self.sparse_table_handle)
+        max_unique = sum(c.categorical_column.bucket_size for c in feature_columns)
+        self.link = self.table.link(max_unique)
+        self.out_dim = dim + (2 if self.use_cvm else 0)
+        self._anchor = torch.zeros(1, requires_grad=True, device=core.runtime().device)
+        self._pending_push = False
+
+    # --------------------------------------------------------------------------------
+    @property
+    def feature_columns(self):
+        return self._feature_columns
+
+    def forward(self, features: Dict, training: Optional[bool] = None):
+        if not isinstance(features, dict):
+            raise ValueError("We expected a dictionary here. Instead we got: ", features)
+        training = self.training if training is None else bool(training)
+        dev = core.runtime().device
+        self.table.set_training(training)
+        ids, offsets, B = gather_columns(features, self._keys, dev)
+        S = len(self._keys)
+        labels, label_mod = None, 0
+        if self._target_columns:
+            y = features[self._target_columns[0]].to(dev, non_blocking=True).reshape(-1).float()
+            if offsets is None:
+                labels, label_mod = y, B
+            else:
+                lens = (offsets[1:] - offsets[:-1]).long()
+                labels = torch.repeat_interleave(y.repeat(S), lens, output_size=int(ids.numel()))
+        count = training and self.trainable
+        out = pull_pool(self._anchor, self.link, ids, offsets, B, S, self.combiner, labels, label_mod, count)
+        self._pending_push = count
+        if self.is_concat:
+            return out
+        pd = self.out_dim
+        return [out[:, s * pd:(s + 1) * pd] for s in range(S)]
+
+    def backwards(self, grads_and_vars=None):
+        """Push this step's sparse gradients to the owning shards and apply the sparse optimizer."""
+        if self._pending_push:
+            self.link.push()
+            self._pending_push = False
+
+    # --------------------------------------------------------------------------------
+    def save_sparse_table(self, filepath: str, mode: str = "txt"):
+        return core.save_sparse_table(self.sparse_table_handle, filepath, mode)
+
+    def load_sparse_table(self, filepath: str, mode: str = "txt"):
+        return core.load_sparse_table(self.sparse_table_handle, filepath, mode)
+
+    def show_decay(self, delta_days: int = 0):
+        return core.show_decay(self.sparse_table_handle, delta_days)

@@ -1,0 +1,428 @@
+"""``tn.model.Model``: training / inference driver around an ``nn.Module``.
+
+Same life-cycle as the reference's Keras subclass (tensornet/model/Model.py:60-256): a custom
+train step (forward, backward, ONE fused dense update, then ``backwards`` = sparse push on every
+embedding layer), ``predict_step`` returning ``(y, y_pred)``, composite
+``save_weights / load_weights / load_sparse_weights / show_decay`` over sparse tables, dense
+table and batch-norm tables, and a ``_checkpoint`` done-file written last.
+
+B200 specifics: after a few eager steps the whole step (pull kernel, towers, loss, dense
+update, push kernel) is captured into one CUDA graph and replayed; inputs are copied into
+static device buffers straight from pinned host memory.
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import Any, Callable, Dict, Iterable, List, Optional, Sequence
+
+import torch
+from torch import nn
+
+from .. import core
+from .._opentelemetry import start_as_current_span
+from ..data.features import PACKED_KEY, PackedFeatures, Ragged
+from ..ops import functional as F
+
+
+# ----------------------------------------------------------------------------------------------
+# done-file helpers (tensornet/model/Model.py:27-58)
+# ----------------------------------------------------------------------------------------------
+def load_done_info(cp_dir: str):
+    done_file = os.path.join(cp_dir, "_checkpoint")
+    if not os.path.exists(done_file):
+        return None
+    with open(done_file) as f:
+        return json.load(f)
+
+
+def save_done_info(cp_dir: str, dt: str):
+    os.makedirs(cp_dir, exist_ok=True)
+    tmp = os.path.join(cp_dir, "_checkpoint.tmp")
+    with open(tmp, "w") as f:
+        json.dump({"dt": dt}, f)
+    os.replace(tmp, os.path.join(cp_dir, "_checkpoint"))
+
+
+def read_last_train_dt(filepath: str):
+    info = load_done_info(filepath)
+    return info.get("dt") if info else None
+
+
+def match_dtype_and_rank(y_t, y_p, sw=None):
+    """Bring labels (and sample weights) to the prediction's dtype and rank
+    (tensornet/model/compile_utils.py)."""
+    if y_t.dim() == 1 and y_p.dim() == 2:
+        y_t = y_t.unsqueeze(-1)
+    y_t = y_t.to(y_p.dtype)
+    if sw is not None:
+        if sw.dim() == 1 and y_p.dim() == 2:
+            sw = sw.unsqueeze(-1)
+        sw = sw.to(y_p.dtype)
+    return y_t, y_p, sw
+
+
+def apply_mask(y_p, sw, mask):
+    """Fold a boolean mask into the sample weights (tensornet/model/compile_utils.py)."""
+    if mask is None:
+        return sw
+    mask = mask.to(y_p.dtype)
+    if sw is None:
+        return mask
+    return sw * mask
+
+
+# ----------------------------------------------------------------------------------------------
+def _flatten(obj, out: List[torch.Tensor]):
+    """Structure-preserving flatten of (nested) batch containers into a list of tensors."""
+    if torch.is_tensor(obj):
+        out.append(obj)
+        return ("t",)
+    if isinstance(obj, PackedFeatures):
+        spec = []
+        for name in ("ids", "values", "offsets"):
+            t = getattr(obj, name)
+            spec.append(None if t is None else _flatten(t, out))
+        return ("packed", obj.keys, obj.batch_size, spec)
+    if isinstance(obj, Ragged):
+        return ("ragged", [_flatten(obj.values, out), _flatten(obj.offsets, out)])
+    if isinstance(obj, dict):
+        return ("dict", [(k, _flatten(v, out)) for k, v in obj.items()])
+    if isinstance(obj, (list, tuple)):
+        return ("list", [_flatten(v, out) for v in obj])
+    return ("const", obj)
+
+
+def _unflatten(spec, it):
+    kind = spec[0]
+    if kind == "t":
+        return next(it)
+    if kind == "packed":
+        _, keys, bs, sub = spec
+        vals = [None if s is None else _unflatten(s, it) for s in sub]
+        return PackedFeatures(keys, vals[0], vals[1], vals[2], bs)
+    if kind == "ragged":
+        return Ragged(*[_unflatten(s, it) for s in spec[1]])
+    if kind == "dict":
+        return {k: _unflatten(s, it) for k, s in spec[1]}
+    if kind == "list":
+        return [_unflatten(s, it) for s in spec[1]]
+    return spec[1]
+
+
+def _is_static(spec) -> bool:
+    """True when every tensor of the batch has a batch-independent shape (no ragged features)."""
+    kind = spec[0]
+    if kind == "ragged":
+        return False
+    if kind == "packed":
+        return spec[3][0] is not None
+    if kind == "dict":
+        return all(_is_static(s) for _, s in spec[1])
+    if kind == "list":
+        return all(_is_static(s) for s in spec[1])
+    return True
+
+
+class Model(nn.Module):
+    """Wrap a network that maps a feature dict to logits ``[B, 1]``.
+
+    Either subclass and define ``forward`` or pass ``network=`` (any ``nn.Module``)."""
+
+    def __init__(self, network: Optional[nn.Module] = None, name: str = "model"):
+        super().__init__()
+        self.network = network
+        self.model_name = name
+        self.optimizer = None
+        self.loss_fn: Optional[Callable] = None
+        self.metrics: List[Any] = []
+        self.is_loaded_from_checkpoint = False
+        self._sums: Optional[torch.Tensor] = None
+        self._graph = None
+        self._graph_key = None
+        self._static_leaves: List[torch.Tensor] = []
+        self._static_loss = None
+        self._eager_steps = 0
+        self._use_graph = False
+        self.stop_training = False
+
+    # ------------------------------------------------------------------ construction
+    def forward(self, features):
+        if self.network is None:
+            raise NotImplementedError("subclass Model or pass network=")
+        return self.network(features)
+
+    def compile(self, optimizer=None, loss="binary_crossentropy", metrics: Optional[Sequence] = None,
+                cuda_graph: Optional[bool] = None, graph_warmup: int = 3):
+        rt = core.runtime()
+        self.to(rt.device)
+        self.optimizer = optimizer
+        self.loss_fn = loss
+        self.metrics = list(metrics or [])
+        self._sums = torch.zeros(4, dtype=torch.float32, device=rt.device)
+        self._use_graph = rt.on_gpu and (core.config.cuda_graph if cuda_graph is None else cuda_graph)
+        self._graph_warmup = graph_warmup
+        if optimizer is not None:
+            optimizer.attach(self.named_parameters())
+        return self
+
+    def sparse_layers(self):
+        return [m for m in self.modules() if hasattr(m, "backwards") and m is not self]
+
+    # ------------------------------------------------------------------ steps
+    def _loss(self, logits, labels):
+        if callable(self.loss_fn):
+            return self.loss_fn(logits, labels), torch.sigmoid(logits.detach())
+        return F.bce_with_logits(logits, labels, self._sums)
+
+    def backwards(self, grads_and_vars=None):
+        for layer in self.sparse_layers():
+            layer.backwards(grads_and_vars)
+
+    def _step_impl(self, features, labels):
+        logits = self(features)
+        loss, _ = self._loss(logits, labels)
+        loss.backward()
+        if self.optimizer is not None:
+            self.optimizer.step()
+        self.backwards()
+        return loss.detach()
+
+    def _to_device(self, obj):
+        dev = core.runtime().device
+        leaves: List[torch.Tensor] = []
+        spec = _flatten(obj, leaves)
+        moved = [t.to(dev, non_blocking=True) for t in leaves]
+        return _unflatten(spec, iter(moved)), spec, leaves
+
+    def train_step(self, data):
+        """One optimisation step on ``data = (features, labels)``; returns the loss (device tensor)."""
+        features, labels = data
+        self.train()
+        if not self._use_graph:
+            (f, y), _, _ = self._to_device((features, labels))
+            return self._step_impl(f, y)
+        leaves: List[torch.Tensor] = []
+        spec = _flatten((features, labels), leaves)
+        key = (repr(spec), tuple((tuple(t.shape), t.dtype) for t in leaves))
+        static_ok = _is_static(spec)
+        if not static_ok or self._eager_steps < self._graph_warmup:
+            self._eager_steps += 1
+            (f, y), _, _ = self._to_device((features, labels))
+            return self._step_impl(f, y)
+        if self._graph is None or self._graph_key != key:
+            self._capture(spec, leaves, key)
+        for dst, src in zip(self._static_leaves, leaves):
+            dst.copy_(src, non_blocking=True)
+        if self.optimizer is not None:
+            self.optimizer.table.set_lr(self.optimizer._lr())
+        self._graph.replay()
+        if self.optimizer is not None:
+            self.optimizer.iterations += 1
+            self.optimizer.table.step_count += 1
+        return self._static_loss
+
+    def _capture(self, spec, leaves, key):
+        dev = core.runtime().device
+        self._static_leaves = [torch.empty(t.shape, dtype=t.dtype, device=dev) for t in leaves]
+        for dst, src in zip(self._static_leaves, leaves):
+            dst.copy_(src, non_blocking=True)
+        f, y = _unflatten(spec, iter(self._static_leaves))
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        iters = self.optimizer.iterations if self.optimizer is not None else 0
+        from .. import _build
+        c0 = _build.cuda_ext().launch_count()
+        with torch.cuda.graph(g):
+            self._static_loss = self._step_impl(f, y)
+        self._launches_per_step = _build.cuda_ext().launch_count() - c0
+        if self.optimizer is not None:      # capture only records work, it does not run a step
+            self.optimizer.iterations = iters
+            self.optimizer.table.step_count -= 1
+        self._graph, self._graph_key = g, key
+
+    def train_on_batch(self, x, y=None, return_dict: bool = False):
+        with start_as_current_span("train_on_batch"):
+            loss = self.train_step((x, y))
+        return {"loss": loss} if return_dict else loss
+
+    def test_step(self, data):
+        features, labels = data
+        self.eval()
+        with torch.no_grad():
+            (f, y), _, _ = self._to_device((features, labels))
+            logits = self(f)
+            loss, pred = self._loss(logits, y)
+        return loss, pred
+
+    def predict_step(self, data):
+        """Returns ``(y, y_pred)`` like the reference (tensornet/model/Model.py:117-124)."""
+        features, labels = data if isinstance(data, (tuple, list)) and len(data) == 2 else (data, None)
+        self.eval()
+        with torch.no_grad():
+            (f, y), _, _ = self._to_device((features, labels))
+            pred = torch.sigmoid(self(f))
+        return y, pred
+
+    def predict_on_batch(self, x):
+        with start_as_current_span("predict_on_batch"):
+            return self.predict_step((x, None))[1]
+
+    def predict(self, dataset: Iterable, steps: Optional[int] = None):
+        with start_as_current_span("predict"):
+            ys, ps = [], []
+            for i, batch in enumerate(dataset):
+                if steps is not None and i >= steps:
+                    break
+                y, p = self.predict_step(batch)
+                ps.append(p.cpu())
+                if y is not None:
+                    ys.append(y.cpu())
+            return (torch.cat(ys) if ys else None), (torch.cat(ps) if ps else None)
+
+    def fit(self, dataset: Iterable, epochs: int = 1, steps_per_epoch: Optional[int] = None, callbacks: Sequence = (),
+            verbose: int = 0, log_every: int = 100):
+        """Iterate ``dataset`` (yielding ``(features, labels)``) for ``epochs`` passes."""
+        with start_as_current_span("fit"):
+            history = {"loss": []}
+            for cb in callbacks:
+                cb.set_model(self)
+                cb.on_train_begin()
+            for epoch in range(epochs):
+                for cb in callbacks:
+                    cb.on_epoch_begin(epoch)
+                last = None
+                for i, batch in enumerate(dataset):
+                    if steps_per_epoch is not None and i >= steps_per_epoch:
+                        break
+                    last = self.train_step(batch)
+                    if verbose and (i + 1) % log_every == 0:
+                        print(f"epoch {epoch} step {i + 1} loss {float(last):.5f}", flush=True)
+                    if self.stop_training:
+                        break
+                core.runtime().check_status()
+                history["loss"].append(float(last) if last is not None else float("nan"))
+                for cb in callbacks:
+                    cb.on_epoch_end(epoch, {"loss": history["loss"][-1]})
+            for cb in callbacks:
+                cb.on_train_end()
+            return history
+
+    # ------------------------------------------------------------------ metrics
+    def metric_sums(self) -> Dict[str, float]:
+        """Running loss / CTR / PCTR / COPC since the last reset."""
+        s = self._sums.tolist() if self._sums is not None else [0, 0, 0, 0]
+        n = max(s[3], 1.0)
+        return {"loss_sum": s[0], "ctr": s[1] / n, "pctr": s[2] / n, "copc": s[1] / max(s[2], 1e-12), "count": s[3]}
+
+    def reset_metrics(self):
+        if self._sums is not None:
+            self._sums.zero_()
+
+    # ------------------------------------------------------------------ checkpoints
+    def _tn_children(self):
+        from ..layers.embedding_features import EmbeddingFeatures
+
+        seen_tables = set()
+        for m in self.modules():
+            if m is self:
+                continue
+            if isinstance(m, EmbeddingFeatures) or hasattr(m, "save_sparse_table"):
+                h = getattr(m, "sparse_table_handle", None)
+                if h in seen_tables:      # shared tables are written once
+                    continue
+                seen_tables.add(h)
+                yield "sparse", m
+            elif hasattr(m, "save_bn_table"):
+                yield "bn", m
+
+    def save_weights(self, filepath: str, dt: str = "", mode: str = "txt", **kwargs):
+        """<filepath>/<dt>/{sparse_table,dense_table,bn_table,torch_checkpoint.pt}; ``_checkpoint`` last."""
+        rt = core.runtime()
+        cp_dir = os.path.join(filepath, dt) if dt else filepath
+        if rt.rank == 0:
+            os.makedirs(cp_dir, exist_ok=True)
+        core.barrier()
+        for kind, m in self._tn_children():
+            if kind == "sparse":
+                m.save_sparse_table(cp_dir, mode)
+            elif rt.rank == 0:
+                m.save_bn_table(cp_dir)
+        if self.optimizer is not None and self.optimizer.table.initialized:
+            self.optimizer.save_dense_table(cp_dir)
+        core.barrier()
+        if rt.rank == 0:
+            torch.save({k: v.detach().cpu() for k, v in self.state_dict().items()}, os.path.join(cp_dir, "torch_checkpoint.pt"))
+            save_done_info(filepath, dt)
+        core.barrier()
+
+    def _resolve_cp_dir(self, filepath: str, include_dt: bool):
+        if include_dt:
+            return filepath if os.path.isdir(filepath) else None
+        info = load_done_info(filepath)
+        if not info:
+            return None
+        return os.path.join(filepath, info["dt"]) if info.get("dt") else filepath
+
+    def load_weights(self, filepath: str, include_dt: bool = False, mode: str = "txt", **kwargs):
+        cp_dir = self._resolve_cp_dir(filepath, include_dt)
+        if cp_dir is None:
+            return False      # nothing trained yet: silent no-op like the reference (Model.py:179-181)
+        if not self.is_loaded_from_checkpoint:
+            self._load_tn(cp_dir, mode, dense=True)
+            self.is_loaded_from_checkpoint = True
+        return True
+
+    def load_sparse_weights(self, filepath: str, include_dt: bool = False, mode: str = "txt", **kwargs):
+        cp_dir = self._resolve_cp_dir(filepath, include_dt)
+        if cp_dir is None:
+            return False
+        self._load_tn(cp_dir, mode, dense=False)
+        return True
+
+    def _load_tn(self, cp_dir: str, mode: str, dense: bool):
+        for kind, m in self._tn_children():
+            if kind == "sparse":
+                m.load_sparse_table(cp_dir, mode)
+            else:
+                m.load_bn_table(cp_dir)
+        pt = os.path.join(cp_dir, "torch_checkpoint.pt")
+        if os.path.exists(pt):
+            sd = torch.load(pt, map_location="cpu")
+            with torch.no_grad():
+                own = self.state_dict()
+                for k, v in sd.items():
+                    if k in own and own[k].shape == v.shape:
+                        own[k].copy_(v)
+        if dense and self.optimizer is not None:
+            if not self.optimizer.table.initialized:
+                self.optimizer.attach(self.named_parameters())
+            self.optimizer.load_dense_table(cp_dir)
+        core.barrier()
+
+    def show_decay(self, delta_days: int = 0):
+        for kind, m in self._tn_children():
+            if kind == "sparse":
+                m.show_decay(delta_days)
+
+
+class PCGradModel(Model):
+    """Multi-task variant: ``forward`` returns one logit column per task; every task loss is
+    back-propagated separately and the dense gradients are combined by PCGrad
+    (tensornet/model/Model.py:259-293, tensornet/model/compile_utils.py:55-126)."""
+
+    def _step_impl(self, features, labels):
+        from ..optimizer import PCGrad
+
+        logits = self(features)
+        n_task = logits.shape[1]
+        labels = labels.reshape(logits.shape[0], -1).float()
+        losses = [torch.nn.functional.binary_cross_entropy_with_logits(logits[:, k], labels[:, min(k, labels.shape[1] - 1)])
+                  for k in range(n_task)]
+        if isinstance(self.optimizer, PCGrad):
+            self.optimizer.step_multi(losses)
+        else:
+            torch.stack(losses).sum().backward()
+            self.optimizer.step()
+        self.backwards()
+        return torch.stack(losses).sum().detach()

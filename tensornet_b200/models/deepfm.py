@@ -1,0 +1,67 @@
+"""DeepFM (examples/models/deepfm.py in the reference): a linear term over dim-1 embeddings,
+a second-order FM term and a ReLU MLP over the concatenated deep embeddings (plus optional
+dense features), joined by a final ``Dense(1)``.
+
+As in the reference the model is split into an embedding part (``emb_model``: the two
+EmbeddingFeatures layers) and a pure dense ``sub_model`` (what gets exported for serving).
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+from torch import nn
+
+from .. import core, feature_column as fc
+from ..layers import DenseHead, EmbeddingFeatures, MLP
+from ..model import Model
+from ..ops import functional as F
+
+
+class DeepFMSubModel(nn.Module):
+    """Dense part: inputs are the pooled embeddings, output is the logit."""
+
+    def __init__(self, n_linear: int, n_fields: int, emb_dim: int, dense_dim: int, hidden_units: Sequence[int]):
+        super().__init__()
+        self.n_linear, self.n_fields, self.emb_dim, self.dense_dim = n_linear, n_fields, emb_dim, dense_dim
+        self.mlp = MLP(n_fields * emb_dim + dense_dim, hidden_units)
+        self.head = DenseHead(self.mlp.out_dim + n_linear + 1)
+
+    def forward(self, linear_emb: Optional[torch.Tensor], deep_emb: torch.Tensor, dense: Optional[torch.Tensor] = None):
+        fm = F.fm(deep_emb, self.n_fields, self.emb_dim)
+        pieces = [deep_emb] + ([dense.float()] if self.dense_dim else [])
+        x0 = F.concat_cast(pieces, ones=True)
+        h = self.mlp(x0)
+        tail = [h] + ([linear_emb] if self.n_linear else []) + [fm]
+        z = F.concat_cast(tail, ones=True, widths=[self.mlp.out_dim] + [None] * (len(tail) - 1))
+        return self.head(z)
+
+
+class DeepFM(Model):
+    def __init__(self, linear_features: Sequence[str], dnn_features: Sequence[str], dnn_hidden_units: Sequence[int] = (128, 128),
+                 embedding_dim: int = 8, dense_dim: int = 0, dense_key: str = "dense", sparse_opt=None, linear_sparse_opt=None,
+                 bucket_size: int = 1024, target_columns: Optional[Sequence[str]] = None, combiner: str = "mean",
+                 table_rows: Optional[int] = None):
+        super().__init__(name="full_model")
+        sparse_opt = sparse_opt or core.AdaGrad(learning_rate=0.01, initial_g2sum=0.1, initial_scale=0.1)
+        linear_sparse_opt = linear_sparse_opt or sparse_opt
+        cols = {s: fc.category_column(key=s, bucket_size=bucket_size) for s in dict.fromkeys(list(linear_features) + list(dnn_features))}
+        self.dense_key, self.dense_dim = dense_key, dense_dim
+        self.linear_emb = None
+        if linear_features:
+            self.linear_emb = EmbeddingFeatures([fc.embedding_column(cols[s], 1, combiner) for s in linear_features],
+                                                linear_sparse_opt, name="linear_input", is_concat=True,
+                                                target_columns=target_columns, rows=table_rows)
+        self.deep_emb = EmbeddingFeatures([fc.embedding_column(cols[s], embedding_dim, combiner) for s in dnn_features],
+                                          sparse_opt, name="deep_input", is_concat=True, target_columns=target_columns,
+                                          rows=table_rows)
+        n_lin = len(linear_features) * (self.linear_emb.out_dim if self.linear_emb else 0)
+        self.sub_model = DeepFMSubModel(n_lin, len(dnn_features), self.deep_emb.out_dim, dense_dim, dnn_hidden_units)
+
+    def forward(self, features):
+        lin = self.linear_emb(features) if self.linear_emb is not None else None
+        deep = self.deep_emb(features)
+        dense = None
+        if self.dense_dim:
+            dense = features[self.dense_key].to(deep.device, non_blocking=True)
+        return self.sub_model(lin, deep, dense)

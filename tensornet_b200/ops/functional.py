@@ -1,0 +1,315 @@
+"""Differentiable front-ends of the dense-tower kernels.
+
+On a CUDA tensor each function runs the hand-written sm_100a kernels through a
+``torch.autograd.Function``; on a CPU tensor it runs the same arithmetic in plain PyTorch
+(the oracle path).  Layout conventions shared by the GPU kernels:
+
+* GEMM operands are bf16 with the row length padded to a multiple of 8 elements
+  (16 bytes, the TMA stride rule).  Column ``K`` of an activation matrix holds the constant
+  1.0, so a layer's bias is simply column ``K`` of its ``[N, K_pad]`` weight matrix and the
+  bias gradient falls out of the weight-gradient GEMM.
+* Weight gradients are accumulated straight into ``param.grad`` (fp32).
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+
+from .. import _build
+from ..core.runtime import runtime
+
+
+def pad8(n: int) -> int:
+    return (int(n) + 7) // 8 * 8
+
+
+def _ext():
+    return _build.cuda_ext()
+
+
+def _status():
+    return runtime().status
+
+
+def _bf16_of(p: torch.Tensor) -> torch.Tensor:
+    """bf16 shadow of a parameter (kept current by the dense optimizer) or a fresh cast."""
+    sh = getattr(p, "_tn_bf16", None)
+    if sh is not None:
+        return sh
+    return p.detach().to(torch.bfloat16)
+
+
+def _grad_buffer(p: torch.Tensor) -> torch.Tensor:
+    if p.grad is None:
+        p.grad = torch.zeros_like(p)
+    return p.grad
+
+
+# =========================================================================================
+# concat + cast to the padded bf16 operand
+# =========================================================================================
+class _ConcatCast(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ones: bool, widths, *pieces):
+        B = pieces[0].shape[0]
+        widths = [int(p.shape[1]) if w is None else int(w) for p, w in zip(pieces, widths)]
+        K = sum(widths)
+        ld = pad8(K + (1 if ones else 0))
+        out = torch.empty((B, ld), dtype=torch.bfloat16, device=pieces[0].device)
+        ps = [p if p.stride(-1) == 1 else p.contiguous() for p in pieces]
+        _ext().concat_cast(list(ps), widths, [int(p.stride(0)) for p in ps], out, B, ld, K if ones else -1)
+        ctx.meta = (B, widths, ld, [p.dtype for p in pieces], [p.requires_grad for p in pieces], [int(p.shape[1]) for p in pieces])
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        B, widths, ld, dtypes, needs, full = ctx.meta
+        g = g.contiguous()
+        outs: List[Optional[torch.Tensor]] = []
+        for w, dt, need, fw in zip(widths, dtypes, needs, full):
+            if not need:
+                outs.append(None)
+            elif fw == w:
+                outs.append(torch.empty((B, w), dtype=dt, device=g.device))
+            else:       # piece wider than the columns used: the unused columns get zero gradient
+                outs.append(torch.zeros((B, fw), dtype=dt, device=g.device))
+        _ext().split_cast(outs, widths, list(full), g, B, ld, -1)
+        return (None, None, *outs)
+
+
+def concat_cast(pieces: Sequence[torch.Tensor], ones: bool = True, widths: Optional[Sequence[Optional[int]]] = None) -> torch.Tensor:
+    """``[B, sum(widths) (+1)]`` bf16, zero padded to a multiple of 8 columns; with ``ones`` the
+    column right after the data is the constant 1 that carries the next layer's bias.
+    ``widths[i]`` (optional) uses only the first columns of piece i (e.g. to drop its padding)."""
+    pieces = [p if p.dim() == 2 else p.reshape(p.shape[0], -1) for p in pieces]
+    widths = list(widths) if widths is not None else [None] * len(pieces)
+    if pieces[0].is_cuda:
+        return _ConcatCast.apply(ones, widths, *pieces)
+    B = pieces[0].shape[0]
+    cols = [p.float() if w is None else p.float()[:, :w] for p, w in zip(pieces, widths)]
+    K = sum(int(c.shape[1]) for c in cols)
+    if ones:
+        cols.append(torch.ones(B, 1))
+    ld = pad8(K + (1 if ones else 0))
+    if ld > K + (1 if ones else 0):
+        cols.append(torch.zeros(B, ld - K - (1 if ones else 0)))
+    return torch.cat(cols, dim=1).to(torch.bfloat16)
+
+
+# =========================================================================================
+# MLP tower: chain of (bf16 GEMM + bias + ReLU) layers on the tcgen05 kernel
+# =========================================================================================
+class _MLP(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, dims, relu_last, *weights):
+        # x: bf16 [B, Kp0] (ones column at dims[0]);  weights[l]: fp32 [N_l, pad8(K_l + 1)]
+        ext, st = _ext(), _status()
+        B = x.shape[0]
+        acts = [x]
+        h = x
+        L = len(weights)
+        for l, w in enumerate(weights):
+            N, Kp = int(w.shape[0]), int(w.shape[1])
+            K = dims[l]
+            Np = pad8(N + 1)
+            y = torch.empty((B, Np), dtype=torch.bfloat16, device=x.device)
+            relu = relu_last or l < L - 1
+            ext.gemm(h, _bf16_of(w), y, B, N, K + 1, int(h.stride(0)), Kp, Np, False, False, False, relu, None, None, None,
+                     None, 0, N, Np, 1, 0, st)
+            acts.append(y)
+            h = y
+        ctx.save_for_backward(*acts)
+        ctx.weights = weights
+        ctx.dims = dims
+        ctx.relu_last = relu_last
+        return h
+
+    @staticmethod
+    def backward(ctx, gy):
+        ext, st = _ext(), _status()
+        acts = ctx.saved_tensors
+        weights = ctx.weights
+        dims = ctx.dims
+        L = len(weights)
+        B = gy.shape[0]
+        g = gy.contiguous()
+        if ctx.relu_last:
+            g = g.clone()
+            ext.relu_mask(g, acts[L])
+        gx = None
+        for l in range(L - 1, -1, -1):
+            w = weights[l]
+            N, Kp = int(w.shape[0]), int(w.shape[1])
+            K = dims[l]
+            h = acts[l]
+            ldh = int(h.stride(0))
+            # weight gradient (incl. the bias column): dW[N, Kp] += g[:, :N]^T . h   (contraction over the batch)
+            if w.requires_grad:
+                gw = _grad_buffer(w)
+                split = max(1, min(16, B // 1024))
+                ext.gemm(g, h, gw, N, K + 1, B, int(g.stride(0)), ldh, Kp, True, True, True, False, None, None, None, None,
+                         0, -1, K + 1, split, 0, st)
+            # input gradient: gh[B, ldh] = g[:, :N] . W   masked by the ReLU of the layer below
+            if l > 0 or ctx.needs_input_grad[0]:
+                gh = torch.empty((B, ldh), dtype=torch.bfloat16, device=g.device)
+                mask = h if l > 0 else None
+                ext.gemm(g, _bf16_of(w), gh, B, min(Kp, ldh), N, int(g.stride(0)), Kp, ldh, False, True, False, False, None,
+                         mask, None, None, ldh, -1, ldh, 1, 0, st)
+                g = gh
+                gx = gh
+        return (gx if ctx.needs_input_grad[0] else None, None, None, *([None] * L))
+
+
+def mlp(x: torch.Tensor, weights: Sequence[torch.Tensor], in_dim: int, relu_last: bool = True) -> torch.Tensor:
+    """Run ``x`` (bf16, ones column at ``in_dim``) through the layers ``weights``.
+    Returns bf16 ``[B, pad8(N_last + 1)]`` whose column ``N_last`` is again the constant 1."""
+    dims = [in_dim] + [int(w.shape[0]) for w in weights[:-1]]
+    if x.is_cuda:
+        return _MLP.apply(x, dims, relu_last, *weights)
+    h = x.float()
+    L = len(weights)
+    for l, w in enumerate(weights):
+        K, N = dims[l], int(w.shape[0])
+        wq = w.to(torch.bfloat16).float()
+        y = h[:, :K + 1] @ wq[:, :K + 1].t()
+        if relu_last or l < L - 1:
+            y = torch.relu(y)
+        Np = pad8(N + 1)
+        y = torch.cat([y, torch.ones(y.shape[0], 1), torch.zeros(y.shape[0], Np - N - 1)], dim=1)
+        h = y.to(torch.bfloat16).float()
+    return h.to(torch.bfloat16)
+
+
+# =========================================================================================
+# FM second-order term
+# =========================================================================================
+class _FM(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, e, F, D):
+        e = e.contiguous()
+        B = e.shape[0]
+        out = torch.empty(B, dtype=torch.float32, device=e.device)
+        _ext().fm_fwd(e, F * D, B, F, D, out)
+        ctx.save_for_backward(e)
+        ctx.fd = (F, D)
+        return out.view(B, 1)
+
+    @staticmethod
+    def backward(ctx, g):
+        (e,) = ctx.saved_tensors
+        F, D = ctx.fd
+        B = e.shape[0]
+        ge = torch.empty_like(e)
+        _ext().fm_bwd(e, F * D, B, F, D, g.contiguous().view(-1), ge, F * D, False)
+        return ge, None, None
+
+
+def fm(e: torch.Tensor, fields: int, dim: int) -> torch.Tensor:
+    """``0.5 * sum_d((sum_f e)^2 - sum_f e^2)`` of ``e [B, fields*dim]`` -> ``[B, 1]``."""
+    if e.is_cuda:
+        return _FM.apply(e.reshape(e.shape[0], fields * dim), fields, dim)
+    x = e.reshape(e.shape[0], fields, dim)
+    s = x.sum(dim=1)
+    return 0.5 * (s * s - (x * x).sum(dim=1)).sum(dim=1, keepdim=True)
+
+
+# =========================================================================================
+# Dense(1) head on a padded bf16 operand
+# =========================================================================================
+class _Head(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, z, w):
+        B, ld = z.shape[0], int(z.stride(0))
+        K1 = int(w.numel())
+        y = torch.empty(B, dtype=torch.float32, device=z.device)
+        _ext().gemv_fwd(z, ld, B, K1, w, y)
+        ctx.save_for_backward(z)
+        ctx.w = w
+        return y.view(B, 1)
+
+    @staticmethod
+    def backward(ctx, gy):
+        (z,) = ctx.saved_tensors
+        w = ctx.w
+        B, ld = z.shape[0], int(z.stride(0))
+        dz = torch.empty_like(z)
+        gw = _grad_buffer(w)
+        _ext().gemv_bwd(z, ld, B, int(w.numel()), w, gy.contiguous().view(-1), dz, gw, 0)
+        return dz, None
+
+
+def head(z: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``z[:, :len(w)] @ w`` -> ``[B, 1]`` fp32; ``w``'s last element multiplies z's ones column (bias)."""
+    if z.is_cuda:
+        return _Head.apply(z, w)
+    return (z.float()[:, : w.numel()] @ w).view(-1, 1)
+
+
+# =========================================================================================
+# sigmoid binary cross-entropy (mean) with fused dlogit and CTR / PCTR sums
+# =========================================================================================
+class _BCE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logit, label, sums):
+        B = logit.numel()
+        lg = logit.contiguous().view(-1)
+        dl = torch.empty_like(lg)
+        pred = torch.empty_like(lg)
+        s = sums if sums is not None else torch.zeros(4, dtype=torch.float32, device=lg.device)
+        loss_before = s[0].clone()
+        _ext().bce(lg, label.contiguous().view(-1).float(), pred, dl, 1.0 / B, s)
+        ctx.save_for_backward(dl)
+        ctx.shape = logit.shape
+        ctx.mark_non_differentiable(pred)
+        return s[0] - loss_before, pred.view(logit.shape)
+
+    @staticmethod
+    def backward(ctx, gloss, _gpred):
+        (dl,) = ctx.saved_tensors
+        return (dl * gloss).view(ctx.shape), None, None
+
+
+def bce_with_logits(logit: torch.Tensor, label: torch.Tensor, sums: Optional[torch.Tensor] = None):
+    """Mean sigmoid cross-entropy.  Returns ``(loss, prediction)``.  ``sums`` (fp32[4]), when given,
+    accumulates ``[loss, sum(label), sum(prediction), count]`` for the CTR / PCTR / COPC metrics."""
+    if logit.is_cuda:
+        return _BCE.apply(logit, label, sums)
+    lg = logit.view(-1)
+    y = label.view(-1).float()
+    loss = torch.nn.functional.binary_cross_entropy_with_logits(lg, y)
+    pred = torch.sigmoid(lg).detach()
+    if sums is not None:
+        with torch.no_grad():
+            sums += torch.stack([loss.detach(), y.sum(), pred.sum(), torch.tensor(float(y.numel()))])
+    return loss, pred.view(logit.shape)
+
+
+# =========================================================================================
+# DCN-v1 cross layer  y = x0 * (xl . w) + b + xl     (examples/common/layers.py:53-59)
+# =========================================================================================
+class _CrossV1(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x0, xl, w, b):
+        x0, xl = x0.contiguous(), xl.contiguous()
+        y = torch.empty_like(x0)
+        dot = torch.empty(x0.shape[0], dtype=torch.float32, device=x0.device)
+        _ext().cross_v1_fwd(x0, xl, w.contiguous().view(-1), b.contiguous(), y, dot)
+        ctx.save_for_backward(x0, xl, w, dot)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        x0, xl, w, dot = ctx.saved_tensors
+        gy = gy.contiguous()
+        gx0, gxl = torch.empty_like(x0), torch.empty_like(xl)
+        gw = torch.zeros(w.numel(), dtype=torch.float32, device=w.device)
+        gb = torch.zeros(w.numel(), dtype=torch.float32, device=w.device)
+        _ext().cross_v1_bwd(x0, xl, w.contiguous().view(-1), dot, gy, gx0, gxl, gw, gb)
+        return gx0, gxl, gw.view(w.shape), gb
+
+
+def cross_v1(x0, xl, w, b):
+    if x0.is_cuda:
+        return _CrossV1.apply(x0, xl, w, b)
+    return x0 * (xl @ w.view(-1, 1)) + b + xl

@@ -1,0 +1,222 @@
+"""GPU shard of one sparse embedding table and its exchange buffers.
+
+What the reference keeps in ``SparseTable`` + ``SparseOptimizerKernel`` on every CPU rank
+(core/ps/table/sparse_table.cc:52-137, core/ps/optimizer/optimizer_kernel.h:439-560) lives
+here in HBM: an open-addressing key array, a dense slab of rows (weights + optimizer slots +
+show/click counters in one contiguous record) and the symmetric-memory inboxes the fused
+pull / push kernels use to talk to the other GPUs.  Row ownership is ``sign % world`` as in
+the reference (core/kernels/sparse_table_ops.cc:221), so checkpoint directories line up.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import numpy as np
+import torch
+
+from .. import _build
+from ..core.config import config
+from ..core.optimizers import KIND_ADAGRAD, KIND_ADAM, KIND_FTRL, OptimizerBase
+from ..core.runtime import runtime
+from ..parallel.symm import SymmArena
+
+
+def round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+def row_floats(kind: int, dim: int) -> int:
+    return dim + 4 if kind == KIND_ADAGRAD else 3 * dim + 2
+
+
+def next_pow2(x: int) -> int:
+    return 1 << max(1, (int(x) - 1).bit_length())
+
+
+class GpuSparseTable:
+    def __init__(self, opt: OptimizerBase, dim: int, use_cvm: bool = False, name: str = "", rows: Optional[int] = None):
+        rt = runtime()
+        assert rt.on_gpu, "GpuSparseTable needs a CUDA device"
+        self.ext = _build.cuda_ext()
+        self.opt = opt
+        self.kind = opt.kind
+        self.dim = int(dim)
+        self.use_cvm = bool(use_cvm)
+        self.name = name
+        self.dev = rt.device
+        self.world, self.rank = rt.world, rt.rank
+        self.row_cap = int(rows or config.table_rows_per_gpu)
+        self.stride = round_up(row_floats(self.kind, self.dim), 4)
+        self.pdim = self.dim + (2 if self.use_cvm else 0)
+        self.ustride = round_up(self.pdim, 4)
+        self.gstride = round_up(self.dim + 2, 4)
+        cap = next_pow2(int(self.row_cap / config.table_load_factor))
+        d = self.dev
+        self.keys = torch.full((cap,), -1, dtype=torch.int64, device=d)
+        self.slots = torch.full((cap,), -1, dtype=torch.int32, device=d)
+        self.rows = torch.empty((self.row_cap, self.stride), dtype=torch.float32, device=d)
+        self.row_keys = torch.empty((self.row_cap,), dtype=torch.int64, device=d)
+        self.row_tag = torch.zeros((self.row_cap,), dtype=torch.int64, device=d)
+        self.n_rows_dev = torch.zeros((1,), dtype=torch.int32, device=d)
+        self.epoch = torch.zeros((1,), dtype=torch.int64, device=d)
+        self.links = []
+        self._zero_init = False
+
+    # ------------------------------------------------------------------ views for the kernels
+    def table_dict(self):
+        return dict(keys=self.keys, slots=self.slots, rows=self.rows, row_keys=self.row_keys, row_tag=self.row_tag,
+                    n_rows=self.n_rows_dev, dim=self.dim, stride=self.stride, use_cvm=int(self.use_cvm))
+
+    def _opt_dict(self):
+        d = self.opt.sparse_params()
+        d["zero_init"] = int(self._zero_init)
+        return d
+
+    def link(self, max_unique: int) -> "GpuSparseLink":
+        """Exchange buffers + kernel context for one user (layer) of this table.  Collective when
+        world > 1: all ranks must create their links in the same order."""
+        lk = GpuSparseLink(self, max_unique)
+        self.links.append(lk)
+        return lk
+
+    def set_training(self, training: bool):
+        """Inference mode creates all-zero rows (core/ps/optimizer/ada_grad_kernel.cc:80-84)."""
+        zi = not training
+        if zi != self._zero_init:
+            self._zero_init = zi
+            self.refresh_opt()
+
+    # ------------------------------------------------------------------ maintenance
+    @property
+    def n_rows(self) -> int:
+        return int(self.n_rows_dev.item())
+
+    def refresh_opt(self):
+        for lk in self.links:
+            lk.ctx.set_opt(self._opt_dict())
+
+    def show_decay(self, delta_days: int):
+        rate = float(getattr(self.opt, "show_decay_rate", 1.0))
+        self.ext.table_decay(self.table_dict(), self.kind, rate, int(delta_days))
+
+    def clear(self):
+        self.keys.fill_(-1)
+        self.slots.fill_(-1)
+        self.row_tag.zero_()
+        self.n_rows_dev.zero_()
+
+    def dump(self) -> Tuple[np.ndarray, np.ndarray]:
+        """Host copy of (signs [n] uint64, rows [n, row_floats] float32) of this shard."""
+        n = self.n_rows
+        rf = row_floats(self.kind, self.dim)
+        keys = self.row_keys[:n].cpu().numpy().view(np.uint64)
+        rows = self.rows[:n, :rf].contiguous().cpu().numpy()
+        return keys, rows
+
+    def load_rows(self, signs: np.ndarray, rows: np.ndarray, chunk: int = 1 << 20):
+        """Insert (or overwrite) rows given as host arrays; ``signs`` must be distinct."""
+        rt = runtime()
+        rf = row_floats(self.kind, self.dim)
+        assert rows.shape[1] == rf
+        for s in range(0, len(signs), chunk):
+            k = torch.from_numpy(signs[s:s + chunk].view(np.int64).copy()).to(self.dev)
+            r = torch.from_numpy(np.ascontiguousarray(rows[s:s + chunk])).to(self.dev)
+            idx = torch.empty(k.numel(), dtype=torch.int32, device=self.dev)
+            self.ext.table_insert_keys(self.table_dict(), k, idx, rt.status)
+            ok = idx >= 0
+            li = idx[ok].long()
+            full = torch.zeros((int(ok.sum().item()), self.stride), dtype=torch.float32, device=self.dev)
+            full[:, :rf] = r[ok]
+            self.rows.index_copy_(0, li, full)
+        rt.check_status()
+
+    def lookup_rows(self, ids: torch.Tensor) -> torch.Tensor:
+        """Row index of each sign on this shard (-1 when absent); read-only."""
+        out = torch.empty(ids.numel(), dtype=torch.int32, device=self.dev)
+        self.ext.table_lookup(self.table_dict(), ids.reshape(-1).contiguous(), out)
+        return out
+
+    def compact(self, keep_mask: torch.Tensor):
+        """Rebuild the shard keeping only rows where ``keep_mask[:n_rows]`` is true."""
+        n = self.n_rows
+        rf = row_floats(self.kind, self.dim)
+        keep = keep_mask[:n].nonzero().flatten()
+        signs = self.row_keys[:n][keep].cpu().numpy().view(np.uint64)
+        rows = self.rows[:n, :rf][keep].cpu().numpy()
+        self.clear()
+        self.load_rows(signs, rows)
+
+
+class GpuSparseLink:
+    """Per-layer exchange state of a table: symmetric inboxes, the per-batch unique-row matrix
+    ``U``, its gradient ``gU`` and the bookkeeping that ties one pull to the following push."""
+
+    def __init__(self, table: GpuSparseTable, max_unique: int):
+        rt = runtime()
+        self.table = table
+        self.dim, self.pdim, self.kind = table.dim, table.pdim, table.kind
+        self.ustride, self.gstride = table.ustride, table.gstride
+        self.dev = table.dev
+        W = table.world
+        self.max_unique = int(max_unique)
+        if W == 1:
+            capo = round_up(self.max_unique + 4, 4)
+        else:
+            capo = round_up(int(math.ceil(self.max_unique / W * config.owner_segment_slack)) + 64, 4)
+        self.capo = capo
+        n_seg = W * capo
+        multi = W > 1
+        arena = SymmArena([
+            ("inbox_ids", (n_seg if multi else 4,), torch.int64),
+            ("ginbox", (n_seg * self.gstride if multi else 4,), torch.float32),
+            ("U", (n_seg * self.ustride,), torch.float32),
+            ("sig", (3 * 8,), torch.int64),
+        ])
+        d = self.dev
+        dd_cap = next_pow2(2 * self.max_unique + 16)
+        loc = dict(
+            stage_ids=torch.zeros(n_seg, dtype=torch.int64, device=d),
+            gU=torch.zeros(n_seg * self.gstride, dtype=torch.float32, device=d),
+            cnt=torch.zeros(8, dtype=torch.int32, device=d),
+            cnt_saved=torch.zeros(8, dtype=torch.int32, device=d),
+            req_n=torch.zeros(8, dtype=torch.int32, device=d),
+            req_row=torch.full((n_seg,), -1, dtype=torch.int32, device=d),
+            req_ou=torch.full((n_seg,), -1, dtype=torch.int32, device=d),
+            ou_row=torch.full((n_seg if multi else 4,), -1, dtype=torch.int32, device=d),
+            ocount=torch.zeros(1, dtype=torch.int32, device=d),
+            acc=torch.zeros(n_seg * self.gstride if multi else 4, dtype=torch.float32, device=d),
+            dd_keys=torch.full((dd_cap,), -1, dtype=torch.int64, device=d),
+            dd_vals=torch.zeros(dd_cap, dtype=torch.int32, device=d),
+            bar=torch.zeros(4, dtype=torch.int32, device=d),
+        )
+        self.arena = arena
+        self.U = arena.tensor("U").view(n_seg, self.ustride)
+        self.gU = loc["gU"].view(n_seg, self.gstride)
+        self.cnt_saved = loc["cnt_saved"]
+        self.comm = dict(world=W, rank=table.rank, capo=capo, gstride=self.gstride, ustride=self.ustride,
+                         inbox_ids=arena.ptrs("inbox_ids"), ginbox=arena.ptrs("ginbox"), U=arena.ptrs("U"),
+                         sig=arena.ptrs("sig"), epoch=table.epoch, status=rt.status, wait_ns=rt.wait_ns, **loc)
+        self.ctx = table.ext.SparseCtx(table.table_dict(), self.comm, table._opt_dict())
+        self._last_n_ids = 0
+        if multi:
+            rt.barrier()
+
+    def pull(self, ids: torch.Tensor, labels: Optional[torch.Tensor] = None, label_mod: int = 0, training: bool = True,
+             inverse: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Dedup ``ids``, fetch (creating on miss) their rows from the owning GPUs into ``self.U`` and
+        return ``inverse``: the row of ``self.U`` holding each id's embedding."""
+        n = ids.numel()
+        if inverse is None:
+            inverse = torch.empty(n, dtype=torch.int32, device=self.dev)
+        self._last_n_ids = n
+        self.ctx.pull(ids.reshape(-1), inverse, labels, int(label_mod), bool(training))
+        return inverse
+
+    def push(self):
+        """Apply the accumulated unique-row gradients (``self.gU``) on the owning GPUs."""
+        self.ctx.push(max(self._last_n_ids, 1))
+
+    def unique_counts(self):
+        """Per-owner unique-sign counts of the last pull (host sync)."""
+        return self.cnt_saved[: self.table.world].tolist()

@@ -1,0 +1,92 @@
+"""tcgen05 GEMM family against a plain fp32 PyTorch reference of the same op."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ext():
+    from tensornet_b200 import _build
+
+    return _build.cuda_ext()
+
+
+def _rel_err(a, b):
+    return float((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-6))
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 64, 64), (256, 80, 200), (1000, 400, 430), (8192, 400, 430)])
+def test_forward_kk_relu_ones(tn_gpu, status_ok, M, N, K):
+    """C = relu(A . B^T), ones column at N, zero pad after it (MLP forward layer)."""
+    dev = tn_gpu.core.runtime().device
+    Kp, Np = (K + 7) // 8 * 8, (N + 1 + 7) // 8 * 8
+    g = torch.Generator(device="cpu").manual_seed(M * 31 + N)
+    A = torch.zeros(M, Kp).bfloat16()
+    A[:, :K] = torch.randn(M, K, generator=g).bfloat16()
+    B = torch.zeros(N, Kp).bfloat16()
+    B[:, :K] = (torch.randn(N, K, generator=g) * 0.1).bfloat16()
+    A, B = A.to(dev), B.to(dev)
+    C = torch.full((M, Np), 7.0, dtype=torch.bfloat16, device=dev)
+    _ext().gemm(A, B, C, M, N, K, Kp, Kp, Np, False, False, False, True, None, None, None, None, 0, N, Np, 1, 0,
+                tn_gpu.core.runtime().status)
+    ref = torch.relu(A.float()[:, :K] @ B.float()[:, :K].t())
+    assert _rel_err(C[:, :N], ref) < 2e-2
+    assert torch.all(C[:, N] == 1.0)
+    assert torch.all(C[:, N + 1:] == 0.0)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 128, 64), (512, 432, 400), (8192, 432, 400)])
+def test_dgrad_k_mn_mask(tn_gpu, status_ok, M, N, K):
+    """dX[M,N] = (dY[M,K] . W[K,N]) masked by X > 0   (A contraction-major, B output-major)."""
+    dev = tn_gpu.core.runtime().device
+    Kp = (K + 7) // 8 * 8
+    g = torch.Generator(device="cpu").manual_seed(N * 17 + K)
+    dY = torch.zeros(M, Kp + 8).bfloat16()
+    dY[:, :K] = torch.randn(M, K, generator=g).bfloat16()
+    dY[:, K:] = 3.0    # columns beyond K must be ignored
+    W = (torch.randn(K, N, generator=g) * 0.1).bfloat16()
+    X = torch.randn(M, N, generator=g).bfloat16()
+    dY, W, X = dY.to(dev), W.to(dev), X.to(dev)
+    dX = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    _ext().gemm(dY, W, dX, M, N, K, Kp + 8, N, N, False, True, False, False, None, X, None, None, N, -1, N, 1, 0,
+                tn_gpu.core.runtime().status)
+    ref = (dY.float()[:, :K] @ W.float()) * (X.float() > 0)
+    assert _rel_err(dX, ref) < 2e-2
+
+
+@pytest.mark.parametrize("Bt,N,K,split", [(256, 128, 64, 1), (1024, 400, 430, 2), (8192, 400, 430, 8)])
+def test_wgrad_mn_mn_accumulate(tn_gpu, status_ok, Bt, N, K, split):
+    """dW[N,K] += dY[Bt,N]^T . X[Bt,K]   (both operands output-major, split-K, fp32 accumulate)."""
+    dev = tn_gpu.core.runtime().device
+    Np, Kp = (N + 1 + 7) // 8 * 8, (K + 7) // 8 * 8
+    g = torch.Generator(device="cpu").manual_seed(Bt + N)
+    dY = torch.zeros(Bt, Np).bfloat16()
+    dY[:, :N] = torch.randn(Bt, N, generator=g).bfloat16()
+    dY[:, N:] = 5.0
+    X = torch.zeros(Bt, Kp).bfloat16()
+    X[:, :K] = torch.randn(Bt, K, generator=g).bfloat16()
+    dY, X = dY.to(dev), X.to(dev)
+    dW = torch.ones(N, Kp, dtype=torch.float32, device=dev)
+    _ext().gemm(dY, X, dW, N, K, Bt, Np, Kp, Kp, True, True, True, False, None, None, None, None, 0, -1, K, split, 0,
+                tn_gpu.core.runtime().status)
+    ref = 1.0 + dY.float()[:, :N].t() @ X.float()[:, :K]
+    err = float((dW[:, :K] - ref).abs().max() / ref.abs().max())
+    assert err < 1e-2
+    assert torch.all(dW[:, K:] == 1.0)
+
+
+def test_hadamard_epilogue(tn_gpu, status_ok):
+    """DCN-v2 cross layer: C = x0 * (A . B^T + bias) + xl."""
+    dev = tn_gpu.core.runtime().device
+    M, N, K = 512, 256, 256
+    g = torch.Generator(device="cpu").manual_seed(5)
+    A = torch.randn(M, K, generator=g).bfloat16().to(dev)
+    B = (torch.randn(N, K, generator=g) * 0.05).bfloat16().to(dev)
+    bias = torch.randn(N, generator=g).to(dev)
+    x0 = torch.randn(M, N, generator=g).bfloat16().to(dev)
+    xl = torch.randn(M, N, generator=g).bfloat16().to(dev)
+    C = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    _ext().gemm(A, B, C, M, N, K, K, K, N, False, False, False, False, bias, None, x0, xl, N, -1, N, 1, 0,
+                tn_gpu.core.runtime().status)
+    ref = x0.float() * (A.float() @ B.float().t() + bias) + xl.float()
+    assert _rel_err(C, ref) < 2e-2

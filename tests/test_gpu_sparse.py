@@ -1,0 +1,162 @@
+"""Fused sparse pull / push on one GPU against a dictionary-based restatement of the reference's
+per-sign algorithms (core/ps/optimizer/{ada_grad,adam,ftrl}_kernel.cc)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _mk(tn, opt, dim, use_cvm=False, rows=1 << 14, max_unique=4096):
+    from tensornet_b200.ops.sparse_table_gpu import GpuSparseTable
+
+    t = GpuSparseTable(opt, dim, use_cvm, rows=rows)
+    return t, t.link(max_unique)
+
+
+def _host_rows(t):
+    keys, rows = t.dump()
+    return {int(k): rows[i].copy() for i, k in enumerate(keys)}
+
+
+@pytest.mark.parametrize("dim", [1, 8, 16, 64])
+def test_pull_dedup_and_init(tn_gpu, status_ok, dim):
+    tn = tn_gpu
+    opt = tn.core.AdaGrad(learning_rate=0.01, initial_g2sum=0.1, initial_scale=0.5)
+    t, lk = _mk(tn, opt, dim)
+    g = torch.Generator().manual_seed(dim)
+    ids = torch.randint(0, 300, (2000,), generator=g, dtype=torch.int64) * 7919 + 11
+    ids_d = ids.to(t.dev)
+    inv = lk.pull(ids_d, training=True)
+    torch.cuda.synchronize()
+    tn.core.runtime().check_status()
+    n_unique = len(set(ids.tolist()))
+    assert lk.unique_counts()[0] == n_unique
+    assert t.n_rows == n_unique
+    inv_h = inv.cpu().long()
+    assert int(inv_h.min()) >= 0
+    # same id -> same virtual row, different ids -> different rows
+    m = {}
+    for i, v in zip(ids.tolist(), inv_h.tolist()):
+        assert m.setdefault(i, v) == v
+    assert len(set(m.values())) == n_unique
+    # pulled rows equal the stored rows; stored rows have the documented initial state
+    U = lk.U.cpu()
+    rows = _host_rows(t)
+    w_all = []
+    for i, v in m.items():
+        assert np.allclose(U[v, :dim].numpy(), rows[i][:dim])
+        assert abs(rows[i][dim] - 0.1) < 1e-7            # g2sum
+        assert rows[i][dim + 1] == 0 and rows[i][dim + 2] == 0
+        w_all.append(rows[i][:dim])
+    w_all = np.concatenate(w_all)
+    assert abs(w_all.std() - 0.5 / math.sqrt(dim)) < 0.15 * 0.5 / math.sqrt(dim) + 0.02
+    # show counts landed in the gradient record
+    gU = lk.gU.cpu()
+    cnt = {}
+    for i in ids.tolist():
+        cnt[i] = cnt.get(i, 0) + 1
+    for i, v in m.items():
+        assert gU[v, dim] == cnt[i]
+    # a second pull of the same ids finds the same rows (no growth) and the same values
+    lk.gU.zero_()
+    inv2 = lk.pull(ids_d, training=False)
+    torch.cuda.synchronize()
+    assert t.n_rows == n_unique
+    U2 = lk.U.cpu()
+    assert torch.equal(U2[inv2.cpu().long()], U[inv_h])
+
+
+def _apply_ref(kind, opt, row, g, show, click, dim):
+    row = row.copy()
+    if kind == "AdaGrad":
+        row[dim + 1] += show
+        row[dim + 2] += click
+        row[dim] += float((g.astype(np.float64) ** 2).sum() / dim)
+        row[:dim] -= opt.learning_rate * g / (opt.epsilon + math.sqrt(row[dim]))
+    elif kind == "Adam":
+        m, v = row[dim:2 * dim], row[2 * dim:3 * dim]
+        m[:] = opt.beta1 * m + (1 - opt.beta1) * g
+        v[:] = opt.beta2 * v + (1 - opt.beta2) * g * g
+        row[:dim] -= opt.learning_rate * m / (opt.epsilon + np.sqrt(v))
+    else:
+        w, z, n = row[:dim], row[dim:2 * dim], row[2 * dim:3 * dim]
+        g2 = g * g
+        z += g - opt.learning_rate * (np.sqrt(n + g2) - np.sqrt(n)) * w
+        n += g2
+        neww = -1.0 / ((opt.beta + np.sqrt(n)) * opt.learning_rate + opt.lambda2) * np.where(z > 0, z - opt.lambda1, z + opt.lambda1)
+        w[:] = np.where(np.abs(z) <= opt.lambda1, 0.0, neww)
+    return row
+
+
+@pytest.mark.parametrize("kind", ["AdaGrad", "Adam", "Ftrl"])
+@pytest.mark.parametrize("dim", [8, 16])
+def test_push_matches_reference_math(tn_gpu, status_ok, kind, dim):
+    tn = tn_gpu
+    opt = {"AdaGrad": tn.core.AdaGrad(learning_rate=0.05, initial_g2sum=0.1, initial_scale=0.3),
+           "Adam": tn.core.Adam(learning_rate=0.01, initial_scale=0.3),
+           "Ftrl": tn.core.Ftrl(learning_rate=0.05, initial_scale=0.3, lambda1=0.001)}[kind]
+    t, lk = _mk(tn, opt, dim)
+    g = torch.Generator().manual_seed(3)
+    ids = (torch.randint(0, 500, (1500,), generator=g, dtype=torch.int64) * 104729 + 5).to(t.dev)
+    labels = (torch.rand(1500, generator=g) < 0.3).float().to(t.dev)
+    for step in range(3):
+        inv = lk.pull(ids, labels=labels, label_mod=0, training=True)
+        torch.cuda.synchronize()
+        before = _host_rows(t)
+        n_u = lk.unique_counts()[0]
+        grad = torch.randn(n_u, dim, generator=g)
+        lk.gU[:n_u, :dim] = grad.to(t.dev)
+        gU = lk.gU.cpu().numpy().copy()
+        stage = lk.comm["stage_ids"].cpu().numpy().view(np.uint64)
+        lk.push()
+        torch.cuda.synchronize()
+        tn.core.runtime().check_status()
+        after = _host_rows(t)
+        assert float(lk.gU.abs().sum()) == 0.0      # re-zeroed for the next step
+        for j in range(n_u):
+            key = int(stage[j])
+            exp = _apply_ref(kind, opt, before[key], gU[j, :dim], gU[j, dim], gU[j, dim + 1], dim)
+            got = after[key]
+            nf = dim + 3 if kind == "AdaGrad" else 3 * dim
+            assert np.allclose(got[:nf], exp[:nf], rtol=2e-5, atol=1e-6), (kind, step, j)
+
+
+def test_cvm_columns_and_zero_init(tn_gpu, status_ok):
+    tn = tn_gpu
+    dim = 8
+    opt = tn.core.AdaGrad(learning_rate=0.05, initial_g2sum=0.1)
+    t, lk = _mk(tn, opt, dim, use_cvm=True)
+    ids = torch.arange(1, 65, dtype=torch.int64).to(t.dev) * 1000003
+    labels = torch.ones(64, device=t.dev)
+    lk.pull(ids, labels=labels, training=True)
+    lk.push()
+    inv = lk.pull(ids, labels=labels, training=False)
+    torch.cuda.synchronize()
+    U = lk.U.cpu()[inv.cpu().long()]
+    assert torch.allclose(U[:, dim], torch.ones(64))                        # show
+    assert torch.allclose(U[:, dim + 1], torch.zeros(64), atol=1e-6)         # ln(2) - ln(2)
+    # unseen signs in inference mode come back as zeros (and are inserted, like the reference)
+    t.set_training(False)
+    new = torch.arange(1, 9, dtype=torch.int64).to(t.dev) * 7 + 123456789
+    inv = lk.pull(new, training=False)
+    torch.cuda.synchronize()
+    assert float(lk.U[inv.long()].abs().sum()) == 0.0
+    assert t.n_rows == 72
+
+
+def test_table_full_is_reported_not_fatal(tn_gpu):
+    tn = tn_gpu
+    opt = tn.core.Adam()
+    t, lk = _mk(tn, opt, 8, rows=64, max_unique=1024)
+    ids = torch.arange(1, 513, dtype=torch.int64).to(t.dev)
+    lk.pull(ids, training=False)
+    torch.cuda.synchronize()
+    with pytest.raises(tn.core.DeviceError) as e:
+        tn.core.runtime().check_status()
+    assert e.value.code == 3
+    assert t.n_rows == 64
+    # the context is still usable
+    assert float(torch.ones(4, device=t.dev).sum()) == 4.0
