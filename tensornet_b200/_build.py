@@ -71,7 +71,7 @@ def _build(name: str, sources, cuda: bool, verbose: bool = False):
     kwargs = dict(
         name=name,
         sources=sources,
-        extra_cflags=["-O3", "-std=c++17", "-fopenmp"] if not cuda else ["-O3", "-std=c++17"],
+        extra_cflags=["-O3", "-std=c++17"],
         extra_include_paths=[_CSRC],
         build_directory=os.path.join(_EXT, name),
         verbose=verbose,
@@ -81,7 +81,7 @@ def _build(name: str, sources, cuda: bool, verbose: bool = False):
         kwargs["with_cuda"] = True
         kwargs["extra_ldflags"] = ["-lcuda"] if _has_libcuda() else []
     else:
-        kwargs["extra_ldflags"] = ["-lz", "-fopenmp"]
+        kwargs["extra_ldflags"] = ["-lz"]
     return cpp_extension.load(**kwargs)
 
 

@@ -93,8 +93,10 @@ def show_decay(handle: int, delta_days: int):
 def create_dense_table(opt: OptimizerBase) -> int:
     from ..ops.dense_table import DenseTable
 
-    _dense_tables.append(DenseTable(opt))
-    return len(_dense_tables) - 1
+    t = DenseTable(opt)
+    t.handle = len(_dense_tables)
+    _dense_tables.append(t)
+    return t.handle
 
 
 def dense_table(handle: int):
@@ -117,8 +119,10 @@ def load_dense_table(handle: int, path: str):
 def create_bn_table(name: str, bn_size: int, sync: bool, moment: float, max_count: int, use_pctr_dnn_bn: bool = False) -> int:
     from ..ops.bn_table import BnTable
 
-    _bn_tables.append(BnTable(name, bn_size, sync, moment, max_count, use_pctr_dnn_bn))
-    return len(_bn_tables) - 1
+    t = BnTable(name, bn_size, sync, moment, max_count, use_pctr_dnn_bn)
+    t.handle = len(_bn_tables)
+    _bn_tables.append(t)
+    return t.handle
 
 
 def bn_table(handle: int):

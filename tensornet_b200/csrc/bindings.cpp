@@ -120,6 +120,7 @@ struct SparseCtx {
     c.bar = ptr_of<unsigned>(comm["bar"].cast<at::Tensor>());
     c.status = ptr_of<int>(comm["status"].cast<at::Tensor>());
     c.wait_ns = comm["wait_ns"].cast<uint64_t>();
+    c.prof = comm.contains("prof") && !comm["prof"].is_none() ? ptr_of<unsigned long long>(comm["prof"].cast<at::Tensor>()) : nullptr;
     pull_lanes = tn::lanes_for_width_host(c.ustride);
     push_lanes = tn::lanes_for_width_host(t.dim);
   }
@@ -197,7 +198,7 @@ struct DenseCtx {
 void gemm(at::Tensor A, at::Tensor B, at::Tensor C, int M, int N, int K, int lda, int ldb, int ldc, bool a_mn, bool b_mn,
           bool accumulate, bool relu, c10::optional<at::Tensor> bias, c10::optional<at::Tensor> mask_aux,
           c10::optional<at::Tensor> had_x0, c10::optional<at::Tensor> had_xl, int ld_aux, int ones_col, int n_store,
-          int split_k, int BN, at::Tensor status) {
+          int split_k, int BN, at::Tensor status, c10::optional<at::Tensor> prof) {
   TORCH_CHECK(A.is_cuda() && B.is_cuda() && C.is_cuda(), "gemm: CUDA tensors");
   TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16, "gemm: bf16 operands");
   c10::cuda::CUDAGuard guard(A.device());
@@ -213,6 +214,7 @@ void gemm(at::Tensor A, at::Tensor B, at::Tensor C, int M, int N, int K, int lda
   d.had_xl = had_xl.has_value() ? had_xl->data_ptr() : nullptr;
   d.ld_aux = ld_aux; d.ones_col = ones_col; d.n_store = n_store; d.split_k = split_k; d.BN = BN;
   d.status = ptr_of<int>(status);
+  d.prof = prof.has_value() ? ptr_of<unsigned long long>(*prof) : nullptr;
   const char* err = tn::gemm_bf16(d, cur_stream());
   if (err) throw std::runtime_error(err);
 }
@@ -227,7 +229,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("pull", &SparseCtx::pull)
       .def("push", &SparseCtx::push);
   py::class_<DenseCtx>(m, "DenseCtx").def(py::init<py::dict>()).def("step", &DenseCtx::step);
-  m.def("gemm", &gemm);
+  m.def("gemm", &gemm, py::arg("A"), py::arg("B"), py::arg("C"), py::arg("M"), py::arg("N"), py::arg("K"), py::arg("lda"),
+        py::arg("ldb"), py::arg("ldc"), py::arg("a_mn"), py::arg("b_mn"), py::arg("accumulate"), py::arg("relu"), py::arg("bias"),
+        py::arg("mask_aux"), py::arg("had_x0"), py::arg("had_xl"), py::arg("ld_aux"), py::arg("ones_col"), py::arg("n_store"),
+        py::arg("split_k"), py::arg("BN"), py::arg("status"), py::arg("prof") = py::none());
   m.def("launch_count", []() { return g_launches.load(); });
 
   m.def("pool_fwd", [](at::Tensor U, int ustride, at::Tensor inverse, c10::optional<at::Tensor> offsets, int B, int S, int pd,

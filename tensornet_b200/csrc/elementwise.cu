@@ -58,52 +58,116 @@ __global__ void fm_bwd_kernel(const float* __restrict__ E, int ld, int B, int F,
   }
 }
 
-// ---- concat + cast ----------------------------------------------------------------------
-__global__ void concat_cast_kernel(const ConcatArgs a) {
-  const long long total = (long long)a.B * a.ld_out;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int b = (int)(i / a.ld_out), c = (int)(i - (long long)b * a.ld_out);
-    float v = 0.f;
-    if (c == a.ones_col) {
-      v = 1.f;
-    } else {
-      int off = 0;
-#pragma unroll
-      for (int p = 0; p < kMaxPieces; ++p) {
-        if (p < a.n_pieces) {
-          const int w = a.width[p];
-          if (c >= off && c < off + w) {
-            const size_t idx = (size_t)b * a.ld[p] + (c - off);
-            v = a.is_bf16[p] ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.ptr[p])[idx])
-                             : reinterpret_cast<const float*>(a.ptr[p])[idx];
-          }
-          off += w;
-        }
-      }
+// Vector variants for D % 4 == 0 with D/4 a power of two <= 32: a row is F*D/4 float4 chunks; lane l
+// always sees the same d-chunk (l mod D/4), so per-lane partial sums are combined with xor-shuffles
+// over the lanes that share it.
+__global__ void fm_fwd_vec_kernel(const float* __restrict__ E, int ld, int B, int F, int D, float* __restrict__ out) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  const int dq = D >> 2, nch = F * dq;
+  for (int b = warp; b < B; b += nwarps) {
+    const float4* e = reinterpret_cast<const float4*>(E + (size_t)b * ld);
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    float sq = 0.f;
+    for (int c = lane; c < nch; c += 32) {
+      const float4 x = e[c];
+      s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
+      sq += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
     }
-    reinterpret_cast<__nv_bfloat16*>(a.out)[i] = __float2bfloat16(v);
+    for (int o = 16; o >= dq; o >>= 1) {
+      s.x += __shfl_xor_sync(0xffffffffu, s.x, o); s.y += __shfl_xor_sync(0xffffffffu, s.y, o);
+      s.z += __shfl_xor_sync(0xffffffffu, s.z, o); s.w += __shfl_xor_sync(0xffffffffu, s.w, o);
+    }
+    float part = (lane < dq) ? (s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w) : 0.f;
+    part = warp_sum(part) - warp_sum(sq);
+    if (lane == 0) out[b] = 0.5f * part;
   }
 }
-// reverse: bf16 [B, ld_out] -> fp32 pieces (each piece written densely with its own ld)
-__global__ void split_cast_kernel(const ConcatArgs a) {
-  int total_w = 0;
-  for (int p = 0; p < a.n_pieces; ++p) total_w += a.width[p];
-  const long long total = (long long)a.B * total_w;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int b = (int)(i / total_w), c = (int)(i - (long long)b * total_w);
-    const float v = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.out)[(size_t)b * a.ld_out + c]);
-    int off = 0;
-    for (int p = 0; p < a.n_pieces; ++p) {
+__global__ void fm_bwd_vec_kernel(const float* __restrict__ E, int ld, int B, int F, int D, const float* __restrict__ gout,
+                                  float* __restrict__ gE, int gld, int accumulate) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  const int dq = D >> 2, nch = F * dq;
+  for (int b = warp; b < B; b += nwarps) {
+    const float4* e = reinterpret_cast<const float4*>(E + (size_t)b * ld);
+    float4* g = reinterpret_cast<float4*>(gE + (size_t)b * gld);
+    const float go = gout[b];
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int c = lane; c < nch; c += 32) {
+      const float4 x = e[c];
+      s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
+    }
+    for (int o = 16; o >= dq; o >>= 1) {
+      s.x += __shfl_xor_sync(0xffffffffu, s.x, o); s.y += __shfl_xor_sync(0xffffffffu, s.y, o);
+      s.z += __shfl_xor_sync(0xffffffffu, s.z, o); s.w += __shfl_xor_sync(0xffffffffu, s.w, o);
+    }
+    for (int c = lane; c < nch; c += 32) {
+      const float4 x = e[c];
+      float4 v = make_float4(go * (s.x - x.x), go * (s.y - x.y), go * (s.z - x.z), go * (s.w - x.w));
+      if (accumulate) { const float4 o4 = g[c]; v.x += o4.x; v.y += o4.y; v.z += o4.z; v.w += o4.w; }
+      g[c] = v;
+    }
+  }
+}
+
+// ---- concat + cast ----------------------------------------------------------------------
+__device__ __forceinline__ float concat_src(const ConcatArgs& a, int b, int c) {
+  if (c == a.ones_col) return 1.f;
+  int off = 0;
+#pragma unroll
+  for (int p = 0; p < kMaxPieces; ++p) {
+    if (p < a.n_pieces) {
       const int w = a.width[p];
       if (c >= off && c < off + w) {
-        if (a.ptr[p]) {
-          const size_t idx = (size_t)b * a.ld[p] + (c - off);
-          if (a.is_bf16[p]) reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(a.ptr[p]))[idx] = __float2bfloat16(v);
-          else reinterpret_cast<float*>(const_cast<void*>(a.ptr[p]))[idx] = v;
-        }
-        break;
+        const size_t idx = (size_t)b * a.ld[p] + (c - off);
+        return a.is_bf16[p] ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.ptr[p])[idx])
+                            : reinterpret_cast<const float*>(a.ptr[p])[idx];
       }
       off += w;
+    }
+  }
+  return 0.f;
+}
+// one thread = 8 consecutive output columns = one 16-byte store (ld_out is a multiple of 8)
+__global__ void concat_cast_kernel(const ConcatArgs a) {
+  const int cpr = a.ld_out >> 3;
+  const long long total = (long long)a.B * cpr;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int b = (int)(i / cpr), c0 = (int)(i - (long long)b * cpr) * 8;
+    float v[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] = concat_src(a, b, c0 + k);
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0], v[1]), p1 = __floats2bfloat162_rn(v[2], v[3]);
+    __nv_bfloat162 p2 = __floats2bfloat162_rn(v[4], v[5]), p3 = __floats2bfloat162_rn(v[6], v[7]);
+    uint4 o = make_uint4(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1),
+                         *reinterpret_cast<uint32_t*>(&p2), *reinterpret_cast<uint32_t*>(&p3));
+    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.out) + (size_t)b * a.ld_out + c0) = o;
+  }
+}
+// reverse: bf16 [B, ld_out] -> pieces (each piece written with its own ld); 8 columns per thread
+__global__ void split_cast_kernel(const ConcatArgs a) {
+  const int cpr = a.ld_out >> 3;
+  const long long total = (long long)a.B * cpr;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int b = (int)(i / cpr), c0 = (int)(i - (long long)b * cpr) * 8;
+    const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.out) + (size_t)b * a.ld_out + c0);
+    const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int c = c0 + k;
+      int off = 0;
+      for (int p = 0; p < a.n_pieces; ++p) {
+        const int w = a.width[p];
+        if (c >= off && c < off + w) {
+          if (a.ptr[p]) {
+            const size_t idx = (size_t)b * a.ld[p] + (c - off);
+            if (a.is_bf16[p]) reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(a.ptr[p]))[idx] = x[k];
+            else reinterpret_cast<float*>(const_cast<void*>(a.ptr[p]))[idx] = __bfloat162float(x[k]);
+          }
+          break;
+        }
+        off += w;
+      }
     }
   }
 }
@@ -145,6 +209,53 @@ __global__ void gemv_bwd_kernel(const __nv_bfloat16* __restrict__ Z, int ld, int
       acc += d * z;
     }
     if (k < K) s_gw[k] = acc;
+  }
+  __syncthreads();
+  for (int k = threadIdx.x; k < K; k += blockDim.x) atomicAdd(gw + k, s_gw[k]);
+}
+
+// Row-per-warp variant for ld <= 512: lane l owns column pairs (2l, 2l+1) + 64*i, keeps w and the
+// weight-gradient partial sums in registers, and streams Z / dZ with 4-byte accesses.
+__global__ void gemv_bwd_rows_kernel(const __nv_bfloat16* __restrict__ Z, int ld, int B, int K, const float* __restrict__ w,
+                                     const float* __restrict__ dy, __nv_bfloat16* __restrict__ dZ, float* __restrict__ gw,
+                                     int relu_cols) {
+  constexpr int kPairs = 8;
+  extern __shared__ float s_gw[];   // [ld]
+  for (int k = threadIdx.x; k < ld; k += blockDim.x) s_gw[k] = 0.f;
+  __syncthreads();
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  float2 wv[kPairs], acc[kPairs];
+#pragma unroll
+  for (int i = 0; i < kPairs; ++i) {
+    const int c = 64 * i + 2 * lane;
+    wv[i].x = c < K ? __ldg(w + c) : 0.f;
+    wv[i].y = c + 1 < K ? __ldg(w + c + 1) : 0.f;
+    acc[i] = make_float2(0.f, 0.f);
+  }
+  for (int b = warp; b < B; b += nwarps) {
+    const float d = dy[b];
+    const __nv_bfloat162* z = reinterpret_cast<const __nv_bfloat162*>(Z + (size_t)b * ld);
+    __nv_bfloat162* dz = reinterpret_cast<__nv_bfloat162*>(dZ + (size_t)b * ld);
+#pragma unroll
+    for (int i = 0; i < kPairs; ++i) {
+      const int c = 64 * i + 2 * lane;
+      if (c < ld) {
+        const float2 zz = __bfloat1622float2(z[32 * i + lane]);
+        float gx = d * wv[i].x, gy = d * wv[i].y;
+        if (c < relu_cols && !(zz.x > 0.f)) gx = 0.f;
+        if (c + 1 < relu_cols && !(zz.y > 0.f)) gy = 0.f;
+        dz[32 * i + lane] = __floats2bfloat162_rn(gx, gy);
+        acc[i].x += d * zz.x;
+        acc[i].y += d * zz.y;
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kPairs; ++i) {
+    const int c = 64 * i + 2 * lane;
+    if (c < K) atomicAdd(&s_gw[c], acc[i].x);
+    if (c + 1 < K) atomicAdd(&s_gw[c + 1], acc[i].y);
   }
   __syncthreads();
   for (int k = threadIdx.x; k < K; k += blockDim.x) atomicAdd(gw + k, s_gw[k]);
@@ -231,23 +342,38 @@ inline int blocks_for(long long work, int per_block) {
 
 }  // namespace
 
+static bool fm_vec_ok(const void* p, int ld, int D) {
+  const int dq = D >> 2;
+  return (D & 3) == 0 && dq >= 1 && dq <= 32 && (dq & (dq - 1)) == 0 && (ld & 3) == 0 && (reinterpret_cast<uintptr_t>(p) & 15) == 0;
+}
 void launch_fm_fwd(const float* E, int ld, int B, int F, int D, float* out, cudaStream_t st) {
+  if (fm_vec_ok(E, ld, D)) { fm_fwd_vec_kernel<<<blocks_for(B, 8), 256, 0, st>>>(E, ld, B, F, D, out); return; }
   fm_fwd_kernel<<<blocks_for(B, 8), 256, 0, st>>>(E, ld, B, F, D, out);
 }
 void launch_fm_bwd(const float* E, int ld, int B, int F, int D, const float* gout, float* gE, int gld, int accumulate, cudaStream_t st) {
+  if (fm_vec_ok(E, ld, D) && fm_vec_ok(gE, gld, D)) {
+    fm_bwd_vec_kernel<<<blocks_for(B, 8), 256, 0, st>>>(E, ld, B, F, D, gout, gE, gld, accumulate);
+    return;
+  }
   fm_bwd_kernel<<<blocks_for(B, 8), 256, 0, st>>>(E, ld, B, F, D, gout, gE, gld, accumulate);
 }
 void launch_concat_cast(const ConcatArgs& a, cudaStream_t st) {
-  concat_cast_kernel<<<blocks_for((long long)a.B * a.ld_out, 256), 256, 0, st>>>(a);
+  concat_cast_kernel<<<blocks_for((long long)a.B * (a.ld_out >> 3), 256), 256, 0, st>>>(a);
 }
 void launch_split_cast(const ConcatArgs& a, cudaStream_t st) {
-  split_cast_kernel<<<blocks_for((long long)a.B * a.ld_out, 256), 256, 0, st>>>(a);
+  split_cast_kernel<<<blocks_for((long long)a.B * (a.ld_out >> 3), 256), 256, 0, st>>>(a);
 }
 void launch_gemv_fwd(const void* Z, int ld, int B, int K, const float* w, float* y, cudaStream_t st) {
   gemv_fwd_kernel<<<blocks_for(B, 8), 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(Z), ld, B, K, w, y);
 }
 void launch_gemv_bwd(const void* Z, int ld, int B, int K, const float* w, const float* dy, void* dZ, float* gw, int relu_cols,
                      cudaStream_t st) {
+  if (ld <= 512 && (ld & 1) == 0) {
+    int nb = (B + 7) / 8; if (nb > 148 * 2) nb = 148 * 2; if (nb < 1) nb = 1;
+    gemv_bwd_rows_kernel<<<nb, 256, ld * sizeof(float), st>>>(reinterpret_cast<const __nv_bfloat16*>(Z), ld, B, K, w, dy,
+                                                             reinterpret_cast<__nv_bfloat16*>(dZ), gw, relu_cols);
+    return;
+  }
   int blocks = B / 32; if (blocks < 1) blocks = 1; if (blocks > 296) blocks = 296;
   gemv_bwd_kernel<<<blocks, 256, K * sizeof(float), st>>>(reinterpret_cast<const __nv_bfloat16*>(Z), ld, B, K, w, dy,
                                                           reinterpret_cast<__nv_bfloat16*>(dZ), gw, relu_cols);

@@ -34,7 +34,9 @@ constexpr int kBM = 128;        // tile rows (UMMA M)
 constexpr int kBK = 64;         // contraction elements per stage = one 128-byte swizzle row of bf16
 constexpr int kUmmaK = 16;
 constexpr int kABytes = kBM * kBK * 2;   // 16 KiB
-constexpr int kGemmThreads = 192;        // warp0 TMA, warp1 MMA + TMEM owner, warps 2..5 epilogue
+constexpr int kGemmThreads = 320;        // warp0 TMA, warp1 MMA + TMEM owner, warps 2..9 epilogue
+constexpr int kEpiWarps = 8;
+constexpr int kEpiBytesPerWarp = 12288;  // out block + two auxiliary blocks of 32 rows x 128 B
 constexpr unsigned kWaitSpins = 20u * 1000u * 1000u;   // ~ a second with the nanosleep below
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -102,14 +104,14 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+__device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, uint32_t* r) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
@@ -144,6 +146,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 
   uint32_t tmem_cols = 32;
   while ((int)tmem_cols < BN) tmem_cols <<= 1;
+  unsigned long long* prof = (p.prof && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.prof : nullptr;
+  if (prof && threadIdx.x == 0) prof[0] = globaltimer_ns();
 
   if (threadIdx.x == 0) {
     *s_abort = 0;
@@ -162,6 +166,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = s_tmem;
+  if (prof && threadIdx.x == 0) prof[1] = globaltimer_ns();
 
   if (warp == 0) {
     // ------------------------------- TMA producer ---------------------------------------
@@ -188,6 +193,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         }
       }
     }
+    __syncwarp();
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -----------------------------------------
     if (lane == 0) {
@@ -202,6 +208,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         const uint32_t ph = (uint32_t)(i / kStages) & 1u;
         if (!mbar_wait(smem_u32(&s_full[s]), ph, s_abort)) { *s_abort = 1; ok = false; break; }
         tc_fence_after();
+        if (prof && i < 8) prof[2 + i] = globaltimer_ns();
         const uint32_t a_base = a_smem + s * kABytes;
         const uint32_t b_base = b_smem + s * b_bytes;
 #pragma unroll
@@ -214,80 +221,182 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       }
       if (ok) umma_commit(smem_u32(&s_accum));
     }
+    __syncwarp();
   } else {
-    // ------------------------------- epilogue (warps 2..5) ------------------------------
+    // ------------------------------- epilogue (warps 2..9) ------------------------------
+    // Two warps share each TMEM lane quarter and take alternate column chunks.
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
-    const int row = m0 + q * 32 + lane;
+    const int half = (warp - 2) >> 2;       // 0 or 1: which of the alternating chunks
     bool ok = nk > 0;
     if (ok && !mbar_wait(smem_u32(&s_accum), 0u, s_abort)) { *s_abort = 1; ok = false; }
     tc_fence_after();
+    if (prof && warp == 2 && lane == 0) prof[10] = globaltimer_ns();
     if (ok) {
+      // The accumulator barrier has fired: every TMA load has landed and every MMA has read its
+      // operands, so the stage ring is free.  Each epilogue warp takes 12 KiB of it as a transpose
+      // buffer: TMEM gives a lane one ROW of the tile, global memory wants a warp on one LINE.
+      // Blocks of 32 rows x 128 bytes go through shared memory (16-byte pieces, XOR-swizzled by
+      // row so both the row-wise writes and the line-wise reads are bank-conflict free) and leave
+      // as full 128-byte lines.
+      uint8_t* smem_gen = smem_raw + (base - smem_u32(smem_raw));
+      uint8_t* sm_out = smem_gen + (warp - 2) * kEpiBytesPerWarp;
+      uint8_t* sm_a0 = sm_out + 4096;
+      uint8_t* sm_a1 = sm_out + 8192;
       const int n_store = p.n_store;
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        const int nb = n0 + c0;
-        if (nb >= n_store) break;           // warp-uniform
-        uint32_t r[16];
-        tmem_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
-        if (row >= p.M) continue;
-        float v[16];
+      const int row_base = m0 + q * 32;
+      const uint32_t tm_lane = tmem + ((uint32_t)(q * 32) << 16);
+      const int lrow = lane >> 3, lpc = lane & 7;          // line-wise mapping: 8 lanes per row
+      const bool has_aux = p.mask_aux != nullptr || p.had_x0 != nullptr;
+      const bool has_bias = p.bias != nullptr, relu = p.relu != 0;
+      if (!p.out_f32) {
+        for (int c0 = 64 * half; c0 < BN; c0 += 128) {
+          if (n0 + c0 >= n_store) break;                   // warp-uniform
+          if (has_aux) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
-        if (p.bias) {
+            for (int i = 0; i < 8; ++i) {
+              const int r = 4 * i + lrow;
+              const int grow = row_base + r, gcol = n0 + c0 + lpc * 8;
+              uint4 va = make_uint4(0u, 0u, 0u, 0u), vb = va;
+              if (grow < p.M && gcol + 8 <= p.ld_aux) {
+                const size_t off = (size_t)grow * p.ld_aux + gcol;
+                if (p.mask_aux) va = *reinterpret_cast<const uint4*>(p.mask_aux + off);
+                else { va = *reinterpret_cast<const uint4*>(p.had_x0 + off); vb = *reinterpret_cast<const uint4*>(p.had_xl + off); }
+              }
+              const int so = r * 128 + ((lpc ^ (r & 7)) << 4);
+              *reinterpret_cast<uint4*>(sm_a0 + so) = va;
+              if (p.had_x0) *reinterpret_cast<uint4*>(sm_a1 + so) = vb;
+            }
+            __syncwarp();
+          }
+          uint32_t acc[64];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) if (nb + j < p.N) v[j] += __ldg(p.bias + nb + j);
-        }
-        if (p.relu) {
+          for (int g = 0; g < 4; ++g) {
+            if (c0 + 16 * g < BN) tmem_ld16_nowait(tm_lane + (uint32_t)(c0 + 16 * g), acc + 16 * g);
+            else {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = fmaxf(v[j], 0.f);
-        }
-        if (p.mask_aux) {   // backward of ReLU: keep the gradient where the forward activation was positive
-          const __nv_bfloat16* mrow = p.mask_aux + (size_t)row * p.ld_aux + nb;
-#pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if (nb + j < n_store && !(__bfloat162float(mrow[j]) > 0.f)) v[j] = 0.f;
-        }
-        if (p.had_x0) {     // DCN-v2: x0 * (acc + bias) + xl
-          const __nv_bfloat16* x0 = p.had_x0 + (size_t)row * p.ld_aux + nb;
-          const __nv_bfloat16* xl = p.had_xl + (size_t)row * p.ld_aux + nb;
-#pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if (nb + j < p.N) v[j] = __bfloat162float(x0[j]) * v[j] + __bfloat162float(xl[j]);
-        }
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int n = nb + j;
-          if (n >= p.N) v[j] = (n == p.ones_col) ? 1.f : 0.f;
-        }
-        if (p.out_f32) {
-          float* crow = reinterpret_cast<float*>(p.C) + (size_t)row * p.ldc + nb;
-          if (nb + 16 <= n_store && p.accumulate) {
-#pragma unroll
-            for (int j = 0; j < 16; j += 4) red_add_f32x4(crow + j, make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]));
-          } else if (nb + 16 <= n_store) {
-#pragma unroll
-            for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(crow + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-          } else {
-            for (int j = 0; j < 16 && nb + j < n_store; ++j) {
-              if (p.accumulate) atomicAdd(crow + j, v[j]); else crow[j] = v[j];
+              for (int j = 0; j < 16; ++j) acc[16 * g + j] = 0u;
             }
           }
-        } else {
-          __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)row * p.ldc + nb;
-          if (nb + 16 <= n_store) {
-            uint4 lo = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
-            uint4 hi = make_uint4(pack_bf16(v[8], v[9]), pack_bf16(v[10], v[11]), pack_bf16(v[12], v[13]), pack_bf16(v[14], v[15]));
-            *reinterpret_cast<uint4*>(crow) = lo;
-            *reinterpret_cast<uint4*>(crow + 8) = hi;
-          } else {
-            for (int j = 0; j < 16 && nb + j < n_store; ++j) crow[j] = __float2bfloat16(v[j]);
+          tmem_ld_wait();
+#pragma unroll
+          for (int pc = 0; pc < 8; ++pc) {
+            const int nb = n0 + c0 + pc * 8;
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(acc[pc * 8 + j]);
+            if (has_bias) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) if (nb + j < p.N) v[j] += __ldg(p.bias + nb + j);
+            }
+            if (relu) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = fmaxf(v[j], 0.f);
+            }
+            const int so = lane * 128 + ((pc ^ (lane & 7)) << 4);
+            if (has_aux) {
+              const uint4 a0 = *reinterpret_cast<const uint4*>(sm_a0 + so);
+              const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&a0);
+              if (p.mask_aux) {   // backward of ReLU: keep the gradient where the forward activation was positive
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                  const float2 m2 = __bfloat1622float2(h0[k]);
+                  if (!(m2.x > 0.f)) v[2 * k] = 0.f;
+                  if (!(m2.y > 0.f)) v[2 * k + 1] = 0.f;
+                }
+              } else {            // DCN-v2: x0 * (acc + bias) + xl
+                const uint4 a1 = *reinterpret_cast<const uint4*>(sm_a1 + so);
+                const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&a1);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                  const float2 x0 = __bfloat1622float2(h0[k]), xl = __bfloat1622float2(h1[k]);
+                  v[2 * k] = x0.x * v[2 * k] + xl.x;
+                  v[2 * k + 1] = x0.y * v[2 * k + 1] + xl.y;
+                }
+              }
+            }
+            if (nb + 8 > p.N) {   // only the piece that straddles N pays for the ones / padding columns
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const int n = nb + j;
+                if (n >= p.N) v[j] = (n == p.ones_col) ? 1.f : 0.f;
+              }
+            }
+            *reinterpret_cast<uint4*>(sm_out + so) =
+                make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
           }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = 4 * i + lrow;
+            const int grow = row_base + r, gcol = n0 + c0 + lpc * 8;
+            if (grow < p.M && gcol < n_store && c0 + lpc * 8 < BN) {
+              const uint4 o = *reinterpret_cast<const uint4*>(sm_out + r * 128 + ((lpc ^ (r & 7)) << 4));
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)grow * p.ldc + gcol;
+              if (gcol + 8 <= n_store) {
+                *reinterpret_cast<uint4*>(dst) = o;
+              } else {
+                const __nv_bfloat16* ob = reinterpret_cast<const __nv_bfloat16*>(&o);
+                for (int j = 0; j < n_store - gcol; ++j) dst[j] = ob[j];
+              }
+            }
+          }
+          __syncwarp();
+        }
+      } else {
+        for (int c0 = 32 * half; c0 < BN; c0 += 64) {
+          if (n0 + c0 >= n_store) break;                   // warp-uniform
+          uint32_t acc[32];
+#pragma unroll
+          for (int g = 0; g < 2; ++g) {
+            if (c0 + 16 * g < BN) tmem_ld16_nowait(tm_lane + (uint32_t)(c0 + 16 * g), acc + 16 * g);
+            else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) acc[16 * g + j] = 0u;
+            }
+          }
+          tmem_ld_wait();
+#pragma unroll
+          for (int pc = 0; pc < 8; ++pc) {
+            const int nb = n0 + c0 + pc * 4;
+            float v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              v[j] = __uint_as_float(acc[pc * 4 + j]);
+              if (p.bias && nb + j < p.N) v[j] += __ldg(p.bias + nb + j);
+              if (p.relu) v[j] = fmaxf(v[j], 0.f);
+              if (nb + j >= p.N) v[j] = (nb + j == p.ones_col) ? 1.f : 0.f;
+            }
+            *reinterpret_cast<float4*>(sm_out + lane * 128 + ((pc ^ (lane & 7)) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
+          }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = 4 * i + lrow;
+            const int grow = row_base + r, gcol = n0 + c0 + lpc * 4;
+            if (grow < p.M && gcol < n_store && c0 + lpc * 4 < BN) {
+              const float4 o = *reinterpret_cast<const float4*>(sm_out + r * 128 + ((lpc ^ (r & 7)) << 4));
+              float* dst = reinterpret_cast<float*>(p.C) + (size_t)grow * p.ldc + gcol;
+              if (gcol + 4 <= n_store) {
+                if (p.accumulate) red_add_f32x4(dst, o); else *reinterpret_cast<float4*>(dst) = o;
+              } else {
+                const float ov[4] = {o.x, o.y, o.z, o.w};
+                for (int j = 0; j < n_store - gcol; ++j) {
+                  if (p.accumulate) atomicAdd(dst + j, ov[j]); else dst[j] = ov[j];
+                }
+              }
+            }
+          }
+          __syncwarp();
         }
       }
     }
   }
 
+  if (prof && warp == 2 && lane == 0) prof[11] = globaltimer_ns();
+  if (prof && warp == 6 && lane == 0) prof[13] = globaltimer_ns();
   tc_fence_before();
   __syncthreads();
+  if (prof && threadIdx.x == 0) prof[12] = globaltimer_ns();
   if (*s_abort) {
     // a wait ran out: report, give copies in flight time to land, then release TMEM
     if (threadIdx.x == 0) set_status(p.status, kMbarTimeout, 30, (int)blockIdx.x);
@@ -368,6 +477,13 @@ const char* gemm_bf16(const GemmDesc& d, cudaStream_t stream) {
   if ((d.lda % 8) || (d.ldb % 8)) return "gemm_bf16: leading dimensions must be multiples of 8 elements";
   if (d.out_f32 ? (d.ldc % 4) : (d.ldc % 8)) return "gemm_bf16: ldc alignment";
   if (reinterpret_cast<uintptr_t>(d.C) & 15) return "gemm_bf16: C must be 16-byte aligned";
+  if (d.mask_aux || d.had_x0) {
+    if (d.out_f32) return "gemm_bf16: mask / Hadamard epilogues need a bf16 output";
+    if (d.ld_aux % 8) return "gemm_bf16: ld_aux must be a multiple of 8 elements";
+    if ((reinterpret_cast<uintptr_t>(d.mask_aux) | reinterpret_cast<uintptr_t>(d.had_x0) | reinterpret_cast<uintptr_t>(d.had_xl)) & 15)
+      return "gemm_bf16: auxiliary operands must be 16-byte aligned";
+    if (d.had_x0 && !d.had_xl) return "gemm_bf16: Hadamard epilogue needs both x0 and xl";
+  }
 
   // tile N: multiple of 16 (64 when B is MN-major), chosen to keep the grid near one wave
   int n_cover = d.n_store > d.N ? d.n_store : d.N;
@@ -409,11 +525,14 @@ const char* gemm_bf16(const GemmDesc& d, cudaStream_t stream) {
   p.mask_aux = reinterpret_cast<const __nv_bfloat16*>(d.mask_aux);
   p.had_x0 = reinterpret_cast<const __nv_bfloat16*>(d.had_x0);
   p.had_xl = reinterpret_cast<const __nv_bfloat16*>(d.had_xl);
-  p.ld_aux = d.ld_aux; p.ones_col = d.ones_col; p.n_store = n_cover; p.bias = d.bias; p.status = d.status;
+  p.ld_aux = d.ld_aux; p.ones_col = d.ones_col; p.n_store = n_cover; p.bias = d.bias; p.status = d.status; p.prof = d.prof;
 
   dim3 grid((n_cover + BN - 1) / BN, (d.M + kBM - 1) / kBM, splits);
   const size_t b_bytes = (size_t)BN * kBK * 2;
+  const size_t epi_bytes = (size_t)kEpiWarps * kEpiBytesPerWarp + 1024;
   size_t smem4 = 4 * (kABytes + b_bytes) + 1024, smem3 = 3 * (kABytes + b_bytes) + 1024;
+  if (smem4 < epi_bytes) smem4 = epi_bytes;
+  if (smem3 < epi_bytes) smem3 = epi_bytes;
   static bool attr_set = false;
   if (!attr_set) {
     cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);

@@ -27,6 +27,7 @@ struct GemmDesc {
   int split_k = 1;
   int BN = 0;                // tile N override (0 = choose)
   int* status = nullptr;     // device error words
+  unsigned long long* prof = nullptr;   // optional [16] timestamps of CTA (0,0,0) for pipeline diagnosis
 };
 
 // Kernel-side parameter block.
@@ -40,6 +41,7 @@ struct GemmParams {
   int ld_aux, ones_col, n_store;
   const float* bias;
   int* status;
+  unsigned long long* prof;
 };
 
 // Returns nullptr on success, otherwise a static error string.

@@ -43,6 +43,60 @@ __global__ void pool_fwd_kernel(const float* __restrict__ U, int ustride, const 
   }
 }
 
+// pd % 4 == 0: every lane moves float4 chunks.
+__global__ void pool_fwd_vec4_kernel(const float* __restrict__ U, int ustride, const int* __restrict__ inverse,
+                                     const int* __restrict__ offsets, int B, int S, int pd, int combiner,
+                                     float* __restrict__ out, int out_ld, int G) {
+  const int lane = threadIdx.x % G;
+  const int gid = (blockIdx.x * blockDim.x + threadIdx.x) / G;
+  const int ngroups = (gridDim.x * blockDim.x) / G;
+  const int nbags = B * S, nch = pd >> 2;
+  for (int g = gid; g < nbags; g += ngroups) {
+    const int s = g / B, b = g - s * B;
+    int k0 = g, k1 = g + 1;
+    if (offsets) { k0 = offsets[g]; k1 = offsets[g + 1]; }
+    const float sc = bag_scale(combiner, k1 - k0);
+    float* o = out + (size_t)b * out_ld + (size_t)s * pd;
+    for (int ch = lane; ch < nch; ch += G) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int k = k0; k < k1; ++k) {
+        const int v = inverse[k];
+        if (v >= 0) {
+          const float4 x = ldcg_f4(U + (size_t)v * ustride + 4 * ch);
+          acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+        }
+      }
+      acc.x *= sc; acc.y *= sc; acc.z *= sc; acc.w *= sc;
+      *reinterpret_cast<float4*>(o + 4 * ch) = acc;
+    }
+  }
+}
+
+// dim % 4 == 0 and pd % 4 == 0: vector reductions into the unique-gradient rows.
+__global__ void pool_bwd_vec4_kernel(float* __restrict__ gU, int gstride, const int* __restrict__ inverse,
+                                     const int* __restrict__ offsets, int B, int S, int pd, int dim, int combiner,
+                                     const float* __restrict__ gout, int gout_ld, int G) {
+  const int lane = threadIdx.x % G;
+  const int gid = (blockIdx.x * blockDim.x + threadIdx.x) / G;
+  const int ngroups = (gridDim.x * blockDim.x) / G;
+  const int nbags = B * S, nch = dim >> 2;
+  for (int g = gid; g < nbags; g += ngroups) {
+    const int s = g / B, b = g - s * B;
+    int k0 = g, k1 = g + 1;
+    if (offsets) { k0 = offsets[g]; k1 = offsets[g + 1]; }
+    const float sc = bag_scale(combiner, k1 - k0);
+    const float* go = gout + (size_t)b * gout_ld + (size_t)s * pd;
+    for (int ch = lane; ch < nch; ch += G) {
+      float4 x = *reinterpret_cast<const float4*>(go + 4 * ch);
+      x.x *= sc; x.y *= sc; x.z *= sc; x.w *= sc;
+      for (int k = k0; k < k1; ++k) {
+        const int v = inverse[k];
+        if (v >= 0) red_add_f32x4(gU + (size_t)v * gstride + 4 * ch, x);
+      }
+    }
+  }
+}
+
 __global__ void pool_bwd_kernel(float* __restrict__ gU, int gstride, const int* __restrict__ inverse,
                                 const int* __restrict__ offsets, int B, int S, int pd, int dim, int combiner,
                                 const float* __restrict__ gout, int gout_ld, int G) {
@@ -113,12 +167,24 @@ inline int grid_for(long long groups, int G, int threads) {
 
 void launch_pool_fwd(const float* U, int ustride, const int* inverse, const int* offsets, int B, int S, int pd,
                      int combiner, float* out, int out_ld, cudaStream_t st) {
+  if ((pd & 3) == 0 && (out_ld & 3) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+    int G = lanes_for_width(pd);
+    pool_fwd_vec4_kernel<<<grid_for((long long)B * S, G, 256), 256, 0, st>>>(U, ustride, inverse, offsets, B, S, pd,
+                                                                               combiner, out, out_ld, G);
+    return;
+  }
   int G = pd >= 32 ? 32 : (pd >= 16 ? 16 : (pd >= 8 ? 8 : (pd >= 4 ? 4 : (pd >= 2 ? 2 : 1))));
   pool_fwd_kernel<<<grid_for((long long)B * S, G, 256), 256, 0, st>>>(U, ustride, inverse, offsets, B, S, pd, combiner,
                                                                         out, out_ld, G);
 }
 void launch_pool_bwd(float* gU, int gstride, const int* inverse, const int* offsets, int B, int S, int pd, int dim,
                      int combiner, const float* gout, int gout_ld, cudaStream_t st) {
+  if ((pd & 3) == 0 && (dim & 3) == 0 && (gout_ld & 3) == 0 && (reinterpret_cast<uintptr_t>(gout) & 15) == 0) {
+    int G = lanes_for_width(dim);
+    pool_bwd_vec4_kernel<<<grid_for((long long)B * S, G, 256), 256, 0, st>>>(gU, gstride, inverse, offsets, B, S, pd, dim,
+                                                                               combiner, gout, gout_ld, G);
+    return;
+  }
   int G = dim >= 32 ? 32 : (dim >= 16 ? 16 : (dim >= 8 ? 8 : (dim >= 4 ? 4 : (dim >= 2 ? 2 : 1))));
   pool_bwd_kernel<<<grid_for((long long)B * S, G, 256), 256, 0, st>>>(gU, gstride, inverse, offsets, B, S, pd, dim,
                                                                         combiner, gout, gout_ld, G);

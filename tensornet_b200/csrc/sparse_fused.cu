@@ -13,13 +13,18 @@
 //
 // Semantics that differ on purpose: the step is synchronous, and gradients of one sign
 // arriving from several GPUs (or several columns) are summed and applied once.
+//
+// Counters that every thread would otherwise hit (per-owner unique counts, the row slab
+// bump pointer, the owner-unique index) are advanced once per warp: lanes that need a slot
+// are found with a ballot, one lane adds the population count and the others take their
+// rank inside the ballot.
 #include "sparse_table.cuh"
 
 namespace tn {
 
 namespace {
 
-constexpr int kThreads = 256;
+constexpr int kThreads = 1024;
 enum SigKind { kSigPullReq = 0, kSigPullDone = 1, kSigPushReq = 2 };
 __device__ __forceinline__ unsigned long long* sig_word(unsigned long long* base, int kind, int src) {
   return base + kind * kMaxWorld + src;
@@ -30,6 +35,23 @@ __device__ __forceinline__ unsigned group_mask(int G) {
   unsigned lane = threadIdx.x & 31;
   return ((1u << G) - 1u) << (lane & ~(unsigned)(G - 1));
 }
+__device__ __forceinline__ unsigned lanemask_lt() {
+  unsigned m;
+  asm("mov.u32 %0, %%lanemask_lt;" : "=r"(m));
+  return m;
+}
+
+// Warp-aggregated "counter += 1 for every lane in `mask`"; returns this lane's old value.
+// Must be called by all 32 lanes; lanes outside `mask` get an unspecified value.
+__device__ __forceinline__ int warp_alloc(int* counter, unsigned mask) {
+  if (mask == 0) return 0;
+  const unsigned lane = threadIdx.x & 31;
+  const int leader = __ffs(mask) - 1;
+  int base = 0;
+  if ((int)lane == leader) base = atomicAdd(counter, __popc(mask));
+  base = __shfl_sync(0xffffffffu, base, leader);
+  return base + __popc(mask & lanemask_lt());
+}
 
 // Default value of stored-row element `e` (e < stride) for a brand-new row.
 __device__ __forceinline__ float new_row_elem(const SparseOptParams& o, unsigned long long key, int e, int dim) {
@@ -38,23 +60,8 @@ __device__ __forceinline__ float new_row_elem(const SparseOptParams& o, unsigned
   return 0.f;  // slots, show, click; int fields are bit-zero
 }
 
-// Claim (or read) this step's owner-unique index of an existing row.
-__device__ __forceinline__ int claim_ou(const SparseCommView& c, unsigned long long* tag, int r, unsigned long long epoch,
-                                        bool* is_new_this_step) {
-  unsigned long long t = *((volatile unsigned long long*)tag);
-  *is_new_this_step = false;
-  if ((t >> 32) == epoch) {
-    *is_new_this_step = (t & kTagNew) != 0;
-    return (int)(t & 0x7fffffffull);
-  }
-  int ou = atomicAdd(c.ocount, 1);
-  unsigned long long old = atomicCAS(tag, t, (epoch << 32) | (unsigned long long)ou);
-  if (old == t) {
-    c.ou_row[ou] = r;
-    return ou;
-  }
-  c.ou_row[ou] = -1;  // hole: someone else claimed the row first
-  return (int)(old & 0x7fffffffull);
+__device__ __forceinline__ void prof_mark(const SparseCommView& c, int slot) {
+  if (c.prof != nullptr && blockIdx.x == 0 && threadIdx.x == 0) c.prof[slot] = globaltimer_ns();
 }
 
 }  // namespace
@@ -62,7 +69,7 @@ __device__ __forceinline__ int claim_ou(const SparseCommView& c, unsigned long l
 // =======================================================================================
 // sparse_pull_fused
 // =======================================================================================
-__global__ void __launch_bounds__(kThreads) sparse_pull_fused_kernel(const __grid_constant__ PullArgs a) {
+__global__ void __launch_bounds__(kThreads, 1) sparse_pull_fused_kernel(const __grid_constant__ PullArgs a) {
   const SparseCommView& c = a.c;
   const TableView& t = a.tbl;
   GridSync gs;
@@ -72,39 +79,60 @@ __global__ void __launch_bounds__(kThreads) sparse_pull_fused_kernel(const __gri
 
   const int tid = blockIdx.x * blockDim.x + threadIdx.x;
   const int nth = gridDim.x * blockDim.x;
+  const int lane = threadIdx.x & 31;
   const int W = c.world, R = c.rank, capo = c.capo;
   const unsigned long long epoch = __ldcg(c.epoch) + 1ull;
   const int dim = t.dim;
-
-  if (tid == 0) *c.ocount = 0;
   const bool need_ou = a.training && W > 1;
 
+  if (tid == 0) *c.ocount = 0;
+  prof_mark(c, 0);
+
   // ---- phase A: dedup; first occurrence of a sign allocates a slot in its owner's segment --------
-  for (int i = tid; i < a.n_ids; i += nth) {
-    unsigned long long key = canon_key((unsigned long long)a.ids[i]);
-    unsigned h = (unsigned)mix64(key ^ 0x2545F4914F6CDD1Dull) & c.dd_mask;
-    bool done = false;
-    for (unsigned probes = 0; probes <= c.dd_mask; ++probes) {
-      unsigned long long old = atomicCAS(&c.dd_keys[h], kEmptyKey, key);
-      if (old == kEmptyKey) {
-        int owner = owner_of(key, W);
-        int pos = atomicAdd(&c.cnt[owner], 1);
-        if (pos >= capo) {
-          set_status(c.status, kOwnerSegOverflow, 1, owner);
-          c.dd_vals[h] = -1;
-        } else {
-          c.stage_ids[owner * capo + pos] = key;
-          c.dd_vals[h] = owner * capo + pos;
-        }
-        done = true;
-        break;
+  for (int base = tid - lane; base < a.n_ids; base += nth) {
+    const int i = base + lane;
+    bool winner = false;
+    unsigned hw = 0;
+    unsigned long long key = 0;
+    if (i < a.n_ids) {
+      key = canon_key((unsigned long long)a.ids[i]);
+      unsigned h = (unsigned)mix64(key ^ 0x2545F4914F6CDD1Dull) & c.dd_mask;
+      bool done = false;
+      for (unsigned probes = 0; probes <= c.dd_mask; ++probes) {
+        unsigned long long old = atomicCAS(&c.dd_keys[h], kEmptyKey, key);
+        if (old == kEmptyKey) { winner = true; hw = h; done = true; break; }
+        if (old == key) { done = true; break; }
+        h = (h + 1) & c.dd_mask;
       }
-      if (old == key) { done = true; break; }
-      h = (h + 1) & c.dd_mask;
+      if (!done) set_status(c.status, kDedupOverflow, 1, 0);
     }
-    if (!done) set_status(c.status, kDedupOverflow, 1, 0);
+    __syncwarp();
+    int owner = 0, pos = 0;
+    if (W == 1) {
+      pos = warp_alloc(&c.cnt[0], __ballot_sync(0xffffffffu, winner));
+    } else {
+      owner = winner ? owner_of(key, W) : -1;
+      const unsigned peers = __match_any_sync(0xffffffffu, owner);
+      if (winner) {
+        const int leader = __ffs(peers) - 1;
+        int b = 0;
+        if (lane == leader) b = atomicAdd(&c.cnt[owner], __popc(peers));
+        b = __shfl_sync(peers, b, leader);
+        pos = b + __popc(peers & lanemask_lt());
+      }
+    }
+    if (winner) {
+      if (pos >= capo) {
+        set_status(c.status, kOwnerSegOverflow, 1, owner);
+        c.dd_vals[hw] = -1;
+      } else {
+        c.stage_ids[owner * capo + pos] = key;
+        c.dd_vals[hw] = owner * capo + pos;
+      }
+    }
   }
   if (!gs.sync(1, false)) goto done;
+  prof_mark(c, 1);
 
   // ---- phase A2: inverse map, show/click counts; ship id segments to the owners -------------------
   for (int i = tid; i < a.n_ids; i += nth) {
@@ -145,6 +173,7 @@ __global__ void __launch_bounds__(kThreads) sparse_pull_fused_kernel(const __gri
       st_release_sys_u64(sig_word(c.sig[p], kSigPullReq, R), (epoch << 32) | (unsigned long long)n);
     }
   }
+  prof_mark(c, 2);
 
   // ---- phase B1: as owner, probe / insert every requested sign ------------------------------------
   for (int si = 0; si < W; ++si) {
@@ -165,66 +194,89 @@ __global__ void __launch_bounds__(kThreads) sparse_pull_fused_kernel(const __gri
     if (threadIdx.x == 0) s_n[s] = n_s;
     if (tid == 0) c.req_n[s] = n_s;
     const unsigned long long* src = (s == R) ? c.stage_ids + (size_t)R * capo : c.inbox_ids[R] + (size_t)s * capo;
-    for (int j = tid; j < n_s; j += nth) {
-      const unsigned long long key = __ldcg(&src[j]);
-      const int q = s * capo + j;
-      unsigned h = table_home(t, key);
+    for (int base = tid - lane; base < n_s; base += nth) {
+      const int j = base + lane;
+      const bool valid = j < n_s;
       int rr = kReqNone, ou = -1;
-      bool placed = false;
-      for (unsigned probes = 0; probes <= t.cap_mask && !placed; ++probes) {
-        unsigned long long k = __ldcg(&t.keys[h]);
-        if (k == kEmptyKey) {
-          k = atomicCAS(&t.keys[h], kEmptyKey, key);
-          if (k == kEmptyKey) {  // this thread owns the new key
-            int r = atomicAdd(t.n_rows, 1);
-            if (r >= t.row_cap) {
-              atomicSub(t.n_rows, 1);
-              set_status(c.status, kTableFull, 3, s);
-              t.slots[h] = -3;
-            } else {
-              t.row_keys[r] = key;
-              unsigned long long tag = (epoch << 32) | kTagNew;
-              if (need_ou) {
-                ou = atomicAdd(c.ocount, 1);
-                c.ou_row[ou] = r;
-                tag |= (unsigned long long)ou;
+      bool is_new = false, need_claim = false;
+      unsigned hnew = 0;
+      int r_exist = -1;
+      unsigned long long tag_seen = 0, key = 0;
+      if (valid) {
+        key = __ldcg(&src[j]);
+        unsigned h = table_home(t, key);
+        bool placed = false;
+        for (unsigned probes = 0; probes <= t.cap_mask; ++probes) {
+          unsigned long long k = __ldcg(&t.keys[h]);
+          if (k == kEmptyKey) {
+            k = atomicCAS(&t.keys[h], kEmptyKey, key);
+            if (k == kEmptyKey) { is_new = true; hnew = h; placed = true; break; }
+          }
+          if (k == key) {
+            const int r = ld_volatile_s32(&t.slots[h]);
+            if (r == -1) {          // inserter has not published the row yet: resolve after the barrier
+              rr = kReqPending;
+              ou = (int)h;
+            } else if (r >= 0) {
+              rr = r;
+              if (W > 1) {
+                const unsigned long long tg = *((volatile unsigned long long*)&t.row_tag[r]);
+                if ((tg >> 32) == epoch) {
+                  if (tg & kTagNew) rr = r | kReqNewCopy;
+                  if (need_ou) ou = (int)(tg & 0x7fffffffull);
+                } else if (need_ou) {
+                  need_claim = true; r_exist = r; tag_seen = tg;
+                }
               }
-              t.row_tag[r] = tag;
-              __threadfence();
-              *((volatile int*)&t.slots[h]) = r;
-              rr = r | kReqNewOwner;
             }
             placed = true;
             break;
           }
+          h = (h + 1) & t.cap_mask;
         }
-        if (k == key) {
-          int r = ld_volatile_s32(&t.slots[h]);
-          if (r == -1) {          // inserter has not published the row yet: resolve after the barrier
-            rr = kReqPending;
-            ou = (int)h;
-          } else if (r >= 0) {
-            bool fresh = false;
-            if (need_ou) {
-              ou = claim_ou(c, &t.row_tag[r], r, epoch, &fresh);
-            } else if (W > 1) {
-              unsigned long long tg = *((volatile unsigned long long*)&t.row_tag[r]);
-              fresh = (tg >> 32) == epoch && (tg & kTagNew);
-            }
-            rr = fresh ? (r | kReqNewCopy) : r;
-          }
-          placed = true;
-          break;
-        }
-        h = (h + 1) & t.cap_mask;
+        if (!placed) set_status(c.status, kTableFull, 3, s);
       }
-      if (!placed) set_status(c.status, kTableFull, 3, s);
-      c.req_row[q] = rr;
-      c.req_ou[q] = ou;
+      __syncwarp();
+      const unsigned nm = __ballot_sync(0xffffffffu, is_new);
+      const unsigned cm = __ballot_sync(0xffffffffu, need_claim);
+      const int r_new = warp_alloc(t.n_rows, nm);
+      int my_ou = -1;
+      if (need_ou) my_ou = warp_alloc(c.ocount, nm | cm);
+      if (is_new) {
+        if (r_new >= t.row_cap) {
+          atomicSub(t.n_rows, 1);
+          set_status(c.status, kTableFull, 3, s);
+          *((volatile int*)&t.slots[hnew]) = -3;
+          if (need_ou) c.ou_row[my_ou] = -1;
+        } else {
+          t.row_keys[r_new] = key;
+          unsigned long long tag = (epoch << 32) | kTagNew;
+          if (need_ou) { c.ou_row[my_ou] = r_new; tag |= (unsigned long long)my_ou; ou = my_ou; }
+          t.row_tag[r_new] = tag;
+          __threadfence();
+          *((volatile int*)&t.slots[hnew]) = r_new;
+          rr = r_new | kReqNewOwner;
+        }
+      } else if (need_claim) {
+        const unsigned long long old = atomicCAS(&t.row_tag[r_exist], tag_seen, (epoch << 32) | (unsigned long long)my_ou);
+        if (old == tag_seen) {
+          c.ou_row[my_ou] = r_exist;
+          ou = my_ou;
+        } else {                     // another sender claimed the row first: my index stays a hole
+          c.ou_row[my_ou] = -1;
+          ou = (int)(old & 0x7fffffffull);
+        }
+      }
+      if (valid) {
+        const int q = s * capo + j;
+        c.req_row[q] = rr;
+        c.req_ou[q] = ou;
+      }
     }
   }
   if (gs.failed) goto done;
   if (!gs.sync(4, false)) goto done;
+  prof_mark(c, 3);
 
   if (blockIdx.x == 0 && threadIdx.x < W) {  // counts of this step for pooling / push, then re-arm
     c.cnt_saved[threadIdx.x] = min(c.cnt[threadIdx.x], capo);
@@ -234,7 +286,7 @@ __global__ void __launch_bounds__(kThreads) sparse_pull_fused_kernel(const __gri
   // ---- phase B2: initialise new rows, write rows straight into each requester's matrix -----------
   {
     const int G = a.lanes;
-    const int lane = threadIdx.x % G;
+    const int gl = threadIdx.x % G;
     const int gid = tid / G, ngroups = nth / G;
     const int ustride = c.ustride, stride = t.stride;
     const int uchunks = ustride >> 2, rchunks = stride >> 2;
@@ -254,17 +306,17 @@ __global__ void __launch_bounds__(kThreads) sparse_pull_fused_kernel(const __gri
             unsigned long long tg = __ldcg(&t.row_tag[r]);
             bool fresh = (tg >> 32) == epoch && (tg & kTagNew);
             rr = fresh ? (r | kReqNewCopy) : r;
-            if (lane == 0) {
+            if (gl == 0) {
               c.req_row[q] = rr;
               c.req_ou[q] = need_ou ? (int)(tg & 0x7fffffffull) : -1;
             }
           } else {
             rr = kReqNone;
-            if (lane == 0) { c.req_row[q] = kReqNone; c.req_ou[q] = -1; }
+            if (gl == 0) { c.req_row[q] = kReqNone; c.req_ou[q] = -1; }
           }
         }
         if (rr == kReqNone) {
-          for (int ch = lane; ch < uchunks; ch += G)
+          for (int ch = gl; ch < uchunks; ch += G)
             *reinterpret_cast<float4*>(dst + 4 * ch) = make_float4(0.f, 0.f, 0.f, 0.f);
           continue;
         }
@@ -274,7 +326,7 @@ __global__ void __launch_bounds__(kThreads) sparse_pull_fused_kernel(const __gri
           const unsigned long long key = __ldcg(&src[j]);
           const bool write_row = (rr & kReqNewOwner) != 0;
           const int nch = write_row ? max(rchunks, uchunks) : uchunks;
-          for (int ch = lane; ch < nch; ch += G) {
+          for (int ch = gl; ch < nch; ch += G) {
             float4 v;
             v.x = new_row_elem(o, key, 4 * ch + 0, dim);
             v.y = new_row_elem(o, key, 4 * ch + 1, dim);
@@ -294,48 +346,49 @@ __global__ void __launch_bounds__(kThreads) sparse_pull_fused_kernel(const __gri
         } else {
           float show = 0.f, click = 0.f;
           if (t.use_cvm && o.kind == kAdaGrad) { show = row[dim + 1]; click = row[dim + 2]; }
-          for (int ch = lane; ch < uchunks; ch += G) {
-            float4 v = *reinterpret_cast<const float4*>(row + 4 * ch);  // stride >= ustride - 2 is guaranteed by layout
-            float e[4] = {v.x, v.y, v.z, v.w};
+          for (int ch = gl; ch < uchunks; ch += G) {
+            float4 v = *reinterpret_cast<const float4*>(row + 4 * ch);  // stride >= ustride by layout
+            if (4 * ch + 4 > dim) {
+              float e[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              int idx = 4 * ch + k;
-              if (idx >= dim) {
-                float x = 0.f;
-                if (t.use_cvm && o.kind == kAdaGrad) {
-                  if (idx == dim) x = show;
-                  else if (idx == dim + 1) x = logf(click + 1.f) - logf(show + 1.f);
+              for (int k = 0; k < 4; ++k) {
+                int idx = 4 * ch + k;
+                if (idx >= dim) {
+                  float x = 0.f;
+                  if (t.use_cvm && o.kind == kAdaGrad) {
+                    if (idx == dim) x = show;
+                    else if (idx == dim + 1) x = logf(click + 1.f) - logf(show + 1.f);
+                  }
+                  e[k] = x;
                 }
-                e[k] = x;
               }
+              v = make_float4(e[0], e[1], e[2], e[3]);
             }
-            *reinterpret_cast<float4*>(dst + 4 * ch) = make_float4(e[0], e[1], e[2], e[3]);
+            *reinterpret_cast<float4*>(dst + 4 * ch) = v;
           }
         }
       }
     }
   }
+  prof_mark(c, 4);
 
-  if (W > 1) {
-    if (!gs.sync(5, true)) goto done;
-    if (blockIdx.x == 0 && threadIdx.x < W && threadIdx.x != R)
-      st_release_sys_u64(sig_word(c.sig[threadIdx.x], kSigPullDone, R), epoch << 32);
-  } else {
-    if (!gs.sync(5, false)) goto done;
-  }
-
-  // ---- phase C: clear the dedup scratch while the owners' rows arrive ----------------------------
+  // ---- phase C: clear the dedup scratch; tell the requesters their rows have landed ---------------
   {
     ulonglong2* kk = reinterpret_cast<ulonglong2*>(c.dd_keys);
     const int n2 = (int)((c.dd_mask + 1u) >> 1);
     for (int i = tid; i < n2; i += nth) kk[i] = make_ulonglong2(kEmptyKey, kEmptyKey);
   }
-  if (W > 1 && blockIdx.x == 0 && threadIdx.x < W && threadIdx.x != R) {
-    unsigned long long v;
-    wait_flag_ge(sig_word(c.sig[R], kSigPullDone, threadIdx.x), epoch, &v, c.wait_ns, c.status, 6, threadIdx.x);
+  if (W > 1) {
+    if (!gs.sync(5, true)) goto done;
+    if (blockIdx.x == 0 && threadIdx.x < W && threadIdx.x != R) {
+      st_release_sys_u64(sig_word(c.sig[threadIdx.x], kSigPullDone, R), epoch << 32);
+      unsigned long long v;
+      wait_flag_ge(sig_word(c.sig[R], kSigPullDone, threadIdx.x), epoch, &v, c.wait_ns, c.status, 6, threadIdx.x);
+    }
+    __syncthreads();
   }
-  __syncthreads();
   if (tid == 0) *c.epoch = epoch;
+  prof_mark(c, 5);
 
 done:
   gs.leave();
@@ -348,16 +401,34 @@ namespace {
 
 // One optimizer step on one row by a group of G lanes.  `g` points at the gradient record:
 // grad[dim] | show | click.   Math as in the reference's Sparse*Value::Apply.
+// VEC: dim is a multiple of 4, every lane works on float4 chunks.
+template <bool VEC>
 __device__ __forceinline__ void apply_row(const SparseOptParams& o, float* row, const float* g, int dim, int lane, int G,
                                           unsigned gmask) {
   const float bshow = g[dim], bclick = g[dim + 1];
   if (o.kind == kAdaGrad) {
     float ss = 0.f;
-    for (int e = lane; e < dim; e += G) { float x = g[e]; ss += x * x; }
+    if (VEC) {
+      for (int ch = lane; ch < (dim >> 2); ch += G) {
+        const float4 x = *reinterpret_cast<const float4*>(g + 4 * ch);
+        ss += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+      }
+    } else {
+      for (int e = lane; e < dim; e += G) { float x = g[e]; ss += x * x; }
+    }
     for (int off = G >> 1; off > 0; off >>= 1) ss += __shfl_xor_sync(gmask, ss, off);
-    float g2 = row[dim] + ss / (float)dim;
-    float scale = o.lr / (o.eps + sqrtf(g2));
-    for (int e = lane; e < dim; e += G) row[e] -= scale * g[e];
+    const float g2 = row[dim] + ss / (float)dim;
+    const float scale = o.lr / (o.eps + sqrtf(g2));
+    if (VEC) {
+      for (int ch = lane; ch < (dim >> 2); ch += G) {
+        const float4 x = *reinterpret_cast<const float4*>(g + 4 * ch);
+        float4 w = *reinterpret_cast<float4*>(row + 4 * ch);
+        w.x -= scale * x.x; w.y -= scale * x.y; w.z -= scale * x.z; w.w -= scale * x.w;
+        *reinterpret_cast<float4*>(row + 4 * ch) = w;
+      }
+    } else {
+      for (int e = lane; e < dim; e += G) row[e] -= scale * g[e];
+    }
     __syncwarp(gmask);
     if (lane == 0) {
       row[dim] = g2;
@@ -368,12 +439,29 @@ __device__ __forceinline__ void apply_row(const SparseOptParams& o, float* row, 
   } else if (o.kind == kAdam) {
     float* m = row + dim;
     float* v = row + 2 * dim;
-    for (int e = lane; e < dim; e += G) {
-      float x = g[e];
-      float mm = o.beta1 * m[e] + (1.f - o.beta1) * x;
-      float vv = o.beta2 * v[e] + (1.f - o.beta2) * x * x;
-      m[e] = mm; v[e] = vv;
-      row[e] -= o.lr * mm / (o.eps + sqrtf(vv));
+    const float c1 = 1.f - o.beta1, c2 = 1.f - o.beta2;
+    if (VEC) {
+      for (int ch = lane; ch < (dim >> 2); ch += G) {
+        const float4 x = *reinterpret_cast<const float4*>(g + 4 * ch);
+        float4 mm = *reinterpret_cast<float4*>(m + 4 * ch), vv = *reinterpret_cast<float4*>(v + 4 * ch);
+        float4 w = *reinterpret_cast<float4*>(row + 4 * ch);
+#define TN_SADAM(cmp) \
+        mm.cmp = o.beta1 * mm.cmp + c1 * x.cmp; vv.cmp = o.beta2 * vv.cmp + c2 * x.cmp * x.cmp; \
+        w.cmp -= o.lr * mm.cmp / (o.eps + sqrtf(vv.cmp));
+        TN_SADAM(x) TN_SADAM(y) TN_SADAM(z) TN_SADAM(w)
+#undef TN_SADAM
+        *reinterpret_cast<float4*>(m + 4 * ch) = mm;
+        *reinterpret_cast<float4*>(v + 4 * ch) = vv;
+        *reinterpret_cast<float4*>(row + 4 * ch) = w;
+      }
+    } else {
+      for (int e = lane; e < dim; e += G) {
+        float x = g[e];
+        float mm = o.beta1 * m[e] + c1 * x;
+        float vv = o.beta2 * v[e] + c2 * x * x;
+        m[e] = mm; v[e] = vv;
+        row[e] -= o.lr * mm / (o.eps + sqrtf(vv));
+      }
     }
     if (lane == 0) reinterpret_cast<int*>(row)[3 * dim + 1] += (int)bshow;
   } else {
@@ -397,7 +485,7 @@ __device__ __forceinline__ void apply_row(const SparseOptParams& o, float* row, 
 
 }  // namespace
 
-__global__ void __launch_bounds__(kThreads) sparse_push_fused_kernel(const __grid_constant__ PushArgs a) {
+__global__ void __launch_bounds__(kThreads, 1) sparse_push_fused_kernel(const __grid_constant__ PushArgs a) {
   const SparseCommView& c = a.c;
   const TableView& t = a.tbl;
   GridSync gs;
@@ -414,6 +502,7 @@ __global__ void __launch_bounds__(kThreads) sparse_push_fused_kernel(const __gri
   const int gid = tid / G, ngroups = nth / G;
   const unsigned gmask = group_mask(G);
   const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  const bool vec = (dim & 3) == 0;
 
   if (W == 1) {
     // single GPU: every unique sign of the batch maps to exactly one row; update in place
@@ -421,8 +510,11 @@ __global__ void __launch_bounds__(kThreads) sparse_push_fused_kernel(const __gri
     for (int j = gid; j < n; j += ngroups) {
       int rr = __ldcg(&c.req_row[j]);
       float* g = c.gU + (size_t)j * gstride;
-      if (rr != kReqNone && rr != kReqPending)
-        apply_row(a.opt, t.rows + (size_t)(rr & kReqRowMask) * t.stride, g, dim, lane, G, gmask);
+      if (rr != kReqNone && rr != kReqPending) {
+        float* row = t.rows + (size_t)(rr & kReqRowMask) * t.stride;
+        if (vec) apply_row<true>(a.opt, row, g, dim, lane, G, gmask);
+        else apply_row<false>(a.opt, row, g, dim, lane, G, gmask);
+      }
       __syncwarp(gmask);
       for (int ch = lane; ch < gch; ch += G) *reinterpret_cast<float4*>(g + 4 * ch) = zero4;
     }
@@ -476,7 +568,11 @@ __global__ void __launch_bounds__(kThreads) sparse_push_fused_kernel(const __gri
     for (int ou = gid; ou < n_ou; ou += ngroups) {
       const int r = __ldcg(&c.ou_row[ou]);
       float* g = c.acc + (size_t)ou * gstride;
-      if (r >= 0) apply_row(a.opt, t.rows + (size_t)r * t.stride, g, dim, lane, G, gmask);
+      if (r >= 0) {
+        float* row = t.rows + (size_t)r * t.stride;
+        if (vec) apply_row<true>(a.opt, row, g, dim, lane, G, gmask);
+        else apply_row<false>(a.opt, row, g, dim, lane, G, gmask);
+      }
       __syncwarp(gmask);
       for (int ch = lane; ch < gch; ch += G) *reinterpret_cast<float4*>(g + 4 * ch) = zero4;
     }
@@ -494,7 +590,7 @@ static int coop_grid(const void* fn, int device) {
   cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kThreads, 0);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   if (per_sm < 1) per_sm = 1;
-  if (per_sm > 2) per_sm = 2;
+  if (per_sm > 1) per_sm = 1;
   return per_sm * sms;
 }
 

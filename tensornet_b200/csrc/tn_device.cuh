@@ -35,7 +35,7 @@ __device__ __forceinline__ void set_status(int* status, int code, int phase, int
 
 __device__ __forceinline__ unsigned long long globaltimer_ns() {
   unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t) :: "memory");
   return t;
 }
 

@@ -58,6 +58,7 @@ struct SparseCommView {
   unsigned* bar;                             // [2] grid barrier words (zero between launches)
   int* status;                               // [4] error words
   unsigned long long wait_ns;                // budget of every wait inside the kernels
+  unsigned long long* prof;                  // optional [8] phase timestamps (globaltimer ns) written by CTA 0
 };
 
 struct PullArgs {

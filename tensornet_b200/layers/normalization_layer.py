@@ -1,0 +1,123 @@
+"""Batch normalisation driven by GLOBAL statistics (tensornet/layers/normalization_layer.py:26-242).
+
+Every training batch contributes its per-feature sum / squared sum / count to the BN table;
+the layer always normalises with the table's global mean and variance (treated as
+constants, so no gradient flows through the statistics).  With ``synchronized=True`` the
+increments are exchanged between ranks every ``sync_freq`` batches; otherwise rank 0 gathers
+them once before saving.  ``PCTRDNNBatchNormalization`` accumulates the squared deviation
+from the current global mean instead of the raw squared sum.
+"""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from .. import core
+
+
+class TNBatchNormalizationBase(nn.Module):
+    _USE_PCTR_DNN_BN = False
+
+    def __init__(self, num_features: int = 0, center=True, scale=True, epsilon=1e-5, momentum=0.99, name=None,
+                 synchronized=False, sync_freq=1, max_count=100000):
+        super().__init__()
+        self.center, self.scale, self.epsilon, self.momentum = center, scale, epsilon, momentum
+        self.synchronized, self.sync_freq, self.max_count = synchronized, sync_freq, max_count
+        self.layer_name = name or "tn_batch_normalization"
+        self.batch_counter = 0
+        self.bn_table_handle = None
+        self.gamma = self.beta = None
+        if num_features:
+            self._build(num_features)
+
+    def _build(self, c: int):
+        dev = core.runtime().device
+        self.num_features = c
+        if self.scale:
+            self.gamma = nn.Parameter(torch.ones(c, device=dev))
+        if self.center:
+            self.beta = nn.Parameter(torch.zeros(c, device=dev))
+        self.register_buffer("moving_mean", torch.zeros(c, device=dev))
+        self.register_buffer("moving_variance", torch.ones(c, device=dev))
+        self.bn_table_handle = core.create_bn_table(self.layer_name, c, self.synchronized, self.momentum, self.max_count,
+                                                    self._USE_PCTR_DNN_BN)
+        self.table = core.bn_table(self.bn_table_handle)
+        self.table.handle = self.bn_table_handle
+
+    # ---- table plumbing --------------------------------------------------------------------
+    def _local_stats(self, x: torch.Tensor, center=None):
+        x2 = x.detach().reshape(-1, x.shape[-1]).double()
+        s = x2.sum(dim=0)
+        q = ((x2 - center.double()) ** 2).sum(dim=0) if center is not None else (x2 * x2).sum(dim=0)
+        n = torch.full_like(s, float(x2.shape[0]))
+        return s.cpu().numpy(), q.cpu().numpy(), n.cpu().numpy()
+
+    def bn_statistics_push(self, stats, synchronized: bool):
+        self.table.append(*stats, is_local=True)
+        if synchronized:
+            self.table.sync_increments()
+
+    def _push_counted(self, stats):
+        if self.synchronized:
+            self.batch_counter += 1
+            if self.batch_counter == self.sync_freq:
+                self.bn_statistics_push(stats, True)
+                self.batch_counter = 0
+            else:
+                self.bn_statistics_push(stats, False)
+        else:
+            self.bn_statistics_push(stats, False)
+
+    def update_moments(self):
+        mean, var = self.table.get_moments()
+        self.moving_mean.copy_(torch.from_numpy(mean))
+        self.moving_variance.copy_(torch.from_numpy(var))
+
+    def bn_statistics_pull(self):
+        """Fold the other ranks' pending increments in (called by rank 0 before saving)."""
+        if not self.synchronized or self.sync_freq > 1:
+            self.batch_counter = 0
+            self.table.sync_increments()
+            self.update_moments()
+
+    def _normalize(self, x):
+        y = (x - self.moving_mean) * torch.rsqrt(self.moving_variance + self.epsilon)
+        if self.gamma is not None:
+            y = y * self.gamma
+        if self.beta is not None:
+            y = y + self.beta
+        return y
+
+    def forward(self, inputs: torch.Tensor, training=None):
+        if self.bn_table_handle is None:
+            self._build(inputs.shape[-1])
+        training = self.training if training is None else training
+        if training:
+            self._push_counted(self._local_stats(inputs))
+            self.update_moments()
+        return self._normalize(inputs)
+
+    def save_bn_table(self, filepath):
+        return core.save_bn_table(self.bn_table_handle, filepath)
+
+    def load_bn_table(self, filepath):
+        core.load_bn_table(self.bn_table_handle, filepath)
+        self.update_moments()
+
+
+class TNBatchNormalization(TNBatchNormalizationBase):
+    """var = squared_sum / count - (sum / count)^2"""
+
+
+class PCTRDNNBatchNormalization(TNBatchNormalizationBase):
+    """Accumulates sum and the squared deviation from the current global mean."""
+    _USE_PCTR_DNN_BN = True
+
+    def forward(self, inputs: torch.Tensor, training=None):
+        if self.bn_table_handle is None:
+            self._build(inputs.shape[-1])
+        training = self.training if training is None else training
+        self.update_moments()
+        if training:
+            self._push_counted(self._local_stats(inputs, center=self.moving_mean))
+        return self._normalize(inputs)

@@ -386,6 +386,12 @@ class Model(nn.Module):
                 m.load_sparse_table(cp_dir, mode)
             else:
                 m.load_bn_table(cp_dir)
+        if dense and self.optimizer is not None:
+            if not self.optimizer.table.initialized:
+                self.optimizer.attach(self.named_parameters())
+            self.optimizer.load_dense_table(cp_dir)
+        # the dense table file is text with 6 significant digits (as in the reference); the exact
+        # fp32 weights and buffers come from the framework checkpoint written next to it
         pt = os.path.join(cp_dir, "torch_checkpoint.pt")
         if os.path.exists(pt):
             sd = torch.load(pt, map_location="cpu")
@@ -394,10 +400,8 @@ class Model(nn.Module):
                 for k, v in sd.items():
                     if k in own and own[k].shape == v.shape:
                         own[k].copy_(v)
-        if dense and self.optimizer is not None:
-            if not self.optimizer.table.initialized:
-                self.optimizer.attach(self.named_parameters())
-            self.optimizer.load_dense_table(cp_dir)
+            if self.optimizer is not None and self.optimizer.table.initialized:
+                self.optimizer.table.refresh_shadow()
         core.barrier()
 
     def show_decay(self, delta_days: int = 0):

@@ -134,6 +134,12 @@ class DenseTable:
                 w -= self.lr * self.s2 / (self.s1.sqrt() / self.s0.sqrt() + o.epsilon)
             g.zero_()
 
+    def refresh_shadow(self):
+        """Re-derive the bf16 shadow after the fp32 master was written from outside the optimizer."""
+        if self.Wb is not None:
+            with torch.no_grad():
+                self.Wb.copy_(self.W)
+
     # ------------------------------------------------------------------ checkpoint helpers
     def owned_range(self) -> Tuple[int, int]:
         lo = self.rank * self.chunk

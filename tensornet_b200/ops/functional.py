@@ -313,3 +313,68 @@ def cross_v1(x0, xl, w, b):
     if x0.is_cuda:
         return _CrossV1.apply(x0, xl, w, b)
     return x0 * (xl @ w.view(-1, 1)) + b + xl
+
+
+# =========================================================================================
+# DCN-v2 cross network  x_{l+1} = x0 * (W_l x_l + b_l) + x_l   on padded bf16 operands
+# =========================================================================================
+class _CrossV2(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x0, dim, *weights):
+        ext, st = _ext(), _status()
+        B, Dp = x0.shape[0], int(x0.stride(0))
+        xs = [x0]
+        xl = x0
+        for w in weights:
+            y = torch.empty((B, Dp), dtype=torch.bfloat16, device=x0.device)
+            # tcgen05 GEMM with the Hadamard-residual epilogue; the bias rides on x_l's ones column
+            ext.gemm(xl, _bf16_of(w), y, B, dim, dim + 1, Dp, int(w.shape[1]), Dp, False, False, False, False, None, None, x0, xl,
+                     Dp, dim, Dp, 1, 0, st)
+            xs.append(y)
+            xl = y
+        ctx.save_for_backward(*xs)
+        ctx.weights, ctx.dim = weights, dim
+        return xl
+
+    @staticmethod
+    def backward(ctx, g):
+        ext, st = _ext(), _status()
+        xs = ctx.saved_tensors
+        weights, dim = ctx.weights, ctx.dim
+        x0 = xs[0]
+        B, Dp = x0.shape[0], int(x0.stride(0))
+        g = g.contiguous()
+        gx0 = torch.zeros((B, Dp), dtype=torch.float32, device=g.device)
+        for l in range(len(weights) - 1, -1, -1):
+            w, xl = weights[l], xs[l]
+            wb = _bf16_of(w)
+            Kp = int(w.shape[1])
+            u = torch.empty((B, Dp), dtype=torch.bfloat16, device=g.device)     # u = W x_l + b, recomputed
+            ext.gemm(xl, wb, u, B, dim, dim + 1, Dp, Kp, Dp, False, False, False, False, None, None, None, None, 0, -1, Dp, 1, 0, st)
+            gx0.addcmul_(g.float(), u.float())
+            du = g * x0
+            if w.requires_grad:
+                split = max(1, min(16, B // 1024))
+                ext.gemm(du, xl, _grad_buffer(w), dim, dim + 1, B, Dp, Dp, Kp, True, True, True, False, None, None, None, None, 0, -1,
+                         dim + 1, split, 0, st)
+            gxl = torch.empty((B, Dp), dtype=torch.bfloat16, device=g.device)
+            ext.gemm(du, wb, gxl, B, min(Kp, Dp), dim, Dp, Kp, Dp, False, True, False, False, None, None, None, None, 0, -1, Dp, 1, 0, st)
+            g = g + gxl
+        gx0 += g.float()
+        return (gx0.to(torch.bfloat16), None, *([None] * len(weights)))
+
+
+def cross_v2(x0: torch.Tensor, weights: Sequence[torch.Tensor], dim: int) -> torch.Tensor:
+    """``x0``: bf16 ``[B, pad8(dim+1)]`` with the ones column at ``dim``; ``weights[l]``: fp32 ``[dim, pad8(dim+1)]``
+    (bias in column ``dim``).  Returns the last cross layer's output in the same padded layout."""
+    if x0.is_cuda:
+        return _CrossV2.apply(x0, dim, *weights)
+    x0f = x0.float()
+    xl = x0f
+    for w in weights:
+        wq = w.to(torch.bfloat16).float()
+        u = xl[:, : dim + 1] @ wq[:, : dim + 1].t()
+        y = x0f[:, :dim] * u + xl[:, :dim]
+        y = torch.cat([y, torch.ones(y.shape[0], 1), torch.zeros(y.shape[0], x0.shape[1] - dim - 1)], dim=1)
+        xl = y.to(torch.bfloat16).float()
+    return xl.to(torch.bfloat16)

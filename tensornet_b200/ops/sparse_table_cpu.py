@@ -1,0 +1,143 @@
+"""CPU shard of a sparse table: the reference's algorithms restated in plain C++ (module
+``_tn_cpu``), used when no GPU is present, as the oracle of the GPU kernels and as the CPU
+baseline.  Ranks exchange id lists, rows and gradient records over the gloo process group,
+playing the part of the reference's brpc SparsePull / SparsePush RPCs
+(core/ps/ps_local_server.cc:30-54).
+
+Like the GPU path the step is synchronous: gradients of one sign coming from several ranks
+are summed and applied once by the owner.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import numpy as np
+import torch
+
+from .. import _build
+from ..core.optimizers import KIND_ADAGRAD, OptimizerBase
+from ..core.runtime import runtime
+
+
+def row_floats(kind: int, dim: int) -> int:
+    return dim + 4 if kind == KIND_ADAGRAD else 3 * dim + 2
+
+
+class CpuSparseTable:
+    def __init__(self, opt: OptimizerBase, dim: int, use_cvm: bool = False, name: str = "", rows=None):
+        rt = runtime()
+        self.ext = _build.cpu_ext()
+        self.opt, self.kind, self.dim, self.use_cvm, self.name = opt, opt.kind, int(dim), bool(use_cvm), name
+        self.pdim = self.dim + (2 if self.use_cvm else 0)
+        self.world, self.rank = rt.world, rt.rank
+        self._zero_init = False
+        self.native = self.ext.CpuSparseTable(self._opt_dict(), self.dim, self.use_cvm, self.world, self.rank)
+        self.links = []
+
+    def _opt_dict(self):
+        d = self.opt.sparse_params()
+        d["zero_init"] = int(self._zero_init)
+        return d
+
+    def refresh_opt(self):
+        self.native.set_opt(self._opt_dict())
+
+    def set_training(self, training: bool):
+        zi = not training
+        if zi != self._zero_init:
+            self._zero_init = zi
+            self.refresh_opt()
+
+    def link(self, max_unique: int) -> "CpuSparseLink":
+        lk = CpuSparseLink(self)
+        self.links.append(lk)
+        return lk
+
+    @property
+    def n_rows(self) -> int:
+        return int(self.native.size())
+
+    def show_decay(self, delta_days: int):
+        self.native.show_decay(float(getattr(self.opt, "show_decay_rate", 1.0)), int(delta_days))
+
+    def dump(self) -> Tuple[np.ndarray, np.ndarray]:
+        return self.native.dump()
+
+    def load_rows(self, signs: np.ndarray, rows: np.ndarray):
+        self.native.load_rows(np.ascontiguousarray(signs, dtype=np.uint64), np.ascontiguousarray(rows, dtype=np.float32))
+
+    def clear(self):
+        self.native.clear()
+
+
+class CpuSparseLink:
+    """Per-layer state tying one pull to the following push (mirrors GpuSparseLink)."""
+
+    def __init__(self, table: CpuSparseTable):
+        self.table = table
+        self.dim, self.pdim, self.kind = table.dim, table.pdim, table.kind
+        self.ustride, self.gstride = table.pdim, table.dim
+        self.U = torch.zeros(0, self.pdim)
+        self.gU = torch.zeros(0, self.dim)
+        self._uniq = np.zeros(0, np.uint64)
+        self._show = self._click = np.zeros(0, np.float32)
+        self._route = None
+
+    def unique_counts(self):
+        return [int(len(self._uniq))]
+
+    def pull(self, ids: torch.Tensor, labels: Optional[torch.Tensor] = None, label_mod: int = 0, training: bool = True,
+             inverse=None) -> torch.Tensor:
+        t, rt = self.table, runtime()
+        ids_np = ids.reshape(-1).cpu().numpy()
+        lab = None
+        if labels is not None and training:
+            lab = labels.reshape(-1).float().cpu().numpy()
+            if label_mod > 0:
+                lab = lab[np.arange(len(ids_np)) % label_mod]
+        uniq, inv, show, click = t.ext.unique_first_occurrence(ids_np, lab)
+        self._uniq, self._show, self._click = uniq, show, click
+        if t.world == 1:
+            rows = t.native.pull(uniq)
+        else:
+            owner = (uniq % np.uint64(t.world)).astype(np.int64)
+            order = np.argsort(owner, kind="stable")
+            counts = np.bincount(owner, minlength=t.world)
+            send = np.split(uniq[order], np.cumsum(counts)[:-1])
+            everyone = rt.all_gather_object(send)                    # everyone[src][dst] = signs src wants from dst
+            mine = [everyone[src][t.rank] for src in range(t.world)]
+            answers = [t.native.pull(np.ascontiguousarray(m, dtype=np.uint64)) for m in mine]
+            back = rt.all_gather_object(answers)                     # back[owner][requester]
+            rows = np.zeros((len(uniq), self.pdim), np.float32)
+            rows[order] = np.concatenate([back[o][t.rank] for o in range(t.world)], axis=0)
+            self._route = (order, counts, mine)
+        self.U = torch.from_numpy(np.ascontiguousarray(rows))
+        self.gU = torch.zeros(len(uniq), self.dim)
+        return torch.from_numpy(inv)
+
+    def push(self):
+        t, rt = self.table, runtime()
+        g = self.gU.numpy()
+        if t.world == 1:
+            t.native.push(self._uniq, g, self._show, self._click)
+            return
+        order, counts, _ = self._route
+        cuts = np.cumsum(counts)[:-1]
+        rec = (np.split(self._uniq[order], cuts), np.split(g[order], cuts), np.split(self._show[order], cuts),
+               np.split(self._click[order], cuts))
+        send = [tuple(r[d] for r in rec) for d in range(t.world)]
+        everyone = rt.all_gather_object(send)
+        signs = np.concatenate([everyone[s][t.rank][0] for s in range(t.world)])
+        grads = np.concatenate([everyone[s][t.rank][1] for s in range(t.world)], axis=0)
+        shows = np.concatenate([everyone[s][t.rank][2] for s in range(t.world)])
+        clicks = np.concatenate([everyone[s][t.rank][3] for s in range(t.world)])
+        if len(signs) == 0:
+            return
+        u, inv = np.unique(signs, return_inverse=True)
+        gs = np.zeros((len(u), self.dim), np.float32)
+        np.add.at(gs, inv, grads)
+        sh = np.zeros(len(u), np.float32)
+        cl = np.zeros(len(u), np.float32)
+        np.add.at(sh, inv, shows)
+        np.add.at(cl, inv, clicks)
+        t.native.push(u, gs, sh, cl)

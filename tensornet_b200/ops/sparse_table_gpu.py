@@ -189,11 +189,13 @@ class GpuSparseLink:
             dd_keys=torch.full((dd_cap,), -1, dtype=torch.int64, device=d),
             dd_vals=torch.zeros(dd_cap, dtype=torch.int32, device=d),
             bar=torch.zeros(4, dtype=torch.int32, device=d),
+            prof=torch.zeros(8, dtype=torch.int64, device=d),
         )
         self.arena = arena
         self.U = arena.tensor("U").view(n_seg, self.ustride)
         self.gU = loc["gU"].view(n_seg, self.gstride)
         self.cnt_saved = loc["cnt_saved"]
+        self.prof = loc["prof"]
         self.comm = dict(world=W, rank=table.rank, capo=capo, gstride=self.gstride, ustride=self.ustride,
                          inbox_ids=arena.ptrs("inbox_ids"), ginbox=arena.ptrs("ginbox"), U=arena.ptrs("U"),
                          sig=arena.ptrs("sig"), epoch=table.epoch, status=rt.status, wait_ns=rt.wait_ns, **loc)
@@ -216,6 +218,12 @@ class GpuSparseLink:
     def push(self):
         """Apply the accumulated unique-row gradients (``self.gU``) on the owning GPUs."""
         self.ctx.push(max(self._last_n_ids, 1))
+
+    def pull_phase_us(self):
+        """Durations (microseconds) of the last pull's phases as seen by CTA 0:
+        dedup, inverse+dispatch, owner probe/insert, row return, scratch clear + completion."""
+        t = self.prof.tolist()
+        return [(t[i + 1] - t[i]) / 1e3 for i in range(5)]
 
     def unique_counts(self):
         """Per-owner unique-sign counts of the last pull (host sync)."""

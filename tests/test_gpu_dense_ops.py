@@ -85,21 +85,19 @@ def test_mlp_forward_backward(tn_gpu, status_ok):
     out = mlp(F.concat_cast([xin], ones=True))
     gout = torch.randn(B, out.shape[1]).bfloat16()
     out.backward(gout.to(dev))
+    # reference: the CPU restatement of the same chain (bf16-rounded activations, fp32 accumulate), so both
+    # sides see the same ReLU masks; autograd differentiates it
     xr = x.clone().requires_grad_(True)
-    outr = mlp_ref(F.concat_cast([xr], ones=True).float().to(torch.bfloat16))
-    # CPU restatement is differentiable w.r.t. weights only through float ops: use fp32 chain for reference grads
-    h = torch.cat([xr, torch.ones(B, 1)], 1)
-    ws = [w.detach().clone().requires_grad_(True) for w in mlp_ref.weights]
+    outr = mlp_ref(F.concat_cast([xr], ones=True))
+    outr.backward(gout)
     dims = [K, 400, 400]
-    for l, w in enumerate(ws):
-        h = torch.relu(h[:, :dims[l] + 1] @ w[:, :dims[l] + 1].t())
-        h = torch.cat([h, torch.ones(B, 1)], 1)
-    (h[:, :96] * gout.float()[:, :96]).sum().backward()
     assert float((out.float().cpu()[:, :96] - outr.float()[:, :96]).abs().max()) < 0.1
-    rel = lambda a, b: float((a - b).abs().max() / (b.abs().max() + 1e-6))
-    for l, (w, wr) in enumerate(zip(mlp.weights, ws)):
-        assert rel(w.grad.cpu()[:, :dims[l] + 1], wr.grad[:, :dims[l] + 1]) < 5e-2, l
-    assert rel(xin.grad.cpu(), xr.grad) < 5e-2
+    # a handful of units sit so close to zero that the two summation orders disagree on the ReLU mask;
+    # compare in the Frobenius norm, which such isolated flips barely move
+    rel = lambda a, b: float((a - b).norm() / (b.norm() + 1e-6))
+    for l, (w, wr) in enumerate(zip(mlp.weights, mlp_ref.weights)):
+        assert rel(w.grad.cpu()[:, :dims[l] + 1], wr.grad[:, :dims[l] + 1]) < 1e-2, l
+    assert rel(xin.grad.cpu(), xr.grad) < 1e-2
 
 
 @pytest.mark.parametrize("kind", ["Adam", "AdaGrad"])
