@@ -317,6 +317,18 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     tn::launch_bce(ptr_of<float>(logit), ptr_of<float>(label), (int)logit.numel(), pred ? ptr_of<float>(*pred) : nullptr,
                    dlogit ? ptr_of<float>(*dlogit) : nullptr, grad_scale, ptr_of<float>(sums), cur_stream());
   });
+  m.def("dict_lookup_pool", [](py::dict table, at::Tensor ids, c10::optional<at::Tensor> offsets, int B, int S, int combiner,
+                               at::Tensor out, int ld_out, int ones_col) {
+    c10::cuda::CUDAGuard guard(ids.device());
+    tn::TableView t = table_from_dict(table);
+    TORCH_CHECK(t.dim % 4 == 0, "dict_lookup_pool: dim must be a multiple of 4");
+    tn::launch_dict_lookup_pool(t, ptr_of<long long>(ids), offsets ? ptr_of<int>(*offsets) : nullptr, B, S, combiner, out.data_ptr(),
+                                ld_out, ones_col, cur_stream());
+  });
+  m.def("sigmoid", [](at::Tensor x, at::Tensor y) {
+    c10::cuda::CUDAGuard guard(x.device());
+    tn::launch_sigmoid(ptr_of<float>(x), ptr_of<float>(y), (int)x.numel(), cur_stream());
+  });
   m.def("relu_mask", [](at::Tensor g, at::Tensor y) {
     c10::cuda::CUDAGuard guard(g.device());
     TORCH_CHECK(g.numel() % 8 == 0 && g.numel() == y.numel(), "relu_mask: numel must be a multiple of 8");

@@ -209,7 +209,10 @@ class Model(nn.Module):
         if not static_ok or self._eager_steps < self._graph_warmup:
             self._eager_steps += 1
             (f, y), _, _ = self._to_device((features, labels))
-            return self._step_impl(f, y)
+            loss = self._step_impl(f, y)
+            if self._eager_steps <= self._graph_warmup:
+                core.runtime().check_status()      # surface device-side errors before the step is frozen into a graph
+            return loss
         if self._graph is None or self._graph_key != key:
             self._capture(spec, leaves, key)
         for dst, src in zip(self._static_leaves, leaves):

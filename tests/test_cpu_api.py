@@ -1,0 +1,172 @@
+"""Python surface on the CPU path: feature columns, EmbeddingFeatures (pooling, CVM columns, shared
+tables), sequence features, batch-norm table, metrics, done-file helpers, tools, serving."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import tensornet_b200 as tn
+from tensornet_b200.data import Ragged
+
+
+@pytest.fixture(autouse=True)
+def _cpu_runtime():
+    tn.core.shutdown()
+    tn.core.config.force_cpu = True
+    tn.core.init()
+    yield
+    tn.core.shutdown()
+
+
+def _cols(keys, dim, combiner="sum", bucket=64):
+    return [tn.feature_column.embedding_column(tn.feature_column.category_column(k, bucket), dim, combiner) for k in keys]
+
+
+def test_api_surface_names():
+    for name in ["init", "AdaGrad", "Adam", "Ftrl", "get_opt_learning_rate", "set_sparse_init_mode", "create_sparse_table",
+                 "create_dense_table", "create_bn_table", "save_sparse_table", "load_sparse_table", "save_dense_table",
+                 "load_dense_table", "save_bn_table", "load_bn_table", "shard_num", "self_shard_id", "barrier",
+                 "reset_balance_dataset", "show_decay"]:
+        assert hasattr(tn.core, name), name
+    assert tn.feature_column.category_column("a").bucket_size == 1024
+    assert tn.core.shard_num() == 1 and tn.core.self_shard_id() == 0
+    for name in ["EmbeddingFeatures", "SequenceEmbeddingFeatures", "TNBatchNormalization", "PCTRDNNBatchNormalization",
+                 "TNBatchNormalizationBase", "PositionMappingLayer"]:
+        assert hasattr(tn.layers, name)
+    assert hasattr(tn.model, "Model") and hasattr(tn.model, "PCGradModel") and hasattr(tn.optimizer, "PCGrad")
+    assert hasattr(tn.callbacks, "PsWeightCheckpoint") and hasattr(tn.distribute, "PsStrategy")
+
+
+def test_embedding_features_pooling_and_push():
+    opt = tn.core.AdaGrad(learning_rate=0.1, initial_g2sum=0.1, initial_scale=1.0)
+    layer = tn.layers.EmbeddingFeatures(_cols(["a", "b"], 4, "mean"), opt, name="emb", is_concat=False)
+    feats = {"a": torch.tensor([11, 12, 11]),
+             "b": Ragged(torch.tensor([5, 6, 7, 5]), torch.tensor([0, 2, 2, 4]))}        # bags: [5,6] [] [7,5]
+    layer.train()
+    out = layer(feats)
+    assert len(out) == 2 and out[0].shape == (3, 4)
+    w = {s: layer.table.native.pull(np.array([s], np.uint64))[0] for s in (11, 12, 5, 6, 7)}
+    assert np.allclose(out[0][0].detach(), w[11]) and np.allclose(out[0][1].detach(), w[12])
+    assert np.allclose(out[1][0].detach(), (w[5] + w[6]) / 2) and np.allclose(out[1][1].detach(), 0)
+    assert np.allclose(out[1][2].detach(), (w[7] + w[5]) / 2)
+    loss = (out[0].sum() + 2 * out[1].sum())
+    loss.backward()
+    layer.backwards()
+    # sign 11 appears twice in column a (grad 1 each), sign 5 twice in column b (grad 2 * 1/2 each)
+    g = {11: 2.0, 12: 1.0, 5: 2.0, 6: 1.0, 7: 1.0}
+    for s, gv in g.items():
+        g2 = 0.1 + gv * gv          # mean over dim of g^2 with all components equal
+        want = w[s] - 0.1 * gv / (1e-8 + np.sqrt(g2))
+        assert np.allclose(layer.table.native.pull(np.array([s], np.uint64))[0], want, rtol=1e-5), s
+
+
+def test_cvm_columns_and_shared_table():
+    opt = tn.core.AdaGrad(learning_rate=0.1, initial_g2sum=0.1)
+    l1 = tn.layers.EmbeddingFeatures(_cols(["a"], 4), opt, name="x", is_concat=True, target_columns=["label"], embedding_share="g")
+    l2 = tn.layers.EmbeddingFeatures(_cols(["b"], 4), opt, name="y", is_concat=True, target_columns=["label"], embedding_share="g")
+    assert l1.sparse_table_handle == l2.sparse_table_handle
+    feats = {"a": torch.tensor([1, 1, 2]), "b": torch.tensor([1, 3, 3]), "label": torch.tensor([1.0, 0.0, 1.0])}
+    l1.train()
+    o = l1(feats)
+    assert o.shape == (3, 6) and float(o[:, 4:].abs().sum()) == 0     # no shows yet
+    o.sum().backward()
+    l1.backwards()
+    o = l1(feats, training=False)
+    assert o[0, 4] == 2 and abs(float(o[0, 5]) - (np.log(2) - np.log(3))) < 1e-6     # show 2, click 1 for sign 1
+    o2 = l2(feats, training=False)
+    assert torch.allclose(o2[0, :4], o[0, :4])                         # same table: sign 1 has one row
+
+
+def test_sequence_features_and_position_mapping():
+    opt = tn.core.Adam(learning_rate=0.01)
+    col = tn.feature_column.embedding_column(tn.feature_column.sequence_category_column(tn.feature_column.category_column("s", 64), 3), 4)
+    layer = tn.layers.SequenceEmbeddingFeatures([col], opt, name="seq")
+    feats = {"s": Ragged(torch.tensor([9, 8, 7, 6, 9]), torch.tensor([0, 4, 4, 5]))}
+    layer.train()
+    out, lengths = layer(feats)
+    assert out.shape == (3, 3, 4) and lengths.tolist() == [3, 0, 1]   # first sequence truncated to max_length 3
+    assert torch.allclose(out[0, 0], out[2, 0]) and float(out[1].abs().sum()) == 0
+    out.sum().backward()
+    layer.backwards()
+    pm = tn.layers.PositionMappingLayer([3, 5, 9])
+    pm.train()
+    assert pm(torch.tensor([5, 9])).tolist() == [[0, 1, 0], [0, 0, 1]]
+    pm.eval()
+    assert pm(torch.tensor([5, 9])).tolist() == [[1, 0, 0], [1, 0, 0]]
+    with pytest.raises(ValueError):
+        pm.train()
+        pm(torch.tensor([4]))
+
+
+def test_bn_table_moments_window_and_layer(tmp_path):
+    bn = tn.layers.TNBatchNormalization(3, max_count=50)
+    bn.train()
+    x = torch.randn(40, 3) * 2 + 1
+    y = bn(x)
+    assert torch.allclose(bn.moving_mean, x.mean(0), atol=1e-5) and torch.allclose(bn.moving_variance, x.var(0, unbiased=False), atol=1e-4)
+    assert torch.allclose(y, (x - x.mean(0)) / torch.sqrt(x.var(0, unbiased=False) + 1e-5), atol=1e-4)
+    bn(x)                                   # 80 records > max_count: further batches decay instead of adding
+    before = bn.table.total_count.copy()
+    bn(x)
+    assert np.array_equal(bn.table.total_count, before)
+    bn.save_bn_table(str(tmp_path))
+    mean = bn.moving_mean.clone()
+    tn.core.shutdown(); tn.core.config.force_cpu = True; tn.core.init()     # a fresh process builds the same handles
+    bn2 = tn.layers.TNBatchNormalization(3, max_count=50)
+    bn2.load_bn_table(str(tmp_path))
+    assert torch.allclose(bn2.moving_mean, mean)
+    pc = tn.layers.PCTRDNNBatchNormalization(3)
+    pc.train()
+    pc(x)
+    assert pc.table.use_pctr_dnn_bn
+
+
+def test_metrics_and_done_file(tmp_path):
+    y = torch.tensor([1.0, 0, 0, 1]); p = torch.tensor([0.9, 0.2, 0.4, 0.7])
+    c, pc, co, auc = tn.metric.CTR(), tn.metric.PCTR(), tn.metric.COPC(), tn.metric.AUC()
+    for m in (c, pc, co, auc):
+        m.update_state(y, p)
+    assert c.result() == 0.5 and abs(pc.result() - 0.55) < 1e-6 and abs(co.result() - 2 / 2.2) < 1e-6
+    assert auc.result() > 0.99
+    assert tn.model.read_last_train_dt(str(tmp_path)) is None
+    tn.model.save_done_info(str(tmp_path), "2024-01-02")
+    assert tn.model.load_done_info(str(tmp_path)) == {"dt": "2024-01-02"}
+
+
+def test_tools_merge_resize_and_serving_dictionary(tmp_path):
+    from tensornet_b200 import tools
+    from tensornet_b200.serving import EmbeddingDictionary, InferenceEngine
+    from tensornet_b200.layers import MLP, DenseHead
+
+    opt = tn.core.AdaGrad(learning_rate=0.1, initial_g2sum=0.1)
+    layer = tn.layers.EmbeddingFeatures(_cols(["a", "b"], 4, "mean"), opt, name="deep", is_concat=True)
+    ids = torch.arange(1, 41).view(2, 20)
+    feats = {"a": ids[0], "b": ids[1]}
+    emb = layer(feats, training=True).detach()
+    cp = str(tmp_path / "cp")
+    layer.save_sparse_table(cp, "txt")
+    tdir = os.path.join(cp, "sparse_table", "deep")
+    out = str(tmp_path / "dict.txt")
+    assert tools.merge_sparse(tdir, out) == 40
+    d = EmbeddingDictionary.from_file(out)
+    assert d.n == 40 and d.dim == 4
+    assert np.allclose(d.lookup_cpu(np.array([1, 999], np.uint64))[0], emb[0, :4], rtol=1e-5)
+    assert np.all(d.lookup_cpu(np.array([999], np.uint64)) == 0)
+    # re-shard 1 -> 3 ranks -> merge again: same dictionary
+    assert tools.resize_sparse(tdir, str(tmp_path / "r3"), 3, "bin") == 40
+    assert sorted(os.listdir(tmp_path / "r3")) == ["rank_0", "rank_1", "rank_2"]
+    s3, r3, name, dim = tools.read_sparse_table(str(tmp_path / "r3"), "AdaGrad", 4)
+    assert name == "AdaGrad" and sorted(s3.tolist()) == list(range(1, 41))
+    assert tools.merge_extra_embedding(tdir, str(tmp_path / "extra"), {1: 1001, 77: 1002}) == 1
+    s4, r4, _, _ = tools.read_sparse_table(str(tmp_path / "extra"))
+    assert 1001 in s4.tolist() and np.allclose(r4[s4.tolist().index(1001)], r4[s4.tolist().index(1)])
+    # serving: dictionary lookup + towers equals the training-time forward
+    torch.manual_seed(0)
+    mlp, head = MLP(8, [8, 4]), DenseHead(4)
+    eng = InferenceEngine(d, mlp, head, n_slots=2)
+    from tensornet_b200.ops import functional as F
+    want = torch.sigmoid(head(mlp(F.concat_cast([emb], ones=True)))).view(-1)
+    got = eng.infer(ids)
+    assert torch.allclose(got, want, atol=2e-2)

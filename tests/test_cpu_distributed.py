@@ -1,0 +1,56 @@
+"""Two CPU ranks over gloo (the reference's `mpiexec -n 2` integration test, test/CMakeLists.txt:33-38):
+Wide&Deep with synchronised BN trains, saves per-rank shards, and the checkpoint written by two
+ranks reloads on one rank (re-sharding by sign % world)."""
+import json
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _run(nproc, args, timeout=600):
+    env = dict(os.environ, TN_FORCE_CPU="1", OMP_NUM_THREADS="1", PYTHONPATH=ROOT)
+    if nproc == 1:
+        cmd = [sys.executable, os.path.join(ROOT, "examples", "main.py")] + args
+    else:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+               "--master-port", str(_free_port()), os.path.join(ROOT, "examples", "main.py")] + args
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    line = [l for l in out.stdout.splitlines() if l.startswith("{")][-1]
+    return json.loads(line)
+
+
+@pytest.mark.timeout(900)
+def test_wide_deep_two_ranks_then_reload_on_one(tmp_path):
+    data, model_dir = str(tmp_path / "data"), str(tmp_path / "model")
+    subprocess.run([sys.executable, os.path.join(ROOT, "examples", "gen_example_data.py"), "--out", data, "--examples-per-file",
+                    "3000", "--files-per-day", "3"], check=True, env=dict(os.environ, PYTHONPATH=ROOT))
+    common = ["--data", data, "--model-dir", model_dir, "--hidden", "32", "16", "--batch-size", "64", "--save-mode", "bin"]
+    rep = _run(2, common + ["--days", "2020-05-10"])
+    assert len(rep["days"]) == 1 and rep["days"][0]["loss"] < 0.5
+    cp = os.path.join(model_dir, "2020-05-10")
+    assert json.load(open(os.path.join(model_dir, "_checkpoint"))) == {"dt": "2020-05-10"}
+    for layer in ("linear_input", "deep_input"):
+        for r in (0, 1):
+            d = os.path.join(cp, "sparse_table", layer, f"rank_{r}")
+            assert sorted(os.listdir(d)) == [f"block_{b}_bin.gz" for b in range(8)]
+    assert sorted(os.listdir(os.path.join(cp, "dense_table", "0"))) == ["0", "1"]
+    assert os.path.exists(os.path.join(cp, "bn_table", "0"))
+    # second day on ONE rank: day 1 is skipped (done-file), its 2-rank checkpoint is re-sharded on load
+    rep1 = _run(1, common + ["--days", "2020-05-10", "2020-05-11", "--predict"])
+    assert [d["day"] for d in rep1["days"]] == ["2020-05-11"]
+    assert rep1["days"][0]["loss"] < 0.3
+    assert rep1["predict_auc"] > 0.95
