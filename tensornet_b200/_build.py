@@ -33,6 +33,7 @@ CUDA_SOURCES = [
     "dense_fused.cu",
     "elementwise.cu",
     "serving.cu",
+    "unique.cu",
     "no_alloc.cu",
 ]
 CPU_SOURCES = ["cpu_ref.cpp"]

@@ -6,6 +6,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <cuda_runtime.h>
 #include <atomic>
+#include <cstring>
 #include <string>
 #include <vector>
 
@@ -198,7 +199,7 @@ struct DenseCtx {
 void gemm(at::Tensor A, at::Tensor B, at::Tensor C, int M, int N, int K, int lda, int ldb, int ldc, bool a_mn, bool b_mn,
           bool accumulate, bool relu, c10::optional<at::Tensor> bias, c10::optional<at::Tensor> mask_aux,
           c10::optional<at::Tensor> had_x0, c10::optional<at::Tensor> had_xl, int ld_aux, int ones_col, int n_store,
-          int split_k, int BN, at::Tensor status, c10::optional<at::Tensor> prof) {
+          int split_k, int BN, at::Tensor status, c10::optional<at::Tensor> prof, int dbg) {
   TORCH_CHECK(A.is_cuda() && B.is_cuda() && C.is_cuda(), "gemm: CUDA tensors");
   TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16, "gemm: bf16 operands");
   c10::cuda::CUDAGuard guard(A.device());
@@ -215,6 +216,7 @@ void gemm(at::Tensor A, at::Tensor B, at::Tensor C, int M, int N, int K, int lda
   d.ld_aux = ld_aux; d.ones_col = ones_col; d.n_store = n_store; d.split_k = split_k; d.BN = BN;
   d.status = ptr_of<int>(status);
   d.prof = prof.has_value() ? ptr_of<unsigned long long>(*prof) : nullptr;
+  d.dbg = dbg;
   const char* err = tn::gemm_bf16(d, cur_stream());
   if (err) throw std::runtime_error(err);
 }
@@ -232,8 +234,33 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, py::arg("A"), py::arg("B"), py::arg("C"), py::arg("M"), py::arg("N"), py::arg("K"), py::arg("lda"),
         py::arg("ldb"), py::arg("ldc"), py::arg("a_mn"), py::arg("b_mn"), py::arg("accumulate"), py::arg("relu"), py::arg("bias"),
         py::arg("mask_aux"), py::arg("had_x0"), py::arg("had_xl"), py::arg("ld_aux"), py::arg("ones_col"), py::arg("n_store"),
-        py::arg("split_k"), py::arg("BN"), py::arg("status"), py::arg("prof") = py::none());
+        py::arg("split_k"), py::arg("BN"), py::arg("status"), py::arg("prof") = py::none(), py::arg("dbg") = 0);
   m.def("launch_count", []() { return g_launches.load(); });
+
+  // ---- CUDA IPC peer memory (fallback transport for the symmetric heap) --------------------------
+  m.def("ipc_alloc", [](int64_t nbytes) {
+    void* p = nullptr;
+    check(cudaMalloc(&p, (size_t)nbytes), "cudaMalloc");
+    check(cudaMemset(p, 0, (size_t)nbytes), "cudaMemset");
+    cudaIpcMemHandle_t h;
+    check(cudaIpcGetMemHandle(&h, p), "cudaIpcGetMemHandle");
+    return py::make_tuple((int64_t)reinterpret_cast<uintptr_t>(p), py::bytes(reinterpret_cast<const char*>(&h), sizeof(h)));
+  });
+  m.def("ipc_open", [](py::bytes handle) {
+    std::string hs = handle;
+    TORCH_CHECK(hs.size() == sizeof(cudaIpcMemHandle_t), "bad IPC handle size");
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, hs.data(), sizeof(h));
+    void* p = nullptr;
+    check(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
+    return (int64_t)reinterpret_cast<uintptr_t>(p);
+  });
+  m.def("ipc_close", [](int64_t p) { cudaIpcCloseMemHandle(ptr_of<void>(p)); });
+  m.def("ipc_free", [](int64_t p) { cudaFree(ptr_of<void>(p)); });
+  m.def("tensor_from_ptr", [](int64_t p, int64_t nbytes, int device) {
+    auto opts = at::TensorOptions().dtype(at::kByte).device(at::kCUDA, device);
+    return at::from_blob(ptr_of<void>(p), {nbytes}, opts);
+  });
 
   m.def("pool_fwd", [](at::Tensor U, int ustride, at::Tensor inverse, c10::optional<at::Tensor> offsets, int B, int S, int pd,
                        int combiner, at::Tensor out, int out_ld) {
@@ -316,6 +343,20 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     c10::cuda::CUDAGuard guard(logit.device());
     tn::launch_bce(ptr_of<float>(logit), ptr_of<float>(label), (int)logit.numel(), pred ? ptr_of<float>(*pred) : nullptr,
                    dlogit ? ptr_of<float>(*dlogit) : nullptr, grad_scale, ptr_of<float>(sums), cur_stream());
+  });
+  m.def("unique_assign", [](at::Tensor ids, c10::optional<at::Tensor> labels, at::Tensor dd_keys, at::Tensor dd_vals, at::Tensor uniq,
+                            at::Tensor inverse, c10::optional<at::Tensor> show, c10::optional<at::Tensor> click, at::Tensor count,
+                            at::Tensor status) {
+    c10::cuda::CUDAGuard guard(ids.device());
+    const int64_t cap2 = dd_keys.numel();
+    TORCH_CHECK(cap2 >= 2 && (cap2 & (cap2 - 1)) == 0 && dd_vals.numel() >= cap2, "unique_assign: scratch must be a power of two");
+    TORCH_CHECK(ids.scalar_type() == at::kLong && ids.is_contiguous() && inverse.numel() >= ids.numel(), "unique_assign: bad ids / inverse");
+    g_launches.fetch_add(2, std::memory_order_relaxed);
+    tn::launch_unique_assign(ptr_of<long long>(ids), (int)ids.numel(), labels ? ptr_of<float>(*labels) : nullptr,
+                             ptr_of<unsigned long long>(dd_keys), ptr_of<int>(dd_vals), (unsigned)cap2,
+                             ptr_of<unsigned long long>(uniq), (int)uniq.numel(), ptr_of<int>(inverse),
+                             show ? ptr_of<float>(*show) : nullptr, click ? ptr_of<float>(*click) : nullptr, ptr_of<int>(count),
+                             ptr_of<int>(status), cur_stream());
   });
   m.def("dict_lookup_pool", [](py::dict table, at::Tensor ids, c10::optional<at::Tensor> offsets, int B, int S, int combiner,
                                at::Tensor out, int ld_out, int ones_col) {

@@ -271,15 +271,17 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           uint32_t acc[64];
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
-            if (c0 + 16 * g < BN) tmem_ld16_nowait(tm_lane + (uint32_t)(c0 + 16 * g), acc + 16 * g);
+            if (c0 + 16 * g < BN && !(p.dbg & 4)) tmem_ld16_nowait(tm_lane + (uint32_t)(c0 + 16 * g), acc + 16 * g);
             else {
 #pragma unroll
               for (int j = 0; j < 16; ++j) acc[16 * g + j] = 0u;
             }
           }
           tmem_ld_wait();
+          if (prof && warp == 2 && lane == 0 && c0 == 0) prof[14] = globaltimer_ns();
 #pragma unroll
           for (int pc = 0; pc < 8; ++pc) {
+            if (p.dbg & 1) break;
             const int nb = n0 + c0 + pc * 8;
             float v[8];
 #pragma unroll
@@ -325,8 +327,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
           }
           __syncwarp();
+          if (prof && warp == 2 && lane == 0 && c0 == 0) prof[15] = globaltimer_ns();
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
+            if (p.dbg & 2) break;
             const int r = 4 * i + lrow;
             const int grow = row_base + r, gcol = n0 + c0 + lpc * 8;
             if (grow < p.M && gcol < n_store && c0 + lpc * 8 < BN) {
@@ -525,7 +529,7 @@ const char* gemm_bf16(const GemmDesc& d, cudaStream_t stream) {
   p.mask_aux = reinterpret_cast<const __nv_bfloat16*>(d.mask_aux);
   p.had_x0 = reinterpret_cast<const __nv_bfloat16*>(d.had_x0);
   p.had_xl = reinterpret_cast<const __nv_bfloat16*>(d.had_xl);
-  p.ld_aux = d.ld_aux; p.ones_col = d.ones_col; p.n_store = n_cover; p.bias = d.bias; p.status = d.status; p.prof = d.prof;
+  p.ld_aux = d.ld_aux; p.ones_col = d.ones_col; p.n_store = n_cover; p.bias = d.bias; p.status = d.status; p.prof = d.prof; p.dbg = d.dbg;
 
   dim3 grid((n_cover + BN - 1) / BN, (d.M + kBM - 1) / kBM, splits);
   const size_t b_bytes = (size_t)BN * kBK * 2;

@@ -28,6 +28,7 @@ struct GemmDesc {
   int BN = 0;                // tile N override (0 = choose)
   int* status = nullptr;     // device error words
   unsigned long long* prof = nullptr;   // optional [16] timestamps of CTA (0,0,0) for pipeline diagnosis
+  int dbg = 0;               // diagnosis only: bit0 skip epilogue math, bit1 skip global stores, bit2 skip TMEM loads
 };
 
 // Kernel-side parameter block.
@@ -42,6 +43,7 @@ struct GemmParams {
   const float* bias;
   int* status;
   unsigned long long* prof;
+  int dbg;
 };
 
 // Returns nullptr on success, otherwise a static error string.

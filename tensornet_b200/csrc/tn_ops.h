@@ -49,6 +49,11 @@ void launch_cross_v1_bwd(const float* x0, const float* xl, const float* w, const
                          float* gx0, float* gxl, float* gw, float* gb, cudaStream_t st);
 void launch_relu_mask(void* g, const void* y, long long n, cudaStream_t st);
 
+// unique.cu
+void launch_unique_assign(const long long* ids, int n, const float* labels, unsigned long long* dd_keys, int* dd_vals,
+                          unsigned scratch_cap, unsigned long long* uniq, int cap, int* inverse, float* show, float* click,
+                          int* count, int* status, cudaStream_t st);
+
 // serving.cu
 void launch_dict_lookup_pool(const TableView& t, const long long* ids, const int* offsets, int B, int S, int combiner, void* out,
                              int ld_out, int ones_col, cudaStream_t st);

@@ -9,6 +9,7 @@ buffer is an ordinary tensor and the peer table has a single entry.
 """
 from __future__ import annotations
 
+import os
 from typing import List, Optional
 
 import torch
@@ -30,6 +31,19 @@ class SymmBuffer:
             if zero:
                 self.local.zero_()
             self.ptrs: List[int] = [self.local.data_ptr()]
+        elif os.environ.get("TN_SYMM_BACKEND", "torch") == "ipc":
+            # CUDA IPC: every rank cudaMallocs its copy, the handles travel over the host group and
+            # each peer maps them.  No NVSwitch multicast mapping in this mode.
+            from .. import _build
+
+            ext = _build.cuda_ext()
+            ptr, handle = ext.ipc_alloc(nbytes)
+            self._ipc_own = ptr
+            handles = rt.all_gather_object(handle)
+            self.ptrs = [ptr if r == rt.rank else int(ext.ipc_open(h)) for r, h in enumerate(handles)]
+            self.local = ext.tensor_from_ptr(ptr, nbytes, rt.device.index)
+            torch.cuda.synchronize()
+            rt.barrier()
         else:
             import torch.distributed._symmetric_memory as symm_mem
 
