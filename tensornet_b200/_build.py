@@ -34,6 +34,7 @@ CUDA_SOURCES = [
     "elementwise.cu",
     "serving.cu",
     "unique.cu",
+    "deepfm_fused.cu",
     "no_alloc.cu",
 ]
 CPU_SOURCES = ["cpu_ref.cpp"]

@@ -344,6 +344,35 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     tn::launch_bce(ptr_of<float>(logit), ptr_of<float>(label), (int)logit.numel(), pred ? ptr_of<float>(*pred) : nullptr,
                    dlogit ? ptr_of<float>(*dlogit) : nullptr, grad_scale, ptr_of<float>(sums), cur_stream());
   });
+  m.def("deepfm_input_fwd", [](at::Tensor U, int ustride, at::Tensor inverse, int B, int S, int D, c10::optional<at::Tensor> dense,
+                               at::Tensor X0, at::Tensor fm) {
+    c10::cuda::CUDAGuard guard(U.device());
+    const int Dd = dense ? (int)dense->size(1) : 0;
+    const char* err = tn::launch_deepfm_input_fwd(ptr_of<float>(U), ustride, ptr_of<int>(inverse), B, S, D,
+                                                  dense ? ptr_of<float>(*dense) : nullptr, Dd, dense ? (int)dense->stride(0) : 0,
+                                                  X0.data_ptr(), (int)X0.stride(0), ptr_of<float>(fm), cur_stream());
+    if (err) throw std::runtime_error(err);
+  });
+  m.def("deepfm_input_bwd", [](at::Tensor U, int ustride, at::Tensor inverse, int B, int S, int D, at::Tensor dX0, at::Tensor gfm,
+                               at::Tensor gU, int gstride) {
+    c10::cuda::CUDAGuard guard(U.device());
+    const char* err = tn::launch_deepfm_input_bwd(ptr_of<float>(U), ustride, ptr_of<int>(inverse), B, S, D, dX0.data_ptr(),
+                                                  (int)dX0.stride(0), ptr_of<float>(gfm), ptr_of<float>(gU), gstride, cur_stream());
+    if (err) throw std::runtime_error(err);
+  });
+  m.def("deepfm_head_loss", [](at::Tensor H, int NH, c10::optional<at::Tensor> L, at::Tensor fm, at::Tensor w, at::Tensor label,
+                               at::Tensor dH, c10::optional<at::Tensor> dL, at::Tensor dfm, at::Tensor gw, at::Tensor sums,
+                               c10::optional<at::Tensor> pred, at::Tensor loss_out) {
+    c10::cuda::CUDAGuard guard(H.device());
+    const int NL = L ? (int)L->size(1) : 0;
+    TORCH_CHECK(w.numel() == NH + NL + 2, "deepfm_head_loss: weight must be [NH + NL + 2]");
+    const char* err = tn::launch_deepfm_head_loss(H.data_ptr(), (int)H.stride(0), NH, L ? ptr_of<float>(*L) : nullptr, NL,
+                                                  ptr_of<float>(fm), ptr_of<float>(w), ptr_of<float>(label), (int)H.size(0),
+                                                  dH.data_ptr(), dL ? ptr_of<float>(*dL) : nullptr, ptr_of<float>(dfm),
+                                                  ptr_of<float>(gw), ptr_of<float>(sums), pred ? ptr_of<float>(*pred) : nullptr,
+                                                  ptr_of<float>(loss_out), cur_stream());
+    if (err) throw std::runtime_error(err);
+  });
   m.def("unique_assign", [](at::Tensor ids, c10::optional<at::Tensor> labels, at::Tensor dd_keys, at::Tensor dd_vals, at::Tensor uniq,
                             at::Tensor inverse, c10::optional<at::Tensor> show, c10::optional<at::Tensor> click, at::Tensor count,
                             at::Tensor status) {

@@ -1,0 +1,229 @@
+// DeepFM-specific fusions of the memory-bound glue around the tensor-core towers
+// (model structure: examples/models/deepfm.py, examples/common/layers.py:72-103 in the reference).
+//
+//   deepfm_input_fwd : gather the pulled embedding rows of every slot (single-hot), compute the
+//                      second-order FM term and write the padded bf16 operand of the first MLP layer
+//                      [emb | dense | 1 | 0] in one pass - replaces pool + FM + concat/cast.
+//   deepfm_input_bwd : gradient of that operand (bf16, from the first layer's dgrad) plus the FM
+//                      gradient, scattered straight into the unique-gradient rows - replaces
+//                      split/cast + FM backward + add + pool backward.
+//   deepfm_head_loss : Dense(1) over [h | linear | fm | 1], sigmoid cross-entropy, CTR / PCTR sums
+//                      and the complete backward of the head (dH with the ReLU mask applied, dLinear,
+//                      dFM, weight gradient) in one kernel - the logit gradient depends on nothing
+//                      but the logit and the label, so forward and backward of the head are one pass.
+#include <cuda_bf16.h>
+#include "tn_device.cuh"
+#include "tn_ops.h"
+
+namespace tn {
+
+namespace {
+
+__device__ __forceinline__ float wsum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// D % 4 == 0, dq = D/4 a power of two <= 32.  One warp per example.
+__global__ void deepfm_input_fwd_kernel(const float* __restrict__ U, int ustride, const int* __restrict__ inverse, int B, int S,
+                                        int D, const float* __restrict__ dense, int Dd, int ld_dense,
+                                        __nv_bfloat16* __restrict__ X0, int ld, float* __restrict__ fm) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  const int dq = D >> 2, nch = S * dq;
+  for (int b = warp; b < B; b += nwarps) {
+    __nv_bfloat16* xrow = X0 + (size_t)b * ld;
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    float sq = 0.f;
+    for (int c = lane; c < nch; c += 32) {
+      const int f = c / dq, dc = c - f * dq;
+      const int v = __ldg(inverse + (size_t)f * B + b);
+      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (v >= 0) x = ldcg_f4(U + (size_t)v * ustride + 4 * dc);
+      s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
+      sq += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+      __nv_bfloat162 lo = __floats2bfloat162_rn(x.x, x.y), hi = __floats2bfloat162_rn(x.z, x.w);
+      *reinterpret_cast<uint2*>(xrow + 4 * c) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    }
+    for (int o = 16; o >= dq; o >>= 1) {
+      s.x += __shfl_xor_sync(0xffffffffu, s.x, o); s.y += __shfl_xor_sync(0xffffffffu, s.y, o);
+      s.z += __shfl_xor_sync(0xffffffffu, s.z, o); s.w += __shfl_xor_sync(0xffffffffu, s.w, o);
+    }
+    float part = (lane < dq) ? (s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w) : 0.f;
+    part = wsum(part) - wsum(sq);
+    if (lane == 0) fm[b] = 0.5f * part;
+    const int tail0 = S * D;
+    for (int j = lane; j < ld - tail0; j += 32) {
+      float v = 0.f;
+      if (j < Dd) v = dense[(size_t)b * ld_dense + j];
+      else if (j == Dd) v = 1.f;
+      xrow[tail0 + j] = __float2bfloat16(v);
+    }
+  }
+}
+
+__global__ void deepfm_input_bwd_kernel(const float* __restrict__ U, int ustride, const int* __restrict__ inverse, int B, int S,
+                                        int D, const __nv_bfloat16* __restrict__ dX0, int ld, const float* __restrict__ gfm,
+                                        float* __restrict__ gU, int gstride) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  const int dq = D >> 2, nch = S * dq;
+  for (int b = warp; b < B; b += nwarps) {
+    const __nv_bfloat16* grow = dX0 + (size_t)b * ld;
+    const float gf = gfm[b];
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int c = lane; c < nch; c += 32) {
+      const int f = c / dq, dc = c - f * dq;
+      const int v = __ldg(inverse + (size_t)f * B + b);
+      if (v >= 0) {
+        const float4 x = ldcg_f4(U + (size_t)v * ustride + 4 * dc);
+        s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
+      }
+    }
+    for (int o = 16; o >= dq; o >>= 1) {
+      s.x += __shfl_xor_sync(0xffffffffu, s.x, o); s.y += __shfl_xor_sync(0xffffffffu, s.y, o);
+      s.z += __shfl_xor_sync(0xffffffffu, s.z, o); s.w += __shfl_xor_sync(0xffffffffu, s.w, o);
+    }
+    for (int c = lane; c < nch; c += 32) {
+      const int f = c / dq, dc = c - f * dq;
+      const int v = __ldg(inverse + (size_t)f * B + b);
+      if (v < 0) continue;
+      const float4 x = ldcg_f4(U + (size_t)v * ustride + 4 * dc);
+      const uint2 raw = *reinterpret_cast<const uint2*>(grow + 4 * c);
+      const float2 g01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+      const float2 g23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+      float4 g;
+      g.x = g01.x + gf * (s.x - x.x);
+      g.y = g01.y + gf * (s.y - x.y);
+      g.z = g23.x + gf * (s.z - x.z);
+      g.w = g23.y + gf * (s.w - x.w);
+      red_add_f32x4(gU + (size_t)v * gstride + 4 * dc, g);
+    }
+  }
+}
+
+// Head + loss + head backward.  w = [ wH (NH) | wL (NL) | wfm | bias ].  ldh <= 512, even.
+// sums: [0] += mean loss, [1] += sum(label), [2] += sum(pred), [3] += B
+constexpr int kHeadPairs = 8;
+__global__ void deepfm_head_loss_kernel(const __nv_bfloat16* __restrict__ H, int ldh, int NH, const float* __restrict__ L, int NL,
+                                        const float* __restrict__ fm, const float* __restrict__ w, const float* __restrict__ label,
+                                        int B, __nv_bfloat16* __restrict__ dH, float* __restrict__ dL, float* __restrict__ dfm,
+                                        float* __restrict__ gw, float* __restrict__ sums, float* __restrict__ pred,
+                                        float* __restrict__ loss_out) {
+  extern __shared__ float s_gw[];   // [NH + NL + 2]
+  const int NW = NH + NL + 2;
+  for (int k = threadIdx.x; k < NW; k += blockDim.x) s_gw[k] = 0.f;
+  __syncthreads();
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  float2 wv[kHeadPairs], acc[kHeadPairs];
+#pragma unroll
+  for (int i = 0; i < kHeadPairs; ++i) {
+    const int c = 64 * i + 2 * lane;
+    wv[i].x = c < NH ? __ldg(w + c) : 0.f;
+    wv[i].y = c + 1 < NH ? __ldg(w + c + 1) : 0.f;
+    acc[i] = make_float2(0.f, 0.f);
+  }
+  const float wl = lane < NL ? __ldg(w + NH + lane) : 0.f;       // NL <= 32 linear weights, one per lane
+  const float wfm = __ldg(w + NH + NL), bias = __ldg(w + NH + NL + 1);
+  float accL = 0.f, accfm = 0.f, accb = 0.f, ls = 0.f, ys = 0.f, ps = 0.f;
+  const float invB = 1.f / (float)B;
+  for (int b = warp; b < B; b += nwarps) {
+    const __nv_bfloat162* z = reinterpret_cast<const __nv_bfloat162*>(H + (size_t)b * ldh);
+    float2 zz[kHeadPairs];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < kHeadPairs; ++i) {
+      const int c = 64 * i + 2 * lane;
+      zz[i] = make_float2(0.f, 0.f);
+      if (c < ldh) {
+        zz[i] = __bfloat1622float2(z[32 * i + lane]);
+        dot += zz[i].x * wv[i].x + zz[i].y * wv[i].y;
+      }
+    }
+    const float lv = lane < NL ? L[(size_t)b * NL + lane] : 0.f;
+    dot += lv * wl;
+    dot = wsum(dot);
+    const float f = fm[b], y = label[b];
+    const float logit = dot + f * wfm + bias;
+    const float p = 1.f / (1.f + expf(-logit));
+    const float dl = (p - y) * invB;
+    if (lane == 0) {
+      ls += fmaxf(logit, 0.f) + log1pf(expf(-fabsf(logit))) - y * logit;
+      ys += y; ps += p;
+      if (pred) pred[b] = p;
+      dfm[b] = dl * wfm;
+      accfm += dl * f;
+      accb += dl;
+    }
+    if (lane < NL) { dL[(size_t)b * NL + lane] = dl * wl; accL += dl * lv; }
+    __nv_bfloat162* dz = reinterpret_cast<__nv_bfloat162*>(dH + (size_t)b * ldh);
+#pragma unroll
+    for (int i = 0; i < kHeadPairs; ++i) {
+      const int c = 64 * i + 2 * lane;
+      if (c < ldh) {
+        // gradient w.r.t. the ReLU output h, already masked by h > 0 (columns >= NH are the ones / pad columns)
+        const float gx = (c < NH && zz[i].x > 0.f) ? dl * wv[i].x : 0.f;
+        const float gy = (c + 1 < NH && zz[i].y > 0.f) ? dl * wv[i].y : 0.f;
+        dz[32 * i + lane] = __floats2bfloat162_rn(gx, gy);
+        acc[i].x += dl * zz[i].x;
+        acc[i].y += dl * zz[i].y;
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kHeadPairs; ++i) {
+    const int c = 64 * i + 2 * lane;
+    if (c < NH) atomicAdd(&s_gw[c], acc[i].x);
+    if (c + 1 < NH) atomicAdd(&s_gw[c + 1], acc[i].y);
+  }
+  if (lane < NL) atomicAdd(&s_gw[NH + lane], accL);
+  if (lane == 0) {
+    atomicAdd(&s_gw[NH + NL], accfm);
+    atomicAdd(&s_gw[NH + NL + 1], accb);
+    const float l = ls * invB;
+    atomicAdd(&sums[0], l);
+    atomicAdd(loss_out, l);
+    atomicAdd(&sums[1], ys);
+    atomicAdd(&sums[2], ps);
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&sums[3], (float)B);
+  __syncthreads();
+  for (int k = threadIdx.x; k < NW; k += blockDim.x) atomicAdd(gw + k, s_gw[k]);
+}
+
+}  // namespace
+
+const char* launch_deepfm_input_fwd(const float* U, int ustride, const int* inverse, int B, int S, int D, const float* dense, int Dd,
+                                    int ld_dense, void* X0, int ld, float* fm, cudaStream_t st) {
+  const int dq = D >> 2;
+  if ((D & 3) || dq < 1 || dq > 32 || (dq & (dq - 1))) return "deepfm_input: embedding dim must be 4 * 2^k, at most 128";
+  if (ld < S * D + Dd + 1 || (ld & 3)) return "deepfm_input: operand row too short";
+  int blocks = (B + 7) / 8; if (blocks > 148 * 8) blocks = 148 * 8; if (blocks < 1) blocks = 1;
+  deepfm_input_fwd_kernel<<<blocks, 256, 0, st>>>(U, ustride, inverse, B, S, D, dense, Dd, ld_dense,
+                                                  reinterpret_cast<__nv_bfloat16*>(X0), ld, fm);
+  return nullptr;
+}
+const char* launch_deepfm_input_bwd(const float* U, int ustride, const int* inverse, int B, int S, int D, const void* dX0, int ld,
+                                    const float* gfm, float* gU, int gstride, cudaStream_t st) {
+  const int dq = D >> 2;
+  if ((D & 3) || dq < 1 || dq > 32 || (dq & (dq - 1))) return "deepfm_input: embedding dim must be 4 * 2^k, at most 128";
+  int blocks = (B + 7) / 8; if (blocks > 148 * 8) blocks = 148 * 8; if (blocks < 1) blocks = 1;
+  deepfm_input_bwd_kernel<<<blocks, 256, 0, st>>>(U, ustride, inverse, B, S, D, reinterpret_cast<const __nv_bfloat16*>(dX0), ld, gfm,
+                                                  gU, gstride);
+  return nullptr;
+}
+const char* launch_deepfm_head_loss(const void* H, int ldh, int NH, const float* L, int NL, const float* fm, const float* w,
+                                    const float* label, int B, void* dH, float* dL, float* dfm, float* gw, float* sums, float* pred,
+                                    float* loss_out, cudaStream_t st) {
+  if (ldh > 64 * kHeadPairs || (ldh & 1)) return "deepfm_head: hidden width must be even and at most 512 columns";
+  if (NL > 32) return "deepfm_head: at most 32 linear inputs";
+  int blocks = (B + 7) / 8; if (blocks > 148 * 2) blocks = 148 * 2; if (blocks < 1) blocks = 1;
+  deepfm_head_loss_kernel<<<blocks, 256, (NH + NL + 2) * sizeof(float), st>>>(
+      reinterpret_cast<const __nv_bfloat16*>(H), ldh, NH, L, NL, fm, w, label, B, reinterpret_cast<__nv_bfloat16*>(dH), dL, dfm, gw,
+      sums, pred, loss_out);
+  return nullptr;
+}
+
+}  // namespace tn

@@ -49,6 +49,15 @@ void launch_cross_v1_bwd(const float* x0, const float* xl, const float* w, const
                          float* gx0, float* gxl, float* gw, float* gb, cudaStream_t st);
 void launch_relu_mask(void* g, const void* y, long long n, cudaStream_t st);
 
+// deepfm_fused.cu  (return nullptr or a static error string)
+const char* launch_deepfm_input_fwd(const float* U, int ustride, const int* inverse, int B, int S, int D, const float* dense, int Dd,
+                                    int ld_dense, void* X0, int ld, float* fm, cudaStream_t st);
+const char* launch_deepfm_input_bwd(const float* U, int ustride, const int* inverse, int B, int S, int D, const void* dX0, int ld,
+                                    const float* gfm, float* gU, int gstride, cudaStream_t st);
+const char* launch_deepfm_head_loss(const void* H, int ldh, int NH, const float* L, int NL, const float* fm, const float* w,
+                                    const float* label, int B, void* dH, float* dL, float* dfm, float* gw, float* sums, float* pred,
+                                    float* loss_out, cudaStream_t st);
+
 // unique.cu
 void launch_unique_assign(const long long* ids, int n, const float* labels, unsigned long long* dd_keys, int* dd_vals,
                           unsigned scratch_cap, unsigned long long* uniq, int cap, int* inverse, float* show, float* click,

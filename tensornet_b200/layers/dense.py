@@ -40,8 +40,8 @@ class MLP(nn.Module):
     def out_dim(self) -> int:
         return self.hidden_units[-1]
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return F.mlp(x, list(self.weights), self.in_dim, self.relu_last)
+    def forward(self, x: torch.Tensor, grad_premasked: bool = False) -> torch.Tensor:
+        return F.mlp(x, list(self.weights), self.in_dim, self.relu_last, grad_premasked)
 
     def weight(self, i: int) -> torch.Tensor:
         dims = [self.in_dim] + self.hidden_units

@@ -87,6 +87,19 @@ class EmbeddingFeatures(nn.Module):
         pd = self.out_dim
         return [out[:, s * pd:(s + 1) * pd] for s in range(S)]
 
+    def fused_single_hot_inputs(self, features: Dict, training: bool):
+        """(ids, B) when this layer's slots are all single-hot and carry no CVM columns, else None.
+        Used by model-specific fused kernels that consume the pulled rows directly."""
+        if self.use_cvm or self.dim % 4 != 0:
+            return None
+        dev = core.runtime().device
+        ids, offsets, B = gather_columns(features, self._keys, dev)
+        if offsets is not None:
+            return None
+        self.table.set_training(training)
+        self._pending_push = training and self.trainable
+        return ids, B
+
     def backwards(self, grads_and_vars=None):
         """Push this step's sparse gradients to the owning shards and apply the sparse optimizer."""
         if self._pending_push:

@@ -144,6 +144,7 @@ class Model(nn.Module):
         self._static_loss = None
         self._eager_steps = 0
         self._use_graph = False
+        self.use_fused = True
         self.stop_training = False
 
     # ------------------------------------------------------------------ construction
@@ -180,8 +181,13 @@ class Model(nn.Module):
             layer.backwards(grads_and_vars)
 
     def _step_impl(self, features, labels):
-        logits = self(features)
-        loss, _ = self._loss(logits, labels)
+        loss = None
+        fused = getattr(self, "fused_train_loss", None)
+        if fused is not None and not callable(self.loss_fn) and self.use_fused:
+            loss = fused(features, labels, self._sums)      # model-specific fused kernels, when the batch qualifies
+        if loss is None:
+            logits = self(features)
+            loss, _ = self._loss(logits, labels)
         loss.backward()
         if self.optimizer is not None:
             self.optimizer.step()

@@ -58,6 +58,28 @@ class DeepFM(Model):
         n_lin = len(linear_features) * (self.linear_emb.out_dim if self.linear_emb else 0)
         self.sub_model = DeepFMSubModel(n_lin, len(dnn_features), self.deep_emb.out_dim, dense_dim, dnn_hidden_units)
 
+    def fused_train_loss(self, features, labels, sums):
+        """Training loss through the fused DeepFM kernels (gather + FM + operand build in one kernel; head, loss and
+        head backward in one kernel).  Returns None when the inputs do not qualify (ragged slots, CVM columns,
+        CPU); the caller then uses the generic path."""
+        if not core.runtime().on_gpu or self.linear_emb is None:
+            return None
+        mlp = self.sub_model.mlp
+        dq = self.deep_emb.dim // 4
+        if self.deep_emb.dim % 4 or dq & (dq - 1) or dq > 32 or F.pad8(mlp.out_dim + 1) > 512 or self.sub_model.n_linear > 32:
+            return None
+        got = self.deep_emb.fused_single_hot_inputs(features, True)
+        if got is None:
+            return None
+        ids, B = got
+        lin = self.linear_emb(features, training=True)
+        dense = features[self.dense_key].to(ids.device, non_blocking=True) if self.dense_dim else None
+        x0, fm = F.deepfm_input(self.deep_emb._anchor, self.deep_emb.link, ids, B, len(self.deep_emb._keys), dense, True)
+        h = mlp(x0, grad_premasked=True)
+        loss, _ = F.deepfm_head_loss(h, lin, fm, self.sub_model.head.weight, labels.to(ids.device, non_blocking=True), sums,
+                                     mlp.out_dim)
+        return loss
+
     def forward(self, features):
         lin = self.linear_emb(features) if self.linear_emb is not None else None
         deep = self.deep_emb(features)

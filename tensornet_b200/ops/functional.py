@@ -102,7 +102,7 @@ def concat_cast(pieces: Sequence[torch.Tensor], ones: bool = True, widths: Optio
 # =========================================================================================
 class _MLP(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, dims, relu_last, *weights):
+    def forward(ctx, x, dims, relu_last, premasked, *weights):
         # x: bf16 [B, Kp0] (ones column at dims[0]);  weights[l]: fp32 [N_l, pad8(K_l + 1)]
         ext, st = _ext(), _status()
         B = x.shape[0]
@@ -123,6 +123,7 @@ class _MLP(torch.autograd.Function):
         ctx.weights = weights
         ctx.dims = dims
         ctx.relu_last = relu_last
+        ctx.premasked = premasked
         return h
 
     @staticmethod
@@ -134,7 +135,7 @@ class _MLP(torch.autograd.Function):
         L = len(weights)
         B = gy.shape[0]
         g = gy.contiguous()
-        if ctx.relu_last:
+        if ctx.relu_last and not ctx.premasked:
             g = g.clone()
             ext.relu_mask(g, acts[L])
         gx = None
@@ -158,15 +159,18 @@ class _MLP(torch.autograd.Function):
                          mask, None, None, ldh, -1, ldh, 1, 0, st)
                 g = gh
                 gx = gh
-        return (gx if ctx.needs_input_grad[0] else None, None, None, *([None] * L))
+        return (gx if ctx.needs_input_grad[0] else None, None, None, None, *([None] * L))
 
 
-def mlp(x: torch.Tensor, weights: Sequence[torch.Tensor], in_dim: int, relu_last: bool = True) -> torch.Tensor:
+def mlp(x: torch.Tensor, weights: Sequence[torch.Tensor], in_dim: int, relu_last: bool = True,
+        grad_premasked: bool = False) -> torch.Tensor:
     """Run ``x`` (bf16, ones column at ``in_dim``) through the layers ``weights``.
-    Returns bf16 ``[B, pad8(N_last + 1)]`` whose column ``N_last`` is again the constant 1."""
+    Returns bf16 ``[B, pad8(N_last + 1)]`` whose column ``N_last`` is again the constant 1.
+    ``grad_premasked``: the consumer hands back a gradient that is already zero where the last ReLU was
+    inactive (the fused DeepFM head does), so the backward skips its own masking pass."""
     dims = [in_dim] + [int(w.shape[0]) for w in weights[:-1]]
     if x.is_cuda:
-        return _MLP.apply(x, dims, relu_last, *weights)
+        return _MLP.apply(x, dims, relu_last, grad_premasked, *weights)
     h = x.float()
     L = len(weights)
     for l, w in enumerate(weights):
@@ -378,3 +382,70 @@ def cross_v2(x0: torch.Tensor, weights: Sequence[torch.Tensor], dim: int) -> tor
         y = torch.cat([y, torch.ones(y.shape[0], 1), torch.zeros(y.shape[0], x0.shape[1] - dim - 1)], dim=1)
         xl = y.to(torch.bfloat16).float()
     return xl.to(torch.bfloat16)
+
+
+# =========================================================================================
+# DeepFM fusions (GPU only): embedding gather + FM + operand build; head + loss + head backward
+# =========================================================================================
+class _DeepFMInput(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, anchor, link, ids, B, S, dense, training):
+        inverse = link.pull(ids, None, 0, training)
+        D = link.dim
+        Dd = 0 if dense is None else int(dense.shape[1])
+        ld = pad8(S * D + Dd + 1)
+        x0 = torch.empty((B, ld), dtype=torch.bfloat16, device=ids.device)
+        fm = torch.empty(B, dtype=torch.float32, device=ids.device)
+        _ext().deepfm_input_fwd(link.U, link.ustride, inverse, B, S, D, dense, x0, fm)
+        ctx.link, ctx.inverse, ctx.meta = link, inverse, (B, S, D)
+        return x0, fm.view(B, 1)
+
+    @staticmethod
+    def backward(ctx, gx0, gfm):
+        link = ctx.link
+        B, S, D = ctx.meta
+        if gfm is None:
+            gfm = torch.zeros(B, dtype=torch.float32, device=gx0.device)
+        _ext().deepfm_input_bwd(link.U, link.ustride, ctx.inverse, B, S, D, gx0.contiguous(), gfm.contiguous().view(-1), link.gU,
+                                link.gstride)
+        return (None,) * 7
+
+
+def deepfm_input(anchor, link, ids, B, S, dense=None, training=True):
+    """Pull the S single-hot slots of ``ids`` ([S*B], slot after slot) and build in one pass the padded bf16 operand
+    ``[emb | dense | 1 | 0]`` of the first MLP layer plus the second-order FM term ``[B, 1]``."""
+    if dense is not None:
+        dense = dense.float().contiguous()
+    return _DeepFMInput.apply(anchor, link, ids, B, S, dense, training)
+
+
+class _DeepFMHeadLoss(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, h, lin, fm, w, label, sums, n_hidden):
+        B = h.shape[0]
+        dev = h.device
+        dh = torch.empty_like(h)
+        dl = torch.empty_like(lin) if lin is not None else None
+        dfm = torch.empty(B, dtype=torch.float32, device=dev)
+        loss = torch.zeros((), dtype=torch.float32, device=dev)
+        pred = torch.empty(B, dtype=torch.float32, device=dev)
+        _ext().deepfm_head_loss(h, n_hidden, None if lin is None else lin.contiguous(), fm.contiguous().view(-1), w,
+                                label.contiguous().view(-1).float(), dh, dl, dfm, _grad_buffer(w), sums, pred, loss)
+        ctx.save_for_backward(dh, dl if dl is not None else dfm, dfm)
+        ctx.has_lin = lin is not None
+        ctx.mark_non_differentiable(pred)
+        return loss, pred
+
+    @staticmethod
+    def backward(ctx, gloss, _gpred):
+        # The head's gradients were produced by the forward pass for d(loss) = 1, which is what
+        # ``loss.backward()`` supplies; a caller that scales the loss must use the unfused head.
+        dh, dl, dfm = ctx.saved_tensors
+        return dh, (dl if ctx.has_lin else None), dfm.view(-1, 1), None, None, None, None
+
+
+def deepfm_head_loss(h, lin, fm, w, label, sums, n_hidden):
+    """``Dense(1)`` over ``[h[:, :n_hidden] | lin | fm | 1]`` + mean sigmoid cross-entropy, with the whole backward of
+    the head computed in the same kernel.  The weight gradient is accumulated into ``w.grad`` right away and the
+    returned loss must be back-propagated with a unit gradient.  Returns ``(loss, prediction)``."""
+    return _DeepFMHeadLoss.apply(h, lin, fm, w, label, sums, n_hidden)

@@ -1,0 +1,57 @@
+"""Worker of tests/test_gpu_multi.py: trains a small DeepFM on WORLD_SIZE GPUs.  Every rank draws the
+same global batches and trains on its own slice, so the run is comparable with a one-GPU run on the
+full batch.  Rank 0 prints one JSON line."""
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch
+
+import tensornet_b200 as tn
+
+
+def main():
+    out = sys.argv[1]
+    tn.core.init()
+    rt = tn.core.runtime()
+    torch.manual_seed(0)
+    slots = [str(i) for i in range(1, 7)]
+    Bg = 1024
+    B = Bg // rt.world
+    model = tn.models.DeepFM(slots, slots, dnn_hidden_units=(64, 32), embedding_dim=8, dense_dim=5,
+                             sparse_opt=tn.core.Adam(learning_rate=5e-3, initial_scale=0.1), bucket_size=Bg, table_rows=1 << 16)
+    model.compile(optimizer=tn.optimizer.Optimizer(tn.core.Adam(learning_rate=5e-3)), cuda_graph=True, graph_warmup=2)
+    g = torch.Generator().manual_seed(1)
+    data = []
+    for _ in range(6):
+        ids = torch.randint(0, 3000, (len(slots), Bg), generator=g, dtype=torch.int64) * 2654435761 + 17
+        dense = torch.randn(Bg, 5, generator=g)
+        label = ((ids[0] % 3 == 0) ^ (torch.rand(Bg, generator=g) < 0.1)).float()
+        lo, hi = rt.rank * B, (rt.rank + 1) * B
+        data.append(({tn.data.PACKED_KEY: tn.data.PackedFeatures(slots, ids=ids[:, lo:hi].contiguous()), "dense": dense[lo:hi]}, label[lo:hi]))
+    losses = []
+    for epoch in range(5):
+        for f, y in data:
+            l = model.train_on_batch(f, y)
+            t = l.detach().clone()
+            if rt.world > 1:
+                torch.distributed.all_reduce(t, group=rt.device_group)
+            losses.append(float(t) / rt.world)
+    torch.cuda.synchronize()
+    rt.check_status()
+    rows = [int(m.table.n_rows) for m in (model.linear_emb, model.deep_emb)]
+    allrows = rt.all_gather_object(rows)
+    w = model.sub_model.head.weight.detach().float().cpu()
+    ws = rt.all_gather_object(w)
+    if rt.rank == 0:
+        same = all(torch.equal(ws[0], x) for x in ws)
+        json.dump({"world": rt.world, "losses": losses, "rows": [sum(r[i] for r in allrows) for i in range(2)],
+                   "replicas_identical": same, "graph": model._graph is not None,
+                   "multimem": bool(getattr(model.optimizer.table, "uses_multimem", False))}, open(out, "w"))
+    tn.core.shutdown()
+
+
+if __name__ == "__main__":
+    main()

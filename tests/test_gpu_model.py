@@ -48,3 +48,28 @@ def test_deepfm_learns_and_graph_matches_eager(tn_gpu):
     assert p.shape[0] == B and float(p.min()) >= 0 and float(p.max()) <= 1
     s = m1.metric_sums()
     assert s["count"] > 0 and 0 < s["ctr"] < 1
+
+
+def test_fused_deepfm_path_matches_generic_path(tn_gpu):
+    """The DeepFM-specific fused kernels (gather+FM+operand, head+loss+head backward) against the generic op chain."""
+    tn = tn_gpu
+    B = 512
+    m1, slots = _make(tn, graph=False)
+    m2, _ = _make(tn, graph=False)
+    m1.use_fused = False
+    data = _batches(tn, slots, B, 4, seed=3)
+    # same initial dense weights
+    m2.load_state_dict(m1.state_dict())
+    m2.optimizer.table.refresh_shadow()
+    l1, l2 = [], []
+    for epoch in range(3):
+        for f, y in data:
+            l1.append(float(m1.train_on_batch(f, y)))
+            l2.append(float(m2.train_on_batch(f, y)))
+    torch.cuda.synchronize()
+    tn.core.runtime().check_status()
+    for a, b in zip(l1, l2):
+        assert abs(a - b) < 2e-2 * max(1.0, abs(a)), (l1, l2)
+    assert l2[-1] < l2[0]
+    s1, s2 = m1.metric_sums(), m2.metric_sums()
+    assert abs(s1["ctr"] - s2["ctr"]) < 1e-6 and abs(s1["pctr"] - s2["pctr"]) < 2e-2
