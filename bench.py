@@ -134,6 +134,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8192, help="examples per GPU per step")
     ap.add_argument("--pool", type=int, default=16, help="distinct synthetic batches cycled through")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--separate-tables", action="store_true", help="keep the dim-1 linear weights in a table of their own")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -159,7 +160,7 @@ def main():
     torch.manual_seed(1234)
     model = tn.models.DeepFM(slots, slots, dnn_hidden_units=(400, 400, 400), embedding_dim=emb_dim, dense_dim=n_dense,
                              sparse_opt=tn.core.Adam(learning_rate=1e-3, initial_scale=0.1), bucket_size=B,
-                             table_rows=rows)
+                             table_rows=rows, share_linear_table=not args.separate_tables)
     model.compile(optimizer=tn.optimizer.Optimizer(tn.core.Adam(learning_rate=1e-3)), loss="binary_crossentropy",
                   cuda_graph=not args.no_graph)
 
@@ -239,7 +240,7 @@ def main():
             "config": {"model": "DeepFM 26 slots x dim16 (+dim1 linear), FM, MLP 429-400-400-400-1, sparse Adam, dense Adam",
                        "global_batch": G, "seq_len": 1, "parallelism": f"dp{rt.world}+row-sharded embedding tables",
                        "l2": f"inputs cycle through {args.pool} distinct batches; touched table rows exceed L2",
-                       "cuda_graph": model._graph is not None, "last_loss": last,
+                       "cuda_graph": model._graph is not None, "linear_weights": "stored in the embedding rows (one table)" if model.share_linear_table else "separate dim-1 table", "last_loss": last,
                        "dense_multimem": bool(getattr(model.optimizer.table, "uses_multimem", False))},
             "clocks": clocks,
             "e2e": {"value": e2e, "unit": "examples/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": h2d,

@@ -345,19 +345,21 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                    dlogit ? ptr_of<float>(*dlogit) : nullptr, grad_scale, ptr_of<float>(sums), cur_stream());
   });
   m.def("deepfm_input_fwd", [](at::Tensor U, int ustride, at::Tensor inverse, int B, int S, int D, c10::optional<at::Tensor> dense,
-                               at::Tensor X0, at::Tensor fm) {
+                               at::Tensor X0, at::Tensor fm, int lin_col, c10::optional<at::Tensor> Lout) {
     c10::cuda::CUDAGuard guard(U.device());
     const int Dd = dense ? (int)dense->size(1) : 0;
     const char* err = tn::launch_deepfm_input_fwd(ptr_of<float>(U), ustride, ptr_of<int>(inverse), B, S, D,
                                                   dense ? ptr_of<float>(*dense) : nullptr, Dd, dense ? (int)dense->stride(0) : 0,
-                                                  X0.data_ptr(), (int)X0.stride(0), ptr_of<float>(fm), cur_stream());
+                                                  X0.data_ptr(), (int)X0.stride(0), ptr_of<float>(fm), Lout ? lin_col : -1,
+                                                  Lout ? ptr_of<float>(*Lout) : nullptr, cur_stream());
     if (err) throw std::runtime_error(err);
   });
   m.def("deepfm_input_bwd", [](at::Tensor U, int ustride, at::Tensor inverse, int B, int S, int D, at::Tensor dX0, at::Tensor gfm,
-                               at::Tensor gU, int gstride) {
+                               at::Tensor gU, int gstride, int lin_col, c10::optional<at::Tensor> dL) {
     c10::cuda::CUDAGuard guard(U.device());
     const char* err = tn::launch_deepfm_input_bwd(ptr_of<float>(U), ustride, ptr_of<int>(inverse), B, S, D, dX0.data_ptr(),
-                                                  (int)dX0.stride(0), ptr_of<float>(gfm), ptr_of<float>(gU), gstride, cur_stream());
+                                                  (int)dX0.stride(0), ptr_of<float>(gfm), ptr_of<float>(gU), gstride, dL ? lin_col : -1,
+                                                  dL ? ptr_of<float>(*dL) : nullptr, cur_stream());
     if (err) throw std::runtime_error(err);
   });
   m.def("deepfm_head_loss", [](at::Tensor H, int NH, c10::optional<at::Tensor> L, at::Tensor fm, at::Tensor w, at::Tensor label,

@@ -28,7 +28,8 @@ __device__ __forceinline__ float wsum(float v) {
 // D % 4 == 0, dq = D/4 a power of two <= 32.  One warp per example.
 __global__ void deepfm_input_fwd_kernel(const float* __restrict__ U, int ustride, const int* __restrict__ inverse, int B, int S,
                                         int D, const float* __restrict__ dense, int Dd, int ld_dense,
-                                        __nv_bfloat16* __restrict__ X0, int ld, float* __restrict__ fm) {
+                                        __nv_bfloat16* __restrict__ X0, int ld, float* __restrict__ fm, int lin_col,
+                                        float* __restrict__ Lout) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   const int nwarps = (gridDim.x * blockDim.x) >> 5;
   const int dq = D >> 2, nch = S * dq;
@@ -53,6 +54,12 @@ __global__ void deepfm_input_fwd_kernel(const float* __restrict__ U, int ustride
     float part = (lane < dq) ? (s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w) : 0.f;
     part = wsum(part) - wsum(sq);
     if (lane == 0) fm[b] = 0.5f * part;
+    if (lin_col >= 0) {   // the slot's linear weight rides in column `lin_col` of the same row
+      for (int f = lane; f < S; f += 32) {
+        const int v = __ldg(inverse + (size_t)f * B + b);
+        Lout[(size_t)b * S + f] = v >= 0 ? __ldcg(U + (size_t)v * ustride + lin_col) : 0.f;
+      }
+    }
     const int tail0 = S * D;
     for (int j = lane; j < ld - tail0; j += 32) {
       float v = 0.f;
@@ -65,7 +72,7 @@ __global__ void deepfm_input_fwd_kernel(const float* __restrict__ U, int ustride
 
 __global__ void deepfm_input_bwd_kernel(const float* __restrict__ U, int ustride, const int* __restrict__ inverse, int B, int S,
                                         int D, const __nv_bfloat16* __restrict__ dX0, int ld, const float* __restrict__ gfm,
-                                        float* __restrict__ gU, int gstride) {
+                                        float* __restrict__ gU, int gstride, int lin_col, const float* __restrict__ dL) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   const int nwarps = (gridDim.x * blockDim.x) >> 5;
   const int dq = D >> 2, nch = S * dq;
@@ -99,6 +106,12 @@ __global__ void deepfm_input_bwd_kernel(const float* __restrict__ U, int ustride
       g.z = g23.x + gf * (s.z - x.z);
       g.w = g23.y + gf * (s.w - x.w);
       red_add_f32x4(gU + (size_t)v * gstride + 4 * dc, g);
+    }
+    if (lin_col >= 0) {
+      for (int f = lane; f < S; f += 32) {
+        const int v = __ldg(inverse + (size_t)f * B + b);
+        if (v >= 0) atomicAdd(gU + (size_t)v * gstride + lin_col, dL[(size_t)b * S + f]);
+      }
     }
   }
 }
@@ -196,22 +209,22 @@ __global__ void deepfm_head_loss_kernel(const __nv_bfloat16* __restrict__ H, int
 }  // namespace
 
 const char* launch_deepfm_input_fwd(const float* U, int ustride, const int* inverse, int B, int S, int D, const float* dense, int Dd,
-                                    int ld_dense, void* X0, int ld, float* fm, cudaStream_t st) {
+                                    int ld_dense, void* X0, int ld, float* fm, int lin_col, float* Lout, cudaStream_t st) {
   const int dq = D >> 2;
   if ((D & 3) || dq < 1 || dq > 32 || (dq & (dq - 1))) return "deepfm_input: embedding dim must be 4 * 2^k, at most 128";
   if (ld < S * D + Dd + 1 || (ld & 3)) return "deepfm_input: operand row too short";
   int blocks = (B + 7) / 8; if (blocks > 148 * 8) blocks = 148 * 8; if (blocks < 1) blocks = 1;
   deepfm_input_fwd_kernel<<<blocks, 256, 0, st>>>(U, ustride, inverse, B, S, D, dense, Dd, ld_dense,
-                                                  reinterpret_cast<__nv_bfloat16*>(X0), ld, fm);
+                                                  reinterpret_cast<__nv_bfloat16*>(X0), ld, fm, lin_col, Lout);
   return nullptr;
 }
 const char* launch_deepfm_input_bwd(const float* U, int ustride, const int* inverse, int B, int S, int D, const void* dX0, int ld,
-                                    const float* gfm, float* gU, int gstride, cudaStream_t st) {
+                                    const float* gfm, float* gU, int gstride, int lin_col, const float* dL, cudaStream_t st) {
   const int dq = D >> 2;
   if ((D & 3) || dq < 1 || dq > 32 || (dq & (dq - 1))) return "deepfm_input: embedding dim must be 4 * 2^k, at most 128";
   int blocks = (B + 7) / 8; if (blocks > 148 * 8) blocks = 148 * 8; if (blocks < 1) blocks = 1;
   deepfm_input_bwd_kernel<<<blocks, 256, 0, st>>>(U, ustride, inverse, B, S, D, reinterpret_cast<const __nv_bfloat16*>(dX0), ld, gfm,
-                                                  gU, gstride);
+                                                  gU, gstride, lin_col, dL);
   return nullptr;
 }
 const char* launch_deepfm_head_loss(const void* H, int ldh, int NH, const float* L, int NL, const float* fm, const float* w,

@@ -489,28 +489,40 @@ const char* gemm_bf16(const GemmDesc& d, cudaStream_t stream) {
     if (d.had_x0 && !d.had_xl) return "gemm_bf16: Hadamard epilogue needs both x0 and xl";
   }
 
-  // tile N: multiple of 16 (64 when B is MN-major), chosen to keep the grid near one wave
-  int n_cover = d.n_store > d.N ? d.n_store : d.N;
-  int BN = d.BN;
-  if (BN <= 0) {
+  // Tile N (multiple of 16; 64 when B is MN-major) and the split-K factor are chosen together with a small
+  // cost model fitted to measurements on B200: a CTA ingests operand tiles at ~120 GB/s, the epilogue
+  // costs ~22 ns per accumulator column (more for the fp32 reduce), a launch ~3 us, and CTAs run in
+  // waves of 148.
+  const int n_cover = d.n_store > d.N ? d.n_store : d.N;
+  const int kt_total = (d.K + kBK - 1) / kBK;
+  const int m_tiles = (d.M + kBM - 1) / kBM;
+  const bool may_split = d.out_f32 && d.accumulate;
+  if (d.split_k > 1 && !may_split) return "gemm_bf16: split-K needs an fp32 accumulate epilogue";
+  int BN = d.BN, splits = d.split_k;
+  {
     const int gran = d.b_mn ? 64 : 16;
-    const int m_tiles = (d.M + kBM - 1) / kBM;
-    int best = 0; double best_cost = 1e30;
-    for (int cand = gran; cand <= 256; cand += gran) {
-      int n_tiles = (n_cover + cand - 1) / cand;
-      long long ctas = (long long)m_tiles * n_tiles;
-      long long waves = (ctas + 147) / 148;
-      double cost = (double)waves * (cand + 48);   // per-tile time ~ BN plus fixed overhead
-      if (cost < best_cost - 1e-9) { best_cost = cost; best = cand; }
+    double best_cost = 1e30;
+    int best_bn = 0, best_sp = 1;
+    for (int cand = (BN > 0 ? BN : gran); cand <= (BN > 0 ? BN : 256); cand += gran) {
+      const int n_tiles = (n_cover + cand - 1) / cand;
+      const int sp_lo = splits > 0 ? splits : 1;
+      const int sp_hi = splits > 0 ? splits : (may_split ? (kt_total < 32 ? kt_total : 32) : 1);
+      for (int sp = sp_lo; sp <= sp_hi; ++sp) {
+        const int ktps = (kt_total + sp - 1) / sp;
+        const int sp_eff = (kt_total + ktps - 1) / ktps;
+        const long long ctas = (long long)m_tiles * n_tiles * sp_eff;
+        const long long waves = (ctas + 147) / 148;
+        const double per_cta = ktps * (128.0 + cand) * 1.07 + cand * (d.out_f32 ? 33.0 : 22.0) + 600.0;
+        const double cost = waves * per_cta;
+        if (cost < best_cost - 1e-9) { best_cost = cost; best_bn = cand; best_sp = sp_eff; }
+      }
     }
-    BN = best;
+    BN = best_bn;
+    splits = best_sp;
   }
   if (BN % 16 || BN < 16 || BN > 256 || (d.b_mn && BN % 64)) return "gemm_bf16: bad tile N";
-
-  const int kt_total = (d.K + kBK - 1) / kBK;
-  int splits = d.split_k > 0 ? d.split_k : 1;
+  if (splits < 1) splits = 1;
   if (splits > kt_total) splits = kt_total;
-  if (splits > 1 && !(d.out_f32 && d.accumulate)) return "gemm_bf16: split-K needs an fp32 accumulate epilogue";
   int ktps = (kt_total + splits - 1) / splits;
   splits = (kt_total + ktps - 1) / ktps;
 

@@ -24,7 +24,7 @@ struct GemmDesc {
   int ld_aux = 0;
   int ones_col = -1;         // column (>= N) that is written as 1.0: the bias input of the next layer
   int n_store = 0;           // columns written per row (>= N; columns past N get 0, or 1 at ones_col)
-  int split_k = 1;
+  int split_k = 0;           // 0 = choose (only fp32 accumulate outputs may be split)
   int BN = 0;                // tile N override (0 = choose)
   int* status = nullptr;     // device error words
   unsigned long long* prof = nullptr;   // optional [16] timestamps of CTA (0,0,0) for pipeline diagnosis

@@ -51,9 +51,9 @@ void launch_relu_mask(void* g, const void* y, long long n, cudaStream_t st);
 
 // deepfm_fused.cu  (return nullptr or a static error string)
 const char* launch_deepfm_input_fwd(const float* U, int ustride, const int* inverse, int B, int S, int D, const float* dense, int Dd,
-                                    int ld_dense, void* X0, int ld, float* fm, cudaStream_t st);
+                                    int ld_dense, void* X0, int ld, float* fm, int lin_col, float* Lout, cudaStream_t st);
 const char* launch_deepfm_input_bwd(const float* U, int ustride, const int* inverse, int B, int S, int D, const void* dX0, int ld,
-                                    const float* gfm, float* gU, int gstride, cudaStream_t st);
+                                    const float* gfm, float* gU, int gstride, int lin_col, const float* dL, cudaStream_t st);
 const char* launch_deepfm_head_loss(const void* H, int ldh, int NH, const float* L, int NL, const float* fm, const float* w,
                                     const float* label, int B, void* dH, float* dL, float* dfm, float* gw, float* sums, float* pred,
                                     float* loss_out, cudaStream_t st);

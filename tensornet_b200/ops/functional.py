@@ -148,9 +148,8 @@ class _MLP(torch.autograd.Function):
             # weight gradient (incl. the bias column): dW[N, Kp] += g[:, :N]^T . h   (contraction over the batch)
             if w.requires_grad:
                 gw = _grad_buffer(w)
-                split = max(1, min(16, B // 1024))
                 ext.gemm(g, h, gw, N, K + 1, B, int(g.stride(0)), ldh, Kp, True, True, True, False, None, None, None, None,
-                         0, -1, K + 1, split, 0, st)
+                         0, -1, K + 1, 0, 0, st)
             # input gradient: gh[B, ldh] = g[:, :N] . W   masked by the ReLU of the layer below
             if l > 0 or ctx.needs_input_grad[0]:
                 gh = torch.empty((B, ldh), dtype=torch.bfloat16, device=g.device)
@@ -358,9 +357,8 @@ class _CrossV2(torch.autograd.Function):
             gx0.addcmul_(g.float(), u.float())
             du = g * x0
             if w.requires_grad:
-                split = max(1, min(16, B // 1024))
                 ext.gemm(du, xl, _grad_buffer(w), dim, dim + 1, B, Dp, Dp, Kp, True, True, True, False, None, None, None, None, 0, -1,
-                         dim + 1, split, 0, st)
+                         dim + 1, 0, 0, st)
             gxl = torch.empty((B, Dp), dtype=torch.bfloat16, device=g.device)
             ext.gemm(du, wb, gxl, B, min(Kp, Dp), dim, Dp, Kp, Dp, False, True, False, False, None, None, None, None, 0, -1, Dp, 1, 0, st)
             g = g + gxl
@@ -389,34 +387,41 @@ def cross_v2(x0: torch.Tensor, weights: Sequence[torch.Tensor], dim: int) -> tor
 # =========================================================================================
 class _DeepFMInput(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, anchor, link, ids, B, S, dense, training):
+    def forward(ctx, anchor, link, ids, B, S, dense, training, emb_dim, lin_col):
         inverse = link.pull(ids, None, 0, training)
-        D = link.dim
+        D = emb_dim
         Dd = 0 if dense is None else int(dense.shape[1])
         ld = pad8(S * D + Dd + 1)
         x0 = torch.empty((B, ld), dtype=torch.bfloat16, device=ids.device)
         fm = torch.empty(B, dtype=torch.float32, device=ids.device)
-        _ext().deepfm_input_fwd(link.U, link.ustride, inverse, B, S, D, dense, x0, fm)
-        ctx.link, ctx.inverse, ctx.meta = link, inverse, (B, S, D)
-        return x0, fm.view(B, 1)
+        lin = torch.empty((B, S), dtype=torch.float32, device=ids.device) if lin_col >= 0 else None
+        _ext().deepfm_input_fwd(link.U, link.ustride, inverse, B, S, D, dense, x0, fm, lin_col, lin)
+        ctx.link, ctx.inverse, ctx.meta = link, inverse, (B, S, D, lin_col)
+        if lin is None:
+            lin = torch.empty(0, device=ids.device)
+            ctx.mark_non_differentiable(lin)
+        return x0, fm.view(B, 1), lin
 
     @staticmethod
-    def backward(ctx, gx0, gfm):
+    def backward(ctx, gx0, gfm, glin):
         link = ctx.link
-        B, S, D = ctx.meta
+        B, S, D, lin_col = ctx.meta
         if gfm is None:
             gfm = torch.zeros(B, dtype=torch.float32, device=gx0.device)
+        dl = glin.contiguous() if (lin_col >= 0 and glin is not None) else None
         _ext().deepfm_input_bwd(link.U, link.ustride, ctx.inverse, B, S, D, gx0.contiguous(), gfm.contiguous().view(-1), link.gU,
-                                link.gstride)
-        return (None,) * 7
+                                link.gstride, lin_col, dl)
+        return (None,) * 9
 
 
-def deepfm_input(anchor, link, ids, B, S, dense=None, training=True):
+def deepfm_input(anchor, link, ids, B, S, dense=None, training=True, emb_dim=None, lin_col=-1):
     """Pull the S single-hot slots of ``ids`` ([S*B], slot after slot) and build in one pass the padded bf16 operand
-    ``[emb | dense | 1 | 0]`` of the first MLP layer plus the second-order FM term ``[B, 1]``."""
+    ``[emb | dense | 1 | 0]`` of the first MLP layer plus the second-order FM term ``[B, 1]``.  When the table rows carry
+    the slot's linear weight in column ``lin_col`` (``emb_dim`` < row width), also returns those weights ``[B, S]``."""
     if dense is not None:
         dense = dense.float().contiguous()
-    return _DeepFMInput.apply(anchor, link, ids, B, S, dense, training)
+    x0, fm, lin = _DeepFMInput.apply(anchor, link, ids, B, S, dense, training, emb_dim or link.dim, lin_col)
+    return x0, fm, (lin if lin_col >= 0 else None)
 
 
 class _DeepFMHeadLoss(torch.autograd.Function):

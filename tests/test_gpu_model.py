@@ -5,11 +5,12 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _make(tn, graph, seed=0, B=512):
+def _make(tn, graph, seed=0, B=512, share=False):
     torch.manual_seed(seed)
     slots = [str(i) for i in range(1, 7)]
     model = tn.models.DeepFM(slots, slots, dnn_hidden_units=(64, 32), embedding_dim=8, dense_dim=5,
-                             sparse_opt=tn.core.Adam(learning_rate=5e-3, initial_scale=0.1), bucket_size=B, table_rows=1 << 16)
+                             sparse_opt=tn.core.Adam(learning_rate=5e-3, initial_scale=0.1), bucket_size=B, table_rows=1 << 16,
+                             share_linear_table=share)
     model.compile(optimizer=tn.optimizer.Optimizer(tn.core.Adam(learning_rate=5e-3)), cuda_graph=graph, graph_warmup=2)
     return model, slots
 
@@ -50,12 +51,15 @@ def test_deepfm_learns_and_graph_matches_eager(tn_gpu):
     assert s["count"] > 0 and 0 < s["ctr"] < 1
 
 
-def test_fused_deepfm_path_matches_generic_path(tn_gpu):
-    """The DeepFM-specific fused kernels (gather+FM+operand, head+loss+head backward) against the generic op chain."""
+@pytest.mark.parametrize("share", [False, True])
+def test_fused_deepfm_path_matches_generic_path(tn_gpu, share):
+    """The DeepFM-specific fused kernels (gather+FM+operand, head+loss+head backward) against the generic op chain,
+    with separate linear / deep tables and with the linear weight stored in the embedding row."""
     tn = tn_gpu
     B = 512
-    m1, slots = _make(tn, graph=False)
-    m2, _ = _make(tn, graph=False)
+    m1, slots = _make(tn, graph=False, share=share)
+    m2, _ = _make(tn, graph=False, share=share)
+    assert m2.share_linear_table == share
     m1.use_fused = False
     data = _batches(tn, slots, B, 4, seed=3)
     # same initial dense weights
