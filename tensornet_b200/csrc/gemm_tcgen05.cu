@@ -34,9 +34,10 @@ constexpr int kBM = 128;        // tile rows (UMMA M)
 constexpr int kBK = 64;         // contraction elements per stage = one 128-byte swizzle row of bf16
 constexpr int kUmmaK = 16;
 constexpr int kABytes = kBM * kBK * 2;   // 16 KiB
-constexpr int kGemmThreads = 320;        // warp0 TMA, warp1 MMA + TMEM owner, warps 2..9 epilogue
-constexpr int kEpiWarps = 8;
-constexpr int kEpiBytesPerWarp = 12288;  // out block + two auxiliary blocks of 32 rows x 128 B
+constexpr int kEpiSubs = 4;               // epilogue warps per TMEM lane quarter
+constexpr int kEpiWarps = 4 * kEpiSubs;
+constexpr int kGemmThreads = 32 * (2 + kEpiWarps);   // warp0 TMA, warp1 MMA + TMEM owner, the rest epilogue
+constexpr int kEpiBytesPerWarp = 6144;   // out block + two auxiliary blocks of 32 rows x 64 B
 constexpr unsigned kWaitSpins = 20u * 1000u * 1000u;   // ~ a second with the nanosleep below
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -223,38 +224,40 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     }
     __syncwarp();
   } else {
-    // ------------------------------- epilogue (warps 2..9) ------------------------------
-    // Two warps share each TMEM lane quarter and take alternate column chunks.
+    // ------------------------------- epilogue (warps 2..) --------------------------------
+    // kEpiSubs warps share each TMEM lane quarter and take column chunks round-robin.
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
-    const int half = (warp - 2) >> 2;       // 0 or 1: which of the alternating chunks
+    const int sub = (warp - 2) >> 2;        // which of the interleaved chunk sequences
     bool ok = nk > 0;
     if (ok && !mbar_wait(smem_u32(&s_accum), 0u, s_abort)) { *s_abort = 1; ok = false; }
     tc_fence_after();
     if (prof && warp == 2 && lane == 0) prof[10] = globaltimer_ns();
     if (ok) {
       // The accumulator barrier has fired: every TMA load has landed and every MMA has read its
-      // operands, so the stage ring is free.  Each epilogue warp takes 12 KiB of it as a transpose
-      // buffer: TMEM gives a lane one ROW of the tile, global memory wants a warp on one LINE.
-      // Blocks of 32 rows x 128 bytes go through shared memory (16-byte pieces, XOR-swizzled by
-      // row so both the row-wise writes and the line-wise reads are bank-conflict free) and leave
-      // as full 128-byte lines.
+      // operands, so the stage ring is free.  Each epilogue warp takes 6 KiB of it as a transpose
+      // buffer: TMEM gives a lane one ROW of the tile, global memory wants a warp on whole lines.
+      // Blocks of 32 rows x 64 bytes go through shared memory (16-byte pieces, XOR-swizzled so both
+      // the row-wise writes and the line-wise reads are bank-conflict free) and leave as 64-byte
+      // row segments, eight rows per store instruction.
       uint8_t* smem_gen = smem_raw + (base - smem_u32(smem_raw));
       uint8_t* sm_out = smem_gen + (warp - 2) * kEpiBytesPerWarp;
-      uint8_t* sm_a0 = sm_out + 4096;
-      uint8_t* sm_a1 = sm_out + 8192;
+      uint8_t* sm_a0 = sm_out + 2048;
+      uint8_t* sm_a1 = sm_out + 4096;
       const int n_store = p.n_store;
       const int row_base = m0 + q * 32;
       const uint32_t tm_lane = tmem + ((uint32_t)(q * 32) << 16);
-      const int lrow = lane >> 3, lpc = lane & 7;          // line-wise mapping: 8 lanes per row
+      const int lrow = lane >> 2, lpc = lane & 3;          // line-wise mapping: 4 lanes per row
       const bool has_aux = p.mask_aux != nullptr || p.had_x0 != nullptr;
       const bool has_bias = p.bias != nullptr, relu = p.relu != 0;
+      const int my_off = lane * 64;
+      const int my_sw = (lane >> 1) & 3;
       if (!p.out_f32) {
-        for (int c0 = 64 * half; c0 < BN; c0 += 128) {
+        for (int c0 = 32 * sub; c0 < BN; c0 += 32 * kEpiSubs) {
           if (n0 + c0 >= n_store) break;                   // warp-uniform
           if (has_aux) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int r = 4 * i + lrow;
+            for (int i = 0; i < 4; ++i) {
+              const int r = 8 * i + lrow;
               const int grow = row_base + r, gcol = n0 + c0 + lpc * 8;
               uint4 va = make_uint4(0u, 0u, 0u, 0u), vb = va;
               if (grow < p.M && gcol + 8 <= p.ld_aux) {
@@ -262,26 +265,22 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 if (p.mask_aux) va = *reinterpret_cast<const uint4*>(p.mask_aux + off);
                 else { va = *reinterpret_cast<const uint4*>(p.had_x0 + off); vb = *reinterpret_cast<const uint4*>(p.had_xl + off); }
               }
-              const int so = r * 128 + ((lpc ^ (r & 7)) << 4);
+              const int so = r * 64 + ((lpc ^ ((r >> 1) & 3)) << 4);
               *reinterpret_cast<uint4*>(sm_a0 + so) = va;
               if (p.had_x0) *reinterpret_cast<uint4*>(sm_a1 + so) = vb;
             }
             __syncwarp();
           }
-          uint32_t acc[64];
+          uint32_t acc[32];
+          tmem_ld16_nowait(tm_lane + (uint32_t)c0, acc);
+          if (c0 + 16 < BN) tmem_ld16_nowait(tm_lane + (uint32_t)(c0 + 16), acc + 16);
+          else {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            if (c0 + 16 * g < BN && !(p.dbg & 4)) tmem_ld16_nowait(tm_lane + (uint32_t)(c0 + 16 * g), acc + 16 * g);
-            else {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) acc[16 * g + j] = 0u;
-            }
+            for (int j = 16; j < 32; ++j) acc[j] = 0u;
           }
           tmem_ld_wait();
-          if (prof && warp == 2 && lane == 0 && c0 == 0) prof[14] = globaltimer_ns();
 #pragma unroll
-          for (int pc = 0; pc < 8; ++pc) {
-            if (p.dbg & 1) break;
+          for (int pc = 0; pc < 4; ++pc) {
             const int nb = n0 + c0 + pc * 8;
             float v[8];
 #pragma unroll
@@ -294,7 +293,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 #pragma unroll
               for (int j = 0; j < 8; ++j) v[j] = fmaxf(v[j], 0.f);
             }
-            const int so = lane * 128 + ((pc ^ (lane & 7)) << 4);
+            const int so = my_off + ((pc ^ my_sw) << 4);
             if (has_aux) {
               const uint4 a0 = *reinterpret_cast<const uint4*>(sm_a0 + so);
               const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&a0);
@@ -327,14 +326,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
           }
           __syncwarp();
-          if (prof && warp == 2 && lane == 0 && c0 == 0) prof[15] = globaltimer_ns();
+          const int gcol = n0 + c0 + lpc * 8;
+          const bool col_ok = gcol < n_store && c0 + lpc * 8 < BN;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            if (p.dbg & 2) break;
-            const int r = 4 * i + lrow;
-            const int grow = row_base + r, gcol = n0 + c0 + lpc * 8;
-            if (grow < p.M && gcol < n_store && c0 + lpc * 8 < BN) {
-              const uint4 o = *reinterpret_cast<const uint4*>(sm_out + r * 128 + ((lpc ^ (r & 7)) << 4));
+          for (int i = 0; i < 4; ++i) {
+            const int r = 8 * i + lrow;
+            const int grow = row_base + r;
+            if (grow < p.M && col_ok) {
+              const uint4 o = *reinterpret_cast<const uint4*>(sm_out + r * 64 + ((lpc ^ ((r >> 1) & 3)) << 4));
               __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)grow * p.ldc + gcol;
               if (gcol + 8 <= n_store) {
                 *reinterpret_cast<uint4*>(dst) = o;
@@ -347,38 +346,33 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           __syncwarp();
         }
       } else {
-        for (int c0 = 32 * half; c0 < BN; c0 += 64) {
+        for (int c0 = 16 * sub; c0 < BN; c0 += 16 * kEpiSubs) {
           if (n0 + c0 >= n_store) break;                   // warp-uniform
-          uint32_t acc[32];
-#pragma unroll
-          for (int g = 0; g < 2; ++g) {
-            if (c0 + 16 * g < BN) tmem_ld16_nowait(tm_lane + (uint32_t)(c0 + 16 * g), acc + 16 * g);
-            else {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) acc[16 * g + j] = 0u;
-            }
-          }
+          uint32_t acc[16];
+          tmem_ld16_nowait(tm_lane + (uint32_t)c0, acc);
           tmem_ld_wait();
 #pragma unroll
-          for (int pc = 0; pc < 8; ++pc) {
+          for (int pc = 0; pc < 4; ++pc) {
             const int nb = n0 + c0 + pc * 4;
             float v[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               v[j] = __uint_as_float(acc[pc * 4 + j]);
-              if (p.bias && nb + j < p.N) v[j] += __ldg(p.bias + nb + j);
-              if (p.relu) v[j] = fmaxf(v[j], 0.f);
+              if (has_bias && nb + j < p.N) v[j] += __ldg(p.bias + nb + j);
+              if (relu) v[j] = fmaxf(v[j], 0.f);
               if (nb + j >= p.N) v[j] = (nb + j == p.ones_col) ? 1.f : 0.f;
             }
-            *reinterpret_cast<float4*>(sm_out + lane * 128 + ((pc ^ (lane & 7)) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
+            *reinterpret_cast<float4*>(sm_out + my_off + ((pc ^ my_sw) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
           }
           __syncwarp();
+          const int gcol = n0 + c0 + lpc * 4;
+          const bool col_ok = gcol < n_store && c0 + lpc * 4 < BN;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int r = 4 * i + lrow;
-            const int grow = row_base + r, gcol = n0 + c0 + lpc * 4;
-            if (grow < p.M && gcol < n_store && c0 + lpc * 4 < BN) {
-              const float4 o = *reinterpret_cast<const float4*>(sm_out + r * 128 + ((lpc ^ (r & 7)) << 4));
+          for (int i = 0; i < 4; ++i) {
+            const int r = 8 * i + lrow;
+            const int grow = row_base + r;
+            if (grow < p.M && col_ok) {
+              const float4 o = *reinterpret_cast<const float4*>(sm_out + r * 64 + ((lpc ^ ((r >> 1) & 3)) << 4));
               float* dst = reinterpret_cast<float*>(p.C) + (size_t)grow * p.ldc + gcol;
               if (gcol + 4 <= n_store) {
                 if (p.accumulate) red_add_f32x4(dst, o); else *reinterpret_cast<float4*>(dst) = o;
@@ -397,7 +391,6 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   }
 
   if (prof && warp == 2 && lane == 0) prof[11] = globaltimer_ns();
-  if (prof && warp == 6 && lane == 0) prof[13] = globaltimer_ns();
   tc_fence_before();
   __syncthreads();
   if (prof && threadIdx.x == 0) prof[12] = globaltimer_ns();
