@@ -189,9 +189,21 @@ class Model(nn.Module):
             logits = self(features)
             loss, _ = self._loss(logits, labels)
         loss.backward()
-        if self.optimizer is not None:
+        rt = core.runtime()
+        if rt.on_gpu and rt.world == 1 and self.optimizer is not None:
+            # one GPU: the sparse push and the dense update touch disjoint state and neither waits on other
+            # CTAs, so they run side by side
+            main = torch.cuda.current_stream()
+            side = F._side_stream(rt.device)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                self.backwards()
             self.optimizer.step()
-        self.backwards()
+            main.wait_stream(side)
+        else:
+            if self.optimizer is not None:
+                self.optimizer.step()
+            self.backwards()
         return loss.detach()
 
     def _to_device(self, obj):

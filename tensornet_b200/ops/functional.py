@@ -40,6 +40,18 @@ def _bf16_of(p: torch.Tensor) -> torch.Tensor:
     return p.detach().to(torch.bfloat16)
 
 
+_SIDE_STREAMS = {}
+
+
+def _side_stream(device) -> "torch.cuda.Stream":
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    s = _SIDE_STREAMS.get(key)
+    if s is None:
+        s = torch.cuda.Stream(device=device)
+        _SIDE_STREAMS[key] = s
+    return s
+
+
 def _grad_buffer(p: torch.Tensor) -> torch.Tensor:
     if p.grad is None:
         p.grad = torch.zeros_like(p)
@@ -139,6 +151,11 @@ class _MLP(torch.autograd.Function):
             g = g.clone()
             ext.relu_mask(g, acts[L])
         gx = None
+        # The weight gradients are off the critical path (only the optimizer needs them): they run on a side
+        # stream next to the input-gradient chain and are joined before this function returns.
+        main = torch.cuda.current_stream()
+        side = _side_stream(g.device)
+        keep = []
         for l in range(L - 1, -1, -1):
             w = weights[l]
             N, Kp = int(w.shape[0]), int(w.shape[1])
@@ -148,8 +165,13 @@ class _MLP(torch.autograd.Function):
             # weight gradient (incl. the bias column): dW[N, Kp] += g[:, :N]^T . h   (contraction over the batch)
             if w.requires_grad:
                 gw = _grad_buffer(w)
-                ext.gemm(g, h, gw, N, K + 1, B, int(g.stride(0)), ldh, Kp, True, True, True, False, None, None, None, None,
-                         0, -1, K + 1, 0, 0, st)
+                ev = torch.cuda.Event()
+                ev.record(main)
+                side.wait_event(ev)
+                keep.append(g)
+                with torch.cuda.stream(side):
+                    ext.gemm(g, h, gw, N, K + 1, B, int(g.stride(0)), ldh, Kp, True, True, True, False, None, None, None, None,
+                             0, -1, K + 1, 0, 0, st)
             # input gradient: gh[B, ldh] = g[:, :N] . W   masked by the ReLU of the layer below
             if l > 0 or ctx.needs_input_grad[0]:
                 gh = torch.empty((B, ldh), dtype=torch.bfloat16, device=g.device)
@@ -158,6 +180,8 @@ class _MLP(torch.autograd.Function):
                          mask, None, None, ldh, -1, ldh, 1, 0, st)
                 g = gh
                 gx = gh
+        main.wait_stream(side)
+        del keep
         return (gx if ctx.needs_input_grad[0] else None, None, None, None, *([None] * L))
 
 
