@@ -1,0 +1,120 @@
+"""Small, self-contained launches of the hot kernels, for timing with CUDA events and for capturing
+with Nsight Compute (one GPU, a few launches, a few hundred MB on the device).
+
+    python benchmarks/kernel_cases.py gemm_fwd|gemm_dgrad|gemm_wgrad|sparse|deepfm|dense  [--iters N]
+
+Each case prints the per-launch device time (CUDA events around N back-to-back launches after warm-up,
+inputs larger than L2 for the sparse cases) and the algorithmic bytes / FLOPs so a roofline fraction
+can be formed against MEASURED_PEAKS.json.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch
+
+import tensornet_b200 as tn
+from tensornet_b200 import _build
+
+
+def timed(fn, iters):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / iters
+
+
+def peaks():
+    try:
+        return json.load(open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")))
+    except Exception:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "fallback": True}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=["gemm_fwd", "gemm_dgrad", "gemm_wgrad", "sparse", "deepfm", "dense"])
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--batch", type=int, default=8192)
+    a = ap.parse_args()
+    tn.core.init()
+    rt = tn.core.runtime()
+    ext, st, dev = _build.cuda_ext(), rt.status, rt.device
+    pk = peaks()
+    tag = "of fallback" if pk.get("fallback") else "of measured"
+    out = {"case": a.case}
+    if a.case.startswith("gemm"):
+        M, N, K = a.batch, 400, 430
+        A = torch.randn(M, 432, device=dev).bfloat16()
+        Bw = (torch.randn(N, 432, device=dev) * 0.1).bfloat16()
+        C = torch.empty(M, 408, dtype=torch.bfloat16, device=dev)
+        dX = torch.empty(M, 432, dtype=torch.bfloat16, device=dev)
+        dW = torch.zeros(N, 432, device=dev)
+        fns = {"gemm_fwd": lambda: ext.gemm(A, Bw, C, M, N, K, 432, 432, 408, False, False, False, True, None, None, None, None, 0, N, 408, 1, 0, st),
+               "gemm_dgrad": lambda: ext.gemm(C, Bw, dX, M, 432, N, 408, 432, 432, False, True, False, False, None, A, None, None, 432, -1, 432, 1, 0, st),
+               "gemm_wgrad": lambda: ext.gemm(C, A, dW, N, K, M, 408, 432, 432, True, True, True, False, None, None, None, None, 0, -1, K, 0, 0, st)}
+        us = timed(fns[a.case], a.iters)
+        flops = 2.0 * M * N * K
+        out.update(us=us, tflops=flops / us / 1e6, frac_of_bf16_peak=flops / us / 1e6 / pk["bf16_tflops"], peak=tag,
+                   shape=[M, N, K], min_bytes=(M * 432 + N * 432 + M * 408) * 2, hbm_floor_us=(M * 432 + N * 432 + M * 408) * 2 / pk["hbm_gbs"] / 1e3)
+    elif a.case == "sparse":
+        import bench
+        from tensornet_b200.ops.sparse_table_gpu import GpuSparseTable
+        B, S, dim = a.batch, 26, 20
+        data = [b[0].to(dev).reshape(-1) for b in bench.make_batches(8, B, S, 13, 5)]
+        t = GpuSparseTable(tn.core.Adam(learning_rate=1e-3, initial_scale=0.1), dim, rows=1 << 22)
+        lk = t.link(B * S)
+        for ids in data + data:
+            lk.pull(ids, training=True); lk.push()
+        k = [0]
+        def pull():
+            lk.pull(data[k[0] % 8], training=True); k[0] += 1
+        def both():
+            lk.pull(data[k[0] % 8], training=True); lk.push(); k[0] += 1
+        tp = timed(pull, a.iters)
+        lk.push()
+        tb = timed(both, a.iters)
+        nu = lk.unique_counts()[0]
+        pull_bytes = B * S * 8 + nu * (8 + 2 * 4 * t.ustride)
+        push_bytes = nu * 4 * t.gstride + nu * 2 * 4 * t.stride
+        out.update(pull_us=tp, push_us=tb - tp, unique=nu, ids=B * S, phases_us=lk.pull_phase_us(), pull_GBps=pull_bytes / tp / 1e3,
+                   push_GBps=push_bytes / (tb - tp) / 1e3, pull_frac_of_hbm=pull_bytes / tp / 1e3 / pk["hbm_gbs"],
+                   push_frac_of_hbm=push_bytes / (tb - tp) / 1e3 / pk["hbm_gbs"], peak=tag)
+    elif a.case == "deepfm":
+        import bench
+        slots = [str(i) for i in range(1, 27)]
+        model = tn.models.DeepFM(slots, slots, dnn_hidden_units=(400, 400, 400), embedding_dim=16, dense_dim=13,
+                                 sparse_opt=tn.core.Adam(learning_rate=1e-3, initial_scale=0.1), bucket_size=a.batch,
+                                 table_rows=1 << 22, share_linear_table=True)
+        model.compile(optimizer=tn.optimizer.Optimizer(tn.core.Adam(learning_rate=1e-3)), cuda_graph=False)
+        data = [(i.to(dev), d.to(dev), l.to(dev)) for i, d, l in bench.make_batches(4, a.batch, 26, 13, 7)]
+        k = [0]
+        def step():
+            i, d, l = data[k[0] % 4]; k[0] += 1
+            model.train_on_batch({tn.data.PACKED_KEY: tn.data.PackedFeatures(slots, ids=i), "dense": d}, l)
+        out.update(step_us_eager=timed(step, a.iters))
+    else:
+        from tensornet_b200.ops.dense_table import DenseTable
+        p = torch.nn.Parameter(torch.randn(64 << 20, device=dev))
+        dt = DenseTable(tn.core.Adam(learning_rate=1e-3)); dt.init([("p", p)])
+        us = timed(lambda: dt.step(), a.iters)
+        nbytes = p.numel() * (4 * 7 + 2)          # read g,w,m,v; write w,m,v,g(zero) ; write bf16
+        out.update(us=us, GBps=nbytes / us / 1e3, frac_of_hbm=nbytes / us / 1e3 / pk["hbm_gbs"], peak=tag)
+    rt.check_status()
+    print(json.dumps(out), flush=True)
+    tn.core.shutdown()
+
+
+if __name__ == "__main__":
+    main()

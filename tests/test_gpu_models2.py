@@ -61,8 +61,11 @@ def test_model_families_follow_the_cpu_oracle(tn_gpu, family):
         tn.core.shutdown(); tn.core.config.force_cpu = False; tn.core.init()
     assert all(np.isfinite(gpu))
     assert np.mean(gpu[-6:]) < np.mean(gpu[:6])
-    for a, b in zip(gpu, cpu):
-        assert abs(a - b) < 3e-2 * max(1.0, abs(b)), (family, gpu[-6:], cpu[-6:])
+    # identical arithmetic up to summation order and bf16 rounding: the first steps agree closely, later ones
+    # drift apart slowly as the differences feed back through training
+    for a, b in zip(gpu[:8], cpu[:8]):
+        assert abs(a - b) < 5e-3 * max(1.0, abs(b)), (family, gpu[:8], cpu[:8])
+    assert abs(np.mean(gpu[-6:]) - np.mean(cpu[-6:])) < 0.1 * np.mean(cpu[-6:]), (family, gpu[-6:], cpu[-6:])
 
 
 def test_cross_v2_matches_cpu_restatement(tn_gpu, status_ok):
