@@ -99,7 +99,9 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_pull_fused_kernel(const __
       unsigned h = (unsigned)mix64(key ^ 0x2545F4914F6CDD1Dull) & c.dd_mask;
       bool done = false;
       for (unsigned probes = 0; probes <= c.dd_mask; ++probes) {
-        unsigned long long old = atomicCAS(&c.dd_keys[h], kEmptyKey, key);
+        // read first: later occurrences of a hot sign find it without queueing an atomic on the same word
+        unsigned long long old = __ldcg(&c.dd_keys[h]);
+        if (old == kEmptyKey) old = atomicCAS(&c.dd_keys[h], kEmptyKey, key);
         if (old == kEmptyKey) { winner = true; hw = h; done = true; break; }
         if (old == key) { done = true; break; }
         h = (h + 1) & c.dd_mask;

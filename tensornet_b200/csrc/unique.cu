@@ -35,7 +35,9 @@ __global__ void unique_insert_kernel(const long long* __restrict__ ids, int n, u
       unsigned h = uq_home(key, mask);
       bool done = false;
       for (unsigned probes = 0; probes <= mask; ++probes) {
-        const unsigned long long old = atomicCAS(&dd_keys[h], kEmptyKey, key);
+        // read first: later occurrences of a hot sign find it without queueing an atomic on the same word
+        unsigned long long old = __ldcg(&dd_keys[h]);
+        if (old == kEmptyKey) old = atomicCAS(&dd_keys[h], kEmptyKey, key);
         if (old == kEmptyKey) { winner = true; hw = h; done = true; break; }
         if (old == key) { done = true; break; }
         h = (h + 1) & mask;
