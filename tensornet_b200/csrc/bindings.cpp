@@ -103,6 +103,7 @@ struct SparseCtx {
     }
     c.stage_ids = ptr_of<unsigned long long>(comm["stage_ids"].cast<at::Tensor>());
     c.gU = ptr_of<float>(comm["gU"].cast<at::Tensor>());
+    c.cnts = ptr_of<float>(comm["cnts"].cast<at::Tensor>());
     c.cnt = ptr_of<int>(comm["cnt"].cast<at::Tensor>());
     c.cnt_saved = ptr_of<int>(comm["cnt_saved"].cast<at::Tensor>());
     c.req_n = ptr_of<int>(comm["req_n"].cast<at::Tensor>());
@@ -122,7 +123,7 @@ struct SparseCtx {
     c.status = ptr_of<int>(comm["status"].cast<at::Tensor>());
     c.wait_ns = comm["wait_ns"].cast<uint64_t>();
     c.prof = comm.contains("prof") && !comm["prof"].is_none() ? ptr_of<unsigned long long>(comm["prof"].cast<at::Tensor>()) : nullptr;
-    pull_lanes = tn::lanes_for_width_host(c.ustride);
+    pull_lanes = tn::lanes_for_width_host((c.ustride + 3) / 4);   // each lane keeps up to four 16-byte chunks in flight
     push_lanes = tn::lanes_for_width_host(t.dim);
   }
 

@@ -94,8 +94,11 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_pull_fused_kernel(const __
     bool winner = false;
     unsigned hw = 0;
     unsigned long long key = 0;
-    if (i < a.n_ids) {
-      key = canon_key((unsigned long long)a.ids[i]);
+    if (i < a.n_ids) key = canon_key((unsigned long long)a.ids[i]);
+    else key = kEmptyKey;
+    // lanes of the warp that carry the same sign elect one representative: a hot sign costs one probe per warp
+    const unsigned same = __match_any_sync(0xffffffffu, key);
+    if (i < a.n_ids && lane == __ffs(same) - 1) {
       unsigned h = (unsigned)mix64(key ^ 0x2545F4914F6CDD1Dull) & c.dd_mask;
       bool done = false;
       for (unsigned probes = 0; probes <= c.dd_mask; ++probes) {
@@ -137,20 +140,27 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_pull_fused_kernel(const __
   prof_mark(c, 1);
 
   // ---- phase A2: inverse map, show/click counts; ship id segments to the owners -------------------
-  for (int i = tid; i < a.n_ids; i += nth) {
-    unsigned long long key = canon_key((unsigned long long)a.ids[i]);
-    unsigned h = (unsigned)mix64(key ^ 0x2545F4914F6CDD1Dull) & c.dd_mask;
+  for (int base = tid - lane; base < a.n_ids; base += nth) {
+    const int i = base + lane;
+    const bool valid = i < a.n_ids;
+    const unsigned long long key = valid ? canon_key((unsigned long long)a.ids[i]) : kEmptyKey;
+    const unsigned same = __match_any_sync(0xffffffffu, key);
+    const int leader = __ffs(same) - 1;
     int v = -1;
-    for (unsigned probes = 0; probes <= c.dd_mask; ++probes) {
-      unsigned long long k = __ldcg(&c.dd_keys[h]);
-      if (k == key) { v = __ldcg(&c.dd_vals[h]); break; }
-      if (k == kEmptyKey) break;
-      h = (h + 1) & c.dd_mask;
+    if (valid && lane == leader) {
+      unsigned h = (unsigned)mix64(key ^ 0x2545F4914F6CDD1Dull) & c.dd_mask;
+      for (unsigned probes = 0; probes <= c.dd_mask; ++probes) {
+        unsigned long long k = __ldcg(&c.dd_keys[h]);
+        if (k == key) { v = __ldcg(&c.dd_vals[h]); break; }
+        if (k == kEmptyKey) break;
+        h = (h + 1) & c.dd_mask;
+      }
     }
-    a.inverse[i] = v;
-    if (a.training && v >= 0) {
-      float* rec = c.gU + (size_t)v * c.gstride + dim;
-      atomicAdd(rec, 1.0f);
+    v = __shfl_sync(same, v, leader);
+    if (valid) a.inverse[i] = v;
+    if (a.training && valid && v >= 0) {
+      float* rec = c.cnts + 2 * (size_t)v;                             // compact (show, click) pair: stays in L2
+      if (lane == leader) atomicAdd(rec, (float)__popc(same));      // show: occurrences, one add per warp and sign
       if (a.labels != nullptr) {
         float y = a.label_mod > 0 ? a.labels[i % a.label_mod] : a.labels[i];
         if (y != 0.f) atomicAdd(rec + 1, y);
@@ -348,20 +358,30 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_pull_fused_kernel(const __
         } else {
           float show = 0.f, click = 0.f;
           if (t.use_cvm && o.kind == kAdaGrad) { show = row[dim + 1]; click = row[dim + 2]; }
-          for (int ch = gl; ch < uchunks; ch += G) {
-            float4 v = *reinterpret_cast<const float4*>(row + 4 * ch);  // stride >= ustride by layout
+          // up to four 16-byte loads in flight per lane (G >= ceil(uchunks / 4)), then the stores
+          float4 buf[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int ch = gl + k * G;
+            if (ch < uchunks) buf[k] = *reinterpret_cast<const float4*>(row + 4 * ch);   // stride >= ustride by layout
+          }
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int ch = gl + k * G;
+            if (ch >= uchunks) continue;
+            float4 v = buf[k];
             if (4 * ch + 4 > dim) {
               float e[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-              for (int k = 0; k < 4; ++k) {
-                int idx = 4 * ch + k;
+              for (int kk = 0; kk < 4; ++kk) {
+                int idx = 4 * ch + kk;
                 if (idx >= dim) {
                   float x = 0.f;
                   if (t.use_cvm && o.kind == kAdaGrad) {
                     if (idx == dim) x = show;
                     else if (idx == dim + 1) x = logf(click + 1.f) - logf(show + 1.f);
                   }
-                  e[k] = x;
+                  e[kk] = x;
                 }
               }
               v = make_float4(e[0], e[1], e[2], e[3]);
@@ -401,13 +421,12 @@ done:
 // =======================================================================================
 namespace {
 
-// One optimizer step on one row by a group of G lanes.  `g` points at the gradient record:
-// grad[dim] | show | click.   Math as in the reference's Sparse*Value::Apply.
+// One optimizer step on one row by a group of G lanes.  `g` points at the gradient (dim floats), bshow / bclick
+// are the batch's show and click counts of the sign.   Math as in the reference's Sparse*Value::Apply.
 // VEC: dim is a multiple of 4, every lane works on float4 chunks.
 template <bool VEC>
-__device__ __forceinline__ void apply_row(const SparseOptParams& o, float* row, const float* g, int dim, int lane, int G,
-                                          unsigned gmask) {
-  const float bshow = g[dim], bclick = g[dim + 1];
+__device__ __forceinline__ void apply_row(const SparseOptParams& o, float* row, const float* g, float bshow, float bclick,
+                                          int dim, int lane, int G, unsigned gmask) {
   if (o.kind == kAdaGrad) {
     float ss = 0.f;
     if (VEC) {
@@ -512,13 +531,16 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_push_fused_kernel(const __
     for (int j = gid; j < n; j += ngroups) {
       int rr = __ldcg(&c.req_row[j]);
       float* g = c.gU + (size_t)j * gstride;
+      float* cn = c.cnts + 2 * (size_t)j;
       if (rr != kReqNone && rr != kReqPending) {
         float* row = t.rows + (size_t)(rr & kReqRowMask) * t.stride;
-        if (vec) apply_row<true>(a.opt, row, g, dim, lane, G, gmask);
-        else apply_row<false>(a.opt, row, g, dim, lane, G, gmask);
+        const float bshow = cn[0], bclick = cn[1];
+        if (vec) apply_row<true>(a.opt, row, g, bshow, bclick, dim, lane, G, gmask);
+        else apply_row<false>(a.opt, row, g, bshow, bclick, dim, lane, G, gmask);
       }
       __syncwarp(gmask);
       for (int ch = lane; ch < gch; ch += G) *reinterpret_cast<float4*>(g + 4 * ch) = zero4;
+      if (lane == 0) { cn[0] = 0.f; cn[1] = 0.f; }
     }
     goto done;
   }
@@ -531,6 +553,17 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_push_fused_kernel(const __
     const int total = n * gch;
     for (int i = tid; i < total; i += nth) {
       float4 v = *reinterpret_cast<const float4*>(src + 4 * (size_t)i);
+      const int j = i / gch, e0 = 4 * (i - j * gch);
+      if (e0 + 3 >= dim && e0 <= dim + 1) {          // the record's show / click slots come from the compact counters
+        float* cn = c.cnts + 2 * ((size_t)p * capo + j);
+        float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          if (e0 + k == dim) { e[k] = cn[0]; cn[0] = 0.f; }
+          if (e0 + k == dim + 1) { e[k] = cn[1]; cn[1] = 0.f; }
+        }
+        v = make_float4(e[0], e[1], e[2], e[3]);
+      }
       *reinterpret_cast<float4*>(dst + 4 * (size_t)i) = v;
       *reinterpret_cast<float4*>(src + 4 * (size_t)i) = zero4;
     }
@@ -572,8 +605,9 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_push_fused_kernel(const __
       float* g = c.acc + (size_t)ou * gstride;
       if (r >= 0) {
         float* row = t.rows + (size_t)r * t.stride;
-        if (vec) apply_row<true>(a.opt, row, g, dim, lane, G, gmask);
-        else apply_row<false>(a.opt, row, g, dim, lane, G, gmask);
+        const float bshow = g[dim], bclick = g[dim + 1];
+        if (vec) apply_row<true>(a.opt, row, g, bshow, bclick, dim, lane, G, gmask);
+        else apply_row<false>(a.opt, row, g, bshow, bclick, dim, lane, G, gmask);
       }
       __syncwarp(gmask);
       for (int ch = lane; ch < gch; ch += G) *reinterpret_cast<float4*>(g + 4 * ch) = zero4;

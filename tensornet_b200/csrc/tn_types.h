@@ -42,7 +42,8 @@ struct SparseCommView {
   float* U[kMaxWorld];                       // [owner][capo][ustride]    written by owners
   unsigned long long* sig[kMaxWorld];        // [3][kMaxWorld] flag words (epoch << 32 | payload)
   unsigned long long* stage_ids;             // [owner][capo] outgoing signs, grouped by owner
-  float* gU;                                 // [owner][capo][gstride] gradient wrt the pulled rows (+show, click)
+  float* gU;                                 // [owner][capo][gstride] gradient wrt the pulled rows
+  float* cnts;                               // [owner][capo][2] show / click counts of the batch per distinct sign
   int* cnt;                                  // [world] running per-owner unique counts (zero between steps)
   int* cnt_saved;                            // [world] per-owner unique counts of the current step
   int* req_n;                                // [world] as owner: number of signs requested by each sender

@@ -30,8 +30,9 @@ __global__ void unique_insert_kernel(const long long* __restrict__ ids, int n, u
     bool winner = false;
     unsigned hw = 0;
     unsigned long long key = 0;
-    if (i < n) {
-      key = canon_key((unsigned long long)ids[i]);
+    key = i < n ? canon_key((unsigned long long)ids[i]) : kEmptyKey;
+    const unsigned same = __match_any_sync(0xffffffffu, key);      // one probe per warp and distinct sign
+    if (i < n && (int)lane == __ffs(same) - 1) {
       unsigned h = uq_home(key, mask);
       bool done = false;
       for (unsigned probes = 0; probes <= mask; ++probes) {
@@ -66,19 +67,28 @@ __global__ void unique_insert_kernel(const long long* __restrict__ ids, int n, u
 __global__ void unique_lookup_kernel(const long long* __restrict__ ids, int n, const unsigned long long* __restrict__ dd_keys,
                                      const int* __restrict__ dd_vals, unsigned mask, int* __restrict__ inverse,
                                      const float* __restrict__ labels, float* show, float* click) {
-  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
-    const unsigned long long key = canon_key((unsigned long long)ids[i]);
-    unsigned h = uq_home(key, mask);
+  const int tid = blockIdx.x * blockDim.x + threadIdx.x, nth = gridDim.x * blockDim.x;
+  const int lane = threadIdx.x & 31;
+  for (int base = tid - lane; base < n; base += nth) {
+    const int i = base + lane;
+    const bool valid = i < n;
+    const unsigned long long key = valid ? canon_key((unsigned long long)ids[i]) : kEmptyKey;
+    const unsigned same = __match_any_sync(0xffffffffu, key);
+    const int leader = __ffs(same) - 1;
     int v = -1;
-    for (unsigned probes = 0; probes <= mask; ++probes) {
-      const unsigned long long k = dd_keys[h];
-      if (k == key) { v = dd_vals[h]; break; }
-      if (k == kEmptyKey) break;
-      h = (h + 1) & mask;
+    if (valid && lane == leader) {
+      unsigned h = uq_home(key, mask);
+      for (unsigned probes = 0; probes <= mask; ++probes) {
+        const unsigned long long k = dd_keys[h];
+        if (k == key) { v = dd_vals[h]; break; }
+        if (k == kEmptyKey) break;
+        h = (h + 1) & mask;
+      }
     }
-    inverse[i] = v;
-    if (v >= 0) {
-      if (show) atomicAdd(show + v, 1.0f);
+    v = __shfl_sync(same, v, leader);
+    if (valid) inverse[i] = v;
+    if (valid && v >= 0) {
+      if (show && lane == leader) atomicAdd(show + v, (float)__popc(same));
       if (click && labels && labels[i] != 0.f) atomicAdd(click + v, labels[i]);
     }
   }

@@ -178,6 +178,7 @@ class GpuSparseLink:
         loc = dict(
             stage_ids=torch.zeros(n_seg, dtype=torch.int64, device=d),
             gU=torch.zeros(n_seg * self.gstride, dtype=torch.float32, device=d),
+            cnts=torch.zeros(n_seg * 2, dtype=torch.float32, device=d),
             cnt=torch.zeros(8, dtype=torch.int32, device=d),
             cnt_saved=torch.zeros(8, dtype=torch.int32, device=d),
             req_n=torch.zeros(8, dtype=torch.int32, device=d),
@@ -194,6 +195,7 @@ class GpuSparseLink:
         self.arena = arena
         self.U = arena.tensor("U").view(n_seg, self.ustride)
         self.gU = loc["gU"].view(n_seg, self.gstride)
+        self.cnts = loc["cnts"].view(n_seg, 2)       # (show, click) of the batch per distinct sign
         self.cnt_saved = loc["cnt_saved"]
         self.prof = loc["prof"]
         self.comm = dict(world=W, rank=table.rank, capo=capo, gstride=self.gstride, ustride=self.ustride,

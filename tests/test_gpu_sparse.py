@@ -54,14 +54,14 @@ def test_pull_dedup_and_init(tn_gpu, status_ok, dim):
     w_all = np.concatenate(w_all)
     assert abs(w_all.std() - 0.5 / math.sqrt(dim)) < 0.15 * 0.5 / math.sqrt(dim) + 0.02
     # show counts landed in the gradient record
-    gU = lk.gU.cpu()
+    shows = lk.cnts.cpu()
     cnt = {}
     for i in ids.tolist():
         cnt[i] = cnt.get(i, 0) + 1
     for i, v in m.items():
-        assert gU[v, dim] == cnt[i]
+        assert shows[v, 0] == cnt[i]
     # a second pull of the same ids finds the same rows (no growth) and the same values
-    lk.gU.zero_()
+    lk.cnts.zero_()
     inv2 = lk.pull(ids_d, training=False)
     torch.cuda.synchronize()
     assert t.n_rows == n_unique
@@ -110,15 +110,16 @@ def test_push_matches_reference_math(tn_gpu, status_ok, kind, dim):
         grad = torch.randn(n_u, dim, generator=g)
         lk.gU[:n_u, :dim] = grad.to(t.dev)
         gU = lk.gU.cpu().numpy().copy()
+        cn = lk.cnts.cpu().numpy().copy()
         stage = lk.comm["stage_ids"].cpu().numpy().view(np.uint64)
         lk.push()
         torch.cuda.synchronize()
         tn.core.runtime().check_status()
         after = _host_rows(t)
-        assert float(lk.gU.abs().sum()) == 0.0      # re-zeroed for the next step
+        assert float(lk.gU.abs().sum()) == 0.0 and float(lk.cnts.abs().sum()) == 0.0     # re-zeroed for the next step
         for j in range(n_u):
             key = int(stage[j])
-            exp = _apply_ref(kind, opt, before[key], gU[j, :dim], gU[j, dim], gU[j, dim + 1], dim)
+            exp = _apply_ref(kind, opt, before[key], gU[j, :dim], cn[j, 0], cn[j, 1], dim)
             got = after[key]
             nf = dim + 3 if kind == "AdaGrad" else 3 * dim
             assert np.allclose(got[:nf], exp[:nf], rtol=2e-5, atol=1e-6), (kind, step, j)
