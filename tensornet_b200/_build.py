@@ -33,6 +33,8 @@ CUDA_SOURCES = [
     "dense_fused.cu",
     "elementwise.cu",
     "serving.cu",
+    "peer_probe.cu",
+    "bn.cu",
     "unique.cu",
     "deepfm_fused.cu",
     "no_alloc.cu",

@@ -117,9 +117,10 @@ def load_dense_table(handle: int, path: str):
 
 # ----------------------------------------------------------------------------- batch norm
 def create_bn_table(name: str, bn_size: int, sync: bool, moment: float, max_count: int, use_pctr_dnn_bn: bool = False) -> int:
-    from ..ops.bn_table import BnTable
+    from ..ops.bn_table import BnTable, GpuBnTable
 
-    t = BnTable(name, bn_size, sync, moment, max_count, use_pctr_dnn_bn)
+    cls = GpuBnTable if runtime().on_gpu else BnTable
+    t = cls(name, bn_size, sync, moment, max_count, use_pctr_dnn_bn)
     t.handle = len(_bn_tables)
     _bn_tables.append(t)
     return t.handle

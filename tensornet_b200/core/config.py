@@ -33,6 +33,7 @@ class Config:
     seed: int = 0x7E50A
     #: use NVSwitch multicast (multimem) in the dense path when the mapping exists
     use_multimem: bool = True
+    gate_first_gemm: bool = True   # multi-GPU: first MLP GEMM waits for the dense all-gather (no closing barrier)
     #: capture the train step in a CUDA graph
     cuda_graph: bool = True
     #: force the CPU oracle path even when a GPU is visible
@@ -47,6 +48,7 @@ class Config:
         c.wait_budget_s = _env("TN_WAIT_BUDGET_S", c.wait_budget_s, float)
         c.seed = _env("TN_SEED", c.seed, int)
         c.use_multimem = _env("TN_USE_MULTIMEM", c.use_multimem, bool)
+        c.gate_first_gemm = _env("TN_GATE_FIRST_GEMM", c.gate_first_gemm, bool)
         c.cuda_graph = _env("TN_CUDA_GRAPH", c.cuda_graph, bool)
         c.force_cpu = _env("TN_FORCE_CPU", c.force_cpu, bool)
         return c

@@ -91,13 +91,15 @@ struct SparseCtx {
     TORCH_CHECK(c.capo % 4 == 0, "segment capacity must be a multiple of 4");
     auto inbox = comm["inbox_ids"].cast<std::vector<int64_t>>();
     auto ginbox = comm["ginbox"].cast<std::vector<int64_t>>();
+    auto cinbox = comm["cinbox"].cast<std::vector<int64_t>>();
     auto U = comm["U"].cast<std::vector<int64_t>>();
     auto sig = comm["sig"].cast<std::vector<int64_t>>();
-    TORCH_CHECK((int)inbox.size() == c.world && (int)ginbox.size() == c.world && (int)U.size() == c.world &&
+    TORCH_CHECK((int)inbox.size() == c.world && (int)ginbox.size() == c.world && (int)cinbox.size() == c.world && (int)U.size() == c.world &&
                     (int)sig.size() == c.world, "peer pointer tables must have `world` entries");
     for (int p = 0; p < c.world; ++p) {
       c.inbox_ids[p] = ptr_of<unsigned long long>(inbox[p]);
       c.ginbox[p] = ptr_of<float>(ginbox[p]);
+      c.cinbox[p] = ptr_of<float>(cinbox[p]);
       c.U[p] = ptr_of<float>(U[p]);
       c.sig[p] = ptr_of<unsigned long long>(sig[p]);
     }
@@ -174,6 +176,10 @@ struct DenseCtx {
     a.world = d["world"].cast<int>();
     a.rank = d["rank"].cast<int>();
     a.grad_scale = d["grad_scale"].cast<float>();
+    // small arrays: the owner re-zeroes every replica's gradient through the switch (no extra grid barrier);
+    // large ones: each GPU clears its own replica after the closing barrier (no NVLink bytes)
+    a.gated = d.contains("gated") ? d["gated"].cast<int>() : 0;
+    a.zero_local = d.contains("zero_local") ? d["zero_local"].cast<int>() : (a.world > 1 && a.n > (1ll << 21) ? 1 : 0);
     auto W = d["W"].cast<std::vector<int64_t>>();
     auto G = d["G"].cast<std::vector<int64_t>>();
     auto Wb = d["Wb"].cast<std::vector<int64_t>>();
@@ -195,12 +201,80 @@ struct DenseCtx {
     a.wait_ns = d["wait_ns"].cast<uint64_t>();
   }
   void step() { check(tn::launch_dense_step(a, cur_stream()), "dense step launch"); }
+  void set_gated(bool g) { a.gated = g ? 1 : 0; }
+};
+
+// Device-resident batch-norm table and the per-step kernels of the layer.
+struct BnCtx {
+  tn::BnTableView t{};
+  tn::BnSyncView s{};
+  bool has_sync = false;
+  double* batch = nullptr;     // [3][C] per-step scratch, kept zero between steps
+  double* scratch = nullptr;   // [3][C] sum of the peers' increments during an exchange
+  py::dict keep;
+  BnCtx(py::dict d) {
+    keep = d;
+    t.C = d["C"].cast<int>();
+    t.pctr = d["pctr"].cast<int>();
+    t.moment = d["moment"].cast<double>();
+    t.max_count = d["max_count"].cast<long long>();
+    t.total_sum = ptr_of<double>(d["total_sum"].cast<at::Tensor>());
+    t.total_sum_err = ptr_of<double>(d["total_sum_err"].cast<at::Tensor>());
+    t.total_sq = ptr_of<double>(d["total_sq"].cast<at::Tensor>());
+    t.total_sq_err = ptr_of<double>(d["total_sq_err"].cast<at::Tensor>());
+    t.total_count = ptr_of<double>(d["total_count"].cast<at::Tensor>());
+    t.inc = ptr_of<double>(d["inc"].cast<at::Tensor>());
+    t.mean = ptr_of<float>(d["mean"].cast<at::Tensor>());
+    t.var = ptr_of<float>(d["var"].cast<at::Tensor>());
+    batch = ptr_of<double>(d["batch"].cast<at::Tensor>());
+    scratch = ptr_of<double>(d["scratch"].cast<at::Tensor>());
+    s.world = d["world"].cast<int>();
+    s.rank = d["rank"].cast<int>();
+    if (s.world > 1) {
+      auto inc = d["inc_ptrs"].cast<std::vector<int64_t>>();
+      auto sig = d["sig_ptrs"].cast<std::vector<int64_t>>();
+      TORCH_CHECK((int)inc.size() == s.world && (int)sig.size() == s.world, "peer tables");
+      for (int p = 0; p < s.world; ++p) { s.inc[p] = ptr_of<const double>(inc[p]); s.sig[p] = ptr_of<unsigned long long>(sig[p]); }
+      s.epoch = ptr_of<unsigned long long>(d["epoch"].cast<at::Tensor>());
+      s.status = ptr_of<int>(d["status"].cast<at::Tensor>());
+      s.wait_ns = d["wait_ns"].cast<uint64_t>();
+      has_sync = true;
+    }
+  }
+  // sums of one batch -> totals, increments and moments (two launches)
+  void push(at::Tensor x, bool centered) {
+    TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kFloat && x.dim() == 2 && x.size(1) == t.C && x.stride(1) == 1, "x must be fp32 [B, C]");
+    c10::cuda::CUDAGuard guard(x.device());
+    tn::launch_bn_batch_stats(ptr_of<float>(x), (int)x.stride(0), (int)x.size(0), t.C, centered ? t.mean : nullptr, batch, cur_stream());
+    tn::launch_bn_table_append(t, batch, cur_stream());
+  }
+  // fold a record the host has staged in `batch`
+  void append_staged() { tn::launch_bn_table_append(t, batch, cur_stream()); }
+  void refresh() { tn::launch_bn_table_refresh(t, cur_stream()); }
+  void sync() {
+    if (has_sync) tn::launch_bn_table_sync(t, s, scratch, cur_stream());
+  }
+  void apply_fwd(at::Tensor x, at::Tensor mean, at::Tensor var, c10::optional<at::Tensor> gamma, c10::optional<at::Tensor> beta, double eps,
+                 at::Tensor y) {
+    c10::cuda::CUDAGuard guard(x.device());
+    tn::launch_bn_apply_fwd(ptr_of<float>(x), (int)x.stride(0), (int)x.size(0), t.C, ptr_of<float>(mean), ptr_of<float>(var), gamma ? ptr_of<float>(*gamma) : nullptr,
+                            beta ? ptr_of<float>(*beta) : nullptr, (float)eps, ptr_of<float>(y), (int)y.stride(0), cur_stream());
+  }
+  void apply_bwd(at::Tensor dy, at::Tensor x, at::Tensor mean, at::Tensor var, c10::optional<at::Tensor> gamma, double eps,
+                 c10::optional<at::Tensor> dx, c10::optional<at::Tensor> gg, c10::optional<at::Tensor> gb) {
+    c10::cuda::CUDAGuard guard(x.device());
+    tn::launch_bn_apply_bwd(ptr_of<float>(dy), (int)dy.stride(0), ptr_of<float>(x), (int)x.stride(0), (int)x.size(0), t.C,
+                            ptr_of<float>(mean), ptr_of<float>(var),
+                            gamma ? ptr_of<float>(*gamma) : nullptr, (float)eps, dx ? ptr_of<float>(*dx) : nullptr,
+                            dx ? (int)dx->stride(0) : 0, gg ? ptr_of<float>(*gg) : nullptr, gb ? ptr_of<float>(*gb) : nullptr, cur_stream());
+  }
 };
 
 void gemm(at::Tensor A, at::Tensor B, at::Tensor C, int M, int N, int K, int lda, int ldb, int ldc, bool a_mn, bool b_mn,
           bool accumulate, bool relu, c10::optional<at::Tensor> bias, c10::optional<at::Tensor> mask_aux,
           c10::optional<at::Tensor> had_x0, c10::optional<at::Tensor> had_xl, int ld_aux, int ones_col, int n_store,
-          int split_k, int BN, at::Tensor status, c10::optional<at::Tensor> prof, int dbg) {
+          int split_k, int BN, at::Tensor status, c10::optional<at::Tensor> prof, int dbg, c10::optional<at::Tensor> gate_flags,
+          c10::optional<at::Tensor> gate_epoch, int gate_world, uint64_t gate_wait_ns) {
   TORCH_CHECK(A.is_cuda() && B.is_cuda() && C.is_cuda(), "gemm: CUDA tensors");
   TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16, "gemm: bf16 operands");
   c10::cuda::CUDAGuard guard(A.device());
@@ -218,6 +292,13 @@ void gemm(at::Tensor A, at::Tensor B, at::Tensor C, int M, int N, int K, int lda
   d.status = ptr_of<int>(status);
   d.prof = prof.has_value() ? ptr_of<unsigned long long>(*prof) : nullptr;
   d.dbg = dbg;
+  if (gate_flags.has_value()) {
+    TORCH_CHECK(gate_epoch.has_value() && gate_world >= 1 && gate_world <= tn::kMaxWorld, "gemm: gate wants flags, epoch and a world size");
+    d.gate_flags = ptr_of<const unsigned long long>(*gate_flags);
+    d.gate_epoch = ptr_of<const unsigned long long>(*gate_epoch);
+    d.gate_world = gate_world;
+    d.gate_wait_ns = gate_wait_ns;
+  }
   const char* err = tn::gemm_bf16(d, cur_stream());
   if (err) throw std::runtime_error(err);
 }
@@ -231,11 +312,20 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("set_table", &SparseCtx::set_table)
       .def("pull", &SparseCtx::pull)
       .def("push", &SparseCtx::push);
-  py::class_<DenseCtx>(m, "DenseCtx").def(py::init<py::dict>()).def("step", &DenseCtx::step);
+  py::class_<BnCtx>(m, "BnCtx")
+      .def(py::init<py::dict>())
+      .def("push", &BnCtx::push)
+      .def("append_staged", &BnCtx::append_staged)
+      .def("refresh", &BnCtx::refresh)
+      .def("sync", &BnCtx::sync)
+      .def("apply_fwd", &BnCtx::apply_fwd)
+      .def("apply_bwd", &BnCtx::apply_bwd);
+  py::class_<DenseCtx>(m, "DenseCtx").def(py::init<py::dict>()).def("step", &DenseCtx::step).def("set_gated", &DenseCtx::set_gated);
   m.def("gemm", &gemm, py::arg("A"), py::arg("B"), py::arg("C"), py::arg("M"), py::arg("N"), py::arg("K"), py::arg("lda"),
         py::arg("ldb"), py::arg("ldc"), py::arg("a_mn"), py::arg("b_mn"), py::arg("accumulate"), py::arg("relu"), py::arg("bias"),
         py::arg("mask_aux"), py::arg("had_x0"), py::arg("had_xl"), py::arg("ld_aux"), py::arg("ones_col"), py::arg("n_store"),
-        py::arg("split_k"), py::arg("BN"), py::arg("status"), py::arg("prof") = py::none(), py::arg("dbg") = 0);
+        py::arg("split_k"), py::arg("BN"), py::arg("status"), py::arg("prof") = py::none(), py::arg("dbg") = 0,
+        py::arg("gate_flags") = py::none(), py::arg("gate_epoch") = py::none(), py::arg("gate_world") = 0, py::arg("gate_wait_ns") = 0);
   m.def("launch_count", []() { return g_launches.load(); });
 
   // ---- CUDA IPC peer memory (fallback transport for the symmetric heap) --------------------------
@@ -262,6 +352,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     auto opts = at::TensorOptions().dtype(at::kByte).device(at::kCUDA, device);
     return at::from_blob(ptr_of<void>(p), {nbytes}, opts);
   });
+
+  m.def("peer_copy", [](int64_t dst, int64_t src, int64_t nbytes, int mode, int blocks, int threads, bool fence) {
+    TORCH_CHECK(nbytes % 16 == 0 && dst % 16 == 0 && src % 16 == 0, "peer_copy wants 16-byte aligned pointers and size");
+    TORCH_CHECK(threads >= 32 && threads <= 1024 && blocks >= 1, "bad launch shape");
+    tn::launch_peer_copy(ptr_of<void>(dst), ptr_of<void>(src), nbytes, mode, blocks, threads, fence ? 1 : 0, cur_stream());
+  }, "SM-issued copy between raw (possibly peer) addresses; link bandwidth probe");
 
   m.def("pool_fwd", [](at::Tensor U, int ustride, at::Tensor inverse, c10::optional<at::Tensor> offsets, int B, int S, int pd,
                        int combiner, at::Tensor out, int out_ld) {

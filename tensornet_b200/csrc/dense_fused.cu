@@ -125,6 +125,26 @@ __device__ __forceinline__ bool peer_barrier(const DenseStepArgs& a, int which, 
   return ok;
 }
 
+// Optimizer update of one 4-element group of the owned chunk: reduced gradient in, new weight out.
+__device__ __forceinline__ float4 dense_update4(const DenseStepArgs& a, float alpha, float lr, float4 g, long long i, long long li) {
+  const DenseOptParams& o = a.opt;
+  g.x *= a.grad_scale; g.y *= a.grad_scale; g.z *= a.grad_scale; g.w *= a.grad_scale;
+  float4 w = reinterpret_cast<float4*>(a.W[a.rank])[i];
+  float4 s0 = reinterpret_cast<float4*>(a.s0)[li], s1 = reinterpret_cast<float4*>(a.s1)[li];   // state is indexed within the chunk
+  if (o.kind == 0) {
+    adam4(o, alpha, g, w, s0, s1);
+  } else {
+    float4 s2 = reinterpret_cast<float4*>(a.s2)[li];
+    adagrad4(o, lr, g, w, s0, s1, s2);
+    reinterpret_cast<float4*>(a.s2)[li] = s2;
+  }
+  reinterpret_cast<float4*>(a.s0)[li] = s0;
+  reinterpret_cast<float4*>(a.s1)[li] = s1;
+  return w;
+}
+
+constexpr int kDenseUnroll = 4;   // independent 16-byte reductions in flight per thread (NVLink round trips overlap)
+
 __global__ void __launch_bounds__(kDThreads) dense_fused_kernel(const __grid_constant__ DenseStepArgs a) {
   const DenseOptParams& o = a.opt;
   GridSync gs;
@@ -139,56 +159,81 @@ __global__ void __launch_bounds__(kDThreads) dense_fused_kernel(const __grid_con
   long long hi4 = lo4 + chunk4;
   const long long n4 = a.n >> 2;
   if (hi4 > n4) hi4 = n4;
+  const long long nth = (long long)gridDim.x * blockDim.x;
+  const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  // Re-zeroing the gradient replicas through the switch costs as much NVLink ingress as the fp32 weights;
+  // large arrays are zeroed by their own GPU instead, once every peer has finished reading them.
+  const bool zero_remote = !a.zero_local;
 
   // all GPUs have finished writing their gradients (stream order on each GPU + this barrier)
-  __threadfence_system();
   peer_barrier(a, 0, epoch, 41);
   if (!gs.sync(42, false)) goto done;
 
-  for (long long i = lo4 + blockIdx.x * (long long)blockDim.x + threadIdx.x; i < hi4; i += (long long)gridDim.x * blockDim.x) {
-    float4 g;
+  for (long long base = lo4 + blockIdx.x * (long long)blockDim.x + threadIdx.x; base < hi4; base += nth * kDenseUnroll) {
+    float4 g[kDenseUnroll];
     if (a.G_mc) {
-      g = mm_ld_reduce_f4(a.G_mc + 4 * i);
+#pragma unroll
+      for (int u = 0; u < kDenseUnroll; ++u) {
+        const long long i = base + u * nth;
+        if (i < hi4) g[u] = mm_ld_reduce_f4(a.G_mc + 4 * i);
+      }
     } else {
-      g = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int u = 0; u < kDenseUnroll; ++u) g[u] = z4;
       for (int p = 0; p < W; ++p) {
-        float4 x = ldcg_f4(a.G[(R + p) % W] + 4 * i);
-        g.x += x.x; g.y += x.y; g.z += x.z; g.w += x.w;
+        const float* Gp = a.G[(R + p) % W];
+        float4 x[kDenseUnroll];
+#pragma unroll
+        for (int u = 0; u < kDenseUnroll; ++u) {
+          const long long i = base + u * nth;
+          if (i < hi4) x[u] = ldcg_f4(Gp + 4 * i);
+        }
+#pragma unroll
+        for (int u = 0; u < kDenseUnroll; ++u) {
+          const long long i = base + u * nth;
+          if (i < hi4) { g[u].x += x[u].x; g[u].y += x[u].y; g[u].z += x[u].z; g[u].w += x[u].w; }
+        }
       }
     }
-    g.x *= a.grad_scale; g.y *= a.grad_scale; g.z *= a.grad_scale; g.w *= a.grad_scale;
-    // owner state is indexed within the chunk
-    const long long li = i - lo4;
-    float4 w = reinterpret_cast<float4*>(a.W[R])[i];
-    float4 s0 = reinterpret_cast<float4*>(a.s0)[li], s1 = reinterpret_cast<float4*>(a.s1)[li];
-    if (o.kind == 0) {
-      adam4(o, alpha, g, w, s0, s1);
-    } else {
-      float4 s2 = reinterpret_cast<float4*>(a.s2)[li];
-      adagrad4(o, lr, g, w, s0, s1, s2);
-      reinterpret_cast<float4*>(a.s2)[li] = s2;
-    }
-    reinterpret_cast<float4*>(a.s0)[li] = s0;
-    reinterpret_cast<float4*>(a.s1)[li] = s1;
-    const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
-    const uint2 wb = f4_to_bf16x4(w);
-    if (a.G_mc) {
-      mm_st_f4(a.W_mc + 4 * i, w);
-      if (a.Wb_mc) mm_st_b32x2(reinterpret_cast<uint2*>(a.Wb_mc) + i, wb);
-      mm_st_f4(a.G_mc + 4 * i, z4);
-    } else {
-      for (int p = 0; p < W; ++p) {
-        const int d = (R + p) % W;
-        reinterpret_cast<float4*>(a.W[d])[i] = w;
-        if (a.Wb[d]) reinterpret_cast<uint2*>(a.Wb[d])[i] = wb;
-        reinterpret_cast<float4*>(a.G[d])[i] = z4;
+#pragma unroll
+    for (int u = 0; u < kDenseUnroll; ++u) {
+      const long long i = base + u * nth;
+      if (i >= hi4) continue;
+      const float4 w = dense_update4(a, alpha, lr, g[u], i, i - lo4);
+      const uint2 wb = f4_to_bf16x4(w);
+      if (a.G_mc) {
+        mm_st_f4(a.W_mc + 4 * i, w);
+        if (a.Wb_mc) mm_st_b32x2(reinterpret_cast<uint2*>(a.Wb_mc) + i, wb);
+        if (zero_remote) mm_st_f4(a.G_mc + 4 * i, z4);
+        else reinterpret_cast<float4*>(a.G[R])[i] = z4;
+      } else {
+        for (int p = 0; p < W; ++p) {
+          const int d = (R + p) % W;
+          reinterpret_cast<float4*>(a.W[d])[i] = w;
+          if (a.Wb[d]) reinterpret_cast<uint2*>(a.Wb[d])[i] = wb;
+          if (zero_remote || d == R) reinterpret_cast<float4*>(a.G[d])[i] = z4;
+        }
       }
     }
   }
 
   // every owner's chunk has landed in every replica before anyone's next forward starts
   if (!gs.sync(43, true)) goto done;
-  peer_barrier(a, 1, epoch, 44);
+  if (a.gated && zero_remote) {
+    // no closing wait: tell every GPU (this one included) that the owned chunk is in place; the consumer checks
+    if (blockIdx.x == 0 && threadIdx.x < W) st_release_sys_u64(a.sig[threadIdx.x] + 2 * kMaxWorld + R, epoch << 32);
+  } else {
+    peer_barrier(a, 1, epoch, 44);
+    if (a.gated && blockIdx.x == 0 && threadIdx.x < W)      // keep the gate words current in this mode too
+      st_release_sys_u64(a.sig[R] + 2 * kMaxWorld + threadIdx.x, epoch << 32);
+  }
+  if (!zero_remote) {
+    // every peer has read its chunk of this GPU's gradient: clear the part this GPU does not own
+    if (!gs.sync(45, false)) goto done;
+    float4* Gl = reinterpret_cast<float4*>(a.G[R]);
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += nth)
+      if (i < lo4 || i >= hi4) Gl[i] = z4;
+  }
   __syncthreads();
   if (blockIdx.x == 0 && threadIdx.x == 0) {
     *a.epoch = epoch;
@@ -218,8 +263,10 @@ cudaError_t launch_dense_step(const DenseStepArgs& a, cudaStream_t st) {
   long long n4 = a.chunk >> 2;
   int blocks = (int)((n4 + kDThreads - 1) / kDThreads);
   if (blocks < 1) blocks = 1;
-  int cap = sms * (per_sm > 2 ? 2 : (per_sm < 1 ? 1 : per_sm));
+  blocks = (blocks + kDenseUnroll - 1) / kDenseUnroll;
+  int cap = sms * (per_sm < 1 ? 1 : per_sm);      // as many warps as fit: the loop is bound by loads in flight
   if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
   void* params[] = {(void*)&a};
   return cudaLaunchCooperativeKernel((const void*)dense_fused_kernel, dim3(blocks), dim3(kDThreads), params, 0, st);
 }

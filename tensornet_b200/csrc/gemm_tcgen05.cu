@@ -172,7 +172,23 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   if (warp == 0) {
     // ------------------------------- TMA producer ---------------------------------------
     if (lane == 0) {
-      for (int i = 0; i < nk; ++i) {
+      bool gate_ok = true;
+      if (p.gate_flags != nullptr) {
+        // every owner's chunk of the weight array has landed in this GPU's replica
+        const unsigned long long want = __ldcg(p.gate_epoch);
+        for (int q = 0; q < p.gate_world && gate_ok; ++q) {
+          const unsigned long long t0 = globaltimer_ns();
+          unsigned spins = 0;
+          while ((ld_acquire_sys_u64(p.gate_flags + q) >> 32) < want) {
+            if (((++spins) & 63u) == 0 && globaltimer_ns() - t0 > p.gate_wait_ns) { gate_ok = false; break; }
+            __nanosleep(64);
+          }
+          if (!gate_ok) set_status(p.status, kPeerWaitTimeout, 70, q);
+        }
+        asm volatile("fence.proxy.async;" ::: "memory");
+        if (!gate_ok) *s_abort = 1;
+      }
+      for (int i = 0; i < nk && gate_ok; ++i) {
         const int s = i % kStages;
         const uint32_t ph = (uint32_t)(i / kStages) & 1u;
         if (!mbar_wait(smem_u32(&s_empty[s]), ph ^ 1u, s_abort)) { *s_abort = 1; break; }
@@ -535,6 +551,7 @@ const char* gemm_bf16(const GemmDesc& d, cudaStream_t stream) {
   p.had_x0 = reinterpret_cast<const __nv_bfloat16*>(d.had_x0);
   p.had_xl = reinterpret_cast<const __nv_bfloat16*>(d.had_xl);
   p.ld_aux = d.ld_aux; p.ones_col = d.ones_col; p.n_store = n_cover; p.bias = d.bias; p.status = d.status; p.prof = d.prof; p.dbg = d.dbg;
+  p.gate_flags = d.gate_flags; p.gate_epoch = d.gate_epoch; p.gate_world = d.gate_world; p.gate_wait_ns = d.gate_wait_ns;
 
   dim3 grid((n_cover + BN - 1) / BN, (d.M + kBM - 1) / kBM, splits);
   const size_t b_bytes = (size_t)BN * kBK * 2;

@@ -26,6 +26,14 @@ struct GemmDesc {
   int n_store = 0;           // columns written per row (>= N; columns past N get 0, or 1 at ones_col)
   int split_k = 0;           // 0 = choose (only fp32 accumulate outputs may be split)
   int BN = 0;                // tile N override (0 = choose)
+  // Weight gate ("all-gather fused with the GEMM"): the B operand lives in an array whose chunks other GPUs
+  // write during the dense optimizer step.  When gate_flags is set the TMA producer first waits (bounded) until
+  // each of the gate_world flag words carries at least the epoch stored at *gate_epoch in its high 32 bits, then
+  // orders the asynchronous proxy behind those writes.  The operand itself is always read from local memory.
+  const unsigned long long* gate_flags = nullptr;
+  const unsigned long long* gate_epoch = nullptr;
+  int gate_world = 0;
+  unsigned long long gate_wait_ns = 0;
   int* status = nullptr;     // device error words
   unsigned long long* prof = nullptr;   // optional [16] timestamps of CTA (0,0,0) for pipeline diagnosis
   int dbg = 0;               // diagnosis only: bit0 skip epilogue math, bit1 skip global stores, bit2 skip TMEM loads
@@ -41,6 +49,10 @@ struct GemmParams {
   const __nv_bfloat16* had_xl;
   int ld_aux, ones_col, n_store;
   const float* bias;
+  const unsigned long long* gate_flags;
+  const unsigned long long* gate_epoch;
+  int gate_world;
+  unsigned long long gate_wait_ns;
   int* status;
   unsigned long long* prof;
   int dbg;

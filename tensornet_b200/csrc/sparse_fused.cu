@@ -60,6 +60,12 @@ __device__ __forceinline__ float new_row_elem(const SparseOptParams& o, unsigned
   return 0.f;  // slots, show, click; int fields are bit-zero
 }
 
+// A group's lanes ask L2 for the 128-byte lines of a row the group will touch in its next loop iteration,
+// so the HBM latency of iteration k+1 overlaps the arithmetic and stores of iteration k.
+__device__ __forceinline__ void prefetch_row_l2(const float* row, int n_floats, int lane, int G) {
+  for (int l = lane; l * 32 < n_floats; l += G) asm volatile("prefetch.global.L2 [%0];" ::"l"(row + 32 * l));
+}
+
 __device__ __forceinline__ void prof_mark(const SparseCommView& c, int slot) {
   if (c.prof != nullptr && blockIdx.x == 0 && threadIdx.x == 0) c.prof[slot] = globaltimer_ns();
 }
@@ -178,8 +184,9 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_pull_fused_kernel(const __
       int n2 = (n + 1) >> 1;
       for (int j = tid; j < n2; j += nth) dst[j] = __ldcg(&src[j]);
     }
-    if (!gs.sync(2, true)) goto done;
-    if (blockIdx.x == 0 && threadIdx.x < W && threadIdx.x != R) {
+    // no grid barrier: the CTA that finishes shipping last tells the owners their segments are complete, while
+    // the others already probe the local segment (which only needs phase A, and that is behind barrier 1)
+    if (last_cta_arrives(&c.bar[2], true) && threadIdx.x < W && threadIdx.x != R) {
       int p = threadIdx.x;
       int n = min(__ldcg(&c.cnt[p]), capo);
       st_release_sys_u64(sig_word(c.sig[p], kSigPullReq, R), (epoch << 32) | (unsigned long long)n);
@@ -310,6 +317,10 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_pull_fused_kernel(const __
       for (int j = gid; j < n_s; j += ngroups) {
         const int q = s * capo + j;
         int rr = __ldcg(&c.req_row[q]);
+        if (j + ngroups < n_s) {
+          const int r2 = __ldcg(&c.req_row[q + ngroups]);
+          if (r2 >= 0 && !(r2 & (kReqNewOwner | kReqNewCopy))) prefetch_row_l2(t.rows + (size_t)r2 * stride, ustride, gl, G);
+        }
         float* dst = dst_base + (size_t)j * ustride;
         if (rr == kReqPending) {
           int h = __ldcg(&c.req_ou[q]);
@@ -392,6 +403,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_pull_fused_kernel(const __
       }
     }
   }
+  if (c.prof != nullptr && threadIdx.x == 0) atomicMax(&c.prof[6], globaltimer_ns());   // slowest CTA's end of the row return
   prof_mark(c, 4);
 
   // ---- phase C: clear the dedup scratch; tell the requesters their rows have landed ---------------
@@ -401,9 +413,11 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_pull_fused_kernel(const __
     for (int i = tid; i < n2; i += nth) kk[i] = make_ulonglong2(kEmptyKey, kEmptyKey);
   }
   if (W > 1) {
-    if (!gs.sync(5, true)) goto done;
-    if (blockIdx.x == 0 && threadIdx.x < W && threadIdx.x != R) {
+    // the CTA that returns its rows last tells every requester that its matrix is complete; CTA 0 then keeps
+    // the kernel alive until the same word has arrived from every owner
+    if (last_cta_arrives(&c.bar[3], true) && threadIdx.x < W && threadIdx.x != R)
       st_release_sys_u64(sig_word(c.sig[threadIdx.x], kSigPullDone, R), epoch << 32);
+    if (blockIdx.x == 0 && threadIdx.x < W && threadIdx.x != R) {
       unsigned long long v;
       wait_flag_ge(sig_word(c.sig[R], kSigPullDone, threadIdx.x), epoch, &v, c.wait_ns, c.status, 6, threadIdx.x);
     }
@@ -525,11 +539,16 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_push_fused_kernel(const __
   const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
   const bool vec = (dim & 3) == 0;
 
+  prof_mark(c, 8);
   if (W == 1) {
     // single GPU: every unique sign of the batch maps to exactly one row; update in place
     const int n = __ldcg(&c.cnt_saved[0]);
     for (int j = gid; j < n; j += ngroups) {
       int rr = __ldcg(&c.req_row[j]);
+      if (j + ngroups < n) {
+        const int r2 = __ldcg(&c.req_row[j + ngroups]);
+        if (r2 != kReqNone && r2 != kReqPending) prefetch_row_l2(t.rows + (size_t)(r2 & kReqRowMask) * t.stride, t.stride, lane, G);
+      }
       float* g = c.gU + (size_t)j * gstride;
       float* cn = c.cnts + 2 * (size_t)j;
       if (rr != kReqNone && rr != kReqPending) {
@@ -545,32 +564,31 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_push_fused_kernel(const __
     goto done;
   }
 
-  // ---- phase A: ship gradient records (grad | show | click) to the owners, re-zero local rows ------
+  // ---- phase A: ship gradient records and the (show, click) pairs to the owners, re-zero the local copies ----
+  // Two plain streaming loops: every warp moves whole 512-byte runs.  (Patching the counters into the records
+  // on the fly made one lane in gstride/4 leave the stream for an 8-byte side access and cost 3x the time.)
   for (int p = 0; p < W; ++p) {
     const int n = __ldcg(&c.cnt_saved[p]);
     float* src = c.gU + (size_t)p * capo * gstride;
     float* dst = c.ginbox[p] + (size_t)R * capo * gstride;
     const int total = n * gch;
     for (int i = tid; i < total; i += nth) {
-      float4 v = *reinterpret_cast<const float4*>(src + 4 * (size_t)i);
-      const int j = i / gch, e0 = 4 * (i - j * gch);
-      if (e0 + 3 >= dim && e0 <= dim + 1) {          // the record's show / click slots come from the compact counters
-        float* cn = c.cnts + 2 * ((size_t)p * capo + j);
-        float e[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          if (e0 + k == dim) { e[k] = cn[0]; cn[0] = 0.f; }
-          if (e0 + k == dim + 1) { e[k] = cn[1]; cn[1] = 0.f; }
-        }
-        v = make_float4(e[0], e[1], e[2], e[3]);
-      }
-      *reinterpret_cast<float4*>(dst + 4 * (size_t)i) = v;
+      *reinterpret_cast<float4*>(dst + 4 * (size_t)i) = *reinterpret_cast<const float4*>(src + 4 * (size_t)i);
       *reinterpret_cast<float4*>(src + 4 * (size_t)i) = zero4;
     }
+    float2* csrc = reinterpret_cast<float2*>(c.cnts) + (size_t)p * capo;
+    float2* cdst = reinterpret_cast<float2*>(c.cinbox[p]) + (size_t)R * capo;
+    for (int j = tid; j < n; j += nth) {
+      cdst[j] = csrc[j];
+      csrc[j] = make_float2(0.f, 0.f);
+    }
+    if (p == 0) prof_mark(c, 14);
   }
+  prof_mark(c, 9);
   if (!gs.sync(11, true)) goto done;
   if (blockIdx.x == 0 && threadIdx.x < W && threadIdx.x != R)
     st_release_sys_u64(sig_word(c.sig[threadIdx.x], kSigPushReq, R), epoch << 32);
+  prof_mark(c, 10);
 
   // ---- phase B: as owner, sum records of equal sign coming from different GPUs --------------------
   for (int si = 0; si < W; ++si) {
@@ -593,15 +611,30 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_push_fused_kernel(const __
       float4 v = ldcg_f4(src + 4 * (size_t)i);
       red_add_f32x4(c.acc + (size_t)ou * gstride + 4 * ch, v);
     }
+    const float2* csrc = reinterpret_cast<const float2*>(c.cinbox[R]) + (size_t)s * capo;
+    for (int j = tid; j < n_s; j += nth) {
+      const int ou = __ldcg(&c.req_ou[s * capo + j]);
+      if (ou < 0) continue;
+      const float2 sc = __ldcg(&csrc[j]);
+      float* g = c.acc + (size_t)ou * gstride + dim;          // the record's show / click slots
+      atomicAdd(g, sc.x);
+      if (sc.y != 0.f) atomicAdd(g + 1, sc.y);
+    }
   }
   if (gs.failed) goto done;
+  prof_mark(c, 11);
   if (!gs.sync(13, false)) goto done;
+  prof_mark(c, 12);
 
   // ---- phase C: one optimizer update per touched row ----------------------------------------------
   {
     const int n_ou = __ldcg(c.ocount);
     for (int ou = gid; ou < n_ou; ou += ngroups) {
       const int r = __ldcg(&c.ou_row[ou]);
+      if (ou + ngroups < n_ou) {
+        const int r2 = __ldcg(&c.ou_row[ou + ngroups]);
+        if (r2 >= 0) prefetch_row_l2(t.rows + (size_t)r2 * t.stride, t.stride, lane, G);
+      }
       float* g = c.acc + (size_t)ou * gstride;
       if (r >= 0) {
         float* row = t.rows + (size_t)r * t.stride;
@@ -613,6 +646,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_push_fused_kernel(const __
       for (int ch = lane; ch < gch; ch += G) *reinterpret_cast<float4*>(g + 4 * ch) = zero4;
     }
   }
+  prof_mark(c, 13);
 
 done:
   gs.leave();

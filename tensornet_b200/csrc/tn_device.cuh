@@ -67,8 +67,8 @@ __device__ __forceinline__ void red_add_f32x4(float* p, float4 v) {
 
 // ---------------------------------------------------------------------------------------
 // Grid barrier for persistent kernels launched cooperatively (all CTAs co-resident).
-// `bar[0]` counts arrivals (monotonic within a launch), `bar[1]` counts exiting CTAs; the
-// last CTA to leave the kernel zeroes both so the next launch starts clean.
+// `bar[0]` counts arrivals (monotonic within a launch), `bar[1]` counts exiting CTAs, `bar[2..3]` serve
+// `last_cta_arrives`; the last CTA to leave the kernel zeroes all four so the next launch starts clean.
 // ---------------------------------------------------------------------------------------
 struct GridSync {
   unsigned* bar;
@@ -86,9 +86,11 @@ struct GridSync {
   // `sys_fence`: make this CTA's peer-memory stores visible system-wide first.
   __device__ __forceinline__ bool sync(int phase, bool sys_fence) {
     __shared__ int s_ok;
-    if (sys_fence) __threadfence_system(); else __threadfence();
+    // The CTA barrier orders every thread's earlier writes before thread 0's fence, and fences are
+    // cumulative, so one fence per CTA publishes them all (the pattern of a cooperative grid sync).
     __syncthreads();
     if (threadIdx.x == 0) {
+      if (sys_fence) __threadfence_system(); else __threadfence();
       gen += 1;
       unsigned target = gen * nblocks;
       atomicAdd(&bar[0], 1u);
@@ -122,11 +124,32 @@ struct GridSync {
       if (prev == nblocks - 1) {
         bar[0] = 0;
         bar[1] = 0;
+        bar[2] = 0;
+        bar[3] = 0;
         __threadfence();
       }
     }
   }
 };
+
+// "Last CTA out": true in exactly one CTA per launch for a given counter, namely the last whose threads all
+// reached this point.  Everything the other CTAs wrote before arriving (peer memory included when `sys_fence`)
+// is ordered before what the elected CTA does next, so it may publish a completion flag without a grid barrier.
+__device__ __forceinline__ bool last_cta_arrives(unsigned* ctr, bool sys_fence) {
+  __shared__ int s_last;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (sys_fence) __threadfence_system(); else __threadfence();
+    const unsigned prev = atomicAdd(ctr, 1u);
+    const int last = prev == gridDim.x - 1;
+    if (last) { if (sys_fence) __threadfence_system(); else __threadfence(); }
+    s_last = last;
+  }
+  __syncthreads();
+  const bool r = s_last != 0;
+  __syncthreads();
+  return r;
+}
 
 // One thread waits until *flag (a 64-bit word another GPU release-stores) reaches `want`.
 // Returns the observed word, or sets status and returns ~0 on expiry.

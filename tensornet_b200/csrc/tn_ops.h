@@ -63,6 +63,19 @@ void launch_unique_assign(const long long* ids, int n, const float* labels, unsi
                           unsigned scratch_cap, unsigned long long* uniq, int cap, int* inverse, float* show, float* click,
                           int* count, int* status, cudaStream_t st);
 
+// bn.cu
+void launch_bn_batch_stats(const float* x, int ld, int B, int C, const float* center, double* batch, cudaStream_t st);
+void launch_bn_table_append(const BnTableView& t, double* batch, cudaStream_t st);
+void launch_bn_table_refresh(const BnTableView& t, cudaStream_t st);
+void launch_bn_table_sync(const BnTableView& t, const BnSyncView& s, double* scratch, cudaStream_t st);
+void launch_bn_apply_fwd(const float* x, int ldx, int B, int C, const float* mean, const float* var, const float* gamma,
+                         const float* beta, float eps, float* y, int ldy, cudaStream_t st);
+void launch_bn_apply_bwd(const float* dy, int ldd, const float* x, int ldx, int B, int C, const float* mean, const float* var,
+                         const float* gamma, float eps, float* dx, int ldo, float* gg, float* gb, cudaStream_t st);
+
+// peer_probe.cu
+void launch_peer_copy(void* dst, const void* src, long long nbytes, int mode, int blocks, int threads, int fence, cudaStream_t st);
+
 // serving.cu
 void launch_dict_lookup_pool(const TableView& t, const long long* ids, const int* offsets, int B, int S, int combiner, void* out,
                              int ld_out, int ones_col, cudaStream_t st);

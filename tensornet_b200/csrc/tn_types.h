@@ -39,6 +39,7 @@ struct SparseCommView {
   int ustride;   // floats per pulled row: round_up4(dim + 2 * use_cvm)
   unsigned long long* inbox_ids[kMaxWorld];  // [sender][capo]            written by senders
   float* ginbox[kMaxWorld];                  // [sender][capo][gstride]   written by senders
+  float* cinbox[kMaxWorld];                  // [sender][capo][2]         (show, click) of each record, written by senders
   float* U[kMaxWorld];                       // [owner][capo][ustride]    written by owners
   unsigned long long* sig[kMaxWorld];        // [3][kMaxWorld] flag words (epoch << 32 | payload)
   unsigned long long* stage_ids;             // [owner][capo] outgoing signs, grouped by owner
@@ -59,7 +60,7 @@ struct SparseCommView {
   unsigned* bar;                             // [2] grid barrier words (zero between launches)
   int* status;                               // [4] error words
   unsigned long long wait_ns;                // budget of every wait inside the kernels
-  unsigned long long* prof;                  // optional [8] phase timestamps (globaltimer ns) written by CTA 0
+  unsigned long long* prof;                  // optional [16] phase timestamps: pull 0..5, push 8..13 (globaltimer ns) written by CTA 0
 };
 
 struct PullArgs {
@@ -96,6 +97,9 @@ struct DenseStepArgs {
   long long chunk;      // elements owned per GPU (multiple of 4); n for world == 1
   int world, rank;
   float grad_scale;     // 1/world for the mean gradient
+  int gated;            // world > 1: publish per-owner "chunk written" flags (row 2 of sig) instead of waiting in a closing barrier;
+                        // the first kernel that reads the weights waits on them (GemmDesc::gate_flags)
+  int zero_local;       // world > 1: each GPU clears its own gradient replica after the closing barrier
   float* W[kMaxWorld];  // fp32 master replica of every GPU
   float* G[kMaxWorld];  // fp32 gradient of every GPU
   void* Wb[kMaxWorld];  // bf16 shadow of every GPU (may be null)
@@ -105,9 +109,33 @@ struct DenseStepArgs {
   float* s0;            // optimizer state of the owned chunk: Adam m | AdaGrad d2sum
   float* s1;            //                                      Adam v | AdaGrad g2sum
   float* s2;            //                                               AdaGrad m
-  unsigned long long* sig[kMaxWorld];   // [2][kMaxWorld] flag words per GPU
+  unsigned long long* sig[kMaxWorld];   // [3][kMaxWorld] flag words per GPU: gradients ready, weights written (barrier), weights written (gate)
   unsigned long long* epoch;
   unsigned* bar;
+  int* status;
+  unsigned long long wait_ns;
+};
+
+// Device-resident batch-norm statistics table (all arrays have C entries unless noted).
+struct BnTableView {
+  int C;
+  int pctr;                 // 1: squared sums are deviations from the current mean and `var` reports them raw
+  double moment;            // moving-window momentum
+  long long max_count;      // records after which the window starts sliding (0 = never)
+  double* total_sum;
+  double* total_sum_err;    // Kahan compensation terms
+  double* total_sq;
+  double* total_sq_err;
+  double* total_count;
+  double* inc;              // [3][C] pending increments (sum, squared sum, count) for the cross-GPU exchange
+  float* mean;              // moments the layer normalises with
+  float* var;
+};
+struct BnSyncView {
+  int world, rank;
+  const double* inc[kMaxWorld];          // every GPU's pending increments
+  unsigned long long* sig[kMaxWorld];    // [2][kMaxWorld] flag words per GPU
+  unsigned long long* epoch;
   int* status;
   unsigned long long wait_ns;
 };

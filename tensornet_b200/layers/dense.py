@@ -35,13 +35,16 @@ class MLP(nn.Module):
         self.relu_last = relu_last
         dims = [self.in_dim] + self.hidden_units
         self.weights = nn.ParameterList([nn.Parameter(_glorot_aug(dims[i + 1], dims[i])) for i in range(len(self.hidden_units))])
+        # set by Model.compile on multi-GPU runs when this tower is the first reader of the dense weights in a step:
+        # its first GEMM then waits for the optimizer's all-gather instead of the optimizer kernel waiting for everyone
+        self.weight_gate = None
 
     @property
     def out_dim(self) -> int:
         return self.hidden_units[-1]
 
     def forward(self, x: torch.Tensor, grad_premasked: bool = False) -> torch.Tensor:
-        return F.mlp(x, list(self.weights), self.in_dim, self.relu_last, grad_premasked)
+        return F.mlp(x, list(self.weights), self.in_dim, self.relu_last, grad_premasked, gate=self.weight_gate)
 
     def weight(self, i: int) -> torch.Tensor:
         dims = [self.in_dim] + self.hidden_units

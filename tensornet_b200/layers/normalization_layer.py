@@ -15,6 +15,30 @@ from torch import nn
 from .. import core
 
 
+class _BnApply(torch.autograd.Function):
+    """y = (x - mean) * rsqrt(var + eps) * gamma + beta with the table's moments as constants, as the reference's
+    layer does (tensornet/layers/normalization_layer.py:149-156): no gradient flows into the statistics."""
+
+    @staticmethod
+    def forward(ctx, x, gamma, beta, table, eps):
+        y = torch.empty_like(x)
+        mean, var = table.mean.clone(), table.var.clone()      # the table moves on before the backward pass runs
+        table.ctx.apply_fwd(x, mean, var, gamma, beta, float(eps), y)
+        ctx.save_for_backward(x, gamma, mean, var)
+        ctx.table, ctx.eps, ctx.has_beta = table, float(eps), beta is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, gamma, mean, var = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = torch.empty_like(x) if ctx.needs_input_grad[0] else None
+        gg = torch.zeros_like(gamma) if gamma is not None else None
+        gb = torch.zeros(x.shape[1], dtype=torch.float32, device=x.device) if ctx.has_beta else None
+        ctx.table.ctx.apply_bwd(dy, x, mean, var, gamma, ctx.eps, dx, gg, gb)
+        return dx, gg, gb, None, None
+
+
 class TNBatchNormalizationBase(nn.Module):
     _USE_PCTR_DNN_BN = False
 
@@ -43,6 +67,10 @@ class TNBatchNormalizationBase(nn.Module):
                                                     self._USE_PCTR_DNN_BN)
         self.table = core.bn_table(self.bn_table_handle)
         self.table.handle = self.bn_table_handle
+        self._on_device = hasattr(self.table, "push_batch")
+        if self._on_device:
+            self.moving_mean = self.table.mean
+            self.moving_variance = self.table.var
 
     # ---- table plumbing --------------------------------------------------------------------
     def _local_stats(self, x: torch.Tensor, center=None):
@@ -69,9 +97,31 @@ class TNBatchNormalizationBase(nn.Module):
             self.bn_statistics_push(stats, False)
 
     def update_moments(self):
+        if self._on_device:
+            return          # moving_mean / moving_variance alias the table's device arrays
         mean, var = self.table.get_moments()
         self.moving_mean.copy_(torch.from_numpy(mean))
         self.moving_variance.copy_(torch.from_numpy(var))
+
+    # ---- device path: statistics, table update and normalisation without leaving the GPU ------
+    def _device_push(self, x2: torch.Tensor, centered: bool):
+        self.table.push_batch(x2, centered)
+        if self.synchronized:
+            self.batch_counter += 1
+            if self.batch_counter == self.sync_freq:
+                self.table.sync_increments()
+                self.batch_counter = 0
+
+    def _device_forward(self, inputs: torch.Tensor, training: bool, centered: bool):
+        x2 = inputs.reshape(-1, inputs.shape[-1])
+        if x2.dtype != torch.float32 or x2.stride(-1) != 1:
+            x2 = x2.float().contiguous()
+        if training and not centered:
+            self._device_push(x2.detach(), False)
+        y = _BnApply.apply(x2, self.gamma, self.beta, self.table, self.epsilon)
+        if training and centered:
+            self._device_push(x2.detach(), True)
+        return y.view(*inputs.shape[:-1], inputs.shape[-1])
 
     def bn_statistics_pull(self):
         """Fold the other ranks' pending increments in (called by rank 0 before saving)."""
@@ -92,6 +142,8 @@ class TNBatchNormalizationBase(nn.Module):
         if self.bn_table_handle is None:
             self._build(inputs.shape[-1])
         training = self.training if training is None else training
+        if self._on_device:
+            return self._device_forward(inputs, training, False)
         if training:
             self._push_counted(self._local_stats(inputs))
             self.update_moments()
@@ -117,6 +169,8 @@ class PCTRDNNBatchNormalization(TNBatchNormalizationBase):
         if self.bn_table_handle is None:
             self._build(inputs.shape[-1])
         training = self.training if training is None else training
+        if self._on_device:
+            return self._device_forward(inputs, training, True)
         self.update_moments()
         if training:
             self._push_counted(self._local_stats(inputs, center=self.moving_mean))

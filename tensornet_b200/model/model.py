@@ -165,6 +165,12 @@ class Model(nn.Module):
         self._graph_warmup = graph_warmup
         if optimizer is not None:
             optimizer.attach(self.named_parameters())
+            # A model whose first reader of dense weights is an MLP tower names it in ``first_dense_tower``; on
+            # several GPUs that tower's first GEMM then waits for the optimizer's weight all-gather and the dense
+            # kernel ends without a barrier of its own.
+            tower = getattr(self, "first_dense_tower", None)
+            if tower is not None and rt.on_gpu and rt.world > 1 and core.config.gate_first_gemm:
+                tower().weight_gate = optimizer.table.enable_gate()
         return self
 
     def sparse_layers(self):

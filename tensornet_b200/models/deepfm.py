@@ -69,6 +69,10 @@ class DeepFM(Model):
         n_lin = len(linear_features) * (self.linear_emb.out_dim if self.linear_emb else 0)
         self.sub_model = DeepFMSubModel(n_lin, len(dnn_features), self.deep_emb.out_dim, dense_dim, dnn_hidden_units)
 
+    def first_dense_tower(self):
+        """The embedding pooling, FM term and input assembly read no dense parameter: the MLP is the first reader."""
+        return self.sub_model.mlp
+
     def fused_train_loss(self, features, labels, sums):
         """Training loss through the fused DeepFM kernels (gather + FM + operand build in one kernel; head, loss and
         head backward in one kernel).  Returns None when the inputs do not qualify (ragged slots, CVM columns,

@@ -56,7 +56,7 @@ class DenseTable:
         self.world, self.rank = W, rt.rank
         if rt.on_gpu:
             self.arena = SymmArena([("W", (self.n,), torch.float32), ("G", (self.n,), torch.float32),
-                                    ("Wb", (self.n,), torch.bfloat16), ("sig", (2 * 8,), torch.int64)])
+                                    ("Wb", (self.n,), torch.bfloat16), ("sig", (4 * 8,), torch.int64)])
             self.W, self.G, self.Wb = self.arena.tensor("W"), self.arena.tensor("G"), self.arena.tensor("Wb")
         else:
             self.W = torch.zeros(self.n)
@@ -102,6 +102,18 @@ class DenseTable:
         rt.barrier()
 
     # ------------------------------------------------------------------
+    def enable_gate(self):
+        """Drop the closing cross-GPU barrier of the dense step: every owner instead publishes a "my chunk is
+        written" flag on every GPU, and the returned gate ``(flags, epoch, world, wait_ns)`` makes the first GEMM
+        that reads the weights wait for those flags (``ops.functional.mlp(..., gate=...)``).  Only valid when that
+        GEMM really is the first reader of any dense parameter in a step.  Returns None with one GPU."""
+        rt = runtime()
+        if not (rt.on_gpu and self.world > 1 and self.initialized):
+            return None
+        self.ctx.set_gated(True)
+        flags = self.arena.tensor("sig")[2 * 8: 2 * 8 + self.world]
+        return (flags, self._ctx_args["epoch"], self.world, int(rt.wait_ns))
+
     def set_lr(self, lr: float):
         if lr != self.lr:
             self.lr = float(lr)

@@ -114,8 +114,10 @@ def concat_cast(pieces: Sequence[torch.Tensor], ones: bool = True, widths: Optio
 # =========================================================================================
 class _MLP(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, dims, relu_last, premasked, *weights):
+    def forward(ctx, x, dims, relu_last, premasked, gate, *weights):
         # x: bf16 [B, Kp0] (ones column at dims[0]);  weights[l]: fp32 [N_l, pad8(K_l + 1)]
+        # gate: None or (flags, epoch, world, wait_ns): the first GEMM waits until every owner's chunk of the
+        # dense weight array has landed on this GPU (the dense step then ends without a closing barrier)
         ext, st = _ext(), _status()
         B = x.shape[0]
         acts = [x]
@@ -127,8 +129,12 @@ class _MLP(torch.autograd.Function):
             Np = pad8(N + 1)
             y = torch.empty((B, Np), dtype=torch.bfloat16, device=x.device)
             relu = relu_last or l < L - 1
-            ext.gemm(h, _bf16_of(w), y, B, N, K + 1, int(h.stride(0)), Kp, Np, False, False, False, relu, None, None, None,
-                     None, 0, N, Np, 1, 0, st)
+            if l == 0 and gate is not None:
+                ext.gemm(h, _bf16_of(w), y, B, N, K + 1, int(h.stride(0)), Kp, Np, False, False, False, relu, None, None, None,
+                         None, 0, N, Np, 1, 0, st, gate_flags=gate[0], gate_epoch=gate[1], gate_world=gate[2], gate_wait_ns=gate[3])
+            else:
+                ext.gemm(h, _bf16_of(w), y, B, N, K + 1, int(h.stride(0)), Kp, Np, False, False, False, relu, None, None, None,
+                         None, 0, N, Np, 1, 0, st)
             acts.append(y)
             h = y
         ctx.save_for_backward(*acts)
@@ -182,18 +188,18 @@ class _MLP(torch.autograd.Function):
                 gx = gh
         main.wait_stream(side)
         del keep
-        return (gx if ctx.needs_input_grad[0] else None, None, None, None, *([None] * L))
+        return (gx if ctx.needs_input_grad[0] else None, None, None, None, None, *([None] * L))
 
 
 def mlp(x: torch.Tensor, weights: Sequence[torch.Tensor], in_dim: int, relu_last: bool = True,
-        grad_premasked: bool = False) -> torch.Tensor:
+        grad_premasked: bool = False, gate=None) -> torch.Tensor:
     """Run ``x`` (bf16, ones column at ``in_dim``) through the layers ``weights``.
     Returns bf16 ``[B, pad8(N_last + 1)]`` whose column ``N_last`` is again the constant 1.
     ``grad_premasked``: the consumer hands back a gradient that is already zero where the last ReLU was
     inactive (the fused DeepFM head does), so the backward skips its own masking pass."""
     dims = [in_dim] + [int(w.shape[0]) for w in weights[:-1]]
     if x.is_cuda:
-        return _MLP.apply(x, dims, relu_last, grad_premasked, *weights)
+        return _MLP.apply(x, dims, relu_last, grad_premasked, gate, *weights)
     h = x.float()
     L = len(weights)
     for l, w in enumerate(weights):

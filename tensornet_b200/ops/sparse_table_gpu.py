@@ -170,6 +170,7 @@ class GpuSparseLink:
         arena = SymmArena([
             ("inbox_ids", (n_seg if multi else 4,), torch.int64),
             ("ginbox", (n_seg * self.gstride if multi else 4,), torch.float32),
+            ("cinbox", (n_seg * 2 if multi else 4,), torch.float32),
             ("U", (n_seg * self.ustride,), torch.float32),
             ("sig", (3 * 8,), torch.int64),
         ])
@@ -190,7 +191,7 @@ class GpuSparseLink:
             dd_keys=torch.full((dd_cap,), -1, dtype=torch.int64, device=d),
             dd_vals=torch.zeros(dd_cap, dtype=torch.int32, device=d),
             bar=torch.zeros(4, dtype=torch.int32, device=d),
-            prof=torch.zeros(8, dtype=torch.int64, device=d),
+            prof=torch.zeros(16, dtype=torch.int64, device=d),
         )
         self.arena = arena
         self.U = arena.tensor("U").view(n_seg, self.ustride)
@@ -199,7 +200,7 @@ class GpuSparseLink:
         self.cnt_saved = loc["cnt_saved"]
         self.prof = loc["prof"]
         self.comm = dict(world=W, rank=table.rank, capo=capo, gstride=self.gstride, ustride=self.ustride,
-                         inbox_ids=arena.ptrs("inbox_ids"), ginbox=arena.ptrs("ginbox"), U=arena.ptrs("U"),
+                         inbox_ids=arena.ptrs("inbox_ids"), ginbox=arena.ptrs("ginbox"), cinbox=arena.ptrs("cinbox"), U=arena.ptrs("U"),
                          sig=arena.ptrs("sig"), epoch=table.epoch, status=rt.status, wait_ns=rt.wait_ns, **loc)
         self.ctx = table.ext.SparseCtx(table.table_dict(), self.comm, table._opt_dict())
         self._last_n_ids = 0
@@ -226,6 +227,13 @@ class GpuSparseLink:
         dedup, inverse+dispatch, owner probe/insert, row return, scratch clear + completion."""
         t = self.prof.tolist()
         return [(t[i + 1] - t[i]) / 1e3 for i in range(5)]
+
+    def push_phase_us(self):
+        """Durations (microseconds) of the last multi-GPU push's phases as seen by CTA 0: record shipping,
+        grid barrier + signal, owner-side accumulation (includes the wait for the peers' records),
+        grid barrier, optimizer update."""
+        t = self.prof.tolist()
+        return [(t[i + 1] - t[i]) / 1e3 for i in range(8, 13)]
 
     def unique_counts(self):
         """Per-owner unique-sign counts of the last pull (host sync)."""

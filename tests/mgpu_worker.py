@@ -41,6 +41,19 @@ def main():
             losses.append(float(t) / rt.world)
     torch.cuda.synchronize()
     rt.check_status()
+    # synchronised batch norm: every rank ends with the statistics of all ranks' batches
+    bn = tn.layers.TNBatchNormalization(11, name="bn_sync", synchronized=True, sync_freq=2)
+    bn.train()
+    gb = torch.Generator().manual_seed(7)
+    allx = [torch.randn(rt.world * 64, 11, generator=gb) * (k + 1) + k for k in range(4)]
+    for xk in allx:
+        bn(xk[rt.rank * 64:(rt.rank + 1) * 64].to(rt.device))
+    torch.cuda.synchronize()
+    rt.check_status()
+    cat = torch.cat(allx).double()
+    bn_ok = bool(torch.allclose(bn.moving_mean.cpu().double(), cat.mean(0), atol=1e-5)
+                 and torch.allclose(bn.moving_variance.cpu().double(), cat.var(0, unbiased=False), rtol=1e-3, atol=1e-3))
+    bn_oks = rt.all_gather_object(bn_ok)
     rows = [int(m.table.n_rows) for m in (model.linear_emb, model.deep_emb)]
     allrows = rt.all_gather_object(rows)
     w = model.sub_model.head.weight.detach().float().cpu()
@@ -48,7 +61,7 @@ def main():
     if rt.rank == 0:
         same = all(torch.equal(ws[0], x) for x in ws)
         json.dump({"world": rt.world, "losses": losses, "rows": [sum(r[i] for r in allrows) for i in range(2)],
-                   "replicas_identical": same, "graph": model._graph is not None,
+                   "replicas_identical": same, "bn_sync_ok": all(bn_oks), "graph": model._graph is not None,
                    "multimem": bool(getattr(model.optimizer.table, "uses_multimem", False))}, open(out, "w"))
     tn.core.shutdown()
 

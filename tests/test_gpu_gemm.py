@@ -90,3 +90,33 @@ def test_hadamard_epilogue(tn_gpu, status_ok):
                 tn_gpu.core.runtime().status)
     ref = x0.float() * (A.float() @ B.float().t() + bias) + xl.float()
     assert _rel_err(C, ref) < 2e-2
+
+
+def test_weight_gate_passes_and_times_out(tn_gpu):
+    """The gated GEMM waits for per-owner "chunk written" flags before loading its weights: with the flags at the
+    expected epoch it computes as usual; with a flag nothing sets, its bounded wait runs out, the kernel gives up
+    cleanly, the status words name the missing owner and the context stays usable."""
+    M, N, K = 256, 64, 128
+    g = torch.Generator().manual_seed(5)
+    A, W = torch.randn(M, K, generator=g).bfloat16(), (torch.randn(N, K, generator=g) * 0.1).bfloat16()
+    dev = tn_gpu.core.runtime().device
+    C = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+    epoch = torch.tensor([3], dtype=torch.int64, device=dev)
+    flags = torch.tensor([3 << 32, 4 << 32, 0, 0], dtype=torch.int64, device=dev)
+    rt = tn_gpu.core.runtime()
+    _ext().gemm(A.to(dev), W.to(dev), C, M, N, K, K, K, N, False, False, False, False, None, None, None, None, 0, -1, N, 1, 0,
+                tn_gpu.core.runtime().status, gate_flags=flags, gate_epoch=epoch, gate_world=2, gate_wait_ns=10_000_000)
+    torch.cuda.synchronize()
+    rt.check_status()
+    ref = A.float() @ W.float().t()
+    assert (C.float().cpu() - ref).abs().max() < 2e-2 * ref.abs().max()
+    # owner 2's flag never reaches epoch 3
+    C2 = torch.zeros_like(C)
+    _ext().gemm(A.to(dev), W.to(dev), C2, M, N, K, K, K, N, False, False, False, False, None, None, None, None, 0, -1, N, 1, 0,
+                tn_gpu.core.runtime().status, gate_flags=flags, gate_epoch=epoch, gate_world=3, gate_wait_ns=2_000_000)
+    torch.cuda.synchronize()
+    with pytest.raises(tn_gpu.core.DeviceError) as e:
+        rt.check_status()
+    assert e.value.code == 5 and e.value.phase == 70 and e.value.aux == 2
+    assert float(torch.ones(4, device=dev).sum()) == 4.0
+    rt.check_status()      # the words were cleared by the raise

@@ -34,7 +34,7 @@ def test_multi_gpu_follows_single_gpu(tmp_path, world):
         pytest.skip(f"needs {world} GPUs")
     one = _run(1, str(tmp_path / "one.json"))
     many = _run(world, str(tmp_path / "many.json"))
-    assert many["graph"] and many["replicas_identical"]
+    assert many["graph"] and many["replicas_identical"] and many["bn_sync_ok"]
     assert many["rows"] == one["rows"]                      # every sign lives on exactly one shard
     assert many["losses"][-1] < 0.8 * many["losses"][0]
     for a, b in zip(one["losses"], many["losses"]):
@@ -47,5 +47,5 @@ def test_multi_gpu_over_plain_peer_loads(tmp_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     r = _run(2, str(tmp_path / "ipc.json"), {"TN_SYMM_BACKEND": "ipc", "NCCL_NVLS_ENABLE": "0"})
-    assert r["replicas_identical"] and not r["multimem"]
+    assert r["replicas_identical"] and not r["multimem"] and r["bn_sync_ok"]
     assert r["losses"][-1] < 0.8 * r["losses"][0]
