@@ -34,6 +34,13 @@ class Config:
     #: use NVSwitch multicast (multimem) in the dense path when the mapping exists
     use_multimem: bool = True
     gate_first_gemm: bool = True   # multi-GPU: first MLP GEMM waits for the dense all-gather (no closing barrier)
+    #: multi-GPU: run the dense step beside the sparse push (small dense arrays only); measured at 2 GPUs on the
+    #: DeepFM step: 2 % slower than back to back (both kernels are latency-bound and lose CTAs), so off by default
+    overlap_dense_push: bool = False
+    #: multi-GPU: cap on the dense kernel's grid for small arrays (cheaper grid barriers); 0 = fill the GPU
+    dense_small_grid: int = 0
+    #: rows per streamed piece when a GPU shard is saved (bounds the pinned host staging buffer)
+    checkpoint_chunk_rows: int = 1 << 22
     #: capture the train step in a CUDA graph
     cuda_graph: bool = True
     #: force the CPU oracle path even when a GPU is visible
@@ -49,6 +56,9 @@ class Config:
         c.seed = _env("TN_SEED", c.seed, int)
         c.use_multimem = _env("TN_USE_MULTIMEM", c.use_multimem, bool)
         c.gate_first_gemm = _env("TN_GATE_FIRST_GEMM", c.gate_first_gemm, bool)
+        c.dense_small_grid = _env("TN_DENSE_SMALL_GRID", c.dense_small_grid, int)
+        c.overlap_dense_push = _env("TN_OVERLAP_DENSE_PUSH", c.overlap_dense_push, bool)
+        c.checkpoint_chunk_rows = _env("TN_CKPT_CHUNK_ROWS", c.checkpoint_chunk_rows, int)
         c.cuda_graph = _env("TN_CUDA_GRAPH", c.cuda_graph, bool)
         c.force_cpu = _env("TN_FORCE_CPU", c.force_cpu, bool)
         return c

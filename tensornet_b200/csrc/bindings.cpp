@@ -150,12 +150,12 @@ struct SparseCtx {
     check(tn::launch_sparse_pull(a, (int)work, cur_stream()), "sparse_pull_fused launch");
   }
 
-  void push(int64_t work_hint) {
+  void push(int64_t work_hint, int max_ctas) {
     tn::PushArgs a{};
     a.c = c; a.tbl = t; a.opt = o; a.lanes = push_lanes;
     long long work = work_hint * push_lanes;
     if (work > (1ll << 30)) work = 1ll << 30;
-    check(tn::launch_sparse_push(a, (int)work, cur_stream()), "sparse_push_fused launch");
+    check(tn::launch_sparse_push(a, (int)work, max_ctas, cur_stream()), "sparse_push_fused launch");
   }
 };
 
@@ -202,6 +202,7 @@ struct DenseCtx {
   }
   void step() { check(tn::launch_dense_step(a, cur_stream()), "dense step launch"); }
   void set_gated(bool g) { a.gated = g ? 1 : 0; }
+  void set_max_ctas(int n) { a.max_ctas = n; }
 };
 
 // Device-resident batch-norm table and the per-step kernels of the layer.
@@ -311,7 +312,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("set_opt", &SparseCtx::set_opt)
       .def("set_table", &SparseCtx::set_table)
       .def("pull", &SparseCtx::pull)
-      .def("push", &SparseCtx::push);
+      .def("push", &SparseCtx::push, py::arg("work_hint"), py::arg("max_ctas") = 0);
   py::class_<BnCtx>(m, "BnCtx")
       .def(py::init<py::dict>())
       .def("push", &BnCtx::push)
@@ -320,7 +321,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("sync", &BnCtx::sync)
       .def("apply_fwd", &BnCtx::apply_fwd)
       .def("apply_bwd", &BnCtx::apply_bwd);
-  py::class_<DenseCtx>(m, "DenseCtx").def(py::init<py::dict>()).def("step", &DenseCtx::step).def("set_gated", &DenseCtx::set_gated);
+  py::class_<DenseCtx>(m, "DenseCtx").def(py::init<py::dict>()).def("step", &DenseCtx::step).def("set_gated", &DenseCtx::set_gated).def("set_max_ctas", &DenseCtx::set_max_ctas);
   m.def("gemm", &gemm, py::arg("A"), py::arg("B"), py::arg("C"), py::arg("M"), py::arg("N"), py::arg("K"), py::arg("lda"),
         py::arg("ldb"), py::arg("ldc"), py::arg("a_mn"), py::arg("b_mn"), py::arg("accumulate"), py::arg("relu"), py::arg("bias"),
         py::arg("mask_aux"), py::arg("had_x0"), py::arg("had_xl"), py::arg("ld_aux"), py::arg("ones_col"), py::arg("n_store"),
@@ -395,6 +396,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("table_decay", [](py::dict table, int kind, float rate, int delta_days) {
     tn::launch_table_decay(table_from_dict(table), kind, rate, delta_days, cur_stream());
   });
+  m.def("table_export", [](py::dict table, int kind, bool evict, float show_threshold, int no_show_days, int logic, int r0, int r1,
+                           at::Tensor counts, at::Tensor cursors, at::Tensor out_keys, at::Tensor out_rows) {
+    TORCH_CHECK(counts.numel() >= 8 && cursors.numel() >= 8 && out_rows.dim() == 2 && out_rows.is_contiguous(), "table_export buffers");
+    TORCH_CHECK(out_keys.numel() >= r1 - r0 && out_rows.size(0) >= r1 - r0, "table_export: staging buffers smaller than the row range");
+    tn::ExportRule rule{evict ? 1 : 0, show_threshold, no_show_days, logic};
+    c10::cuda::CUDAGuard guard(out_rows.device());
+    tn::launch_table_export(table_from_dict(table), kind, rule, r0, r1, ptr_of<int>(counts), ptr_of<int>(cursors),
+                            ptr_of<unsigned long long>(out_keys), ptr_of<float>(out_rows), (int)out_rows.size(1), cur_stream());
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+  }, "filter rows [r0, r1) by the save-time eviction rule and pack them grouped by block file");
   m.def("fm_fwd", [](at::Tensor E, int ld, int B, int F, int D, at::Tensor out) {
     c10::cuda::CUDAGuard guard(E.device());
     tn::launch_fm_fwd(ptr_of<float>(E), ld, B, F, D, ptr_of<float>(out), cur_stream());

@@ -357,10 +357,7 @@ struct EvictRule {   // DeleteByShow, applied only while saving
 };
 
 // rows are in table layout ([w|g2sum|show|click|no_show_days] or [w|s1|s2|show|delta_show])
-void serialize_block(GzWriter& w, bool bin, int kind, int dim, bool use_cvm, const uint64_t* signs, const float* rows, int rf,
-                     const std::vector<size_t>& idx, const EvictRule& rule) {
-  std::string buf;
-  buf.reserve(1 << 20);
+void block_header(std::string& buf, bool bin, int kind, int dim) {
   if (bin) {
     int32_t d = dim;
     buf.append(reinterpret_cast<const char*>(&d), 4);
@@ -368,78 +365,161 @@ void serialize_block(GzWriter& w, bool bin, int kind, int dim, bool use_cvm, con
     buf += "opt_name:"; buf += opt_name(kind); buf += "\n";
     buf += "dim:" + std::to_string(dim) + "\n";
   }
-  for (size_t i : idx) {
-    const float* row = rows + i * rf;
-    if (rule.drop(kind, row, dim)) continue;
-    if (bin) {
-      buf.append(reinterpret_cast<const char*>(&signs[i]), 8);
-      if (kind == kAdaGrad) {
-        buf.append(reinterpret_cast<const char*>(row), 4 * dim);          // w
-        buf.append(reinterpret_cast<const char*>(row + dim), 4);          // g2sum
-        buf.append(reinterpret_cast<const char*>(row + dim + 1), 4);      // show
-        buf.append(reinterpret_cast<const char*>(row + dim + 3), 4);      // no_show_days (int32)
-        if (use_cvm) buf.append(reinterpret_cast<const char*>(row + dim + 2), 4);  // click
-      } else {
-        buf.append(reinterpret_cast<const char*>(row), 4 * 3 * dim);      // w, m|z, v|n
-        buf.append(reinterpret_cast<const char*>(row + 3 * dim), 4);      // show
-      }
-    } else {
-      buf += std::to_string(signs[i]); buf += "\t";
-      if (kind == kAdaGrad) {
-        buf += std::to_string(dim); buf += "\t";
-        for (int k = 0; k < dim; ++k) { append_g(buf, row[k]); buf += "\t"; }
-        append_g(buf, row[dim]); buf += "\t";
-        append_g(buf, row[dim + 1]); buf += "\t";
-        buf += std::to_string(reinterpret_cast<const int32_t*>(row)[dim + 3]); buf += "\t";
-        if (use_cvm) append_g(buf, row[dim + 2]);
-      } else {
-        for (int k = 0; k < dim; ++k) {
-          append_g(buf, row[k]); buf += "\t";
-          append_g(buf, row[dim + k]); buf += "\t";
-          append_g(buf, row[2 * dim + k]); buf += "\t";
-        }
-        append_g(buf, row[3 * dim]);
-      }
-      buf += "\n";
-    }
-    if (buf.size() > (1 << 20)) { w.write(buf); buf.clear(); }
-  }
-  buf += "\n";   // the `<< std::endl` after the block
-  w.write(buf);
 }
+
+// Appends one record; returns false when the eviction rule drops the row.
+inline bool append_record(std::string& buf, bool bin, int kind, int dim, bool use_cvm, uint64_t sign, const float* row,
+                          const EvictRule& rule) {
+  if (rule.drop(kind, row, dim)) return false;
+  if (bin) {
+    buf.append(reinterpret_cast<const char*>(&sign), 8);
+    if (kind == kAdaGrad) {
+      buf.append(reinterpret_cast<const char*>(row), 4 * dim);          // w
+      buf.append(reinterpret_cast<const char*>(row + dim), 4);          // g2sum
+      buf.append(reinterpret_cast<const char*>(row + dim + 1), 4);      // show
+      buf.append(reinterpret_cast<const char*>(row + dim + 3), 4);      // no_show_days (int32)
+      if (use_cvm) buf.append(reinterpret_cast<const char*>(row + dim + 2), 4);  // click
+    } else {
+      buf.append(reinterpret_cast<const char*>(row), 4 * 3 * dim);      // w, m|z, v|n
+      buf.append(reinterpret_cast<const char*>(row + 3 * dim), 4);      // show
+    }
+  } else {
+    buf += std::to_string(sign); buf += "\t";
+    if (kind == kAdaGrad) {
+      buf += std::to_string(dim); buf += "\t";
+      for (int k = 0; k < dim; ++k) { append_g(buf, row[k]); buf += "\t"; }
+      append_g(buf, row[dim]); buf += "\t";
+      append_g(buf, row[dim + 1]); buf += "\t";
+      buf += std::to_string(reinterpret_cast<const int32_t*>(row)[dim + 3]); buf += "\t";
+      if (use_cvm) append_g(buf, row[dim + 2]);
+    } else {
+      for (int k = 0; k < dim; ++k) {
+        append_g(buf, row[k]); buf += "\t";
+        append_g(buf, row[dim + k]); buf += "\t";
+        append_g(buf, row[2 * dim + k]); buf += "\t";
+      }
+      append_g(buf, row[3 * dim]);
+    }
+    buf += "\n";
+  }
+  return true;
+}
+
+// Streaming writer of one rank directory: the eight block files stay open while the table arrives in chunks,
+// so a shard far larger than host memory can be saved.  Every append serialises and compresses the eight
+// blocks on eight threads (the reference saves with one thread per block as well,
+// core/ps/optimizer/optimizer_kernel.h:462-486).
+class SparseDirWriter {
+ public:
+  SparseDirWriter(const std::string& dir, const std::string& mode, int kind, int dim, bool use_cvm, bool evict,
+                  float show_threshold, int no_show_days, int logic)
+      : bin_(mode == "bin"), kind_(kind), dim_(dim), use_cvm_(use_cvm), rf_(tn::row_floats(kind, dim)),
+        rule_{evict, show_threshold, no_show_days, logic} {
+    mkdirs(dir);
+    for (int b = 0; b < tn::kSparseBlockNum; ++b) {
+      // text blocks keep the reference's file name; binary blocks carry the `_bin` suffix its reader
+      // needs to recognise them (core/ps/optimizer/optimizer_kernel.h:488-517)
+      w_.emplace_back(new GzWriter(dir + "/block_" + std::to_string(b) + (bin_ ? "_bin" : "") + ".gz"));
+      std::string h;
+      block_header(h, bin_, kind_, dim_);
+      w_[b]->write(h);
+    }
+  }
+
+  // records [offsets[b], offsets[b+1]) belong to block b (what the device-side export produces)
+  void append_grouped(py::array_t<uint64_t, py::array::c_style | py::array::forcecast> signs,
+                      py::array_t<float, py::array::c_style | py::array::forcecast> rows,
+                      py::array_t<int64_t, py::array::c_style | py::array::forcecast> offsets) {
+    check_open();
+    const ssize_t n = signs.shape(0);
+    if (rows.shape(0) != n || (n > 0 && rows.shape(1) != rf_)) throw std::invalid_argument("append: rows must be [n, row_floats]");
+    if (offsets.shape(0) != tn::kSparseBlockNum + 1) throw std::invalid_argument("append_grouped: offsets must have 9 entries");
+    const int64_t* off = offsets.data();
+    if (off[0] != 0 || off[tn::kSparseBlockNum] != n) throw std::invalid_argument("append_grouped: offsets do not cover the records");
+    const uint64_t* s = signs.data();
+    const float* r = rows.data();
+    run_blocks([&](int b, std::string& buf) {
+      int64_t kept = 0;
+      for (int64_t i = off[b]; i < off[b + 1]; ++i) {
+        if (tn::block_of(s[i]) != b) throw std::runtime_error("append_grouped: record outside its block range");
+        kept += append_record(buf, bin_, kind_, dim_, use_cvm_, s[i], r + (size_t)i * rf_, rule_);
+        if (buf.size() > (1 << 20)) { w_[b]->write(buf); buf.clear(); }
+      }
+      return kept;
+    });
+  }
+
+  // records in any order
+  void append(py::array_t<uint64_t, py::array::c_style | py::array::forcecast> signs,
+              py::array_t<float, py::array::c_style | py::array::forcecast> rows) {
+    check_open();
+    const ssize_t n = signs.shape(0);
+    if (rows.shape(0) != n || (n > 0 && rows.shape(1) != rf_)) throw std::invalid_argument("append: rows must be [n, row_floats]");
+    const uint64_t* s = signs.data();
+    const float* r = rows.data();
+    std::vector<std::vector<size_t>> per(tn::kSparseBlockNum);
+    for (ssize_t i = 0; i < n; ++i) per[tn::block_of(s[i])].push_back((size_t)i);
+    run_blocks([&](int b, std::string& buf) {
+      int64_t kept = 0;
+      for (size_t i : per[b]) {
+        kept += append_record(buf, bin_, kind_, dim_, use_cvm_, s[i], r + i * rf_, rule_);
+        if (buf.size() > (1 << 20)) { w_[b]->write(buf); buf.clear(); }
+      }
+      return kept;
+    });
+  }
+
+  int64_t close() {
+    if (!closed_) {
+      for (auto& w : w_) { w->write(std::string("\n")); w.reset(); }   // the `<< std::endl` after the block
+      closed_ = true;
+    }
+    return written_;
+  }
+
+ private:
+  void check_open() const { if (closed_) throw std::runtime_error("SparseDirWriter is closed"); }
+  template <class F>
+  void run_blocks(F fn) {
+    std::vector<std::thread> threads;
+    std::vector<std::string> errors(tn::kSparseBlockNum);
+    std::vector<int64_t> kept(tn::kSparseBlockNum, 0);
+    {
+      py::gil_scoped_release rel;
+      for (int b = 0; b < tn::kSparseBlockNum; ++b) {
+        threads.emplace_back([&, b]() {
+          try {
+            std::string buf;
+            buf.reserve(1 << 20);
+            kept[b] = fn(b, buf);
+            w_[b]->write(buf);
+          } catch (const std::exception& e) { errors[b] = e.what(); }
+        });
+      }
+      for (auto& t : threads) t.join();
+    }
+    for (auto& e : errors) if (!e.empty()) throw std::runtime_error(e);
+    for (int64_t k : kept) written_ += k;
+  }
+
+  bool bin_;
+  int kind_, dim_;
+  bool use_cvm_;
+  int rf_;
+  EvictRule rule_;
+  std::vector<std::unique_ptr<GzWriter>> w_;
+  bool closed_ = false;
+  int64_t written_ = 0;
+};
 
 int write_sparse_dir(const std::string& dir, const std::string& mode, int kind, int dim, bool use_cvm,
                      py::array_t<uint64_t, py::array::c_style | py::array::forcecast> signs,
                      py::array_t<float, py::array::c_style | py::array::forcecast> rows, bool evict, float show_threshold,
                      int no_show_days, int logic) {
-  const ssize_t n = signs.shape(0);
-  const int rf = tn::row_floats(kind, dim);
-  if (rows.shape(0) != n || (n > 0 && rows.shape(1) != rf)) throw std::invalid_argument("write_sparse_dir: rows must be [n, row_floats]");
-  const bool bin = mode == "bin";
-  const uint64_t* s = signs.data();
-  const float* r = rows.data();
-  EvictRule rule{evict, show_threshold, no_show_days, logic};
-  mkdirs(dir);
-  std::vector<std::vector<size_t>> per(tn::kSparseBlockNum);
-  for (ssize_t i = 0; i < n; ++i) per[tn::block_of(s[i])].push_back((size_t)i);
-  std::vector<std::thread> threads;
-  std::vector<std::string> errors(tn::kSparseBlockNum);
-  {
-    py::gil_scoped_release rel;
-    for (int b = 0; b < tn::kSparseBlockNum; ++b) {
-      threads.emplace_back([&, b]() {
-        try {
-          // text blocks keep the reference's file name; binary blocks carry the `_bin` suffix its reader
-          // needs to recognise them (core/ps/optimizer/optimizer_kernel.h:488-517)
-          GzWriter w(dir + "/block_" + std::to_string(b) + (bin ? "_bin" : "") + ".gz");
-          serialize_block(w, bin, kind, dim, use_cvm, s, r, rf, per[b], rule);
-        } catch (const std::exception& e) { errors[b] = e.what(); }
-      });
-    }
-    for (auto& t : threads) t.join();
-  }
-  for (auto& e : errors) if (!e.empty()) throw std::runtime_error(e);
-  return (int)n;
+  SparseDirWriter w(dir, mode, kind, dim, use_cvm, evict, show_threshold, no_show_days, logic);
+  w.append(signs, rows);
+  w.close();
+  return (int)signs.shape(0);
 }
 
 std::vector<std::string> list_dir(const std::string& dir) {
@@ -765,6 +845,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("dump", &CpuSparseTable::dump)
       .def("load_rows", &CpuSparseTable::load_rows)
       .def("clear", &CpuSparseTable::clear);
+  py::class_<SparseDirWriter>(m, "SparseDirWriter")
+      .def(py::init<const std::string&, const std::string&, int, int, bool, bool, float, int, int>())
+      .def("append", &SparseDirWriter::append)
+      .def("append_grouped", &SparseDirWriter::append_grouped)
+      .def("close", &SparseDirWriter::close);
   m.def("unique_first_occurrence", &unique_first_occurrence);
   m.def("write_sparse_dir", &write_sparse_dir);
   m.def("read_sparse_dir", &read_sparse_dir);

@@ -266,6 +266,7 @@ cudaError_t launch_dense_step(const DenseStepArgs& a, cudaStream_t st) {
   blocks = (blocks + kDenseUnroll - 1) / kDenseUnroll;
   int cap = sms * (per_sm < 1 ? 1 : per_sm);      // as many warps as fit: the loop is bound by loads in flight
   if (blocks > cap) blocks = cap;
+  if (a.max_ctas > 0 && blocks > a.max_ctas) blocks = a.max_ctas;
   if (blocks < 1) blocks = 1;
   void* params[] = {(void*)&a};
   return cudaLaunchCooperativeKernel((const void*)dense_fused_kernel, dim3(blocks), dim3(kDThreads), params, 0, st);

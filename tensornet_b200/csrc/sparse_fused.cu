@@ -82,6 +82,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_pull_fused_kernel(const __
   gs.init(c.bar, c.status, c.wait_ns);
   __shared__ unsigned long long s_flag;
   __shared__ int s_n[kMaxWorld];
+  __shared__ int s_pre[kMaxWorld + 1];
 
   const int tid = blockIdx.x * blockDim.x + threadIdx.x;
   const int nth = gridDim.x * blockDim.x;
@@ -195,27 +196,46 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_pull_fused_kernel(const __
   prof_mark(c, 2);
 
   // ---- phase B1: as owner, probe / insert every requested sign ------------------------------------
-  for (int si = 0; si < W; ++si) {
-    const int s = (R + si) % W;
+  // Two passes: this GPU's own segment first (nothing to wait for), then the segments of all other senders as
+  // ONE flat index space, so that with many GPUs no thread idles on a short per-sender segment.
+  // s_pre[k] = ids of senders R+1 .. R+k (mod W) that precede sender R+1+k in that space.
+  for (int part = 0; part < (W > 1 ? 2 : 1); ++part) {
     __syncthreads();
     if (threadIdx.x == 0) {
       unsigned long long v = 0;
-      if (s == R) {
+      if (part == 0) {
         v = (unsigned long long)min(__ldcg(&c.cnt[R]), capo);
-      } else if (!wait_flag_ge(sig_word(c.sig[R], kSigPullReq, s), epoch, &v, c.wait_ns, c.status, 3, s)) {
-        v = ~0ull;
+        s_n[R] = (int)v;
+        if (blockIdx.x == 0) c.req_n[R] = (int)v;
+      } else {
+        s_pre[0] = 0;
+        for (int k = 0; k + 1 < W; ++k) {
+          const int sk = (R + 1 + k) % W;
+          unsigned long long f = 0;
+          if (v != ~0ull && !wait_flag_ge(sig_word(c.sig[R], kSigPullReq, sk), epoch, &f, c.wait_ns, c.status, 3, sk)) v = ~0ull;
+          const int n_k = v == ~0ull ? 0 : (int)(f & 0xffffffffull);
+          s_n[sk] = n_k;
+          if (blockIdx.x == 0) c.req_n[sk] = n_k;
+          s_pre[k + 1] = s_pre[k] + n_k;
+        }
+        if (v != ~0ull) v = (unsigned long long)s_pre[W - 1];
       }
       s_flag = v;
     }
     __syncthreads();
     if (s_flag == ~0ull) { gs.failed = true; break; }
-    const int n_s = (int)(s_flag & 0xffffffffull);
-    if (threadIdx.x == 0) s_n[s] = n_s;
-    if (tid == 0) c.req_n[s] = n_s;
-    const unsigned long long* src = (s == R) ? c.stage_ids + (size_t)R * capo : c.inbox_ids[R] + (size_t)s * capo;
-    for (int base = tid - lane; base < n_s; base += nth) {
-      const int j = base + lane;
-      const bool valid = j < n_s;
+    const int n_part = (int)(s_flag & 0xffffffffull);
+    for (int base = tid - lane; base < n_part; base += nth) {
+      const int jj = base + lane;
+      const bool valid = jj < n_part;
+      int s = R, j = jj;
+      if (part == 1 && valid) {
+        int k = 0;
+        while (jj >= s_pre[k + 1]) ++k;
+        s = (R + 1 + k) % W;
+        j = jj - s_pre[k];
+      }
+      const unsigned long long* src = (s == R) ? c.stage_ids + (size_t)R * capo : c.inbox_ids[R] + (size_t)s * capo;
       int rr = kReqNone, ou = -1;
       bool is_new = false, need_claim = false;
       unsigned hnew = 0;
@@ -310,15 +330,28 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_pull_fused_kernel(const __
     const int ustride = c.ustride, stride = t.stride;
     const int uchunks = ustride >> 2, rchunks = stride >> 2;
     const SparseOptParams& o = a.opt;
-    for (int s = 0; s < W; ++s) {
-      const int n_s = s_n[s];
-      const unsigned long long* src = (s == R) ? c.stage_ids + (size_t)R * capo : c.inbox_ids[R] + (size_t)s * capo;
-      float* dst_base = c.U[s] + (size_t)R * capo * ustride;
-      for (int j = gid; j < n_s; j += ngroups) {
+    // all requesters as one flat index space (own segment first): s_pre[k] = rows of requesters R .. R+k-1 (mod W)
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      s_pre[0] = 0;
+      for (int k = 0; k < W; ++k) s_pre[k + 1] = s_pre[k] + s_n[(R + k) % W];
+    }
+    __syncthreads();
+    const int n_all = s_pre[W];
+    {
+      for (int jj = gid; jj < n_all; jj += ngroups) {
+        int k = 0;
+        while (jj >= s_pre[k + 1]) ++k;
+        const int s = (R + k) % W, j = jj - s_pre[k];
+        const unsigned long long* src = (s == R) ? c.stage_ids + (size_t)R * capo : c.inbox_ids[R] + (size_t)s * capo;
+        float* dst_base = c.U[s] + (size_t)R * capo * ustride;
         const int q = s * capo + j;
         int rr = __ldcg(&c.req_row[q]);
-        if (j + ngroups < n_s) {
-          const int r2 = __ldcg(&c.req_row[q + ngroups]);
+        if (jj + ngroups < n_all) {
+          const int j2 = jj + ngroups;
+          int k2 = k;
+          while (j2 >= s_pre[k2 + 1]) ++k2;
+          const int r2 = __ldcg(&c.req_row[((R + k2) % W) * capo + (j2 - s_pre[k2])]);
           if (r2 >= 0 && !(r2 & (kReqNewOwner | kReqNewCopy))) prefetch_row_l2(t.rows + (size_t)r2 * stride, ustride, gl, G);
         }
         float* dst = dst_base + (size_t)j * ustride;
@@ -442,6 +475,37 @@ template <bool VEC>
 __device__ __forceinline__ void apply_row(const SparseOptParams& o, float* row, const float* g, float bshow, float bclick,
                                           int dim, int lane, int G, unsigned gmask) {
   if (o.kind == kAdaGrad) {
+    if (VEC && (dim >> 2) <= 2 * G) {
+      // Every load of the row is issued before the first use, so a row costs one memory round trip instead of
+      // three (gradient -> squared norm -> accumulator -> weights): up to two float4 chunks per lane.
+      const int nch = dim >> 2;
+      const int c0 = lane, c1 = lane + G;
+      float4 x0 = make_float4(0.f, 0.f, 0.f, 0.f), x1 = x0, w0 = x0, w1 = x0;
+      if (c0 < nch) { x0 = *reinterpret_cast<const float4*>(g + 4 * c0); w0 = *reinterpret_cast<const float4*>(row + 4 * c0); }
+      if (c1 < nch) { x1 = *reinterpret_cast<const float4*>(g + 4 * c1); w1 = *reinterpret_cast<const float4*>(row + 4 * c1); }
+      const float g2old = row[dim];
+      float ss = x0.x * x0.x + x0.y * x0.y + x0.z * x0.z + x0.w * x0.w;
+      ss += x1.x * x1.x + x1.y * x1.y + x1.z * x1.z + x1.w * x1.w;
+      for (int off = G >> 1; off > 0; off >>= 1) ss += __shfl_xor_sync(gmask, ss, off);
+      const float g2 = g2old + ss / (float)dim;
+      const float scale = o.lr / (o.eps + sqrtf(g2));
+      if (c0 < nch) {
+        w0.x -= scale * x0.x; w0.y -= scale * x0.y; w0.z -= scale * x0.z; w0.w -= scale * x0.w;
+        *reinterpret_cast<float4*>(row + 4 * c0) = w0;
+      }
+      if (c1 < nch) {
+        w1.x -= scale * x1.x; w1.y -= scale * x1.y; w1.z -= scale * x1.z; w1.w -= scale * x1.w;
+        *reinterpret_cast<float4*>(row + 4 * c1) = w1;
+      }
+      __syncwarp(gmask);
+      if (lane == 0) {
+        row[dim] = g2;
+        row[dim + 1] += bshow;
+        row[dim + 2] += bclick;
+        reinterpret_cast<int*>(row)[dim + 3] = 0;
+      }
+      return;
+    }
     float ss = 0.f;
     if (VEC) {
       for (int ch = lane; ch < (dim >> 2); ch += G) {
@@ -526,6 +590,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_push_fused_kernel(const __
   GridSync gs;
   gs.init(c.bar, c.status, c.wait_ns);
   __shared__ unsigned long long s_flag;
+  __shared__ int s_pre[kMaxWorld + 1];
 
   const int tid = blockIdx.x * blockDim.x + threadIdx.x;
   const int nth = gridDim.x * blockDim.x;
@@ -564,10 +629,14 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_push_fused_kernel(const __
     goto done;
   }
 
-  // ---- phase A: ship gradient records and the (show, click) pairs to the owners, re-zero the local copies ----
-  // Two plain streaming loops: every warp moves whole 512-byte runs.  (Patching the counters into the records
-  // on the fly made one lane in gstride/4 leave the stream for an 8-byte side access and cost 3x the time.)
-  for (int p = 0; p < W; ++p) {
+  // ---- phase A: move gradient records and the (show, click) pairs into the owners' inboxes (this GPU's own inbox
+  // included), re-zero the local copies.  Two plain streaming loops: every warp moves whole 512-byte runs.
+  // (Patching the counters into the records on the fly made one lane in gstride/4 leave the stream for an 8-byte
+  // side access and cost 3x the time.  Accumulating the own records straight from the gradient matrix instead of
+  // staging them in the own inbox was also tried: whenever the matrix is not L2-resident that pass took 27 us
+  // instead of 6, so the staging copy stays.)
+  for (int pi = 0; pi < W; ++pi) {
+    const int p = (R + pi) % W;
     const int n = __ldcg(&c.cnt_saved[p]);
     float* src = c.gU + (size_t)p * capo * gstride;
     float* dst = c.ginbox[p] + (size_t)R * capo * gstride;
@@ -582,7 +651,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_push_fused_kernel(const __
       cdst[j] = csrc[j];
       csrc[j] = make_float2(0.f, 0.f);
     }
-    if (p == 0) prof_mark(c, 14);
   }
   prof_mark(c, 9);
   if (!gs.sync(11, true)) goto done;
@@ -591,34 +659,69 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_push_fused_kernel(const __
   prof_mark(c, 10);
 
   // ---- phase B: as owner, sum records of equal sign coming from different GPUs --------------------
-  for (int si = 0; si < W; ++si) {
-    const int s = (R + si) % W;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      unsigned long long v = 0;
-      if (s != R && !wait_flag_ge(sig_word(c.sig[R], kSigPushReq, s), epoch, &v, c.wait_ns, c.status, 12, s)) v = ~0ull;
-      s_flag = v;
-    }
-    __syncthreads();
-    if (s_flag == ~0ull) { gs.failed = true; break; }
-    const int n_s = __ldcg(&c.req_n[s]);
-    const float* src = c.ginbox[R] + (size_t)s * capo * gstride;
+  // own records first (nothing to wait for)
+  {
+    const int n_s = __ldcg(&c.req_n[R]);
+    const float* src = c.ginbox[R] + (size_t)R * capo * gstride;
     const int total = n_s * gch;
     for (int i = tid; i < total; i += nth) {
       const int j = i / gch, ch = i - j * gch;
-      const int ou = __ldcg(&c.req_ou[s * capo + j]);
+      const int ou = __ldcg(&c.req_ou[R * capo + j]);
       if (ou < 0) continue;
-      float4 v = ldcg_f4(src + 4 * (size_t)i);
-      red_add_f32x4(c.acc + (size_t)ou * gstride + 4 * ch, v);
+      red_add_f32x4(c.acc + (size_t)ou * gstride + 4 * ch, ldcg_f4(src + 4 * (size_t)i));
     }
-    const float2* csrc = reinterpret_cast<const float2*>(c.cinbox[R]) + (size_t)s * capo;
+    const float2* csrc = reinterpret_cast<const float2*>(c.cinbox[R]) + (size_t)R * capo;
     for (int j = tid; j < n_s; j += nth) {
-      const int ou = __ldcg(&c.req_ou[s * capo + j]);
+      const int ou = __ldcg(&c.req_ou[R * capo + j]);
       if (ou < 0) continue;
       const float2 sc = __ldcg(&csrc[j]);
       float* g = c.acc + (size_t)ou * gstride + dim;          // the record's show / click slots
       atomicAdd(g, sc.x);
       if (sc.y != 0.f) atomicAdd(g + 1, sc.y);
+    }
+  }
+  prof_mark(c, 14);
+  // then everybody else's, as one flat index space over the senders so that no thread idles on a short segment
+  {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int ok = 1;
+      s_pre[0] = 0;
+      for (int k = 0; k + 1 < W; ++k) {
+        const int sk = (R + 1 + k) % W;
+        unsigned long long v;
+        if (ok && !wait_flag_ge(sig_word(c.sig[R], kSigPushReq, sk), epoch, &v, c.wait_ns, c.status, 12, sk)) ok = 0;
+        s_pre[k + 1] = s_pre[k] + __ldcg(&c.req_n[sk]);
+      }
+      s_flag = ok ? 0ull : ~0ull;
+    }
+    __syncthreads();
+    prof_mark(c, 15);
+    if (s_flag == ~0ull) { gs.failed = true; }
+    else {
+      const int n_all = s_pre[W - 1];
+      const int total = n_all * gch;
+      for (int i = tid; i < total; i += nth) {
+        const int jj = i / gch, ch = i - jj * gch;
+        int k = 0;
+        while (jj >= s_pre[k + 1]) ++k;
+        const int sk = (R + 1 + k) % W, j = jj - s_pre[k];
+        const int ou = __ldcg(&c.req_ou[sk * capo + j]);
+        if (ou < 0) continue;
+        const float4 v = ldcg_f4(c.ginbox[R] + ((size_t)sk * capo + j) * gstride + 4 * ch);
+        red_add_f32x4(c.acc + (size_t)ou * gstride + 4 * ch, v);
+      }
+      for (int jj = tid; jj < n_all; jj += nth) {
+        int k = 0;
+        while (jj >= s_pre[k + 1]) ++k;
+        const int sk = (R + 1 + k) % W, j = jj - s_pre[k];
+        const int ou = __ldcg(&c.req_ou[sk * capo + j]);
+        if (ou < 0) continue;
+        const float2 sc = __ldcg(reinterpret_cast<const float2*>(c.cinbox[R]) + (size_t)sk * capo + j);
+        float* g = c.acc + (size_t)ou * gstride + dim;
+        atomicAdd(g, sc.x);
+        if (sc.y != 0.f) atomicAdd(g + 1, sc.y);
+      }
     }
   }
   if (gs.failed) goto done;
@@ -676,7 +779,8 @@ cudaError_t launch_sparse_pull(const PullArgs& args, int work_items, cudaStream_
   return cudaLaunchCooperativeKernel((const void*)sparse_pull_fused_kernel, dim3(grid), dim3(kThreads), params, 0, stream);
 }
 
-cudaError_t launch_sparse_push(const PushArgs& args, int work_items, cudaStream_t stream) {
+// `max_ctas` > 0 caps the grid below the SM count, leaving whole SMs to a kernel running on another stream.
+cudaError_t launch_sparse_push(const PushArgs& args, int work_items, int max_ctas, cudaStream_t stream) {
   int dev = 0;
   cudaGetDevice(&dev);
   static int grid_max[64] = {0};
@@ -684,6 +788,7 @@ cudaError_t launch_sparse_push(const PushArgs& args, int work_items, cudaStream_
   int grid = (work_items + kThreads - 1) / kThreads;
   if (grid < 1) grid = 1;
   if (grid > grid_max[dev]) grid = grid_max[dev];
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   void* params[] = {(void*)&args};
   return cudaLaunchCooperativeKernel((const void*)sparse_push_fused_kernel, dim3(grid), dim3(kThreads), params, 0, stream);
 }

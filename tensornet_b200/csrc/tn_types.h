@@ -97,6 +97,7 @@ struct DenseStepArgs {
   long long chunk;      // elements owned per GPU (multiple of 4); n for world == 1
   int world, rank;
   float grad_scale;     // 1/world for the mean gradient
+  int max_ctas;         // world > 1: cap on the cooperative grid (0 = fill the GPU); a small cap leaves SMs to a kernel on another stream
   int gated;            // world > 1: publish per-owner "chunk written" flags (row 2 of sig) instead of waiting in a closing barrier;
                         // the first kernel that reads the weights waits on them (GemmDesc::gate_flags)
   int zero_local;       // world > 1: each GPU clears its own gradient replica after the closing barrier
@@ -114,6 +115,15 @@ struct DenseStepArgs {
   unsigned* bar;
   int* status;
   unsigned long long wait_ns;
+};
+
+// Save-time eviction rule (the reference's DeleteByShow): AdaGrad rows go when `show < show_threshold`
+// or / and (logic 0 / 1) `no_show_days > no_show_days`; Ftrl rows when `show < show_threshold`.
+struct ExportRule {
+  int enabled;
+  float show_threshold;
+  int no_show_days;
+  int logic;
 };
 
 // Device-resident batch-norm statistics table (all arrays have C entries unless noted).
@@ -142,6 +152,6 @@ struct BnSyncView {
 
 cudaError_t launch_dense_step(const DenseStepArgs& a, cudaStream_t st);
 cudaError_t launch_sparse_pull(const PullArgs& args, int work_items, cudaStream_t stream);
-cudaError_t launch_sparse_push(const PushArgs& args, int work_items, cudaStream_t stream);
+cudaError_t launch_sparse_push(const PushArgs& args, int work_items, int max_ctas, cudaStream_t stream);
 
 }  // namespace tn

@@ -171,6 +171,19 @@ class Model(nn.Module):
             tower = getattr(self, "first_dense_tower", None)
             if tower is not None and rt.on_gpu and rt.world > 1 and core.config.gate_first_gemm:
                 tower().weight_gate = optimizer.table.enable_gate()
+            # Several GPUs, small dense array: the dense step and the sparse push both wait on their peers, so they
+            # may only share the GPU if each fits beside the other whatever order the hardware picks.  The push
+            # gives up 8 SMs, the dense kernel takes at most 32 small CTAs (they fit on those 8 SMs); then neither
+            # can block the other from becoming resident and the two run side by side.
+            self._overlap_dense = bool(rt.on_gpu and rt.world > 1 and core.config.overlap_dense_push and
+                                       optimizer.table.n <= (4 << 20) and self.sparse_layers())
+            if rt.on_gpu and rt.world > 1 and core.config.dense_small_grid > 0 and optimizer.table.n <= (4 << 20):
+                optimizer.table.limit_grid(core.config.dense_small_grid)
+            if self._overlap_dense:
+                optimizer.table.limit_grid(32)
+                for layer in self.sparse_layers():
+                    for lk in getattr(layer, "links", None) or [layer.link]:
+                        lk.push_cta_cap = 140
         return self
 
     def sparse_layers(self):
@@ -205,6 +218,14 @@ class Model(nn.Module):
             with torch.cuda.stream(side):
                 self.backwards()
             self.optimizer.step()
+            main.wait_stream(side)
+        elif rt.on_gpu and self.optimizer is not None and getattr(self, "_overlap_dense", False):
+            main = torch.cuda.current_stream()
+            side = F._side_stream(rt.device)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                self.optimizer.step()
+            self.backwards()
             main.wait_stream(side)
         else:
             if self.optimizer is not None:

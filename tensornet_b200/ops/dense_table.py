@@ -114,6 +114,11 @@ class DenseTable:
         flags = self.arena.tensor("sig")[2 * 8: 2 * 8 + self.world]
         return (flags, self._ctx_args["epoch"], self.world, int(rt.wait_ns))
 
+    def limit_grid(self, max_ctas: int):
+        """Cap the multi-GPU dense kernel's grid so that it can share the GPU with a kernel on another stream."""
+        if runtime().on_gpu and self.initialized:
+            self.ctx.set_max_ctas(int(max_ctas))
+
     def set_lr(self, lr: float):
         if lr != self.lr:
             self.lr = float(lr)

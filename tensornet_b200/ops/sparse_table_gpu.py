@@ -114,6 +114,35 @@ class GpuSparseTable:
         rows = self.rows[:n, :rf].contiguous().cpu().numpy()
         return keys, rows
 
+    def export_chunks(self, chunk_rows: int = 1 << 22, evict=(False, 0.0, 0, 0)):
+        """Stream this shard for a checkpoint.  Yields ``(signs uint64 [m], rows float32 [m, row_floats],
+        offsets int64 [9])`` per slab range of ``chunk_rows`` rows: rows the save-time eviction rule drops are
+        already gone and the rest is grouped by block file (``offsets[b]:offsets[b+1]`` is block b), packed on
+        the device and copied out through one pinned staging buffer that is reused, so host memory stays at one
+        chunk however large the shard is.  The arrays are views of that buffer: consume them before the next one."""
+        n = self.n_rows
+        rf = row_floats(self.kind, self.dim)
+        chunk_rows = max(1, min(int(chunk_rows), max(n, 1)))
+        d = self.dev
+        k_dev = torch.empty(chunk_rows, dtype=torch.int64, device=d)
+        r_dev = torch.empty((chunk_rows, rf), dtype=torch.float32, device=d)
+        cnt = torch.zeros(16, dtype=torch.int32, device=d)
+        k_host = torch.empty(chunk_rows, dtype=torch.int64).pin_memory()
+        r_host = torch.empty((chunk_rows, rf), dtype=torch.float32).pin_memory()
+        for r0 in range(0, n, chunk_rows):
+            r1 = min(n, r0 + chunk_rows)
+            cnt.zero_()
+            self.ext.table_export(self.table_dict(), self.kind, bool(evict[0]), float(evict[1]), int(evict[2]), int(evict[3]),
+                                  r0, r1, cnt[:8], cnt[8:], k_dev, r_dev)
+            counts = cnt[:8].cpu().numpy().astype(np.int64)
+            m = int(counts.sum())
+            k_host[:m].copy_(k_dev[:m], non_blocking=True)
+            r_host[:m].copy_(r_dev[:m], non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            offsets = np.zeros(9, dtype=np.int64)
+            offsets[1:] = np.cumsum(counts)
+            yield k_host[:m].numpy().view(np.uint64), r_host[:m].numpy(), offsets
+
     def load_rows(self, signs: np.ndarray, rows: np.ndarray, chunk: int = 1 << 20):
         """Insert (or overwrite) rows given as host arrays; ``signs`` must be distinct."""
         rt = runtime()
@@ -204,6 +233,7 @@ class GpuSparseLink:
                          sig=arena.ptrs("sig"), epoch=table.epoch, status=rt.status, wait_ns=rt.wait_ns, **loc)
         self.ctx = table.ext.SparseCtx(table.table_dict(), self.comm, table._opt_dict())
         self._last_n_ids = 0
+        self.push_cta_cap = 0        # > 0: the push kernel leaves the remaining SMs to a kernel on another stream
         if multi:
             rt.barrier()
 
@@ -220,7 +250,7 @@ class GpuSparseLink:
 
     def push(self):
         """Apply the accumulated unique-row gradients (``self.gU``) on the owning GPUs."""
-        self.ctx.push(max(self._last_n_ids, 1))
+        self.ctx.push(max(self._last_n_ids, 1), int(self.push_cta_cap))
 
     def pull_phase_us(self):
         """Durations (microseconds) of the last pull's phases as seen by CTA 0:
@@ -229,9 +259,9 @@ class GpuSparseLink:
         return [(t[i + 1] - t[i]) / 1e3 for i in range(5)]
 
     def push_phase_us(self):
-        """Durations (microseconds) of the last multi-GPU push's phases as seen by CTA 0: record shipping,
-        grid barrier + signal, owner-side accumulation (includes the wait for the peers' records),
-        grid barrier, optimizer update."""
+        """Durations (microseconds) of the last multi-GPU push's phases as seen by CTA 0: moving records into the
+        owners' inboxes, grid barrier + signal, owner-side accumulation (own records, then the wait for and the
+        sum over the peers' records), grid barrier, optimizer update."""
         t = self.prof.tolist()
         return [(t[i + 1] - t[i]) / 1e3 for i in range(8, 13)]
 

@@ -22,6 +22,7 @@ import torch
 
 from .. import _build
 from ..core.optimizers import KIND_ADAGRAD, KIND_ADAM, KIND_FTRL
+from ..core.config import config
 from ..core.runtime import runtime
 
 
@@ -41,8 +42,14 @@ def save_sparse_table(table, path: str, mode: str = "txt") -> int:
     rt = runtime()
     ext = _build.cpu_ext()
     d = os.path.join(path, "sparse_table", _table_dirname(table), f"rank_{rt.rank}")
-    signs, rows = table.dump()
     ev = _evict_args(table.opt)
+    if hasattr(table, "export_chunks"):
+        # GPU shard: filtered and grouped by block on the device, streamed through one pinned buffer
+        w = ext.SparseDirWriter(d, mode, table.kind, table.dim, table.use_cvm, *ev)
+        for signs, rows, offsets in table.export_chunks(config.checkpoint_chunk_rows, ev):
+            w.append_grouped(signs, rows, offsets)
+        return int(w.close())
+    signs, rows = table.dump()
     return ext.write_sparse_dir(d, mode, table.kind, table.dim, table.use_cvm, np.ascontiguousarray(signs, dtype=np.uint64),
                                 np.ascontiguousarray(rows, dtype=np.float32), *ev)
 

@@ -161,3 +161,46 @@ def test_table_full_is_reported_not_fatal(tn_gpu):
     assert t.n_rows == 64
     # the context is still usable
     assert float(torch.ones(4, device=t.dev).sum()) == 4.0
+
+
+@pytest.mark.parametrize("kind,mode", [("adagrad", "txt"), ("adagrad", "bin"), ("adam", "bin"), ("ftrl", "txt")])
+def test_streamed_export_matches_dump_and_applies_eviction(tn_gpu, status_ok, tmp_path, kind, mode):
+    """A shard saved in small streamed pieces (device-side filter + grouping by block file) reads back as the rows
+    of the plain dump minus those the save-time eviction rule drops."""
+    from tensornet_b200 import _build
+    from tensornet_b200.utils import checkpoint
+
+    tn = tn_gpu
+    opt = {"adagrad": tn.core.AdaGrad(learning_rate=0.01, show_threshold=1.5, no_show_days=10),
+           "adam": tn.core.Adam(learning_rate=0.01), "ftrl": tn.core.Ftrl(learning_rate=0.01)}[kind]
+    dim = 6
+    t, lk = _mk(tn, opt, dim, rows=1 << 13, max_unique=8192)
+    t.name = f"exp_{kind}_{mode}"
+    g = torch.Generator().manual_seed(11)
+    ids = (torch.randint(0, 3000, (6000,), generator=g, dtype=torch.int64) * 0x9E3779B97F4A7C15) .to(t.dev)
+    lk.pull(ids, labels=torch.ones(6000, device=t.dev), training=True)
+    lk.gU.normal_()
+    lk.push()
+    torch.cuda.synchronize()
+    full = _host_rows(t)
+    assert len(full) > 1500
+    old = tn.core.config.checkpoint_chunk_rows
+    tn.core.config.checkpoint_chunk_rows = 700          # several pieces
+    try:
+        n_written = checkpoint.save_sparse_table(t, str(tmp_path), mode)
+    finally:
+        tn.core.config.checkpoint_chunk_rows = old
+    signs, rows = _build.cpu_ext().read_sparse_dir(str(tmp_path / "sparse_table" / t.name / "rank_0"), t.kind, dim, False)
+    if kind == "adagrad":
+        keep = {k for k, r in full.items() if not (r[dim + 1] < 1.5)}     # no_show_days is 0 everywhere: only the show rule bites
+    else:        # Adam has no rule; Ftrl's show stays 0 (its update only counts delta_show), threshold 0 keeps all
+        keep = set(full)
+    assert n_written == len(keep) == len(signs)
+    assert 0 < len(keep) and (kind != "adagrad" or len(keep) < len(full))
+    assert set(int(s) for s in signs) == keep
+    for s, r in zip(signs, rows):
+        ref = full[int(s)]
+        if mode == "bin":
+            assert np.array_equal(r[:dim], ref[:dim])
+        else:
+            assert np.allclose(r[:dim], ref[:dim], rtol=1e-5, atol=1e-6)     # text keeps 6 significant digits
