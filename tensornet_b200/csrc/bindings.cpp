@@ -76,6 +76,7 @@ struct SparseCtx {
   tn::TableView t{};
   tn::SparseOptParams o{};
   int pull_lanes = 1, push_lanes = 1;
+  int tile_rows = 0;   // staged row return of the multi-GPU pull (0 = rows go straight to the requester)
   py::dict keep;   // keeps the tensors alive
 
   SparseCtx(py::dict table, py::dict comm, py::dict opt) {
@@ -127,6 +128,14 @@ struct SparseCtx {
     c.prof = comm.contains("prof") && !comm["prof"].is_none() ? ptr_of<unsigned long long>(comm["prof"].cast<at::Tensor>()) : nullptr;
     pull_lanes = tn::lanes_for_width_host((c.ustride + 3) / 4);   // each lane keeps up to four 16-byte chunks in flight
     push_lanes = tn::lanes_for_width_host(t.dim);
+    if (c.world > 1 && (!comm.contains("staged_return") || comm["staged_return"].cast<bool>())) {
+      // rows per tile: whole 128-byte lines per tile, about 4 KiB of shared memory per warp at most
+      int tr = 32;
+      while (tr > 8 && tr * c.ustride * 4 > 4096) tr >>= 1;
+      const int rpp = 32 / pull_lanes;
+      const bool fits = (size_t)tr * c.ustride * 4 * 32 <= 160 * 1024;
+      if (fits && tr % rpp == 0 && c.capo % tr == 0 && (tr * c.ustride * 4) % 128 == 0) tile_rows = tr;
+    }
   }
 
   void set_opt(py::dict opt) { o = opt_from_dict(opt); }
@@ -145,6 +154,7 @@ struct SparseCtx {
     a.label_mod = label_mod;
     a.training = training ? 1 : 0;
     a.lanes = pull_lanes;
+    a.tile_rows = tile_rows;
     long long work = (long long)a.n_ids * (pull_lanes > 4 ? pull_lanes / 2 : 2);
     if (work > (1ll << 30)) work = 1ll << 30;
     check(tn::launch_sparse_pull(a, (int)work, cur_stream()), "sparse_pull_fused launch");

@@ -70,6 +70,96 @@ __device__ __forceinline__ void prof_mark(const SparseCommView& c, int slot) {
   if (c.prof != nullptr && blockIdx.x == 0 && threadIdx.x == 0) c.prof[slot] = globaltimer_ns();
 }
 
+// One requested row, handled by a group of G lanes: resolve a request that lost the insert race, initialise a
+// brand-new row (owner) or recompute its initial value (other requesters of the same step), or read the stored
+// row; write the pulled row (w[dim], the two CVM columns when enabled, zero padding) to `dst`, which is either
+// the requester's matrix itself or a shared-memory tile that is written out afterwards.
+__device__ __forceinline__ void pull_return_row(const PullArgs& a, unsigned long long epoch, bool need_ou, int q,
+                                                unsigned long long key, float* dst, int gl, int G) {
+  const SparseCommView& c = a.c;
+  const TableView& t = a.tbl;
+  const SparseOptParams& o = a.opt;
+  const int dim = t.dim, stride = t.stride;
+  const int uchunks = c.ustride >> 2, rchunks = stride >> 2;
+  int rr = __ldcg(&c.req_row[q]);
+  if (rr == kReqPending) {
+    int h = __ldcg(&c.req_ou[q]);
+    int r = ld_volatile_s32(&t.slots[h]);
+    if (r >= 0) {
+      unsigned long long tg = __ldcg(&t.row_tag[r]);
+      bool fresh = (tg >> 32) == epoch && (tg & kTagNew);
+      rr = fresh ? (r | kReqNewCopy) : r;
+      if (gl == 0) {
+        c.req_row[q] = rr;
+        c.req_ou[q] = need_ou ? (int)(tg & 0x7fffffffull) : -1;
+      }
+    } else {
+      rr = kReqNone;
+      if (gl == 0) { c.req_row[q] = kReqNone; c.req_ou[q] = -1; }
+    }
+  }
+  if (rr == kReqNone) {
+    for (int ch = gl; ch < uchunks; ch += G) *reinterpret_cast<float4*>(dst + 4 * ch) = make_float4(0.f, 0.f, 0.f, 0.f);
+    return;
+  }
+  const int r = rr & kReqRowMask;
+  float* row = t.rows + (size_t)r * stride;
+  if (rr & (kReqNewOwner | kReqNewCopy)) {
+    const bool write_row = (rr & kReqNewOwner) != 0;
+    const int nch = write_row ? max(rchunks, uchunks) : uchunks;
+    for (int ch = gl; ch < nch; ch += G) {
+      float4 v;
+      v.x = new_row_elem(o, key, 4 * ch + 0, dim);
+      v.y = new_row_elem(o, key, 4 * ch + 1, dim);
+      v.z = new_row_elem(o, key, 4 * ch + 2, dim);
+      v.w = new_row_elem(o, key, 4 * ch + 3, dim);
+      if (write_row && ch < rchunks) *reinterpret_cast<float4*>(row + 4 * ch) = v;
+      if (ch < uchunks) {
+        // pulled row = w[dim] (+ two zero CVM columns for a new row), zero padding
+        float4 u;
+        u.x = 4 * ch + 0 < dim ? v.x : 0.f;
+        u.y = 4 * ch + 1 < dim ? v.y : 0.f;
+        u.z = 4 * ch + 2 < dim ? v.z : 0.f;
+        u.w = 4 * ch + 3 < dim ? v.w : 0.f;
+        *reinterpret_cast<float4*>(dst + 4 * ch) = u;
+      }
+    }
+    return;
+  }
+  float show = 0.f, click = 0.f;
+  if (t.use_cvm && o.kind == kAdaGrad) { show = row[dim + 1]; click = row[dim + 2]; }
+  // up to four 16-byte loads in flight per lane (G >= ceil(uchunks / 4)), then the stores
+  float4 buf[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int ch = gl + k * G;
+    if (ch < uchunks) buf[k] = *reinterpret_cast<const float4*>(row + 4 * ch);   // stride >= ustride by layout
+  }
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int ch = gl + k * G;
+    if (ch >= uchunks) continue;
+    float4 v = buf[k];
+    if (4 * ch + 4 > dim) {
+      float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        int idx = 4 * ch + kk;
+        if (idx >= dim) {
+          float x = 0.f;
+          if (t.use_cvm && o.kind == kAdaGrad) {
+            if (idx == dim) x = show;
+            else if (idx == dim + 1) x = logf(click + 1.f) - logf(show + 1.f);
+          }
+          e[kk] = x;
+        }
+      }
+      v = make_float4(e[0], e[1], e[2], e[3]);
+    }
+    *reinterpret_cast<float4*>(dst + 4 * ch) = v;
+  }
+}
+
 }  // namespace
 
 // =======================================================================================
@@ -146,7 +236,27 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_pull_fused_kernel(const __
   if (!gs.sync(1, false)) goto done;
   prof_mark(c, 1);
 
-  // ---- phase A2: inverse map, show/click counts; ship id segments to the owners -------------------
+  // ---- phase A2: ship id segments to the owners (first, so that the link latency and the owners' wait overlap
+  // the rest of this phase), then inverse map and show/click counts ---------------------------------------
+  if (W > 1) {
+    // coalesced 16-byte peer stores of each owner's id segment
+    for (int p = 0; p < W; ++p) {
+      if (p == R) continue;
+      int n = __ldcg(&c.cnt[p]);
+      if (n > capo) n = capo;
+      const ulonglong2* src = reinterpret_cast<const ulonglong2*>(c.stage_ids + (size_t)p * capo);
+      ulonglong2* dst = reinterpret_cast<ulonglong2*>(c.inbox_ids[p] + (size_t)R * capo);
+      int n2 = (n + 1) >> 1;
+      for (int j = tid; j < n2; j += nth) dst[j] = __ldcg(&src[j]);
+    }
+    // no grid barrier: the CTA that finishes shipping last tells the owners their segments are complete, while
+    // the others already probe the local segment (which only needs phase A, and that is behind barrier 1)
+    if (last_cta_arrives(&c.bar[2], true) && threadIdx.x < W && threadIdx.x != R) {
+      int p = threadIdx.x;
+      int n = min(__ldcg(&c.cnt[p]), capo);
+      st_release_sys_u64(sig_word(c.sig[p], kSigPullReq, R), (epoch << 32) | (unsigned long long)n);
+    }
+  }
   for (int base = tid - lane; base < a.n_ids; base += nth) {
     const int i = base + lane;
     const bool valid = i < a.n_ids;
@@ -172,25 +282,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_pull_fused_kernel(const __
         float y = a.label_mod > 0 ? a.labels[i % a.label_mod] : a.labels[i];
         if (y != 0.f) atomicAdd(rec + 1, y);
       }
-    }
-  }
-  if (W > 1) {
-    // coalesced 16-byte peer stores of each owner's id segment
-    for (int p = 0; p < W; ++p) {
-      if (p == R) continue;
-      int n = __ldcg(&c.cnt[p]);
-      if (n > capo) n = capo;
-      const ulonglong2* src = reinterpret_cast<const ulonglong2*>(c.stage_ids + (size_t)p * capo);
-      ulonglong2* dst = reinterpret_cast<ulonglong2*>(c.inbox_ids[p] + (size_t)R * capo);
-      int n2 = (n + 1) >> 1;
-      for (int j = tid; j < n2; j += nth) dst[j] = __ldcg(&src[j]);
-    }
-    // no grid barrier: the CTA that finishes shipping last tells the owners their segments are complete, while
-    // the others already probe the local segment (which only needs phase A, and that is behind barrier 1)
-    if (last_cta_arrives(&c.bar[2], true) && threadIdx.x < W && threadIdx.x != R) {
-      int p = threadIdx.x;
-      int n = min(__ldcg(&c.cnt[p]), capo);
-      st_release_sys_u64(sig_word(c.sig[p], kSigPullReq, R), (epoch << 32) | (unsigned long long)n);
     }
   }
   prof_mark(c, 2);
@@ -326,27 +417,53 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_pull_fused_kernel(const __
   {
     const int G = a.lanes;
     const int gl = threadIdx.x % G;
-    const int gid = tid / G, ngroups = nth / G;
     const int ustride = c.ustride, stride = t.stride;
-    const int uchunks = ustride >> 2, rchunks = stride >> 2;
-    const SparseOptParams& o = a.opt;
-    // all requesters as one flat index space (own segment first): s_pre[k] = rows of requesters R .. R+k-1 (mod W)
+    const int uchunks = ustride >> 2;
+    // all requesters as one flat index space (own segment first)
     __syncthreads();
     if (threadIdx.x == 0) {
       s_pre[0] = 0;
-      for (int k = 0; k < W; ++k) s_pre[k + 1] = s_pre[k] + s_n[(R + k) % W];
+      if (a.tile_rows > 0) {     // s_pre[k] = tiles of requesters R .. R+k-1 (mod W)
+        for (int k = 0; k < W; ++k) s_pre[k + 1] = s_pre[k] + (s_n[(R + k) % W] + a.tile_rows - 1) / a.tile_rows;
+      } else {                   // s_pre[k] = rows of those requesters
+        for (int k = 0; k < W; ++k) s_pre[k + 1] = s_pre[k] + s_n[(R + k) % W];
+      }
     }
     __syncthreads();
     const int n_all = s_pre[W];
-    {
+    if (a.tile_rows > 0) {
+      // Staged return: a warp gathers TR consecutive rows of one requester into shared memory and then writes
+      // the tile out as one contiguous run of full 128-byte lines (16 bytes per lane, 512 per instruction).
+      // Row-by-row stores of short rows (80 bytes for dim 16 + linear) reach the peer as partial lines and
+      // lose about a third of the NVLink write rate.
+      extern __shared__ float4 s_tiles[];
+      const int TR = a.tile_rows;
+      const int rpp = 32 / G;                                   // rows gathered per pass
+      const int sub = lane / G;
+      float* tile = reinterpret_cast<float*>(s_tiles) + (size_t)(threadIdx.x >> 5) * TR * ustride;
+      const int n_warps = nth >> 5;
+      for (int tl = tid >> 5; tl < n_all; tl += n_warps) {
+        int k = 0;
+        while (tl >= s_pre[k + 1]) ++k;
+        const int s = (R + k) % W, j0 = (tl - s_pre[k]) * TR;
+        const int nrows = min(TR, s_n[s] - j0);
+        const unsigned long long* src = (s == R) ? c.stage_ids + (size_t)R * capo : c.inbox_ids[R] + (size_t)s * capo;
+        for (int jr = sub; jr < nrows; jr += rpp)
+          pull_return_row(a, epoch, need_ou, s * capo + j0 + jr, __ldcg(&src[j0 + jr]), tile + (size_t)jr * ustride, gl, G);
+        __syncwarp();
+        float4* d4 = reinterpret_cast<float4*>(c.U[s] + ((size_t)R * capo + j0) * ustride);
+        const float4* t4 = reinterpret_cast<const float4*>(tile);
+        const int n4 = nrows * uchunks;
+        for (int i = lane; i < n4; i += 32) d4[i] = t4[i];
+        __syncwarp();
+      }
+    } else {
+      const int gid = tid / G, ngroups = nth / G;
       for (int jj = gid; jj < n_all; jj += ngroups) {
         int k = 0;
         while (jj >= s_pre[k + 1]) ++k;
         const int s = (R + k) % W, j = jj - s_pre[k];
         const unsigned long long* src = (s == R) ? c.stage_ids + (size_t)R * capo : c.inbox_ids[R] + (size_t)s * capo;
-        float* dst_base = c.U[s] + (size_t)R * capo * ustride;
-        const int q = s * capo + j;
-        int rr = __ldcg(&c.req_row[q]);
         if (jj + ngroups < n_all) {
           const int j2 = jj + ngroups;
           int k2 = k;
@@ -354,85 +471,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_pull_fused_kernel(const __
           const int r2 = __ldcg(&c.req_row[((R + k2) % W) * capo + (j2 - s_pre[k2])]);
           if (r2 >= 0 && !(r2 & (kReqNewOwner | kReqNewCopy))) prefetch_row_l2(t.rows + (size_t)r2 * stride, ustride, gl, G);
         }
-        float* dst = dst_base + (size_t)j * ustride;
-        if (rr == kReqPending) {
-          int h = __ldcg(&c.req_ou[q]);
-          int r = ld_volatile_s32(&t.slots[h]);
-          if (r >= 0) {
-            unsigned long long tg = __ldcg(&t.row_tag[r]);
-            bool fresh = (tg >> 32) == epoch && (tg & kTagNew);
-            rr = fresh ? (r | kReqNewCopy) : r;
-            if (gl == 0) {
-              c.req_row[q] = rr;
-              c.req_ou[q] = need_ou ? (int)(tg & 0x7fffffffull) : -1;
-            }
-          } else {
-            rr = kReqNone;
-            if (gl == 0) { c.req_row[q] = kReqNone; c.req_ou[q] = -1; }
-          }
-        }
-        if (rr == kReqNone) {
-          for (int ch = gl; ch < uchunks; ch += G)
-            *reinterpret_cast<float4*>(dst + 4 * ch) = make_float4(0.f, 0.f, 0.f, 0.f);
-          continue;
-        }
-        const int r = rr & kReqRowMask;
-        float* row = t.rows + (size_t)r * stride;
-        if (rr & (kReqNewOwner | kReqNewCopy)) {
-          const unsigned long long key = __ldcg(&src[j]);
-          const bool write_row = (rr & kReqNewOwner) != 0;
-          const int nch = write_row ? max(rchunks, uchunks) : uchunks;
-          for (int ch = gl; ch < nch; ch += G) {
-            float4 v;
-            v.x = new_row_elem(o, key, 4 * ch + 0, dim);
-            v.y = new_row_elem(o, key, 4 * ch + 1, dim);
-            v.z = new_row_elem(o, key, 4 * ch + 2, dim);
-            v.w = new_row_elem(o, key, 4 * ch + 3, dim);
-            if (write_row && ch < rchunks) *reinterpret_cast<float4*>(row + 4 * ch) = v;
-            if (ch < uchunks) {
-              // pulled row = w[dim] (+ two zero CVM columns for a new row), zero padding
-              float4 u;
-              u.x = 4 * ch + 0 < dim ? v.x : 0.f;
-              u.y = 4 * ch + 1 < dim ? v.y : 0.f;
-              u.z = 4 * ch + 2 < dim ? v.z : 0.f;
-              u.w = 4 * ch + 3 < dim ? v.w : 0.f;
-              *reinterpret_cast<float4*>(dst + 4 * ch) = u;
-            }
-          }
-        } else {
-          float show = 0.f, click = 0.f;
-          if (t.use_cvm && o.kind == kAdaGrad) { show = row[dim + 1]; click = row[dim + 2]; }
-          // up to four 16-byte loads in flight per lane (G >= ceil(uchunks / 4)), then the stores
-          float4 buf[4];
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const int ch = gl + k * G;
-            if (ch < uchunks) buf[k] = *reinterpret_cast<const float4*>(row + 4 * ch);   // stride >= ustride by layout
-          }
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const int ch = gl + k * G;
-            if (ch >= uchunks) continue;
-            float4 v = buf[k];
-            if (4 * ch + 4 > dim) {
-              float e[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-              for (int kk = 0; kk < 4; ++kk) {
-                int idx = 4 * ch + kk;
-                if (idx >= dim) {
-                  float x = 0.f;
-                  if (t.use_cvm && o.kind == kAdaGrad) {
-                    if (idx == dim) x = show;
-                    else if (idx == dim + 1) x = logf(click + 1.f) - logf(show + 1.f);
-                  }
-                  e[kk] = x;
-                }
-              }
-              v = make_float4(e[0], e[1], e[2], e[3]);
-            }
-            *reinterpret_cast<float4*>(dst + 4 * ch) = v;
-          }
-        }
+        pull_return_row(a, epoch, need_ou, s * capo + j, __ldcg(&src[j]), c.U[s] + ((size_t)R * capo + j) * ustride, gl, G);
       }
     }
   }
@@ -468,6 +507,16 @@ done:
 // =======================================================================================
 namespace {
 
+// The row updates run at 1024 threads per SM with a dozen memory operations per element group; IEEE division and
+// square root (software sequences of 10-20 instructions each) then cost as much issue time as the memory
+// round trips.  The approximate forms are good to 2 ulp, far inside the parity tolerance with the CPU restatement.
+__device__ __forceinline__ float fast_sqrt(float x) {
+  float y;
+  asm("sqrt.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float fast_div(float a, float b) { return __fdividef(a, b); }
+
 // One optimizer step on one row by a group of G lanes.  `g` points at the gradient (dim floats), bshow / bclick
 // are the batch's show and click counts of the sign.   Math as in the reference's Sparse*Value::Apply.
 // VEC: dim is a multiple of 4, every lane works on float4 chunks.
@@ -488,7 +537,7 @@ __device__ __forceinline__ void apply_row(const SparseOptParams& o, float* row, 
       ss += x1.x * x1.x + x1.y * x1.y + x1.z * x1.z + x1.w * x1.w;
       for (int off = G >> 1; off > 0; off >>= 1) ss += __shfl_xor_sync(gmask, ss, off);
       const float g2 = g2old + ss / (float)dim;
-      const float scale = o.lr / (o.eps + sqrtf(g2));
+      const float scale = fast_div(o.lr, o.eps + fast_sqrt(g2));
       if (c0 < nch) {
         w0.x -= scale * x0.x; w0.y -= scale * x0.y; w0.z -= scale * x0.z; w0.w -= scale * x0.w;
         *reinterpret_cast<float4*>(row + 4 * c0) = w0;
@@ -546,7 +595,7 @@ __device__ __forceinline__ void apply_row(const SparseOptParams& o, float* row, 
         float4 w = *reinterpret_cast<float4*>(row + 4 * ch);
 #define TN_SADAM(cmp) \
         mm.cmp = o.beta1 * mm.cmp + c1 * x.cmp; vv.cmp = o.beta2 * vv.cmp + c2 * x.cmp * x.cmp; \
-        w.cmp -= o.lr * mm.cmp / (o.eps + sqrtf(vv.cmp));
+        w.cmp -= fast_div(o.lr * mm.cmp, o.eps + fast_sqrt(vv.cmp));
         TN_SADAM(x) TN_SADAM(y) TN_SADAM(z) TN_SADAM(w)
 #undef TN_SADAM
         *reinterpret_cast<float4*>(m + 4 * ch) = mm;
@@ -775,8 +824,15 @@ cudaError_t launch_sparse_pull(const PullArgs& args, int work_items, cudaStream_
   int grid = (work_items + kThreads - 1) / kThreads;
   if (grid < 1) grid = 1;
   if (grid > grid_max[dev]) grid = grid_max[dev];
+  const size_t smem = (size_t)args.tile_rows * args.c.ustride * sizeof(float) * (kThreads / 32);
+  static bool attr_set[64] = {false};
+  if (smem > 48 * 1024 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute((const void*)sparse_pull_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
   void* params[] = {(void*)&args};
-  return cudaLaunchCooperativeKernel((const void*)sparse_pull_fused_kernel, dim3(grid), dim3(kThreads), params, 0, stream);
+  return cudaLaunchCooperativeKernel((const void*)sparse_pull_fused_kernel, dim3(grid), dim3(kThreads), params, smem, stream);
 }
 
 // `max_ctas` > 0 caps the grid below the SM count, leaving whole SMs to a kernel running on another stream.

@@ -74,6 +74,7 @@ struct PullArgs {
   int label_mod;
   int training;           // count show/click and prepare the push bookkeeping
   int lanes;              // lanes per row in the row-copy phase
+  int tile_rows;          // > 0: rows per shared-memory tile of the staged row return (multi-GPU); capo is a multiple of it
 };
 
 struct PushArgs {

@@ -192,7 +192,7 @@ class GpuSparseLink:
         if W == 1:
             capo = round_up(self.max_unique + 4, 4)
         else:
-            capo = round_up(int(math.ceil(self.max_unique / W * config.owner_segment_slack)) + 64, 4)
+            capo = round_up(int(math.ceil(self.max_unique / W * config.owner_segment_slack)) + 64, 32)   # whole row tiles
         self.capo = capo
         n_seg = W * capo
         multi = W > 1
