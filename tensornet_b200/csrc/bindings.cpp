@@ -482,15 +482,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   });
   m.def("deepfm_head_loss", [](at::Tensor H, int NH, c10::optional<at::Tensor> L, at::Tensor fm, at::Tensor w, at::Tensor label,
                                at::Tensor dH, c10::optional<at::Tensor> dL, at::Tensor dfm, at::Tensor gw, at::Tensor sums,
-                               c10::optional<at::Tensor> pred, at::Tensor loss_out) {
+                               c10::optional<at::Tensor> pred, at::Tensor loss_out, at::Tensor scratch) {
     c10::cuda::CUDAGuard guard(H.device());
+    TORCH_CHECK(scratch.numel() >= 2 && scratch.scalar_type() == at::kFloat, "deepfm_head_loss: scratch must be two fp32 words (zero between calls)");
     const int NL = L ? (int)L->size(1) : 0;
     TORCH_CHECK(w.numel() == NH + NL + 2, "deepfm_head_loss: weight must be [NH + NL + 2]");
     const char* err = tn::launch_deepfm_head_loss(H.data_ptr(), (int)H.stride(0), NH, L ? ptr_of<float>(*L) : nullptr, NL,
                                                   ptr_of<float>(fm), ptr_of<float>(w), ptr_of<float>(label), (int)H.size(0),
                                                   dH.data_ptr(), dL ? ptr_of<float>(*dL) : nullptr, ptr_of<float>(dfm),
                                                   ptr_of<float>(gw), ptr_of<float>(sums), pred ? ptr_of<float>(*pred) : nullptr,
-                                                  ptr_of<float>(loss_out), cur_stream());
+                                                  ptr_of<float>(loss_out), ptr_of<float>(scratch), cur_stream());
     if (err) throw std::runtime_error(err);
   });
   m.def("unique_assign", [](at::Tensor ids, c10::optional<at::Tensor> labels, at::Tensor dd_keys, at::Tensor dd_vals, at::Tensor uniq,

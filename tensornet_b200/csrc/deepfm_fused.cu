@@ -30,6 +30,7 @@ __global__ void deepfm_input_fwd_kernel(const float* __restrict__ U, int ustride
                                         int D, const float* __restrict__ dense, int Dd, int ld_dense,
                                         __nv_bfloat16* __restrict__ X0, int ld, float* __restrict__ fm, int lin_col,
                                         float* __restrict__ Lout) {
+  pdl_sync();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   const int nwarps = (gridDim.x * blockDim.x) >> 5;
   const int dq = D >> 2, nch = S * dq;
@@ -37,15 +38,31 @@ __global__ void deepfm_input_fwd_kernel(const float* __restrict__ U, int ustride
     __nv_bfloat16* xrow = X0 + (size_t)b * ld;
     float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
     float sq = 0.f;
-    for (int c = lane; c < nch; c += 32) {
-      const int f = c / dq, dc = c - f * dq;
-      const int v = __ldg(inverse + (size_t)f * B + b);
-      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (v >= 0) x = ldcg_f4(U + (size_t)v * ustride + 4 * dc);
-      s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
-      sq += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
-      __nv_bfloat162 lo = __floats2bfloat162_rn(x.x, x.y), hi = __floats2bfloat162_rn(x.z, x.w);
-      *reinterpret_cast<uint2*>(xrow + 4 * c) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    // batches of 4 x 32 chunks: first all row indices, then all row gathers, then the arithmetic, so that a
+    // warp has four independent loads in flight at each of the two dependent steps
+    for (int c0 = 0; c0 < nch; c0 += 128) {
+      int v[4];
+      float4 x[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int c = c0 + 32 * k + lane;
+        v[k] = c < nch ? __ldg(inverse + (size_t)(c / dq) * B + b) : -1;
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int c = c0 + 32 * k + lane;
+        x[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (v[k] >= 0) x[k] = ldcg_f4(U + (size_t)v[k] * ustride + 4 * (c % dq));
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int c = c0 + 32 * k + lane;
+        if (c >= nch) continue;
+        s.x += x[k].x; s.y += x[k].y; s.z += x[k].z; s.w += x[k].w;
+        sq += x[k].x * x[k].x + x[k].y * x[k].y + x[k].z * x[k].z + x[k].w * x[k].w;
+        __nv_bfloat162 lo = __floats2bfloat162_rn(x[k].x, x[k].y), hi = __floats2bfloat162_rn(x[k].z, x[k].w);
+        *reinterpret_cast<uint2*>(xrow + 4 * c) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+      }
     }
     for (int o = 16; o >= dq; o >>= 1) {
       s.x += __shfl_xor_sync(0xffffffffu, s.x, o); s.y += __shfl_xor_sync(0xffffffffu, s.y, o);
@@ -73,6 +90,7 @@ __global__ void deepfm_input_fwd_kernel(const float* __restrict__ U, int ustride
 __global__ void deepfm_input_bwd_kernel(const float* __restrict__ U, int ustride, const int* __restrict__ inverse, int B, int S,
                                         int D, const __nv_bfloat16* __restrict__ dX0, int ld, const float* __restrict__ gfm,
                                         float* __restrict__ gU, int gstride, int lin_col, const float* __restrict__ dL) {
+  pdl_sync();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   const int nwarps = (gridDim.x * blockDim.x) >> 5;
   const int dq = D >> 2, nch = S * dq;
@@ -80,32 +98,69 @@ __global__ void deepfm_input_bwd_kernel(const float* __restrict__ U, int ustride
     const __nv_bfloat16* grow = dX0 + (size_t)b * ld;
     const float gf = gfm[b];
     float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int c = lane; c < nch; c += 32) {
-      const int f = c / dq, dc = c - f * dq;
-      const int v = __ldg(inverse + (size_t)f * B + b);
-      if (v >= 0) {
-        const float4 x = ldcg_f4(U + (size_t)v * ustride + 4 * dc);
-        s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
+    if (nch <= 128) {
+      // the usual case: the example's rows stay in registers between the field sum and the gradient
+      int v[4];
+      float4 x[4];
+      uint2 raw[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int c = 32 * k + lane;
+        v[k] = c < nch ? __ldg(inverse + (size_t)(c / dq) * B + b) : -1;
+        raw[k] = c < nch ? *reinterpret_cast<const uint2*>(grow + 4 * c) : make_uint2(0u, 0u);
       }
-    }
-    for (int o = 16; o >= dq; o >>= 1) {
-      s.x += __shfl_xor_sync(0xffffffffu, s.x, o); s.y += __shfl_xor_sync(0xffffffffu, s.y, o);
-      s.z += __shfl_xor_sync(0xffffffffu, s.z, o); s.w += __shfl_xor_sync(0xffffffffu, s.w, o);
-    }
-    for (int c = lane; c < nch; c += 32) {
-      const int f = c / dq, dc = c - f * dq;
-      const int v = __ldg(inverse + (size_t)f * B + b);
-      if (v < 0) continue;
-      const float4 x = ldcg_f4(U + (size_t)v * ustride + 4 * dc);
-      const uint2 raw = *reinterpret_cast<const uint2*>(grow + 4 * c);
-      const float2 g01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-      const float2 g23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-      float4 g;
-      g.x = g01.x + gf * (s.x - x.x);
-      g.y = g01.y + gf * (s.y - x.y);
-      g.z = g23.x + gf * (s.z - x.z);
-      g.w = g23.y + gf * (s.w - x.w);
-      red_add_f32x4(gU + (size_t)v * gstride + 4 * dc, g);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int c = 32 * k + lane;
+        x[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (v[k] >= 0) x[k] = ldcg_f4(U + (size_t)v[k] * ustride + 4 * (c % dq));
+        s.x += x[k].x; s.y += x[k].y; s.z += x[k].z; s.w += x[k].w;
+      }
+      for (int o = 16; o >= dq; o >>= 1) {
+        s.x += __shfl_xor_sync(0xffffffffu, s.x, o); s.y += __shfl_xor_sync(0xffffffffu, s.y, o);
+        s.z += __shfl_xor_sync(0xffffffffu, s.z, o); s.w += __shfl_xor_sync(0xffffffffu, s.w, o);
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int c = 32 * k + lane;
+        if (v[k] < 0) continue;
+        const float2 g01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[k].x));
+        const float2 g23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[k].y));
+        float4 g;
+        g.x = g01.x + gf * (s.x - x[k].x);
+        g.y = g01.y + gf * (s.y - x[k].y);
+        g.z = g23.x + gf * (s.z - x[k].z);
+        g.w = g23.y + gf * (s.w - x[k].w);
+        red_add_f32x4(gU + (size_t)v[k] * gstride + 4 * (c % dq), g);
+      }
+    } else {
+      for (int c = lane; c < nch; c += 32) {
+        const int f = c / dq, dc = c - f * dq;
+        const int v = __ldg(inverse + (size_t)f * B + b);
+        if (v >= 0) {
+          const float4 x = ldcg_f4(U + (size_t)v * ustride + 4 * dc);
+          s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
+        }
+      }
+      for (int o = 16; o >= dq; o >>= 1) {
+        s.x += __shfl_xor_sync(0xffffffffu, s.x, o); s.y += __shfl_xor_sync(0xffffffffu, s.y, o);
+        s.z += __shfl_xor_sync(0xffffffffu, s.z, o); s.w += __shfl_xor_sync(0xffffffffu, s.w, o);
+      }
+      for (int c = lane; c < nch; c += 32) {
+        const int f = c / dq, dc = c - f * dq;
+        const int v = __ldg(inverse + (size_t)f * B + b);
+        if (v < 0) continue;
+        const float4 x = ldcg_f4(U + (size_t)v * ustride + 4 * dc);
+        const uint2 raw = *reinterpret_cast<const uint2*>(grow + 4 * c);
+        const float2 g01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 g23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        float4 g;
+        g.x = g01.x + gf * (s.x - x.x);
+        g.y = g01.y + gf * (s.y - x.y);
+        g.z = g23.x + gf * (s.z - x.z);
+        g.w = g23.y + gf * (s.w - x.w);
+        red_add_f32x4(gU + (size_t)v * gstride + 4 * dc, g);
+      }
     }
     if (lin_col >= 0) {
       for (int f = lane; f < S; f += 32) {
@@ -123,7 +178,8 @@ __global__ void deepfm_head_loss_kernel(const __nv_bfloat16* __restrict__ H, int
                                         const float* __restrict__ fm, const float* __restrict__ w, const float* __restrict__ label,
                                         int B, __nv_bfloat16* __restrict__ dH, float* __restrict__ dL, float* __restrict__ dfm,
                                         float* __restrict__ gw, float* __restrict__ sums, float* __restrict__ pred,
-                                        float* __restrict__ loss_out) {
+                                        float* __restrict__ loss_out, float* __restrict__ scratch) {
+  pdl_sync();
   extern __shared__ float s_gw[];   // [NH + NL + 2]
   const int NW = NH + NL + 2;
   for (int k = threadIdx.x; k < NW; k += blockDim.x) s_gw[k] = 0.f;
@@ -197,13 +253,24 @@ __global__ void deepfm_head_loss_kernel(const __nv_bfloat16* __restrict__ H, int
     atomicAdd(&s_gw[NH + NL + 1], accb);
     const float l = ls * invB;
     atomicAdd(&sums[0], l);
-    atomicAdd(loss_out, l);
+    atomicAdd(&scratch[0], l);
     atomicAdd(&sums[1], ys);
     atomicAdd(&sums[2], ps);
   }
   if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&sums[3], (float)B);
   __syncthreads();
   for (int k = threadIdx.x; k < NW; k += blockDim.x) atomicAdd(gw + k, s_gw[k]);
+  // The loss is summed in a persistent scratch word that is zero between launches; the last block to finish
+  // moves the total into `loss_out` and re-arms the scratch, so the caller never has to clear anything.
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned prev = atomicAdd(reinterpret_cast<unsigned*>(scratch) + 1, 1u);
+    if (prev == gridDim.x - 1) {
+      __threadfence();
+      *loss_out = atomicExch(&scratch[0], 0.f);
+      reinterpret_cast<unsigned*>(scratch)[1] = 0u;
+    }
+  }
 }
 
 }  // namespace
@@ -214,29 +281,29 @@ const char* launch_deepfm_input_fwd(const float* U, int ustride, const int* inve
   if ((D & 3) || dq < 1 || dq > 32 || (dq & (dq - 1))) return "deepfm_input: embedding dim must be 4 * 2^k, at most 128";
   if (ld < S * D + Dd + 1 || (ld & 3)) return "deepfm_input: operand row too short";
   int blocks = (B + 7) / 8; if (blocks > 148 * 8) blocks = 148 * 8; if (blocks < 1) blocks = 1;
-  deepfm_input_fwd_kernel<<<blocks, 256, 0, st>>>(U, ustride, inverse, B, S, D, dense, Dd, ld_dense,
-                                                  reinterpret_cast<__nv_bfloat16*>(X0), ld, fm, lin_col, Lout);
-  return nullptr;
+  cudaError_t e = launch_pdl(deepfm_input_fwd_kernel, dim3(blocks), dim3(256), 0, st, U, ustride, inverse, B, S, D, dense, Dd, ld_dense,
+                             reinterpret_cast<__nv_bfloat16*>(X0), ld, fm, lin_col, Lout);
+  return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
 const char* launch_deepfm_input_bwd(const float* U, int ustride, const int* inverse, int B, int S, int D, const void* dX0, int ld,
                                     const float* gfm, float* gU, int gstride, int lin_col, const float* dL, cudaStream_t st) {
   const int dq = D >> 2;
   if ((D & 3) || dq < 1 || dq > 32 || (dq & (dq - 1))) return "deepfm_input: embedding dim must be 4 * 2^k, at most 128";
   int blocks = (B + 7) / 8; if (blocks > 148 * 8) blocks = 148 * 8; if (blocks < 1) blocks = 1;
-  deepfm_input_bwd_kernel<<<blocks, 256, 0, st>>>(U, ustride, inverse, B, S, D, reinterpret_cast<const __nv_bfloat16*>(dX0), ld, gfm,
-                                                  gU, gstride, lin_col, dL);
-  return nullptr;
+  cudaError_t e = launch_pdl(deepfm_input_bwd_kernel, dim3(blocks), dim3(256), 0, st, U, ustride, inverse, B, S, D,
+                             reinterpret_cast<const __nv_bfloat16*>(dX0), ld, gfm, gU, gstride, lin_col, dL);
+  return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
 const char* launch_deepfm_head_loss(const void* H, int ldh, int NH, const float* L, int NL, const float* fm, const float* w,
                                     const float* label, int B, void* dH, float* dL, float* dfm, float* gw, float* sums, float* pred,
-                                    float* loss_out, cudaStream_t st) {
+                                    float* loss_out, float* scratch, cudaStream_t st) {
   if (ldh > 64 * kHeadPairs || (ldh & 1)) return "deepfm_head: hidden width must be even and at most 512 columns";
   if (NL > 32) return "deepfm_head: at most 32 linear inputs";
-  int blocks = (B + 7) / 8; if (blocks > 148 * 2) blocks = 148 * 2; if (blocks < 1) blocks = 1;
-  deepfm_head_loss_kernel<<<blocks, 256, (NH + NL + 2) * sizeof(float), st>>>(
-      reinterpret_cast<const __nv_bfloat16*>(H), ldh, NH, L, NL, fm, w, label, B, reinterpret_cast<__nv_bfloat16*>(dH), dL, dfm, gw,
-      sums, pred, loss_out);
-  return nullptr;
+  int blocks = (B + 7) / 8; if (blocks > 148 * 4) blocks = 148 * 4; if (blocks < 1) blocks = 1;   // 2 rows per warp at B = 8192
+  cudaError_t e = launch_pdl(deepfm_head_loss_kernel, dim3(blocks), dim3(256), (NH + NL + 2) * sizeof(float), st,
+                             reinterpret_cast<const __nv_bfloat16*>(H), ldh, NH, L, NL, fm, w, label, B,
+                             reinterpret_cast<__nv_bfloat16*>(dH), dL, dfm, gw, sums, pred, loss_out, scratch);
+  return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
 
 }  // namespace tn

@@ -24,6 +24,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 // E: [B, F, D] (row stride ld).  One warp per example; lane d handles component d (D <= 32)
 // or strides over D.
 __global__ void fm_fwd_kernel(const float* __restrict__ E, int ld, int B, int F, int D, float* __restrict__ out) {
+  pdl_sync();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   const int nwarps = (gridDim.x * blockDim.x) >> 5;
   for (int b = warp; b < B; b += nwarps) {
@@ -41,6 +42,7 @@ __global__ void fm_fwd_kernel(const float* __restrict__ E, int ld, int B, int F,
 // gE[b,f,d] = gout[b] * (sum_f E[b,:,d] - E[b,f,d])
 __global__ void fm_bwd_kernel(const float* __restrict__ E, int ld, int B, int F, int D, const float* __restrict__ gout,
                               float* __restrict__ gE, int gld, int accumulate) {
+  pdl_sync();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   const int nwarps = (gridDim.x * blockDim.x) >> 5;
   for (int b = warp; b < B; b += nwarps) {
@@ -62,6 +64,7 @@ __global__ void fm_bwd_kernel(const float* __restrict__ E, int ld, int B, int F,
 // always sees the same d-chunk (l mod D/4), so per-lane partial sums are combined with xor-shuffles
 // over the lanes that share it.
 __global__ void fm_fwd_vec_kernel(const float* __restrict__ E, int ld, int B, int F, int D, float* __restrict__ out) {
+  pdl_sync();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   const int nwarps = (gridDim.x * blockDim.x) >> 5;
   const int dq = D >> 2, nch = F * dq;
@@ -85,6 +88,7 @@ __global__ void fm_fwd_vec_kernel(const float* __restrict__ E, int ld, int B, in
 }
 __global__ void fm_bwd_vec_kernel(const float* __restrict__ E, int ld, int B, int F, int D, const float* __restrict__ gout,
                                   float* __restrict__ gE, int gld, int accumulate) {
+  pdl_sync();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   const int nwarps = (gridDim.x * blockDim.x) >> 5;
   const int dq = D >> 2, nch = F * dq;
@@ -130,6 +134,7 @@ __device__ __forceinline__ float concat_src(const ConcatArgs& a, int b, int c) {
 }
 // one thread = 8 consecutive output columns = one 16-byte store (ld_out is a multiple of 8)
 __global__ void concat_cast_kernel(const ConcatArgs a) {
+  pdl_sync();
   const int cpr = a.ld_out >> 3;
   const long long total = (long long)a.B * cpr;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -146,6 +151,7 @@ __global__ void concat_cast_kernel(const ConcatArgs a) {
 }
 // reverse: bf16 [B, ld_out] -> pieces (each piece written with its own ld); 8 columns per thread
 __global__ void split_cast_kernel(const ConcatArgs a) {
+  pdl_sync();
   const int cpr = a.ld_out >> 3;
   const long long total = (long long)a.B * cpr;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -176,6 +182,7 @@ __global__ void split_cast_kernel(const ConcatArgs a) {
 // y[b] = sum_k Z[b,k] * w[k]   (Z bf16 [B, ld], w fp32 [K]; the bias rides on Z's ones column)
 __global__ void gemv_fwd_kernel(const __nv_bfloat16* __restrict__ Z, int ld, int B, int K, const float* __restrict__ w,
                                 float* __restrict__ y) {
+  pdl_sync();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   const int nwarps = (gridDim.x * blockDim.x) >> 5;
   for (int b = warp; b < B; b += nwarps) {
@@ -190,6 +197,7 @@ __global__ void gemv_fwd_kernel(const __nv_bfloat16* __restrict__ Z, int ld, int
 __global__ void gemv_bwd_kernel(const __nv_bfloat16* __restrict__ Z, int ld, int B, int K, const float* __restrict__ w,
                                 const float* __restrict__ dy, __nv_bfloat16* __restrict__ dZ, float* __restrict__ gw,
                                 int relu_cols) {
+  pdl_sync();
   extern __shared__ float s_gw[];   // [K]
   for (int k = threadIdx.x; k < K; k += blockDim.x) s_gw[k] = 0.f;
   __syncthreads();
@@ -219,6 +227,7 @@ __global__ void gemv_bwd_kernel(const __nv_bfloat16* __restrict__ Z, int ld, int
 __global__ void gemv_bwd_rows_kernel(const __nv_bfloat16* __restrict__ Z, int ld, int B, int K, const float* __restrict__ w,
                                      const float* __restrict__ dy, __nv_bfloat16* __restrict__ dZ, float* __restrict__ gw,
                                      int relu_cols) {
+  pdl_sync();
   constexpr int kPairs = 8;
   extern __shared__ float s_gw[];   // [ld]
   for (int k = threadIdx.x; k < ld; k += blockDim.x) s_gw[k] = 0.f;
@@ -266,6 +275,7 @@ __global__ void gemv_bwd_rows_kernel(const __nv_bfloat16* __restrict__ Z, int ld
 // sums[0] += loss_sum/B, sums[1] += sum(y), sums[2] += sum(pred), sums[3] += B
 __global__ void bce_kernel(const float* __restrict__ logit, const float* __restrict__ label, int B, float* __restrict__ pred,
                            float* __restrict__ dlogit, float grad_scale, float* __restrict__ sums) {
+  pdl_sync();
   float ls = 0.f, ys = 0.f, ps = 0.f;
   for (int b = blockIdx.x * blockDim.x + threadIdx.x; b < B; b += gridDim.x * blockDim.x) {
     const float l = logit[b], y = label[b];
@@ -289,6 +299,7 @@ __global__ void bce_kernel(const float* __restrict__ logit, const float* __restr
 // ---- DCN-v1 cross layer: y = x0 * (xl . w) + b + xl ---------------------------------------------
 __global__ void cross_v1_fwd_kernel(const float* __restrict__ x0, const float* __restrict__ xl, const float* __restrict__ w,
                                     const float* __restrict__ bias, int B, int D, float* __restrict__ y, float* __restrict__ dot) {
+  pdl_sync();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   const int nwarps = (gridDim.x * blockDim.x) >> 5;
   for (int b = warp; b < B; b += nwarps) {
@@ -304,6 +315,7 @@ __global__ void cross_v1_fwd_kernel(const float* __restrict__ x0, const float* _
 __global__ void cross_v1_bwd_kernel(const float* __restrict__ x0, const float* __restrict__ xl, const float* __restrict__ w,
                                     const float* __restrict__ dot, const float* __restrict__ gy, int B, int D,
                                     float* __restrict__ gx0, float* __restrict__ gxl, float* __restrict__ gw, float* __restrict__ gb) {
+  pdl_sync();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   const int nwarps = (gridDim.x * blockDim.x) >> 5;
   for (int b = warp; b < B; b += nwarps) {
@@ -323,6 +335,7 @@ __global__ void cross_v1_bwd_kernel(const float* __restrict__ x0, const float* _
 
 // g[i] = y[i] > 0 ? g[i] : 0   (bf16, 8 elements per thread)
 __global__ void relu_mask_kernel(uint4* __restrict__ g, const uint4* __restrict__ y, long long n8) {
+  pdl_sync();
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
     uint4 gv = g[i]; const uint4 yv = y[i];
     __nv_bfloat16* gp = reinterpret_cast<__nv_bfloat16*>(&gv);
@@ -347,51 +360,51 @@ static bool fm_vec_ok(const void* p, int ld, int D) {
   return (D & 3) == 0 && dq >= 1 && dq <= 32 && (dq & (dq - 1)) == 0 && (ld & 3) == 0 && (reinterpret_cast<uintptr_t>(p) & 15) == 0;
 }
 void launch_fm_fwd(const float* E, int ld, int B, int F, int D, float* out, cudaStream_t st) {
-  if (fm_vec_ok(E, ld, D)) { fm_fwd_vec_kernel<<<blocks_for(B, 8), 256, 0, st>>>(E, ld, B, F, D, out); return; }
-  fm_fwd_kernel<<<blocks_for(B, 8), 256, 0, st>>>(E, ld, B, F, D, out);
+  if (fm_vec_ok(E, ld, D)) { launch_pdl(fm_fwd_vec_kernel, dim3(blocks_for(B, 8)), dim3(256), 0, st, E, ld, B, F, D, out); return; }
+  launch_pdl(fm_fwd_kernel, dim3(blocks_for(B, 8)), dim3(256), 0, st, E, ld, B, F, D, out);
 }
 void launch_fm_bwd(const float* E, int ld, int B, int F, int D, const float* gout, float* gE, int gld, int accumulate, cudaStream_t st) {
   if (fm_vec_ok(E, ld, D) && fm_vec_ok(gE, gld, D)) {
-    fm_bwd_vec_kernel<<<blocks_for(B, 8), 256, 0, st>>>(E, ld, B, F, D, gout, gE, gld, accumulate);
+    launch_pdl(fm_bwd_vec_kernel, dim3(blocks_for(B, 8)), dim3(256), 0, st, E, ld, B, F, D, gout, gE, gld, accumulate);
     return;
   }
-  fm_bwd_kernel<<<blocks_for(B, 8), 256, 0, st>>>(E, ld, B, F, D, gout, gE, gld, accumulate);
+  launch_pdl(fm_bwd_kernel, dim3(blocks_for(B, 8)), dim3(256), 0, st, E, ld, B, F, D, gout, gE, gld, accumulate);
 }
 void launch_concat_cast(const ConcatArgs& a, cudaStream_t st) {
-  concat_cast_kernel<<<blocks_for((long long)a.B * (a.ld_out >> 3), 256), 256, 0, st>>>(a);
+  launch_pdl(concat_cast_kernel, dim3(blocks_for((long long)a.B * (a.ld_out >> 3), 256)), dim3(256), 0, st, a);
 }
 void launch_split_cast(const ConcatArgs& a, cudaStream_t st) {
-  split_cast_kernel<<<blocks_for((long long)a.B * (a.ld_out >> 3), 256), 256, 0, st>>>(a);
+  launch_pdl(split_cast_kernel, dim3(blocks_for((long long)a.B * (a.ld_out >> 3), 256)), dim3(256), 0, st, a);
 }
 void launch_gemv_fwd(const void* Z, int ld, int B, int K, const float* w, float* y, cudaStream_t st) {
-  gemv_fwd_kernel<<<blocks_for(B, 8), 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(Z), ld, B, K, w, y);
+  launch_pdl(gemv_fwd_kernel, dim3(blocks_for(B, 8)), dim3(256), 0, st, reinterpret_cast<const __nv_bfloat16*>(Z), ld, B, K, w, y);
 }
 void launch_gemv_bwd(const void* Z, int ld, int B, int K, const float* w, const float* dy, void* dZ, float* gw, int relu_cols,
                      cudaStream_t st) {
   if (ld <= 512 && (ld & 1) == 0) {
     int nb = (B + 7) / 8; if (nb > 148 * 2) nb = 148 * 2; if (nb < 1) nb = 1;
-    gemv_bwd_rows_kernel<<<nb, 256, ld * sizeof(float), st>>>(reinterpret_cast<const __nv_bfloat16*>(Z), ld, B, K, w, dy,
+    launch_pdl(gemv_bwd_rows_kernel, dim3(nb), dim3(256), ld * sizeof(float), st, reinterpret_cast<const __nv_bfloat16*>(Z), ld, B, K, w, dy,
                                                              reinterpret_cast<__nv_bfloat16*>(dZ), gw, relu_cols);
     return;
   }
   int blocks = B / 32; if (blocks < 1) blocks = 1; if (blocks > 296) blocks = 296;
-  gemv_bwd_kernel<<<blocks, 256, K * sizeof(float), st>>>(reinterpret_cast<const __nv_bfloat16*>(Z), ld, B, K, w, dy,
+  launch_pdl(gemv_bwd_kernel, dim3(blocks), dim3(256), K * sizeof(float), st, reinterpret_cast<const __nv_bfloat16*>(Z), ld, B, K, w, dy,
                                                           reinterpret_cast<__nv_bfloat16*>(dZ), gw, relu_cols);
 }
 void launch_bce(const float* logit, const float* label, int B, float* pred, float* dlogit, float grad_scale, float* sums,
                 cudaStream_t st) {
-  bce_kernel<<<blocks_for(B, 256), 256, 0, st>>>(logit, label, B, pred, dlogit, grad_scale, sums);
+  launch_pdl(bce_kernel, dim3(blocks_for(B, 256)), dim3(256), 0, st, logit, label, B, pred, dlogit, grad_scale, sums);
 }
 void launch_relu_mask(void* g, const void* y, long long n, cudaStream_t st) {
-  relu_mask_kernel<<<blocks_for(n / 8, 256), 256, 0, st>>>(reinterpret_cast<uint4*>(g), reinterpret_cast<const uint4*>(y), n / 8);
+  launch_pdl(relu_mask_kernel, dim3(blocks_for(n / 8, 256)), dim3(256), 0, st, reinterpret_cast<uint4*>(g), reinterpret_cast<const uint4*>(y), n / 8);
 }
 void launch_cross_v1_fwd(const float* x0, const float* xl, const float* w, const float* bias, int B, int D, float* y, float* dot,
                          cudaStream_t st) {
-  cross_v1_fwd_kernel<<<blocks_for(B, 8), 256, 0, st>>>(x0, xl, w, bias, B, D, y, dot);
+  launch_pdl(cross_v1_fwd_kernel, dim3(blocks_for(B, 8)), dim3(256), 0, st, x0, xl, w, bias, B, D, y, dot);
 }
 void launch_cross_v1_bwd(const float* x0, const float* xl, const float* w, const float* dot, const float* gy, int B, int D,
                          float* gx0, float* gxl, float* gw, float* gb, cudaStream_t st) {
-  cross_v1_bwd_kernel<<<blocks_for(B, 8), 256, 0, st>>>(x0, xl, w, dot, gy, B, D, gx0, gxl, gw, gb);
+  launch_pdl(cross_v1_bwd_kernel, dim3(blocks_for(B, 8)), dim3(256), 0, st, x0, xl, w, dot, gy, B, D, gx0, gxl, gw, gb);
 }
 
 }  // namespace tn

@@ -21,6 +21,7 @@
 #include <cuda_runtime.h>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 #include "gemm_tcgen05.h"
@@ -167,6 +168,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = s_tmem;
+  // Programmatic dependent launch: everything above (barrier init, TMEM allocation, descriptor prefetch) touches
+  // no tensor data and may overlap the tail of the kernel launched before this one; from here on the previous
+  // kernel's results are needed.  The kernel launched after this one may start its own set-up right away.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (prof && threadIdx.x == 0) prof[1] = globaltimer_ns();
 
   if (warp == 0) {
@@ -565,11 +571,27 @@ const char* gemm_bf16(const GemmDesc& d, cudaStream_t stream) {
     cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
     attr_set = true;
   }
-  if (smem4 <= 200 * 1024)
-    gemm_bf16_tcgen05_kernel<4><<<grid, kGemmThreads, smem4, stream>>>(tmA, tmB, p);
-  else
-    gemm_bf16_tcgen05_kernel<3><<<grid, kGemmThreads, smem3, stream>>>(tmA, tmB, p);
-  cudaError_t e = cudaGetLastError();
+  // launched as a programmatic dependent of whatever precedes it in the stream (plain serialisation when the
+  // predecessor is not a kernel or the attribute is switched off)
+  static const bool use_pdl = []() { const char* e = getenv("TN_PDL"); return e == nullptr || atoi(e) != 0; }();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = use_pdl ? 1 : 0;
+  cudaError_t e;
+  if (smem4 <= 200 * 1024) {
+    cfg.dynamicSmemBytes = smem4;
+    e = cudaLaunchKernelEx(&cfg, gemm_bf16_tcgen05_kernel<4>, tmA, tmB, p);
+  } else {
+    cfg.dynamicSmemBytes = smem3;
+    e = cudaLaunchKernelEx(&cfg, gemm_bf16_tcgen05_kernel<3>, tmA, tmB, p);
+  }
+  if (e == cudaSuccess) e = cudaGetLastError();
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
 

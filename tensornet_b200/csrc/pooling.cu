@@ -22,6 +22,7 @@ __device__ __forceinline__ float bag_scale(int combiner, int len) {
 __global__ void pool_fwd_kernel(const float* __restrict__ U, int ustride, const int* __restrict__ inverse,
                                 const int* __restrict__ offsets, int B, int S, int pd, int combiner,
                                 float* __restrict__ out, int out_ld, int G) {
+  pdl_sync();
   const int lane = threadIdx.x % G;
   const int gid = (blockIdx.x * blockDim.x + threadIdx.x) / G;
   const int ngroups = (gridDim.x * blockDim.x) / G;
@@ -47,6 +48,7 @@ __global__ void pool_fwd_kernel(const float* __restrict__ U, int ustride, const 
 __global__ void pool_fwd_vec4_kernel(const float* __restrict__ U, int ustride, const int* __restrict__ inverse,
                                      const int* __restrict__ offsets, int B, int S, int pd, int combiner,
                                      float* __restrict__ out, int out_ld, int G) {
+  pdl_sync();
   const int lane = threadIdx.x % G;
   const int gid = (blockIdx.x * blockDim.x + threadIdx.x) / G;
   const int ngroups = (gridDim.x * blockDim.x) / G;
@@ -76,6 +78,7 @@ __global__ void pool_fwd_vec4_kernel(const float* __restrict__ U, int ustride, c
 __global__ void pool_bwd_vec4_kernel(float* __restrict__ gU, int gstride, const int* __restrict__ inverse,
                                      const int* __restrict__ offsets, int B, int S, int pd, int dim, int combiner,
                                      const float* __restrict__ gout, int gout_ld, int G) {
+  pdl_sync();
   const int lane = threadIdx.x % G;
   const int gid = (blockIdx.x * blockDim.x + threadIdx.x) / G;
   const int ngroups = (gridDim.x * blockDim.x) / G;
@@ -100,6 +103,7 @@ __global__ void pool_bwd_vec4_kernel(float* __restrict__ gU, int gstride, const 
 __global__ void pool_bwd_kernel(float* __restrict__ gU, int gstride, const int* __restrict__ inverse,
                                 const int* __restrict__ offsets, int B, int S, int pd, int dim, int combiner,
                                 const float* __restrict__ gout, int gout_ld, int G) {
+  pdl_sync();
   const int lane = threadIdx.x % G;
   const int gid = (blockIdx.x * blockDim.x + threadIdx.x) / G;
   const int ngroups = (gridDim.x * blockDim.x) / G;
@@ -125,6 +129,7 @@ __global__ void pool_bwd_kernel(float* __restrict__ gU, int gstride, const int* 
 __global__ void seq_fwd_kernel(const float* __restrict__ U, int ustride, const int* __restrict__ inverse,
                                const int* __restrict__ offsets, int B, int T, int pd, float* __restrict__ out,
                                int* __restrict__ lengths, int G) {
+  pdl_sync();
   const int lane = threadIdx.x % G;
   const int gid = (blockIdx.x * blockDim.x + threadIdx.x) / G;
   const int ngroups = (gridDim.x * blockDim.x) / G;
@@ -142,6 +147,7 @@ __global__ void seq_fwd_kernel(const float* __restrict__ U, int ustride, const i
 __global__ void seq_bwd_kernel(float* __restrict__ gU, int gstride, const int* __restrict__ inverse,
                                const int* __restrict__ offsets, int B, int T, int pd, int dim,
                                const float* __restrict__ gout, int G) {
+  pdl_sync();
   const int lane = threadIdx.x % G;
   const int gid = (blockIdx.x * blockDim.x + threadIdx.x) / G;
   const int ngroups = (gridDim.x * blockDim.x) / G;
@@ -169,36 +175,36 @@ void launch_pool_fwd(const float* U, int ustride, const int* inverse, const int*
                      int combiner, float* out, int out_ld, cudaStream_t st) {
   if ((pd & 3) == 0 && (out_ld & 3) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
     int G = lanes_for_width(pd);
-    pool_fwd_vec4_kernel<<<grid_for((long long)B * S, G, 256), 256, 0, st>>>(U, ustride, inverse, offsets, B, S, pd,
+    launch_pdl(pool_fwd_vec4_kernel, dim3(grid_for((long long)B * S, G, 256)), dim3(256), 0, st, U, ustride, inverse, offsets, B, S, pd,
                                                                                combiner, out, out_ld, G);
     return;
   }
   int G = pd >= 32 ? 32 : (pd >= 16 ? 16 : (pd >= 8 ? 8 : (pd >= 4 ? 4 : (pd >= 2 ? 2 : 1))));
-  pool_fwd_kernel<<<grid_for((long long)B * S, G, 256), 256, 0, st>>>(U, ustride, inverse, offsets, B, S, pd, combiner,
+  launch_pdl(pool_fwd_kernel, dim3(grid_for((long long)B * S, G, 256)), dim3(256), 0, st, U, ustride, inverse, offsets, B, S, pd, combiner,
                                                                         out, out_ld, G);
 }
 void launch_pool_bwd(float* gU, int gstride, const int* inverse, const int* offsets, int B, int S, int pd, int dim,
                      int combiner, const float* gout, int gout_ld, cudaStream_t st) {
   if ((pd & 3) == 0 && (dim & 3) == 0 && (gout_ld & 3) == 0 && (reinterpret_cast<uintptr_t>(gout) & 15) == 0) {
     int G = lanes_for_width(dim);
-    pool_bwd_vec4_kernel<<<grid_for((long long)B * S, G, 256), 256, 0, st>>>(gU, gstride, inverse, offsets, B, S, pd, dim,
+    launch_pdl(pool_bwd_vec4_kernel, dim3(grid_for((long long)B * S, G, 256)), dim3(256), 0, st, gU, gstride, inverse, offsets, B, S, pd, dim,
                                                                                combiner, gout, gout_ld, G);
     return;
   }
   int G = dim >= 32 ? 32 : (dim >= 16 ? 16 : (dim >= 8 ? 8 : (dim >= 4 ? 4 : (dim >= 2 ? 2 : 1))));
-  pool_bwd_kernel<<<grid_for((long long)B * S, G, 256), 256, 0, st>>>(gU, gstride, inverse, offsets, B, S, pd, dim,
+  launch_pdl(pool_bwd_kernel, dim3(grid_for((long long)B * S, G, 256)), dim3(256), 0, st, gU, gstride, inverse, offsets, B, S, pd, dim,
                                                                         combiner, gout, gout_ld, G);
 }
 void launch_seq_fwd(const float* U, int ustride, const int* inverse, const int* offsets, int B, int T, int pd,
                     float* out, int* lengths, cudaStream_t st) {
   int G = pd >= 32 ? 32 : (pd >= 16 ? 16 : (pd >= 8 ? 8 : (pd >= 4 ? 4 : (pd >= 2 ? 2 : 1))));
-  seq_fwd_kernel<<<grid_for((long long)B * T, G, 256), 256, 0, st>>>(U, ustride, inverse, offsets, B, T, pd, out,
+  launch_pdl(seq_fwd_kernel, dim3(grid_for((long long)B * T, G, 256)), dim3(256), 0, st, U, ustride, inverse, offsets, B, T, pd, out,
                                                                        lengths, G);
 }
 void launch_seq_bwd(float* gU, int gstride, const int* inverse, const int* offsets, int B, int T, int pd, int dim,
                     const float* gout, cudaStream_t st) {
   int G = dim >= 32 ? 32 : (dim >= 16 ? 16 : (dim >= 8 ? 8 : (dim >= 4 ? 4 : (dim >= 2 ? 2 : 1))));
-  seq_bwd_kernel<<<grid_for((long long)B * T, G, 256), 256, 0, st>>>(gU, gstride, inverse, offsets, B, T, pd, dim, gout, G);
+  launch_pdl(seq_bwd_kernel, dim3(grid_for((long long)B * T, G, 256)), dim3(256), 0, st, gU, gstride, inverse, offsets, B, T, pd, dim, gout, G);
 }
 
 }  // namespace tn

@@ -9,6 +9,7 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <cstdint>
+#include <cstdlib>
 #include "tn_hash.h"
 
 namespace tn {
@@ -169,6 +170,31 @@ __device__ __forceinline__ bool wait_flag_ge(const unsigned long long* flag, uns
   }
   set_status(status, kPeerWaitTimeout, phase, peer);
   return false;
+}
+
+// Programmatic dependent launch.  A kernel launched with `launch_pdl` may start while the kernel before it in
+// the stream is still draining; `pdl_sync()` is the point after which it may touch data (it returns once the
+// previous kernel has completed and its writes are visible) and also lets the next kernel in the stream start its
+// own ramp-up.  Both instructions are no-ops in a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_sync() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  static const bool use_pdl = []() { const char* e = getenv("TN_PDL"); return e == nullptr || atoi(e) != 0; }();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = use_pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 // Lanes-per-row for row-wise kernels: power of two >= ceil(width/4), at most 32.

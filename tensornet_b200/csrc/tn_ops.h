@@ -58,7 +58,7 @@ const char* launch_deepfm_input_bwd(const float* U, int ustride, const int* inve
                                     const float* gfm, float* gU, int gstride, int lin_col, const float* dL, cudaStream_t st);
 const char* launch_deepfm_head_loss(const void* H, int ldh, int NH, const float* L, int NL, const float* fm, const float* w,
                                     const float* label, int B, void* dH, float* dL, float* dfm, float* gw, float* sums, float* pred,
-                                    float* loss_out, cudaStream_t st);
+                                    float* loss_out, float* scratch, cudaStream_t st);
 
 // unique.cu
 void launch_unique_assign(const long long* ids, int n, const float* labels, unsigned long long* dd_keys, int* dd_vals,

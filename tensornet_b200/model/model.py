@@ -161,6 +161,7 @@ class Model(nn.Module):
         self.loss_fn = loss
         self.metrics = list(metrics or [])
         self._sums = torch.zeros(4, dtype=torch.float32, device=rt.device)
+        self._unit_grad = torch.ones((), dtype=torch.float32, device=rt.device)
         self._use_graph = rt.on_gpu and (core.config.cuda_graph if cuda_graph is None else cuda_graph)
         self._graph_warmup = graph_warmup
         if optimizer is not None:
@@ -207,8 +208,11 @@ class Model(nn.Module):
         if loss is None:
             logits = self(features)
             loss, _ = self._loss(logits, labels)
-        loss.backward()
         rt = core.runtime()
+        if rt.on_gpu and loss.dim() == 0 and loss.dtype == torch.float32:
+            loss.backward(self._unit_grad)      # a resident 1.0: autograd would otherwise launch a fill kernel for it
+        else:
+            loss.backward()
         if rt.on_gpu and rt.world == 1 and self.optimizer is not None:
             # one GPU: the sparse push and the dense update touch disjoint state and neither waits on other
             # CTAs, so they run side by side

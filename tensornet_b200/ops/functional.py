@@ -454,6 +454,17 @@ def deepfm_input(anchor, link, ids, B, S, dense=None, training=True, emb_dim=Non
     return x0, fm, (lin if lin_col >= 0 else None)
 
 
+_HEAD_SCRATCH = {}
+
+
+def _head_scratch(dev) -> torch.Tensor:
+    """Two persistent words per device (partial loss, finished-block count) that the head kernel leaves at zero."""
+    key = (dev.type, dev.index)
+    if key not in _HEAD_SCRATCH:
+        _HEAD_SCRATCH[key] = torch.zeros(2, dtype=torch.float32, device=dev)
+    return _HEAD_SCRATCH[key]
+
+
 class _DeepFMHeadLoss(torch.autograd.Function):
     @staticmethod
     def forward(ctx, h, lin, fm, w, label, sums, n_hidden):
@@ -462,10 +473,11 @@ class _DeepFMHeadLoss(torch.autograd.Function):
         dh = torch.empty_like(h)
         dl = torch.empty_like(lin) if lin is not None else None
         dfm = torch.empty(B, dtype=torch.float32, device=dev)
-        loss = torch.zeros((), dtype=torch.float32, device=dev)
+        loss = torch.empty((), dtype=torch.float32, device=dev)     # written (not accumulated) by the last block
         pred = torch.empty(B, dtype=torch.float32, device=dev)
         _ext().deepfm_head_loss(h, n_hidden, None if lin is None else lin.contiguous(), fm.contiguous().view(-1), w,
-                                label.contiguous().view(-1).float(), dh, dl, dfm, _grad_buffer(w), sums, pred, loss)
+                                label.contiguous().view(-1).float(), dh, dl, dfm, _grad_buffer(w), sums, pred, loss,
+                                _head_scratch(dev))
         ctx.save_for_backward(dh, dl if dl is not None else dfm, dfm)
         ctx.has_lin = lin is not None
         ctx.mark_non_differentiable(pred)
