@@ -1,7 +1,7 @@
 """Small, self-contained launches of the hot kernels, for timing with CUDA events and for capturing
 with Nsight Compute (one GPU, a few launches, a few hundred MB on the device).
 
-    python benchmarks/kernel_cases.py gemm_fwd|gemm_dgrad|gemm_wgrad|sparse|deepfm|dense  [--iters N]
+    python benchmarks/kernel_cases.py gemm_fwd|gemm_dgrad|gemm_wgrad|gemm_big|sparse|deepfm|dense  [--iters N]
 
 Each case prints the per-launch device time (CUDA events around N back-to-back launches after warm-up,
 inputs larger than L2 for the sparse cases) and the algorithmic bytes / FLOPs so a roofline fraction
@@ -44,7 +44,7 @@ def peaks():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm_fwd", "gemm_dgrad", "gemm_wgrad", "sparse", "deepfm", "dense"])
+    ap.add_argument("case", choices=["gemm_fwd", "gemm_dgrad", "gemm_wgrad", "gemm_big", "sparse", "deepfm", "dense"])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--batch", type=int, default=8192)
     a = ap.parse_args()
@@ -54,7 +54,22 @@ def main():
     pk = peaks()
     tag = "of fallback" if pk.get("fallback") else "of measured"
     out = {"case": a.case}
-    if a.case.startswith("gemm"):
+    if a.case == "gemm_big":
+        # one DCN-v2 cross layer: [8192, 6416] x [6416, 6416]^T, the three operand layouts, against the library GEMM
+        M, N, K = a.batch, 6416, 6416
+        A = torch.randn(M, K, device=dev).bfloat16()
+        Bw = (torch.randn(N, K, device=dev) * 0.02).bfloat16()
+        C = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        dW = torch.zeros(N, K, device=dev)
+        flops = 2.0 * M * N * K
+        res = {}
+        res["fwd_kk"] = timed(lambda: ext.gemm(A, Bw, C, M, N, K, K, K, N, False, False, False, False, None, None, None, None, 0, -1, N, 1, 0, st), a.iters)
+        res["dgrad_k_mn"] = timed(lambda: ext.gemm(A, Bw, C, M, K, N, K, K, N, False, True, False, False, None, None, None, None, 0, -1, K, 1, 0, st), a.iters)
+        res["wgrad_mn_mn"] = timed(lambda: ext.gemm(C, A, dW, N, K, M, N, K, K, True, True, True, False, None, None, None, None, 0, -1, K, 0, 0, st), a.iters)
+        res["library_matmul"] = timed(lambda: torch.matmul(A, Bw.t(), out=C), a.iters)
+        out.update(shape=[M, N, K], us=res, tflops={k: flops / v / 1e6 for k, v in res.items()},
+                   frac_of_bf16_sustained={k: flops / v / 1e6 / pk.get("bf16_tflops_sustained", pk["bf16_tflops"]) for k, v in res.items()}, peak=tag)
+    elif a.case.startswith("gemm"):
         M, N, K = a.batch, 400, 430
         A = torch.randn(M, 432, device=dev).bfloat16()
         Bw = (torch.randn(N, 432, device=dev) * 0.1).bfloat16()
