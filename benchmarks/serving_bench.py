@@ -4,6 +4,10 @@ Reports p50 / p99 latency (host wall clock per request batch incl. H2D of the id
 probabilities) and request batches / s.
 
     python benchmarks/serving_bench.py --requests 500
+    torchrun --nproc-per-node 8 --master-addr 127.0.0.1 benchmarks/serving_bench.py --sharded     # dictionary sharded over the GPUs
+
+With ``--sharded`` every rank serves its own request batches while the lookups cross NVLink inside the fused pull
+kernel (read-only); the reported rate is the sum over ranks and the latencies are those of the slowest rank.
 """
 from __future__ import annotations
 
@@ -20,7 +24,7 @@ import torch
 
 import tensornet_b200 as tn
 from tensornet_b200.layers import DenseHead, MLP
-from tensornet_b200.serving import EmbeddingDictionary, InferenceEngine
+from tensornet_b200.serving import EmbeddingDictionary, InferenceEngine, ShardedInferenceEngine
 
 
 def main():
@@ -30,16 +34,21 @@ def main():
     ap.add_argument("--batch", type=int, default=512)
     ap.add_argument("--dict-rows", type=int, default=5_000_000)
     ap.add_argument("--requests", type=int, default=300)
+    ap.add_argument("--sharded", action="store_true", help="shard the dictionary over all ranks (sign %% world)")
     a = ap.parse_args()
     tn.core.init()
     rt = tn.core.runtime()
     rng = np.random.default_rng(0)
     signs = np.unique(rng.integers(1, 2 ** 40, a.dict_rows, dtype=np.int64).astype(np.uint64))
-    d = EmbeddingDictionary(signs, rng.standard_normal((len(signs), a.dim)).astype(np.float32) * 0.05)
+    weights = rng.standard_normal((len(signs), a.dim)).astype(np.float32) * 0.05
     torch.manual_seed(0)
     mlp = MLP(a.slots * a.dim, [1024, 512, 256]).to(rt.device)
     head = DenseHead(256).to(rt.device)
-    eng = InferenceEngine(d, mlp, head, a.slots)
+    if a.sharded:
+        eng = ShardedInferenceEngine.from_dictionary(signs, weights, mlp, head, a.slots, a.slots * a.batch)
+        rng = np.random.default_rng(100 + rt.rank)           # every rank serves its own requests
+    else:
+        eng = InferenceEngine(EmbeddingDictionary(signs, weights), mlp, head, a.slots)
     s = 1.1
     def req():
         u = rng.random((a.slots, a.batch))
@@ -57,6 +66,17 @@ def main():
         lat.append((time.perf_counter() - t0) * 1e3)
     total = time.perf_counter() - t_all
     lat = np.array(lat)
+    rate = a.requests / total
+    if rt.world > 1:
+        stats = rt.all_gather_object((float(np.percentile(lat, 50)), float(np.percentile(lat, 99)), rate))
+        if rt.rank == 0:
+            print(json.dumps({"metric": "sharded serving latency, batch %d x %d slots per rank" % (a.batch, a.slots), "world": rt.world,
+                              "p50_ms": max(x[0] for x in stats), "p99_ms": max(x[1] for x in stats),
+                              "request_batches_per_s": sum(x[2] for x in stats), "examples_per_s": sum(x[2] for x in stats) * a.batch,
+                              "dict_rows": int(len(signs))}), flush=True)
+        rt.barrier()
+        tn.core.shutdown()
+        return
     print(json.dumps({"metric": "serving latency, batch %d x %d slots" % (a.batch, a.slots), "p50_ms": float(np.percentile(lat, 50)),
                       "p99_ms": float(np.percentile(lat, 99)), "request_batches_per_s": a.requests / total,
                       "examples_per_s": a.requests * a.batch / total, "dict_rows": int(len(signs)), "device": str(rt.device),

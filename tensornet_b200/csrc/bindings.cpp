@@ -141,7 +141,7 @@ struct SparseCtx {
   void set_opt(py::dict opt) { o = opt_from_dict(opt); }
   void set_table(py::dict table) { keep["table"] = table; t = table_from_dict(table); }
 
-  void pull(at::Tensor ids, at::Tensor inverse, c10::optional<at::Tensor> labels, int label_mod, bool training) {
+  void pull(at::Tensor ids, at::Tensor inverse, c10::optional<at::Tensor> labels, int label_mod, bool training, bool lookup_only) {
     TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous(), "ids: contiguous int64 CUDA tensor");
     TORCH_CHECK(inverse.scalar_type() == at::kInt && inverse.numel() >= ids.numel(), "inverse: int32, one per id");
     c10::cuda::CUDAGuard guard(ids.device());
@@ -153,6 +153,8 @@ struct SparseCtx {
     a.labels = labels.has_value() ? ptr_of<const float>(*labels) : nullptr;
     a.label_mod = label_mod;
     a.training = training ? 1 : 0;
+    a.lookup_only = lookup_only ? 1 : 0;
+    TORCH_CHECK(!(training && lookup_only), "a training pull creates rows; lookup_only is for inference");
     a.lanes = pull_lanes;
     a.tile_rows = tile_rows;
     long long work = (long long)a.n_ids * (pull_lanes > 4 ? pull_lanes / 2 : 2);
@@ -321,7 +323,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def(py::init<py::dict, py::dict, py::dict>())
       .def("set_opt", &SparseCtx::set_opt)
       .def("set_table", &SparseCtx::set_table)
-      .def("pull", &SparseCtx::pull)
+      .def("pull", &SparseCtx::pull, py::arg("ids"), py::arg("inverse"), py::arg("labels"), py::arg("label_mod"), py::arg("training"),
+           py::arg("lookup_only") = false)
       .def("push", &SparseCtx::push, py::arg("work_hint"), py::arg("max_ctas") = 0);
   py::class_<BnCtx>(m, "BnCtx")
       .def(py::init<py::dict>())

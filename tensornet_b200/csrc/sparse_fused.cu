@@ -339,6 +339,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_pull_fused_kernel(const __
         for (unsigned probes = 0; probes <= t.cap_mask; ++probes) {
           unsigned long long k = __ldcg(&t.keys[h]);
           if (k == kEmptyKey) {
+            if (a.lookup_only) { placed = true; break; }        // read-only table (serving): an unknown sign pulls zeros
             k = atomicCAS(&t.keys[h], kEmptyKey, key);
             if (k == kEmptyKey) { is_new = true; hnew = h; placed = true; break; }
           }

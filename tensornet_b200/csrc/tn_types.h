@@ -73,6 +73,7 @@ struct PullArgs {
   const float* labels;    // optional click labels: labels[i % label_mod] (label_mod > 0) or labels[i]
   int label_mod;
   int training;           // count show/click and prepare the push bookkeeping
+  int lookup_only;        // never insert: signs the table does not hold come back as zero rows (serving)
   int lanes;              // lanes per row in the row-copy phase
   int tile_rows;          // > 0: rows per shared-memory tile of the staged row return (multi-GPU); capo is a multiple of it
 };

@@ -238,14 +238,15 @@ class GpuSparseLink:
             rt.barrier()
 
     def pull(self, ids: torch.Tensor, labels: Optional[torch.Tensor] = None, label_mod: int = 0, training: bool = True,
-             inverse: Optional[torch.Tensor] = None) -> torch.Tensor:
+             inverse: Optional[torch.Tensor] = None, lookup_only: bool = False) -> torch.Tensor:
         """Dedup ``ids``, fetch (creating on miss) their rows from the owning GPUs into ``self.U`` and
-        return ``inverse``: the row of ``self.U`` holding each id's embedding."""
+        return ``inverse``: the row of ``self.U`` holding each id's embedding.  ``lookup_only`` (inference)
+        never creates rows: signs no shard holds come back as zeros."""
         n = ids.numel()
         if inverse is None:
             inverse = torch.empty(n, dtype=torch.int32, device=self.dev)
         self._last_n_ids = n
-        self.ctx.pull(ids.reshape(-1), inverse, labels, int(label_mod), bool(training))
+        self.ctx.pull(ids.reshape(-1), inverse, labels, int(label_mod), bool(training), bool(lookup_only))
         return inverse
 
     def push(self):

@@ -7,6 +7,6 @@ sub-graph" (README.md:42-44): the dictionary is ``sign -> w[0..dim)`` cut out of
 (doc/tutorial/04-deploy-tf-graph-online.ipynb); its online demo fakes the lookup
 (examples/online_serving/main.cc:76-81).  Here the lookup is real.
 """
-from .engine import EmbeddingDictionary, InferenceEngine, export_sparse_dictionary
+from .engine import EmbeddingDictionary, InferenceEngine, ShardedInferenceEngine, export_sparse_dictionary
 
-__all__ = ["EmbeddingDictionary", "InferenceEngine", "export_sparse_dictionary"]
+__all__ = ["EmbeddingDictionary", "InferenceEngine", "ShardedInferenceEngine", "export_sparse_dictionary"]

@@ -144,3 +144,83 @@ class InferenceEngine:
         static_ids.copy_(ids.reshape(-1), non_blocking=True)
         g.replay()
         return out
+
+
+class ShardedInferenceEngine:
+    """Serving with the dictionary sharded over all GPUs of the job (``sign % world`` decides the owner), for
+    dictionaries too large for one GPU's memory.  The reference's exported dictionary "may approach TB"
+    (doc/tutorial/05-export-sparse-feature-embedding.ipynb:156) and its demo fakes the lookup
+    (examples/online_serving/main.cc:76-81); here every rank takes its own request batches and the lookups cross
+    NVLink inside the fused pull kernel running read-only (``lookup_only``: signs no shard holds pull zeros and
+    nothing is inserted).  Lookup, pooling, towers and sigmoid are captured in one CUDA graph per batch shape.
+
+    All ranks must call :meth:`infer` the same number of times with the same batch shape: the pull is collective.
+    With one GPU it behaves like :class:`InferenceEngine` over a training-format table."""
+
+    def __init__(self, table, mlp, head, n_slots: int, max_ids: int, combiner: str = "mean"):
+        from ..ops.embedding import COMBINERS
+
+        self.table, self.mlp, self.head, self.S = table, mlp, head, n_slots
+        self.combiner = COMBINERS[combiner]
+        self.link = table.link(max_ids)
+        self._graphs = {}
+        assert mlp.in_dim == n_slots * table.dim, "tower input width must equal slots * dim"
+
+    @classmethod
+    def from_dictionary(cls, signs: np.ndarray, weights: np.ndarray, mlp, head, n_slots: int, max_ids: int,
+                        combiner: str = "mean", rows_per_gpu: Optional[int] = None):
+        """Build the sharded table from a full ``sign -> embedding`` dictionary held on the host: every rank keeps
+        the signs it owns."""
+        from ..core.optimizers import Adam
+        from ..ops.sparse_table_gpu import GpuSparseTable, row_floats
+
+        rt = runtime()
+        signs = np.ascontiguousarray(signs, dtype=np.uint64)
+        mine = (signs % np.uint64(rt.world)) == np.uint64(rt.rank)
+        opt = Adam(learning_rate=0.0)
+        dim = int(weights.shape[1])
+        table = GpuSparseTable(opt, dim, rows=rows_per_gpu or max(1024, int(mine.sum()) + 1024))
+        rows = np.zeros((int(mine.sum()), row_floats(table.kind, dim)), dtype=np.float32)
+        rows[:, :dim] = weights[mine]
+        table.load_rows(signs[mine], rows)
+        return cls(table, mlp, head, n_slots, max_ids, combiner)
+
+    def _forward(self, ids, offsets, B):
+        ext = _build.cuda_ext()
+        lk = self.link
+        inverse = lk.pull(ids, None, 0, training=False, lookup_only=True)
+        pd = lk.pdim
+        pooled = torch.empty((B, self.S * pd), dtype=torch.float32, device=ids.device)
+        ext.pool_fwd(lk.U, lk.ustride, inverse, offsets, B, self.S, pd, self.combiner, pooled, self.S * pd)
+        x0 = F.concat_cast([pooled], ones=True)
+        logit = self.head(self.mlp(x0)).view(-1)
+        prob = torch.empty_like(logit)
+        ext.sigmoid(logit, prob)
+        return prob
+
+    @torch.no_grad()
+    def infer(self, ids: torch.Tensor, offsets: Optional[torch.Tensor] = None, use_graph: bool = True) -> torch.Tensor:
+        rt = runtime()
+        assert rt.on_gpu, "sharded serving runs on GPUs"
+        dev = rt.device
+        if offsets is not None or not use_graph:
+            B = ids.shape[1] if offsets is None else (offsets.numel() - 1) // self.S
+            return self._forward(ids.to(dev).reshape(-1), None if offsets is None else offsets.to(dev).int(), B)
+        B = int(ids.shape[1])
+        entry = self._graphs.get(B)
+        if entry is None:
+            static_ids = torch.empty((self.S * B,), dtype=torch.int64, device=dev)
+            static_ids.copy_(ids.reshape(-1), non_blocking=True)
+            for _ in range(2):
+                self._forward(static_ids, None, B)
+            torch.cuda.synchronize()
+            rt.check_status()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                out = self._forward(static_ids, None, B)
+            entry = (g, static_ids, out)
+            self._graphs[B] = entry
+        g, static_ids, out = entry
+        static_ids.copy_(ids.reshape(-1), non_blocking=True)
+        g.replay()
+        return out

@@ -118,3 +118,33 @@ def test_serving_engine_matches_training_forward(tn_gpu, status_ok):
     assert torch.allclose(got1, want, atol=1e-2) and torch.allclose(got2, want, atol=1e-2)
     unseen = eng.infer(ids * 0 + 999999937)    # signs missing from the dictionary contribute zeros
     assert torch.isfinite(unseen).all()
+
+
+def test_sharded_serving_matches_single_dictionary(tn_gpu, status_ok):
+    """The read-only pull (lookup_only) + pooling + towers gives the same probabilities as the single-GPU
+    dictionary engine, creates no rows for unknown signs, and replays from its CUDA graph."""
+    import numpy as np
+    from tensornet_b200.layers import DenseHead, MLP
+    from tensornet_b200.serving import EmbeddingDictionary, InferenceEngine, ShardedInferenceEngine
+
+    tn = tn_gpu
+    dev = tn.core.runtime().device
+    rng = np.random.default_rng(3)
+    S, D, B = 6, 8, 64
+    signs = np.unique(rng.integers(1, 2 ** 40, 5000, dtype=np.int64).astype(np.uint64))
+    weights = rng.standard_normal((len(signs), D)).astype(np.float32) * 0.3
+    torch.manual_seed(1)
+    mlp = MLP(S * D, [32, 16]).to(dev)
+    head = DenseHead(16).to(dev)
+    ref = InferenceEngine(EmbeddingDictionary(signs, weights), mlp, head, S, combiner="mean")
+    eng = ShardedInferenceEngine.from_dictionary(signs, weights, mlp, head, S, S * B, combiner="mean")
+    n0 = eng.table.n_rows
+    for k in range(3):
+        pick = signs[rng.integers(0, len(signs), (S, B))].view(np.int64)
+        unknown = rng.integers(2 ** 41, 2 ** 42, (S, B), dtype=np.int64)
+        ids = torch.from_numpy(np.where(rng.random((S, B)) < 0.8, pick, unknown))
+        a = ref.infer(ids).cpu()
+        b = eng.infer(ids).cpu()
+        assert torch.allclose(a, b, atol=2e-3), float((a - b).abs().max())
+    assert eng.table.n_rows == n0                      # nothing was inserted
+    assert B in eng._graphs
