@@ -28,12 +28,14 @@ class Config:
     #: head-room factor of one (sender, owner) segment over the even split unique/world
     owner_segment_slack: float = 1.3
     #: wall-time budget of every device-side wait, in seconds
-    wait_budget_s: float = 2.0
+    wait_budget_s: float = 5.0
     #: seed of the deterministic row initialiser
     seed: int = 0x7E50A
     #: use NVSwitch multicast (multimem) in the dense path when the mapping exists
     use_multimem: bool = True
     gate_first_gemm: bool = True   # multi-GPU: first MLP GEMM waits for the dense all-gather (no closing barrier)
+    #: pull returns rows through shared-memory tiles: -1 = only with several GPUs, 0 = never, 1 = always
+    staged_row_return: int = -1
     #: multi-GPU: run the dense step beside the sparse push (small dense arrays only); measured at 2 GPUs on the
     #: DeepFM step: 2 % slower than back to back (both kernels are latency-bound and lose CTAs), so off by default
     overlap_dense_push: bool = False
@@ -56,6 +58,7 @@ class Config:
         c.seed = _env("TN_SEED", c.seed, int)
         c.use_multimem = _env("TN_USE_MULTIMEM", c.use_multimem, bool)
         c.gate_first_gemm = _env("TN_GATE_FIRST_GEMM", c.gate_first_gemm, bool)
+        c.staged_row_return = _env("TN_STAGED_RETURN", c.staged_row_return, int)
         c.dense_small_grid = _env("TN_DENSE_SMALL_GRID", c.dense_small_grid, int)
         c.overlap_dense_push = _env("TN_OVERLAP_DENSE_PUSH", c.overlap_dense_push, bool)
         c.checkpoint_chunk_rows = _env("TN_CKPT_CHUNK_ROWS", c.checkpoint_chunk_rows, int)

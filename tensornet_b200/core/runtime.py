@@ -47,6 +47,7 @@ class Runtime:
         self.device = torch.device("cpu")
         self.on_gpu = False
         self.host_group = None      # gloo group: barriers, object exchange
+        self.peer_synced_pushes = 0  # multi-GPU sparse pushes launched so far (each one waits for all peers)
         self.device_group = None    # nccl group: symmetric memory rendezvous, baseline collectives
         self._status = None
         self._owns_pg = False

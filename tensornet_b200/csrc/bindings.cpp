@@ -76,7 +76,7 @@ struct SparseCtx {
   tn::TableView t{};
   tn::SparseOptParams o{};
   int pull_lanes = 1, push_lanes = 1;
-  int tile_rows = 0;   // staged row return of the multi-GPU pull (0 = rows go straight to the requester)
+  int tile_rows = 0;   // staged row return of the pull (0 = rows go straight to the requester's matrix)
   py::dict keep;   // keeps the tensors alive
 
   SparseCtx(py::dict table, py::dict comm, py::dict opt) {
@@ -128,7 +128,7 @@ struct SparseCtx {
     c.prof = comm.contains("prof") && !comm["prof"].is_none() ? ptr_of<unsigned long long>(comm["prof"].cast<at::Tensor>()) : nullptr;
     pull_lanes = tn::lanes_for_width_host((c.ustride + 3) / 4);   // each lane keeps up to four 16-byte chunks in flight
     push_lanes = tn::lanes_for_width_host(t.dim);
-    if (c.world > 1 && (!comm.contains("staged_return") || comm["staged_return"].cast<bool>())) {
+    if (!comm.contains("staged_return") || comm["staged_return"].cast<bool>()) {
       // rows per tile: whole 128-byte lines per tile, about 4 KiB of shared memory per warp at most
       int tr = 32;
       while (tr > 8 && tr * c.ustride * 4 > 4096) tr >>= 1;
@@ -212,7 +212,11 @@ struct DenseCtx {
     a.status = ptr_of<int>(d["status"].cast<at::Tensor>());
     a.wait_ns = d["wait_ns"].cast<uint64_t>();
   }
-  void step() { check(tn::launch_dense_step(a, cur_stream()), "dense step launch"); }
+  void step(bool skip_open) {
+    tn::DenseStepArgs b = a;
+    b.skip_open = skip_open ? 1 : 0;
+    check(tn::launch_dense_step(b, cur_stream()), "dense step launch");
+  }
   void set_gated(bool g) { a.gated = g ? 1 : 0; }
   void set_max_ctas(int n) { a.max_ctas = n; }
 };
@@ -334,7 +338,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("sync", &BnCtx::sync)
       .def("apply_fwd", &BnCtx::apply_fwd)
       .def("apply_bwd", &BnCtx::apply_bwd);
-  py::class_<DenseCtx>(m, "DenseCtx").def(py::init<py::dict>()).def("step", &DenseCtx::step).def("set_gated", &DenseCtx::set_gated).def("set_max_ctas", &DenseCtx::set_max_ctas);
+  py::class_<DenseCtx>(m, "DenseCtx").def(py::init<py::dict>()).def("step", &DenseCtx::step, py::arg("skip_open") = false).def("set_gated", &DenseCtx::set_gated).def("set_max_ctas", &DenseCtx::set_max_ctas);
   m.def("gemm", &gemm, py::arg("A"), py::arg("B"), py::arg("C"), py::arg("M"), py::arg("N"), py::arg("K"), py::arg("lda"),
         py::arg("ldb"), py::arg("ldc"), py::arg("a_mn"), py::arg("b_mn"), py::arg("accumulate"), py::arg("relu"), py::arg("bias"),
         py::arg("mask_aux"), py::arg("had_x0"), py::arg("had_xl"), py::arg("ld_aux"), py::arg("ones_col"), py::arg("n_store"),

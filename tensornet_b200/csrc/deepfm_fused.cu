@@ -299,7 +299,8 @@ const char* launch_deepfm_head_loss(const void* H, int ldh, int NH, const float*
                                     float* loss_out, float* scratch, cudaStream_t st) {
   if (ldh > 64 * kHeadPairs || (ldh & 1)) return "deepfm_head: hidden width must be even and at most 512 columns";
   if (NL > 32) return "deepfm_head: at most 32 linear inputs";
-  int blocks = (B + 7) / 8; if (blocks > 148 * 4) blocks = 148 * 4; if (blocks < 1) blocks = 1;   // 2 rows per warp at B = 8192
+  // two blocks per SM: every block ends with one global add per weight, and four per SM cost the step 10 us
+  int blocks = (B + 7) / 8; if (blocks > 148 * 2) blocks = 148 * 2; if (blocks < 1) blocks = 1;
   cudaError_t e = launch_pdl(deepfm_head_loss_kernel, dim3(blocks), dim3(256), (NH + NL + 2) * sizeof(float), st,
                              reinterpret_cast<const __nv_bfloat16*>(H), ldh, NH, L, NL, fm, w, label, B,
                              reinterpret_cast<__nv_bfloat16*>(dH), dL, dfm, gw, sums, pred, loss_out, scratch);

@@ -165,9 +165,13 @@ __global__ void __launch_bounds__(kDThreads) dense_fused_kernel(const __grid_con
   // large arrays are zeroed by their own GPU instead, once every peer has finished reading them.
   const bool zero_remote = !a.zero_local;
 
-  // all GPUs have finished writing their gradients (stream order on each GPU + this barrier)
-  peer_barrier(a, 0, epoch, 41);
-  if (!gs.sync(42, false)) goto done;
+  // all GPUs have finished writing their gradients: stream order on each GPU + this barrier.  The caller may skip
+  // it when a kernel that ran just before on this stream already waited for every peer to get past its backward
+  // pass (the multi-GPU sparse push does: a peer ships its gradient records only after its own backward).
+  if (!a.skip_open) {
+    peer_barrier(a, 0, epoch, 41);
+    if (!gs.sync(42, false)) goto done;
+  }
 
   for (long long base = lo4 + blockIdx.x * (long long)blockDim.x + threadIdx.x; base < hi4; base += nth * kDenseUnroll) {
     float4 g[kDenseUnroll];

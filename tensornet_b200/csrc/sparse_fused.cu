@@ -435,8 +435,8 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_pull_fused_kernel(const __
     if (a.tile_rows > 0) {
       // Staged return: a warp gathers TR consecutive rows of one requester into shared memory and then writes
       // the tile out as one contiguous run of full 128-byte lines (16 bytes per lane, 512 per instruction).
-      // Row-by-row stores of short rows (80 bytes for dim 16 + linear) reach the peer as partial lines and
-      // lose about a third of the NVLink write rate.
+      // Row-by-row stores of short rows (80 bytes for dim 16 + linear) reach a peer as partial lines and lose
+      // about a third of the NVLink write rate; the local case gains too (7 us instead of 10 for 144 K rows).
       extern __shared__ float4 s_tiles[];
       const int TR = a.tile_rows;
       const int rpp = 32 / G;                                   // rows gathered per pass

@@ -75,7 +75,7 @@ struct PullArgs {
   int training;           // count show/click and prepare the push bookkeeping
   int lookup_only;        // never insert: signs the table does not hold come back as zero rows (serving)
   int lanes;              // lanes per row in the row-copy phase
-  int tile_rows;          // > 0: rows per shared-memory tile of the staged row return (multi-GPU); capo is a multiple of it
+  int tile_rows;          // > 0: rows per shared-memory tile of the staged row return; capo is a multiple of it
 };
 
 struct PushArgs {
@@ -99,6 +99,7 @@ struct DenseStepArgs {
   long long chunk;      // elements owned per GPU (multiple of 4); n for world == 1
   int world, rank;
   float grad_scale;     // 1/world for the mean gradient
+  int skip_open;        // world > 1: this launch does not need the opening "gradients ready" barrier (see dense_fused.cu)
   int max_ctas;         // world > 1: cap on the cooperative grid (0 = fill the GPU); a small cap leaves SMs to a kernel on another stream
   int gated;            // world > 1: publish per-owner "chunk written" flags (row 2 of sig) instead of waiting in a closing barrier;
                         // the first kernel that reads the weights waits on them (GemmDesc::gate_flags)

@@ -232,9 +232,12 @@ class Model(nn.Module):
             self.backwards()
             main.wait_stream(side)
         else:
-            if self.optimizer is not None:
-                self.optimizer.step()
+            # several GPUs: push first.  A push kernel only completes after every peer has shipped its gradient
+            # records, i.e. after every peer's backward pass, so the dense kernel behind it needs no opening barrier.
+            before = rt.peer_synced_pushes
             self.backwards()
+            if self.optimizer is not None:
+                self.optimizer.step(peers_past_backward=rt.peer_synced_pushes > before)
         return loss.detach()
 
     def _to_device(self, obj):
@@ -292,6 +295,9 @@ class Model(nn.Module):
             self.optimizer.iterations = iters
             self.optimizer.table.step_count -= 1
         self._graph, self._graph_key = g, key
+        # Capture takes a different time on every rank; the first replay's kernels wait for their peers on the
+        # device with a finite budget, so line the ranks up on the host first.
+        core.runtime().barrier()
 
     def train_on_batch(self, x, y=None, return_dict: bool = False):
         with start_as_current_span("train_on_batch"):

@@ -124,12 +124,14 @@ class DenseTable:
             self.lr = float(lr)
             self.state[2] = self.lr
 
-    def step(self):
-        """Average the gradient over ranks, update the owned chunk, publish the new weights, zero the gradient."""
+    def step(self, peers_past_backward: bool = False):
+        """Average the gradient over ranks, update the owned chunk, publish the new weights, zero the gradient.
+        ``peers_past_backward``: a kernel launched earlier on this stream in this step has already waited for every
+        peer to finish its backward pass (the multi-GPU sparse push has), so the kernel skips its opening barrier."""
         rt = runtime()
         self.step_count += 1
         if rt.on_gpu:
-            self.ctx.step()
+            self.ctx.step(bool(peers_past_backward and self.world > 1))
             return
         with torch.no_grad():
             if self.world > 1:

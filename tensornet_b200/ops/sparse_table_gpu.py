@@ -190,7 +190,7 @@ class GpuSparseLink:
         W = table.world
         self.max_unique = int(max_unique)
         if W == 1:
-            capo = round_up(self.max_unique + 4, 4)
+            capo = round_up(self.max_unique + 4, 32)
         else:
             capo = round_up(int(math.ceil(self.max_unique / W * config.owner_segment_slack)) + 64, 32)   # whole row tiles
         self.capo = capo
@@ -228,7 +228,8 @@ class GpuSparseLink:
         self.cnts = loc["cnts"].view(n_seg, 2)       # (show, click) of the batch per distinct sign
         self.cnt_saved = loc["cnt_saved"]
         self.prof = loc["prof"]
-        self.comm = dict(world=W, rank=table.rank, capo=capo, gstride=self.gstride, ustride=self.ustride,
+        staged = multi if config.staged_row_return < 0 else bool(config.staged_row_return)
+        self.comm = dict(world=W, rank=table.rank, capo=capo, staged_return=staged, gstride=self.gstride, ustride=self.ustride,
                          inbox_ids=arena.ptrs("inbox_ids"), ginbox=arena.ptrs("ginbox"), cinbox=arena.ptrs("cinbox"), U=arena.ptrs("U"),
                          sig=arena.ptrs("sig"), epoch=table.epoch, status=rt.status, wait_ns=rt.wait_ns, **loc)
         self.ctx = table.ext.SparseCtx(table.table_dict(), self.comm, table._opt_dict())
@@ -252,6 +253,8 @@ class GpuSparseLink:
     def push(self):
         """Apply the accumulated unique-row gradients (``self.gU``) on the owning GPUs."""
         self.ctx.push(max(self._last_n_ids, 1), int(self.push_cta_cap))
+        if self.table.world > 1:
+            runtime().peer_synced_pushes += 1      # this kernel waited for every peer's gradient records
 
     def pull_phase_us(self):
         """Durations (microseconds) of the last pull's phases as seen by CTA 0:

@@ -35,11 +35,12 @@ class Optimizer:
     def _lr(self) -> float:
         return self.dense_opt.current_lr(self.iterations)
 
-    def step(self):
+    def step(self, peers_past_backward: bool = False):
         """One fused dense update: mean gradient over ranks -> optimizer on the owned chunk ->
-        new weights visible on every rank; gradients are re-zeroed."""
+        new weights visible on every rank; gradients are re-zeroed.  ``peers_past_backward``: see
+        :meth:`tensornet_b200.ops.dense_table.DenseTable.step`."""
         self.table.set_lr(self._lr())
-        self.table.step()
+        self.table.step(peers_past_backward)
         self.iterations += 1
 
     def apply_gradients(self, grads_and_vars=None):

@@ -49,3 +49,56 @@ def test_multi_gpu_over_plain_peer_loads(tmp_path):
     r = _run(2, str(tmp_path / "ipc.json"), {"TN_SYMM_BACKEND": "ipc", "NCCL_NVLS_ENABLE": "0"})
     assert r["replicas_identical"] and not r["multimem"] and r["bn_sync_ok"]
     assert r["losses"][-1] < 0.8 * r["losses"][0]
+
+
+@pytest.mark.timeout(300)
+def test_survivor_notices_departed_rank_before_its_next_launch(tmp_path):
+    """A rank leaves between steps with nothing in flight; the survivor learns of it on the host (short
+    process-group timeout on the pre-step barrier) and launches no kernel that would wait for the dead peer.
+    Plain peer loads only: no NVSwitch multicast mapping is bound while a rank dies."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    script = tmp_path / "leaver.py"
+    script.write_text('''
+import os, sys, time, torch
+import tensornet_b200 as tn
+tn.core.init()
+rt = tn.core.runtime()
+slots = [str(i) for i in range(1, 5)]
+B = 128
+model = tn.models.DeepFM(slots, slots, dnn_hidden_units=(32, 16), embedding_dim=8, dense_dim=3,
+                         sparse_opt=tn.core.Adam(learning_rate=1e-2, initial_scale=0.1), bucket_size=2 * B, table_rows=1 << 14)
+model.compile(optimizer=tn.optimizer.Optimizer(tn.core.Adam(learning_rate=1e-2)), cuda_graph=False)
+g = torch.Generator().manual_seed(rt.rank)
+def batch():
+    ids = torch.randint(0, 500, (len(slots), B), generator=g, dtype=torch.int64)
+    return {tn.data.PACKED_KEY: tn.data.PackedFeatures(slots, ids=ids), "dense": torch.randn(B, 3, generator=g)}, (torch.rand(B, generator=g) < 0.3).float()
+for _ in range(3):
+    tn.core.barrier()                      # pre-step health check on the host
+    f, y = batch()
+    model.train_on_batch(f, y)
+torch.cuda.synchronize()
+rt.check_status()
+tn.core.barrier()
+if rt.rank == 1:
+    os._exit(0)                            # between steps, none of its kernels or collectives in flight
+t0 = time.time()
+try:
+    tn.core.barrier()                      # the next step's health check
+    print("NOT DETECTED", flush=True)
+except Exception as e:
+    print("DETECTED after %.1fs: %s" % (time.time() - t0, type(e).__name__), flush=True)
+assert float(torch.ones(4, device=rt.device).sum()) == 4.0     # the survivor's context is intact
+print("CONTEXT OK", flush=True)
+os._exit(0)
+''')
+    port = _port()
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                   TN_PG_TIMEOUT_S="10", TN_WAIT_BUDGET_S="1.0", TN_SYMM_BACKEND="ipc", TN_USE_MULTIMEM="0", NCCL_NVLS_ENABLE="0",
+                   PYTHONPATH=ROOT)
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    out0, _ = procs[0].communicate(timeout=240)
+    procs[1].wait(timeout=60)
+    assert "DETECTED" in out0 and "NOT DETECTED" not in out0 and "CONTEXT OK" in out0, out0[-3000:]
