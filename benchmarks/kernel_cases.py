@@ -64,6 +64,7 @@ def main():
         flops = 2.0 * M * N * K
         res = {}
         res["fwd_kk"] = timed(lambda: ext.gemm(A, Bw, C, M, N, K, K, K, N, False, False, False, False, None, None, None, None, 0, -1, N, 1, 0, st), a.iters)
+        res["fwd_kk_two_accumulators"] = timed(lambda: ext.gemm(A, Bw, C, M, N, K, K, K, N, False, False, False, False, None, None, None, None, 0, -1, N, 1, 256, st, m_halves=2), a.iters)
         res["dgrad_k_mn"] = timed(lambda: ext.gemm(A, Bw, C, M, K, N, K, K, N, False, True, False, False, None, None, None, None, 0, -1, K, 1, 0, st), a.iters)
         res["wgrad_mn_mn"] = timed(lambda: ext.gemm(C, A, dW, N, K, M, N, K, K, True, True, True, False, None, None, None, None, 0, -1, K, 0, 0, st), a.iters)
         res["library_matmul"] = timed(lambda: torch.matmul(A, Bw.t(), out=C), a.iters)

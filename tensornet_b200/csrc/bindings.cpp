@@ -291,7 +291,7 @@ void gemm(at::Tensor A, at::Tensor B, at::Tensor C, int M, int N, int K, int lda
           bool accumulate, bool relu, c10::optional<at::Tensor> bias, c10::optional<at::Tensor> mask_aux,
           c10::optional<at::Tensor> had_x0, c10::optional<at::Tensor> had_xl, int ld_aux, int ones_col, int n_store,
           int split_k, int BN, at::Tensor status, c10::optional<at::Tensor> prof, int dbg, c10::optional<at::Tensor> gate_flags,
-          c10::optional<at::Tensor> gate_epoch, int gate_world, uint64_t gate_wait_ns) {
+          c10::optional<at::Tensor> gate_epoch, int gate_world, uint64_t gate_wait_ns, int m_halves, c10::optional<at::Tensor> aux_out) {
   TORCH_CHECK(A.is_cuda() && B.is_cuda() && C.is_cuda(), "gemm: CUDA tensors");
   TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16, "gemm: bf16 operands");
   c10::cuda::CUDAGuard guard(A.device());
@@ -309,6 +309,11 @@ void gemm(at::Tensor A, at::Tensor B, at::Tensor C, int M, int N, int K, int lda
   d.status = ptr_of<int>(status);
   d.prof = prof.has_value() ? ptr_of<unsigned long long>(*prof) : nullptr;
   d.dbg = dbg;
+  d.m_halves = m_halves;
+  if (aux_out.has_value()) {
+    TORCH_CHECK(aux_out->scalar_type() == at::kBFloat16 && aux_out->stride(0) == ld_aux, "gemm: aux_out must be bf16 with row stride ld_aux");
+    d.aux_out = aux_out->data_ptr();
+  }
   if (gate_flags.has_value()) {
     TORCH_CHECK(gate_epoch.has_value() && gate_world >= 1 && gate_world <= tn::kMaxWorld, "gemm: gate wants flags, epoch and a world size");
     d.gate_flags = ptr_of<const unsigned long long>(*gate_flags);
@@ -343,7 +348,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("ldb"), py::arg("ldc"), py::arg("a_mn"), py::arg("b_mn"), py::arg("accumulate"), py::arg("relu"), py::arg("bias"),
         py::arg("mask_aux"), py::arg("had_x0"), py::arg("had_xl"), py::arg("ld_aux"), py::arg("ones_col"), py::arg("n_store"),
         py::arg("split_k"), py::arg("BN"), py::arg("status"), py::arg("prof") = py::none(), py::arg("dbg") = 0,
-        py::arg("gate_flags") = py::none(), py::arg("gate_epoch") = py::none(), py::arg("gate_world") = 0, py::arg("gate_wait_ns") = 0);
+        py::arg("gate_flags") = py::none(), py::arg("gate_epoch") = py::none(), py::arg("gate_world") = 0, py::arg("gate_wait_ns") = 0,
+        py::arg("m_halves") = 0, py::arg("aux_out") = py::none());
   m.def("launch_count", []() { return g_launches.load(); });
 
   // ---- CUDA IPC peer memory (fallback transport for the symmetric heap) --------------------------
@@ -526,6 +532,18 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sigmoid", [](at::Tensor x, at::Tensor y) {
     c10::cuda::CUDAGuard guard(x.device());
     tn::launch_sigmoid(ptr_of<float>(x), ptr_of<float>(y), (int)x.numel(), cur_stream());
+  });
+  m.def("cross_v2_bwd_elem", [](at::Tensor g, at::Tensor u, at::Tensor x0, at::Tensor gx0, at::Tensor du, bool first) {
+    TORCH_CHECK(g.is_contiguous() && u.is_contiguous() && x0.is_contiguous() && gx0.is_contiguous() && du.is_contiguous(), "contiguous operands");
+    TORCH_CHECK(g.numel() % 8 == 0 && u.numel() == g.numel() && x0.numel() == g.numel() && gx0.numel() == g.numel() && du.numel() == g.numel(), "sizes");
+    TORCH_CHECK(g.scalar_type() == at::kBFloat16 && gx0.scalar_type() == at::kFloat, "g / u / x0 / du are bf16, gx0 is fp32");
+    c10::cuda::CUDAGuard guard(g.device());
+    tn::launch_cross_v2_bwd_elem(g.data_ptr(), u.data_ptr(), x0.data_ptr(), ptr_of<float>(gx0), du.data_ptr(), g.numel(), first ? 1 : 0, cur_stream());
+  });
+  m.def("cross_v2_bwd_final", [](at::Tensor gx0, at::Tensor g, at::Tensor out) {
+    TORCH_CHECK(gx0.is_contiguous() && g.is_contiguous() && out.is_contiguous() && g.numel() % 8 == 0 && gx0.numel() == g.numel() && out.numel() == g.numel(), "operands");
+    c10::cuda::CUDAGuard guard(g.device());
+    tn::launch_cross_v2_bwd_final(ptr_of<float>(gx0), g.data_ptr(), out.data_ptr(), g.numel(), cur_stream());
   });
   m.def("relu_mask", [](at::Tensor g, at::Tensor y) {
     c10::cuda::CUDAGuard guard(g.device());

@@ -346,6 +346,55 @@ __global__ void relu_mask_kernel(uint4* __restrict__ g, const uint4* __restrict_
   }
 }
 
+// DCN-v2 backward, elementwise part of one cross layer (y = x0 * u + x_l, u = W x_l + b), 8 elements per thread:
+//   gx0 += g * u   (fp32 accumulator over the layers)      du = g * x0   (bf16, input of the two GEMMs)
+// `first` writes gx0 instead of accumulating (no zero fill needed before the first layer).
+__global__ void cross_v2_bwd_elem_kernel(const uint4* __restrict__ g, const uint4* __restrict__ u, const uint4* __restrict__ x0,
+                                         float4* __restrict__ gx0, uint4* __restrict__ du, long long n8, int first) {
+  pdl_sync();
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    const uint4 gv = g[i], uv = u[i], xv = x0[i];
+    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gv);
+    const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&uv);
+    const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+    float4 a = first ? make_float4(0.f, 0.f, 0.f, 0.f) : gx0[2 * i], b = first ? a : gx0[2 * i + 1];
+    uint4 dv;
+    uint32_t* dp = reinterpret_cast<uint32_t*>(&dv);
+    float acc[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 gf = __bfloat1622float2(gp[k]), uf = __bfloat1622float2(up[k]), xf = __bfloat1622float2(xp[k]);
+      acc[2 * k] += gf.x * uf.x;
+      acc[2 * k + 1] += gf.y * uf.y;
+      __nv_bfloat162 d = __floats2bfloat162_rn(gf.x * xf.x, gf.y * xf.y);
+      dp[k] = *reinterpret_cast<uint32_t*>(&d);
+    }
+    gx0[2 * i] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    gx0[2 * i + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    du[i] = dv;
+  }
+}
+
+// out = bf16(gx0 + g): the gradient that reaches x0 through the residual chain joins the Hadamard terms.
+__global__ void cross_v2_bwd_final_kernel(const float4* __restrict__ gx0, const uint4* __restrict__ g, uint4* __restrict__ out, long long n8) {
+  pdl_sync();
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    const float4 a = gx0[2 * i], b = gx0[2 * i + 1];
+    const uint4 gv = g[i];
+    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gv);
+    const float acc[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    uint4 ov;
+    uint32_t* op = reinterpret_cast<uint32_t*>(&ov);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 gf = __bfloat1622float2(gp[k]);
+      __nv_bfloat162 d = __floats2bfloat162_rn(acc[2 * k] + gf.x, acc[2 * k + 1] + gf.y);
+      op[k] = *reinterpret_cast<uint32_t*>(&d);
+    }
+    out[i] = ov;
+  }
+}
+
 inline int blocks_for(long long work, int per_block) {
   long long b = (work + per_block - 1) / per_block;
   if (b < 1) b = 1;
@@ -397,6 +446,15 @@ void launch_bce(const float* logit, const float* label, int B, float* pred, floa
 }
 void launch_relu_mask(void* g, const void* y, long long n, cudaStream_t st) {
   launch_pdl(relu_mask_kernel, dim3(blocks_for(n / 8, 256)), dim3(256), 0, st, reinterpret_cast<uint4*>(g), reinterpret_cast<const uint4*>(y), n / 8);
+}
+void launch_cross_v2_bwd_elem(const void* g, const void* u, const void* x0, float* gx0, void* du, long long n, int first, cudaStream_t st) {
+  launch_pdl(cross_v2_bwd_elem_kernel, dim3(blocks_for(n / 8, 256)), dim3(256), 0, st, reinterpret_cast<const uint4*>(g),
+             reinterpret_cast<const uint4*>(u), reinterpret_cast<const uint4*>(x0), reinterpret_cast<float4*>(gx0), reinterpret_cast<uint4*>(du),
+             n / 8, first);
+}
+void launch_cross_v2_bwd_final(const float* gx0, const void* g, void* out, long long n, cudaStream_t st) {
+  launch_pdl(cross_v2_bwd_final_kernel, dim3(blocks_for(n / 8, 256)), dim3(256), 0, st, reinterpret_cast<const float4*>(gx0),
+             reinterpret_cast<const uint4*>(g), reinterpret_cast<uint4*>(out), n / 8);
 }
 void launch_cross_v1_fwd(const float* x0, const float* xl, const float* w, const float* bias, int B, int D, float* y, float* dot,
                          cudaStream_t st) {

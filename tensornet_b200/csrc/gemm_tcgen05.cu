@@ -120,7 +120,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int kStages>
+template <int kStages, int kHalves>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                          const GemmParams p) {
@@ -135,12 +135,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int BN = p.BN;
   const uint32_t b_bytes = (uint32_t)BN * kBK * 2;
+  // A CTA owns one or two 128-row accumulators that share every B tile: with two, the operand bytes per FLOP drop
+  // by a third (the 128 x 256 tile is bound by the ~120 GB/s at which one SM can ingest operands).
+  constexpr int halves = kHalves;
+  const uint32_t a_stage = (uint32_t)halves * kABytes;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t a_smem = base;
-  const uint32_t b_smem = base + kStages * kABytes;
+  const uint32_t b_smem = base + kStages * a_stage;
 
   const int n0 = blockIdx.x * BN;
-  const int m0 = blockIdx.y * kBM;
+  const int m0 = blockIdx.y * kBM * halves;
   const int kt_total = (p.K + kBK - 1) / kBK;
   const int kt0 = blockIdx.z * p.k_tiles_per_split;
   int nk = kt_total - kt0;
@@ -148,6 +152,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 
   uint32_t tmem_cols = 32;
   while ((int)tmem_cols < BN) tmem_cols <<= 1;
+  if (halves == 2) tmem_cols = 512;          // second accumulator at column 256
   unsigned long long* prof = (p.prof && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.prof : nullptr;
   if (prof && threadIdx.x == 0) prof[0] = globaltimer_ns();
 
@@ -199,15 +204,19 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         const uint32_t ph = (uint32_t)(i / kStages) & 1u;
         if (!mbar_wait(smem_u32(&s_empty[s]), ph ^ 1u, s_abort)) { *s_abort = 1; break; }
         const uint32_t full = smem_u32(&s_full[s]);
-        mbar_expect_tx(full, kABytes + b_bytes);
+        mbar_expect_tx(full, a_stage + b_bytes);
         const int kc = (kt0 + i) * kBK;
-        const uint32_t a_dst = a_smem + s * kABytes;
         const uint32_t b_dst = b_smem + s * b_bytes;
-        if (!p.a_mn) {
-          tma_load_2d(a_dst, &tmA, kc, m0, full);
-        } else {
-          tma_load_2d(a_dst, &tmA, m0, kc, full);
-          tma_load_2d(a_dst + 8192, &tmA, m0 + 64, kc, full);
+#pragma unroll
+        for (int h = 0; h < halves; ++h) {
+          const uint32_t a_dst = a_smem + s * a_stage + h * kABytes;
+          const int mh = m0 + h * kBM;
+          if (!p.a_mn) {
+            tma_load_2d(a_dst, &tmA, kc, mh, full);
+          } else {
+            tma_load_2d(a_dst, &tmA, mh, kc, full);
+            tma_load_2d(a_dst + 8192, &tmA, mh + 64, kc, full);
+          }
         }
         if (!p.b_mn) {
           tma_load_2d(b_dst, &tmB, kc, n0, full);
@@ -232,13 +241,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         if (!mbar_wait(smem_u32(&s_full[s]), ph, s_abort)) { *s_abort = 1; ok = false; break; }
         tc_fence_after();
         if (prof && i < 8) prof[2 + i] = globaltimer_ns();
-        const uint32_t a_base = a_smem + s * kABytes;
+        const uint32_t a_base = a_smem + s * a_stage;
         const uint32_t b_base = b_smem + s * b_bytes;
 #pragma unroll
         for (int k = 0; k < kBK / kUmmaK; ++k) {
-          const uint64_t ad = make_smem_desc(a_base + k * a_kstep, a_lbo, 1024u);
           const uint64_t bd = make_smem_desc(b_base + k * b_kstep, b_lbo, 1024u);
-          umma_f16(tmem, ad, bd, idesc, (i > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+          for (int h = 0; h < halves; ++h) {
+            const uint64_t ad = make_smem_desc(a_base + h * kABytes + k * a_kstep, a_lbo, 1024u);
+            umma_f16(tmem + (uint32_t)(h * 256), ad, bd, idesc, (i > 0 || k > 0) ? 1u : 0u);
+          }
         }
         umma_commit(smem_u32(&s_empty[s]));   // frees the stage once the MMAs have read it
       }
@@ -266,10 +278,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       uint8_t* sm_a0 = sm_out + 2048;
       uint8_t* sm_a1 = sm_out + 4096;
       const int n_store = p.n_store;
-      const int row_base = m0 + q * 32;
-      const uint32_t tm_lane = tmem + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+      for (int half = 0; half < halves; ++half) {
+      const int row_base = m0 + half * kBM + q * 32;
+      const uint32_t tm_lane = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * 256);
       const int lrow = lane >> 2, lpc = lane & 3;          // line-wise mapping: 4 lanes per row
-      const bool has_aux = p.mask_aux != nullptr || p.had_x0 != nullptr;
+      const bool has_aux = p.mask_aux != nullptr || p.had_x0 != nullptr || p.had_xl != nullptr;
       const bool has_bias = p.bias != nullptr, relu = p.relu != 0;
       const int my_off = lane * 64;
       const int my_sw = (lane >> 1) & 3;
@@ -285,11 +299,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
               if (grow < p.M && gcol + 8 <= p.ld_aux) {
                 const size_t off = (size_t)grow * p.ld_aux + gcol;
                 if (p.mask_aux) va = *reinterpret_cast<const uint4*>(p.mask_aux + off);
-                else { va = *reinterpret_cast<const uint4*>(p.had_x0 + off); vb = *reinterpret_cast<const uint4*>(p.had_xl + off); }
+                else {
+                  if (p.had_x0) va = *reinterpret_cast<const uint4*>(p.had_x0 + off);
+                  vb = *reinterpret_cast<const uint4*>(p.had_xl + off);
+                }
               }
               const int so = r * 64 + ((lpc ^ ((r >> 1) & 3)) << 4);
               *reinterpret_cast<uint4*>(sm_a0 + so) = va;
-              if (p.had_x0) *reinterpret_cast<uint4*>(sm_a1 + so) = vb;
+              if (!p.mask_aux) *reinterpret_cast<uint4*>(sm_a1 + so) = vb;
             }
             __syncwarp();
           }
@@ -326,14 +343,27 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                   if (!(m2.x > 0.f)) v[2 * k] = 0.f;
                   if (!(m2.y > 0.f)) v[2 * k + 1] = 0.f;
                 }
-              } else {            // DCN-v2: x0 * (acc + bias) + xl
+              } else {            // DCN-v2: x0 * (acc + bias) + xl, or just + xl when there is no x0
                 const uint4 a1 = *reinterpret_cast<const uint4*>(sm_a1 + so);
                 const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&a1);
+                if (p.aux_out) {  // keep u = acc + bias for the backward pass; this lane owns the slot it just read
+                  *reinterpret_cast<uint4*>(sm_a1 + so) =
+                      make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+                }
+                if (p.had_x0) {
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                  const float2 x0 = __bfloat1622float2(h0[k]), xl = __bfloat1622float2(h1[k]);
-                  v[2 * k] = x0.x * v[2 * k] + xl.x;
-                  v[2 * k + 1] = x0.y * v[2 * k + 1] + xl.y;
+                  for (int k = 0; k < 4; ++k) {
+                    const float2 x0 = __bfloat1622float2(h0[k]), xl = __bfloat1622float2(h1[k]);
+                    v[2 * k] = x0.x * v[2 * k] + xl.x;
+                    v[2 * k + 1] = x0.y * v[2 * k + 1] + xl.y;
+                  }
+                } else {
+#pragma unroll
+                  for (int k = 0; k < 4; ++k) {
+                    const float2 xl = __bfloat1622float2(h1[k]);
+                    v[2 * k] += xl.x;
+                    v[2 * k + 1] += xl.y;
+                  }
                 }
               }
             }
@@ -355,7 +385,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             const int r = 8 * i + lrow;
             const int grow = row_base + r;
             if (grow < p.M && col_ok) {
-              const uint4 o = *reinterpret_cast<const uint4*>(sm_out + r * 64 + ((lpc ^ ((r >> 1) & 3)) << 4));
+              const int sl = r * 64 + ((lpc ^ ((r >> 1) & 3)) << 4);
+              const uint4 o = *reinterpret_cast<const uint4*>(sm_out + sl);
               __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)grow * p.ldc + gcol;
               if (gcol + 8 <= n_store) {
                 *reinterpret_cast<uint4*>(dst) = o;
@@ -363,6 +394,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 const __nv_bfloat16* ob = reinterpret_cast<const __nv_bfloat16*>(&o);
                 for (int j = 0; j < n_store - gcol; ++j) dst[j] = ob[j];
               }
+              if (p.aux_out && gcol + 8 <= p.ld_aux)
+                *reinterpret_cast<uint4*>(p.aux_out + (size_t)grow * p.ld_aux + gcol) = *reinterpret_cast<const uint4*>(sm_a1 + sl);
             }
           }
           __syncwarp();
@@ -409,6 +442,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           __syncwarp();
         }
       }
+      }   // halves
     }
   }
 
@@ -496,12 +530,16 @@ const char* gemm_bf16(const GemmDesc& d, cudaStream_t stream) {
   if ((d.lda % 8) || (d.ldb % 8)) return "gemm_bf16: leading dimensions must be multiples of 8 elements";
   if (d.out_f32 ? (d.ldc % 4) : (d.ldc % 8)) return "gemm_bf16: ldc alignment";
   if (reinterpret_cast<uintptr_t>(d.C) & 15) return "gemm_bf16: C must be 16-byte aligned";
-  if (d.mask_aux || d.had_x0) {
+  if (d.mask_aux || d.had_x0 || d.had_xl) {
     if (d.out_f32) return "gemm_bf16: mask / Hadamard epilogues need a bf16 output";
     if (d.ld_aux % 8) return "gemm_bf16: ld_aux must be a multiple of 8 elements";
     if ((reinterpret_cast<uintptr_t>(d.mask_aux) | reinterpret_cast<uintptr_t>(d.had_x0) | reinterpret_cast<uintptr_t>(d.had_xl)) & 15)
       return "gemm_bf16: auxiliary operands must be 16-byte aligned";
     if (d.had_x0 && !d.had_xl) return "gemm_bf16: Hadamard epilogue needs both x0 and xl";
+  }
+  if (d.aux_out) {
+    if (!d.had_xl || d.mask_aux) return "gemm_bf16: aux_out goes with the Hadamard / residual epilogue";
+    if (reinterpret_cast<uintptr_t>(d.aux_out) & 15) return "gemm_bf16: aux_out must be 16-byte aligned";
   }
 
   // Tile N (multiple of 16; 64 when B is MN-major) and the split-K factor are chosen together with a small
@@ -550,25 +588,39 @@ const char* gemm_bf16(const GemmDesc& d, cudaStream_t stream) {
   else         ok = get_tensor_map(d.B, d.K, d.N, d.ldb, kBK, &tmB);          // [K, N]
   if (!ok) return "gemm_bf16: cuTensorMapEncodeTiled failed for B";
 
+  // 256-row tiles pay off when the problem is compute-sized: several waves of full-width tiles, no split-K
+  int halves = d.m_halves;
+  if (halves == 0) {
+    const long long tiles256 = (long long)((d.M + 2 * kBM - 1) / (2 * kBM)) * ((n_cover + BN - 1) / BN);
+    // measured on 8192 x 6416 x 6416: (K,MN) 1000 -> 1207 TFLOP/s, (MN,MN) 962 -> 1134, but (K,K) 1086 -> 908
+    halves = (BN == 256 && splits == 1 && tiles256 >= 3 * 148 && kt_total >= 16 && (d.a_mn || d.b_mn)) ? 2 : 1;
+  }
+  if (halves != 1 && halves != 2) return "gemm_bf16: m_halves must be 1 or 2";
+  if (halves == 2 && BN > 256) return "gemm_bf16: bad tile N";
+
   GemmParams p;
+  p.m_halves = halves;
   p.M = d.M; p.N = d.N; p.K = d.K; p.BN = BN; p.a_mn = d.a_mn; p.b_mn = d.b_mn; p.k_tiles_per_split = ktps;
   p.C = d.C; p.ldc = d.ldc; p.out_f32 = d.out_f32; p.accumulate = d.accumulate; p.relu = d.relu;
   p.mask_aux = reinterpret_cast<const __nv_bfloat16*>(d.mask_aux);
   p.had_x0 = reinterpret_cast<const __nv_bfloat16*>(d.had_x0);
   p.had_xl = reinterpret_cast<const __nv_bfloat16*>(d.had_xl);
+  p.aux_out = reinterpret_cast<__nv_bfloat16*>(d.aux_out);
   p.ld_aux = d.ld_aux; p.ones_col = d.ones_col; p.n_store = n_cover; p.bias = d.bias; p.status = d.status; p.prof = d.prof; p.dbg = d.dbg;
   p.gate_flags = d.gate_flags; p.gate_epoch = d.gate_epoch; p.gate_world = d.gate_world; p.gate_wait_ns = d.gate_wait_ns;
 
-  dim3 grid((n_cover + BN - 1) / BN, (d.M + kBM - 1) / kBM, splits);
+  dim3 grid((n_cover + BN - 1) / BN, (d.M + kBM * halves - 1) / (kBM * halves), splits);
   const size_t b_bytes = (size_t)BN * kBK * 2;
   const size_t epi_bytes = (size_t)kEpiWarps * kEpiBytesPerWarp + 1024;
-  size_t smem4 = 4 * (kABytes + b_bytes) + 1024, smem3 = 3 * (kABytes + b_bytes) + 1024;
+  const size_t a_stage = (size_t)halves * kABytes;
+  size_t smem4 = 4 * (a_stage + b_bytes) + 1024, smem3 = 3 * (a_stage + b_bytes) + 1024;
   if (smem4 < epi_bytes) smem4 = epi_bytes;
   if (smem3 < epi_bytes) smem3 = epi_bytes;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
-    cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<4, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<3, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<3, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
     attr_set = true;
   }
   // launched as a programmatic dependent of whatever precedes it in the stream (plain serialisation when the
@@ -584,12 +636,16 @@ const char* gemm_bf16(const GemmDesc& d, cudaStream_t stream) {
   cfg.attrs = attr;
   cfg.numAttrs = use_pdl ? 1 : 0;
   cudaError_t e;
-  if (smem4 <= 200 * 1024) {
+  if (halves == 2) {
+    if (smem3 > 220 * 1024) return "gemm_bf16: two-accumulator tile does not fit in shared memory";
+    cfg.dynamicSmemBytes = smem3;
+    e = cudaLaunchKernelEx(&cfg, gemm_bf16_tcgen05_kernel<3, 2>, tmA, tmB, p);
+  } else if (smem4 <= 200 * 1024) {
     cfg.dynamicSmemBytes = smem4;
-    e = cudaLaunchKernelEx(&cfg, gemm_bf16_tcgen05_kernel<4>, tmA, tmB, p);
+    e = cudaLaunchKernelEx(&cfg, gemm_bf16_tcgen05_kernel<4, 1>, tmA, tmB, p);
   } else {
     cfg.dynamicSmemBytes = smem3;
-    e = cudaLaunchKernelEx(&cfg, gemm_bf16_tcgen05_kernel<3>, tmA, tmB, p);
+    e = cudaLaunchKernelEx(&cfg, gemm_bf16_tcgen05_kernel<3, 1>, tmA, tmB, p);
   }
   if (e == cudaSuccess) e = cudaGetLastError();
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);

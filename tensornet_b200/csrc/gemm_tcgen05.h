@@ -20,12 +20,14 @@ struct GemmDesc {
   const float* bias = nullptr;      // optional fp32 [N], added before ReLU
   const void* mask_aux = nullptr;   // optional bf16 [M, ld_aux]: result is zeroed where mask_aux <= 0
   const void* had_x0 = nullptr;     // optional bf16 [M, ld_aux]: result = had_x0 * result + had_xl
-  const void* had_xl = nullptr;
+  const void* had_xl = nullptr;     // with had_x0 == nullptr: result = result + had_xl (residual add)
+  void* aux_out = nullptr;          // optional bf16 [M, ld_aux]: receives the result before the Hadamard step (acc + bias)
   int ld_aux = 0;
   int ones_col = -1;         // column (>= N) that is written as 1.0: the bias input of the next layer
   int n_store = 0;           // columns written per row (>= N; columns past N get 0, or 1 at ones_col)
   int split_k = 0;           // 0 = choose (only fp32 accumulate outputs may be split)
   int BN = 0;                // tile N override (0 = choose)
+  int m_halves = 0;          // 128-row accumulators per CTA: 1, 2 (256-row tile sharing one B tile) or 0 = choose
   // Weight gate ("all-gather fused with the GEMM"): the B operand lives in an array whose chunks other GPUs
   // write during the dense optimizer step.  When gate_flags is set the TMA producer first waits (bounded) until
   // each of the gate_world flag words carries at least the epoch stored at *gate_epoch in its high 32 bits, then
@@ -41,12 +43,13 @@ struct GemmDesc {
 
 // Kernel-side parameter block.
 struct GemmParams {
-  int M, N, K, BN, a_mn, b_mn, k_tiles_per_split;
+  int M, N, K, BN, a_mn, b_mn, k_tiles_per_split, m_halves;
   void* C;
   int ldc, out_f32, accumulate, relu;
   const __nv_bfloat16* mask_aux;
   const __nv_bfloat16* had_x0;
   const __nv_bfloat16* had_xl;
+  __nv_bfloat16* aux_out;
   int ld_aux, ones_col, n_store;
   const float* bias;
   const unsigned long long* gate_flags;

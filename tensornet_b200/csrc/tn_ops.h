@@ -50,6 +50,8 @@ void launch_cross_v1_fwd(const float* x0, const float* xl, const float* w, const
 void launch_cross_v1_bwd(const float* x0, const float* xl, const float* w, const float* dot, const float* gy, int B, int D,
                          float* gx0, float* gxl, float* gw, float* gb, cudaStream_t st);
 void launch_relu_mask(void* g, const void* y, long long n, cudaStream_t st);
+void launch_cross_v2_bwd_elem(const void* g, const void* u, const void* x0, float* gx0, void* du, long long n, int first, cudaStream_t st);
+void launch_cross_v2_bwd_final(const float* gx0, const void* g, void* out, long long n, cudaStream_t st);
 
 // deepfm_fused.cu  (return nullptr or a static error string)
 const char* launch_deepfm_input_fwd(const float* U, int ustride, const int* inverse, int B, int S, int D, const float* dense, int Dd,

@@ -60,7 +60,7 @@ struct SparseCommView {
   unsigned* bar;                             // [2] grid barrier words (zero between launches)
   int* status;                               // [4] error words
   unsigned long long wait_ns;                // budget of every wait inside the kernels
-  unsigned long long* prof;                  // optional [16] phase timestamps: pull 0..5, push 8..13 (globaltimer ns) written by CTA 0
+  unsigned long long* prof;                  // optional [16] phase timestamps (globaltimer ns) by CTA 0: pull 0..5 (6 = slowest CTA's end of the row return), push 8..13 (14 / 15 = after the own records / after the wait for the peers)
 };
 
 struct PullArgs {

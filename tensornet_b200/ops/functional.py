@@ -356,44 +356,52 @@ class _CrossV2(torch.autograd.Function):
     def forward(ctx, x0, dim, *weights):
         ext, st = _ext(), _status()
         B, Dp = x0.shape[0], int(x0.stride(0))
-        xs = [x0]
+        xs, us = [x0], []
         xl = x0
+        keep_u = any(w.requires_grad for w in weights) or x0.requires_grad
         for w in weights:
             y = torch.empty((B, Dp), dtype=torch.bfloat16, device=x0.device)
+            # u = W x_l + b is needed again by the backward pass; the epilogue writes it next to y (105 MB per layer at
+            # batch 8192 x width 6416) instead of the backward pass recomputing it with a fourth GEMM per layer
+            u = torch.empty((B, Dp), dtype=torch.bfloat16, device=x0.device) if keep_u else None
             # tcgen05 GEMM with the Hadamard-residual epilogue; the bias rides on x_l's ones column
             ext.gemm(xl, _bf16_of(w), y, B, dim, dim + 1, Dp, int(w.shape[1]), Dp, False, False, False, False, None, None, x0, xl,
-                     Dp, dim, Dp, 1, 0, st)
+                     Dp, dim, Dp, 1, 0, st, aux_out=u)
             xs.append(y)
+            us.append(u)
             xl = y
-        ctx.save_for_backward(*xs)
-        ctx.weights, ctx.dim = weights, dim
+        ctx.save_for_backward(*xs, *[u for u in us if u is not None])
+        ctx.weights, ctx.dim, ctx.keep_u = weights, dim, keep_u
         return xl
 
     @staticmethod
     def backward(ctx, g):
         ext, st = _ext(), _status()
-        xs = ctx.saved_tensors
+        L = len(ctx.weights)
+        saved = ctx.saved_tensors
+        xs, us = saved[:L + 1], saved[L + 1:]
         weights, dim = ctx.weights, ctx.dim
         x0 = xs[0]
         B, Dp = x0.shape[0], int(x0.stride(0))
         g = g.contiguous()
-        gx0 = torch.zeros((B, Dp), dtype=torch.float32, device=g.device)
-        for l in range(len(weights) - 1, -1, -1):
+        gx0 = torch.empty((B, Dp), dtype=torch.float32, device=g.device)
+        du = torch.empty((B, Dp), dtype=torch.bfloat16, device=g.device)
+        for l in range(L - 1, -1, -1):
             w, xl = weights[l], xs[l]
             wb = _bf16_of(w)
             Kp = int(w.shape[1])
-            u = torch.empty((B, Dp), dtype=torch.bfloat16, device=g.device)     # u = W x_l + b, recomputed
-            ext.gemm(xl, wb, u, B, dim, dim + 1, Dp, Kp, Dp, False, False, False, False, None, None, None, None, 0, -1, Dp, 1, 0, st)
-            gx0.addcmul_(g.float(), u.float())
-            du = g * x0
+            # gx0 (+)= g * u ; du = g * x0   in one pass
+            ext.cross_v2_bwd_elem(g, us[l], x0, gx0, du, l == L - 1)
             if w.requires_grad:
                 ext.gemm(du, xl, _grad_buffer(w), dim, dim + 1, B, Dp, Dp, Kp, True, True, True, False, None, None, None, None, 0, -1,
                          dim + 1, 0, 0, st)
-            gxl = torch.empty((B, Dp), dtype=torch.bfloat16, device=g.device)
-            ext.gemm(du, wb, gxl, B, min(Kp, Dp), dim, Dp, Kp, Dp, False, True, False, False, None, None, None, None, 0, -1, Dp, 1, 0, st)
-            g = g + gxl
-        gx0 += g.float()
-        return (gx0.to(torch.bfloat16), None, *([None] * len(weights)))
+            # g_{l} = g_{l+1} + du . W   (the residual add rides in the GEMM epilogue)
+            gn = torch.empty((B, Dp), dtype=torch.bfloat16, device=g.device)
+            ext.gemm(du, wb, gn, B, min(Kp, Dp), dim, Dp, Kp, Dp, False, True, False, False, None, None, None, g, Dp, -1, Dp, 1, 0, st)
+            g = gn
+        out = torch.empty((B, Dp), dtype=torch.bfloat16, device=g.device)
+        ext.cross_v2_bwd_final(gx0, g, out)
+        return (out, None, *([None] * L))
 
 
 def cross_v2(x0: torch.Tensor, weights: Sequence[torch.Tensor], dim: int) -> torch.Tensor:

@@ -120,3 +120,73 @@ def test_weight_gate_passes_and_times_out(tn_gpu):
     assert e.value.code == 5 and e.value.phase == 70 and e.value.aux == 2
     assert float(torch.ones(4, device=dev).sum()) == 4.0
     rt.check_status()      # the words were cleared by the raise
+
+
+@pytest.mark.parametrize("layout", ["kk", "k_mn", "mn_mn"])
+def test_two_accumulator_tile(tn_gpu, status_ok, layout):
+    """256-row tiles (two 128-row TMEM accumulators sharing each B tile) against an fp32 reference, with a ragged
+    last row tile and a ragged last column tile."""
+    dev = tn_gpu.core.runtime().device
+    M, N, K = 640 + 40, 512 + 64, 1024
+    g = torch.Generator().manual_seed(12)
+    st = tn_gpu.core.runtime().status
+    if layout == "kk":
+        A = torch.randn(M, K, generator=g).bfloat16().to(dev)
+        B = (torch.randn(N, K, generator=g) * 0.05).bfloat16().to(dev)
+        C = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+        _ext().gemm(A, B, C, M, N, K, K, K, N, False, False, False, False, None, None, None, None, 0, -1, N, 1, 256, st, m_halves=2)
+        ref = A.float() @ B.float().t()
+    elif layout == "k_mn":
+        A = torch.randn(M, K, generator=g).bfloat16().to(dev)
+        B = (torch.randn(K, N, generator=g) * 0.05).bfloat16().to(dev)          # [K, N]: N contiguous
+        C = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+        _ext().gemm(A, B, C, M, N, K, K, N, N, False, True, False, False, None, None, None, None, 0, -1, N, 1, 256, st, m_halves=2)
+        ref = A.float() @ B.float()
+    else:
+        A = torch.randn(K, M + 0, generator=g).bfloat16().to(dev)              # [K, M]: M contiguous
+        B = (torch.randn(K, N, generator=g) * 0.05).bfloat16().to(dev)
+        C = torch.zeros(M, N, dtype=torch.float32, device=dev)
+        _ext().gemm(A, B, C, M, N, K, M, N, N, True, True, True, False, None, None, None, None, 0, -1, N, 1, 256, st, m_halves=2)
+        ref = A.float().t() @ B.float()
+    assert _rel_err(C, ref) < 2e-2
+
+
+def test_hadamard_epilogue_keeps_pre_activation_and_residual_mode(tn_gpu, status_ok):
+    """aux_out receives u = A . B^T + bias next to y = x0 * u + xl; without x0 the epilogue is a plain residual add."""
+    dev = tn_gpu.core.runtime().device
+    M, N, K = 384, 272, 320
+    g = torch.Generator(device="cpu").manual_seed(9)
+    A = torch.randn(M, K, generator=g).bfloat16().to(dev)
+    B = (torch.randn(N, K, generator=g) * 0.05).bfloat16().to(dev)
+    bias = torch.randn(N, generator=g).to(dev)
+    x0 = torch.randn(M, N, generator=g).bfloat16().to(dev)
+    xl = torch.randn(M, N, generator=g).bfloat16().to(dev)
+    st = tn_gpu.core.runtime().status
+    C = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    U = torch.full((M, N), 7.0, dtype=torch.bfloat16, device=dev)
+    _ext().gemm(A, B, C, M, N, K, K, K, N, False, False, False, False, bias, None, x0, xl, N, -1, N, 1, 0, st, aux_out=U)
+    u_ref = A.float() @ B.float().t() + bias
+    assert _rel_err(U, u_ref) < 2e-2
+    assert _rel_err(C, x0.float() * u_ref + xl.float()) < 2e-2
+    R = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    _ext().gemm(A, B, R, M, N, K, K, K, N, False, False, False, False, None, None, None, xl, N, -1, N, 1, 0, st)
+    assert _rel_err(R, A.float() @ B.float().t() + xl.float()) < 2e-2
+
+
+def test_cross_v2_backward_elementwise_kernels(tn_gpu, status_ok):
+    dev = tn_gpu.core.runtime().device
+    n = 256 * 136
+    g = torch.Generator(device="cpu").manual_seed(2)
+    gg, u, x0 = (torch.randn(n, generator=g).bfloat16().to(dev) for _ in range(3))
+    acc = torch.randn(n, generator=g).to(dev)
+    gx0 = acc.clone()
+    du = torch.empty(n, dtype=torch.bfloat16, device=dev)
+    _ext().cross_v2_bwd_elem(gg, u, x0, gx0, du, False)
+    assert torch.allclose(gx0, acc + gg.float() * u.float(), rtol=1e-5, atol=1e-5)
+    assert torch.equal(du, (gg.float() * x0.float()).bfloat16())
+    first = torch.full((n,), 3.0, device=dev)
+    _ext().cross_v2_bwd_elem(gg, u, x0, first, du, True)
+    assert torch.allclose(first, gg.float() * u.float(), rtol=1e-5, atol=1e-5)
+    out = torch.empty(n, dtype=torch.bfloat16, device=dev)
+    _ext().cross_v2_bwd_final(gx0, gg, out)
+    assert torch.equal(out, (gx0 + gg.float()).bfloat16())
