@@ -592,8 +592,8 @@ const char* gemm_bf16(const GemmDesc& d, cudaStream_t stream) {
   int halves = d.m_halves;
   if (halves == 0) {
     const long long tiles256 = (long long)((d.M + 2 * kBM - 1) / (2 * kBM)) * ((n_cover + BN - 1) / BN);
-    // measured on 8192 x 6416 x 6416: (K,MN) 1000 -> 1207 TFLOP/s, (MN,MN) 962 -> 1134, but (K,K) 1086 -> 908
-    halves = (BN == 256 && splits == 1 && tiles256 >= 3 * 148 && kt_total >= 16 && (d.a_mn || d.b_mn)) ? 2 : 1;
+    // measured on 8192 x 6416 x 6416: (K,K) 1087 -> 1313 TFLOP/s, (K,MN) 1000 -> 1327, (MN,MN) 962 -> 1238
+    halves = (BN >= 128 && splits == 1 && tiles256 >= 3 * 148 && kt_total >= 16) ? 2 : 1;
   }
   if (halves != 1 && halves != 2) return "gemm_bf16: m_halves must be 1 or 2";
   if (halves == 2 && BN > 256) return "gemm_bf16: bad tile N";
