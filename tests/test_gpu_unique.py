@@ -37,7 +37,8 @@ def test_unique_assign_properties(tn_gpu, status_ok):
 
     dev = tn_gpu.core.runtime().device
     ua = UniqueAssign(512)
-    wide = st.lists(st.integers(min_value=-2**63, max_value=2**63 - 2), min_size=1, max_size=400)
+    # -1 (all ones) is the tables' empty marker and is folded onto another sign by design: keep it out of the identity checks
+    wide = st.lists(st.integers(min_value=-2**63, max_value=2**63 - 2).filter(lambda v: v != -1), min_size=1, max_size=400)
     hot = st.lists(st.integers(min_value=0, max_value=12), min_size=1, max_size=400)
 
     @settings(max_examples=40, deadline=None)
@@ -68,7 +69,7 @@ def test_table_insert_lookup_properties(tn_gpu, status_ok):
     seen = {}
 
     @settings(max_examples=30, deadline=None)
-    @given(st.lists(st.integers(min_value=-2**63, max_value=2**63 - 2), min_size=1, max_size=64, unique=True))
+    @given(st.lists(st.integers(min_value=-2**63, max_value=2**63 - 2).filter(lambda v: v != -1), min_size=1, max_size=64, unique=True))
     def check(ids):
         if len(seen) + len(ids) > 3000:
             return
