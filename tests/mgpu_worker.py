@@ -54,6 +54,26 @@ def main():
     bn_ok = bool(torch.allclose(bn.moving_mean.cpu().double(), cat.mean(0), atol=1e-5)
                  and torch.allclose(bn.moving_variance.cpu().double(), cat.var(0, unbiased=False), rtol=1e-3, atol=1e-3))
     bn_oks = rt.all_gather_object(bn_ok)
+    # sharded serving: lookups through the read-only fused pull against a replicated dictionary on the same rank
+    import numpy as np
+    from tensornet_b200.layers import DenseHead, MLP
+    from tensornet_b200.serving import EmbeddingDictionary, InferenceEngine, ShardedInferenceEngine
+    rng = np.random.default_rng(5)
+    signs = np.unique(rng.integers(1, 2 ** 40, 4000, dtype=np.int64).astype(np.uint64))
+    weights = rng.standard_normal((len(signs), 8)).astype(np.float32) * 0.3
+    torch.manual_seed(3)
+    s_mlp, s_head = MLP(4 * 8, [16]).to(rt.device), DenseHead(16).to(rt.device)
+    ref_eng = InferenceEngine(EmbeddingDictionary(signs, weights), s_mlp, s_head, 4)
+    sh_eng = ShardedInferenceEngine.from_dictionary(signs, weights, s_mlp, s_head, 4, 4 * 32)
+    rq = np.random.default_rng(50 + rt.rank)
+    serving_ok = True
+    for _ in range(3):
+        pick = signs[rq.integers(0, len(signs), (4, 32))].view(np.int64)
+        req = torch.from_numpy(np.where(rq.random((4, 32)) < 0.85, pick, rq.integers(2 ** 41, 2 ** 42, (4, 32), dtype=np.int64)))
+        serving_ok = serving_ok and bool(torch.allclose(ref_eng.infer(req).cpu(), sh_eng.infer(req).cpu(), atol=2e-3))
+    torch.cuda.synchronize()
+    rt.check_status()
+    serving_oks = rt.all_gather_object(serving_ok)
     rows = [int(m.table.n_rows) for m in (model.linear_emb, model.deep_emb)]
     allrows = rt.all_gather_object(rows)
     w = model.sub_model.head.weight.detach().float().cpu()
@@ -61,7 +81,7 @@ def main():
     if rt.rank == 0:
         same = all(torch.equal(ws[0], x) for x in ws)
         json.dump({"world": rt.world, "losses": losses, "rows": [sum(r[i] for r in allrows) for i in range(2)],
-                   "replicas_identical": same, "bn_sync_ok": all(bn_oks), "graph": model._graph is not None,
+                   "replicas_identical": same, "bn_sync_ok": all(bn_oks), "serving_ok": all(serving_oks), "graph": model._graph is not None,
                    "multimem": bool(getattr(model.optimizer.table, "uses_multimem", False))}, open(out, "w"))
     tn.core.shutdown()
 
