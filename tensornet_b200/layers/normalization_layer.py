@@ -107,6 +107,12 @@ class TNBatchNormalizationBase(nn.Module):
     def _device_push(self, x2: torch.Tensor, centered: bool):
         self.table.push_batch(x2, centered)
         if self.synchronized:
+            if torch.cuda.is_current_stream_capturing():
+                # a captured step replays the same launches every time, so the exchange cannot run every
+                # sync_freq-th step only: inside a CUDA graph it runs every step (one small kernel)
+                self.table.sync_increments()
+                self.batch_counter = 0
+                return
             self.batch_counter += 1
             if self.batch_counter == self.sync_freq:
                 self.table.sync_increments()

@@ -139,6 +139,8 @@ class Model(nn.Module):
         self.is_loaded_from_checkpoint = False
         self._sums: Optional[torch.Tensor] = None
         self._graph = None
+        self._graphs = {}            # batch signature -> (graph, static input leaves, static loss)
+        self._max_graphs = 8
         self._graph_key = None
         self._static_leaves: List[torch.Tensor] = []
         self._static_loss = None
@@ -258,6 +260,13 @@ class Model(nn.Module):
         spec = _flatten((features, labels), leaves)
         key = (repr(spec), tuple((tuple(t.shape), t.dtype) for t in leaves))
         static_ok = _is_static(spec)
+        if not static_ok and key not in self._graphs:
+            # Ragged batches can be replayed too as long as their shapes repeat (fixed bag lengths, bucketed loaders):
+            # one graph per distinct shape, a handful at most, and only on one GPU (ranks would disagree on when to
+            # capture).  Shapes beyond that run eagerly.
+            static_ok = core.runtime().world == 1 and len(self._graphs) < self._max_graphs
+        else:
+            static_ok = True
         if not static_ok or self._eager_steps < self._graph_warmup:
             self._eager_steps += 1
             (f, y), _, _ = self._to_device((features, labels))
@@ -265,36 +274,51 @@ class Model(nn.Module):
             if self._eager_steps <= self._graph_warmup:
                 core.runtime().check_status()      # surface device-side errors before the step is frozen into a graph
             return loss
-        if self._graph is None or self._graph_key != key:
-            self._capture(spec, leaves, key)
-        for dst, src in zip(self._static_leaves, leaves):
+        if key not in self._graphs:
+            if _is_static(spec):
+                self._capture(spec, leaves, key)
+            else:
+                try:
+                    self._capture(spec, leaves, key)
+                except Exception:           # an op of the ragged path that cannot be captured: stay eager for good
+                    torch.cuda.synchronize()
+                    self._max_graphs = 0
+                    self._graphs.clear()
+                    (f, y), _, _ = self._to_device((features, labels))
+                    return self._step_impl(f, y)
+        graph, static_leaves, static_loss = self._graphs[key]
+        for dst, src in zip(static_leaves, leaves):
             dst.copy_(src, non_blocking=True)
         if self.optimizer is not None:
             self.optimizer.table.set_lr(self.optimizer._lr())
-        self._graph.replay()
+        graph.replay()
         if self.optimizer is not None:
             self.optimizer.iterations += 1
             self.optimizer.table.step_count += 1
-        return self._static_loss
+        self._graph, self._graph_key, self._static_leaves, self._static_loss = graph, key, static_leaves, static_loss
+        return static_loss
 
     def _capture(self, spec, leaves, key):
         dev = core.runtime().device
-        self._static_leaves = [torch.empty(t.shape, dtype=t.dtype, device=dev) for t in leaves]
-        for dst, src in zip(self._static_leaves, leaves):
+        static_leaves = [torch.empty(t.shape, dtype=t.dtype, device=dev) for t in leaves]
+        for dst, src in zip(static_leaves, leaves):
             dst.copy_(src, non_blocking=True)
-        f, y = _unflatten(spec, iter(self._static_leaves))
+        f, y = _unflatten(spec, iter(static_leaves))
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
         iters = self.optimizer.iterations if self.optimizer is not None else 0
         from .. import _build
         c0 = _build.cuda_ext().launch_count()
         with torch.cuda.graph(g):
-            self._static_loss = self._step_impl(f, y)
+            static_loss = self._step_impl(f, y)
         self._launches_per_step = _build.cuda_ext().launch_count() - c0
         if self.optimizer is not None:      # capture only records work, it does not run a step
             self.optimizer.iterations = iters
             self.optimizer.table.step_count -= 1
-        self._graph, self._graph_key = g, key
+        if len(self._graphs) >= self._max_graphs:          # static shapes beyond the cap replace the oldest graph
+            self._graphs.pop(next(iter(self._graphs)))
+        self._graphs[key] = (g, static_leaves, static_loss)
+        self._graph, self._graph_key, self._static_leaves, self._static_loss = g, key, static_leaves, static_loss
         # Capture takes a different time on every rank; the first replay's kernels wait for their peers on the
         # device with a finite budget, so line the ranks up on the host first.
         core.runtime().barrier()

@@ -84,7 +84,8 @@ class DenseTable:
         self.lr = self.opt.current_lr(0)
         self.state = torch.tensor([1.0, 1.0, self.lr, 0.0], dtype=torch.float32, device=dev)
         if rt.on_gpu:
-            use_mc = config.use_multimem and W > 1 and self.arena.buf.mc_ptr != 0
+            want_mc = (W >= 4) if int(config.use_multimem) < 0 else bool(int(config.use_multimem))
+            use_mc = want_mc and W > 1 and self.arena.buf.mc_ptr != 0
             d = dict(kind=0 if self.opt.kind == KIND_ADAM else 1,
                      beta1=float(getattr(self.opt, "beta1", 0.9)), beta2=float(getattr(self.opt, "beta2", 0.999)),
                      eps=float(self.opt.epsilon), grad_decay=float(getattr(self.opt, "grad_decay_rate", 1.0)),

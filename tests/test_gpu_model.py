@@ -77,3 +77,42 @@ def test_fused_deepfm_path_matches_generic_path(tn_gpu, share):
     assert l2[-1] < l2[0]
     s1, s2 = m1.metric_sums(), m2.metric_sums()
     assert abs(s1["ctr"] - s2["ctr"]) < 1e-6 and abs(s1["pctr"] - s2["pctr"]) < 2e-2
+
+
+def test_ragged_batches_with_repeating_shapes_replay_from_graphs(tn_gpu):
+    """Multi-hot (ragged) Wide&Deep batches whose shapes repeat are captured too, one graph per shape; the replayed
+    trajectory follows the eager one, and a batch of a new shape simply gets its own graph."""
+    import numpy as np
+    tn = tn_gpu
+
+    def make(graph):
+        torch.manual_seed(4)
+        slots = ["1", "2", "3"]
+        m = tn.models.WideDeep(slots, slots, dnn_hidden_units=(32, 16), embedding_dim=4, bucket_size=4096, table_rows=1 << 14,
+                               use_bn=False)
+        m.compile(optimizer=tn.optimizer.Optimizer(tn.core.Adam(learning_rate=5e-3)), cuda_graph=graph, graph_warmup=2)
+        return m, slots
+
+    def batch(rng, B, lens_per_slot):
+        lens = np.concatenate([np.full((1, B), n, np.int64) for n in lens_per_slot])
+        offs = np.concatenate([[0], np.cumsum(lens.reshape(-1))]).astype(np.int32)
+        ids = rng.integers(0, 300, int(offs[-1]), dtype=np.int64) * 2654435761 + 5
+        y = (rng.random(B) < 0.3).astype(np.float32)
+        return torch.from_numpy(ids), torch.from_numpy(offs), torch.from_numpy(y)
+
+    rng = np.random.default_rng(0)
+    shapes = [(64, (1, 2, 3)), (64, (1, 2, 3)), (64, (2, 2, 2)), (64, (2, 2, 3)), (64, (2, 2, 2)), (64, (2, 2, 3))] * 3
+    data = [batch(rng, B, lens) for B, lens in shapes]
+    m1, slots = make(False)
+    m2, _ = make(True)
+    l1, l2 = [], []
+    for ids, offs, y in data:
+        f = {tn.data.PACKED_KEY: tn.data.PackedFeatures(slots, values=ids, offsets=offs, batch_size=64)}
+        l1.append(float(m1.train_on_batch(f, y)))
+        l2.append(float(m2.train_on_batch(f, y)))
+    torch.cuda.synchronize()
+    tn.core.runtime().check_status()
+    # (1,2,3) and (2,2,2) both have 384 ids: one graph serves both (the offsets are data); (2,2,3) has 448: a second one
+    assert len(m2._graphs) == 2, len(m2._graphs)
+    for a, b in zip(l1, l2):
+        assert abs(a - b) < 5e-2 * max(1.0, abs(a)), (l1, l2)
