@@ -235,7 +235,7 @@ def main():
             "value": value, "unit": "examples/s", "n_gpus": rt.world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": value / REFERENCE_EXAMPLES_PER_S,
-            "baseline_note": "BASELINE.md's only published training throughput: reference Wide&Deep, batch 32, one CPU host, ~4000 examples/s",
+            "baseline_note": "the only training throughput the reference publishes: Wide&Deep, batch 32, one CPU host, ~4000 examples/s (doc/tutorial/01-begin-with-wide-deep.ipynb:446)",
             "dtype": "bf16", "data": "synthetic",
             "config": {"model": "DeepFM 26 slots x dim16 (+dim1 linear), FM, MLP 429-400-400-400-1, sparse Adam, dense Adam",
                        "global_batch": G, "seq_len": 1, "parallelism": f"dp{rt.world}+row-sharded embedding tables",

@@ -127,7 +127,13 @@ struct SparseCtx {
     c.wait_ns = comm["wait_ns"].cast<uint64_t>();
     c.prof = comm.contains("prof") && !comm["prof"].is_none() ? ptr_of<unsigned long long>(comm["prof"].cast<at::Tensor>()) : nullptr;
     pull_lanes = tn::lanes_for_width_host((c.ustride + 3) / 4);   // each lane keeps up to four 16-byte chunks in flight
-    push_lanes = tn::lanes_for_width_host(t.dim);
+    {
+      // Lanes per row in the row update.  Fewer lanes per row = more rows in flight per warp, which is what the
+      // update is short of (dependent random accesses): with 1 M ids per batch, two 16-byte chunks per lane take the
+      // push from 169 to 131 us at dim 64 and four from 318 to 233 us at dim 128; short rows (dim 20) are best at one.
+      const int cpl = t.dim >= 128 ? 4 : (t.dim >= 32 ? 2 : 1);
+      push_lanes = tn::lanes_for_width_host((t.dim + cpl - 1) / cpl);
+    }
     if (!comm.contains("staged_return") || comm["staged_return"].cast<bool>()) {
       // rows per tile: whole 128-byte lines per tile, about 4 KiB of shared memory per warp at most
       int tr = 32;

@@ -21,7 +21,7 @@ def _host_rows(t):
     return {int(k): rows[i].copy() for i, k in enumerate(keys)}
 
 
-@pytest.mark.parametrize("dim", [1, 8, 16, 64])
+@pytest.mark.parametrize("dim", [1, 8, 16, 64, 128])
 def test_pull_dedup_and_init(tn_gpu, status_ok, dim):
     tn = tn_gpu
     opt = tn.core.AdaGrad(learning_rate=0.01, initial_g2sum=0.1, initial_scale=0.5)
@@ -92,7 +92,7 @@ def _apply_ref(kind, opt, row, g, show, click, dim):
 
 
 @pytest.mark.parametrize("kind", ["AdaGrad", "Adam", "Ftrl"])
-@pytest.mark.parametrize("dim", [8, 16])
+@pytest.mark.parametrize("dim", [8, 16, 64, 128])
 def test_push_matches_reference_math(tn_gpu, status_ok, kind, dim):
     tn = tn_gpu
     opt = {"AdaGrad": tn.core.AdaGrad(learning_rate=0.05, initial_g2sum=0.1, initial_scale=0.3),
