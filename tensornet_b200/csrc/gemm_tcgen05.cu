@@ -143,8 +143,21 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   const uint32_t a_smem = base;
   const uint32_t b_smem = base + kStages * a_stage;
 
-  const int n0 = blockIdx.x * BN;
-  const int m0 = blockIdx.y * kBM * halves;
+  // Tile order.  Large grids walk the tiles in groups of kRasterGroup rows of tiles, column by column inside a
+  // group, so that the CTAs resident at one time share a compact block of A and B tiles in L2 instead of a thin
+  // stripe that streams all of B for every few rows of A.
+  int tile_n = blockIdx.x, tile_m = blockIdx.y;
+  if (p.raster_group > 1) {
+    const int gx = gridDim.x, gy = gridDim.y;
+    const int pid = blockIdx.y * gx + blockIdx.x;
+    const int width = p.raster_group * gx;
+    const int first_m = (pid / width) * p.raster_group;
+    const int gsize = min(gy - first_m, p.raster_group);
+    tile_m = first_m + (pid % width) % gsize;
+    tile_n = (pid % width) / gsize;
+  }
+  const int n0 = tile_n * BN;
+  const int m0 = tile_m * kBM * halves;
   const int kt_total = (p.K + kBK - 1) / kBK;
   const int kt0 = blockIdx.z * p.k_tiles_per_split;
   int nk = kt_total - kt0;
@@ -600,6 +613,11 @@ const char* gemm_bf16(const GemmDesc& d, cudaStream_t stream) {
 
   GemmParams p;
   p.m_halves = halves;
+  {
+    static const int rg_env = []() { const char* e = getenv("TN_GEMM_RASTER_GROUP"); return e ? atoi(e) : -1; }();
+    const long long tiles = (long long)((d.M + kBM * halves - 1) / (kBM * halves)) * ((n_cover + BN - 1) / BN);
+    p.raster_group = rg_env >= 0 ? rg_env : ((splits == 1 && tiles >= 2 * 148) ? 16 : 1);   // 1 % on 8192 x 6416 x 6416
+  }
   p.M = d.M; p.N = d.N; p.K = d.K; p.BN = BN; p.a_mn = d.a_mn; p.b_mn = d.b_mn; p.k_tiles_per_split = ktps;
   p.C = d.C; p.ldc = d.ldc; p.out_f32 = d.out_f32; p.accumulate = d.accumulate; p.relu = d.relu;
   p.mask_aux = reinterpret_cast<const __nv_bfloat16*>(d.mask_aux);

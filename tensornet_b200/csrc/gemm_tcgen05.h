@@ -43,7 +43,7 @@ struct GemmDesc {
 
 // Kernel-side parameter block.
 struct GemmParams {
-  int M, N, K, BN, a_mn, b_mn, k_tiles_per_split, m_halves;
+  int M, N, K, BN, a_mn, b_mn, k_tiles_per_split, m_halves, raster_group;
   void* C;
   int ldc, out_f32, accumulate, relu;
   const __nv_bfloat16* mask_aux;
