@@ -362,11 +362,60 @@ class Model(nn.Module):
                     ys.append(y.cpu())
             return (torch.cat(ys) if ys else None), (torch.cat(ps) if ps else None)
 
+    def _prefetched(self, dataset: Iterable):
+        """Yield the batches of ``dataset`` already on the device: batch k+1 is copied host -> device on a second
+        stream while step k runs (pinned host tensors make the copy asynchronous)."""
+        rt = core.runtime()
+        if not rt.on_gpu:
+            yield from dataset
+            return
+        main = torch.cuda.current_stream()
+        copy = self._copy_stream = getattr(self, "_copy_stream", None) or torch.cuda.Stream(device=rt.device)
+
+        def stage(batch):
+            leaves: List[torch.Tensor] = []
+            spec = _flatten(batch, leaves)
+            with torch.cuda.stream(copy):
+                moved = [t.to(rt.device, non_blocking=True) for t in leaves]
+                ev = torch.cuda.Event()
+                ev.record(copy)
+            for t in moved:
+                t.record_stream(main)
+            return _unflatten(spec, iter(moved)), ev
+
+        it = iter(dataset)
+        try:
+            nxt = stage(next(it))
+        except StopIteration:
+            return
+        while nxt is not None:
+            cur, ev = nxt
+            try:
+                nxt = stage(next(it))
+            except StopIteration:
+                nxt = None
+            main.wait_event(ev)
+            yield cur
+
     def fit(self, dataset: Iterable, epochs: int = 1, steps_per_epoch: Optional[int] = None, callbacks: Sequence = (),
-            verbose: int = 0, log_every: int = 100):
-        """Iterate ``dataset`` (yielding ``(features, labels)``) for ``epochs`` passes."""
+            verbose: int = 0, log_every: int = 100, prefetch: bool = True, record_step_loss: bool = False):
+        """Iterate ``dataset`` (yielding ``(features, labels)``) for ``epochs`` passes.
+
+        ``prefetch``: copy the next batch to the device on a second stream while the current step runs.
+        ``record_step_loss``: read every step's loss back to the host (``history["step_loss"]``); the 4-byte copy
+        of step k is issued right behind the step and collected while step k+1 runs, so it costs no stall."""
         with start_as_current_span("fit"):
             history = {"loss": []}
+            if record_step_loss:
+                history["step_loss"] = []
+            rt = core.runtime()
+            gpu = rt.on_gpu
+            pinned = None
+            if gpu and record_step_loss:
+                if getattr(self, "_pinned_loss", None) is None:      # page-locked allocation is slow: once per model
+                    self._pinned_loss = [torch.zeros((), dtype=torch.float32).pin_memory() for _ in range(2)]
+                pinned = self._pinned_loss
+            events = [None, None]
             for cb in callbacks:
                 cb.set_model(self)
                 cb.on_train_begin()
@@ -374,14 +423,31 @@ class Model(nn.Module):
                 for cb in callbacks:
                     cb.on_epoch_begin(epoch)
                 last = None
-                for i, batch in enumerate(dataset):
+                pending = None       # index of the pinned slot holding the previous step's loss
+                source = self._prefetched(dataset) if prefetch else dataset
+                for i, batch in enumerate(source):
                     if steps_per_epoch is not None and i >= steps_per_epoch:
                         break
                     last = self.train_step(batch)
+                    if record_step_loss:
+                        if pinned is None:
+                            history["step_loss"].append(float(last))
+                        else:
+                            slot = i & 1
+                            pinned[slot].copy_(last.detach(), non_blocking=True)
+                            events[slot] = torch.cuda.Event()
+                            events[slot].record()
+                            if pending is not None:
+                                events[pending].synchronize()
+                                history["step_loss"].append(float(pinned[pending]))
+                            pending = slot
                     if verbose and (i + 1) % log_every == 0:
                         print(f"epoch {epoch} step {i + 1} loss {float(last):.5f}", flush=True)
                     if self.stop_training:
                         break
+                if pinned is not None and pending is not None:
+                    events[pending].synchronize()
+                    history["step_loss"].append(float(pinned[pending]))
                 core.runtime().check_status()
                 history["loss"].append(float(last) if last is not None else float("nan"))
                 for cb in callbacks:

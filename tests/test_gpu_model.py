@@ -116,3 +116,22 @@ def test_ragged_batches_with_repeating_shapes_replay_from_graphs(tn_gpu):
     assert len(m2._graphs) == 2, len(m2._graphs)
     for a, b in zip(l1, l2):
         assert abs(a - b) < 5e-2 * max(1.0, abs(a)), (l1, l2)
+
+
+def test_fit_prefetches_and_reads_every_step_loss(tn_gpu):
+    """Model.fit with host batches: the next batch is staged on a copy stream, every step's loss reaches the host
+    (one step late), and the trajectory equals train_on_batch on the same data."""
+    tn = tn_gpu
+    B = 256
+    m1, slots = _make(tn, graph=True, B=B)
+    m2, _ = _make(tn, graph=True, B=B)
+    data = [( {k: (v.pin_memory() if k != tn.data.PACKED_KEY else v.pin_memory()) for k, v in f.items()}, y.pin_memory())
+            for f, y in _batches(tn, slots, B, 10)]
+    ref = [float(m1.train_on_batch(f, y)) for f, y in data]
+    hist = m2.fit(iter(data), epochs=1, prefetch=True, record_step_loss=True)
+    torch.cuda.synchronize()
+    tn.core.runtime().check_status()
+    assert len(hist["step_loss"]) == len(data)
+    for a, b in zip(ref, hist["step_loss"]):
+        assert abs(a - b) < 5e-2 * max(1.0, abs(a)), (ref, hist["step_loss"])
+    assert hist["loss"][-1] == hist["step_loss"][-1]
