@@ -74,6 +74,22 @@ def main():
     torch.cuda.synchronize()
     rt.check_status()
     serving_oks = rt.all_gather_object(serving_ok)
+    # checkpoint round trip across the ranks: save (streamed export per rank), move the weights on, load, same predictions
+    ck = out + ".ckpt"
+    f0, y0 = data[0]
+    _, p_before = model.predict_step((f0, y0))
+    p_before = p_before.detach().float().cpu().clone()
+    model.save_weights(ck, mode="bin")
+    model.train_on_batch(f0, y0)
+    _, p_moved = model.predict_step((f0, y0))
+    model.is_loaded_from_checkpoint = False
+    model.load_weights(ck, mode="bin")
+    _, p_after = model.predict_step((f0, y0))
+    torch.cuda.synchronize()
+    rt.check_status()
+    ckpt_ok = bool(torch.allclose(p_after.detach().float().cpu(), p_before, atol=2e-3)) and \
+        not bool(torch.allclose(p_moved.detach().float().cpu(), p_before, atol=1e-6))
+    ckpt_oks = rt.all_gather_object(ckpt_ok)
     rows = [int(m.table.n_rows) for m in (model.linear_emb, model.deep_emb)]
     allrows = rt.all_gather_object(rows)
     w = model.sub_model.head.weight.detach().float().cpu()
@@ -81,7 +97,7 @@ def main():
     if rt.rank == 0:
         same = all(torch.equal(ws[0], x) for x in ws)
         json.dump({"world": rt.world, "losses": losses, "rows": [sum(r[i] for r in allrows) for i in range(2)],
-                   "replicas_identical": same, "bn_sync_ok": all(bn_oks), "serving_ok": all(serving_oks), "graph": model._graph is not None,
+                   "replicas_identical": same, "bn_sync_ok": all(bn_oks), "serving_ok": all(serving_oks), "ckpt_ok": all(ckpt_oks), "graph": model._graph is not None,
                    "multimem": bool(getattr(model.optimizer.table, "uses_multimem", False))}, open(out, "w"))
     tn.core.shutdown()
 
