@@ -60,7 +60,42 @@ class ClockSampler:
         self.rows = []
         self.proc = None
 
+    def _start_nvml(self) -> bool:
+        """Read-only NVML polling every ~4 ms from a thread (the timed region of a short run lasts milliseconds)."""
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(self.gpu)
+            smax = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+            pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            return False
+        bits = [("hw_slowdown", getattr(pynvml, "nvmlClocksThrottleReasonHwSlowdown", 0x8)),
+                ("hw_thermal_slowdown", getattr(pynvml, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40)),
+                ("sw_thermal_slowdown", getattr(pynvml, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20)),
+                ("sw_power_cap", getattr(pynvml, "nvmlClocksThrottleReasonSwPowerCap", 0x4))]
+        self._stop = False
+
+        def poll():
+            while not self._stop:
+                try:
+                    sm = float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
+                    mask = int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h))
+                    act = ["Active" if mask & b else "Not Active" for _, b in bits]
+                    self.rows.append((time.time(), ",".join([str(self.gpu), str(sm), str(smax), "0", "x"] + act)))
+                except Exception:
+                    pass
+                time.sleep(0.004)
+
+        self.thread = threading.Thread(target=poll, daemon=True)
+        self.thread.start()
+        self.nvml = True
+        return True
+
     def start(self):
+        self.nvml = False
+        if self._start_nvml():
+            return
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
                                           "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
@@ -74,14 +109,18 @@ class ClockSampler:
             self.rows.append((time.time(), line.strip()))
 
     def stop(self, t0: float, t1: float):
-        if self.proc is None:
+        if getattr(self, "nvml", False):
+            self._stop = True
+            self.thread.join(timeout=1)
+        elif self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=2)
-        except Exception:
-            self.proc.kill()
+        else:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
         sm, smax, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for t, line in self.rows:
