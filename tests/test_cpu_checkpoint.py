@@ -156,3 +156,39 @@ def test_bn_file_layout(tmp_path):
     assert raw == struct.pack("<?I6d", True, 2, 1.5, 3.0, 10.0, 2.5, 4.0, 10.0)
     pctr, s2, q2, c2 = ext.read_bn_file(path)
     assert pctr and np.array_equal(s2, s) and np.array_equal(q2, q) and np.array_equal(c2, c)
+
+
+@pytest.mark.parametrize("mode", ["txt", "bin"])
+def test_streaming_writer_equals_one_shot_write(tmp_path, mode):
+    """A shard appended in pieces (in any order, or already grouped by block file as the device export delivers it)
+    produces the same block contents as one write of the whole shard."""
+    rng = np.random.default_rng(4)
+    dim = 3
+    signs = np.unique(rng.integers(1, 2 ** 62, 3000, dtype=np.int64).astype(np.uint64))
+    rows = _adagrad_rows(signs, dim, rng)
+    ext.write_sparse_dir(str(tmp_path / "one"), mode, ADAGRAD, dim, True, signs, rows, True, 5.0, 6, 0)
+    w = ext.SparseDirWriter(str(tmp_path / "pieces"), mode, ADAGRAD, dim, True, True, 5.0, 6, 0)
+    for lo in range(0, len(signs), 700):
+        w.append(signs[lo:lo + 700], rows[lo:lo + 700])
+    kept = w.close()
+    blocks = np.array([_block_of(int(s)) for s in signs])
+    order = np.argsort(blocks, kind="stable")
+    gs, gr = signs[order], rows[order]
+    offsets = np.concatenate([[0], np.cumsum(np.bincount(blocks, minlength=8))]).astype(np.int64)
+    g = ext.SparseDirWriter(str(tmp_path / "grouped"), mode, ADAGRAD, dim, True, True, 5.0, 6, 0)
+    g.append_grouped(gs, gr, offsets)
+    assert g.close() == kept
+    sfx = "_bin" if mode == "bin" else ""
+    total = 0
+    for b in range(8):
+        one = gzip.open(tmp_path / "one" / f"block_{b}{sfx}.gz", "rb").read()
+        assert gzip.open(tmp_path / "pieces" / f"block_{b}{sfx}.gz", "rb").read() == one
+        assert gzip.open(tmp_path / "grouped" / f"block_{b}{sfx}.gz", "rb").read() == one
+    s2, r2 = ext.read_sparse_dir(str(tmp_path / "pieces"), ADAGRAD, dim, True)
+    assert len(s2) == kept and 0 < kept < len(signs)            # the eviction rule dropped some rows
+    with pytest.raises(Exception):
+        g.append(signs[:1], rows[:1])                           # closed
+    bad = offsets.copy(); bad[1], bad[2] = bad[2], bad[1]
+    g2 = ext.SparseDirWriter(str(tmp_path / "bad"), mode, ADAGRAD, dim, True, False, 0.0, 0, 0)
+    with pytest.raises(Exception):
+        g2.append_grouped(gs, gr, bad)
