@@ -1,7 +1,7 @@
 """Small, self-contained launches of the hot kernels, for timing with CUDA events and for capturing
 with Nsight Compute (one GPU, a few launches, a few hundred MB on the device).
 
-    python benchmarks/kernel_cases.py gemm_fwd|gemm_dgrad|gemm_wgrad|gemm_big|sparse|deepfm|dense  [--iters N]
+    python benchmarks/kernel_cases.py gemm_fwd|gemm_dgrad|gemm_wgrad|gemm_big|sparse|deepfm|dense|small_ops  [--iters N]
 
 Each case prints the per-launch device time (CUDA events around N back-to-back launches after warm-up,
 inputs larger than L2 for the sparse cases) and the algorithmic bytes / FLOPs so a roofline fraction
@@ -44,7 +44,7 @@ def peaks():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm_fwd", "gemm_dgrad", "gemm_wgrad", "gemm_big", "sparse", "deepfm", "dense"])
+    ap.add_argument("case", choices=["gemm_fwd", "gemm_dgrad", "gemm_wgrad", "gemm_big", "sparse", "deepfm", "dense", "small_ops"])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--batch", type=int, default=8192)
     a = ap.parse_args()
@@ -107,6 +107,46 @@ def main():
         out.update(pull_us=tp, push_us=tb - tp, unique=nu, ids=B * S, phases_us=lk.pull_phase_us(), pull_GBps=pull_bytes / tp / 1e3,
                    push_GBps=push_bytes / (tb - tp) / 1e3, pull_frac_of_hbm=pull_bytes / tp / 1e3 / pk["hbm_gbs"],
                    push_frac_of_hbm=push_bytes / (tb - tp) / 1e3 / pk["hbm_gbs"], peak=tag)
+    elif a.case == "small_ops":
+        # the remaining hand-written kernels against the library op a PyTorch user would reach for
+        import torch.nn.functional as TF
+        from tensornet_b200.ops import functional as F
+        from tensornet_b200.ops.unique import UniqueAssign
+        import bench
+        B, S, D = a.batch, 26, 16
+        ids = bench.make_batches(1, B, S, 13, 3)[0][0].to(dev).reshape(-1)
+        ua = UniqueAssign(B * S)
+        res = {"unique_assign_us": timed(lambda: ua(ids), a.iters),
+               "torch_unique_us": timed(lambda: torch.unique(ids, return_inverse=True, return_counts=True), a.iters)}
+        # bag pooling: 100 slots x Poisson(5) ids per bag, dim 64, sum
+        nb = B * 20
+        lens = torch.poisson(torch.full((nb,), 5.0)).clamp(min=1).long()
+        offs = torch.cat([torch.zeros(1, dtype=torch.long), lens.cumsum(0)]).to(dev)
+        nnz = int(offs[-1])
+        U = torch.randn(200_000, 64, device=dev)
+        inv = torch.randint(0, 200_000, (nnz,), device=dev, dtype=torch.int32)
+        pooled = torch.empty(B, 20 * 64, device=dev)
+        offs32 = offs.int()
+        res["pool_fwd_us"] = timed(lambda: ext.pool_fwd(U, 64, inv, offs32, B, 20, 64, 0, pooled, 20 * 64), a.iters)
+        inv64 = inv.long()
+        res["torch_embedding_bag_us"] = timed(lambda: TF.embedding_bag(inv64, U, offs[:-1], mode="sum"), a.iters)
+        gU = torch.zeros(200_000, 64, device=dev)
+        gout = torch.randn(B, 20 * 64, device=dev)
+        res["pool_bwd_us"] = timed(lambda: ext.pool_bwd(gU, 64, inv, offs32, B, 20, 64, 64, 0, gout, 20 * 64), a.iters)
+        bag = torch.repeat_interleave(torch.arange(nb, device=dev), lens.to(dev))
+        gflat = gout.view(B, 20, 64).permute(1, 0, 2).reshape(nb, 64)
+        res["torch_index_add_us"] = timed(lambda: gU.index_add_(0, inv64, gflat[bag]), a.iters)
+        # FM second-order term and BCE
+        E = torch.randn(B, S * D, device=dev)
+        res["fm_fwd_us"] = timed(lambda: F.fm(E, S, D), a.iters)
+        def torch_fm():
+            x = E.view(B, S, D); s_ = x.sum(1)
+            return 0.5 * (s_ * s_ - (x * x).sum(1)).sum(1, keepdim=True)
+        res["torch_fm_us"] = timed(torch_fm, a.iters)
+        logit, y = torch.randn(B, 1, device=dev), (torch.rand(B, device=dev) < 0.3).float()
+        res["bce_us"] = timed(lambda: F.bce_with_logits(logit, y), a.iters)
+        res["torch_bce_us"] = timed(lambda: (TF.binary_cross_entropy_with_logits(logit.view(-1), y), torch.sigmoid(logit)), a.iters)
+        out.update({k: round(v, 2) for k, v in res.items()}, nnz=nnz, ids=int(ids.numel()))
     elif a.case == "deepfm":
         import bench
         slots = [str(i) for i in range(1, 27)]
