@@ -827,7 +827,8 @@ cudaError_t launch_sparse_pull(const PullArgs& args, int work_items, cudaStream_
   if (grid > grid_max[dev]) grid = grid_max[dev];
   const size_t smem = (size_t)args.tile_rows * args.c.ustride * sizeof(float) * (kThreads / 32);
   static bool attr_set[64] = {false};
-  if (smem > 48 * 1024 && !attr_set[dev]) {
+  // static + dynamic shared memory beyond 48 KiB needs the opt-in; a 48 KiB tile buffer alone already crosses it
+  if (smem > 32 * 1024 && !attr_set[dev]) {
     cudaError_t e = cudaFuncSetAttribute((const void*)sparse_pull_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;

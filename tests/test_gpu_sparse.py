@@ -204,3 +204,24 @@ def test_streamed_export_matches_dump_and_applies_eviction(tn_gpu, status_ok, tm
             assert np.array_equal(r[:dim], ref[:dim])
         else:
             assert np.allclose(r[:dim], ref[:dim], rtol=1e-5, atol=1e-6)     # text keeps 6 significant digits
+
+
+def test_staged_row_return_with_a_48k_tile_buffer(tn_gpu, status_ok):
+    """Row width 12 floats (dim 8 + two CVM columns, padded) makes the staged return ask for exactly 48 KiB of dynamic
+    shared memory; together with the kernel's static words that needs the large-shared-memory opt-in."""
+    tn = tn_gpu
+    old = tn.core.config.staged_row_return
+    tn.core.config.staged_row_return = 1
+    try:
+        t, lk = _mk(tn, tn.core.AdaGrad(learning_rate=0.01, initial_scale=0.2), 8, use_cvm=True, rows=1 << 12, max_unique=1024)
+        assert lk.ustride == 12
+        ids = torch.arange(1, 601, dtype=torch.int64, device=t.dev) * 7919
+        inv = lk.pull(ids, training=True)
+        torch.cuda.synchronize()
+        rows = _host_rows(t)
+        U = lk.U.cpu()
+        for i in (0, 17, 599):
+            assert np.allclose(U[int(inv[i]), :8].numpy(), rows[int(ids[i])][:8])
+        lk.push()
+    finally:
+        tn.core.config.staged_row_return = old
