@@ -437,6 +437,10 @@ void launch_gemv_bwd(const void* Z, int ld, int B, int K, const float* w, const 
     return;
   }
   int blocks = B / 32; if (blocks < 1) blocks = 1; if (blocks > 296) blocks = 296;
+  if (K * sizeof(float) > 40 * 1024) {   // very wide last layer: the weight copy needs the large-shared-memory opt-in
+    static bool opted = false;
+    if (!opted) { cudaFuncSetAttribute((const void*)gemv_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); opted = true; }
+  }
   launch_pdl(gemv_bwd_kernel, dim3(blocks), dim3(256), K * sizeof(float), st, reinterpret_cast<const __nv_bfloat16*>(Z), ld, B, K, w, dy,
                                                           reinterpret_cast<__nv_bfloat16*>(dZ), gw, relu_cols);
 }

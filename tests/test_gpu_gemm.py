@@ -190,3 +190,26 @@ def test_cross_v2_backward_elementwise_kernels(tn_gpu, status_ok):
     out = torch.empty(n, dtype=torch.bfloat16, device=dev)
     _ext().cross_v2_bwd_final(gx0, gg, out)
     assert torch.equal(out, (gx0 + gg.float()).bfloat16())
+
+
+@pytest.mark.parametrize("K", [300, 6672, 13000])
+def test_head_forward_backward_wide(tn_gpu, status_ok, K):
+    """Dense(1) head against fp32 matmul; 13000 columns need more than 48 KiB of shared memory for the weight copy."""
+    from tensornet_b200.ops import functional as F
+    dev = torch.device("cuda", 0)
+    B, ld = 512, (K + 8 + 7) // 8 * 8
+    g = torch.Generator(device="cpu").manual_seed(K)
+    z = (torch.randn(B, ld, generator=g) * 0.5).to(dev).to(torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(K, generator=g) * 0.05).to(dev)
+    w.grad = None
+    y = F.head(z, w)
+    ref = z.detach().float()[:, :K] @ w
+    assert torch.allclose(y.view(-1), ref, rtol=2e-3, atol=2e-3)
+    gy = torch.randn(B, 1, generator=g).to(dev)
+    y.backward(gy)
+    torch.cuda.synchronize()
+    dz_ref = gy * w.view(1, -1)
+    assert torch.allclose(z.grad.float()[:, :K], dz_ref, rtol=2e-2, atol=2e-3)
+    gw = F._grad_buffer(w)
+    gw_ref = z.detach().float()[:, :K].t() @ gy.view(-1)
+    assert torch.allclose(gw[:K], gw_ref, rtol=2e-2, atol=5e-2)
