@@ -170,3 +170,40 @@ def test_tools_merge_resize_and_serving_dictionary(tmp_path):
     want = torch.sigmoid(head(mlp(F.concat_cast([emb], ones=True)))).view(-1)
     got = eng.infer(ids)
     assert torch.allclose(got, want, atol=2e-2)
+
+
+def test_pcgrad_projection_and_two_task_model():
+    """Conflicting task gradients are projected onto each other's normal plane; agreeing ones are summed untouched
+    (tensornet/optimizer/pcgrad.py).  Then one two-task step on the CPU path moves dense and sparse weights."""
+    from tensornet_b200.optimizer import PCGrad
+
+    g1 = torch.tensor([1.0, 0.0])
+    g2 = torch.tensor([-1.0, 1.0])                      # g1.g2 = -1: conflict
+    p1 = g1 - (g1 @ g2) / (g2 @ g2) * g2                # (0.5, 0.5)
+    p2 = g2 - (g2 @ g1) / (g1 @ g1) * g1                # (0, 1)
+    got = PCGrad.project(None, [g1, g2])
+    assert torch.allclose(got, p1 + p2)
+    assert torch.allclose(PCGrad.project(None, [g1, torch.tensor([2.0, 1.0])]), torch.tensor([3.0, 1.0]))
+
+    class TwoTask(tn.model.PCGradModel):
+        def __init__(self):
+            super().__init__()
+            self.emb = tn.layers.EmbeddingFeatures(_cols(["a", "b"], 4), tn.core.AdaGrad(learning_rate=0.05), name="emb",
+                                                   is_concat=True)
+            self.tower = torch.nn.Linear(8, 2)
+
+        def forward(self, features):
+            return self.tower(self.emb(features))
+
+    torch.manual_seed(0)
+    m = TwoTask()
+    m.compile(optimizer=PCGrad(tn.core.Adam(learning_rate=0.01)))
+    feats = {"a": torch.tensor([1, 2, 3, 1]), "b": torch.tensor([7, 7, 8, 9])}
+    labels = torch.tensor([[1.0, 0.0], [0.0, 0.0], [1.0, 1.0], [0.0, 1.0]])
+    l0 = float(m.train_on_batch(feats, labels))
+    w0 = m.tower.weight.detach().clone()
+    row0 = m.emb.table.native.pull(np.array([1], np.uint64))[0].copy()
+    losses = [float(m.train_on_batch(feats, labels)) for _ in range(30)]
+    assert losses[-1] < l0
+    assert not torch.allclose(m.tower.weight.detach(), w0)
+    assert not np.allclose(m.emb.table.native.pull(np.array([1], np.uint64))[0], row0)
