@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import glob
 import os
-from typing import Iterable, Iterator, List, Sequence
+from typing import Iterable, Iterator, List, Optional, Sequence
 
 import torch
 
@@ -39,13 +39,32 @@ def reset_balance_dataset():
 class BalanceDataset:
     """Wrap an iterable of batches so that all ranks yield the same number of batches.
 
-    Each round every rank tells the others whether it still has a batch.  While at least one rank
-    has data, ranks without data are handed a batch by the lowest-ranked donor that has more than
-    it needs for itself (donors read one batch ahead, up to ``buffer_size`` batches)."""
+    One round = one synchronous step.  Every rank reports how many batches it holds (each reads ahead up to
+    ``min(buffer_size, world)`` batches, so a single rank that still has input can feed all the others).  While
+    the ranks hold at least ``world`` batches between them, every rank without one is handed a batch by the
+    rank with the most to spare, and every rank yields exactly one batch.  When fewer than ``world`` batches
+    are left all ranks stop together; at most ``world - 1`` trailing batches of a pass are not used."""
 
     def __init__(self, input_dataset: Iterable, buffer_size: int = 100):
         self._input = input_dataset
         self.buffer_size = buffer_size
+
+    @staticmethod
+    def plan(have: Sequence[int]) -> Optional[List[tuple]]:
+        """Gifts ``(receiver, donor)`` for one round given every rank's batch count, or None when the round
+        cannot give one batch to every rank.  Pure and deterministic: all ranks compute the same plan."""
+        world = len(have)
+        if sum(have) < world:
+            return None
+        spare = {r: h - 1 for r, h in enumerate(have) if h >= 2}
+        gifts = []
+        for n in (r for r, h in enumerate(have) if h == 0):
+            d = max(spare, key=lambda r: (spare[r], -r))
+            gifts.append((n, d))
+            spare[d] -= 1
+            if spare[d] == 0:
+                del spare[d]
+        return gifts
 
     def __iter__(self) -> Iterator:
         rt = runtime()
@@ -55,10 +74,11 @@ class BalanceDataset:
             return
         buf: List = []
         exhausted = False
+        ahead = max(2, min(int(self.buffer_size), rt.world))
 
         def refill():
             nonlocal exhausted
-            while not exhausted and len(buf) < 2:
+            while not exhausted and len(buf) < ahead:
                 try:
                     buf.append(next(it))
                 except StopIteration:
@@ -67,25 +87,14 @@ class BalanceDataset:
         while True:
             refill()
             have = rt.all_gather_object(len(buf))
-            if sum(have) == 0:
+            gifts = self.plan(have)
+            if gifts is None:
                 return
-            needy = [r for r, h in enumerate(have) if h == 0]
-            donors = [r for r, h in enumerate(have) if h >= 2]
-            gifts = {}
-            for n, d in zip(needy, donors):
-                gifts[n] = d
             # every rank takes part in every exchange so the object collectives stay matched
             mine = None
-            for n, d in sorted(gifts.items()):
+            for n, d in gifts:
                 payload = buf.pop() if rt.rank == d else None
                 got = rt.broadcast_object(payload, src=d)
                 if rt.rank == n:
                     mine = got
-            if have[rt.rank] > 0:
-                yield buf.pop(0)
-            elif mine is not None:
-                yield mine
-            elif len(needy) > len(donors):
-                # not enough spare batches this round: everyone stops together
-                if all(h <= 1 for h in have) and any(h == 0 for h in have):
-                    return
+            yield buf.pop(0) if have[rt.rank] > 0 else mine
