@@ -68,6 +68,7 @@ def main():
     ap.add_argument("--save-mode", default="txt", choices=["txt", "bin"])
     ap.add_argument("--predict", action="store_true")
     ap.add_argument("--max-steps", type=int, default=0)
+    ap.add_argument("--step-log", default="", help="append one JSON line per 100 steps (throughput, loss, table sizes) to this file")
     a = ap.parse_args()
 
     strategy = tn.distribute.PsStrategy()
@@ -87,7 +88,8 @@ def main():
         ds = read_dataset(files, a.batch_size, slots, a.dense_dim, rt.rank, rt.world)
         cb = tn.callbacks.PsWeightCheckpoint(a.model_dir, need_save_model=True, dt=day, delta_days=1, save_mode=a.save_mode)
         t0 = time.time()
-        hist = model.fit(ds, epochs=1, steps_per_epoch=a.max_steps or None, callbacks=[cb])
+        cbs = [cb] + ([tn.utils.StepLog(a.step_log, every=100)] if a.step_log else [])
+        hist = model.fit(ds, epochs=1, steps_per_epoch=a.max_steps or None, callbacks=cbs)
         steps = model.optimizer.iterations
         report["days"].append({"day": day, "loss": hist["loss"][-1], "seconds": time.time() - t0, "steps": steps,
                                **{k: v for k, v in model.metric_sums().items() if k in ("ctr", "pctr", "copc")}})

@@ -14,6 +14,7 @@ from . import data
 from . import metric
 from . import callbacks
 from . import distribute
+from . import utils
 from .version import VERSION as __version__
 
 __all__ = ["core", "feature_column", "layers", "optimizer", "model", "models", "data", "metric", "callbacks",

@@ -419,6 +419,7 @@ class Model(nn.Module):
             for cb in callbacks:
                 cb.set_model(self)
                 cb.on_train_begin()
+            batch_cbs = [cb for cb in callbacks if hasattr(cb, "on_train_batch_end")]
             for epoch in range(epochs):
                 for cb in callbacks:
                     cb.on_epoch_begin(epoch)
@@ -441,6 +442,8 @@ class Model(nn.Module):
                                 events[pending].synchronize()
                                 history["step_loss"].append(float(pinned[pending]))
                             pending = slot
+                    for cb in batch_cbs:
+                        cb.on_train_batch_end(i, {"batch": int(batch[1].shape[0])})
                     if verbose and (i + 1) % log_every == 0:
                         print(f"epoch {epoch} step {i + 1} loss {float(last):.5f}", flush=True)
                     if self.stop_training:

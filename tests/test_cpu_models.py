@@ -59,3 +59,38 @@ def test_model_family_trains_on_cpu(kind):
     p = m.predict_on_batch(f)
     p = torch.as_tensor(p).reshape(-1)
     assert p.shape[0] == 64 and float(p.min()) >= 0.0 and float(p.max()) <= 1.0
+
+
+def test_interrupted_save_keeps_previous_done_file(tmp_path):
+    """The done-file is written last (tensornet/model/Model.py:165-172): a save that dies between the sparse and the
+    dense part leaves `_checkpoint` naming the previous day, and a fresh model resumes from that day."""
+    torch.manual_seed(2)
+    m, _ = _build("wide_deep")
+    m.compile(optimizer=tn.optimizer.Optimizer(tn.core.Adam(learning_rate=0.01)))
+    f, y = _batch()
+    for _ in range(3):
+        m.train_on_batch(f, y)
+    root = str(tmp_path / "model")
+    m.save_weights(root, dt="day1", mode="bin")
+    want = torch.as_tensor(m.predict_on_batch(f)).reshape(-1).clone()
+    for _ in range(3):
+        m.train_on_batch(f, y)
+
+    def boom(path):
+        raise OSError("disk full")
+
+    real = m.optimizer.save_dense_table
+    m.optimizer.save_dense_table = boom
+    with pytest.raises(OSError):
+        m.save_weights(root, dt="day2", mode="bin")
+    m.optimizer.save_dense_table = real
+    assert tn.model.read_last_train_dt(root) == "day1"
+
+    tn.core.shutdown(); tn.core.config.force_cpu = True; tn.core.init()
+    torch.manual_seed(3)
+    m2, _ = _build("wide_deep")
+    m2.compile(optimizer=tn.optimizer.Optimizer(tn.core.Adam(learning_rate=0.01)))
+    m2.predict_on_batch(f)                       # builds the dense table
+    assert m2.load_weights(root, mode="bin")
+    got = torch.as_tensor(m2.predict_on_batch(f)).reshape(-1)
+    assert torch.allclose(got, want, atol=1e-5)
