@@ -23,6 +23,7 @@ from .. import core
 from .._opentelemetry import start_as_current_span
 from ..data.features import PACKED_KEY, PackedFeatures, Ragged
 from ..ops import functional as F
+from ..parallel.symm import verify_all_arenas
 
 
 # ----------------------------------------------------------------------------------------------
@@ -452,6 +453,7 @@ class Model(nn.Module):
                     events[pending].synchronize()
                     history["step_loss"].append(float(pinned[pending]))
                 core.runtime().check_status()
+                verify_all_arenas()
                 history["loss"].append(float(last) if last is not None else float("nan"))
                 for cb in callbacks:
                     cb.on_epoch_end(epoch, {"loss": history["loss"][-1]})
@@ -490,6 +492,7 @@ class Model(nn.Module):
     def save_weights(self, filepath: str, dt: str = "", mode: str = "txt", **kwargs):
         """<filepath>/<dt>/{sparse_table,dense_table,bn_table,torch_checkpoint.pt}; ``_checkpoint`` last."""
         rt = core.runtime()
+        verify_all_arenas()       # never write a checkpoint from memory a stray peer store has damaged
         cp_dir = os.path.join(filepath, dt) if dt else filepath
         if rt.rank == 0:
             os.makedirs(cp_dir, exist_ok=True)

@@ -10,6 +10,7 @@ buffer is an ordinary tensor and the peer table has a single entry.
 from __future__ import annotations
 
 import os
+import weakref
 from typing import List, Optional
 
 import torch
@@ -73,13 +74,24 @@ class SymmBuffer:
         return self.mc_ptr + offset if self.mc_ptr else 0
 
 
+_GUARD_BYTES = 256
+_GUARD_PATTERN = 0xA5
+_arenas = weakref.WeakSet()
+
+
 class SymmArena:
-    """Carves named, 256-byte aligned regions out of one SymmBuffer."""
+    """Carves named, 256-byte aligned regions out of one SymmBuffer.
+
+    Every region is followed by a 256-byte guard filled with a fixed pattern.  Peers write into these regions at
+    offsets their kernels compute, so an offset bug on any GPU shows up as a damaged guard on the GPU that owns
+    the memory; ``verify`` (and ``verify_all_arenas``, called at the end of every training pass and before a
+    checkpoint is written) reads the guards back and names the region in front of the damaged one."""
 
     def __init__(self, layout):
         # layout: list of (name, shape, dtype)
         self.offsets = {}
         self.meta = {}
+        self.guards = {}
         off = 0
         for name, shape, dtype in layout:
             n = 1
@@ -89,7 +101,19 @@ class SymmArena:
             self.offsets[name] = off
             self.meta[name] = (tuple(int(s) for s in shape), dtype)
             off += (nb + 255) // 256 * 256
+            self.guards[name] = off
+            off += _GUARD_BYTES
         self.buf = SymmBuffer(max(off, 256))
+        if self.guards:
+            g = self.buf.local[: off].view(-1, _GUARD_BYTES)
+            idx = torch.tensor([o // _GUARD_BYTES for o in self.guards.values()], device=g.device)
+            g[idx] = _GUARD_PATTERN
+            self._guard_idx = idx
+            if runtime().on_gpu:
+                torch.cuda.synchronize()
+            if runtime().world > 1:
+                runtime().barrier()       # no peer may start writing before every guard is in place
+        _arenas.add(self)
 
     def tensor(self, name: str) -> torch.Tensor:
         shape, dtype = self.meta[name]
@@ -100,3 +124,24 @@ class SymmArena:
 
     def mc(self, name: str) -> int:
         return self.buf.mc(self.offsets[name])
+
+    def damaged(self) -> List[str]:
+        """Names of the regions whose trailing guard no longer holds the pattern (one small device read)."""
+        if not self.guards:
+            return []
+        end = max(self.guards.values()) + _GUARD_BYTES
+        g = self.buf.local[:end].view(-1, _GUARD_BYTES)[self._guard_idx]
+        bad = (g != _GUARD_PATTERN).any(dim=1).cpu().tolist()
+        return [name for name, b in zip(self.guards, bad) if b]
+
+    def verify(self):
+        bad = self.damaged()
+        if bad:
+            raise RuntimeError("symmetric memory was written out of bounds: the guard behind region(s) "
+                               + ", ".join(repr(b) for b in bad) + f" on rank {runtime().rank} is damaged")
+
+
+def verify_all_arenas():
+    """Check the guards of every live arena of this process."""
+    for a in list(_arenas):
+        a.verify()

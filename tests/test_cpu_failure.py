@@ -68,3 +68,25 @@ def test_bucket_overflow_and_bad_checkpoint_raise(tmp_path):
     with pytest.raises(RuntimeError, match="not create yet"):
         t.push(np.array([99], np.uint64), np.zeros((1, 4), np.float32), np.ones(1, np.float32), np.zeros(1, np.float32))
     tn.core.shutdown()
+
+
+def test_guard_words_behind_shared_regions_catch_a_stray_write():
+    """Every region of a symmetric arena is followed by a guard; a write past a region's end is reported by name."""
+    import torch
+    import tensornet_b200 as tn
+    from tensornet_b200.parallel.symm import SymmArena, verify_all_arenas
+
+    tn.core.shutdown(); tn.core.config.force_cpu = True; tn.core.init()
+    a = SymmArena([("inbox", (100,), torch.float32), ("flags", (8,), torch.int64), ("rows", (3, 5), torch.float32)])
+    a.tensor("inbox").fill_(1.0); a.tensor("flags").fill_(-1); a.tensor("rows").fill_(2.0)     # in-bounds writes
+    assert a.damaged() == []
+    verify_all_arenas()
+    assert a.offsets["flags"] >= a.offsets["inbox"] + 400 + 256
+    end_of_flags = a.offsets["flags"] + 256            # the region is padded to 256 bytes; the guard starts here
+    a.buf.local[end_of_flags + 3] = 0
+    assert a.damaged() == ["flags"]
+    with pytest.raises(RuntimeError, match="flags"):
+        verify_all_arenas()
+    a.buf.local[end_of_flags + 3] = 0xA5
+    verify_all_arenas()
+    tn.core.shutdown()
