@@ -135,3 +135,23 @@ def test_fit_prefetches_and_reads_every_step_loss(tn_gpu):
     for a, b in zip(ref, hist["step_loss"]):
         assert abs(a - b) < 5e-2 * max(1.0, abs(a)), (ref, hist["step_loss"])
     assert hist["loss"][-1] == hist["step_loss"][-1]
+
+
+@pytest.mark.gpu
+def test_step_log_windows_on_the_graph_path(tn_gpu, tmp_path):
+    """The structured step log closes its windows around graph-replayed steps and reads the table sizes."""
+    import json
+    tn = tn_gpu
+    B = 256
+    m, slots = _make(tn, graph=True, B=B)
+    data = list(_batches(tn, slots, B, 13))
+    path = str(tmp_path / "steps.jsonl")
+    log = tn.utils.StepLog(path, every=4)
+    m.fit(iter(data), epochs=1, callbacks=[log])
+    tn.core.runtime().check_status()
+    lines = [json.loads(l) for l in open(path)]
+    assert [l["steps"] for l in lines] == [4, 4, 4]
+    for l in lines:
+        assert l["examples"] == 4 * B and l["examples_per_s"] > 0 and l["loss"] > 0 and l["status"] == "ok"
+        for t in l["tables"].values():
+            assert t["rows"] > 0 and 0 < t["max_load"] < 1
