@@ -40,7 +40,8 @@ class BalanceDataset:
     """Wrap an iterable of batches so that all ranks yield the same number of batches.
 
     One round = one synchronous step.  Every rank reports how many batches it holds (each reads ahead up to
-    ``min(buffer_size, world)`` batches, so a single rank that still has input can feed all the others).  While
+    ``min(buffer_size, max(world, 16))`` batches, so a single rank that still has input can feed all the others,
+    and while every rank holds several batches one exchange covers several rounds).  While
     the ranks hold at least ``world`` batches between them, every rank without one is handed a batch by the
     rank with the most to spare, and every rank yields exactly one batch.  When fewer than ``world`` batches
     are left all ranks stop together; at most ``world - 1`` trailing batches of a pass are not used."""
@@ -74,7 +75,9 @@ class BalanceDataset:
             return
         buf: List = []
         exhausted = False
-        ahead = max(2, min(int(self.buffer_size), rt.world))
+        # read-ahead: enough for one rank to feed all others, and enough that ranks with plenty of input can agree
+        # on several rounds per exchange
+        ahead = max(2, min(int(self.buffer_size), max(rt.world, 16)))
 
         def refill():
             nonlocal exhausted
@@ -87,6 +90,12 @@ class BalanceDataset:
         while True:
             refill()
             have = rt.all_gather_object(len(buf))
+            if min(have) >= 2:
+                # every rank can serve the next rounds from its own buffer: no exchange until the poorest rank is
+                # down to its last batch (all ranks derive the same number from the same counts)
+                for _ in range(min(have) - 1):
+                    yield buf.pop(0)
+                continue
             gifts = self.plan(have)
             if gifts is None:
                 return

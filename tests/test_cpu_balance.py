@@ -40,14 +40,15 @@ def test_list_files_sorted_per_day_and_error(tmp_path):
 
 
 @pytest.mark.timeout(300)
-def test_three_ranks_with_unequal_input_take_equal_steps(tmp_path):
+@pytest.mark.parametrize("counts", [[11, 0, 2], [40, 9, 23]])
+def test_three_ranks_with_unequal_input_take_equal_steps(tmp_path, counts):
     script = tmp_path / "worker.py"
     script.write_text(textwrap.dedent("""
         import os
         import tensornet_b200 as tn
         tn.core.init()
         rank = tn.core.self_shard_id()
-        counts = [11, 0, 2]                    # 13 batches over 3 ranks: 4 rounds, one batch unused
+        counts = COUNTS                        # e.g. 13 batches over 3 ranks: 4 rounds, one batch unused
         ds = tn.data.BalanceDataset([(rank, i) for i in range(counts[rank])])
         seen = []
         for b in ds:
@@ -56,7 +57,7 @@ def test_three_ranks_with_unequal_input_take_equal_steps(tmp_path):
         print("SEEN", rank, seen, flush=True)
         tn.core.barrier()
         os._exit(0)
-    """))
+    """).replace("COUNTS", repr(counts)))
     s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
     procs = []
     for r in range(3):
@@ -70,7 +71,8 @@ def test_three_ranks_with_unequal_input_take_equal_steps(tmp_path):
         assert line, o[-2000:]
         _, r, rest = line[0].split(" ", 2)
         seen[int(r)] = eval(rest)
-    assert len(seen[0]) == len(seen[1]) == len(seen[2]) == 4
+    rounds = sum(counts) // 3
+    assert len(seen[0]) == len(seen[1]) == len(seen[2]) == rounds
     used = [b for r in range(3) for b in seen[r]]
-    assert len(set(used)) == 12                       # no batch is used twice
-    assert all(src in (0, 2) for src, _ in used)
+    assert len(set(used)) == 3 * rounds               # no batch is used twice
+    assert all(i < counts[src] for src, i in used)
