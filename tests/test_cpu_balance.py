@@ -1,5 +1,6 @@
 """BalanceDataset: ranks with unequal input take the same number of steps (the purpose of the reference's balance op,
 core/kernels/data/balance_dataset_ops.cc:198-311), checked on the pure planning rule and on three gloo ranks."""
+import json
 import os
 import socket
 import subprocess
@@ -44,7 +45,7 @@ def test_list_files_sorted_per_day_and_error(tmp_path):
 def test_three_ranks_with_unequal_input_take_equal_steps(tmp_path, counts):
     script = tmp_path / "worker.py"
     script.write_text(textwrap.dedent("""
-        import os
+        import json, os
         import tensornet_b200 as tn
         tn.core.init()
         rank = tn.core.self_shard_id()
@@ -54,7 +55,7 @@ def test_three_ranks_with_unequal_input_take_equal_steps(tmp_path, counts):
         for b in ds:
             seen.append(tuple(b))
             tn.core.barrier()                  # stands for the collectives of a training step
-        print("SEEN", rank, seen, flush=True)
+        print("SEEN", rank, json.dumps(seen), flush=True)
         tn.core.barrier()
         os._exit(0)
     """).replace("COUNTS", repr(counts)))
@@ -70,7 +71,7 @@ def test_three_ranks_with_unequal_input_take_equal_steps(tmp_path, counts):
         line = [l for l in o.splitlines() if l.startswith("SEEN")]
         assert line, o[-2000:]
         _, r, rest = line[0].split(" ", 2)
-        seen[int(r)] = eval(rest)
+        seen[int(r)] = [tuple(b) for b in json.loads(rest)]
     rounds = sum(counts) // 3
     assert len(seen[0]) == len(seen[1]) == len(seen[2]) == rounds
     used = [b for r in range(3) for b in seen[r]]
