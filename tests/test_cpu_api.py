@@ -207,3 +207,39 @@ def test_pcgrad_projection_and_two_task_model():
     assert losses[-1] < l0
     assert not torch.allclose(m.tower.weight.detach(), w0)
     assert not np.allclose(m.emb.table.native.pull(np.array([1], np.uint64))[0], row0)
+
+
+def test_dense_learning_rate_schedule_is_evaluated_every_step():
+    """``learning_rate`` may be a callable ``step -> float`` (the reference accepts a Keras schedule object,
+    core/main/py_wrapper.cc:47-59; tensornet/optimizer/optimizer.py:30-36): with the rate at zero nothing moves, and the
+    first non-zero step moves every weight by about that rate (Adam's first update is lr * sign(g))."""
+    seen = []
+
+    def sched(step):
+        seen.append(step)
+        return 0.0 if step < 2 else 0.5
+
+    opt = tn.core.Adam(learning_rate=sched)
+    assert tn.core.get_opt_learning_rate(opt) is sched          # handed back as given, like the reference
+
+    class Tiny(tn.model.Model):
+        def __init__(self):
+            super().__init__()
+            self.emb = tn.layers.EmbeddingFeatures(_cols(["a"], 4), tn.core.AdaGrad(learning_rate=0.0), name="e", is_concat=True)
+            self.lin = torch.nn.Linear(4, 1)
+
+        def forward(self, features):
+            return self.lin(self.emb(features))
+
+    torch.manual_seed(0)
+    m = Tiny()
+    m.compile(optimizer=tn.optimizer.Optimizer(opt))
+    f, y = {"a": torch.tensor([1, 2, 3, 4])}, torch.tensor([1.0, 0.0, 1.0, 0.0])
+    m.train_on_batch(f, y)
+    w0 = m.lin.weight.detach().clone()
+    m.train_on_batch(f, y)
+    assert torch.equal(m.lin.weight.detach(), w0)            # steps 0 and 1 ran with rate 0
+    m.train_on_batch(f, y)
+    moved = (m.lin.weight.detach() - w0).abs()
+    assert float(moved.max()) > 0.05 and float(moved.max()) < 0.6
+    assert seen[-3:] == [0, 1, 2] or seen[-1] == 2
