@@ -39,7 +39,12 @@ def get_opt_learning_rate(opt: OptimizerBase):
 
 
 def set_sparse_init_mode(opt: OptimizerBase, is_training: bool):
+    """Rows created while ``is_training`` is false start at zero instead of the random initial value
+    (core/main/py_wrapper.cc: ``set_sparse_init_mode``); applies to every table that uses ``opt``."""
     opt.sparse_zero_init = not is_training
+    for t in _sparse_tables:
+        if t.opt is opt:
+            t.refresh_opt()
 
 
 # ----------------------------------------------------------------------------- sparse

@@ -36,7 +36,7 @@ class CpuSparseTable:
 
     def _opt_dict(self):
         d = self.opt.sparse_params()
-        d["zero_init"] = int(self._zero_init)
+        d["zero_init"] = int(self._zero_init or self.opt.sparse_zero_init)
         return d
 
     def refresh_opt(self):

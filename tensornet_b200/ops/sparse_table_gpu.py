@@ -70,7 +70,7 @@ class GpuSparseTable:
 
     def _opt_dict(self):
         d = self.opt.sparse_params()
-        d["zero_init"] = int(self._zero_init)
+        d["zero_init"] = int(self._zero_init or self.opt.sparse_zero_init)
         return d
 
     def link(self, max_unique: int) -> "GpuSparseLink":

@@ -243,3 +243,17 @@ def test_dense_learning_rate_schedule_is_evaluated_every_step():
     moved = (m.lin.weight.detach() - w0).abs()
     assert float(moved.max()) > 0.05 and float(moved.max()) < 0.6
     assert seen[-3:] == [0, 1, 2] or seen[-1] == 2
+
+
+def test_set_sparse_init_mode_zeroes_new_rows_until_switched_back():
+    """core/main/py_wrapper.cc `set_sparse_init_mode`: rows created outside training start at zero."""
+    opt = tn.core.AdaGrad(learning_rate=0.1, initial_scale=1.0)
+    h = tn.core.create_sparse_table(opt, "t", 4)
+    t = tn.core.sparse_table(h)
+    a = t.native.pull(np.array([101], np.uint64))[0]
+    assert np.abs(a).sum() > 0
+    tn.core.set_sparse_init_mode(opt, False)
+    assert np.abs(t.native.pull(np.array([202], np.uint64))[0]).sum() == 0
+    assert np.allclose(t.native.pull(np.array([101], np.uint64))[0], a)       # existing rows are untouched
+    tn.core.set_sparse_init_mode(opt, True)
+    assert np.abs(t.native.pull(np.array([303], np.uint64))[0]).sum() > 0
