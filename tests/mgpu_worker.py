@@ -90,6 +90,21 @@ def main():
     ckpt_ok = bool(torch.allclose(p_after.detach().float().cpu(), p_before, atol=2e-3)) and \
         not bool(torch.allclose(p_moved.detach().float().cpu(), p_before, atol=1e-6))
     ckpt_oks = rt.all_gather_object(ckpt_ok)
+    # unequal input: rank 0 holds 9 batches, the others 3; BalanceDataset hands batches over so that every rank takes
+    # the same number of steps, the step log aggregates over ranks, the guard words of the shared regions are intact
+    from tensornet_b200.parallel.symm import verify_all_arenas
+    mine = [data[i % len(data)] for i in range(9 if rt.rank == 0 else 3)]
+    log = tn.utils.StepLog(None, every=2)
+    steps0 = model.optimizer.iterations
+    model.fit(tn.data.BalanceDataset(mine), epochs=1, callbacks=[log], prefetch=False)
+    torch.cuda.synchronize()
+    rt.check_status()
+    verify_all_arenas()
+    took = model.optimizer.iterations - steps0
+    tooks = rt.all_gather_object(took)
+    balance_ok = len(set(tooks)) == 1 and took == (9 + 3 * (rt.world - 1)) // rt.world and len(log.records) >= 1 \
+        and all(r["world"] == rt.world and r["examples"] == r["steps"] * Bg for r in log.records)
+    balance_oks = rt.all_gather_object(bool(balance_ok))
     rows = [int(m.table.n_rows) for m in (model.linear_emb, model.deep_emb)]
     allrows = rt.all_gather_object(rows)
     w = model.sub_model.head.weight.detach().float().cpu()
@@ -97,7 +112,7 @@ def main():
     if rt.rank == 0:
         same = all(torch.equal(ws[0], x) for x in ws)
         json.dump({"world": rt.world, "losses": losses, "rows": [sum(r[i] for r in allrows) for i in range(2)],
-                   "replicas_identical": same, "bn_sync_ok": all(bn_oks), "serving_ok": all(serving_oks), "ckpt_ok": all(ckpt_oks), "graph": model._graph is not None,
+                   "replicas_identical": same, "bn_sync_ok": all(bn_oks), "serving_ok": all(serving_oks), "ckpt_ok": all(ckpt_oks), "balance_ok": all(balance_oks), "balance_steps": tooks, "graph": model._graph is not None,
                    "multimem": bool(getattr(model.optimizer.table, "uses_multimem", False))}, open(out, "w"))
     tn.core.shutdown()
 

@@ -35,6 +35,7 @@ def test_multi_gpu_follows_single_gpu(tmp_path, world):
     one = _run(1, str(tmp_path / "one.json"))
     many = _run(world, str(tmp_path / "many.json"), {"TN_USE_MULTIMEM": "1"})      # the NVSwitch multimem dense path at every size
     assert many["graph"] and many["replicas_identical"] and many["bn_sync_ok"] and many["serving_ok"] and many["ckpt_ok"]
+    assert many["balance_ok"], many["balance_steps"]
     assert many["rows"] == one["rows"]                      # every sign lives on exactly one shard
     assert many["losses"][-1] < 0.8 * many["losses"][0]
     for a, b in zip(one["losses"], many["losses"]):
