@@ -13,8 +13,6 @@ import glob
 import os
 from typing import Iterable, Iterator, List, Optional, Sequence
 
-import torch
-
 from ..core.runtime import runtime
 
 _balance_epoch = 0

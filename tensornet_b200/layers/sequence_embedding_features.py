@@ -9,7 +9,6 @@ import torch
 from torch import nn
 
 from .. import core
-from ..data.features import Ragged
 from ..feature_column import EmbeddingColumn
 from ..ops.embedding import pull_sequence
 

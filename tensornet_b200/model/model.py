@@ -21,7 +21,7 @@ from torch import nn
 
 from .. import core
 from .._opentelemetry import start_as_current_span
-from ..data.features import PACKED_KEY, PackedFeatures, Ragged
+from ..data.features import PackedFeatures, Ragged
 from ..ops import functional as F
 from ..parallel.symm import verify_all_arenas
 

@@ -7,7 +7,7 @@ whose cross layers are tcgen05 GEMMs with the Hadamard-residual fused into the e
 from __future__ import annotations
 
 import math
-from typing import Optional, Sequence
+from typing import Sequence
 
 import torch
 from torch import nn

@@ -1,6 +1,5 @@
 """Python surface on the CPU path: feature columns, EmbeddingFeatures (pooling, CVM columns, shared
 tables), sequence features, batch-norm table, metrics, done-file helpers, tools, serving."""
-import json
 import os
 
 import numpy as np

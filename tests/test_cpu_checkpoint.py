@@ -10,7 +10,6 @@ import pytest
 
 import tensornet_b200 as tn
 from tensornet_b200 import _build
-from tensornet_b200.utils import checkpoint
 
 ext = _build.cpu_ext()
 ADAGRAD, ADAM, FTRL = 0, 1, 2

@@ -4,7 +4,6 @@ the silent peer named in its status words.  No GPU is involved and nothing hangs
 import time
 
 import numpy as np
-import pytest
 
 import tensornet_b200 as tn
 from tensornet_b200 import _build

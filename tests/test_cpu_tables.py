@@ -4,7 +4,6 @@ import math
 
 import numpy as np
 import pytest
-import torch
 
 import tensornet_b200 as tn
 from tensornet_b200 import _build
