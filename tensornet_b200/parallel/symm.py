@@ -109,6 +109,7 @@ class SymmArena:
             idx = torch.tensor([o // _GUARD_BYTES for o in self.guards.values()], device=g.device)
             g[idx] = _GUARD_PATTERN
             self._guard_idx = idx
+            self._guard_rows = g
             if runtime().on_gpu:
                 torch.cuda.synchronize()
             if runtime().world > 1:
@@ -129,8 +130,9 @@ class SymmArena:
         """Names of the regions whose trailing guard no longer holds the pattern (one small device read)."""
         if not self.guards:
             return []
-        end = max(self.guards.values()) + _GUARD_BYTES
-        g = self.buf.local[:end].view(-1, _GUARD_BYTES)[self._guard_idx]
+        g = self._guard_rows[self._guard_idx]
+        if bool((g == _GUARD_PATTERN).all()):          # the common case: one gather, one reduction, one read-back
+            return []
         bad = (g != _GUARD_PATTERN).any(dim=1).cpu().tolist()
         return [name for name, b in zip(self.guards, bad) if b]
 
