@@ -44,6 +44,9 @@ class Config:
     dense_small_grid: int = 0
     #: rows per streamed piece when a GPU shard is saved (bounds the pinned host staging buffer)
     checkpoint_chunk_rows: int = 1 << 22
+    #: check the guard words behind the shared-memory regions after every training pass as well (they are always
+    #: checked before a checkpoint is written and when a step-log window closes); costs a few small kernels and a sync
+    verify_guards_each_pass: bool = False
     #: capture the train step in a CUDA graph
     cuda_graph: bool = True
     #: force the CPU oracle path even when a GPU is visible
@@ -63,6 +66,7 @@ class Config:
         c.dense_small_grid = _env("TN_DENSE_SMALL_GRID", c.dense_small_grid, int)
         c.overlap_dense_push = _env("TN_OVERLAP_DENSE_PUSH", c.overlap_dense_push, bool)
         c.checkpoint_chunk_rows = _env("TN_CKPT_CHUNK_ROWS", c.checkpoint_chunk_rows, int)
+        c.verify_guards_each_pass = _env("TN_VERIFY_GUARDS", c.verify_guards_each_pass, bool)
         c.cuda_graph = _env("TN_CUDA_GRAPH", c.cuda_graph, bool)
         c.force_cpu = _env("TN_FORCE_CPU", c.force_cpu, bool)
         return c

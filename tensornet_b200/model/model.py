@@ -453,7 +453,8 @@ class Model(nn.Module):
                     events[pending].synchronize()
                     history["step_loss"].append(float(pinned[pending]))
                 core.runtime().check_status()
-                verify_all_arenas()
+                if core.config.verify_guards_each_pass:
+                    verify_all_arenas()
                 history["loss"].append(float(last) if last is not None else float("nan"))
                 for cb in callbacks:
                     cb.on_epoch_end(epoch, {"loss": history["loss"][-1]})

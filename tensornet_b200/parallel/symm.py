@@ -84,8 +84,9 @@ class SymmArena:
 
     Every region is followed by a 256-byte guard filled with a fixed pattern.  Peers write into these regions at
     offsets their kernels compute, so an offset bug on any GPU shows up as a damaged guard on the GPU that owns
-    the memory; ``verify`` (and ``verify_all_arenas``, called at the end of every training pass and before a
-    checkpoint is written) reads the guards back and names the region in front of the damaged one."""
+    the memory; ``verify`` (and ``verify_all_arenas``, called before a checkpoint is written, when a step-log window
+    closes and, with ``config.verify_guards_each_pass``, after every training pass) reads the guards back and
+    names the region in front of the damaged one."""
 
     def __init__(self, layout):
         # layout: list of (name, shape, dtype)

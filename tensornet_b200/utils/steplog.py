@@ -19,6 +19,7 @@ from typing import Dict, List, Optional
 
 from .. import core
 from ..callbacks import Callback
+from ..parallel.symm import verify_all_arenas
 
 
 def merge_rank_records(per_rank: List[Dict]) -> Dict:
@@ -142,6 +143,7 @@ class StepLog(Callback):
         per_rank = rt.all_gather_object(rec) if rt.world > 1 else [rec]
         merged = merge_rank_records(per_rank)
         core.runtime().check_status()
+        verify_all_arenas()
         merged["status"] = "ok"
         self.records.append(merged)
         if self.path and rt.rank == 0:
