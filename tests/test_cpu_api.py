@@ -256,3 +256,37 @@ def test_set_sparse_init_mode_zeroes_new_rows_until_switched_back():
     assert np.allclose(t.native.pull(np.array([101], np.uint64))[0], a)       # existing rows are untouched
     tn.core.set_sparse_init_mode(opt, True)
     assert np.abs(t.native.pull(np.array([303], np.uint64))[0]).sum() > 0
+
+
+def test_ps_strategy_scope_and_checkpoint_callback_cycle(tmp_path):
+    """`PsStrategy().scope()` (tensornet/distribute/ps_strategy.py:23-58) plus the callback cycle of the example driver:
+    train a day with PsWeightCheckpoint, then a fresh model under the same strategy resumes from the done-file."""
+    strategy = tn.distribute.PsStrategy()
+    assert strategy.num_replicas_in_sync == 1 and strategy.should_checkpoint
+
+    def build():
+        m = tn.models.WideDeep(["a", "b"], ["a", "b"], dnn_hidden_units=(8,), embedding_dim=4, bucket_size=64)
+        m.compile(optimizer=tn.optimizer.Optimizer(tn.core.Adam(learning_rate=0.01)))
+        return m
+
+    g = torch.Generator().manual_seed(0)
+    data = []
+    for _ in range(6):
+        f = {s: torch.randint(1, 30, (16,), generator=g) for s in ("a", "b")}
+        data.append((f, (f["a"] % 2 == 0).float()))
+    root = str(tmp_path / "model")
+    with strategy.scope():
+        m = build()
+        cb = tn.callbacks.PsWeightCheckpoint(root, need_save_model=True, dt="2020-05-10", delta_days=1, save_mode="bin")
+        m.fit(iter(data), epochs=1, callbacks=[cb])
+        want = torch.as_tensor(m.predict_on_batch(data[0][0])).reshape(-1).clone()
+    assert tn.model.read_last_train_dt(root) == "2020-05-10"
+    tn.core.shutdown(); tn.core.config.force_cpu = True
+    with tn.distribute.PsStrategy().scope():
+        m2 = build()
+        cb2 = tn.callbacks.PsWeightCheckpoint(root, need_save_model=False, dt="2020-05-11", save_mode="bin")
+        cb2.set_model(m2)
+        m2.predict_on_batch(data[0][0])          # creates the dense table the checkpoint is loaded into
+        cb2.on_predict_begin()
+        got = torch.as_tensor(m2.predict_on_batch(data[0][0])).reshape(-1)
+    assert torch.allclose(got, want, atol=1e-5)
