@@ -68,12 +68,14 @@ def main():
     ap.add_argument("--save-mode", default="txt", choices=["txt", "bin"])
     ap.add_argument("--predict", action="store_true")
     ap.add_argument("--max-steps", type=int, default=0)
+    ap.add_argument("--seed", type=int, default=0, help="seed of the dense initialisation (the same on every rank)")
     ap.add_argument("--step-log", default="", help="append one JSON line per 100 steps (throughput, loss, table sizes) to this file")
     a = ap.parse_args()
 
     strategy = tn.distribute.PsStrategy()
     rt = tn.core.runtime()
     slots = [str(i + 1) for i in range(a.slots)]
+    torch.manual_seed(a.seed)
     with strategy.scope():
         model = build_model(a.model, slots, a.dense_dim, a.hidden, a.emb_dim)
         model.compile(optimizer=tn.optimizer.Optimizer(tn.core.Adam(learning_rate=0.001)), loss="binary_crossentropy",

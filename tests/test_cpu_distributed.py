@@ -54,3 +54,20 @@ def test_wide_deep_two_ranks_then_reload_on_one(tmp_path):
     assert [d["day"] for d in rep1["days"]] == ["2020-05-11"]
     assert rep1["days"][0]["loss"] < 0.3
     assert rep1["predict_auc"] > 0.95
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("model", ["deep_cross"])
+def test_other_model_families_on_two_ranks(tmp_path, model):
+    """Deep&Cross through the same driver on two gloo ranks: sharded tables, replicated dense part.  (DeepFM with the
+    example's CVM columns is left out: its FM term multiplies raw show counters, as in the reference's example, and the
+    first day's loss depends on the seed.)"""
+    data, model_dir = str(tmp_path / "data"), str(tmp_path / "model")
+    subprocess.run([sys.executable, os.path.join(ROOT, "examples", "gen_example_data.py"), "--out", data, "--examples-per-file",
+                    "3000", "--files-per-day", "3", "--days", "2020-05-10"], check=True, env=dict(os.environ, PYTHONPATH=ROOT))
+    rep = _run(2, ["--data", data, "--model-dir", model_dir, "--model", model, "--hidden", "32", "16", "--batch-size", "64",
+                   "--days", "2020-05-10", "--save-mode", "bin", "--predict"])
+    assert rep["days"][0]["loss"] < 0.5 and rep["predict_auc"] > 0.9
+    assert 0.5 < rep["days"][0]["copc"] < 2.0
+    cp = os.path.join(model_dir, "2020-05-10")
+    assert sorted(os.listdir(os.path.join(cp, "sparse_table", "deep_input"))) == ["rank_0", "rank_1"]
