@@ -444,7 +444,7 @@ class Model(nn.Module):
                                 history["step_loss"].append(float(pinned[pending]))
                             pending = slot
                     for cb in batch_cbs:
-                        cb.on_train_batch_end(i, {"batch": int(batch[1].shape[0])})
+                        cb.on_train_batch_end(i, {"batch": int(batch[1].shape[0]) if torch.is_tensor(batch[1]) else 0})
                     if verbose and (i + 1) % log_every == 0:
                         print(f"epoch {epoch} step {i + 1} loss {float(last):.5f}", flush=True)
                     if self.stop_training:
