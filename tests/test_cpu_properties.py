@@ -60,3 +60,38 @@ def test_table_size_and_pull_stability(batches, kind):
         g = np.zeros((len(s), 4), dtype=np.float32)
         t.native.push(s, g, np.ones(len(s), np.float32), np.zeros(len(s), np.float32))
         assert t.native.size() == len(seen)                                  # pushing never creates rows
+
+
+@settings(max_examples=12, deadline=None)
+@given(st.lists(st.integers(min_value=1, max_value=2**63 - 1), min_size=1, max_size=120, unique=True),
+       st.integers(1, 5), st.integers(1, 5), st.sampled_from(["adagrad", "adam", "ftrl"]))
+def test_resharding_keeps_every_row_and_routes_by_sign(tmp_path_factory, signs, w1, w2, kind):
+    """world w1 -> w2 in binary mode: the same rows come back bit for bit, and every row sits in rank_(sign % w2)
+    (what the reference needs an offline Spark job for, tensornet_tools/python/resize_sparse.py:35-54)."""
+    import os
+    from tensornet_b200 import tools
+    from tensornet_b200.utils import checkpoint
+
+    opt = {"adagrad": tn.core.AdaGrad(learning_rate=0.01), "adam": tn.core.Adam(learning_rate=0.01),
+           "ftrl": tn.core.Ftrl(learning_rate=0.01)}[kind]
+    name = {"adagrad": "AdaGrad", "adam": "Adam", "ftrl": "Ftrl"}[kind]
+    t = CpuSparseTable(opt, 4, name="t")
+    s = np.array(signs, dtype=np.uint64)
+    t.native.pull(s)
+    t.native.push(s, np.ones((len(s), 4), np.float32) * 0.5, np.ones(len(s), np.float32), np.zeros(len(s), np.float32))
+    root = tmp_path_factory.mktemp("reshard")
+    checkpoint.save_sparse_table(t, str(root / "cp"), "bin")
+    src = os.path.join(str(root / "cp"), "sparse_table", "t")
+    a = tools.resize_sparse(src, str(root / "a"), w1, "bin", name, 4)
+    b = tools.resize_sparse(str(root / "a"), str(root / "b"), w2, "bin", name, 4)
+    assert a == b == len(s)
+    s0, r0, _, _ = tools.read_sparse_table(src, name, 4)
+    s2, r2, _, _ = tools.read_sparse_table(str(root / "b"), name, 4)
+    o0, o2 = np.argsort(s0), np.argsort(s2)
+    assert np.array_equal(s0[o0], s2[o2]) and np.array_equal(r0[o0], r2[o2])
+    assert sorted(os.listdir(root / "b")) == [f"rank_{r}" for r in range(w2)]
+    ext = _build.cpu_ext()
+    kind_id = {"adagrad": 0, "adam": 1, "ftrl": 2}[kind]
+    for r in range(w2):
+        sr, _ = ext.read_sparse_dir(os.path.join(str(root / "b"), f"rank_{r}"), kind_id, 4, False)
+        assert all(int(x) % w2 == r for x in np.asarray(sr).tolist())
