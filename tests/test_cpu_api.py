@@ -36,6 +36,8 @@ def test_api_surface_names():
         assert hasattr(tn.layers, name)
     assert hasattr(tn.model, "Model") and hasattr(tn.model, "PCGradModel") and hasattr(tn.optimizer, "PCGrad")
     assert hasattr(tn.callbacks, "PsWeightCheckpoint") and hasattr(tn.distribute, "PsStrategy")
+    assert hasattr(tn.data, "list_files") and hasattr(tn.data, "BalanceDataset") and callable(tn.utils.StepLog)
+    assert isinstance(tn.__version__, str) and tn.__version__
 
 
 def test_embedding_features_pooling_and_push():
