@@ -18,6 +18,18 @@ from tensornet_b200 import _build  # noqa: E402
 from tensornet_b200.parallel.symm import SymmBuffer  # noqa: E402
 
 
+def load_probe():
+    """Compile (once, next to this file) and import the probe kernel."""
+    from torch.utils import cpp_extension
+
+    here = os.path.dirname(os.path.abspath(__file__))
+    out = os.path.join(here, "_ext", "peer_probe")
+    os.makedirs(out, exist_ok=True)
+    os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0a")
+    return cpp_extension.load(name="tn_peer_probe", sources=[os.path.join(here, "peer_probe.cu")], build_directory=out,
+                              extra_cuda_cflags=_build.NVCC_FLAGS, with_cuda=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--sizes-mb", type=float, nargs="+", default=[0.5, 4, 32, 256])
@@ -25,7 +37,7 @@ def main():
     args = ap.parse_args()
     tn.core.init()
     rt = tn.core.runtime()
-    ext = _build.cuda_ext()
+    ext = load_probe()
     big = int(max(args.sizes_mb) * (1 << 20))
     buf = SymmBuffer(big)
     local = torch.ones(big, dtype=torch.uint8, device=rt.device)

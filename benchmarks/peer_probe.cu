@@ -2,10 +2,11 @@
 // (or this GPU's own memory)?  The fused sparse and dense kernels move their data exactly
 // this way, so these figures are the denominators of their NVLink rooflines.
 // No counterpart in the reference (its transport is brpc over TCP).
-#include "tn_device.cuh"
-#include "tn_ops.h"
-
-namespace tn {
+// Built on demand by p2p_microbench.py as a small extension of its own (it is a measuring tool,
+// not part of the library).
+#include <cuda_runtime.h>
+#include <torch/extension.h>
+#include <c10/cuda/CUDAStream.h>
 
 namespace {
 
@@ -42,9 +43,11 @@ __global__ void __launch_bounds__(1024, 1) peer_copy_kernel(float4* __restrict__
 
 }  // namespace
 
-void launch_peer_copy(void* dst, const void* src, long long nbytes, int mode, int blocks, int threads, int fence, cudaStream_t st) {
-  peer_copy_kernel<<<blocks, threads, 0, st>>>(reinterpret_cast<float4*>(dst), reinterpret_cast<const float4*>(src), nbytes / 16, mode,
-                                               fence);
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("peer_copy", [](int64_t dst, int64_t src, int64_t nbytes, int mode, int blocks, int threads, bool fence) {
+    TORCH_CHECK(nbytes % 16 == 0 && dst % 16 == 0 && src % 16 == 0, "peer_copy wants 16-byte aligned pointers and size");
+    TORCH_CHECK(threads >= 32 && threads <= 1024 && blocks >= 1, "bad launch shape");
+    peer_copy_kernel<<<blocks, threads, 0, c10::cuda::getCurrentCUDAStream()>>>(
+        reinterpret_cast<float4*>(dst), reinterpret_cast<const float4*>(src), nbytes / 16, mode, fence ? 1 : 0);
+  }, "SM-issued copy between raw (possibly peer) addresses; link bandwidth probe");
 }
-
-}  // namespace tn

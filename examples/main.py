@@ -70,6 +70,7 @@ def main():
     ap.add_argument("--max-steps", type=int, default=0)
     ap.add_argument("--seed", type=int, default=0, help="seed of the dense initialisation (the same on every rank)")
     ap.add_argument("--step-log", default="", help="append one JSON line per 100 steps (throughput, loss, table sizes) to this file")
+    ap.add_argument("--profile-dir", default="", help="write a timeline of training steps 50-60 of the first day here")
     a = ap.parse_args()
 
     strategy = tn.distribute.PsStrategy()
@@ -91,11 +92,15 @@ def main():
         cb = tn.callbacks.PsWeightCheckpoint(a.model_dir, need_save_model=True, dt=day, delta_days=1, save_mode=a.save_mode)
         t0 = time.time()
         cbs = [cb] + ([tn.utils.StepLog(a.step_log, every=100)] if a.step_log else [])
+        if a.profile_dir and not report["days"]:
+            cbs.append(tn.callbacks.ProfileBatches(a.profile_dir, 50, 60))
         hist = model.fit(ds, epochs=1, steps_per_epoch=a.max_steps or None, callbacks=cbs)
         steps = model.optimizer.iterations
-        report["days"].append({"day": day, "loss": hist["loss"][-1], "seconds": time.time() - t0, "steps": steps,
-                               **{k: v for k, v in model.metric_sums().items() if k in ("ctr", "pctr", "copc")}})
-        model.reset_metrics()
+        # the compiled metrics of the pass (fit resets them when a pass begins)
+        day_metrics = {m.name.lower(): hist[m.name][-1] for m in model.metrics}
+        report["days"].append({"day": day, "loss": hist["loss"][-1], "seconds": time.time() - t0, "steps": steps, **day_metrics})
+        if rt.rank == 0:
+            print(f"{day}: loss {hist['loss'][-1]:.5f} " + " ".join(f"{k} {v:.5f}" for k, v in day_metrics.items()), flush=True)
     if rt.rank == 0:
         os.makedirs(a.model_dir, exist_ok=True)
         torch.save(model.sub_model.state_dict(), os.path.join(a.model_dir, "sub_model.pt"))

@@ -8,11 +8,13 @@ Two shared objects are produced under ``tensornet_b200/_ext``:
 * ``_tn_cpu``  - the plain C++ restatement of the reference's parameter-server algorithms
   (CPU oracle and CPU execution path) and the checkpoint reader/writer.
 
-At import time a previously built ``.so`` is loaded directly; building happens only through
-:func:`build_all` (or lazily on first use when no built object exists).
+A built ``.so`` is loaded directly when the digest of the sources it was built from (kept next
+to it) still matches ``csrc``; otherwise it is rebuilt first, so an edited kernel can never run
+as its previous build.
 """
 from __future__ import annotations
 
+import hashlib
 import importlib.util
 import os
 import sys
@@ -33,7 +35,6 @@ CUDA_SOURCES = [
     "dense_fused.cu",
     "elementwise.cu",
     "serving.cu",
-    "peer_probe.cu",
     "bn.cu",
     "unique.cu",
     "deepfm_fused.cu",
@@ -86,7 +87,10 @@ def _build(name: str, sources, cuda: bool, verbose: bool = False):
         kwargs["extra_ldflags"] = ["-lcuda"] if _has_libcuda() else []
     else:
         kwargs["extra_ldflags"] = ["-lz"]
-    return cpp_extension.load(**kwargs)
+    mod = cpp_extension.load(**kwargs)
+    with open(_digest_path(name), "w") as f:
+        f.write(_digest(sources))
+    return mod
 
 
 def _has_libcuda() -> bool:
@@ -95,13 +99,31 @@ def _has_libcuda() -> bool:
     return False
 
 
+def _digest(sources) -> str:
+    """SHA-256 over the sources and every header of ``csrc`` (content, not time stamps: a checkout or a copy of
+    the tree changes the latter)."""
+    h = hashlib.sha256()
+    deps = sorted(set(sources) | {os.path.join(_CSRC, f) for f in os.listdir(_CSRC) if f.endswith((".h", ".cuh"))})
+    for d in deps:
+        h.update(os.path.basename(d).encode())
+        with open(d, "rb") as f:
+            h.update(f.read())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
+def _digest_path(name: str) -> str:
+    return os.path.join(_EXT, name, "sources.sha256")
+
+
 def _stale(name: str, sources) -> bool:
-    so = _so_path(name)
-    if not os.path.exists(so):
+    if not os.path.exists(_so_path(name)):
         return True
-    t = os.path.getmtime(so)
-    deps = list(sources) + [os.path.join(_CSRC, f) for f in os.listdir(_CSRC) if f.endswith((".h", ".cuh"))]
-    return any(os.path.getmtime(d) > t for d in deps)
+    try:
+        with open(_digest_path(name)) as f:
+            return f.read().strip() != _digest(sources)
+    except OSError:
+        return True
 
 
 def load(name: str, *, rebuild: bool = False, verbose: bool = False):
@@ -111,7 +133,7 @@ def load(name: str, *, rebuild: bool = False, verbose: bool = False):
             return _LOADED[name]
         cuda = name == "_tn_cuda"
         sources = _existing(CUDA_SOURCES if cuda else CPU_SOURCES)
-        if rebuild or not os.path.exists(_so_path(name)):
+        if rebuild or _stale(name, sources):
             mod = _build(name, sources, cuda, verbose)
         else:
             mod = _import_so(name)

@@ -160,6 +160,52 @@ def barrier():
     runtime().barrier()
 
 
+def recover() -> int:
+    """Collective: make the exchange state usable again after a ``DeviceError``.
+
+    A kernel that reports an error (a wait on a peer that ran out, a full table, an overflowing segment) stops
+    where it is, and from then on every fused kernel of the process returns at once, so no step is half-applied
+    on top of it; peers that were waiting for this GPU give up after their own wait budget and fail the same way.
+    Once every rank has caught its ``DeviceError`` they all call ``recover()``: it waits for the others on the
+    host, clears the per-step scratch, counters, barrier and flag words of every sparse link and dense table,
+    moves every step counter that flags are compared with to one value agreed between the ranks (beyond anything
+    a stale flag can hold), clears the status words and lines the ranks up again.  Rows already in the tables are
+    kept; the step that failed is lost.  Returns the agreed counter value.  The reference's answer to the same
+    situation is three retries and ``abort()`` (core/ps/ps_remote_server.cc:48-83)."""
+    import torch
+
+    rt = runtime()
+    if not rt.on_gpu:
+        rt.failed = False
+        rt.barrier()
+        return 0
+    rt.barrier()                       # includes a device synchronise: nothing of the failed step is still running
+    mine = 0
+    for t in _sparse_tables:
+        mine = max(mine, int(t.epoch.item()))
+    for t in _dense_tables:
+        mine = max(mine, t.exchange_epoch())
+    for t in _bn_tables:
+        if getattr(t, "_epoch", None) is not None:
+            mine = max(mine, int(t._epoch.item()))
+    agreed = max(rt.all_gather_object(mine)) + 2
+    for t in _sparse_tables:
+        t.epoch.fill_(agreed)
+        for lk in t.links:
+            lk.reset_exchange()
+    for t in _dense_tables:
+        t.reset_exchange(agreed)
+    for t in _bn_tables:
+        if getattr(t, "_epoch", None) is not None:
+            t._epoch.fill_(agreed)
+            t._arena.tensor("sig").zero_()
+    rt.status.zero_()
+    torch.cuda.synchronize()
+    rt.failed = False
+    rt.barrier()
+    return agreed
+
+
 def reset_balance_dataset():
     from ..data import dataset
 
@@ -170,6 +216,6 @@ __all__ = [
     "init", "shutdown", "AdaGrad", "Adam", "Ftrl", "get_opt_learning_rate", "set_sparse_init_mode",
     "create_sparse_table", "create_dense_table", "create_bn_table", "save_sparse_table", "load_sparse_table",
     "save_dense_table", "load_dense_table", "save_bn_table", "load_bn_table", "shard_num", "self_shard_id",
-    "barrier", "reset_balance_dataset", "show_decay", "config", "Config", "DeviceError", "runtime",
+    "barrier", "recover", "reset_balance_dataset", "show_decay", "config", "Config", "DeviceError", "runtime",
     "sparse_table", "dense_table", "bn_table",
 ]

@@ -49,6 +49,8 @@ class Config:
     verify_guards_each_pass: bool = False
     #: capture the train step in a CUDA graph
     cuda_graph: bool = True
+    #: training looks at the device status words every this many steps (asynchronously, no stall)
+    status_poll_steps: int = 16
     #: force the CPU oracle path even when a GPU is visible
     force_cpu: bool = False
 
@@ -68,6 +70,7 @@ class Config:
         c.checkpoint_chunk_rows = _env("TN_CKPT_CHUNK_ROWS", c.checkpoint_chunk_rows, int)
         c.verify_guards_each_pass = _env("TN_VERIFY_GUARDS", c.verify_guards_each_pass, bool)
         c.cuda_graph = _env("TN_CUDA_GRAPH", c.cuda_graph, bool)
+        c.status_poll_steps = _env("TN_STATUS_POLL_STEPS", c.status_poll_steps, int)
         c.force_cpu = _env("TN_FORCE_CPU", c.force_cpu, bool)
         return c
 

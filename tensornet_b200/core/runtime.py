@@ -50,6 +50,7 @@ class Runtime:
         self.device_group = None    # nccl group: symmetric memory rendezvous, baseline collectives
         self._status = None
         self._owns_pg = False
+        self.failed = False          # a device error was raised and recover() has not run since
 
     # ------------------------------------------------------------------
     def init(self) -> bool:
@@ -103,8 +104,14 @@ class Runtime:
             return
         s = self.status.tolist()
         if s[0] != 0:
-            self._status.zero_()
-            raise DeviceError(s[0], s[1], s[2])
+            self.raise_status(s[0], s[1], s[2])
+
+    def raise_status(self, code: int, phase: int, aux: int):
+        """A kernel reported ``code``.  Until :func:`tensornet_b200.core.recover` has run, every fused kernel skips
+        its work (they all test the status word first), so nothing is half-applied behind the error; the runtime is
+        marked failed and says so in the exception."""
+        self.failed = True
+        raise DeviceError(code, phase, aux)
 
     @property
     def wait_ns(self) -> int:

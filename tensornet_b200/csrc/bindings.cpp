@@ -293,10 +293,17 @@ struct BnCtx {
   }
 };
 
+// A metric-sum buffer is fp32[4] or fp32[4 + 2 * nbins]: the tail holds the two u32 prediction histograms of the AUC.
+static int hist_bins(const at::Tensor& sums) {
+  TORCH_CHECK(sums.scalar_type() == at::kFloat && sums.is_contiguous() && sums.numel() >= 4 && (sums.numel() - 4) % 2 == 0,
+              "metric sums must be fp32[4] or fp32[4 + 2 * nbins]");
+  return (int)((sums.numel() - 4) / 2);
+}
+
 void gemm(at::Tensor A, at::Tensor B, at::Tensor C, int M, int N, int K, int lda, int ldb, int ldc, bool a_mn, bool b_mn,
           bool accumulate, bool relu, c10::optional<at::Tensor> bias, c10::optional<at::Tensor> mask_aux,
           c10::optional<at::Tensor> had_x0, c10::optional<at::Tensor> had_xl, int ld_aux, int ones_col, int n_store,
-          int split_k, int BN, at::Tensor status, c10::optional<at::Tensor> prof, int dbg, c10::optional<at::Tensor> gate_flags,
+          int split_k, int BN, at::Tensor status, c10::optional<at::Tensor> prof, c10::optional<at::Tensor> gate_flags,
           c10::optional<at::Tensor> gate_epoch, int gate_world, uint64_t gate_wait_ns, int m_halves, c10::optional<at::Tensor> aux_out) {
   TORCH_CHECK(A.is_cuda() && B.is_cuda() && C.is_cuda(), "gemm: CUDA tensors");
   TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16, "gemm: bf16 operands");
@@ -314,7 +321,6 @@ void gemm(at::Tensor A, at::Tensor B, at::Tensor C, int M, int N, int K, int lda
   d.ld_aux = ld_aux; d.ones_col = ones_col; d.n_store = n_store; d.split_k = split_k; d.BN = BN;
   d.status = ptr_of<int>(status);
   d.prof = prof.has_value() ? ptr_of<unsigned long long>(*prof) : nullptr;
-  d.dbg = dbg;
   d.m_halves = m_halves;
   if (aux_out.has_value()) {
     TORCH_CHECK(aux_out->scalar_type() == at::kBFloat16 && aux_out->stride(0) == ld_aux, "gemm: aux_out must be bf16 with row stride ld_aux");
@@ -353,7 +359,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, py::arg("A"), py::arg("B"), py::arg("C"), py::arg("M"), py::arg("N"), py::arg("K"), py::arg("lda"),
         py::arg("ldb"), py::arg("ldc"), py::arg("a_mn"), py::arg("b_mn"), py::arg("accumulate"), py::arg("relu"), py::arg("bias"),
         py::arg("mask_aux"), py::arg("had_x0"), py::arg("had_xl"), py::arg("ld_aux"), py::arg("ones_col"), py::arg("n_store"),
-        py::arg("split_k"), py::arg("BN"), py::arg("status"), py::arg("prof") = py::none(), py::arg("dbg") = 0,
+        py::arg("split_k"), py::arg("BN"), py::arg("status"), py::arg("prof") = py::none(),
         py::arg("gate_flags") = py::none(), py::arg("gate_epoch") = py::none(), py::arg("gate_world") = 0, py::arg("gate_wait_ns") = 0,
         py::arg("m_halves") = 0, py::arg("aux_out") = py::none());
   m.def("launch_count", []() { return g_launches.load(); });
@@ -382,12 +388,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     auto opts = at::TensorOptions().dtype(at::kByte).device(at::kCUDA, device);
     return at::from_blob(ptr_of<void>(p), {nbytes}, opts);
   });
-
-  m.def("peer_copy", [](int64_t dst, int64_t src, int64_t nbytes, int mode, int blocks, int threads, bool fence) {
-    TORCH_CHECK(nbytes % 16 == 0 && dst % 16 == 0 && src % 16 == 0, "peer_copy wants 16-byte aligned pointers and size");
-    TORCH_CHECK(threads >= 32 && threads <= 1024 && blocks >= 1, "bad launch shape");
-    tn::launch_peer_copy(ptr_of<void>(dst), ptr_of<void>(src), nbytes, mode, blocks, threads, fence ? 1 : 0, cur_stream());
-  }, "SM-issued copy between raw (possibly peer) addresses; link bandwidth probe");
 
   m.def("pool_fwd", [](at::Tensor U, int ustride, at::Tensor inverse, c10::optional<at::Tensor> offsets, int B, int S, int pd,
                        int combiner, at::Tensor out, int out_ld) {
@@ -479,7 +479,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                   float grad_scale, at::Tensor sums) {
     c10::cuda::CUDAGuard guard(logit.device());
     tn::launch_bce(ptr_of<float>(logit), ptr_of<float>(label), (int)logit.numel(), pred ? ptr_of<float>(*pred) : nullptr,
-                   dlogit ? ptr_of<float>(*dlogit) : nullptr, grad_scale, ptr_of<float>(sums), cur_stream());
+                   dlogit ? ptr_of<float>(*dlogit) : nullptr, grad_scale, ptr_of<float>(sums), hist_bins(sums), cur_stream());
   });
   m.def("deepfm_input_fwd", [](at::Tensor U, int ustride, at::Tensor inverse, int B, int S, int D, c10::optional<at::Tensor> dense,
                                at::Tensor X0, at::Tensor fm, int lin_col, c10::optional<at::Tensor> Lout) {
@@ -509,7 +509,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     const char* err = tn::launch_deepfm_head_loss(H.data_ptr(), (int)H.stride(0), NH, L ? ptr_of<float>(*L) : nullptr, NL,
                                                   ptr_of<float>(fm), ptr_of<float>(w), ptr_of<float>(label), (int)H.size(0),
                                                   dH.data_ptr(), dL ? ptr_of<float>(*dL) : nullptr, ptr_of<float>(dfm),
-                                                  ptr_of<float>(gw), ptr_of<float>(sums), pred ? ptr_of<float>(*pred) : nullptr,
+                                                  ptr_of<float>(gw), ptr_of<float>(sums), hist_bins(sums),
+                                                  pred ? ptr_of<float>(*pred) : nullptr,
                                                   ptr_of<float>(loss_out), ptr_of<float>(scratch), cur_stream());
     if (err) throw std::runtime_error(err);
   });

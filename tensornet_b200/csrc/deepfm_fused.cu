@@ -172,13 +172,14 @@ __global__ void deepfm_input_bwd_kernel(const float* __restrict__ U, int ustride
 }
 
 // Head + loss + head backward.  w = [ wH (NH) | wL (NL) | wfm | bias ].  ldh <= 512, even.
-// sums: [0] += mean loss, [1] += sum(label), [2] += sum(pred), [3] += B
+// sums: [0] += mean loss, [1] += sum(label), [2] += sum(pred), [3] += B; with nbins > 0 the words behind them are the
+// two prediction histograms (u32 counts; positives, then negatives) of a streaming AUC.
 constexpr int kHeadPairs = 8;
 __global__ void deepfm_head_loss_kernel(const __nv_bfloat16* __restrict__ H, int ldh, int NH, const float* __restrict__ L, int NL,
                                         const float* __restrict__ fm, const float* __restrict__ w, const float* __restrict__ label,
                                         int B, __nv_bfloat16* __restrict__ dH, float* __restrict__ dL, float* __restrict__ dfm,
-                                        float* __restrict__ gw, float* __restrict__ sums, float* __restrict__ pred,
-                                        float* __restrict__ loss_out, float* __restrict__ scratch) {
+                                        float* __restrict__ gw, float* __restrict__ sums, int nbins,
+                                        float* __restrict__ pred, float* __restrict__ loss_out, float* __restrict__ scratch) {
   pdl_sync();
   extern __shared__ float s_gw[];   // [NH + NL + 2]
   const int NW = NH + NL + 2;
@@ -222,6 +223,8 @@ __global__ void deepfm_head_loss_kernel(const __nv_bfloat16* __restrict__ H, int
       ls += fmaxf(logit, 0.f) + log1pf(expf(-fabsf(logit))) - y * logit;
       ys += y; ps += p;
       if (pred) pred[b] = p;
+      if (nbins > 0)
+        atomicAdd(reinterpret_cast<unsigned*>(sums + 4) + (y > 0.5f ? 0 : nbins) + min(nbins - 1, (int)(p * (float)nbins)), 1u);
       dfm[b] = dl * wfm;
       accfm += dl * f;
       accb += dl;
@@ -304,8 +307,8 @@ const char* launch_deepfm_input_bwd(const float* U, int ustride, const int* inve
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
 const char* launch_deepfm_head_loss(const void* H, int ldh, int NH, const float* L, int NL, const float* fm, const float* w,
-                                    const float* label, int B, void* dH, float* dL, float* dfm, float* gw, float* sums, float* pred,
-                                    float* loss_out, float* scratch, cudaStream_t st) {
+                                    const float* label, int B, void* dH, float* dL, float* dfm, float* gw, float* sums, int nbins,
+                                    float* pred, float* loss_out, float* scratch, cudaStream_t st) {
   if (ldh > 64 * kHeadPairs || (ldh & 1)) return "deepfm_head: hidden width must be even and at most 512 columns";
   if (NL > 32) return "deepfm_head: at most 32 linear inputs";
   // two blocks per SM: measured 254 us per DeepFM step against 257 (three) and 264 (four), with scalar or 16-byte
@@ -313,7 +316,7 @@ const char* launch_deepfm_head_loss(const void* H, int ldh, int NH, const float*
   int blocks = (B + 7) / 8; if (blocks > 148 * 2) blocks = 148 * 2; if (blocks < 1) blocks = 1;
   cudaError_t e = launch_pdl(deepfm_head_loss_kernel, dim3(blocks), dim3(256), (NH + NL + 2) * sizeof(float), st,
                              reinterpret_cast<const __nv_bfloat16*>(H), ldh, NH, L, NL, fm, w, label, B,
-                             reinterpret_cast<__nv_bfloat16*>(dH), dL, dfm, gw, sums, pred, loss_out, scratch);
+                             reinterpret_cast<__nv_bfloat16*>(dH), dL, dfm, gw, sums, nbins, pred, loss_out, scratch);
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
 

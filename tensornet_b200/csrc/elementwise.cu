@@ -273,9 +273,12 @@ __global__ void gemv_bwd_rows_kernel(const __nv_bfloat16* __restrict__ Z, int ld
 // ---- sigmoid BCE ---------------------------------------------------------------------------
 // loss = mean(softplus(l) - y*l) ; dlogit = (sigmoid(l) - y) * scale ; pred = sigmoid(l)
 // sums[0] += loss_sum/B, sums[1] += sum(y), sums[2] += sum(pred), sums[3] += B
+// nbins > 0: the words behind sums[3] are two histograms of the prediction (u32 counts, nbins buckets over [0, 1]):
+// positives (label > 0.5) first, negatives second - what a streaming AUC needs.
 __global__ void bce_kernel(const float* __restrict__ logit, const float* __restrict__ label, int B, float* __restrict__ pred,
-                           float* __restrict__ dlogit, float grad_scale, float* __restrict__ sums) {
+                           float* __restrict__ dlogit, float grad_scale, float* __restrict__ sums, int nbins) {
   pdl_sync();
+  unsigned* hist = reinterpret_cast<unsigned*>(sums + 4);
   float ls = 0.f, ys = 0.f, ps = 0.f;
   for (int b = blockIdx.x * blockDim.x + threadIdx.x; b < B; b += gridDim.x * blockDim.x) {
     const float l = logit[b], y = label[b];
@@ -286,6 +289,7 @@ __global__ void bce_kernel(const float* __restrict__ logit, const float* __restr
     ps += p;
     if (pred) pred[b] = p;
     if (dlogit) dlogit[b] = (p - y) * grad_scale;
+    if (nbins > 0) atomicAdd(hist + (y > 0.5f ? 0 : nbins) + min(nbins - 1, (int)(p * (float)nbins)), 1u);
   }
   ls = warp_sum(ls); ys = warp_sum(ys); ps = warp_sum(ps);
   if ((threadIdx.x & 31) == 0) {
@@ -445,8 +449,8 @@ void launch_gemv_bwd(const void* Z, int ld, int B, int K, const float* w, const 
                                                           reinterpret_cast<__nv_bfloat16*>(dZ), gw, relu_cols);
 }
 void launch_bce(const float* logit, const float* label, int B, float* pred, float* dlogit, float grad_scale, float* sums,
-                cudaStream_t st) {
-  launch_pdl(bce_kernel, dim3(blocks_for(B, 256)), dim3(256), 0, st, logit, label, B, pred, dlogit, grad_scale, sums);
+                int nbins, cudaStream_t st) {
+  launch_pdl(bce_kernel, dim3(blocks_for(B, 256)), dim3(256), 0, st, logit, label, B, pred, dlogit, grad_scale, sums, nbins);
 }
 void launch_relu_mask(void* g, const void* y, long long n, cudaStream_t st) {
   launch_pdl(relu_mask_kernel, dim3(blocks_for(n / 8, 256)), dim3(256), 0, st, reinterpret_cast<uint4*>(g), reinterpret_cast<const uint4*>(y), n / 8);

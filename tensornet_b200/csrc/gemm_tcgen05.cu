@@ -624,7 +624,7 @@ const char* gemm_bf16(const GemmDesc& d, cudaStream_t stream) {
   p.had_x0 = reinterpret_cast<const __nv_bfloat16*>(d.had_x0);
   p.had_xl = reinterpret_cast<const __nv_bfloat16*>(d.had_xl);
   p.aux_out = reinterpret_cast<__nv_bfloat16*>(d.aux_out);
-  p.ld_aux = d.ld_aux; p.ones_col = d.ones_col; p.n_store = n_cover; p.bias = d.bias; p.status = d.status; p.prof = d.prof; p.dbg = d.dbg;
+  p.ld_aux = d.ld_aux; p.ones_col = d.ones_col; p.n_store = n_cover; p.bias = d.bias; p.status = d.status; p.prof = d.prof;
   p.gate_flags = d.gate_flags; p.gate_epoch = d.gate_epoch; p.gate_world = d.gate_world; p.gate_wait_ns = d.gate_wait_ns;
 
   dim3 grid((n_cover + BN - 1) / BN, (d.M + kBM * halves - 1) / (kBM * halves), splits);

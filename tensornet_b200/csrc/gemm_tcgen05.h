@@ -38,7 +38,6 @@ struct GemmDesc {
   unsigned long long gate_wait_ns = 0;
   int* status = nullptr;     // device error words
   unsigned long long* prof = nullptr;   // optional [16] timestamps of CTA (0,0,0) for pipeline diagnosis
-  int dbg = 0;               // diagnosis only: bit0 skip epilogue math, bit1 skip global stores, bit2 skip TMEM loads
 };
 
 // Kernel-side parameter block.
@@ -58,7 +57,6 @@ struct GemmParams {
   unsigned long long gate_wait_ns;
   int* status;
   unsigned long long* prof;
-  int dbg;
 };
 
 // Returns nullptr on success, otherwise a static error string.

@@ -44,7 +44,7 @@ void launch_gemv_fwd(const void* Z, int ld, int B, int K, const float* w, float*
 void launch_gemv_bwd(const void* Z, int ld, int B, int K, const float* w, const float* dy, void* dZ, float* gw, int relu_cols,
                      cudaStream_t st);
 void launch_bce(const float* logit, const float* label, int B, float* pred, float* dlogit, float grad_scale, float* sums,
-                cudaStream_t st);
+                int nbins, cudaStream_t st);
 void launch_cross_v1_fwd(const float* x0, const float* xl, const float* w, const float* bias, int B, int D, float* y, float* dot,
                          cudaStream_t st);
 void launch_cross_v1_bwd(const float* x0, const float* xl, const float* w, const float* dot, const float* gy, int B, int D,
@@ -59,8 +59,8 @@ const char* launch_deepfm_input_fwd(const float* U, int ustride, const int* inve
 const char* launch_deepfm_input_bwd(const float* U, int ustride, const int* inverse, int B, int S, int D, const void* dX0, int ld,
                                     const float* gfm, float* gU, int gstride, int lin_col, const float* dL, cudaStream_t st);
 const char* launch_deepfm_head_loss(const void* H, int ldh, int NH, const float* L, int NL, const float* fm, const float* w,
-                                    const float* label, int B, void* dH, float* dL, float* dfm, float* gw, float* sums, float* pred,
-                                    float* loss_out, float* scratch, cudaStream_t st);
+                                    const float* label, int B, void* dH, float* dL, float* dfm, float* gw, float* sums, int nbins,
+                                    float* pred, float* loss_out, float* scratch, cudaStream_t st);
 
 // unique.cu
 void launch_unique_assign(const long long* ids, int n, const float* labels, unsigned long long* dd_keys, int* dd_vals,
@@ -76,9 +76,6 @@ void launch_bn_apply_fwd(const float* x, int ldx, int B, int C, const float* mea
                          const float* beta, float eps, float* y, int ldy, cudaStream_t st);
 void launch_bn_apply_bwd(const float* dy, int ldd, const float* x, int ldx, int B, int C, const float* mean, const float* var,
                          const float* gamma, float eps, float* dx, int ldo, float* gg, float* gb, cudaStream_t st);
-
-// peer_probe.cu
-void launch_peer_copy(void* dst, const void* src, long long nbytes, int mode, int blocks, int threads, int fence, cudaStream_t st);
 
 // serving.cu
 void launch_dict_lookup_pool(const TableView& t, const long long* ids, const int* offsets, int B, int S, int combiner, void* out,

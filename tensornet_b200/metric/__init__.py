@@ -1,13 +1,63 @@
 """``tn.metric``: CTR (mean label), PCTR (mean prediction), COPC (sum label / sum prediction)
-(tensornet/metric/metrics.py:31-104) and a streaming AUC."""
+(tensornet/metric/metrics.py:31-104) and a streaming AUC (the reference's example compiles
+``tf.keras.metrics.AUC``, examples/main.py:63-74).
+
+Every metric can be driven two ways:
+
+* ``update_state(y_true, y_pred, sample_weight=None)`` with tensors, as in Keras;
+* ``feed(stats)`` with a :class:`BatchStats` delta.  ``tn.model.Model`` uses this one: its loss
+  kernels keep the label / prediction sums and the two prediction histograms on the device, and
+  the model hands the metrics what accumulated since the last hand-over.  A training step
+  therefore costs the metrics nothing, however many are compiled in.
+"""
 from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
 
 import torch
 
+AUC_BINS = 200
 
-class _Mean:
-    def __init__(self, name):
+
+@dataclass
+class BatchStats:
+    """What accumulated on the device since the metrics were last fed."""
+    loss_sum: float          # sum of the per-step mean losses
+    label_sum: float
+    pred_sum: float
+    count: float             # examples
+    steps: int
+    pos_hist: Optional[torch.Tensor] = None     # float64 [bins] predictions of positive examples
+    neg_hist: Optional[torch.Tensor] = None
+
+
+class Metric:
+    """Base class: a name, ``reset_state``, ``result`` and the two ways of feeding."""
+
+    device_backed = False     # True: ``feed`` is enough, the model need not call ``update_state`` every step
+
+    def __init__(self, name: str):
         self.name = name
+
+    def reset_state(self):
+        raise NotImplementedError
+
+    def result(self) -> float:
+        raise NotImplementedError
+
+    def update_state(self, y_true, y_pred, sample_weight=None):
+        raise NotImplementedError
+
+    def feed(self, stats: BatchStats):
+        raise NotImplementedError
+
+
+class _Mean(Metric):
+    device_backed = True
+
+    def __init__(self, name):
+        super().__init__(name)
         self.total, self.count = 0.0, 0.0
 
     def reset_state(self):
@@ -36,6 +86,10 @@ class CTR(_Mean):
     def update_state(self, y_true, y_pred, sample_weight=None):
         self._add(y_true, sample_weight)
 
+    def feed(self, stats: BatchStats):
+        self.total += stats.label_sum
+        self.count += stats.count
+
 
 class PCTR(_Mean):
     """Average of the prediction."""
@@ -46,12 +100,35 @@ class PCTR(_Mean):
     def update_state(self, y_true, y_pred, sample_weight=None):
         self._add(y_pred, sample_weight)
 
+    def feed(self, stats: BatchStats):
+        self.total += stats.pred_sum
+        self.count += stats.count
 
-class COPC:
+
+class MeanLoss(_Mean):
+    """Average of the per-step mean loss (what Keras reports as ``loss``)."""
+
+    def __init__(self, name="loss"):
+        super().__init__(name)
+
+    def update_state(self, y_true, y_pred, sample_weight=None):
+        p = y_pred.detach().float().reshape(-1).clamp(1e-7, 1 - 1e-7)
+        y = y_true.detach().float().reshape(-1)
+        self.total += float(-(y * p.log() + (1 - y) * (1 - p).log()).mean())
+        self.count += 1.0
+
+    def feed(self, stats: BatchStats):
+        self.total += stats.loss_sum
+        self.count += stats.steps
+
+
+class COPC(Metric):
     """Click over predicted click: sum(label) / sum(prediction)."""
 
+    device_backed = True
+
     def __init__(self, name="COPC", dtype=None):
-        self.name = name
+        super().__init__(name)
         self.ctr_total, self.pctr_total = 0.0, 0.0
 
     def reset_state(self):
@@ -61,17 +138,22 @@ class COPC:
         self.ctr_total += float(y_true.detach().float().sum())
         self.pctr_total += float(y_pred.detach().float().sum())
 
+    def feed(self, stats: BatchStats):
+        self.ctr_total += stats.label_sum
+        self.pctr_total += stats.pred_sum
+
     def result(self) -> float:
         return self.ctr_total / self.pctr_total if self.pctr_total else 0.0
 
 
-class AUC:
-    """Histogram AUC with ``num_thresholds`` buckets (the example compiles ``tf.keras.metrics.AUC``,
-    examples/main.py:63-74)."""
+class AUC(Metric):
+    """Area under the ROC curve from two histograms of the prediction (``num_thresholds`` buckets over [0, 1])."""
 
-    def __init__(self, name="auc", num_thresholds: int = 200):
-        self.name = name
-        self.n = num_thresholds
+    device_backed = True
+
+    def __init__(self, name="auc", num_thresholds: int = AUC_BINS):
+        super().__init__(name)
+        self.n = int(num_thresholds)
         self.pos = torch.zeros(self.n, dtype=torch.float64)
         self.neg = torch.zeros(self.n, dtype=torch.float64)
 
@@ -82,9 +164,17 @@ class AUC:
     def update_state(self, y_true, y_pred, sample_weight=None):
         p = y_pred.detach().float().reshape(-1).cpu().clamp(0, 1)
         y = y_true.detach().float().reshape(-1).cpu()
-        idx = (p * (self.n - 1)).long()
+        idx = (p * self.n).long().clamp_(max=self.n - 1)
         self.pos += torch.bincount(idx[y > 0.5], minlength=self.n).double()
         self.neg += torch.bincount(idx[y <= 0.5], minlength=self.n).double()
+
+    def feed(self, stats: BatchStats):
+        if stats.pos_hist is None:
+            raise RuntimeError("AUC.feed needs the prediction histograms; compile the model with this metric")
+        if stats.pos_hist.numel() != self.n:
+            raise ValueError(f"AUC has {self.n} buckets, the model accumulates {stats.pos_hist.numel()}")
+        self.pos += stats.pos_hist
+        self.neg += stats.neg_hist
 
     def result(self) -> float:
         tp = torch.flip(torch.cumsum(torch.flip(self.pos, [0]), 0), [0])
@@ -97,4 +187,19 @@ class AUC:
         return float(torch.trapz(torch.flip(tpr, [0]), torch.flip(fpr, [0])))
 
 
-__all__ = ["CTR", "PCTR", "COPC", "AUC"]
+_BY_NAME = {"auc": AUC, "ctr": CTR, "pctr": PCTR, "copc": COPC, "loss": MeanLoss}
+
+
+def get(spec) -> Metric:
+    """A metric object from an instance or one of the names ``auc / ctr / pctr / copc / loss``."""
+    if isinstance(spec, str):
+        try:
+            return _BY_NAME[spec.lower()]()
+        except KeyError:
+            raise ValueError(f"unknown metric {spec!r}; pass an object with update_state / result") from None
+    if not (hasattr(spec, "update_state") and hasattr(spec, "result")):
+        raise TypeError("a metric needs update_state(y_true, y_pred, sample_weight) and result()")
+    return spec
+
+
+__all__ = ["Metric", "BatchStats", "CTR", "PCTR", "COPC", "AUC", "MeanLoss", "get", "AUC_BINS"]

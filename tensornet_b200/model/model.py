@@ -7,8 +7,11 @@ embedding layer), ``predict_step`` returning ``(y, y_pred)``, composite
 table and batch-norm tables, and a ``_checkpoint`` done-file written last.
 
 B200 specifics: after a few eager steps the whole step (pull kernel, towers, loss, dense
-update, push kernel) is captured into one CUDA graph and replayed; inputs are copied into
-static device buffers straight from pinned host memory.
+update, push kernel) is captured into CUDA graphs and replayed.  Two graphs with two sets of
+static input buffers take turns, so the inputs of step k+1 are copied (straight from pinned host
+memory, on a second stream) while the graph of step k still runs.  The loss kernels keep the
+sums and prediction histograms that the compiled metrics need on the device; the host reads
+them when a result is asked for, not every step.
 """
 from __future__ import annotations
 
@@ -19,7 +22,7 @@ from typing import Any, Callable, Dict, Iterable, List, Optional, Sequence
 import torch
 from torch import nn
 
-from .. import core
+from .. import core, metric as _metric
 from .._opentelemetry import start_as_current_span
 from ..data.features import PackedFeatures, Ragged
 from ..ops import functional as F
@@ -84,13 +87,13 @@ def _flatten(obj, out: List[torch.Tensor]):
         for name in ("ids", "values", "offsets"):
             t = getattr(obj, name)
             spec.append(None if t is None else _flatten(t, out))
-        return ("packed", obj.keys, obj.batch_size, spec)
+        return ("packed", tuple(obj.keys), obj.batch_size, tuple(spec))
     if isinstance(obj, Ragged):
-        return ("ragged", [_flatten(obj.values, out), _flatten(obj.offsets, out)])
+        return ("ragged", (_flatten(obj.values, out), _flatten(obj.offsets, out)))
     if isinstance(obj, dict):
-        return ("dict", [(k, _flatten(v, out)) for k, v in obj.items()])
+        return ("dict", tuple((k, _flatten(v, out)) for k, v in obj.items()))
     if isinstance(obj, (list, tuple)):
-        return ("list", [_flatten(v, out) for v in obj])
+        return ("list", tuple(_flatten(v, out) for v in obj))
     return ("const", obj)
 
 
@@ -101,7 +104,7 @@ def _unflatten(spec, it):
     if kind == "packed":
         _, keys, bs, sub = spec
         vals = [None if s is None else _unflatten(s, it) for s in sub]
-        return PackedFeatures(keys, vals[0], vals[1], vals[2], bs)
+        return PackedFeatures(list(keys), vals[0], vals[1], vals[2], bs)
     if kind == "ragged":
         return Ragged(*[_unflatten(s, it) for s in spec[1]])
     if kind == "dict":
@@ -125,6 +128,66 @@ def _is_static(spec) -> bool:
     return True
 
 
+def graph_decision(world: int, known: bool, static: bool, n_graphs: int, max_graphs: int, eager_steps: int,
+                   warmup: int) -> str:
+    """What ``train_step`` does with a batch: ``"eager"``, ``"capture"`` (then replay) or ``"replay"``.
+
+    Capturing ends with a host barrier, so with several ranks every rank must capture at the same step or none
+    may.  The rule that guarantees it without any exchange: the first capture happens at the same step count on
+    every rank (right after the ``warmup`` eager steps, whatever shape each rank's batch has), and with several
+    ranks no further shape is ever captured - a shorter last batch or a ragged batch runs eagerly, which issues the
+    same kernels as a replay and needs no barrier.  One rank may capture up to ``max_graphs`` shapes."""
+    if known:
+        return "replay"
+    if eager_steps < warmup:
+        return "eager"
+    if world > 1:
+        return "capture" if (n_graphs == 0 and static) else "eager"
+    if n_graphs >= max_graphs and not static:
+        return "eager"
+    return "capture"
+
+
+class _GraphPair:
+    """Two captures of the same step that take turns.  Each has its own static input buffers, so the inputs of the
+    next step land (on the copy stream) while the previous replay still reads the other set."""
+
+    def __init__(self):
+        self.graphs: List[Any] = []
+        self.leaves: List[List[torch.Tensor]] = []
+        self.loss: List[torch.Tensor] = []
+        self.done = [torch.cuda.Event(), torch.cuda.Event()]        # replay that last read set p has finished
+        self.copied = [torch.cuda.Event(), torch.cuda.Event()]      # inputs of set p have landed
+        self.turn = 0
+
+
+class _StatusPoll:
+    """Looks at the device status words every few steps without stalling: an asynchronous copy into pinned memory
+    now, read when the next poll comes round.  A device error therefore surfaces at most two polling periods
+    after the step that hit it."""
+
+    def __init__(self, rt, every: int):
+        self.rt, self.every = rt, max(1, int(every))
+        self.host = torch.zeros(8, dtype=torch.int32).pin_memory()
+        self.event = torch.cuda.Event()
+        self.pending = False
+        self.count = 0
+
+    def tick(self):
+        self.count += 1
+        if self.count % self.every:
+            return
+        if self.pending and self.event.query():
+            self.pending = False
+            code = int(self.host[0])
+            if code != 0:
+                self.rt.raise_status(code, int(self.host[1]), int(self.host[2]))
+        if not self.pending:
+            self.host.copy_(self.rt.status, non_blocking=True)
+            self.event.record()
+            self.pending = True
+
+
 class Model(nn.Module):
     """Wrap a network that maps a feature dict to logits ``[B, 1]``.
 
@@ -139,14 +202,20 @@ class Model(nn.Module):
         self.metrics: List[Any] = []
         self.is_loaded_from_checkpoint = False
         self._sums: Optional[torch.Tensor] = None
+        self._sums_seen = None       # host copy of ``_sums`` at the last hand-over to the metrics
+        self._steps_seen = 0
+        self._loss_steps = 0         # steps whose loss went into ``_sums``
+        self._auc_bins = 0
+        self._host_metrics: List[Any] = []    # metrics that need (labels, predictions) tensors every step
         self._graph = None
-        self._graphs = {}            # batch signature -> (graph, static input leaves, static loss)
+        self._graphs: Dict[Any, _GraphPair] = {}     # batch signature -> the two captures of the step
         self._max_graphs = 8
         self._graph_key = None
         self._static_leaves: List[torch.Tensor] = []
         self._static_loss = None
         self._eager_steps = 0
         self._use_graph = False
+        self._status_poll: Optional[_StatusPoll] = None
         self.use_fused = True
         self.stop_training = False
 
@@ -158,15 +227,29 @@ class Model(nn.Module):
 
     def compile(self, optimizer=None, loss="binary_crossentropy", metrics: Optional[Sequence] = None,
                 cuda_graph: Optional[bool] = None, graph_warmup: int = 3):
+        """``metrics``: objects with ``update_state / result`` or the names ``auc, ctr, pctr, copc, loss``.  The metrics
+        of ``tn.metric`` are fed from sums the loss kernel keeps on the device (no per-step cost); any other metric
+        object gets ``update_state(labels, predictions)`` after every step, which reads the predictions back."""
         rt = core.runtime()
         self.to(rt.device)
         self.optimizer = optimizer
         self.loss_fn = loss
-        self.metrics = list(metrics or [])
-        self._sums = torch.zeros(4, dtype=torch.float32, device=rt.device)
+        self.metrics = [_metric.get(m) for m in (metrics or [])]
+        fed_by_kernel = not callable(loss)
+        self._host_metrics = [m for m in self.metrics if not (fed_by_kernel and getattr(m, "device_backed", False))]
+        bins = {m.n for m in self.metrics if isinstance(m, _metric.AUC) and m not in self._host_metrics}
+        if len(bins) > 1:
+            raise ValueError("all AUC metrics of one model must use the same number of thresholds")
+        self._auc_bins = bins.pop() if bins else 0
+        self._sums = torch.zeros(4 + 2 * self._auc_bins, dtype=torch.float32, device=rt.device)
+        self._sums_seen = None
+        self._steps_seen = self._loss_steps = 0
         self._unit_grad = torch.ones((), dtype=torch.float32, device=rt.device)
         self._use_graph = rt.on_gpu and (core.config.cuda_graph if cuda_graph is None else cuda_graph)
         self._graph_warmup = graph_warmup
+        if rt.on_gpu:
+            self._status_poll = _StatusPoll(rt, core.config.status_poll_steps)
+            self._copy_stream = torch.cuda.Stream(device=rt.device)
         if optimizer is not None:
             optimizer.attach(self.named_parameters())
             # A model whose first reader of dense weights is an MLP tower names it in ``first_dense_tower``; on
@@ -197,6 +280,7 @@ class Model(nn.Module):
     def _loss(self, logits, labels):
         if callable(self.loss_fn):
             return self.loss_fn(logits, labels), torch.sigmoid(logits.detach())
+        self._loss_steps += 1
         return F.bce_with_logits(logits, labels, self._sums)
 
     def backwards(self, grads_and_vars=None):
@@ -206,11 +290,15 @@ class Model(nn.Module):
     def _step_impl(self, features, labels):
         loss = None
         fused = getattr(self, "fused_train_loss", None)
-        if fused is not None and not callable(self.loss_fn) and self.use_fused:
+        if fused is not None and not callable(self.loss_fn) and self.use_fused and not self._host_metrics:
             loss = fused(features, labels, self._sums)      # model-specific fused kernels, when the batch qualifies
+            if loss is not None:
+                self._loss_steps += 1
         if loss is None:
             logits = self(features)
-            loss, _ = self._loss(logits, labels)
+            loss, pred = self._loss(logits, labels)
+            for m in self._host_metrics:
+                m.update_state(labels, pred)
         rt = core.runtime()
         if rt.on_gpu and loss.dim() == 0 and loss.dtype == torch.float32:
             loss.backward(self._unit_grad)      # a resident 1.0: autograd would otherwise launch a fill kernel for it
@@ -250,32 +338,31 @@ class Model(nn.Module):
         moved = [t.to(dev, non_blocking=True) for t in leaves]
         return _unflatten(spec, iter(moved)), spec, leaves
 
+    def _eager_step(self, features, labels):
+        (f, y), _, _ = self._to_device((features, labels))
+        return self._step_impl(f, y)
+
     def train_step(self, data):
         """One optimisation step on ``data = (features, labels)``; returns the loss (device tensor)."""
         features, labels = data
         self.train()
+        if self._status_poll is not None:
+            self._status_poll.tick()
         if not self._use_graph:
-            (f, y), _, _ = self._to_device((features, labels))
-            return self._step_impl(f, y)
+            return self._eager_step(features, labels)
+        rt = core.runtime()
         leaves: List[torch.Tensor] = []
         spec = _flatten((features, labels), leaves)
-        key = (repr(spec), tuple((tuple(t.shape), t.dtype) for t in leaves))
-        static_ok = _is_static(spec)
-        if not static_ok and key not in self._graphs:
-            # Ragged batches can be replayed too as long as their shapes repeat (fixed bag lengths, bucketed loaders):
-            # one graph per distinct shape, a handful at most, and only on one GPU (ranks would disagree on when to
-            # capture).  Shapes beyond that run eagerly.
-            static_ok = core.runtime().world == 1 and len(self._graphs) < self._max_graphs
-        else:
-            static_ok = True
-        if not static_ok or self._eager_steps < self._graph_warmup:
+        key = (spec, tuple((t.shape, t.dtype) for t in leaves))
+        what = graph_decision(rt.world, key in self._graphs, _is_static(spec), len(self._graphs), self._max_graphs,
+                              self._eager_steps, self._graph_warmup)
+        if what == "eager":
             self._eager_steps += 1
-            (f, y), _, _ = self._to_device((features, labels))
-            loss = self._step_impl(f, y)
+            loss = self._eager_step(features, labels)
             if self._eager_steps <= self._graph_warmup:
-                core.runtime().check_status()      # surface device-side errors before the step is frozen into a graph
+                rt.check_status()      # surface device-side errors before the step is frozen into a graph
             return loss
-        if key not in self._graphs:
+        if what == "capture":
             if _is_static(spec):
                 self._capture(spec, leaves, key)
             else:
@@ -285,41 +372,67 @@ class Model(nn.Module):
                     torch.cuda.synchronize()
                     self._max_graphs = 0
                     self._graphs.clear()
-                    (f, y), _, _ = self._to_device((features, labels))
-                    return self._step_impl(f, y)
-        graph, static_leaves, static_loss = self._graphs[key]
-        for dst, src in zip(static_leaves, leaves):
-            dst.copy_(src, non_blocking=True)
+                    return self._eager_step(features, labels)
+        gp = self._graphs[key]
+        p = gp.turn
+        gp.turn ^= 1
+        main = torch.cuda.current_stream()
+        if any(t.is_cuda for t in leaves):
+            # inputs produced on the device come with the stream order of whatever produced them
+            torch._foreach_copy_(gp.leaves[p], [t if t.is_cuda else t.to(rt.device, non_blocking=True) for t in leaves])
+        else:
+            copy = self._copy_stream
+            copy.wait_event(gp.done[p])          # the replay that last read this input set is over
+            with torch.cuda.stream(copy):
+                for dst, src in zip(gp.leaves[p], leaves):
+                    dst.copy_(src, non_blocking=True)
+                gp.copied[p].record(copy)
+            main.wait_event(gp.copied[p])
         if self.optimizer is not None:
             self.optimizer.table.set_lr(self.optimizer._lr())
-        graph.replay()
+        gp.graphs[p].replay()
+        gp.done[p].record(main)
         if self.optimizer is not None:
             self.optimizer.iterations += 1
             self.optimizer.table.step_count += 1
-        self._graph, self._graph_key, self._static_leaves, self._static_loss = graph, key, static_leaves, static_loss
-        return static_loss
+        self._loss_steps += self._graph_loss_steps
+        self._graph, self._graph_key, self._static_leaves, self._static_loss = gp.graphs[p], key, gp.leaves[p], gp.loss[p]
+        return gp.loss[p]
 
     def _capture(self, spec, leaves, key):
+        """Capture the step twice (two sets of static inputs that take turns) into one memory pool."""
         dev = core.runtime().device
-        static_leaves = [torch.empty(t.shape, dtype=t.dtype, device=dev) for t in leaves]
-        for dst, src in zip(static_leaves, leaves):
-            dst.copy_(src, non_blocking=True)
-        f, y = _unflatten(spec, iter(static_leaves))
-        torch.cuda.synchronize()
-        g = torch.cuda.CUDAGraph()
-        iters = self.optimizer.iterations if self.optimizer is not None else 0
+        gp = _GraphPair()
         from .. import _build
-        c0 = _build.cuda_ext().launch_count()
-        with torch.cuda.graph(g):
-            static_loss = self._step_impl(f, y)
-        self._launches_per_step = _build.cuda_ext().launch_count() - c0
+        ext = _build.cuda_ext()
+        iters = self.optimizer.iterations if self.optimizer is not None else 0
+        steps0 = self.optimizer.table.step_count if self.optimizer is not None else 0
+        loss_steps0 = self._loss_steps
+        pool = None
+        for p in range(2):
+            static_leaves = [torch.empty(t.shape, dtype=t.dtype, device=dev) for t in leaves]
+            for dst, src in zip(static_leaves, leaves):
+                dst.copy_(src, non_blocking=True)
+            f, y = _unflatten(spec, iter(static_leaves))
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            c0 = ext.launch_count()
+            with torch.cuda.graph(g, pool=pool):
+                static_loss = self._step_impl(f, y)
+            if p == 0:
+                self._launches_per_step = ext.launch_count() - c0
+                self._graph_loss_steps = self._loss_steps - loss_steps0
+                pool = g.pool()
+            gp.graphs.append(g)
+            gp.leaves.append(static_leaves)
+            gp.loss.append(static_loss)
         if self.optimizer is not None:      # capture only records work, it does not run a step
             self.optimizer.iterations = iters
-            self.optimizer.table.step_count -= 1
-        if len(self._graphs) >= self._max_graphs:          # static shapes beyond the cap replace the oldest graph
+            self.optimizer.table.step_count = steps0
+        self._loss_steps = loss_steps0
+        if len(self._graphs) >= self._max_graphs:          # static shapes beyond the cap replace the oldest capture
             self._graphs.pop(next(iter(self._graphs)))
-        self._graphs[key] = (g, static_leaves, static_loss)
-        self._graph, self._graph_key, self._static_leaves, self._static_loss = g, key, static_leaves, static_loss
+        self._graphs[key] = gp
         # Capture takes a different time on every rank; the first replay's kernels wait for their peers on the
         # device with a finite budget, so line the ranks up on the host first.
         core.runtime().barrier()
@@ -330,12 +443,16 @@ class Model(nn.Module):
         return {"loss": loss} if return_dict else loss
 
     def test_step(self, data):
+        """Forward pass and loss on one batch without touching any parameter; the loss kernel adds the batch to the
+        metric sums.  Returns ``(loss, predictions)`` (tensornet/model/Model.py:117-124 is the predict twin)."""
         features, labels = data
         self.eval()
         with torch.no_grad():
             (f, y), _, _ = self._to_device((features, labels))
             logits = self(f)
             loss, pred = self._loss(logits, y)
+            for m in self._host_metrics:
+                m.update_state(y, pred)
         return loss, pred
 
     def predict_step(self, data):
@@ -351,8 +468,14 @@ class Model(nn.Module):
         with start_as_current_span("predict_on_batch"):
             return self.predict_step((x, None))[1]
 
-    def predict(self, dataset: Iterable, steps: Optional[int] = None):
+    def predict(self, dataset: Iterable, steps: Optional[int] = None, callbacks: Sequence = ()):
+        """``(labels, predictions)`` over ``dataset``.  ``callbacks`` get ``on_predict_begin`` (where
+        ``PsWeightCheckpoint`` loads the checkpoint and re-arms the balanced dataset) and ``on_predict_end``
+        (tensornet/model/Model.py:79-81, tensornet/callbacks/callbacks.py:78-84)."""
         with start_as_current_span("predict"):
+            for cb in callbacks:
+                cb.set_model(self)
+                cb.on_predict_begin()
             ys, ps = [], []
             for i, batch in enumerate(dataset):
                 if steps is not None and i >= steps:
@@ -361,7 +484,36 @@ class Model(nn.Module):
                 ps.append(p.cpu())
                 if y is not None:
                     ys.append(y.cpu())
+            core.runtime().check_status()
+            for cb in callbacks:
+                cb.on_predict_end()
             return (torch.cat(ys) if ys else None), (torch.cat(ps) if ps else None)
+
+    def evaluate(self, dataset: Iterable, steps: Optional[int] = None, callbacks: Sequence = (), return_dict: bool = True):
+        """Loss and every compiled metric over ``dataset`` with the parameters left untouched (rows of unseen signs
+        are created as zeros, as in the reference's inference mode).  ``callbacks`` get ``on_test_begin`` /
+        ``on_test_end`` (tensornet/callbacks/callbacks.py:86-91).  Metric state is reset first, as Keras does."""
+        with start_as_current_span("evaluate"):
+            for cb in callbacks:
+                cb.set_model(self)
+                cb.on_test_begin()
+            self.reset_metrics()
+            total, n = 0.0, 0
+            losses = []
+            for i, batch in enumerate(dataset):
+                if steps is not None and i >= steps:
+                    break
+                loss, _ = self.test_step(batch)
+                losses.append(loss.detach())
+                n += 1
+            if losses:
+                total = float(torch.stack([l.float().reshape(()) for l in losses]).sum())
+            core.runtime().check_status()
+            out = {"loss": total / n if n else float("nan")}
+            out.update(self.metric_results())
+            for cb in callbacks:
+                cb.on_test_end(out)
+            return out if return_dict else [out["loss"]] + [out[m.name] for m in self.metrics]
 
     def _prefetched(self, dataset: Iterable):
         """Yield the batches of ``dataset`` already on the device: batch k+1 is copied host -> device on a second
@@ -398,15 +550,35 @@ class Model(nn.Module):
             main.wait_event(ev)
             yield cur
 
+    def _batch_source(self, dataset: Iterable, prefetch: bool):
+        """Batches for ``fit``.  Static batches on the graph path go to ``train_step`` as they are (it copies them into
+        the idle input set itself, overlapped with the running step); everything else is staged one batch ahead."""
+        if not (prefetch and core.runtime().on_gpu):
+            return dataset
+        if not self._use_graph:
+            return self._prefetched(dataset)
+        it = iter(dataset)
+        try:
+            first = next(it)
+        except StopIteration:
+            return iter(())
+        import itertools
+        rest = itertools.chain([first], it)
+        return rest if _is_static(_flatten(first, [])) else self._prefetched(rest)
+
     def fit(self, dataset: Iterable, epochs: int = 1, steps_per_epoch: Optional[int] = None, callbacks: Sequence = (),
             verbose: int = 0, log_every: int = 100, prefetch: bool = True, record_step_loss: bool = False):
         """Iterate ``dataset`` (yielding ``(features, labels)``) for ``epochs`` passes.
 
         ``prefetch``: copy the next batch to the device on a second stream while the current step runs.
         ``record_step_loss``: read every step's loss back to the host (``history["step_loss"]``); the 4-byte copy
-        of step k is issued right behind the step and collected while step k+1 runs, so it costs no stall."""
+        of step k is issued right behind the step and collected while step k+1 runs, so it costs no stall.
+        The history carries the loss of the last step of every pass and, per compiled metric, its value at the
+        end of every pass (metric state is reset when a pass begins, as Keras does)."""
         with start_as_current_span("fit"):
-            history = {"loss": []}
+            history: Dict[str, list] = {"loss": []}
+            for m in self.metrics:
+                history[m.name] = []
             if record_step_loss:
                 history["step_loss"] = []
             rt = core.runtime()
@@ -415,8 +587,9 @@ class Model(nn.Module):
             if gpu and record_step_loss:
                 if getattr(self, "_pinned_loss", None) is None:      # page-locked allocation is slow: once per model
                     self._pinned_loss = [torch.zeros((), dtype=torch.float32).pin_memory() for _ in range(2)]
+                    self._loss_events = [torch.cuda.Event(), torch.cuda.Event()]
                 pinned = self._pinned_loss
-            events = [None, None]
+                events = self._loss_events
             for cb in callbacks:
                 cb.set_model(self)
                 cb.on_train_begin()
@@ -424,10 +597,11 @@ class Model(nn.Module):
             for epoch in range(epochs):
                 for cb in callbacks:
                     cb.on_epoch_begin(epoch)
+                if self.metrics:
+                    self.reset_metrics()
                 last = None
                 pending = None       # index of the pinned slot holding the previous step's loss
-                source = self._prefetched(dataset) if prefetch else dataset
-                for i, batch in enumerate(source):
+                for i, batch in enumerate(self._batch_source(dataset, prefetch)):
                     if steps_per_epoch is not None and i >= steps_per_epoch:
                         break
                     last = self.train_step(batch)
@@ -437,7 +611,6 @@ class Model(nn.Module):
                         else:
                             slot = i & 1
                             pinned[slot].copy_(last.detach(), non_blocking=True)
-                            events[slot] = torch.cuda.Event()
                             events[slot].record()
                             if pending is not None:
                                 events[pending].synchronize()
@@ -456,22 +629,66 @@ class Model(nn.Module):
                 if core.config.verify_guards_each_pass:
                     verify_all_arenas()
                 history["loss"].append(float(last) if last is not None else float("nan"))
+                logs = {"loss": history["loss"][-1]}
+                if self.metrics:
+                    logs.update(self.metric_results())
+                    for m in self.metrics:
+                        history[m.name].append(logs[m.name])
                 for cb in callbacks:
-                    cb.on_epoch_end(epoch, {"loss": history["loss"][-1]})
+                    cb.on_epoch_end(epoch, logs)
             for cb in callbacks:
                 cb.on_train_end()
             return history
 
     # ------------------------------------------------------------------ metrics
+    def _read_sums(self):
+        """Host copy of the device accumulators: (four sums as float64, histogram counts as int64 or None)."""
+        if self._sums is None:
+            return torch.zeros(4, dtype=torch.float64), None
+        host = self._sums.detach().cpu()
+        hist = host[4:].view(torch.int32).to(torch.int64) & 0xFFFFFFFF if self._auc_bins else None
+        return host[:4].double(), hist
+
+    def _feed_metrics(self):
+        """Hand the compiled metrics what the loss kernels accumulated since the last hand-over (one small read)."""
+        fed = [m for m in self.metrics if m not in self._host_metrics]
+        if not fed or self._sums is None:
+            return
+        sums, hist = self._read_sums()
+        if self._sums_seen is None:
+            prev_s, prev_h = torch.zeros(4, dtype=torch.float64), (torch.zeros_like(hist) if hist is not None else None)
+        else:
+            prev_s, prev_h = self._sums_seen
+        d = sums - prev_s
+        pos = neg = None
+        if hist is not None:
+            dh = (hist - prev_h) & 0xFFFFFFFF            # 32-bit counters wrap; differences stay exact
+            pos, neg = dh[: self._auc_bins].double(), dh[self._auc_bins:].double()
+        stats = _metric.BatchStats(float(d[0]), float(d[1]), float(d[2]), float(d[3]), self._loss_steps - self._steps_seen, pos, neg)
+        self._sums_seen = (sums, hist)
+        self._steps_seen = self._loss_steps
+        if stats.count > 0:
+            for m in fed:
+                m.feed(stats)
+
+    def metric_results(self) -> Dict[str, float]:
+        """Current value of every compiled metric, by name."""
+        self._feed_metrics()
+        return {m.name: float(m.result()) for m in self.metrics}
+
     def metric_sums(self) -> Dict[str, float]:
         """Running loss / CTR / PCTR / COPC since the last reset."""
-        s = self._sums.tolist() if self._sums is not None else [0, 0, 0, 0]
+        s = self._sums[:4].tolist() if self._sums is not None else [0, 0, 0, 0]
         n = max(s[3], 1.0)
         return {"loss_sum": s[0], "ctr": s[1] / n, "pctr": s[2] / n, "copc": s[1] / max(s[2], 1e-12), "count": s[3]}
 
     def reset_metrics(self):
         if self._sums is not None:
             self._sums.zero_()
+        self._sums_seen = None
+        self._steps_seen = self._loss_steps
+        for m in self.metrics:
+            m.reset_state()
 
     # ------------------------------------------------------------------ checkpoints
     def _tn_children(self):
@@ -493,6 +710,7 @@ class Model(nn.Module):
     def save_weights(self, filepath: str, dt: str = "", mode: str = "txt", **kwargs):
         """<filepath>/<dt>/{sparse_table,dense_table,bn_table,torch_checkpoint.pt}; ``_checkpoint`` last."""
         rt = core.runtime()
+        rt.check_status()         # nor one from a step that a device-side error cut short
         verify_all_arenas()       # never write a checkpoint from memory a stray peer store has damaged
         cp_dir = os.path.join(filepath, dt) if dt else filepath
         if rt.rank == 0:

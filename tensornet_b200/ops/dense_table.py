@@ -154,6 +154,21 @@ class DenseTable:
                 w -= self.lr * self.s2 / (self.s1.sqrt() / self.s0.sqrt() + o.epsilon)
             g.zero_()
 
+    def reset_exchange(self, epoch: int):
+        """After a device error: clear the barrier / flag words, drop the partial gradient and restart the step
+        counter the flags are compared with at ``epoch`` (the same on every rank).  Part of
+        :func:`tensornet_b200.core.recover`."""
+        if not (runtime().on_gpu and self.initialized):
+            return
+        self._ctx_args["epoch"].fill_(int(epoch))
+        self._ctx_args["bar"].zero_()
+        self.arena.tensor("sig").zero_()
+        self.state[3] = 0.0
+        self.G.zero_()
+
+    def exchange_epoch(self) -> int:
+        return int(self._ctx_args["epoch"].item()) if (runtime().on_gpu and self.initialized) else 0
+
     def refresh_shadow(self):
         """Re-derive the bf16 shadow after the fp32 master was written from outside the optimizer."""
         if self.Wb is not None:

@@ -290,7 +290,7 @@ class _BCE(torch.autograd.Function):
         dl = torch.empty_like(lg)
         pred = torch.empty_like(lg)
         s = sums if sums is not None else torch.zeros(4, dtype=torch.float32, device=lg.device)
-        loss_before = s[0].clone()
+        loss_before = s[0].clone()      # the kernel adds this step's mean loss to s[0]
         _ext().bce(lg, label.contiguous().view(-1).float(), pred, dl, 1.0 / B, s)
         ctx.save_for_backward(dl)
         ctx.shape = logit.shape
@@ -304,8 +304,10 @@ class _BCE(torch.autograd.Function):
 
 
 def bce_with_logits(logit: torch.Tensor, label: torch.Tensor, sums: Optional[torch.Tensor] = None):
-    """Mean sigmoid cross-entropy.  Returns ``(loss, prediction)``.  ``sums`` (fp32[4]), when given,
-    accumulates ``[loss, sum(label), sum(prediction), count]`` for the CTR / PCTR / COPC metrics."""
+    """Mean sigmoid cross-entropy.  Returns ``(loss, prediction)``.  ``sums`` (fp32[4] or fp32[4 + 2 * bins]), when
+    given, accumulates ``[loss, sum(label), sum(prediction), count]`` for the CTR / PCTR / COPC metrics and, in the
+    longer form, two histograms of the prediction (32-bit counts stored in the same buffer: positives, then
+    negatives) for a streaming AUC."""
     if logit.is_cuda:
         return _BCE.apply(logit, label, sums)
     lg = logit.view(-1)
@@ -314,7 +316,12 @@ def bce_with_logits(logit: torch.Tensor, label: torch.Tensor, sums: Optional[tor
     pred = torch.sigmoid(lg).detach()
     if sums is not None:
         with torch.no_grad():
-            sums += torch.stack([loss.detach(), y.sum(), pred.sum(), torch.tensor(float(y.numel()))])
+            sums[:4] += torch.stack([loss.detach(), y.sum(), pred.sum(), torch.tensor(float(y.numel()))])
+            if sums.numel() > 4:
+                bins = (sums.numel() - 4) // 2
+                hist = sums[4:].view(torch.int32)
+                idx = (pred * bins).long().clamp_(max=bins - 1) + torch.where(y > 0.5, 0, bins)
+                hist += torch.bincount(idx, minlength=2 * bins).to(torch.int32)
     return loss, pred.view(logit.shape)
 
 

@@ -223,6 +223,7 @@ class GpuSparseLink:
             prof=torch.zeros(16, dtype=torch.int64, device=d),
         )
         self.arena = arena
+        self._loc = loc
         self.U = arena.tensor("U").view(n_seg, self.ustride)
         self.gU = loc["gU"].view(n_seg, self.gstride)
         self.cnts = loc["cnts"].view(n_seg, 2)       # (show, click) of the batch per distinct sign
@@ -255,6 +256,19 @@ class GpuSparseLink:
         self.ctx.push(max(self._last_n_ids, 1), int(self.push_cta_cap))
         if self.table.world > 1:
             runtime().peer_synced_pushes += 1      # this kernel waited for every peer's gradient records
+
+    def reset_exchange(self):
+        """Bring this link's per-step state back to "between steps" after a kernel gave up half-way (a wait that ran
+        out skips the clean-up at the end of the pull): dedup scratch empty, counters and accumulators zero, no
+        request bookkeeping, flag words clear.  Part of :func:`tensornet_b200.core.recover`; every rank runs it
+        between two host barriers, so no peer is writing into the inboxes meanwhile."""
+        l = self._loc
+        l["dd_keys"].fill_(-1)
+        for k in ("cnt", "cnt_saved", "req_n", "ocount", "acc", "gU", "cnts", "bar"):
+            l[k].zero_()
+        for k in ("req_row", "req_ou", "ou_row"):
+            l[k].fill_(-1)
+        self.arena.tensor("sig").zero_()
 
     def pull_phase_us(self):
         """Durations (microseconds) of the last pull's phases as seen by CTA 0:

@@ -29,4 +29,8 @@ def status_ok(tn_gpu):
     import torch
 
     torch.cuda.synchronize()
-    tn_gpu.core.runtime().check_status()
+    try:
+        tn_gpu.core.runtime().check_status()
+    except tn_gpu.core.DeviceError:
+        tn_gpu.core.recover()      # a reported error is sticky: clear it so the next test starts clean
+        raise

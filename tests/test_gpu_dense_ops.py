@@ -140,22 +140,3 @@ def test_dense_table_step(tn_gpu, status_ok, kind):
             assert torch.allclose(p.detach().cpu(), w, rtol=1e-4, atol=1e-5)
             assert float(p.grad.abs().sum()) == 0.0
             assert torch.equal(p._tn_bf16.float(), p.detach().bfloat16().float())
-
-
-def test_peer_copy_probe_moves_bytes(tn_gpu, status_ok):
-    """The link probe's copy kernel (all four modes) on local memory."""
-    from tensornet_b200 import _build
-
-    ext = _build.cuda_ext()
-    dev = tn_gpu.core.runtime().device
-    n = 1 << 20
-    for mode in (0, 1, 3):
-        src = torch.arange(n, dtype=torch.float32, device=dev)
-        dst = torch.zeros(n, dtype=torch.float32, device=dev)
-        ext.peer_copy(dst.data_ptr(), src.data_ptr(), n * 4, mode, 148, 1024, True)
-        assert torch.equal(dst, torch.arange(n, dtype=torch.float32, device=dev))
-        if mode == 3:
-            assert float(src.abs().sum()) == 0.0          # move-and-clear
-    dst = torch.zeros(n, dtype=torch.float32, device=dev)
-    ext.peer_copy(dst.data_ptr(), dst.data_ptr(), n * 4, 2, 32, 256, False)
-    assert torch.equal(dst.view(-1, 4)[7], torch.tensor([1.0, 2.0, 3.0, 4.0], device=dev))

@@ -119,7 +119,8 @@ def test_weight_gate_passes_and_times_out(tn_gpu):
         rt.check_status()
     assert e.value.code == 5 and e.value.phase == 70 and e.value.aux == 2
     assert float(torch.ones(4, device=dev).sum()) == 4.0
-    rt.check_status()      # the words were cleared by the raise
+    tn_gpu.core.recover()
+    rt.check_status()      # recover() cleared the words
 
 
 @pytest.mark.parametrize("layout", ["kk", "k_mn", "mn_mn"])

@@ -159,8 +159,13 @@ def test_table_full_is_reported_not_fatal(tn_gpu):
         tn.core.runtime().check_status()
     assert e.value.code == 3
     assert t.n_rows == 64
-    # the context is still usable
+    # the context is still usable, and after recover() so is the table: a batch that fits goes through
     assert float(torch.ones(4, device=t.dev).sum()) == 4.0
+    tn.core.recover()
+    inv = lk.pull(ids[:32], training=False, lookup_only=True)      # the table is still full: read-only pull
+    torch.cuda.synchronize()
+    tn.core.runtime().check_status()
+    assert int(inv.min()) >= 0
 
 
 @pytest.mark.parametrize("kind,mode", [("adagrad", "txt"), ("adagrad", "bin"), ("adam", "bin"), ("ftrl", "txt")])
