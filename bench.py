@@ -264,19 +264,27 @@ def main():
     t_fill = time.time() - t_fill
 
     pool = max(args.pool, args.warmup + K)
-    dev_batches = make_batches(pool, B, ranks_per_slot, dev, seed=1000 + rt.rank)
-    host_batches = [tuple(t.cpu().pin_memory() for t in b) for b in dev_batches]
+    drawn = make_batches(pool, B, ranks_per_slot, dev, seed=1000 + rt.rank)
+    # ids, dense features and labels cycle with different periods (pool, pool-3, pool-5; pairwise coprime for the
+    # default pool), so no (ids, labels) pairing comes back within a run and the random labels cannot be memorised
+    per = (pool, max(pool - 3, 1), max(pool - 5, 1))
+    host_drawn = [tuple(t.cpu().pin_memory() for t in b) for b in drawn]
+
+    def dev_batch(k):
+        return drawn[k % per[0]][0], drawn[k % per[1]][1], drawn[k % per[2]][2]
+
+    def host_batch(k):
+        return host_drawn[k % per[0]][0], host_drawn[k % per[1]][1], host_drawn[k % per[2]][2]
 
     def feats(ids, dense):
         return {tn.data.PACKED_KEY: tn.data.PackedFeatures(slots, ids=ids), "dense": dense}
 
     # ---------------- warm-up (eager steps, graph capture, a few replays) ----------------
     for k in range(args.warmup + 4):
-        i, d, l = dev_batches[k % pool]
+        i, d, l = dev_batch(k)
         model.train_on_batch(feats(i, d), l)
     # the end-to-end path (Model.fit: overlapped input copies, pinned loss buffers) gets its warm-up too
-    model.fit(((feats(*host_batches[k % pool][:2]), host_batches[k % pool][2]) for k in range(args.warmup)), epochs=1,
-              record_step_loss=True)
+    model.fit(((feats(*host_batch(k)[:2]), host_batch(k)[2]) for k in range(args.warmup)), epochs=1, record_step_loss=True)
     torch.cuda.synchronize()
     rt.check_status()
     graphed = model._graph is not None
@@ -284,7 +292,7 @@ def main():
         per_step_launches = model._launches_per_step
     else:
         c0 = ext.launch_count()
-        i, d, l = dev_batches[0]
+        i, d, l = dev_batch(0)
         model.train_on_batch(feats(i, d), l)
         per_step_launches = ext.launch_count() - c0
     torch.cuda.synchronize()
@@ -305,7 +313,7 @@ def main():
 
     def device_block():
         for _ in range(K):
-            i, d, l = dev_batches[step_no[0] % pool]
+            i, d, l = dev_batch(step_no[0])
             step_no[0] += 1
             model.train_on_batch(feats(i, d), l)
 
@@ -353,7 +361,7 @@ def main():
 
     def host_stream():
         for k in range(repeats * K):
-            i, d, l = host_batches[k % pool]                # pinned host tensors: every step's inputs are copied H2D
+            i, d, l = host_batch(k)                         # pinned host tensors: every step's inputs are copied H2D
             yield feats(i, d), l
 
     marks = BlockMarks()
@@ -375,7 +383,7 @@ def main():
     med, e2e_med = statistics.median(blocks), statistics.median(e2e_blocks)
     value = G * K / (med / 1e3)
     e2e = G * K / (e2e_med / 1e3)
-    h2d = sum(t.numel() * t.element_size() for t in host_batches[0])
+    h2d = sum(t.numel() * t.element_size() for t in host_drawn[0])
 
     # ---------------- context arms (not the reference; for orientation) -------------------
     context = {}
@@ -384,7 +392,7 @@ def main():
         try:
             import deepfm_context_arms as arms
             context["library_only_path"] = arms.library_arm(
-                rt, dev_batches, lambda: universe_chunks(B, ranks_per_slot, 0, 1, dev), steps=K, warmup=args.warmup, emb_dim=EMB_DIM)
+                rt, drawn, lambda: universe_chunks(B, ranks_per_slot, 0, 1, dev), steps=K, warmup=args.warmup, emb_dim=EMB_DIM)
         except Exception as e:  # pragma: no cover - orientation only, never fails the bench
             context["library_only_path"] = {"error": f"{type(e).__name__}: {str(e)[:160]}"}
         rt.barrier()

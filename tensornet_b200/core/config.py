@@ -40,6 +40,9 @@ class Config:
     #: multi-GPU: run the dense step beside the sparse push (small dense arrays only); measured at 2 GPUs on the
     #: DeepFM step: 2 % slower than back to back (both kernels are latency-bound and lose CTAs), so off by default
     overlap_dense_push: bool = False
+    #: multi-GPU, dense arrays up to 4 M elements: the dense step runs on a few CTAs of the last sparse push kernel of
+    #: the step instead of in a kernel of its own behind it
+    dense_rides_push: bool = True
     #: multi-GPU: cap on the dense kernel's grid for small arrays (cheaper grid barriers); 0 = fill the GPU
     dense_small_grid: int = 0
     #: rows per streamed piece when a GPU shard is saved (bounds the pinned host staging buffer)
@@ -67,6 +70,7 @@ class Config:
         c.staged_row_return = _env("TN_STAGED_RETURN", c.staged_row_return, int)
         c.dense_small_grid = _env("TN_DENSE_SMALL_GRID", c.dense_small_grid, int)
         c.overlap_dense_push = _env("TN_OVERLAP_DENSE_PUSH", c.overlap_dense_push, bool)
+        c.dense_rides_push = _env("TN_DENSE_RIDES_PUSH", c.dense_rides_push, bool)
         c.checkpoint_chunk_rows = _env("TN_CKPT_CHUNK_ROWS", c.checkpoint_chunk_rows, int)
         c.verify_guards_each_pass = _env("TN_VERIFY_GUARDS", c.verify_guards_each_pass, bool)
         c.cuda_graph = _env("TN_CUDA_GRAPH", c.cuda_graph, bool)

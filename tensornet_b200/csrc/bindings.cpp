@@ -168,12 +168,13 @@ struct SparseCtx {
     check(tn::launch_sparse_pull(a, (int)work, cur_stream()), "sparse_pull_fused launch");
   }
 
-  void push(int64_t work_hint, int max_ctas) {
+  // `dense`: the dense step of the same training step (DenseCtx::rider_args), carried by a few CTAs of this launch.
+  void push(int64_t work_hint, int max_ctas, const tn::DenseStepArgs* dense) {
     tn::PushArgs a{};
     a.c = c; a.tbl = t; a.opt = o; a.lanes = push_lanes;
     long long work = work_hint * push_lanes;
     if (work > (1ll << 30)) work = 1ll << 30;
-    check(tn::launch_sparse_push(a, (int)work, max_ctas, cur_stream()), "sparse_push_fused launch");
+    check(tn::launch_sparse_push(a, (int)work, max_ctas, dense, cur_stream()), "sparse_push_fused launch");
   }
 };
 
@@ -222,6 +223,13 @@ struct DenseCtx {
     tn::DenseStepArgs b = a;
     b.skip_open = skip_open ? 1 : 0;
     check(tn::launch_dense_step(b, cur_stream()), "dense step launch");
+  }
+  // Arguments for a launch in which the sparse push kernel carries this step: the opening "gradients ready"
+  // barrier is always run (the carrying CTAs start together with the push, before any peer has been heard from).
+  tn::DenseStepArgs rider_args() const {
+    tn::DenseStepArgs b = a;
+    b.skip_open = 0;
+    return b;
   }
   void set_gated(bool g) { a.gated = g ? 1 : 0; }
   void set_max_ctas(int n) { a.max_ctas = n; }
@@ -346,7 +354,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("set_table", &SparseCtx::set_table)
       .def("pull", &SparseCtx::pull, py::arg("ids"), py::arg("inverse"), py::arg("labels"), py::arg("label_mod"), py::arg("training"),
            py::arg("lookup_only") = false)
-      .def("push", &SparseCtx::push, py::arg("work_hint"), py::arg("max_ctas") = 0);
+      .def("push", [](SparseCtx& self, int64_t work_hint, int max_ctas, py::object dense) {
+        if (dense.is_none()) { self.push(work_hint, max_ctas, nullptr); return; }
+        const tn::DenseStepArgs d = dense.cast<DenseCtx&>().rider_args();
+        self.push(work_hint, max_ctas, &d);
+      }, py::arg("work_hint"), py::arg("max_ctas") = 0, py::arg("dense") = py::none());
   py::class_<BnCtx>(m, "BnCtx")
       .def(py::init<py::dict>())
       .def("push", &BnCtx::push)

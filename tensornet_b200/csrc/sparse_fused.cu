@@ -19,6 +19,7 @@
 // are found with a ballot, one lane adds the population count and the others take their
 // rank inside the ballot.
 #include "sparse_table.cuh"
+#include "dense_step.cuh"
 
 namespace tn {
 
@@ -292,26 +293,36 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_pull_fused_kernel(const __
   // s_pre[k] = ids of senders R+1 .. R+k (mod W) that precede sender R+1+k in that space.
   for (int part = 0; part < (W > 1 ? 2 : 1); ++part) {
     __syncthreads();
-    if (threadIdx.x == 0) {
-      unsigned long long v = 0;
-      if (part == 0) {
-        v = (unsigned long long)min(__ldcg(&c.cnt[R]), capo);
-        s_n[R] = (int)v;
-        if (blockIdx.x == 0) c.req_n[R] = (int)v;
-      } else {
-        s_pre[0] = 0;
-        for (int k = 0; k + 1 < W; ++k) {
-          const int sk = (R + 1 + k) % W;
-          unsigned long long f = 0;
-          if (v != ~0ull && !wait_flag_ge(sig_word(c.sig[R], kSigPullReq, sk), epoch, &f, c.wait_ns, c.status, 3, sk)) v = ~0ull;
-          const int n_k = v == ~0ull ? 0 : (int)(f & 0xffffffffull);
-          s_n[sk] = n_k;
-          if (blockIdx.x == 0) c.req_n[sk] = n_k;
-          s_pre[k + 1] = s_pre[k] + n_k;
-        }
-        if (v != ~0ull) v = (unsigned long long)s_pre[W - 1];
+    if (part == 0 && threadIdx.x == 0) {
+      const int v = min(__ldcg(&c.cnt[R]), capo);
+      s_n[R] = v;
+      if (blockIdx.x == 0) c.req_n[R] = v;
+      s_flag = (unsigned long long)v;
+    }
+    if (part == 1 && threadIdx.x < 32) {
+      // one lane per sender: the W-1 flags are polled side by side, the counts they carry are turned into the
+      // flat index space with a warp scan
+      const int k = threadIdx.x;
+      const int sk = (R + 1 + k) % W;
+      unsigned long long f = 0;
+      bool ok = true;
+      if (k + 1 < W) ok = wait_flag_ge(sig_word(c.sig[R], kSigPullReq, sk), epoch, &f, c.wait_ns, c.status, 3, sk);
+      const bool all_ok = __all_sync(0xffffffffu, ok);
+      const int n_k = (k + 1 < W && all_ok) ? (int)(f & 0xffffffffull) : 0;
+      int incl = n_k;
+#pragma unroll
+      for (int o = 1; o < kMaxWorld; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (k >= o) incl += up;
       }
-      s_flag = v;
+      if (k + 1 < W) {
+        s_n[sk] = n_k;
+        if (blockIdx.x == 0) c.req_n[sk] = n_k;
+        s_pre[k + 1] = incl;
+      }
+      if (k == 0) s_pre[0] = 0;
+      const int total = __shfl_sync(0xffffffffu, incl, W - 2);
+      if (k == 0) s_flag = all_ok ? (unsigned long long)total : ~0ull;
     }
     __syncthreads();
     if (s_flag == ~0ull) { gs.failed = true; break; }
@@ -634,16 +645,27 @@ __device__ __forceinline__ void apply_row(const SparseOptParams& o, float* row, 
 
 }  // namespace
 
-__global__ void __launch_bounds__(kThreads, 1) sparse_push_fused_kernel(const __grid_constant__ PushArgs a) {
+// `dense_ctas` > 0: the last `dense_ctas` CTAs of the grid run the dense step `d` of the same training step (reduce-
+// scatter of the flat gradient, optimizer on the owned chunk, all-gather of the new weights) while the others push.
+// Both exchanges wait on the same peers at the same point of the step, so side by side they cost one wait instead
+// of two; the dense CTAs use the dense table's own barrier and flag words.
+__global__ void __launch_bounds__(kThreads, 1) sparse_push_fused_kernel(const __grid_constant__ PushArgs a,
+                                                                        const __grid_constant__ DenseStepArgs d,
+                                                                        const int dense_ctas) {
+  const int nb = (int)gridDim.x - dense_ctas;      // CTAs of the push proper
+  if ((int)blockIdx.x >= nb) {
+    dense::fused_step(d, (int)blockIdx.x - nb, dense_ctas);
+    return;
+  }
   const SparseCommView& c = a.c;
   const TableView& t = a.tbl;
   GridSync gs;
-  gs.init(c.bar, c.status, c.wait_ns);
+  gs.init(c.bar, c.status, c.wait_ns, (unsigned)nb);
   __shared__ unsigned long long s_flag;
   __shared__ int s_pre[kMaxWorld + 1];
 
   const int tid = blockIdx.x * blockDim.x + threadIdx.x;
-  const int nth = gridDim.x * blockDim.x;
+  const int nth = nb * blockDim.x;
   const int W = c.world, R = c.rank, capo = c.capo;
   const unsigned long long epoch = __ldcg(c.epoch);
   const int dim = t.dim, gstride = c.gstride, gch = gstride >> 2;
@@ -703,8 +725,9 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_push_fused_kernel(const __
     }
   }
   prof_mark(c, 9);
-  if (!gs.sync(11, true)) goto done;
-  if (blockIdx.x == 0 && threadIdx.x < W && threadIdx.x != R)
+  // no grid barrier: the CTA that finishes shipping last tells the owners that their segments are complete, while
+  // the others already sum this GPU's own records (every thread reads back exactly the pieces it wrote itself)
+  if (last_cta_arrives(&c.bar[2], true, (unsigned)nb) && threadIdx.x < W && threadIdx.x != R)
     st_release_sys_u64(sig_word(c.sig[threadIdx.x], kSigPushReq, R), epoch << 32);
   prof_mark(c, 10);
 
@@ -734,16 +757,21 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_push_fused_kernel(const __
   // then everybody else's, as one flat index space over the senders so that no thread idles on a short segment
   {
     __syncthreads();
-    if (threadIdx.x == 0) {
-      int ok = 1;
-      s_pre[0] = 0;
-      for (int k = 0; k + 1 < W; ++k) {
-        const int sk = (R + 1 + k) % W;
-        unsigned long long v;
-        if (ok && !wait_flag_ge(sig_word(c.sig[R], kSigPushReq, sk), epoch, &v, c.wait_ns, c.status, 12, sk)) ok = 0;
-        s_pre[k + 1] = s_pre[k] + __ldcg(&c.req_n[sk]);
+    if (threadIdx.x < 32) {       // one lane per sender polls its flag; a warp scan lays the segments end to end
+      const int k = threadIdx.x;
+      const int sk = (R + 1 + k) % W;
+      unsigned long long v;
+      bool ok = true;
+      if (k + 1 < W) ok = wait_flag_ge(sig_word(c.sig[R], kSigPushReq, sk), epoch, &v, c.wait_ns, c.status, 12, sk);
+      const bool all_ok = __all_sync(0xffffffffu, ok);
+      int incl = (k + 1 < W) ? __ldcg(&c.req_n[sk]) : 0;
+#pragma unroll
+      for (int o = 1; o < kMaxWorld; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (k >= o) incl += up;
       }
-      s_flag = ok ? 0ull : ~0ull;
+      if (k + 1 < W) s_pre[k + 1] = incl;
+      if (k == 0) { s_pre[0] = 0; s_flag = all_ok ? 0ull : ~0ull; }
     }
     __syncthreads();
     prof_mark(c, 15);
@@ -838,16 +866,31 @@ cudaError_t launch_sparse_pull(const PullArgs& args, int work_items, cudaStream_
 }
 
 // `max_ctas` > 0 caps the grid below the SM count, leaving whole SMs to a kernel running on another stream.
-cudaError_t launch_sparse_push(const PushArgs& args, int work_items, int max_ctas, cudaStream_t stream) {
+// `dense` != null (several GPUs only): the dense step rides on `dense_ctas` extra CTAs of the same cooperative grid.
+cudaError_t launch_sparse_push(const PushArgs& args, int work_items, int max_ctas, const DenseStepArgs* dense, cudaStream_t stream) {
   int dev = 0;
   cudaGetDevice(&dev);
   static int grid_max[64] = {0};
   if (grid_max[dev] == 0) grid_max[dev] = coop_grid((const void*)sparse_push_fused_kernel, dev);
   int grid = (work_items + kThreads - 1) / kThreads;
   if (grid < 1) grid = 1;
-  if (grid > grid_max[dev]) grid = grid_max[dev];
+  int dense_ctas = 0;
+  DenseStepArgs d{};
+  if (dense != nullptr) {
+    if (dense->world < 2 || dense->n % 4 || dense->chunk % 4) return cudaErrorInvalidValue;
+    d = *dense;
+    // one pass of the owned chunk: 1024 threads x kDenseUnroll 16-byte groups per CTA, at most 16 CTAs
+    const long long per_cta = (long long)kThreads * dense::kDenseUnroll * 4;
+    dense_ctas = (int)((d.chunk + per_cta - 1) / per_cta);
+    if (dense_ctas < 1) dense_ctas = 1;
+    if (dense_ctas > 16) dense_ctas = 16;
+  }
+  const int room = grid_max[dev] - dense_ctas;
+  if (grid > room) grid = room;
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-  void* params[] = {(void*)&args};
+  if (grid < 1) return cudaErrorInvalidValue;
+  grid += dense_ctas;
+  void* params[] = {(void*)&args, (void*)&d, (void*)&dense_ctas};
   return cudaLaunchCooperativeKernel((const void*)sparse_push_fused_kernel, dim3(grid), dim3(kThreads), params, 0, stream);
 }
 

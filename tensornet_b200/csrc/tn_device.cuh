@@ -79,8 +79,10 @@ struct GridSync {
   unsigned long long budget_ns;
   bool failed;
 
-  __device__ __forceinline__ void init(unsigned* b, int* st, unsigned long long budget) {
-    bar = b; nblocks = gridDim.x; gen = 0; status = st; budget_ns = budget; failed = false;
+  // `nb`: CTAs taking part (all of the grid by default; a kernel whose CTAs split into roles gives each role its own
+  // barrier words and count).
+  __device__ __forceinline__ void init(unsigned* b, int* st, unsigned long long budget, unsigned nb = 0) {
+    bar = b; nblocks = nb ? nb : gridDim.x; gen = 0; status = st; budget_ns = budget; failed = false;
   }
 
   // Returns false when the barrier timed out or an earlier phase already failed.
@@ -136,13 +138,13 @@ struct GridSync {
 // "Last CTA out": true in exactly one CTA per launch for a given counter, namely the last whose threads all
 // reached this point.  Everything the other CTAs wrote before arriving (peer memory included when `sys_fence`)
 // is ordered before what the elected CTA does next, so it may publish a completion flag without a grid barrier.
-__device__ __forceinline__ bool last_cta_arrives(unsigned* ctr, bool sys_fence) {
+__device__ __forceinline__ bool last_cta_arrives(unsigned* ctr, bool sys_fence, unsigned nb = 0) {
   __shared__ int s_last;
   __syncthreads();
   if (threadIdx.x == 0) {
     if (sys_fence) __threadfence_system(); else __threadfence();
     const unsigned prev = atomicAdd(ctr, 1u);
-    const int last = prev == gridDim.x - 1;
+    const int last = prev == (nb ? nb : gridDim.x) - 1;
     if (last) { if (sys_fence) __threadfence_system(); else __threadfence(); }
     s_last = last;
   }

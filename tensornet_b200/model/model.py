@@ -323,12 +323,28 @@ class Model(nn.Module):
             self.backwards()
             main.wait_stream(side)
         else:
-            # several GPUs: push first.  A push kernel only completes after every peer has shipped its gradient
-            # records, i.e. after every peer's backward pass, so the dense kernel behind it needs no opening barrier.
+            # Several GPUs.  Small dense arrays ride on the last sparse push: a few CTAs of that kernel run the dense
+            # step while the rest exchange gradient records, so the step waits for its peers once, not twice.
+            rider = None
+            if (rt.on_gpu and self.optimizer is not None and core.config.dense_rides_push and
+                    self.optimizer.table.initialized and self.optimizer.table.n <= (4 << 20)):
+                pending = [l for l in self.sparse_layers() if getattr(l, "_pending_push", False)]
+                if pending:
+                    rider = (getattr(pending[-1], "links", None) or [pending[-1].link])[-1]
+                    self.optimizer.table.set_lr(self.optimizer._lr())
+                    rider.dense_rider = self.optimizer.table
+            # Otherwise push first.  A push kernel only completes after every peer has shipped its gradient records,
+            # i.e. after every peer's backward pass, so the dense kernel behind it needs no opening barrier.
             before = rt.peer_synced_pushes
             self.backwards()
             if self.optimizer is not None:
-                self.optimizer.step(peers_past_backward=rt.peer_synced_pushes > before)
+                if rider is not None and rider.dense_rider is None:      # the push took it along
+                    self.optimizer.iterations += 1
+                    self.optimizer.table.step_count += 1
+                else:
+                    if rider is not None:
+                        rider.dense_rider = None
+                    self.optimizer.step(peers_past_backward=rt.peer_synced_pushes > before)
         return loss.detach()
 
     def _to_device(self, obj):

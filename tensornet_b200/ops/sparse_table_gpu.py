@@ -236,6 +236,7 @@ class GpuSparseLink:
         self.ctx = table.ext.SparseCtx(table.table_dict(), self.comm, table._opt_dict())
         self._last_n_ids = 0
         self.push_cta_cap = 0        # > 0: the push kernel leaves the remaining SMs to a kernel on another stream
+        self.dense_rider = None      # a DenseTable whose step the next push carries on a few of its CTAs (several GPUs)
         if multi:
             rt.barrier()
 
@@ -253,7 +254,8 @@ class GpuSparseLink:
 
     def push(self):
         """Apply the accumulated unique-row gradients (``self.gU``) on the owning GPUs."""
-        self.ctx.push(max(self._last_n_ids, 1), int(self.push_cta_cap))
+        rider, self.dense_rider = self.dense_rider, None
+        self.ctx.push(max(self._last_n_ids, 1), int(self.push_cta_cap), rider.ctx if rider is not None else None)
         if self.table.world > 1:
             runtime().peer_synced_pushes += 1      # this kernel waited for every peer's gradient records
 

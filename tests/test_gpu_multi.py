@@ -103,3 +103,64 @@ os._exit(0)
     out0, _ = procs[0].communicate(timeout=240)
     procs[1].wait(timeout=60)
     assert "DETECTED" in out0 and "NOT DETECTED" not in out0 and "CONTEXT OK" in out0, out0[-3000:]
+
+
+@pytest.mark.timeout(300)
+def test_peer_wait_runs_out_on_the_pull_and_recover_realigns(tmp_path):
+    """Rank 1 skips one pull launch (a host-side hook; nothing on any GPU faults or spins for ever).  Rank 0's fused pull
+    kernel gives up waiting for rank 1's id segment after the 50 ms budget, records "peer wait timed out, owner
+    phase, peer 1" and returns; its context keeps computing.  Both ranks then call ``core.recover()`` and the next
+    pull on both returns the same rows as before the failure.  Plain peer loads, no NVSwitch multicast mapping."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    script = tmp_path / "skipper.py"
+    script.write_text('''
+import os, torch
+import tensornet_b200 as tn
+from tensornet_b200.ops.sparse_table_gpu import GpuSparseTable
+tn.core.init()
+rt = tn.core.runtime()
+t = GpuSparseTable(tn.core.Adam(learning_rate=1e-2, initial_scale=0.1), 8, rows=1 << 14)
+lk = t.link(4096)
+g = torch.Generator().manual_seed(5 + rt.rank)
+ids = torch.randint(0, 3000, (2048,), generator=g, dtype=torch.int64).to(rt.device)
+inv = lk.pull(ids, training=False)
+torch.cuda.synchronize(); rt.check_status()
+before = lk.U[inv.long()].clone()
+lk.pull(ids, training=False)
+torch.cuda.synchronize(); rt.check_status(); rt.barrier()
+# ---- the step in which rank 1 never launches its pull
+if rt.rank == 0:
+    lk.pull(ids, training=False)
+    torch.cuda.synchronize()
+    try:
+        rt.check_status()
+        print("NO ERROR", flush=True)
+    except tn.core.DeviceError as e:
+        print("ERROR code=%d phase=%d peer=%d" % (e.code, e.phase, e.aux), flush=True)
+    assert float(torch.ones(4, device=rt.device).sum()) == 4.0
+    # until recover() has run every fused kernel returns at once: nothing is applied on top of the failed step
+    lk.pull(ids, training=False)
+    torch.cuda.synchronize()
+    print("FAILED FLAG", rt.failed, flush=True)
+agreed = tn.core.recover()
+inv2 = lk.pull(ids, training=False)
+torch.cuda.synchronize(); rt.check_status()
+same = bool(torch.equal(lk.U[inv2.long()], before))
+lk.pull(ids, training=True); lk.push()
+torch.cuda.synchronize(); rt.check_status(); rt.barrier()
+print("RECOVERED epoch=%d same_rows=%s" % (agreed, same), flush=True)
+tn.core.shutdown()
+''')
+    port = _port()
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                   TN_PG_TIMEOUT_S="60", TN_WAIT_BUDGET_S="0.05", TN_SYMM_BACKEND="ipc", TN_USE_MULTIMEM="0", NCCL_NVLS_ENABLE="0",
+                   PYTHONPATH=ROOT)
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=240)[0] for p in procs]
+    assert "ERROR code=5 phase=3 peer=1" in outs[0] and "NO ERROR" not in outs[0], outs[0][-3000:]
+    assert "FAILED FLAG True" in outs[0], outs[0][-2000:]
+    for o in outs:
+        assert "same_rows=True" in o, o[-3000:]
