@@ -108,7 +108,7 @@ os._exit(0)
 @pytest.mark.timeout(300)
 def test_peer_wait_runs_out_on_the_pull_and_recover_realigns(tmp_path):
     """Rank 1 skips one pull launch (a host-side hook; nothing on any GPU faults or spins for ever).  Rank 0's fused pull
-    kernel gives up waiting for rank 1's id segment after the 50 ms budget, records "peer wait timed out, owner
+    kernel gives up waiting for rank 1's id segment after the 0.3 s budget, records "peer wait timed out, owner
     phase, peer 1" and returns; its context keeps computing.  Both ranks then call ``core.recover()`` and the next
     pull on both returns the same rows as before the failure.  Plain peer loads, no NVSwitch multicast mapping."""
     if torch.cuda.device_count() < 2:
@@ -124,9 +124,11 @@ t = GpuSparseTable(tn.core.Adam(learning_rate=1e-2, initial_scale=0.1), 8, rows=
 lk = t.link(4096)
 g = torch.Generator().manual_seed(5 + rt.rank)
 ids = torch.randint(0, 3000, (2048,), generator=g, dtype=torch.int64).to(rt.device)
+torch.cuda.synchronize(); rt.barrier()
 inv = lk.pull(ids, training=False)
 torch.cuda.synchronize(); rt.check_status()
 before = lk.U[inv.long()].clone()
+rt.barrier()
 lk.pull(ids, training=False)
 torch.cuda.synchronize(); rt.check_status(); rt.barrier()
 # ---- the step in which rank 1 never launches its pull
@@ -144,9 +146,11 @@ if rt.rank == 0:
     torch.cuda.synchronize()
     print("FAILED FLAG", rt.failed, flush=True)
 agreed = tn.core.recover()
+torch.cuda.synchronize(); rt.barrier()
 inv2 = lk.pull(ids, training=False)
 torch.cuda.synchronize(); rt.check_status()
 same = bool(torch.equal(lk.U[inv2.long()], before))
+rt.barrier()
 lk.pull(ids, training=True); lk.push()
 torch.cuda.synchronize(); rt.check_status(); rt.barrier()
 print("RECOVERED epoch=%d same_rows=%s" % (agreed, same), flush=True)
@@ -156,7 +160,7 @@ tn.core.shutdown()
     procs = []
     for r in range(2):
         env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
-                   TN_PG_TIMEOUT_S="60", TN_WAIT_BUDGET_S="0.05", TN_SYMM_BACKEND="ipc", TN_USE_MULTIMEM="0", NCCL_NVLS_ENABLE="0",
+                   TN_PG_TIMEOUT_S="60", TN_WAIT_BUDGET_S="0.3", TN_SYMM_BACKEND="ipc", TN_USE_MULTIMEM="0", NCCL_NVLS_ENABLE="0",
                    PYTHONPATH=ROOT)
         procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
     outs = [p.communicate(timeout=240)[0] for p in procs]
