@@ -179,21 +179,24 @@ def recover() -> int:
         rt.failed = False
         rt.barrier()
         return 0
+    from ..ops import dense_table as _dt, sparse_table_gpu as _st
+
     rt.barrier()                       # includes a device synchronise: nothing of the failed step is still running
+    sparse, dense = list(_st.live_tables), list(_dt.live_tables)
     mine = 0
-    for t in _sparse_tables:
+    for t in sparse:
         mine = max(mine, int(t.epoch.item()))
-    for t in _dense_tables:
+    for t in dense:
         mine = max(mine, t.exchange_epoch())
     for t in _bn_tables:
         if getattr(t, "_epoch", None) is not None:
             mine = max(mine, int(t._epoch.item()))
     agreed = max(rt.all_gather_object(mine)) + 2
-    for t in _sparse_tables:
+    for t in sparse:
         t.epoch.fill_(agreed)
         for lk in t.links:
             lk.reset_exchange()
-    for t in _dense_tables:
+    for t in dense:
         t.reset_exchange(agreed)
     for t in _bn_tables:
         if getattr(t, "_epoch", None) is not None:

@@ -27,6 +27,11 @@ class Config:
     table_load_factor: float = 0.5
     #: head-room factor of one (sender, owner) segment over the even split unique/world
     owner_segment_slack: float = 1.3
+    #: several GPUs: an exchange segment holds a whole batch (any spread of signs over the owners is accepted) as long
+    #: as one layer's exchange buffers stay below this many MiB per GPU; beyond it segments are sized by the slack above
+    segment_worst_case_mb: int = 1024
+    #: enlarge a shard (row slab x2, key array re-filled) when a status poll finds it this full; 0 = never
+    table_grow_at: float = 0.85
     #: wall-time budget of every device-side wait, in seconds
     wait_budget_s: float = 5.0
     #: seed of the deterministic row initialiser
@@ -63,6 +68,8 @@ class Config:
         c.table_rows_per_gpu = _env("TN_TABLE_ROWS", c.table_rows_per_gpu, int)
         c.table_load_factor = _env("TN_TABLE_LOAD_FACTOR", c.table_load_factor, float)
         c.owner_segment_slack = _env("TN_SEGMENT_SLACK", c.owner_segment_slack, float)
+        c.segment_worst_case_mb = _env("TN_SEGMENT_WORST_CASE_MB", c.segment_worst_case_mb, int)
+        c.table_grow_at = _env("TN_TABLE_GROW_AT", c.table_grow_at, float)
         c.wait_budget_s = _env("TN_WAIT_BUDGET_S", c.wait_budget_s, float)
         c.seed = _env("TN_SEED", c.seed, int)
         c.use_multimem = _env("TN_USE_MULTIMEM", c.use_multimem, int)

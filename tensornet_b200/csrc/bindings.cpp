@@ -78,10 +78,22 @@ struct SparseCtx {
   int pull_lanes = 1, push_lanes = 1;
   int tile_rows = 0;   // staged row return of the pull (0 = rows go straight to the requester's matrix)
   py::dict keep;   // keeps the tensors alive
+  at::Tensor tbl_dev;  // the table descriptor in device memory (what launches inside CUDA graphs read)
+
+  void upload_table() {
+    if (!tbl_dev.defined()) {
+      at::Tensor rows = keep["table"].cast<py::dict>()["rows"].cast<at::Tensor>();
+      tbl_dev = at::empty({(int64_t)((sizeof(tn::TableView) + 7) / 8)}, at::TensorOptions().dtype(at::kLong).device(rows.device()));
+    }
+    // stream-ordered with the launches around it; the source is copied out before the call returns (pageable memory)
+    check(cudaMemcpyAsync(tbl_dev.data_ptr(), &t, sizeof(tn::TableView), cudaMemcpyHostToDevice, at::cuda::getCurrentCUDAStream().stream()),
+          "table descriptor upload");
+  }
 
   SparseCtx(py::dict table, py::dict comm, py::dict opt) {
     keep["table"] = table; keep["comm"] = comm;
     t = table_from_dict(table);
+    upload_table();
     o = opt_from_dict(opt);
     c.world = comm["world"].cast<int>();
     c.rank = comm["rank"].cast<int>();
@@ -145,7 +157,8 @@ struct SparseCtx {
   }
 
   void set_opt(py::dict opt) { o = opt_from_dict(opt); }
-  void set_table(py::dict table) { keep["table"] = table; t = table_from_dict(table); }
+  // The shard's arrays were replaced (growth, compaction): launches already recorded in CUDA graphs pick the new ones up.
+  void set_table(py::dict table) { keep["table"] = table; t = table_from_dict(table); upload_table(); }
 
   void pull(at::Tensor ids, at::Tensor inverse, c10::optional<at::Tensor> labels, int label_mod, bool training, bool lookup_only) {
     TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous(), "ids: contiguous int64 CUDA tensor");
@@ -153,6 +166,7 @@ struct SparseCtx {
     c10::cuda::CUDAGuard guard(ids.device());
     tn::PullArgs a{};
     a.c = c; a.tbl = t; a.opt = o;
+    a.tbl_dev = reinterpret_cast<const tn::TableView*>(tbl_dev.data_ptr());
     a.ids = ptr_of<const long long>(ids);
     a.n_ids = (int)ids.numel();
     a.inverse = ptr_of<int>(inverse);
@@ -172,6 +186,7 @@ struct SparseCtx {
   void push(int64_t work_hint, int max_ctas, const tn::DenseStepArgs* dense) {
     tn::PushArgs a{};
     a.c = c; a.tbl = t; a.opt = o; a.lanes = push_lanes;
+    a.tbl_dev = reinterpret_cast<const tn::TableView*>(tbl_dev.data_ptr());
     long long work = work_hint * push_lanes;
     if (work > (1ll << 30)) work = 1ll << 30;
     check(tn::launch_sparse_push(a, (int)work, max_ctas, dense, cur_stream()), "sparse_push_fused launch");
@@ -434,6 +449,19 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     c10::cuda::CUDAGuard guard(keys.device());
     tn::launch_table_lookup(table_from_dict(table), ptr_of<long long>(keys), (int)keys.numel(), ptr_of<int>(out_rows), cur_stream());
   });
+  m.def("table_rebuild_index", [](py::dict table, int n, at::Tensor status) {
+    tn::TableView t = table_from_dict(table);
+    TORCH_CHECK(n >= 0 && n <= t.row_cap, "table_rebuild_index: more rows than the slab holds");
+    c10::cuda::CUDAGuard guard(status.device());
+    tn::launch_table_rebuild_index(t, n, ptr_of<int>(status), cur_stream());
+  }, "fill an all-empty key array from the signs of rows [0, n)");
+  m.def("table_keep_mask", [](py::dict table, int kind, bool evict, float show_threshold, int no_show_days, int logic, int n,
+                              at::Tensor keep) {
+    TORCH_CHECK(keep.scalar_type() == at::kByte && keep.numel() >= n, "table_keep_mask: keep must be uint8[n]");
+    tn::ExportRule rule{evict ? 1 : 0, show_threshold, no_show_days, logic};
+    c10::cuda::CUDAGuard guard(keep.device());
+    tn::launch_table_keep_mask(table_from_dict(table), kind, rule, n, keep.data_ptr<unsigned char>(), cur_stream());
+  }, "keep[r] = 0 for the rows the save-time eviction rule drops");
   m.def("table_decay", [](py::dict table, int kind, float rate, int delta_days) {
     tn::launch_table_decay(table_from_dict(table), kind, rate, delta_days, cur_stream());
   });

@@ -75,10 +75,9 @@ __device__ __forceinline__ void prof_mark(const SparseCommView& c, int slot) {
 // brand-new row (owner) or recompute its initial value (other requesters of the same step), or read the stored
 // row; write the pulled row (w[dim], the two CVM columns when enabled, zero padding) to `dst`, which is either
 // the requester's matrix itself or a shared-memory tile that is written out afterwards.
-__device__ __forceinline__ void pull_return_row(const PullArgs& a, unsigned long long epoch, bool need_ou, int q,
-                                                unsigned long long key, float* dst, int gl, int G) {
+__device__ __forceinline__ void pull_return_row(const PullArgs& a, const TableView& t, unsigned long long epoch, bool need_ou,
+                                                int q, unsigned long long key, float* dst, int gl, int G) {
   const SparseCommView& c = a.c;
-  const TableView& t = a.tbl;
   const SparseOptParams& o = a.opt;
   const int dim = t.dim, stride = t.stride;
   const int uchunks = c.ustride >> 2, rchunks = stride >> 2;
@@ -168,7 +167,12 @@ __device__ __forceinline__ void pull_return_row(const PullArgs& a, unsigned long
 // =======================================================================================
 __global__ void __launch_bounds__(kThreads, 1) sparse_pull_fused_kernel(const __grid_constant__ PullArgs a) {
   const SparseCommView& c = a.c;
-  const TableView& t = a.tbl;
+  // The table's arrays are read through a descriptor in device memory when the caller has one: the shard can then
+  // grow (new key array, longer row slab) between two launches of an already captured CUDA graph.
+  __shared__ TableView s_tbl;
+  if (threadIdx.x == 0) s_tbl = a.tbl_dev != nullptr ? *a.tbl_dev : a.tbl;
+  __syncthreads();
+  const TableView& t = s_tbl;
   GridSync gs;
   gs.init(c.bar, c.status, c.wait_ns);
   __shared__ unsigned long long s_flag;
@@ -461,7 +465,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_pull_fused_kernel(const __
         const int nrows = min(TR, s_n[s] - j0);
         const unsigned long long* src = (s == R) ? c.stage_ids + (size_t)R * capo : c.inbox_ids[R] + (size_t)s * capo;
         for (int jr = sub; jr < nrows; jr += rpp)
-          pull_return_row(a, epoch, need_ou, s * capo + j0 + jr, __ldcg(&src[j0 + jr]), tile + (size_t)jr * ustride, gl, G);
+          pull_return_row(a, t, epoch, need_ou, s * capo + j0 + jr, __ldcg(&src[j0 + jr]), tile + (size_t)jr * ustride, gl, G);
         __syncwarp();
         float4* d4 = reinterpret_cast<float4*>(c.U[s] + ((size_t)R * capo + j0) * ustride);
         const float4* t4 = reinterpret_cast<const float4*>(tile);
@@ -483,7 +487,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_pull_fused_kernel(const __
           const int r2 = __ldcg(&c.req_row[((R + k2) % W) * capo + (j2 - s_pre[k2])]);
           if (r2 >= 0 && !(r2 & (kReqNewOwner | kReqNewCopy))) prefetch_row_l2(t.rows + (size_t)r2 * stride, ustride, gl, G);
         }
-        pull_return_row(a, epoch, need_ou, s * capo + j, __ldcg(&src[j]), c.U[s] + ((size_t)R * capo + j) * ustride, gl, G);
+        pull_return_row(a, t, epoch, need_ou, s * capo + j, __ldcg(&src[j]), c.U[s] + ((size_t)R * capo + j) * ustride, gl, G);
       }
     }
   }
@@ -627,6 +631,27 @@ __device__ __forceinline__ void apply_row(const SparseOptParams& o, float* row, 
   } else {
     float* z = row + dim;
     float* n = row + 2 * dim;
+    if (VEC) {
+      // all four 16-byte loads of a chunk are issued before the arithmetic; approximate sqrt / division as in the
+      // other two optimizers (three square roots and a division per element otherwise dominate the update)
+      for (int ch = lane; ch < (dim >> 2); ch += G) {
+        const float4 x = *reinterpret_cast<const float4*>(g + 4 * ch);
+        float4 zz = *reinterpret_cast<float4*>(z + 4 * ch), nn = *reinterpret_cast<float4*>(n + 4 * ch);
+        float4 w = *reinterpret_cast<float4*>(row + 4 * ch);
+#define TN_SFTRL(cmp) { \
+        const float g2 = x.cmp * x.cmp; \
+        const float sn = fast_sqrt(nn.cmp + g2); \
+        zz.cmp += x.cmp - o.lr * (sn - fast_sqrt(nn.cmp)) * w.cmp; \
+        nn.cmp += g2; \
+        const float shr = zz.cmp > 0.f ? zz.cmp - o.lambda1 : zz.cmp + o.lambda1; \
+        w.cmp = fabsf(zz.cmp) > o.lambda1 ? -fast_div(shr, (o.ftrl_beta + sn) * o.lr + o.lambda2) : 0.f; }
+        TN_SFTRL(x) TN_SFTRL(y) TN_SFTRL(z) TN_SFTRL(w)
+#undef TN_SFTRL
+        *reinterpret_cast<float4*>(z + 4 * ch) = zz;
+        *reinterpret_cast<float4*>(n + 4 * ch) = nn;
+        *reinterpret_cast<float4*>(row + 4 * ch) = w;
+      }
+    } else {
     for (int e = lane; e < dim; e += G) {
       float x = g[e], w = row[e], nn = n[e];
       float g2 = x * x;
@@ -638,6 +663,7 @@ __device__ __forceinline__ void apply_row(const SparseOptParams& o, float* row, 
         nw *= zz > 0.f ? zz - o.lambda1 : zz + o.lambda1;
       }
       z[e] = zz; n[e] = nn; row[e] = nw;
+    }
     }
     if (lane == 0) reinterpret_cast<int*>(row)[3 * dim + 1] += (int)bshow;
   }
@@ -658,7 +684,10 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_push_fused_kernel(const __
     return;
   }
   const SparseCommView& c = a.c;
-  const TableView& t = a.tbl;
+  __shared__ TableView s_tbl;
+  if (threadIdx.x == 0) s_tbl = a.tbl_dev != nullptr ? *a.tbl_dev : a.tbl;
+  __syncthreads();
+  const TableView& t = s_tbl;
   GridSync gs;
   gs.init(c.bar, c.status, c.wait_ns, (unsigned)nb);
   __shared__ unsigned long long s_flag;

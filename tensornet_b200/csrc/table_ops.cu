@@ -46,6 +46,26 @@ __global__ void table_insert_keys_kernel(TableView t, const long long* __restric
   }
 }
 
+// Rebuild the key array of a shard from its row slab: keys[] / slots[] arrive all-empty, every row r < n gets its
+// sign (row_keys[r]) back in and points at r.  Used after the key array was replaced by a larger one and after a
+// compaction moved rows (the reference's unordered_map rehashes itself, core/ps/optimizer/optimizer_kernel.h:257-270).
+__global__ void table_rebuild_index_kernel(TableView t, int n, int* status) {
+  for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < n; r += gridDim.x * blockDim.x) {
+    const unsigned long long key = t.row_keys[r];
+    unsigned h = table_home(t, key);
+    bool placed = false;
+    for (unsigned probes = 0; probes <= t.cap_mask; ++probes) {
+      unsigned long long k = __ldcg(&t.keys[h]);
+      if (k == kEmptyKey) {
+        k = atomicCAS(&t.keys[h], kEmptyKey, key);
+        if (k == kEmptyKey) { t.slots[h] = r; placed = true; break; }
+      }
+      h = (h + 1) & t.cap_mask;
+    }
+    if (!placed) set_status(status, kTableFull, 21, 0);
+  }
+}
+
 __global__ void table_lookup_kernel(TableView t, const long long* __restrict__ keys, int n, int* __restrict__ out_rows) {
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
     int r = table_find(t, canon_key((unsigned long long)keys[i]));
@@ -82,6 +102,13 @@ __device__ __forceinline__ bool export_drop(const ExportRule& e, int kind, const
   }
   if (kind == kFtrl) return row[3 * dim] < e.show_threshold;
   return false;
+}
+
+// keep[r] = 1 unless the eviction rule drops row r (the DeleteByShow rule the reference applies while saving,
+// ada_grad_kernel.cc:197-204, ftrl_kernel.cc:126; here it can also shed the rows from the live shard).
+__global__ void table_keep_mask_kernel(TableView t, int kind, ExportRule rule, int n, unsigned char* keep) {
+  for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < n; r += gridDim.x * blockDim.x)
+    keep[r] = export_drop(rule, kind, t.rows + (size_t)r * t.stride, t.dim) ? 0 : 1;
 }
 
 __global__ void table_export_count_kernel(TableView t, int kind, ExportRule rule, int r0, int r1, int* counts) {
@@ -145,6 +172,16 @@ void launch_table_lookup(const TableView& t, const long long* keys, int n, int* 
   if (n <= 0) return;
   int blocks = (n + 255) / 256; if (blocks > 148 * 8) blocks = 148 * 8;
   table_lookup_kernel<<<blocks, 256, 0, st>>>(t, keys, n, out_rows);
+}
+void launch_table_rebuild_index(const TableView& t, int n, int* status, cudaStream_t st) {
+  if (n <= 0) return;
+  int blocks = (n + 255) / 256; if (blocks > 148 * 8) blocks = 148 * 8;
+  table_rebuild_index_kernel<<<blocks, 256, 0, st>>>(t, n, status);
+}
+void launch_table_keep_mask(const TableView& t, int kind, const ExportRule& rule, int n, unsigned char* keep, cudaStream_t st) {
+  if (n <= 0) return;
+  int blocks = (n + 255) / 256; if (blocks > 148 * 8) blocks = 148 * 8;
+  table_keep_mask_kernel<<<blocks, 256, 0, st>>>(t, kind, rule, n, keep);
 }
 void launch_table_decay(const TableView& t, int kind, float rate, int delta_days, cudaStream_t st) {
   table_decay_kernel<<<148 * 4, 256, 0, st>>>(t, kind, rate, delta_days);

@@ -20,6 +20,8 @@ void launch_seq_bwd(float* gU, int gstride, const int* inverse, const int* offse
 void launch_table_insert_keys(const TableView& t, const long long* keys, int n, int* out_rows, int* status, cudaStream_t st);
 void launch_table_lookup(const TableView& t, const long long* keys, int n, int* out_rows, cudaStream_t st);
 void launch_table_decay(const TableView& t, int kind, float rate, int delta_days, cudaStream_t st);
+void launch_table_rebuild_index(const TableView& t, int n, int* status, cudaStream_t st);
+void launch_table_keep_mask(const TableView& t, int kind, const ExportRule& rule, int n, unsigned char* keep, cudaStream_t st);
 void launch_table_export(const TableView& t, int kind, const ExportRule& rule, int r0, int r1, int* counts, int* cursors,
                          unsigned long long* out_keys, float* out_rows, int rf, cudaStream_t st);
 

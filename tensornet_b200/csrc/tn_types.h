@@ -66,6 +66,7 @@ struct SparseCommView {
 struct PullArgs {
   SparseCommView c;
   TableView tbl;
+  const TableView* tbl_dev;   // when not null: the same descriptor in device memory, read at kernel start instead of `tbl`
   SparseOptParams opt;
   const long long* ids;   // [n_ids] raw signs of the batch (all columns of the layer)
   int n_ids;
@@ -81,6 +82,7 @@ struct PullArgs {
 struct PushArgs {
   SparseCommView c;
   TableView tbl;
+  const TableView* tbl_dev;   // as in PullArgs
   SparseOptParams opt;
   int lanes;
 };

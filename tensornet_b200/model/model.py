@@ -166,9 +166,10 @@ class _StatusPoll:
     now, read when the next poll comes round.  A device error therefore surfaces at most two polling periods
     after the step that hit it."""
 
-    def __init__(self, rt, every: int):
+    def __init__(self, rt, every: int, tables=()):
         self.rt, self.every = rt, max(1, int(every))
-        self.host = torch.zeros(8, dtype=torch.int32).pin_memory()
+        self.tables = [t for t in tables if hasattr(t, "n_rows_dev")]      # GPU shards whose fill level is watched too
+        self.host = torch.zeros(8 + len(self.tables), dtype=torch.int32).pin_memory()
         self.event = torch.cuda.Event()
         self.pending = False
         self.count = 0
@@ -182,8 +183,13 @@ class _StatusPoll:
             code = int(self.host[0])
             if code != 0:
                 self.rt.raise_status(code, int(self.host[1]), int(self.host[2]))
+            if core.config.table_grow_at > 0:
+                for i, t in enumerate(self.tables):       # a shard that is filling up gets a longer slab before it overflows
+                    t.maybe_grow(int(self.host[8 + i]), core.config.table_grow_at)
         if not self.pending:
-            self.host.copy_(self.rt.status, non_blocking=True)
+            self.host[:8].copy_(self.rt.status, non_blocking=True)
+            for i, t in enumerate(self.tables):
+                self.host[8 + i: 9 + i].copy_(t.n_rows_dev, non_blocking=True)
             self.event.record()
             self.pending = True
 
@@ -248,7 +254,8 @@ class Model(nn.Module):
         self._use_graph = rt.on_gpu and (core.config.cuda_graph if cuda_graph is None else cuda_graph)
         self._graph_warmup = graph_warmup
         if rt.on_gpu:
-            self._status_poll = _StatusPoll(rt, core.config.status_poll_steps)
+            tables = {id(l.table): l.table for l in self.sparse_layers() if hasattr(l, "table")}
+            self._status_poll = _StatusPoll(rt, core.config.status_poll_steps, tables.values())
             self._copy_stream = torch.cuda.Stream(device=rt.device)
         if optimizer is not None:
             optimizer.attach(self.named_parameters())
@@ -797,6 +804,16 @@ class Model(nn.Module):
         for kind, m in self._tn_children():
             if kind == "sparse":
                 m.show_decay(delta_days)
+
+    def evict_sparse_rows(self) -> int:
+        """Drop from the live tables the rows that the optimizer's save-time rule would not write to a checkpoint
+        (the reference applies that rule only while saving, core/ps/optimizer/optimizer_kernel.h:331-334; a long job
+        on fixed HBM wants the memory back as well).  Call between steps; returns the number of rows dropped here."""
+        n = 0
+        for kind, m in self._tn_children():
+            if kind == "sparse" and hasattr(m.table, "evict"):
+                n += m.table.evict()
+        return n
 
 
 class PCGradModel(Model):

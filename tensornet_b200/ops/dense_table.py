@@ -10,6 +10,7 @@ re-pointed to views of the flat array, so there is no copy-back step
 """
 from __future__ import annotations
 
+import weakref
 from typing import List, Sequence, Tuple
 
 import torch
@@ -22,6 +23,9 @@ from ..core.runtime import runtime
 from ..parallel.symm import SymmArena
 
 ALIGN = 8  # elements; keeps every parameter's bf16 shadow 16-byte aligned for TMA
+
+#: every live dense table of this process (``core.recover`` resets the exchange state of all of them)
+live_tables: "weakref.WeakSet[DenseTable]" = weakref.WeakSet()
 
 
 class DenseTable:
@@ -36,6 +40,7 @@ class DenseTable:
         self.offsets: List[int] = []
         self.sizes: List[int] = []
         self.total = 0
+        live_tables.add(self)
 
     # ------------------------------------------------------------------
     def init(self, named_params: Sequence[Tuple[str, torch.Tensor]]):

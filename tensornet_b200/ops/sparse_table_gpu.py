@@ -10,6 +10,7 @@ the reference (core/kernels/sparse_table_ops.cc:221), so checkpoint directories 
 from __future__ import annotations
 
 import math
+import weakref
 from typing import Optional, Tuple
 
 import numpy as np
@@ -32,6 +33,10 @@ def row_floats(kind: int, dim: int) -> int:
 
 def next_pow2(x: int) -> int:
     return 1 << max(1, (int(x) - 1).bit_length())
+
+
+#: every live shard of this process (``core.recover`` resets the exchange state of all of them)
+live_tables: "weakref.WeakSet[GpuSparseTable]" = weakref.WeakSet()
 
 
 class GpuSparseTable:
@@ -62,6 +67,8 @@ class GpuSparseTable:
         self.epoch = torch.zeros((1,), dtype=torch.int64, device=d)
         self.links = []
         self._zero_init = False
+        self.grown = 0               # how many times the shard has been enlarged
+        live_tables.add(self)
 
     # ------------------------------------------------------------------ views for the kernels
     def table_dict(self):
@@ -166,15 +173,91 @@ class GpuSparseTable:
         self.ext.table_lookup(self.table_dict(), ids.reshape(-1).contiguous(), out)
         return out
 
-    def compact(self, keep_mask: torch.Tensor):
-        """Rebuild the shard keeping only rows where ``keep_mask[:n_rows]`` is true."""
+    # ------------------------------------------------------------------ growth and shedding (between steps)
+    def _swap_arrays(self):
+        """The shard's arrays were replaced: hand the new ones to every link.  Launches already recorded in CUDA
+        graphs read the table through a descriptor in device memory, so they follow without a new capture."""
+        for lk in self.links:
+            lk.ctx.set_table(self.table_dict())
+
+    def load_factor(self, rows: Optional[int] = None) -> float:
+        return (self.n_rows if rows is None else rows) / self.keys.numel()
+
+    def grow(self, new_row_cap: Optional[int] = None):
+        """Make room for more rows: a longer row slab (the rows in use are copied over on the device) and, when the
+        key array would pass the configured load factor, a larger key array that is re-filled from the signs of the
+        rows.  Call between steps; rows keep their indices.  The reference's sub-maps rehash themselves and its
+        allocator adds a 65 536-row slab at a time (core/ps/optimizer/optimizer_kernel.h:257-270,
+        core/utility/allocator.h:74-92)."""
+        rt = runtime()
+        torch.cuda.synchronize(self.dev)
         n = self.n_rows
-        rf = row_floats(self.kind, self.dim)
-        keep = keep_mask[:n].nonzero().flatten()
-        signs = self.row_keys[:n][keep].cpu().numpy().view(np.uint64)
-        rows = self.rows[:n, :rf][keep].cpu().numpy()
-        self.clear()
-        self.load_rows(signs, rows)
+        new_cap = int(new_row_cap or max(2 * self.row_cap, 1024))
+        if new_cap <= self.row_cap:
+            return
+        d = self.dev
+        rows = torch.empty((new_cap, self.stride), dtype=torch.float32, device=d)
+        rows[:n].copy_(self.rows[:n])
+        self.rows = rows
+        for name, fill in (("row_keys", None), ("row_tag", 0)):
+            old = getattr(self, name)
+            new = torch.empty((new_cap,), dtype=torch.int64, device=d) if fill is None else torch.zeros((new_cap,), dtype=torch.int64, device=d)
+            new[:n].copy_(old[:n])
+            setattr(self, name, new)
+        self.row_cap = new_cap
+        cap = next_pow2(int(new_cap / config.table_load_factor))
+        if cap > self.keys.numel():
+            self.keys = torch.full((cap,), -1, dtype=torch.int64, device=d)
+            self.slots = torch.full((cap,), -1, dtype=torch.int32, device=d)
+            self.ext.table_rebuild_index(self.table_dict(), n, rt.status)
+        self._swap_arrays()
+        self.grown += 1
+
+    def maybe_grow(self, rows_now: int, threshold: float = 0.85) -> bool:
+        """Grow when the slab is ``threshold`` full (``rows_now``: a recent reading of the row counter)."""
+        if rows_now >= threshold * self.row_cap:
+            self.grow()
+            return True
+        return False
+
+    def compact(self, keep_mask: torch.Tensor):
+        """Drop the rows whose ``keep_mask`` entry is false and close the gaps, all on the device: kept rows from
+        beyond the new end move into the holes before it, then the key array is cleared and re-filled from the
+        rows.  Row indices change, so call it between steps only."""
+        rt = runtime()
+        torch.cuda.synchronize(self.dev)
+        n = self.n_rows
+        keep = keep_mask[:n].to(torch.bool)
+        n_keep = int(keep.sum().item())
+        if n_keep < n:
+            holes = (~keep[:n_keep]).nonzero().flatten()
+            movers = keep[n_keep:].nonzero().flatten() + n_keep
+            piece = 1 << 22                                   # bounds the temporary of the gather
+            for s in range(0, int(movers.numel()), piece):
+                src, dst = movers[s:s + piece], holes[s:s + piece]
+                self.rows[dst] = self.rows[src]
+                self.row_keys[dst] = self.row_keys[src]
+            self.row_tag[:n].zero_()
+            self.n_rows_dev.fill_(n_keep)
+            self.keys.fill_(-1)
+            self.slots.fill_(-1)
+            self.ext.table_rebuild_index(self.table_dict(), n_keep, rt.status)
+        rt.check_status()
+        return n - n_keep
+
+    def evict(self) -> int:
+        """Shed the rows the optimizer's save-time rule would not write (AdaGrad: ``show < show_threshold`` or / and
+        ``no_show_days`` exceeded; Ftrl: ``show < show_threshold``; ada_grad_kernel.cc:197-204, ftrl_kernel.cc:126)
+        from the live shard.  Returns the number of rows dropped."""
+        from ..utils.checkpoint import _evict_args
+
+        ev = _evict_args(self.opt)
+        if not ev[0]:
+            return 0
+        n = self.n_rows
+        keep = torch.empty(max(n, 1), dtype=torch.uint8, device=self.dev)
+        self.ext.table_keep_mask(self.table_dict(), self.kind, True, float(ev[1]), int(ev[2]), int(ev[3]), n, keep)
+        return self.compact(keep)
 
 
 class GpuSparseLink:
@@ -192,7 +275,14 @@ class GpuSparseLink:
         if W == 1:
             capo = round_up(self.max_unique + 4, 32)
         else:
-            capo = round_up(int(math.ceil(self.max_unique / W * config.owner_segment_slack)) + 64, 32)   # whole row tiles
+            # One (sender, owner) segment.  The reference accepts any batch below bucket_size whatever the spread of
+            # its signs over sign % world (core/kernels/sparse_table_ops.cc:135-136), so a segment holds the whole
+            # batch when the exchange buffers stay within `segment_worst_case_mb`; larger layers size it for an even
+            # spread times `owner_segment_slack`, and a batch that overflows it is reported (owner segment overflow).
+            even = round_up(int(math.ceil(self.max_unique / W * config.owner_segment_slack)) + 64, 32)   # whole row tiles
+            worst = round_up(self.max_unique + 4, 32)
+            per_row = 4 * (3 * self.gstride + self.ustride) + 48          # inbox, accumulator, gradient, pulled row, bookkeeping
+            capo = worst if W * worst * per_row <= config.segment_worst_case_mb * (1 << 20) else even
         self.capo = capo
         n_seg = W * capo
         multi = W > 1

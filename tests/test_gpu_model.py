@@ -155,3 +155,43 @@ def test_step_log_windows_on_the_graph_path(tn_gpu, tmp_path):
         assert l["examples"] == 4 * B and l["examples_per_s"] > 0 and l["loss"] > 0 and l["status"] == "ok"
         for t in l["tables"].values():
             assert t["rows"] > 0 and 0 < t["max_load"] < 1
+
+
+def test_training_through_table_growth_matches_a_large_table(tn_gpu):
+    """A model whose shards start tiny trains from a CUDA graph while the status poll enlarges them (twice) and rows
+    are shed once in between; its predictions equal those of the same run on shards that were large from the start."""
+    tn = tn_gpu
+    slots = [str(i) for i in range(1, 5)]
+    B = 32
+
+    def run(rows, grow_at):
+        tn.core.config.status_poll_steps = 1
+        tn.core.config.table_grow_at = grow_at
+        torch.manual_seed(7)
+        opt = tn.core.AdaGrad(learning_rate=0.05, initial_g2sum=0.1, initial_scale=0.1, show_threshold=1.5, no_show_days=1000)
+        m = tn.models.DeepFM(slots, slots, dnn_hidden_units=(32, 16), embedding_dim=8, sparse_opt=opt, bucket_size=4 * B, table_rows=rows)
+        m.compile(optimizer=tn.optimizer.Optimizer(tn.core.Adam(learning_rate=1e-2)))
+        g = torch.Generator().manual_seed(3)
+        dropped = 0
+        for step in range(90):
+            ids = torch.randint(0, 40 * (step + 1), (len(slots), B), generator=g, dtype=torch.int64)
+            f = {tn.data.PACKED_KEY: tn.data.PackedFeatures(slots, ids=ids)}
+            m.train_on_batch(f, (ids[0] % 3 == 0).float())
+            if step == 60:
+                torch.cuda.synchronize()
+                dropped = m.evict_sparse_rows()
+        torch.cuda.synchronize()
+        tn.core.runtime().check_status()
+        ids = torch.randint(0, 2000, (len(slots), B), generator=g, dtype=torch.int64)
+        p = m.predict_on_batch({tn.data.PACKED_KEY: tn.data.PackedFeatures(slots, ids=ids)})
+        return p.float().cpu(), m.deep_emb.table.grown, dropped, m._graph is not None
+
+    try:
+        p_small, grown, dropped_s, graphed = run(512, 0.7)
+        p_big, grown_big, dropped_b, _ = run(1 << 14, 0.0)
+    finally:
+        tn.core.config.status_poll_steps = 16
+        tn.core.config.table_grow_at = 0.85
+    assert graphed and grown >= 2 and grown_big == 0
+    assert dropped_s == dropped_b and dropped_s > 0
+    assert torch.allclose(p_small, p_big, atol=1e-6), float((p_small - p_big).abs().max())

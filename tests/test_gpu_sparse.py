@@ -231,3 +231,44 @@ def test_staged_row_return_with_a_48k_tile_buffer(tn_gpu, status_ok):
         lk.push()
     finally:
         tn.core.config.staged_row_return = old
+
+
+def test_shard_grows_and_compacts_on_the_device(tn_gpu, status_ok):
+    """A shard that starts with 256 rows takes 3 000 signs through two enlargements (longer slab, re-filled key array)
+    and ends up with the same row for every sign as a shard that was large from the start; dropping half of the rows
+    on the device keeps the others findable and frees the slab for new signs."""
+    tn = tn_gpu
+    opt = tn.core.AdaGrad(learning_rate=0.05, initial_g2sum=0.1, initial_scale=0.1)
+    small, lks = _mk(tn, opt, 8, rows=256, max_unique=512)
+    big, lkb = _mk(tn, opt, 8, rows=1 << 13, max_unique=512)
+    g = torch.Generator().manual_seed(11)
+    for step in range(12):
+        ids = (torch.randperm(100000, generator=g)[:250] + 1).to(small.dev)
+        if small.n_rows + 250 > small.row_cap:
+            small.grow()
+        for t, lk in ((small, lks), (big, lkb)):
+            inv = lk.pull(ids, training=True)
+            lk.gU[inv.long().unique(), :8] = 0.25
+            lk.push()
+    torch.cuda.synchronize()
+    assert small.grown >= 2 and small.n_rows == big.n_rows
+    ks, rs = small.dump()
+    kb, rb = big.dump()
+    os_, ob = np.argsort(ks), np.argsort(kb)
+    assert np.array_equal(ks[os_], kb[ob]) and np.array_equal(rs[os_], rb[ob])
+    # compaction: keep the even row indices
+    n = small.n_rows
+    keep = torch.zeros(n, dtype=torch.bool, device=small.dev)
+    keep[::2] = True
+    kept_keys = torch.from_numpy(ks.view(np.int64)).to(small.dev)[::2]
+    dropped_keys = torch.from_numpy(ks.view(np.int64)).to(small.dev)[1::2]
+    kept_rows = torch.from_numpy(rs).to(small.dev)[::2]
+    dropped = small.compact(keep)
+    assert dropped == n - kept_keys.numel() and small.n_rows == kept_keys.numel()
+    idx = small.lookup_rows(kept_keys).long()
+    assert int(idx.min()) >= 0 and int(idx.max()) < small.n_rows
+    assert torch.equal(small.rows[idx, : kept_rows.shape[1]], kept_rows)
+    assert int(small.lookup_rows(dropped_keys).max()) == -1
+    inv = lks.pull(dropped_keys[:200].contiguous(), training=False)      # the freed part of the slab takes new signs
+    torch.cuda.synchronize()
+    assert small.n_rows == kept_keys.numel() + 200
