@@ -187,8 +187,8 @@ def test_training_through_table_growth_matches_a_large_table(tn_gpu):
         return p.float().cpu(), m.deep_emb.table.grown, dropped, m._graph is not None
 
     try:
-        p_small, grown, dropped_s, graphed = run(512, 0.7)
-        p_big, grown_big, dropped_b, _ = run(1 << 14, 0.0)
+        p_small, grown, dropped_s, graphed = run(2048, 0.5)
+        p_big, grown_big, dropped_b, _ = run(1 << 15, 0.0)
     finally:
         tn.core.config.status_poll_steps = 16
         tn.core.config.table_grow_at = 0.85
