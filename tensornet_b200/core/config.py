@@ -52,6 +52,8 @@ class Config:
     dense_small_grid: int = 0
     #: rows per streamed piece when a GPU shard is saved (bounds the pinned host staging buffer)
     checkpoint_chunk_rows: int = 1 << 22
+    #: rows per piece when a shard is read back (eight block files are read side by side, each one piece at a time)
+    checkpoint_load_chunk_rows: int = 1 << 18
     #: check the guard words behind the shared-memory regions after every training pass as well (they are always
     #: checked before a checkpoint is written and when a step-log window closes); costs a few small kernels and a sync
     verify_guards_each_pass: bool = False
@@ -79,6 +81,7 @@ class Config:
         c.overlap_dense_push = _env("TN_OVERLAP_DENSE_PUSH", c.overlap_dense_push, bool)
         c.dense_rides_push = _env("TN_DENSE_RIDES_PUSH", c.dense_rides_push, bool)
         c.checkpoint_chunk_rows = _env("TN_CKPT_CHUNK_ROWS", c.checkpoint_chunk_rows, int)
+        c.checkpoint_load_chunk_rows = _env("TN_CKPT_LOAD_CHUNK_ROWS", c.checkpoint_load_chunk_rows, int)
         c.verify_guards_each_pass = _env("TN_VERIFY_GUARDS", c.verify_guards_each_pass, bool)
         c.cuda_graph = _env("TN_CUDA_GRAPH", c.cuda_graph, bool)
         c.status_poll_steps = _env("TN_STATUS_POLL_STEPS", c.status_poll_steps, int)

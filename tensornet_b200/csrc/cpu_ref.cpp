@@ -540,8 +540,82 @@ struct ParsedBlock {
   std::vector<float> rows;
 };
 
-void parse_txt_block(const std::string& data, int kind, int dim, bool use_cvm, const std::string& want_opt, ParsedBlock& out) {
+// One text data line -> one row appended to `out` (empty lines are skipped).  `line` is modified in place.
+void parse_txt_line(std::string& line, int kind, int dim, bool use_cvm, std::vector<const char*>& tok, ParsedBlock& out) {
   const int rf = tn::row_floats(kind, dim);
+  tok.clear();
+  char* p = &line[0];
+  while (*p) {
+    while (*p == '\t' || *p == ' ' || *p == '\r') ++p;
+    if (!*p) break;
+    tok.push_back(p);
+    while (*p && *p != '\t' && *p != ' ' && *p != '\r') ++p;
+    if (*p) *p++ = 0;
+  }
+  if (tok.empty()) return;
+  const uint64_t sign = std::strtoull(tok[0], nullptr, 10);
+  out.signs.push_back(sign);
+  const size_t base = out.rows.size();
+  out.rows.resize(base + rf, 0.f);
+  float* row = out.rows.data() + base;
+  if (kind == kAdaGrad) {
+    // sign dim w*dim g2sum show [no_show_days [click]]; files written before no_show_days existed have dim+4 columns
+    const int nt = (int)tok.size();
+    if (nt < dim + 4) throw std::runtime_error("sparse block: short AdaGrad line");
+    for (int k = 0; k < dim; ++k) row[k] = std::strtof(tok[2 + k], nullptr);
+    row[dim] = std::strtof(tok[2 + dim], nullptr);
+    row[dim + 1] = std::strtof(tok[3 + dim], nullptr);
+    if (nt >= dim + 5) reinterpret_cast<int32_t*>(row)[dim + 3] = std::atoi(tok[4 + dim]);
+    if (nt >= dim + 6 && use_cvm) row[dim + 2] = std::strtof(tok[5 + dim], nullptr);
+  } else {
+    if ((int)tok.size() < 3 * dim + 2) throw std::runtime_error("sparse block: short Adam/Ftrl line");
+    for (int k = 0; k < dim; ++k) {
+      row[k] = std::strtof(tok[1 + 3 * k], nullptr);
+      row[dim + k] = std::strtof(tok[2 + 3 * k], nullptr);
+      row[2 * dim + k] = std::strtof(tok[3 + 3 * k], nullptr);
+    }
+    row[3 * dim] = std::strtof(tok[1 + 3 * dim], nullptr);
+  }
+}
+
+void check_txt_header(const std::string& l1, const std::string& l2, int dim, const std::string& want_opt) {
+  if (l1.rfind("opt_name:", 0) != 0) throw std::runtime_error("sparse block: missing opt_name header");
+  const std::string name = l1.substr(9);
+  if (name != want_opt)
+    throw std::runtime_error("last trained model with optimizer is:" + name + " but current model use:" + want_opt +
+                             " instead. you must make sure that use same optimizer when incremental training");
+  if (l2.rfind("dim:", 0) != 0) throw std::runtime_error("sparse block: missing dim header");
+  const int fdim = std::atoi(l2.c_str() + 4);
+  if (fdim != dim) throw std::runtime_error("sparse block: dim " + std::to_string(fdim) + " != table dim " + std::to_string(dim));
+}
+
+size_t bin_record_bytes(int kind, int dim, bool use_cvm) {
+  return 8 + (kind == kAdaGrad ? 4 * (size_t)(dim + 3 + (use_cvm ? 1 : 0)) : 4 * (size_t)(3 * dim + 1));
+}
+
+// One binary record at `p` -> one row appended to `out`.
+void parse_bin_record(const char* rec, int kind, int dim, bool use_cvm, ParsedBlock& out) {
+  const int rf = tn::row_floats(kind, dim);
+  uint64_t sign;
+  std::memcpy(&sign, rec, 8);
+  const char* p = rec + 8;
+  out.signs.push_back(sign);
+  const size_t base = out.rows.size();
+  out.rows.resize(base + rf, 0.f);
+  float* row = out.rows.data() + base;
+  if (kind == kAdaGrad) {
+    std::memcpy(row, p, 4 * dim);
+    std::memcpy(row + dim, p + 4 * dim, 4);           // g2sum
+    std::memcpy(row + dim + 1, p + 4 * dim + 4, 4);   // show
+    std::memcpy(row + dim + 3, p + 4 * dim + 8, 4);   // no_show_days
+    if (use_cvm) std::memcpy(row + dim + 2, p + 4 * dim + 12, 4);
+  } else {
+    std::memcpy(row, p, 4 * 3 * dim);
+    std::memcpy(row + 3 * dim, p + 4 * 3 * dim, 4);
+  }
+}
+
+void parse_txt_block(const std::string& data, int kind, int dim, bool use_cvm, const std::string& want_opt, ParsedBlock& out) {
   size_t pos = 0;
   auto next_line = [&](std::string& line) -> bool {
     if (pos >= data.size()) return false;
@@ -551,104 +625,234 @@ void parse_txt_block(const std::string& data, int kind, int dim, bool use_cvm, c
     pos = e + 1;
     return true;
   };
-  std::string line;
-  if (!next_line(line) || line.rfind("opt_name:", 0) != 0) throw std::runtime_error("sparse block: missing opt_name header");
-  const std::string name = line.substr(9);
-  if (name != want_opt)
-    throw std::runtime_error("last trained model with optimizer is:" + name + " but current model use:" + want_opt +
-                             " instead. you must make sure that use same optimizer when incremental training");
-  if (!next_line(line) || line.rfind("dim:", 0) != 0) throw std::runtime_error("sparse block: missing dim header");
-  const int fdim = std::atoi(line.c_str() + 4);
-  if (fdim != dim) throw std::runtime_error("sparse block: dim " + std::to_string(fdim) + " != table dim " + std::to_string(dim));
+  std::string l1, l2, line;
+  if (!next_line(l1)) throw std::runtime_error("sparse block: missing opt_name header");
+  if (!next_line(l2)) throw std::runtime_error("sparse block: missing dim header");
+  check_txt_header(l1, l2, dim, want_opt);
   std::vector<const char*> tok;
   while (next_line(line)) {
-    if (line.empty()) continue;
-    tok.clear();
-    char* p = &line[0];
-    while (*p) {
-      while (*p == '\t' || *p == ' ' || *p == '\r') ++p;
-      if (!*p) break;
-      tok.push_back(p);
-      while (*p && *p != '\t' && *p != ' ' && *p != '\r') ++p;
-      if (*p) *p++ = 0;
-    }
-    if (tok.empty()) continue;
-    const uint64_t sign = std::strtoull(tok[0], nullptr, 10);
-    out.signs.push_back(sign);
-    const size_t base = out.rows.size();
-    out.rows.resize(base + rf, 0.f);
-    float* row = out.rows.data() + base;
-    if (kind == kAdaGrad) {
-      // sign dim w*dim g2sum show [no_show_days [click]]; files written before no_show_days existed have dim+4 columns
-      const int nt = (int)tok.size();
-      if (nt < dim + 4) throw std::runtime_error("sparse block: short AdaGrad line");
-      for (int k = 0; k < dim; ++k) row[k] = std::strtof(tok[2 + k], nullptr);
-      row[dim] = std::strtof(tok[2 + dim], nullptr);
-      row[dim + 1] = std::strtof(tok[3 + dim], nullptr);
-      if (nt >= dim + 5) reinterpret_cast<int32_t*>(row)[dim + 3] = std::atoi(tok[4 + dim]);
-      if (nt >= dim + 6 && use_cvm) row[dim + 2] = std::strtof(tok[5 + dim], nullptr);
-    } else {
-      if ((int)tok.size() < 3 * dim + 2) throw std::runtime_error("sparse block: short Adam/Ftrl line");
-      for (int k = 0; k < dim; ++k) {
-        row[k] = std::strtof(tok[1 + 3 * k], nullptr);
-        row[dim + k] = std::strtof(tok[2 + 3 * k], nullptr);
-        row[2 * dim + k] = std::strtof(tok[3 + 3 * k], nullptr);
-      }
-      row[3 * dim] = std::strtof(tok[1 + 3 * dim], nullptr);
-    }
+    if (!line.empty()) parse_txt_line(line, kind, dim, use_cvm, tok, out);
   }
 }
 
 void parse_bin_block(const std::string& data, int kind, int dim, bool use_cvm, ParsedBlock& out) {
-  const int rf = tn::row_floats(kind, dim);
   if (data.size() < 4) throw std::runtime_error("sparse block: truncated binary header");
   int32_t fdim;
   std::memcpy(&fdim, data.data(), 4);
   if (fdim != dim) throw std::runtime_error("sparse block: dim " + std::to_string(fdim) + " != table dim " + std::to_string(dim));
-  const size_t rec = 8 + (kind == kAdaGrad ? 4 * (size_t)(dim + 3 + (use_cvm ? 1 : 0)) : 4 * (size_t)(3 * dim + 1));
-  size_t pos = 4;
-  while (pos + rec <= data.size()) {
-    uint64_t sign;
-    std::memcpy(&sign, data.data() + pos, 8);
-    const char* p = data.data() + pos + 8;
-    out.signs.push_back(sign);
-    const size_t base = out.rows.size();
-    out.rows.resize(base + rf, 0.f);
-    float* row = out.rows.data() + base;
-    if (kind == kAdaGrad) {
-      std::memcpy(row, p, 4 * dim);
-      std::memcpy(row + dim, p + 4 * dim, 4);           // g2sum
-      std::memcpy(row + dim + 1, p + 4 * dim + 4, 4);   // show
-      std::memcpy(row + dim + 3, p + 4 * dim + 8, 4);   // no_show_days
-      if (use_cvm) std::memcpy(row + dim + 2, p + 4 * dim + 12, 4);
-    } else {
-      std::memcpy(row, p, 4 * 3 * dim);
-      std::memcpy(row + 3 * dim, p + 4 * 3 * dim, 4);
-    }
-    pos += rec;
-  }
+  const size_t rec = bin_record_bytes(kind, dim, use_cvm);
+  for (size_t pos = 4; pos + rec <= data.size(); pos += rec) parse_bin_record(data.data() + pos, kind, dim, use_cvm, out);
 }
+
+// name = <prefix><digits><suffix>.gz  (the reference matches `(.*?)(\d+)(.*)\.gz`); returns false for other names
+bool split_block_name(const std::string& f, std::string* suffix) {
+  if (f.size() < 4 || f.compare(f.size() - 3, 3, ".gz") != 0) return false;
+  const std::string stem = f.substr(0, f.size() - 3);
+  size_t d0 = 0;
+  while (d0 < stem.size() && !(stem[d0] >= '0' && stem[d0] <= '9')) ++d0;
+  if (d0 == stem.size()) return false;
+  size_t d1 = d0;
+  while (d1 < stem.size() && stem[d1] >= '0' && stem[d1] <= '9') ++d1;
+  *suffix = stem.substr(d1);
+  return true;
+}
+
+// Streams ONE block file: every call to next() decompresses and parses up to `max_rows` further rows, so the
+// host never holds more than one piece of a block however large the file is.  The reference parses a block as a
+// stream as well, row by row (core/ps/optimizer/optimizer_kernel.h:366-420).  Mode: an explicit `_bin` / `_txt`
+// suffix decides, otherwise the first bytes are sniffed (`opt_name:` => text).
+class SparseBlockReader {
+ public:
+  SparseBlockReader(const std::string& path, int kind, int dim, bool use_cvm)
+      : path_(path), kind_(kind), dim_(dim), use_cvm_(use_cvm), rf_(tn::row_floats(kind, dim)) {
+    f_ = gzopen(path.c_str(), "rb");
+    if (!f_) throw std::runtime_error("cannot open for reading: " + path);
+    gzbuffer(f_, 1 << 20);
+    std::string name = path.substr(path.find_last_of('/') == std::string::npos ? 0 : path.find_last_of('/') + 1), suffix;
+    split_block_name(name, &suffix);
+    fill();
+    if (suffix == "_bin") bin_ = true;
+    else if (suffix == "_txt") bin_ = false;
+    else bin_ = buf_.compare(0, 9, "opt_name:") != 0;
+    if (bin_) {
+      while (buf_.size() < 4 && !eof_) fill();
+      if (buf_.size() < 4) throw std::runtime_error("sparse block: truncated binary header");
+      int32_t fdim;
+      std::memcpy(&fdim, buf_.data(), 4);
+      if (fdim != dim) throw std::runtime_error("sparse block: dim " + std::to_string(fdim) + " != table dim " + std::to_string(dim));
+      pos_ = 4;
+    } else {
+      std::string l1, l2;
+      if (!take_line(l1)) throw std::runtime_error("sparse block: missing opt_name header");
+      if (!take_line(l2)) throw std::runtime_error("sparse block: missing dim header");
+      check_txt_header(l1, l2, dim, opt_name(kind));
+    }
+  }
+  ~SparseBlockReader() { if (f_) gzclose(f_); }
+
+  // (signs uint64 [m], rows float32 [m, row_floats]) with m <= max_rows; m == 0 only at the end of the file
+  py::tuple next(int64_t max_rows) {
+    ParsedBlock out;
+    {
+      py::gil_scoped_release rel;
+      out.signs.reserve((size_t)std::min<int64_t>(max_rows, 1 << 20));
+      if (bin_) {
+        const size_t rec = bin_record_bytes(kind_, dim_, use_cvm_);
+        while ((int64_t)out.signs.size() < max_rows) {
+          while (buf_.size() - pos_ < rec && !eof_) fill();
+          if (buf_.size() - pos_ < rec) break;          // the trailing newline byte (or nothing) is left
+          parse_bin_record(buf_.data() + pos_, kind_, dim_, use_cvm_, out);
+          pos_ += rec;
+        }
+      } else {
+        std::string line;
+        std::vector<const char*> tok;
+        while ((int64_t)out.signs.size() < max_rows && take_line(line)) {
+          if (!line.empty()) parse_txt_line(line, kind_, dim_, use_cvm_, tok, out);
+        }
+      }
+    }
+    const ssize_t n = (ssize_t)out.signs.size();
+    py::array_t<uint64_t> signs(n);
+    py::array_t<float> rows({n, (ssize_t)rf_});
+    if (n) {
+      std::memcpy(signs.mutable_data(), out.signs.data(), (size_t)n * 8);
+      std::memcpy(rows.mutable_data(), out.rows.data(), (size_t)n * rf_ * 4);
+    }
+    return py::make_tuple(signs, rows);
+  }
+  bool is_binary() const { return bin_; }
+
+ private:
+  void fill() {      // drop what has been consumed, read another piece
+    if (pos_ > 0) { buf_.erase(0, pos_); pos_ = 0; }
+    const size_t old = buf_.size();
+    buf_.resize(old + (1 << 20));
+    const int n = gzread(f_, &buf_[old], 1 << 20);
+    if (n < 0) throw std::runtime_error("gzread failed: " + path_);
+    buf_.resize(old + (size_t)n);
+    if (n == 0) eof_ = true;
+  }
+  bool take_line(std::string& line) {
+    for (;;) {
+      const size_t e = buf_.find('\n', pos_);
+      if (e != std::string::npos) { line.assign(buf_, pos_, e - pos_); pos_ = e + 1; return true; }
+      if (eof_) {
+        if (pos_ >= buf_.size()) return false;
+        line.assign(buf_, pos_, buf_.size() - pos_);
+        pos_ = buf_.size();
+        return true;
+      }
+      fill();
+    }
+  }
+  std::string path_;
+  int kind_, dim_;
+  bool use_cvm_;
+  int rf_;
+  gzFile f_ = nullptr;
+  std::string buf_;
+  size_t pos_ = 0;
+  bool eof_ = false, bin_ = false;
+};
+
+// Block files of a rank directory (names the reference's reader would accept), sorted.
+std::vector<std::string> list_block_files(const std::string& dir) {
+  std::vector<std::string> out;
+  for (auto& f : list_dir(dir)) {
+    std::string suf;
+    if (split_block_name(f, &suf)) out.push_back(f);
+  }
+  std::sort(out.begin(), out.end());
+  return out;
+}
+
+// `sign \t [ \t w0 \t ... \t ]` lines of an exported embedding dictionary (brackets optional), streamed like a block.
+class DictionaryReader {
+ public:
+  explicit DictionaryReader(const std::string& path) : path_(path) {
+    f_ = gzopen(path.c_str(), "rb");      // reads plain files as well
+    if (!f_) throw std::runtime_error("cannot open for reading: " + path);
+    gzbuffer(f_, 1 << 20);
+  }
+  ~DictionaryReader() { if (f_) gzclose(f_); }
+  // (signs uint64 [m], weights float32 [m, dim]); dim is taken from the first line; m == 0 at the end
+  py::tuple next(int64_t max_rows) {
+    std::vector<uint64_t> signs;
+    std::vector<float> w;
+    {
+      py::gil_scoped_release rel;
+      std::string line;
+      std::vector<float> vals;
+      while ((int64_t)signs.size() < max_rows && take_line(line)) {
+        char* p = &line[0];
+        while (*p == ' ' || *p == '\t') ++p;
+        if (!*p) continue;
+        char* end = nullptr;
+        const uint64_t sign = std::strtoull(p, &end, 10);
+        if (end == p) throw std::runtime_error("dictionary: line does not start with a sign: " + path_);
+        p = end;
+        vals.clear();
+        while (*p) {
+          while (*p == ' ' || *p == '\t' || *p == '[' || *p == ']' || *p == ',' || *p == '\r') ++p;
+          if (!*p) break;
+          const float v = std::strtof(p, &end);
+          if (end == p) throw std::runtime_error("dictionary: bad number: " + path_);
+          vals.push_back(v);
+          p = end;
+        }
+        if (dim_ < 0) dim_ = (int)vals.size();
+        if ((int)vals.size() != dim_) throw std::runtime_error("dictionary: rows of different width: " + path_);
+        signs.push_back(sign);
+        w.insert(w.end(), vals.begin(), vals.end());
+      }
+    }
+    const ssize_t n = (ssize_t)signs.size();
+    py::array_t<uint64_t> s(n);
+    py::array_t<float> r({n, (ssize_t)std::max(dim_, 0)});
+    if (n) {
+      std::memcpy(s.mutable_data(), signs.data(), (size_t)n * 8);
+      std::memcpy(r.mutable_data(), w.data(), w.size() * 4);
+    }
+    return py::make_tuple(s, r);
+  }
+
+ private:
+  bool take_line(std::string& line) {
+    for (;;) {
+      const size_t e = buf_.find('\n', pos_);
+      if (e != std::string::npos) { line.assign(buf_, pos_, e - pos_); pos_ = e + 1; return true; }
+      if (eof_) {
+        if (pos_ >= buf_.size()) return false;
+        line.assign(buf_, pos_, buf_.size() - pos_);
+        pos_ = buf_.size();
+        return true;
+      }
+      if (pos_ > 0) { buf_.erase(0, pos_); pos_ = 0; }
+      const size_t old = buf_.size();
+      buf_.resize(old + (1 << 20));
+      const int n = gzread(f_, &buf_[old], 1 << 20);
+      if (n < 0) throw std::runtime_error("gzread failed: " + path_);
+      buf_.resize(old + (size_t)n);
+      if (n == 0) eof_ = true;
+    }
+  }
+  std::string path_;
+  gzFile f_ = nullptr;
+  std::string buf_;
+  size_t pos_ = 0;
+  bool eof_ = false;
+  int dim_ = -1;
+};
 
 // Reads every block file of a rank directory.  File-name rules of the reference's reader:
 // `<prefix><n><suffix>.gz`; an explicit `_bin` / `_txt` suffix decides the mode, otherwise the first
 // bytes are sniffed (`opt_name:` => text) so that suffix-less binary files are still read correctly.
 py::tuple read_sparse_dir(const std::string& dir, int kind, int dim, bool use_cvm) {
-  // name = <prefix><digits><suffix>.gz  (the reference matches `(.*?)(\d+)(.*)\.gz`)
-  auto split_name = [](const std::string& f, std::string* suffix) -> bool {
-    if (f.size() < 4 || f.compare(f.size() - 3, 3, ".gz") != 0) return false;
-    const std::string stem = f.substr(0, f.size() - 3);
-    size_t d0 = 0;
-    while (d0 < stem.size() && !(stem[d0] >= '0' && stem[d0] <= '9')) ++d0;
-    if (d0 == stem.size()) return false;
-    size_t d1 = d0;
-    while (d1 < stem.size() && stem[d1] >= '0' && stem[d1] <= '9') ++d1;
-    *suffix = stem.substr(d1);
-    return true;
-  };
   std::vector<std::string> files, suffixes;
   for (auto& f : list_dir(dir)) {
     std::string suf;
-    if (split_name(f, &suf)) { files.push_back(f); suffixes.push_back(suf); }
+    if (split_block_name(f, &suf)) { files.push_back(f); suffixes.push_back(suf); }
   }
   std::vector<ParsedBlock> parsed(files.size());
   std::vector<std::string> errors(files.size());
@@ -850,6 +1054,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("append", &SparseDirWriter::append)
       .def("append_grouped", &SparseDirWriter::append_grouped)
       .def("close", &SparseDirWriter::close);
+  py::class_<SparseBlockReader>(m, "SparseBlockReader")
+      .def(py::init<const std::string&, int, int, bool>(), py::arg("path"), py::arg("kind"), py::arg("dim"), py::arg("use_cvm"))
+      .def("next", &SparseBlockReader::next, py::arg("max_rows"))
+      .def_property_readonly("is_binary", &SparseBlockReader::is_binary);
+  py::class_<DictionaryReader>(m, "DictionaryReader")
+      .def(py::init<const std::string&>())
+      .def("next", &DictionaryReader::next, py::arg("max_rows"));
+  m.def("list_block_files", &list_block_files);
   m.def("unique_first_occurrence", &unique_first_occurrence);
   m.def("write_sparse_dir", &write_sparse_dir);
   m.def("read_sparse_dir", &read_sparse_dir);

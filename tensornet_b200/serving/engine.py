@@ -56,18 +56,20 @@ class EmbeddingDictionary:
                     n_rows=self.n_rows, dim=self.dim, stride=self.stride, use_cvm=0)
 
     @classmethod
-    def from_file(cls, path: str, dim: Optional[int] = None) -> "EmbeddingDictionary":
-        """Parse ``sign \\t [ \\t w... \\t ]`` lines (brackets optional), plain or gzip."""
-        opener = gzip.open if path.endswith(".gz") else open
+    def from_file(cls, path: str, dim: Optional[int] = None, chunk_rows: int = 1 << 18) -> "EmbeddingDictionary":
+        """Load ``sign \\t [ \\t w... \\t ]`` lines (brackets optional), plain or gzip.  The file is read and parsed in
+        native code, ``chunk_rows`` lines at a time; ``dim`` keeps only the first ``dim`` weights of a row."""
+        reader = _build.cpu_ext().DictionaryReader(path)
         signs, rows = [], []
-        with opener(path, "rt") as f:
-            for line in f:
-                tok = [t for t in line.split() if t not in ("[", "]")]
-                if len(tok) < 2:
-                    continue
-                signs.append(int(tok[0]))
-                rows.append([float(x) for x in (tok[1:1 + dim] if dim else tok[1:])])
-        return cls(np.array(signs, dtype=np.uint64), np.array(rows, dtype=np.float32).reshape(len(signs), -1))
+        while True:
+            s, r = reader.next(int(chunk_rows))
+            if not len(s):
+                break
+            signs.append(s)
+            rows.append(np.ascontiguousarray(r[:, :dim]) if dim else r)
+        if not signs:
+            return cls(np.zeros(0, np.uint64), np.zeros((0, dim or 1), np.float32))
+        return cls(np.concatenate(signs), np.concatenate(rows))
 
     @classmethod
     def from_table(cls, table) -> "EmbeddingDictionary":
