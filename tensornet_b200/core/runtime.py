@@ -130,6 +130,34 @@ class Runtime:
         dist.all_gather_object(out, obj, group=self.host_group)
         return out
 
+    def exchange_counts(self, counts) -> "torch.Tensor":
+        """``out[src][dst]`` = what rank ``src`` passed as ``counts[dst]`` (one small tensor all-gather on the host group)."""
+        mine = torch.as_tensor(counts, dtype=torch.int64).reshape(-1)
+        if self.world == 1:
+            return mine.reshape(1, -1)
+        out = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(out, mine, group=self.host_group)
+        return torch.stack(out)
+
+    def exchange_bytes(self, send, recv_sizes):
+        """All-to-all of raw host buffers on the host group: ``send[d]`` (uint8 tensor) goes to rank ``d`` and the
+        result's entry ``s`` (``recv_sizes[s]`` bytes) came from rank ``s``.  Point-to-point messages, no pickling:
+        this is the CPU path's stand-in for the reference's raw-attachment RPCs (core/ps_interface/ps_raw_interface.h)."""
+        recv = [torch.empty(int(n), dtype=torch.uint8) for n in recv_sizes]
+        recv[self.rank] = send[self.rank]
+        if self.world > 1:
+            ops = []
+            for k in range(1, self.world):
+                dst, src = (self.rank + k) % self.world, (self.rank - k) % self.world
+                if send[dst].numel():
+                    ops.append(dist.P2POp(dist.isend, send[dst].contiguous(), dst, group=self.host_group))
+                if recv[src].numel():
+                    ops.append(dist.P2POp(dist.irecv, recv[src], src, group=self.host_group))
+            if ops:
+                for w in dist.batch_isend_irecv(ops):
+                    w.wait()
+        return recv
+
     def broadcast_object(self, obj, src: int = 0):
         if self.world == 1:
             return obj

@@ -4,8 +4,12 @@ baseline.  Ranks exchange id lists, rows and gradient records over the gloo proc
 playing the part of the reference's brpc SparsePull / SparsePush RPCs
 (core/ps/ps_local_server.cc:30-54).
 
-Like the GPU path the step is synchronous: gradients of one sign coming from several ranks
-are summed and applied once by the owner.
+Like the GPU path the step is synchronous, and by default gradients of one sign coming from
+several ranks are summed and applied once by the owner.  ``apply_mode="arrival"`` restates the
+reference's own behaviour instead: every worker's records are applied one worker after the other
+in arrival order (here: rank order), each on top of the previous one's result
+(core/kernels/sparse_table_ops.cc:363-367, core/ps/ps_local_server.cc:43-54), which is what
+makes N workers pushing the same sign differ from one worker pushing the sum.
 """
 from __future__ import annotations
 
@@ -24,7 +28,11 @@ def row_floats(kind: int, dim: int) -> int:
 
 
 class CpuSparseTable:
-    def __init__(self, opt: OptimizerBase, dim: int, use_cvm: bool = False, name: str = "", rows=None):
+    def __init__(self, opt: OptimizerBase, dim: int, use_cvm: bool = False, name: str = "", rows=None,
+                 apply_mode: str = "sum"):
+        if apply_mode not in ("sum", "arrival"):
+            raise ValueError("apply_mode must be 'sum' (one update per sign and step) or 'arrival' (one per worker)")
+        self.apply_mode = apply_mode
         rt = runtime()
         self.ext = _build.cpu_ext()
         self.opt, self.kind, self.dim, self.use_cvm, self.name = opt, opt.kind, int(dim), bool(use_cvm), name
@@ -50,6 +58,7 @@ class CpuSparseTable:
 
     def link(self, max_unique: int) -> "CpuSparseLink":
         lk = CpuSparseLink(self)
+        lk.max_unique = int(max_unique)
         self.links.append(lk)
         return lk
 
@@ -82,6 +91,7 @@ class CpuSparseLink:
         self._uniq = np.zeros(0, np.uint64)
         self._show = self._click = np.zeros(0, np.float32)
         self._route = None
+        self.max_unique = 0
 
     def unique_counts(self):
         return [int(len(self._uniq))]
@@ -100,16 +110,36 @@ class CpuSparseLink:
         if t.world == 1:
             rows = t.native.pull(uniq)
         else:
-            owner = (uniq % np.uint64(t.world)).astype(np.int64)
+            W = t.world
+            owner = (uniq % np.uint64(W)).astype(np.int64)
             order = np.argsort(owner, kind="stable")
-            counts = np.bincount(owner, minlength=t.world)
-            send = np.split(uniq[order], np.cumsum(counts)[:-1])
-            everyone = rt.all_gather_object(send)                    # everyone[src][dst] = signs src wants from dst
-            mine = [everyone[src][t.rank] for src in range(t.world)]
-            answers = [t.native.pull(np.ascontiguousarray(m, dtype=np.uint64)) for m in mine]
-            back = rt.all_gather_object(answers)                     # back[owner][requester]
+            counts = np.bincount(owner, minlength=W)
+            cuts = np.cumsum(counts)[:-1]
+            pieces = np.split(uniq[order], cuts)
+            cap = self.max_unique
+            if 0 < cap <= (1 << 16) and len(uniq) <= cap:
+                # small layers: fixed-size messages [n | signs | padding] save the round that tells the sizes
+                send = []
+                for p in pieces:
+                    buf = np.zeros(cap + 1, np.uint64)
+                    buf[0] = len(p)
+                    buf[1:1 + len(p)] = p
+                    send.append(torch.from_numpy(buf.view(np.uint8)))
+                got = rt.exchange_bytes(send, [8 * (cap + 1)] * W)
+                mine = []
+                for gbuf in got:
+                    a = gbuf.numpy().view(np.uint64)
+                    mine.append(a[1:1 + int(a[0])])
+            else:
+                send = [torch.from_numpy(np.ascontiguousarray(p).view(np.uint8)) for p in pieces]
+                want = rt.exchange_counts(counts)[:, t.rank].tolist()             # signs each rank asks this shard for
+                got = rt.exchange_bytes(send, [8 * n for n in want])
+                mine = [g.numpy().view(np.uint64) for g in got]
+            answers = [torch.from_numpy(np.ascontiguousarray(t.native.pull(np.ascontiguousarray(m)), dtype=np.float32).reshape(-1).view(np.uint8))
+                       for m in mine]
+            back = rt.exchange_bytes(answers, [4 * self.pdim * int(n) for n in counts])
             rows = np.zeros((len(uniq), self.pdim), np.float32)
-            rows[order] = np.concatenate([back[o][t.rank] for o in range(t.world)], axis=0)
+            rows[order] = np.concatenate([b.numpy().view(np.float32).reshape(-1, self.pdim) for b in back], axis=0)
             self._route = (order, counts, mine)
         self.U = torch.from_numpy(np.ascontiguousarray(rows))
         self.gU = torch.zeros(len(uniq), self.dim)
@@ -121,18 +151,30 @@ class CpuSparseLink:
         if t.world == 1:
             t.native.push(self._uniq, g, self._show, self._click)
             return
-        order, counts, _ = self._route
+        order, counts, mine = self._route
         cuts = np.cumsum(counts)[:-1]
-        rec = (np.split(self._uniq[order], cuts), np.split(g[order], cuts), np.split(self._show[order], cuts),
-               np.split(self._click[order], cuts))
-        send = [tuple(r[d] for r in rec) for d in range(t.world)]
-        everyone = rt.all_gather_object(send)
-        signs = np.concatenate([everyone[s][t.rank][0] for s in range(t.world)])
-        grads = np.concatenate([everyone[s][t.rank][1] for s in range(t.world)], axis=0)
-        shows = np.concatenate([everyone[s][t.rank][2] for s in range(t.world)])
-        clicks = np.concatenate([everyone[s][t.rank][3] for s in range(t.world)])
+        # one message per owner: grad[n, dim] | show[n] | click[n] (the signs went over with the pull, in this order)
+        send = []
+        for gd, sh, cl in zip(np.split(g[order], cuts), np.split(self._show[order], cuts), np.split(self._click[order], cuts)):
+            buf = np.concatenate([np.ascontiguousarray(gd, dtype=np.float32).reshape(-1), sh.astype(np.float32), cl.astype(np.float32)])
+            send.append(torch.from_numpy(buf.view(np.uint8)))
+        got = rt.exchange_bytes(send, [4 * (self.dim + 2) * len(m) for m in mine])
+        parts = []
+        for m, b in zip(mine, got):
+            n = len(m)
+            f = b.numpy().view(np.float32)
+            parts.append((m, f[: n * self.dim].reshape(n, self.dim), f[n * self.dim: n * self.dim + n], f[n * self.dim + n:]))
+        if t.apply_mode == "arrival":
+            for m, gd, sh, cl in parts:         # one worker after the other, as the reference's servers apply them
+                if len(m):
+                    t.native.push(np.ascontiguousarray(m), np.ascontiguousarray(gd), np.ascontiguousarray(sh), np.ascontiguousarray(cl))
+            return
+        signs = np.concatenate([p[0] for p in parts])
         if len(signs) == 0:
             return
+        grads = np.concatenate([p[1] for p in parts], axis=0)
+        shows = np.concatenate([p[2] for p in parts])
+        clicks = np.concatenate([p[3] for p in parts])
         u, inv = np.unique(signs, return_inverse=True)
         gs = np.zeros((len(u), self.dim), np.float32)
         np.add.at(gs, inv, grads)

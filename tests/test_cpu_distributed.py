@@ -71,3 +71,52 @@ def test_other_model_families_on_two_ranks(tmp_path, model):
     assert 0.5 < rep["days"][0]["copc"] < 2.0
     cp = os.path.join(model_dir, "2020-05-10")
     assert sorted(os.listdir(os.path.join(cp, "sparse_table", "deep_input"))) == ["rank_0", "rank_1"]
+
+
+@pytest.mark.timeout(300)
+def test_apply_on_arrival_differs_from_one_summed_update(tmp_path):
+    """What changes when two workers push the same sign in one step.  ``apply_mode="sum"`` (this framework's
+    synchronous step) applies the sum of the two gradients once; ``apply_mode="arrival"`` restates the reference's
+    servers, which apply each worker's records when they arrive, one on top of the other
+    (core/kernels/sparse_table_ops.cc:363-367, core/ps/ps_local_server.cc:43-54).  With AdaGrad the two differ in a
+    way that can be written down: one step of size g1+g2 against g2sum + (g1+g2)^2/dim, versus two steps against
+    accumulators that grow in between."""
+    script = tmp_path / "w.py"
+    script.write_text('''
+import json, sys, numpy as np, torch
+import tensornet_b200 as tn
+from tensornet_b200.ops.sparse_table_cpu import CpuSparseTable
+tn.core.init()
+rt = tn.core.runtime()
+out = {}
+for mode in ("sum", "arrival"):
+    opt = tn.core.AdaGrad(learning_rate=0.1, initial_g2sum=0.5, initial_scale=0.0)
+    t = CpuSparseTable(opt, 2, apply_mode=mode)
+    lk = t.link(16)
+    ids = torch.tensor([4, 6], dtype=torch.int64)           # both owned by rank 0; both ranks pull and push them
+    lk.pull(ids, training=True)
+    lk.gU = torch.full((2, 2), 1.0 if rt.rank == 0 else 3.0)
+    lk.push()
+    rt.barrier()
+    lk.pull(ids, training=False)
+    out[mode] = lk.U[:, :2].tolist()
+if rt.rank == 0:
+    print(json.dumps(out))
+tn.core.shutdown()
+''')
+    env = dict(os.environ, TN_FORCE_CPU="1", OMP_NUM_THREADS="1", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), str(script)]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    got = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
+    lr, eps, g2 = 0.1, 1e-8, 0.5
+    # sum: g = 4 per element, g2sum += (16 + 16) / 2
+    w_sum = -lr * 4.0 / (eps + (g2 + 16.0) ** 0.5)
+    # arrival: rank 0's g = 1 first (g2sum += 1), then rank 1's g = 3 (g2sum += 9)
+    w_arr = -lr * 1.0 / (eps + (g2 + 1.0) ** 0.5) - lr * 3.0 / (eps + (g2 + 10.0) ** 0.5)
+    for row in got["sum"]:
+        assert row == pytest.approx([w_sum, w_sum], rel=1e-5)
+    for row in got["arrival"]:
+        assert row == pytest.approx([w_arr, w_arr], rel=1e-5)
+    assert abs(w_sum - w_arr) > 1e-3
