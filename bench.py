@@ -241,7 +241,7 @@ def main():
     slots = [str(i) for i in range(1, N_SLOTS + 1)]
     ranks_per_slot = max(B, (args.universe + N_SLOTS - 1) // N_SLOTS)
     universe = ranks_per_slot * N_SLOTS
-    rows = int(universe / rt.world * 1.08) + (1 << 16)          # slab of one shard: its part of the universe plus head-room
+    rows = int(universe / rt.world * 1.25) + (1 << 16)          # slab of one shard: its part of the universe at 80 % fill
     torch.manual_seed(1234)
     model = tn.models.DeepFM(slots, slots, dnn_hidden_units=(400, 400, 400), embedding_dim=EMB_DIM, dense_dim=N_DENSE,
                              sparse_opt=tn.core.Adam(learning_rate=1e-3, initial_scale=0.1), bucket_size=B,

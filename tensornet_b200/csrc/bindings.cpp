@@ -11,6 +11,7 @@
 #include <vector>
 
 #include "gemm_tcgen05.h"
+#include "mlp_fused.h"
 #include "tn_ops.h"
 #include "tn_types.h"
 
@@ -360,6 +361,40 @@ void gemm(at::Tensor A, at::Tensor B, at::Tensor C, int M, int N, int K, int lda
   if (err) throw std::runtime_error(err);
 }
 
+// One-kernel MLP chain.  weights[i]: bf16 [N_i, ld]; outs[i]: bf16 [M, ld_out_i] (forward: activations; backward: input
+// gradients); masks[i] (backward): the activation whose ReLU the gradient passes through, or None.
+tn::MlpChainDesc chain_desc(bool backward, const at::Tensor& x, int in_cols, const std::vector<at::Tensor>& weights,
+                            const std::vector<int>& n_rows, const std::vector<int>& k_cols, const std::vector<at::Tensor>& outs,
+                            const std::vector<int>& relu, const std::vector<int>& n_valid,
+                            const std::vector<c10::optional<at::Tensor>>& masks, const at::Tensor& status) {
+  const int L = (int)weights.size();
+  TORCH_CHECK(L >= 1 && L <= tn::kMlpMaxLayers && (int)outs.size() == L && (int)n_rows.size() == L && (int)k_cols.size() == L,
+              "mlp_chain: 1..4 layers with one output each");
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "mlp_chain: input must be a bf16 matrix");
+  tn::MlpChainDesc d;
+  d.L = L; d.M = (int)x.size(0); d.backward = backward ? 1 : 0;
+  d.in = x.data_ptr(); d.in_cols = in_cols; d.ld_in = (int)x.stride(0);
+  d.status = ptr_of<int>(status);
+  for (int i = 0; i < L; ++i) {
+    const at::Tensor& w = weights[i];
+    const at::Tensor& o = outs[i];
+    TORCH_CHECK(w.scalar_type() == at::kBFloat16 && w.dim() == 2 && w.stride(1) == 1, "mlp_chain: weights must be bf16 matrices");
+    TORCH_CHECK(o.scalar_type() == at::kBFloat16 && o.dim() == 2 && o.stride(1) == 1 && o.size(0) == x.size(0), "mlp_chain: bad output");
+    TORCH_CHECK(n_rows[i] <= w.size(0) && k_cols[i] <= w.stride(0), "mlp_chain: layer shape exceeds the weight matrix");
+    tn::MlpChainLayer& l = d.layer[i];
+    l.w = w.data_ptr(); l.n_rows = n_rows[i]; l.k_cols = k_cols[i]; l.ldw = (int)w.stride(0);
+    l.out = o.data_ptr(); l.ld_out = (int)o.stride(0);
+    l.relu = i < (int)relu.size() ? relu[i] : 0;
+    l.n_valid = i < (int)n_valid.size() ? n_valid[i] : 0;
+    if (i < (int)masks.size() && masks[i].has_value()) {
+      const at::Tensor& mk = *masks[i];
+      TORCH_CHECK(mk.scalar_type() == at::kBFloat16 && mk.dim() == 2 && mk.size(0) == x.size(0), "mlp_chain: bad mask");
+      l.mask = mk.data_ptr(); l.ld_mask = (int)mk.stride(0);
+    }
+  }
+  return d;
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -383,6 +418,34 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("apply_fwd", &BnCtx::apply_fwd)
       .def("apply_bwd", &BnCtx::apply_bwd);
   py::class_<DenseCtx>(m, "DenseCtx").def(py::init<py::dict>()).def("step", &DenseCtx::step, py::arg("skip_open") = false).def("set_gated", &DenseCtx::set_gated).def("set_max_ctas", &DenseCtx::set_max_ctas);
+  m.def("mlp_chain", [](bool backward, at::Tensor x, int in_cols, std::vector<at::Tensor> weights, std::vector<int> n_rows,
+                        std::vector<int> k_cols, std::vector<at::Tensor> outs, std::vector<int> relu, std::vector<int> n_valid,
+                        std::vector<c10::optional<at::Tensor>> masks, at::Tensor status, c10::optional<at::Tensor> gate_flags,
+                        c10::optional<at::Tensor> gate_epoch, int gate_world, uint64_t gate_wait_ns, bool probe_only,
+                        c10::optional<at::Tensor> prof) {
+    c10::cuda::CUDAGuard guard(x.device());
+    tn::MlpChainDesc d = chain_desc(backward, x, in_cols, weights, n_rows, k_cols, outs, relu, n_valid, masks, status);
+    if (prof.has_value()) {
+      TORCH_CHECK(prof->scalar_type() == at::kLong && prof->numel() >= 16, "mlp_chain: prof must be int64[16]");
+      d.prof = ptr_of<unsigned long long>(*prof);
+    }
+    if (gate_flags.has_value()) {
+      d.gate_flags = ptr_of<const unsigned long long>(*gate_flags);
+      d.gate_epoch = ptr_of<const unsigned long long>(*gate_epoch);
+      d.gate_world = gate_world;
+      d.gate_wait_ns = gate_wait_ns;
+    }
+    if (probe_only) {
+      const char* why = tn::mlp_chain_supported(d);
+      return std::string(why ? why : "");
+    }
+    const char* err = tn::mlp_chain(d, cur_stream());
+    if (err) throw std::runtime_error(err);
+    return std::string();
+  }, py::arg("backward"), py::arg("x"), py::arg("in_cols"), py::arg("weights"), py::arg("n_rows"), py::arg("k_cols"), py::arg("outs"),
+     py::arg("relu"), py::arg("n_valid"), py::arg("masks"), py::arg("status"), py::arg("gate_flags") = py::none(),
+     py::arg("gate_epoch") = py::none(), py::arg("gate_world") = 0, py::arg("gate_wait_ns") = 0, py::arg("probe_only") = false, py::arg("prof") = py::none(),
+     "a whole MLP tower (forward, or the input-gradient chain of the backward pass) in one kernel");
   m.def("gemm", &gemm, py::arg("A"), py::arg("B"), py::arg("C"), py::arg("M"), py::arg("N"), py::arg("K"), py::arg("lda"),
         py::arg("ldb"), py::arg("ldc"), py::arg("a_mn"), py::arg("b_mn"), py::arg("accumulate"), py::arg("relu"), py::arg("bias"),
         py::arg("mask_aux"), py::arg("had_x0"), py::arg("had_xl"), py::arg("ld_aux"), py::arg("ones_col"), py::arg("n_store"),

@@ -25,9 +25,11 @@
 #include <mutex>
 #include <unordered_map>
 #include "gemm_tcgen05.h"
-#include "tn_device.cuh"
+#include "tc_primitives.cuh"
 
 namespace tn {
+
+using namespace tc;
 
 namespace {
 
@@ -39,86 +41,6 @@ constexpr int kEpiSubs = 4;               // epilogue warps per TMEM lane quarte
 constexpr int kEpiWarps = 4 * kEpiSubs;
 constexpr int kGemmThreads = 32 * (2 + kEpiWarps);   // warp0 TMA, warp1 MMA + TMEM owner, the rest epilogue
 constexpr int kEpiBytesPerWarp = 6144;   // out block + two auxiliary blocks of 32 rows x 64 B
-constexpr unsigned kWaitSpins = 20u * 1000u * 1000u;   // ~ a second with the nanosleep below
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait; false on expiry or when another role of this CTA already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* s_abort) {
-  for (unsigned spins = 0; spins < kWaitSpins; ++spins) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((spins & 255u) == 255u && *s_abort) return false;
-    if (spins > 64) __nanosleep(40);
-  }
-  return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
-      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
-      : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// Shared-memory matrix descriptor, 128-byte swizzle, sm_100 version field set.
-//   K-major : rows of 128 B, 8-row groups 1024 B apart (SBO); LBO unused.
-//   MN-major: 64-element chunks along MN are 128 B rows indexed by k; 8-k groups 1024 B apart
-//             (SBO); the next 64-wide MN chunk starts `lbo_bytes` further (LBO).
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr & 0x3FFFF) >> 4);
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
-  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
-  d |= (uint64_t)1 << 46;   // descriptor version for sm_100
-  d |= (uint64_t)2 << 61;   // SWIZZLE_128B
-  return d;
-}
-
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, uint32_t* r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr));
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
 
 template <int kStages, int kHalves>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -510,6 +432,8 @@ struct MapKeyHash {
   }
 };
 
+}  // namespace
+
 // 2-D bf16 row-major tensor [rows, cols] with leading dimension `ld` elements; box = 64 x box_rows.
 bool get_tensor_map(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out) {
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
@@ -534,8 +458,6 @@ bool get_tensor_map(const void* ptr, long long rows, long long cols, long long l
   *out = m;
   return true;
 }
-
-}  // namespace
 
 const char* gemm_bf16(const GemmDesc& d, cudaStream_t stream) {
   if (d.M <= 0 || d.N <= 0 || d.K <= 0) return "gemm_bf16: empty problem";

@@ -112,6 +112,23 @@ def concat_cast(pieces: Sequence[torch.Tensor], ones: bool = True, widths: Optio
 # =========================================================================================
 # MLP tower: chain of (bf16 GEMM + bias + ReLU) layers on the tcgen05 kernel
 # =========================================================================================
+_chain_ok: dict = {}
+
+
+def _chain_supported(backward: bool, x, in_cols, bws, n_rows, k_cols, outs, relu, n_valid, masks) -> bool:
+    """Does this tower fit the one-kernel path (``csrc/mlp_fused.cu``)?  Asked once per shape."""
+    from ..core.config import config
+
+    if not config.fused_mlp:
+        return False
+    key = (backward, int(x.shape[0]), in_cols, tuple(n_rows), tuple(k_cols), tuple(int(o.stride(0)) for o in outs))
+    ok = _chain_ok.get(key)
+    if ok is None:
+        why = _ext().mlp_chain(backward, x, in_cols, bws, n_rows, k_cols, outs, relu, n_valid, masks, _status(), probe_only=True)
+        ok = _chain_ok[key] = (why == "")
+    return ok
+
+
 class _MLP(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, dims, relu_last, premasked, gate, *weights):
@@ -120,29 +137,39 @@ class _MLP(torch.autograd.Function):
         # dense weight array has landed on this GPU (the dense step then ends without a closing barrier)
         ext, st = _ext(), _status()
         B = x.shape[0]
-        acts = [x]
-        h = x
         L = len(weights)
-        for l, w in enumerate(weights):
-            N, Kp = int(w.shape[0]), int(w.shape[1])
-            K = dims[l]
-            Np = pad8(N + 1)
-            y = torch.empty((B, Np), dtype=torch.bfloat16, device=x.device)
-            relu = relu_last or l < L - 1
-            if l == 0 and gate is not None:
-                ext.gemm(h, _bf16_of(w), y, B, N, K + 1, int(h.stride(0)), Kp, Np, False, False, False, relu, None, None, None,
-                         None, 0, N, Np, 1, 0, st, gate_flags=gate[0], gate_epoch=gate[1], gate_world=gate[2], gate_wait_ns=gate[3])
-            else:
-                ext.gemm(h, _bf16_of(w), y, B, N, K + 1, int(h.stride(0)), Kp, Np, False, False, False, relu, None, None, None,
-                         None, 0, N, Np, 1, 0, st)
-            acts.append(y)
-            h = y
+        bws = [_bf16_of(w) for w in weights]
+        n_rows = [int(w.shape[0]) for w in weights]
+        k_cols = [dims[l] + 1 for l in range(L)]
+        outs = [torch.empty((B, pad8(n + 1)), dtype=torch.bfloat16, device=x.device) for n in n_rows]
+        relu = [1 if (relu_last or l < L - 1) else 0 for l in range(L)]
+        if L <= 4 and x.stride(1) == 1 and _chain_supported(False, x, int(x.shape[1]), bws, n_rows, k_cols, outs, relu, [], []):
+            # the whole tower in one kernel: activations stay in shared memory between the layers
+            g = {} if gate is None else dict(gate_flags=gate[0], gate_epoch=gate[1], gate_world=gate[2], gate_wait_ns=gate[3])
+            ext.mlp_chain(False, x, int(x.shape[1]), bws, n_rows, k_cols, outs, relu, [], [], st, **g)
+            acts = [x] + outs
+        else:
+            acts = [x]
+            h = x
+            for l, w in enumerate(weights):
+                N, Kp = n_rows[l], int(w.shape[1])
+                K = dims[l]
+                Np = pad8(N + 1)
+                y = outs[l]
+                if l == 0 and gate is not None:
+                    ext.gemm(h, bws[l], y, B, N, K + 1, int(h.stride(0)), Kp, Np, False, False, False, bool(relu[l]), None, None, None,
+                             None, 0, N, Np, 1, 0, st, gate_flags=gate[0], gate_epoch=gate[1], gate_world=gate[2], gate_wait_ns=gate[3])
+                else:
+                    ext.gemm(h, bws[l], y, B, N, K + 1, int(h.stride(0)), Kp, Np, False, False, False, bool(relu[l]), None, None, None,
+                             None, 0, N, Np, 1, 0, st)
+                acts.append(y)
+                h = y
         ctx.save_for_backward(*acts)
         ctx.weights = weights
         ctx.dims = dims
         ctx.relu_last = relu_last
         ctx.premasked = premasked
-        return h
+        return acts[-1]
 
     @staticmethod
     def backward(ctx, gy):
@@ -156,39 +183,78 @@ class _MLP(torch.autograd.Function):
         if ctx.relu_last and not ctx.premasked:
             g = g.clone()
             ext.relu_mask(g, acts[L])
-        gx = None
         # The weight gradients are off the critical path (only the optimizer needs them): they run on a side
         # stream next to the input-gradient chain and are joined before this function returns.
         main = torch.cuda.current_stream()
         side = _side_stream(g.device)
-        keep = []
-        for l in range(L - 1, -1, -1):
+        need_x = bool(ctx.needs_input_grad[0])
+        lo = 0 if need_x else 1                       # lowest layer whose input gradient is wanted
+        grads = [None] * L                            # grads[l]: gradient w.r.t. the output of layer l
+        grads[L - 1] = g
+        gx = None
+
+        def wgrad(l):
             w = weights[l]
-            N, Kp = int(w.shape[0]), int(w.shape[1])
-            K = dims[l]
+            if not w.requires_grad:
+                return
             h = acts[l]
-            ldh = int(h.stride(0))
-            # weight gradient (incl. the bias column): dW[N, Kp] += g[:, :N]^T . h   (contraction over the batch)
-            if w.requires_grad:
-                gw = _grad_buffer(w)
-                ev = torch.cuda.Event()
-                ev.record(main)
-                side.wait_event(ev)
-                keep.append(g)
-                with torch.cuda.stream(side):
-                    ext.gemm(g, h, gw, N, K + 1, B, int(g.stride(0)), ldh, Kp, True, True, True, False, None, None, None, None,
-                             0, -1, K + 1, 0, 0, st)
-            # input gradient: gh[B, ldh] = g[:, :N] . W   masked by the ReLU of the layer below
-            if l > 0 or ctx.needs_input_grad[0]:
-                gh = torch.empty((B, ldh), dtype=torch.bfloat16, device=g.device)
-                mask = h if l > 0 else None
-                ext.gemm(g, _bf16_of(w), gh, B, min(Kp, ldh), N, int(g.stride(0)), Kp, ldh, False, True, False, False, None,
-                         mask, None, None, ldh, -1, ldh, 1, 0, st)
-                g = gh
-                gx = gh
+            ext.gemm(grads[l], h, _grad_buffer(w), int(w.shape[0]), dims[l] + 1, B, int(grads[l].stride(0)), int(h.stride(0)),
+                     int(w.shape[1]), True, True, True, False, None, None, None, None, 0, -1, dims[l] + 1, 0, 0, st)
+
+        chain = list(range(L - 1, lo - 1, -1))        # layers the input-gradient chain walks through
+        fused = False
+        if chain and len(chain) <= 4:
+            bws = [_bf16_of(weights[l]) for l in chain]
+            n_rows = [int(weights[l].shape[0]) for l in chain]
+            k_cols = [min(int(weights[l].shape[1]), int(acts[l].stride(0))) for l in chain]
+            outs = [torch.empty((B, int(acts[l].stride(0))), dtype=torch.bfloat16, device=g.device) for l in chain]
+            n_valid = [dims[l] if l > 0 else k_cols[i] for i, l in enumerate(chain)]
+            masks = [acts[l] if l > 0 else None for l in chain]
+            fused = g.stride(1) == 1 and _chain_supported(True, g, int(g.shape[1]), bws, n_rows, k_cols, outs, [], n_valid, masks)
+        if fused:
+            # weight gradient of the top layer needs nothing from the chain: it starts beside it
+            ev = torch.cuda.Event()
+            ev.record(main)
+            side.wait_event(ev)
+            with torch.cuda.stream(side):
+                wgrad(L - 1)
+            ext.mlp_chain(True, g, int(g.shape[1]), bws, n_rows, k_cols, outs, [], n_valid, masks, st)
+            for i, l in enumerate(chain):
+                if l > 0:
+                    grads[l - 1] = outs[i]
+                else:
+                    gx = outs[i]
+            ev2 = torch.cuda.Event()
+            ev2.record(main)
+            side.wait_event(ev2)
+            with torch.cuda.stream(side):
+                for l in range(L - 2, -1, -1):
+                    wgrad(l)
+        else:
+            for l in range(L - 1, -1, -1):
+                w = weights[l]
+                N, Kp = int(w.shape[0]), int(w.shape[1])
+                h = acts[l]
+                ldh = int(h.stride(0))
+                # weight gradient (incl. the bias column): dW[N, Kp] += g[:, :N]^T . h   (contraction over the batch)
+                if w.requires_grad:
+                    ev = torch.cuda.Event()
+                    ev.record(main)
+                    side.wait_event(ev)
+                    with torch.cuda.stream(side):
+                        wgrad(l)
+                # input gradient: gh[B, ldh] = g[:, :N] . W   masked by the ReLU of the layer below
+                if l >= lo:
+                    gh = torch.empty((B, ldh), dtype=torch.bfloat16, device=g.device)
+                    mask = h if l > 0 else None
+                    ext.gemm(grads[l], _bf16_of(w), gh, B, min(Kp, ldh), N, int(grads[l].stride(0)), Kp, ldh, False, True, False, False,
+                             None, mask, None, None, ldh, -1, ldh, 1, 0, st)
+                    if l > 0:
+                        grads[l - 1] = gh
+                    else:
+                        gx = gh
         main.wait_stream(side)
-        del keep
-        return (gx if ctx.needs_input_grad[0] else None, None, None, None, None, *([None] * L))
+        return (gx if need_x else None, None, None, None, None, *([None] * L))
 
 
 def mlp(x: torch.Tensor, weights: Sequence[torch.Tensor], in_dim: int, relu_last: bool = True,
