@@ -44,7 +44,7 @@ def peaks():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm_fwd", "gemm_dgrad", "gemm_wgrad", "gemm_big", "sparse", "deepfm", "dense", "small_ops"])
+    ap.add_argument("case", choices=["gemm_fwd", "gemm_dgrad", "gemm_wgrad", "gemm_big", "sparse", "deepfm", "deepfm_head", "mlp_chain", "dense", "small_ops"])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--batch", type=int, default=8192)
     a = ap.parse_args()
@@ -88,7 +88,7 @@ def main():
         import bench
         from tensornet_b200.ops.sparse_table_gpu import GpuSparseTable
         B, S, dim = a.batch, 26, 20
-        data = [b[0].to(dev).reshape(-1) for b in bench.make_batches(8, B, S, 13, 5)]
+        data = [b[0].reshape(-1) for b in bench.make_batches(8, B, 3846154, dev, 5)]
         t = GpuSparseTable(tn.core.Adam(learning_rate=1e-3, initial_scale=0.1), dim, rows=1 << 22)
         lk = t.link(B * S)
         for ids in data + data:
@@ -147,6 +147,41 @@ def main():
         res["bce_us"] = timed(lambda: F.bce_with_logits(logit, y), a.iters)
         res["torch_bce_us"] = timed(lambda: (TF.binary_cross_entropy_with_logits(logit.view(-1), y), torch.sigmoid(logit)), a.iters)
         out.update({k: round(v, 2) for k, v in res.items()}, nnz=nnz, ids=int(ids.numel()))
+    elif a.case == "deepfm_head":
+        # Dense(1) over [h | linear | fm | 1] + loss + the head's whole backward, alone
+        from tensornet_b200.ops import functional as F
+        B, NH, NL = a.batch, 400, 26
+        h = torch.randn(B, 408, device=dev).relu().bfloat16()
+        lin, fm = torch.randn(B, NL, device=dev) * 0.1, torch.randn(B, device=dev) * 0.1
+        w = torch.nn.Parameter(torch.randn(NH + NL + 2, device=dev) * 0.05)
+        y = (torch.rand(B, device=dev) < 0.25).float()
+        sums = torch.zeros(4, device=dev)
+        us = timed(lambda: F.deepfm_head_loss(h, lin, fm, w, y, sums, NH), a.iters)
+        nbytes = B * 408 * 2 * 2 + B * NL * 4 * 2 + B * 12
+        out.update(us=us, min_bytes=nbytes, GBps=nbytes / us / 1e3, frac_of_hbm=nbytes / us / 1e3 / pk["hbm_gbs"], peak=tag)
+    elif a.case == "mlp_chain":
+        # the DeepFM tower 429-400-400-400 as one kernel per direction against the three GEMM launches it replaces
+        from tensornet_b200.layers import MLP
+        from tensornet_b200.ops import functional as F
+        B = a.batch
+        mlp = MLP(429, (400, 400, 400)).to(dev)
+        x = F.concat_cast([torch.randn(B, 429, device=dev)], ones=True)
+        bws = [w.detach().to(torch.bfloat16) for w in mlp.weights]
+        outs = [torch.empty((B, 408), dtype=torch.bfloat16, device=dev) for _ in range(3)]
+        g = torch.randn(B, 408, device=dev).to(torch.bfloat16)
+        bouts = [torch.empty((B, 408), dtype=torch.bfloat16, device=dev), torch.empty((B, 408), dtype=torch.bfloat16, device=dev),
+                 torch.empty((B, 432), dtype=torch.bfloat16, device=dev)]
+        fwd = lambda: ext.mlp_chain(False, x, 432, bws, [400] * 3, [430, 401, 401], outs, [1, 1, 1], [], [], st)
+        bwd = lambda: ext.mlp_chain(True, g, 408, bws[::-1], [400] * 3, [408, 408, 432], bouts, [], [400, 400, 432], [outs[1], outs[0], None], st)
+        def layers_fwd():
+            h_ = x
+            for l in range(3):
+                ext.gemm(h_, bws[l], outs[l], B, 400, (430, 401, 401)[l], int(h_.stride(0)), int(bws[l].stride(0)), 408, False, False, False, True,
+                         None, None, None, None, 0, 400, 408, 1, 0, st)
+                h_ = outs[l]
+        flops = 2.0 * B * 400 * (430 + 401 + 401)
+        res = {"chain_fwd": timed(fwd, a.iters), "chain_bwd": timed(bwd, a.iters), "three_gemm_launches_fwd": timed(layers_fwd, a.iters)}
+        out.update(us=res, tflops={k: flops / v / 1e6 for k, v in res.items()}, shape=[B, 429, 400, 400, 400])
     elif a.case == "deepfm":
         import bench
         slots = [str(i) for i in range(1, 27)]
@@ -154,7 +189,7 @@ def main():
                                  sparse_opt=tn.core.Adam(learning_rate=1e-3, initial_scale=0.1), bucket_size=a.batch,
                                  table_rows=1 << 22, share_linear_table=True)
         model.compile(optimizer=tn.optimizer.Optimizer(tn.core.Adam(learning_rate=1e-3)), cuda_graph=False)
-        data = [(i.to(dev), d.to(dev), l.to(dev)) for i, d, l in bench.make_batches(4, a.batch, 26, 13, 7)]
+        data = bench.make_batches(4, a.batch, 3846154, dev, 7)
         k = [0]
         def step():
             i, d, l = data[k[0] % 4]; k[0] += 1

@@ -55,7 +55,7 @@ __global__ void __launch_bounds__(kDThreads) dense_local_kernel(const DenseStepA
 }
 
 __global__ void __launch_bounds__(kDThreads) dense_fused_kernel(const __grid_constant__ DenseStepArgs a) {
-  dense::fused_step(a, (int)blockIdx.x, (int)gridDim.x);
+  dense::fused_step<dense::kDenseUnroll>(a, (int)blockIdx.x, (int)gridDim.x);
 }
 
 }  // namespace

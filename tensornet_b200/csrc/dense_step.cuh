@@ -107,6 +107,7 @@ constexpr int kDenseUnroll = 4;   // independent 16-byte reductions in flight pe
 
 // The whole multi-GPU step as seen by CTA `bid` of the `nb` CTAs that share the work (their own barrier words in
 // a.bar).  Every CTA of the group must call it; returns after the group's exit bookkeeping.
+template <int kUnroll>
 __device__ __forceinline__ void fused_step(const DenseStepArgs& a, const int bid, const int nb) {
   const DenseOptParams& o = a.opt;
   GridSync gs;
@@ -135,34 +136,34 @@ __device__ __forceinline__ void fused_step(const DenseStepArgs& a, const int bid
     if (!gs.sync(42, false)) goto done;
   }
 
-  for (long long base = lo4 + bid * (long long)blockDim.x + threadIdx.x; base < hi4; base += nth * kDenseUnroll) {
-    float4 g[kDenseUnroll];
+  for (long long base = lo4 + bid * (long long)blockDim.x + threadIdx.x; base < hi4; base += nth * kUnroll) {
+    float4 g[kUnroll];
     if (a.G_mc) {
 #pragma unroll
-      for (int u = 0; u < kDenseUnroll; ++u) {
+      for (int u = 0; u < kUnroll; ++u) {
         const long long i = base + u * nth;
         if (i < hi4) g[u] = mm_ld_reduce_f4(a.G_mc + 4 * i);
       }
     } else {
 #pragma unroll
-      for (int u = 0; u < kDenseUnroll; ++u) g[u] = z4;
+      for (int u = 0; u < kUnroll; ++u) g[u] = z4;
       for (int p = 0; p < W; ++p) {
         const float* Gp = a.G[(R + p) % W];
-        float4 x[kDenseUnroll];
+        float4 x[kUnroll];
 #pragma unroll
-        for (int u = 0; u < kDenseUnroll; ++u) {
+        for (int u = 0; u < kUnroll; ++u) {
           const long long i = base + u * nth;
           if (i < hi4) x[u] = ldcg_f4(Gp + 4 * i);
         }
 #pragma unroll
-        for (int u = 0; u < kDenseUnroll; ++u) {
+        for (int u = 0; u < kUnroll; ++u) {
           const long long i = base + u * nth;
           if (i < hi4) { g[u].x += x[u].x; g[u].y += x[u].y; g[u].z += x[u].z; g[u].w += x[u].w; }
         }
       }
     }
 #pragma unroll
-    for (int u = 0; u < kDenseUnroll; ++u) {
+    for (int u = 0; u < kUnroll; ++u) {
       const long long i = base + u * nth;
       if (i >= hi4) continue;
       const float4 w = dense_update4(a, alpha, lr, g[u], i, i - lo4);

@@ -26,6 +26,7 @@ namespace tn {
 namespace {
 
 constexpr int kThreads = 1024;
+constexpr int kRiderUnroll = 2;      // 16-byte reductions in flight per thread of the CTAs that carry the dense step
 enum SigKind { kSigPullReq = 0, kSigPullDone = 1, kSigPushReq = 2 };
 __device__ __forceinline__ unsigned long long* sig_word(unsigned long long* base, int kind, int src) {
   return base + kind * kMaxWorld + src;
@@ -680,7 +681,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_push_fused_kernel(const __
                                                                         const int dense_ctas) {
   const int nb = (int)gridDim.x - dense_ctas;      // CTAs of the push proper
   if ((int)blockIdx.x >= nb) {
-    dense::fused_step(d, (int)blockIdx.x - nb, dense_ctas);
+    dense::fused_step<kRiderUnroll>(d, (int)blockIdx.x - nb, dense_ctas);   // two loads in flight: fits the 64-register budget of 1024 threads
     return;
   }
   const SparseCommView& c = a.c;
@@ -909,7 +910,7 @@ cudaError_t launch_sparse_push(const PushArgs& args, int work_items, int max_cta
     if (dense->world < 2 || dense->n % 4 || dense->chunk % 4) return cudaErrorInvalidValue;
     d = *dense;
     // one pass of the owned chunk: 1024 threads x kDenseUnroll 16-byte groups per CTA, at most 16 CTAs
-    const long long per_cta = (long long)kThreads * dense::kDenseUnroll * 4;
+    const long long per_cta = (long long)kThreads * kRiderUnroll * 4;
     dense_ctas = (int)((d.chunk + per_cta - 1) / per_cta);
     if (dense_ctas < 1) dense_ctas = 1;
     if (dense_ctas > 16) dense_ctas = 16;
