@@ -606,7 +606,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                                at::Tensor dH, c10::optional<at::Tensor> dL, at::Tensor dfm, at::Tensor gw, at::Tensor sums,
                                c10::optional<at::Tensor> pred, at::Tensor loss_out, at::Tensor scratch) {
     c10::cuda::CUDAGuard guard(H.device());
-    TORCH_CHECK(scratch.numel() >= 2 && scratch.scalar_type() == at::kFloat, "deepfm_head_loss: scratch must be two fp32 words (zero between calls)");
+    TORCH_CHECK(scratch.numel() >= 4 + 16 * 576 && scratch.scalar_type() == at::kFloat && (reinterpret_cast<uintptr_t>(scratch.data_ptr()) & 15) == 0,
+                "deepfm_head_loss: scratch must be fp32[4 + 16 * 576], 16-byte aligned, zero between calls");
     const int NL = L ? (int)L->size(1) : 0;
     TORCH_CHECK(w.numel() == NH + NL + 2, "deepfm_head_loss: weight must be [NH + NL + 2]");
     const char* err = tn::launch_deepfm_head_loss(H.data_ptr(), (int)H.stride(0), NH, L ? ptr_of<float>(*L) : nullptr, NL,

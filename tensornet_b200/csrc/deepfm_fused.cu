@@ -175,6 +175,8 @@ __global__ void deepfm_input_bwd_kernel(const float* __restrict__ U, int ustride
 // sums: [0] += mean loss, [1] += sum(label), [2] += sum(pred), [3] += B; with nbins > 0 the words behind them are the
 // two prediction histograms (u32 counts; positives, then negatives) of a streaming AUC.
 constexpr int kHeadPairs = 8;
+constexpr int kHeadParts = 16;            // partial copies of the weight gradient in the scratch area
+constexpr int kHeadPartStride = 576;      // floats per copy: >= 64 * kHeadPairs + 32 + 2, multiple of 4
 __global__ void deepfm_head_loss_kernel(const __nv_bfloat16* __restrict__ H, int ldh, int NH, const float* __restrict__ L, int NL,
                                         const float* __restrict__ fm, const float* __restrict__ w, const float* __restrict__ label,
                                         int B, __nv_bfloat16* __restrict__ dH, float* __restrict__ dL, float* __restrict__ dfm,
@@ -262,25 +264,43 @@ __global__ void deepfm_head_loss_kernel(const __nv_bfloat16* __restrict__ H, int
   }
   if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&sums[3], (float)B);
   __syncthreads();
-  // one 16-byte reduction per four weights when the gradient buffer allows it: the number of global reductions per
-  // block, not the rows per warp, is what limits how many blocks this kernel can use
-  if ((reinterpret_cast<uintptr_t>(gw) & 15) == 0) {
+  // The per-block weight gradients are summed in two steps.  Hundreds of blocks adding to the same few hundred words of
+  // `gw` at the same moment queue up behind one another in L2 (that tail used to be most of the kernel); instead a block
+  // adds into one of kHeadParts partial copies in the scratch area (a sixteenth of the blocks per copy), and the last
+  // block to finish folds the copies into `gw` and leaves them at zero for the next launch.
+  float* parts = scratch + 4;                              // [kHeadParts][kHeadPartStride]
+  {
+    float* mine = parts + (size_t)(blockIdx.x % kHeadParts) * kHeadPartStride;
     const int n4 = NW >> 2;
     for (int k = threadIdx.x; k < n4; k += blockDim.x)
-      red_add_f32x4(gw + 4 * k, make_float4(s_gw[4 * k], s_gw[4 * k + 1], s_gw[4 * k + 2], s_gw[4 * k + 3]));
-    for (int k = 4 * n4 + threadIdx.x; k < NW; k += blockDim.x) atomicAdd(gw + k, s_gw[k]);
-  } else {
-    for (int k = threadIdx.x; k < NW; k += blockDim.x) atomicAdd(gw + k, s_gw[k]);
+      red_add_f32x4(mine + 4 * k, make_float4(s_gw[4 * k], s_gw[4 * k + 1], s_gw[4 * k + 2], s_gw[4 * k + 3]));
+    for (int k = 4 * n4 + threadIdx.x; k < NW; k += blockDim.x) atomicAdd(mine + k, s_gw[k]);
   }
   // The loss is summed in a persistent scratch word that is zero between launches; the last block to finish
   // moves the total into `loss_out` and re-arms the scratch, so the caller never has to clear anything.
+  __shared__ int s_last;
+  __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
     const unsigned prev = atomicAdd(reinterpret_cast<unsigned*>(scratch) + 1, 1u);
-    if (prev == gridDim.x - 1) {
+    s_last = prev == gridDim.x - 1;
+    if (s_last) {
       __threadfence();
       *loss_out = atomicExch(&scratch[0], 0.f);
       reinterpret_cast<unsigned*>(scratch)[1] = 0u;
+    }
+  }
+  __syncthreads();
+  if (s_last) {
+    for (int k = threadIdx.x; k < NW; k += blockDim.x) {
+      float sum = 0.f;
+#pragma unroll
+      for (int q = 0; q < kHeadParts; ++q) {
+        float* pq = parts + (size_t)q * kHeadPartStride + k;
+        sum += __ldcg(pq);
+        *pq = 0.f;
+      }
+      gw[k] += sum;          // nobody else touches the head's gradient while this kernel runs
     }
   }
 }
@@ -311,6 +331,7 @@ const char* launch_deepfm_head_loss(const void* H, int ldh, int NH, const float*
                                     float* pred, float* loss_out, float* scratch, cudaStream_t st) {
   if (ldh > 64 * kHeadPairs || (ldh & 1)) return "deepfm_head: hidden width must be even and at most 512 columns";
   if (NL > 32) return "deepfm_head: at most 32 linear inputs";
+  if (NH + NL + 2 > kHeadPartStride) return "deepfm_head: too many head inputs";
   // two blocks per SM: measured 254 us per DeepFM step against 257 (three) and 264 (four), with scalar or 16-byte
   // reductions of the per-block weight gradient alike
   int blocks = (B + 7) / 8; if (blocks > 148 * 2) blocks = 148 * 2; if (blocks < 1) blocks = 1;

@@ -539,10 +539,11 @@ _HEAD_SCRATCH = {}
 
 
 def _head_scratch(dev) -> torch.Tensor:
-    """Two persistent words per device (partial loss, finished-block count) that the head kernel leaves at zero."""
+    """Persistent scratch per device that the head kernel leaves at zero: partial loss, finished-block count and
+    sixteen partial copies of the head's weight gradient."""
     key = (dev.type, dev.index)
     if key not in _HEAD_SCRATCH:
-        _HEAD_SCRATCH[key] = torch.zeros(2, dtype=torch.float32, device=dev)
+        _HEAD_SCRATCH[key] = torch.zeros(4 + 16 * 576, dtype=torch.float32, device=dev)
     return _HEAD_SCRATCH[key]
 
 
