@@ -104,16 +104,16 @@ struct SparseCtx {
     TORCH_CHECK(c.world >= 1 && c.world <= tn::kMaxWorld, "world must be 1..8");
     TORCH_CHECK(c.capo % 4 == 0, "segment capacity must be a multiple of 4");
     auto inbox = comm["inbox_ids"].cast<std::vector<int64_t>>();
-    auto ginbox = comm["ginbox"].cast<std::vector<int64_t>>();
-    auto cinbox = comm["cinbox"].cast<std::vector<int64_t>>();
+    auto gU_peer = comm["gU_peer"].cast<std::vector<int64_t>>();
+    auto cnts_peer = comm["cnts_peer"].cast<std::vector<int64_t>>();
     auto U = comm["U"].cast<std::vector<int64_t>>();
     auto sig = comm["sig"].cast<std::vector<int64_t>>();
-    TORCH_CHECK((int)inbox.size() == c.world && (int)ginbox.size() == c.world && (int)cinbox.size() == c.world && (int)U.size() == c.world &&
+    TORCH_CHECK((int)inbox.size() == c.world && (int)gU_peer.size() == c.world && (int)cnts_peer.size() == c.world && (int)U.size() == c.world &&
                     (int)sig.size() == c.world, "peer pointer tables must have `world` entries");
     for (int p = 0; p < c.world; ++p) {
       c.inbox_ids[p] = ptr_of<unsigned long long>(inbox[p]);
-      c.ginbox[p] = ptr_of<float>(ginbox[p]);
-      c.cinbox[p] = ptr_of<float>(cinbox[p]);
+      c.gU_peer[p] = ptr_of<float>(gU_peer[p]);
+      c.cnts_peer[p] = ptr_of<float>(cnts_peer[p]);
       c.U[p] = ptr_of<float>(U[p]);
       c.sig[p] = ptr_of<unsigned long long>(sig[p]);
     }
@@ -422,9 +422,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                         std::vector<int> k_cols, std::vector<at::Tensor> outs, std::vector<int> relu, std::vector<int> n_valid,
                         std::vector<c10::optional<at::Tensor>> masks, at::Tensor status, c10::optional<at::Tensor> gate_flags,
                         c10::optional<at::Tensor> gate_epoch, int gate_world, uint64_t gate_wait_ns, bool probe_only,
-                        c10::optional<at::Tensor> prof) {
+                        c10::optional<at::Tensor> prof, int split) {
     c10::cuda::CUDAGuard guard(x.device());
     tn::MlpChainDesc d = chain_desc(backward, x, in_cols, weights, n_rows, k_cols, outs, relu, n_valid, masks, status);
+    d.split = split;
     if (prof.has_value()) {
       TORCH_CHECK(prof->scalar_type() == at::kLong && prof->numel() >= 16, "mlp_chain: prof must be int64[16]");
       d.prof = ptr_of<unsigned long long>(*prof);
@@ -444,7 +445,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     return std::string();
   }, py::arg("backward"), py::arg("x"), py::arg("in_cols"), py::arg("weights"), py::arg("n_rows"), py::arg("k_cols"), py::arg("outs"),
      py::arg("relu"), py::arg("n_valid"), py::arg("masks"), py::arg("status"), py::arg("gate_flags") = py::none(),
-     py::arg("gate_epoch") = py::none(), py::arg("gate_world") = 0, py::arg("gate_wait_ns") = 0, py::arg("probe_only") = false, py::arg("prof") = py::none(),
+     py::arg("gate_epoch") = py::none(), py::arg("gate_world") = 0, py::arg("gate_wait_ns") = 0, py::arg("probe_only") = false, py::arg("prof") = py::none(), py::arg("split") = 0,
      "a whole MLP tower (forward, or the input-gradient chain of the backward pass) in one kernel");
   m.def("gemm", &gemm, py::arg("A"), py::arg("B"), py::arg("C"), py::arg("M"), py::arg("N"), py::arg("K"), py::arg("lda"),
         py::arg("ldb"), py::arg("ldc"), py::arg("a_mn"), py::arg("b_mn"), py::arg("accumulate"), py::arg("relu"), py::arg("bias"),

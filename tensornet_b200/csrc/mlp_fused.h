@@ -35,19 +35,24 @@ struct MlpChainDesc {
   const unsigned long long* gate_epoch = nullptr;
   int gate_world = 0;
   unsigned long long gate_wait_ns = 0;
+  int split = 0;             // 0 = choose, 1 = one CTA per stripe, 2 = a pair of CTAs per stripe
   int* status = nullptr;
   unsigned long long* prof = nullptr;   // optional [16] timestamps of CTA 0: start, data ready, then per step: A ready, accumulator ready, epilogue done
 };
 
 struct MlpChainParams {
   int L, M, backward, kt_in, kt_max;
+  int split;                     // CTAs per 128-row stripe: 1, or 2 (a cluster of two that share the stripe's output columns)
+  int stages;                    // weight tiles in flight
   uint32_t stage_bytes;
-  int n_acc[kMlpMaxLayers];      // accumulator columns of step i
+  int n_lo[kMlpMaxLayers][2];    // first accumulator column of CTA r of a stripe in step i
+  int n_cnt[kMlpMaxLayers][2];   // its number of accumulator columns
+  int n_acc[kMlpMaxLayers];      // accumulator columns of step i (all CTAs of a stripe together)
   int n_valid[kMlpMaxLayers];    // columns that take accumulator values
   int ones_col[kMlpMaxLayers];   // column written as 1.0 (-1: none)
   int out_cols[kMlpMaxLayers];   // columns written to the next A operand (multiple of 64)
   int kt[kMlpMaxLayers];         // k-blocks contracted in step i
-  int box_rows[kMlpMaxLayers];   // rows per weight TMA copy (forward)
+  int box_rows[kMlpMaxLayers][2];   // rows per weight TMA copy (forward), per CTA of a stripe
   int relu[kMlpMaxLayers];
   const __nv_bfloat16* mask[kMlpMaxLayers];
   int ld_mask[kMlpMaxLayers];

@@ -27,7 +27,7 @@ namespace {
 
 constexpr int kThreads = 1024;
 constexpr int kRiderUnroll = 2;      // 16-byte reductions in flight per thread of the CTAs that carry the dense step
-enum SigKind { kSigPullReq = 0, kSigPullDone = 1, kSigPushReq = 2 };
+enum SigKind { kSigPullReq = 0, kSigPullDone = 1, kSigPushReq = 2, kSigPushDone = 3 };
 __device__ __forceinline__ unsigned long long* sig_word(unsigned long long* base, int kind, int src) {
   return base + kind * kMaxWorld + src;
 }
@@ -731,41 +731,20 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_push_fused_kernel(const __
     goto done;
   }
 
-  // ---- phase A: move gradient records and the (show, click) pairs into the owners' inboxes (this GPU's own inbox
-  // included), re-zero the local copies.  Two plain streaming loops: every warp moves whole 512-byte runs.
-  // (Patching the counters into the records on the fly made one lane in gstride/4 leave the stream for an 8-byte
-  // side access and cost 3x the time.  Accumulating the own records straight from the gradient matrix instead of
-  // staging them in the own inbox was also tried: whenever the matrix is not L2-resident that pass took 27 us
-  // instead of 6, so the staging copy stays.)
-  for (int pi = 0; pi < W; ++pi) {
-    const int p = (R + pi) % W;
-    const int n = __ldcg(&c.cnt_saved[p]);
-    float* src = c.gU + (size_t)p * capo * gstride;
-    float* dst = c.ginbox[p] + (size_t)R * capo * gstride;
-    const int total = n * gch;
-    for (int i = tid; i < total; i += nth) {
-      *reinterpret_cast<float4*>(dst + 4 * (size_t)i) = *reinterpret_cast<const float4*>(src + 4 * (size_t)i);
-      *reinterpret_cast<float4*>(src + 4 * (size_t)i) = zero4;
-    }
-    float2* csrc = reinterpret_cast<float2*>(c.cnts) + (size_t)p * capo;
-    float2* cdst = reinterpret_cast<float2*>(c.cinbox[p]) + (size_t)R * capo;
-    for (int j = tid; j < n; j += nth) {
-      cdst[j] = csrc[j];
-      csrc[j] = make_float2(0.f, 0.f);
-    }
-  }
-  prof_mark(c, 9);
-  // no grid barrier: the CTA that finishes shipping last tells the owners that their segments are complete, while
-  // the others already sum this GPU's own records (every thread reads back exactly the pieces it wrote itself)
-  if (last_cta_arrives(&c.bar[2], true, (unsigned)nb) && threadIdx.x < W && threadIdx.x != R)
+  // ---- phase A: tell every owner that this GPU's gradient records are complete.  They are: the backward pass that
+  // wrote them precedes this kernel in the stream.  The records stay where they are; each owner READS its segment of
+  // every GPU's records over NVLink and sums as it reads.  (Shipping them into inboxes first cost a pass of peer
+  // stores, a system-wide fence to drain it and a second pass to sum: 36 us of a 72 us push on eight GPUs.)
+  if (blockIdx.x == 0 && threadIdx.x < W && threadIdx.x != R)
     st_release_sys_u64(sig_word(c.sig[threadIdx.x], kSigPushReq, R), epoch << 32);
+  prof_mark(c, 9);
   prof_mark(c, 10);
 
   // ---- phase B: as owner, sum records of equal sign coming from different GPUs --------------------
   // own records first (nothing to wait for)
   {
     const int n_s = __ldcg(&c.req_n[R]);
-    const float* src = c.ginbox[R] + (size_t)R * capo * gstride;
+    const float* src = c.gU + (size_t)R * capo * gstride;
     const int total = n_s * gch;
     for (int i = tid; i < total; i += nth) {
       const int j = i / gch, ch = i - j * gch;
@@ -773,7 +752,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_push_fused_kernel(const __
       if (ou < 0) continue;
       red_add_f32x4(c.acc + (size_t)ou * gstride + 4 * ch, ldcg_f4(src + 4 * (size_t)i));
     }
-    const float2* csrc = reinterpret_cast<const float2*>(c.cinbox[R]) + (size_t)R * capo;
+    const float2* csrc = reinterpret_cast<const float2*>(c.cnts) + (size_t)R * capo;
     for (int j = tid; j < n_s; j += nth) {
       const int ou = __ldcg(&c.req_ou[R * capo + j]);
       if (ou < 0) continue;
@@ -816,7 +795,8 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_push_fused_kernel(const __
         const int sk = (R + 1 + k) % W, j = jj - s_pre[k];
         const int ou = __ldcg(&c.req_ou[sk * capo + j]);
         if (ou < 0) continue;
-        const float4 v = ldcg_f4(c.ginbox[R] + ((size_t)sk * capo + j) * gstride + 4 * ch);
+        // sender sk keeps the records it owes this GPU in segment R of its gradient matrix
+        const float4 v = ldcg_f4(c.gU_peer[sk] + ((size_t)R * capo + j) * gstride + 4 * ch);
         red_add_f32x4(c.acc + (size_t)ou * gstride + 4 * ch, v);
       }
       for (int jj = tid; jj < n_all; jj += nth) {
@@ -825,7 +805,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_push_fused_kernel(const __
         const int sk = (R + 1 + k) % W, j = jj - s_pre[k];
         const int ou = __ldcg(&c.req_ou[sk * capo + j]);
         if (ou < 0) continue;
-        const float2 sc = __ldcg(reinterpret_cast<const float2*>(c.cinbox[R]) + (size_t)sk * capo + j);
+        const float2 sc = __ldcg(reinterpret_cast<const float2*>(c.cnts_peer[sk]) + (size_t)R * capo + j);
         float* g = c.acc + (size_t)ou * gstride + dim;
         atomicAdd(g, sc.x);
         if (sc.y != 0.f) atomicAdd(g + 1, sc.y);
@@ -834,6 +814,9 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_push_fused_kernel(const __
   }
   if (gs.failed) goto done;
   prof_mark(c, 11);
+  // every value read from a peer has been consumed once all CTAs are here: the senders may clear their records
+  if (last_cta_arrives(&c.bar[2], false, (unsigned)nb) && threadIdx.x < W && threadIdx.x != R)
+    st_release_sys_u64(sig_word(c.sig[threadIdx.x], kSigPushDone, R), epoch << 32);
   if (!gs.sync(13, false)) goto done;
   prof_mark(c, 12);
 
@@ -858,6 +841,30 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_push_fused_kernel(const __
     }
   }
   prof_mark(c, 13);
+
+  // ---- tail: once every owner has read this GPU's records, clear them for the next backward pass (the owners' reads
+  // finished while this GPU updated its rows, so the wait is short)
+  {
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      const int p = threadIdx.x;
+      unsigned long long v;
+      bool ok = true;
+      if (p < W && p != R) ok = wait_flag_ge(sig_word(c.sig[R], kSigPushDone, p), epoch, &v, c.wait_ns, c.status, 16, p);
+      const bool all_ok = __all_sync(0xffffffffu, ok);
+      if (threadIdx.x == 0) s_flag = all_ok ? 0ull : ~0ull;
+    }
+    __syncthreads();
+    if (s_flag == ~0ull) { gs.failed = true; goto done; }
+    for (int p = 0; p < W; ++p) {
+      const int n = __ldcg(&c.cnt_saved[p]);
+      float4* g4 = reinterpret_cast<float4*>(c.gU + (size_t)p * capo * gstride);
+      const int total = n * gch;
+      for (int i = tid; i < total; i += nth) g4[i] = zero4;
+      float2* c2 = reinterpret_cast<float2*>(c.cnts) + (size_t)p * capo;
+      for (int j = tid; j < n; j += nth) c2[j] = make_float2(0.f, 0.f);
+    }
+  }
 
 done:
   gs.leave();

@@ -1,5 +1,5 @@
 // Inline-PTX building blocks of the Blackwell tensor-core kernels in this library (gemm_tcgen05.cu, mlp_fused.cu):
-// mbarriers with bounded waits, TMA tile loads / stores (never multicast), shared-memory matrix descriptors,
+// mbarriers with bounded waits, TMA tile loads / stores (one CTA each), shared-memory matrix descriptors,
 // tcgen05.mma issue / commit and TMEM loads.
 #pragma once
 #include <cuda.h>

@@ -38,10 +38,10 @@ struct SparseCommView {
   int gstride;   // floats per gradient record: round_up4(dim + 2)  = grad[dim] | show | click
   int ustride;   // floats per pulled row: round_up4(dim + 2 * use_cvm)
   unsigned long long* inbox_ids[kMaxWorld];  // [sender][capo]            written by senders
-  float* ginbox[kMaxWorld];                  // [sender][capo][gstride]   written by senders
-  float* cinbox[kMaxWorld];                  // [sender][capo][2]         (show, click) of each record, written by senders
+  float* gU_peer[kMaxWorld];                 // [owner][capo][gstride]    every GPU's gradient records; owners read their segment of each
+  float* cnts_peer[kMaxWorld];               // [owner][capo][2]          (show, click) of each record, likewise
   float* U[kMaxWorld];                       // [owner][capo][ustride]    written by owners
-  unsigned long long* sig[kMaxWorld];        // [3][kMaxWorld] flag words (epoch << 32 | payload)
+  unsigned long long* sig[kMaxWorld];        // [4][kMaxWorld] flag words (epoch << 32 | payload)
   unsigned long long* stage_ids;             // [owner][capo] outgoing signs, grouped by owner
   float* gU;                                 // [owner][capo][gstride] gradient wrt the pulled rows
   float* cnts;                               // [owner][capo][2] show / click counts of the batch per distinct sign

@@ -281,24 +281,24 @@ class GpuSparseLink:
             # spread times `owner_segment_slack`, and a batch that overflows it is reported (owner segment overflow).
             even = round_up(int(math.ceil(self.max_unique / W * config.owner_segment_slack)) + 64, 32)   # whole row tiles
             worst = round_up(self.max_unique + 4, 32)
-            per_row = 4 * (3 * self.gstride + self.ustride) + 48          # inbox, accumulator, gradient, pulled row, bookkeeping
+            per_row = 4 * (2 * self.gstride + self.ustride) + 48          # accumulator, gradient records, pulled row, bookkeeping
             capo = worst if W * worst * per_row <= config.segment_worst_case_mb * (1 << 20) else even
         self.capo = capo
         n_seg = W * capo
         multi = W > 1
         arena = SymmArena([
             ("inbox_ids", (n_seg if multi else 4,), torch.int64),
-            ("ginbox", (n_seg * self.gstride if multi else 4,), torch.float32),
-            ("cinbox", (n_seg * 2 if multi else 4,), torch.float32),
+            ("gU", (n_seg * self.gstride,), torch.float32),       # owners read their segment of every GPU's records
+            ("cnts", (n_seg * 2,), torch.float32),
             ("U", (n_seg * self.ustride,), torch.float32),
-            ("sig", (3 * 8,), torch.int64),
+            ("sig", (4 * 8,), torch.int64),
         ])
         d = self.dev
         dd_cap = next_pow2(2 * self.max_unique + 16)
         loc = dict(
             stage_ids=torch.zeros(n_seg, dtype=torch.int64, device=d),
-            gU=torch.zeros(n_seg * self.gstride, dtype=torch.float32, device=d),
-            cnts=torch.zeros(n_seg * 2, dtype=torch.float32, device=d),
+            gU=arena.tensor("gU").zero_(),
+            cnts=arena.tensor("cnts").zero_(),
             cnt=torch.zeros(8, dtype=torch.int32, device=d),
             cnt_saved=torch.zeros(8, dtype=torch.int32, device=d),
             req_n=torch.zeros(8, dtype=torch.int32, device=d),
@@ -321,7 +321,7 @@ class GpuSparseLink:
         self.prof = loc["prof"]
         staged = multi if config.staged_row_return < 0 else bool(config.staged_row_return)
         self.comm = dict(world=W, rank=table.rank, capo=capo, staged_return=staged, gstride=self.gstride, ustride=self.ustride,
-                         inbox_ids=arena.ptrs("inbox_ids"), ginbox=arena.ptrs("ginbox"), cinbox=arena.ptrs("cinbox"), U=arena.ptrs("U"),
+                         inbox_ids=arena.ptrs("inbox_ids"), gU_peer=arena.ptrs("gU"), cnts_peer=arena.ptrs("cnts"), U=arena.ptrs("U"),
                          sig=arena.ptrs("sig"), epoch=table.epoch, status=rt.status, wait_ns=rt.wait_ns, **loc)
         self.ctx = table.ext.SparseCtx(table.table_dict(), self.comm, table._opt_dict())
         self._last_n_ids = 0

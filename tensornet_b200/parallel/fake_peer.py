@@ -4,7 +4,9 @@ The kernels talk through symmetric memory: a sender writes its payload into a re
 release-stores a 64-bit word ``epoch << 32 | count`` into the receiver's flag table; the receiver acquire-loads that
 word with a wall-time budget and, when the budget runs out, records ``{code, phase, peer}`` in its status words,
 skips the rest of its work and returns (csrc/tn_device.cuh ``wait_flag_ge``; csrc/sparse_fused.cu phases A2, B1, B2, C
-of the pull and A, B, C of the push).  This module restates that protocol with ``W`` ranks as threads of one process
+of the pull and A, B, C and the tail of the push).  In the push the payload does not move: a sender only raises
+"my records are complete", every owner reads its segment out of the sender's memory, answers "read", and the sender
+clears its records once every owner has answered.  This module restates that protocol with ``W`` ranks as threads of one process
 and numpy arrays as the "symmetric heap", on top of the CPU tables, so that the hand-shake order and the failure
 behaviour can be exercised without a GPU: a test may drop or delay any single flag and must see every rank return
 within the budget with the right peer named.  The reference's counterpart is the brpc retry loop that ends in
@@ -18,9 +20,9 @@ from typing import Dict, List, Optional, Tuple
 
 import numpy as np
 
-K_PULL_REQ, K_PULL_DONE, K_PUSH_REQ = 0, 1, 2          # flag kinds, as in the kernels
+K_PULL_REQ, K_PULL_DONE, K_PUSH_REQ, K_PUSH_DONE = 0, 1, 2, 3    # flag kinds, as in the kernels
 OK, PEER_WAIT_TIMEOUT = 0, 5                           # status codes, as in the kernels
-PHASE_PULL_IDS, PHASE_PULL_DONE, PHASE_PUSH_RECORDS = 3, 6, 12
+PHASE_PULL_IDS, PHASE_PULL_DONE, PHASE_PUSH_RECORDS, PHASE_PUSH_READ = 3, 6, 12, 16
 
 
 class FakeHeap:
@@ -29,7 +31,7 @@ class FakeHeap:
     def __init__(self, world: int, wait_budget_s: float = 0.5):
         self.world = world
         self.budget = float(wait_budget_s)
-        self.sig = np.zeros((world, 3, world), dtype=np.uint64)             # sig[receiver, kind, sender]
+        self.sig = np.zeros((world, 4, world), dtype=np.uint64)             # sig[receiver, kind, sender]
         self.box: List[Dict[Tuple[int, int], object]] = [dict() for _ in range(world)]   # box[receiver][(kind, sender)]
         self.status = np.zeros((world, 3), dtype=np.int64)                  # code, phase, peer
         self._lock = threading.Lock()
@@ -140,21 +142,27 @@ class FakeRank:
         uniq, order, counts, show, click = self._route
         cuts = np.cumsum(counts)[:-1]
         parts = [np.split(a[order], cuts) for a in (uniq, grads.astype(np.float32), show, click)]
-        for p in range(W):                                                   # phase A: records, then the flag
+        for p in range(W):                                                   # phase A: "my records are complete"
             h.post(K_PUSH_REQ, R, p, tuple(a[p] for a in parts), ep, int(counts[p]))
         acc: Dict[int, list] = {}
         for s in [R] + [s for s in range(W) if s != R]:                      # phase B: own records, then the peers'
             if h.wait(K_PUSH_REQ, s, R, ep, PHASE_PUSH_RECORDS) is None:
                 return False
-            signs, g, sh, ck = h.box[R][(K_PUSH_REQ, s)]
+            signs, g, sh, ck = h.box[R][(K_PUSH_REQ, s)]                      # read out of the sender's memory
             for i, sgn in enumerate(signs.tolist()):
                 a = acc.setdefault(sgn, [np.zeros(self.dim, np.float32), 0.0, 0.0])
                 a[0] += g[i]; a[1] += float(sh[i]); a[2] += float(ck[i])
+        for s in range(W):                                                   # "read": the senders may clear their records
+            if s != R:
+                h.post(K_PUSH_DONE, R, s, None, ep)
         if acc:                                                              # phase C: one update per sign
             signs = np.fromiter(acc.keys(), dtype=np.uint64, count=len(acc))
             self.table.push(signs, np.stack([acc[int(s)][0] for s in signs]),
                             np.array([acc[int(s)][1] for s in signs], np.float32),
                             np.array([acc[int(s)][2] for s in signs], np.float32))
+        for p in range(W):                                                   # tail: every owner has read this rank's records
+            if p != R and h.wait(K_PUSH_DONE, p, R, ep, PHASE_PUSH_READ) is None:
+                return False
         return True
 
 
@@ -174,5 +182,5 @@ def run_ranks(fns) -> list:
     return out
 
 
-__all__ = ["FakeHeap", "FakeRank", "run_ranks", "K_PULL_REQ", "K_PULL_DONE", "K_PUSH_REQ", "PEER_WAIT_TIMEOUT",
-           "PHASE_PULL_IDS", "PHASE_PULL_DONE", "PHASE_PUSH_RECORDS"]
+__all__ = ["FakeHeap", "FakeRank", "run_ranks", "K_PULL_REQ", "K_PULL_DONE", "K_PUSH_REQ", "K_PUSH_DONE", "PEER_WAIT_TIMEOUT",
+           "PHASE_PULL_IDS", "PHASE_PULL_DONE", "PHASE_PUSH_RECORDS", "PHASE_PUSH_READ"]

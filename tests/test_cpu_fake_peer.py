@@ -83,3 +83,18 @@ def test_late_flag_within_the_budget_is_harmless():
     assert all(p is not None for p in pulled)
     ok = fp.run_ranks([lambda r=r: ranks[r].push(np.ones((len(set(ids[r].tolist())), DIM), np.float32)) for r in range(W)])
     assert ok == [True, True, True] and (heap.status[:, 0] == fp.OK).all()
+
+
+def test_sender_waits_for_its_records_to_be_read():
+    """The push leaves the records in the sender's memory: an owner that never answers "read" makes exactly the sender
+    it owes the answer give up in the tail of its push (the rows were updated everywhere; only the sender's clear of
+    its own records is withheld)."""
+    ext, heap, ranks = _job(budget=0.3)
+    ids = [_ids(r) for r in range(W)]
+    pulled = fp.run_ranks([lambda r=r: ranks[r].pull(ids[r]) for r in range(W)])
+    assert all(p is not None for p in pulled)
+    heap.drop_flag(fp.K_PUSH_DONE, sender=2, receiver=0)         # rank 0 never learns that rank 2 has read its records
+    ok = fp.run_ranks([lambda r=r: ranks[r].push(np.ones((len(set(ids[r].tolist())), DIM), np.float32)) for r in range(W)])
+    assert ok == [False, True, True]
+    assert heap.status[0].tolist() == [fp.PEER_WAIT_TIMEOUT, fp.PHASE_PUSH_READ, 2]
+    assert (heap.status[1:, 0] == fp.OK).all()
