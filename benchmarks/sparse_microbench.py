@@ -63,6 +63,29 @@ def time_us(fn, iters, rt, warm=2):
     return float(t)
 
 
+def time_pair_us(first, second, iters, rt, warm=2):
+    """Device time of ``first(k)`` and of ``second(k)`` run back to back, each from its own event pair (max over ranks)."""
+    for k in range(warm):
+        first(k)
+        second(k)
+    rt.barrier()
+    torch.cuda.synchronize()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(iters)]
+    for k in range(iters):
+        ev[k][0].record()
+        first(k)
+        ev[k][1].record()
+        second(k)
+        ev[k][2].record()
+    torch.cuda.synchronize()
+    a = sorted(e[0].elapsed_time(e[1]) * 1e3 for e in ev)[iters // 2]
+    b = sorted(e[1].elapsed_time(e[2]) * 1e3 for e in ev)[iters // 2]
+    t = torch.tensor([a, b], dtype=torch.float64)
+    if rt.world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=rt.host_group)
+    return float(t[0]), float(t[1])
+
+
 class LibraryTable:
     """The same sharded table from library calls: sorted keys + searchsorted, rows in a dense tensor, AdaGrad in torch ops."""
 
@@ -179,10 +202,7 @@ def main():
                 lk.gU[:, :dim] += 1e-3
             torch.cuda.synchronize()
             rt.check_status()
-            t_both = time_us(pull_push, a.iters, rt)
-            t_pull = time_us(pull, a.iters, rt)
-            lk.push()
-            t_push = t_both - t_pull
+            t_pull, t_push = time_pair_us(pull, lambda k: lk.push(), a.iters, rt)      # medians, each from its own events
             nu = float(sum(lk.unique_counts()))
             remote = (W - 1) / W
             row_b, rec_b = 4 * t.ustride, 4 * t.gstride
@@ -207,14 +227,12 @@ def main():
                 def lib_pull(k):
                     state["U"] = lib.pull(batches[k % a.pool])
 
-                def lib_both(k):
-                    U = lib.pull(batches[k % a.pool])
-                    lib.push(torch.full_like(U, 1e-3))
+                def lib_push(k):
+                    lib.push(torch.full_like(state["U"], 1e-3))
 
-                tl_pull = time_us(lib_pull, max(3, a.iters // 2), rt)
-                tl_both = time_us(lib_both, max(3, a.iters // 2), rt)
-                r.update(library_pull_us=tl_pull, library_push_us=tl_both - tl_pull, speedup_vs_library_pull=tl_pull / t_pull,
-                         speedup_vs_library_push=(tl_both - tl_pull) / t_push)
+                tl_pull, tl_push = time_pair_us(lib_pull, lib_push, max(5, a.iters // 2), rt)      # medians, each from its own events
+                r.update(library_pull_us=tl_pull, library_push_us=tl_push, speedup_vs_library_pull=tl_pull / t_pull,
+                         speedup_vs_library_push=tl_push / t_push)
             if rt.rank == 0:
                 print(json.dumps(r), flush=True)
             t.links.remove(lk)

@@ -128,6 +128,9 @@ def _is_static(spec) -> bool:
     return True
 
 
+_LOSS_RING = 8      # pinned slots for per-step losses on their way to the host
+
+
 def graph_decision(world: int, known: bool, static: bool, n_graphs: int, max_graphs: int, eager_steps: int,
                    warmup: int) -> str:
     """What ``train_step`` does with a batch: ``"eager"``, ``"capture"`` (then replay) or ``"replay"``.
@@ -595,7 +598,8 @@ class Model(nn.Module):
 
         ``prefetch``: copy the next batch to the device on a second stream while the current step runs.
         ``record_step_loss``: read every step's loss back to the host (``history["step_loss"]``); the 4-byte copy
-        of step k is issued right behind the step and collected while step k+1 runs, so it costs no stall.
+        of step k is issued right behind the step into a ring of pinned slots and collected when it has arrived, so
+        the host may run a few steps ahead of the device and a late rank's hiccup does not stall the others.
         The history carries the loss of the last step of every pass and, per compiled metric, its value at the
         end of every pass (metric state is reset when a pass begins, as Keras does)."""
         with start_as_current_span("fit"):
@@ -609,8 +613,8 @@ class Model(nn.Module):
             pinned = None
             if gpu and record_step_loss:
                 if getattr(self, "_pinned_loss", None) is None:      # page-locked allocation is slow: once per model
-                    self._pinned_loss = [torch.zeros((), dtype=torch.float32).pin_memory() for _ in range(2)]
-                    self._loss_events = [torch.cuda.Event(), torch.cuda.Event()]
+                    self._pinned_loss = torch.zeros(_LOSS_RING, dtype=torch.float32).pin_memory()
+                    self._loss_events = [torch.cuda.Event() for _ in range(_LOSS_RING)]
                 pinned = self._pinned_loss
                 events = self._loss_events
             for cb in callbacks:
@@ -623,7 +627,7 @@ class Model(nn.Module):
                 if self.metrics:
                     self.reset_metrics()
                 last = None
-                pending = None       # index of the pinned slot holding the previous step's loss
+                issued = collected = 0       # losses copied to / read from the pinned ring (the host runs up to _LOSS_RING - 1 steps ahead)
                 for i, batch in enumerate(self._batch_source(dataset, prefetch)):
                     if steps_per_epoch is not None and i >= steps_per_epoch:
                         break
@@ -632,22 +636,25 @@ class Model(nn.Module):
                         if pinned is None:
                             history["step_loss"].append(float(last))
                         else:
-                            slot = i & 1
-                            pinned[slot].copy_(last.detach(), non_blocking=True)
+                            slot = issued % _LOSS_RING
+                            pinned[slot: slot + 1].copy_(last.detach().reshape(1), non_blocking=True)
                             events[slot].record()
-                            if pending is not None:
-                                events[pending].synchronize()
-                                history["step_loss"].append(float(pinned[pending]))
-                            pending = slot
+                            issued += 1
+                            # read back what has arrived; wait only when the ring is about to wrap
+                            while collected < issued and (issued - collected >= _LOSS_RING or events[collected % _LOSS_RING].query()):
+                                events[collected % _LOSS_RING].synchronize()
+                                history["step_loss"].append(float(pinned[collected % _LOSS_RING]))
+                                collected += 1
                     for cb in batch_cbs:
                         cb.on_train_batch_end(i, {"batch": int(batch[1].shape[0]) if torch.is_tensor(batch[1]) else 0})
                     if verbose and (i + 1) % log_every == 0:
                         print(f"epoch {epoch} step {i + 1} loss {float(last):.5f}", flush=True)
                     if self.stop_training:
                         break
-                if pinned is not None and pending is not None:
-                    events[pending].synchronize()
-                    history["step_loss"].append(float(pinned[pending]))
+                while pinned is not None and collected < issued:
+                    events[collected % _LOSS_RING].synchronize()
+                    history["step_loss"].append(float(pinned[collected % _LOSS_RING]))
+                    collected += 1
                 core.runtime().check_status()
                 if core.config.verify_guards_each_pass:
                     verify_all_arenas()
