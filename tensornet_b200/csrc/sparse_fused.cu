@@ -72,33 +72,16 @@ __device__ __forceinline__ void prof_mark(const SparseCommView& c, int slot) {
   if (c.prof != nullptr && blockIdx.x == 0 && threadIdx.x == 0) c.prof[slot] = globaltimer_ns();
 }
 
-// One requested row, handled by a group of G lanes: resolve a request that lost the insert race, initialise a
-// brand-new row (owner) or recompute its initial value (other requesters of the same step), or read the stored
-// row; write the pulled row (w[dim], the two CVM columns when enabled, zero padding) to `dst`, which is either
-// the requester's matrix itself or a shared-memory tile that is written out afterwards.
-__device__ __forceinline__ void pull_return_row(const PullArgs& a, const TableView& t, unsigned long long epoch, bool need_ou,
-                                                int q, unsigned long long key, float* dst, int gl, int G) {
+// One requested row, handled by a group of G lanes: initialise a brand-new row (owner) or recompute its initial
+// value (other requesters of the same step), or read the stored row; write the pulled row (w[dim], the two CVM
+// columns when enabled, zero padding) to `dst`, which is either the requester's matrix itself or a shared-memory
+// tile that is written out afterwards.  `rr` is the resolved request word of the probe.
+__device__ __forceinline__ void pull_return_row(const PullArgs& a, const TableView& t, int rr, unsigned long long key,
+                                                float* dst, int gl, int G) {
   const SparseCommView& c = a.c;
   const SparseOptParams& o = a.opt;
   const int dim = t.dim, stride = t.stride;
   const int uchunks = c.ustride >> 2, rchunks = stride >> 2;
-  int rr = __ldcg(&c.req_row[q]);
-  if (rr == kReqPending) {
-    int h = __ldcg(&c.req_ou[q]);
-    int r = ld_volatile_s32(&t.slots[h]);
-    if (r >= 0) {
-      unsigned long long tg = __ldcg(&t.row_tag[r]);
-      bool fresh = (tg >> 32) == epoch && (tg & kTagNew);
-      rr = fresh ? (r | kReqNewCopy) : r;
-      if (gl == 0) {
-        c.req_row[q] = rr;
-        c.req_ou[q] = need_ou ? (int)(tg & 0x7fffffffull) : -1;
-      }
-    } else {
-      rr = kReqNone;
-      if (gl == 0) { c.req_row[q] = kReqNone; c.req_ou[q] = -1; }
-    }
-  }
   if (rr == kReqNone) {
     for (int ch = gl; ch < uchunks; ch += G) *reinterpret_cast<float4*>(dst + 4 * ch) = make_float4(0.f, 0.f, 0.f, 0.f);
     return;
@@ -166,6 +149,9 @@ __device__ __forceinline__ void pull_return_row(const PullArgs& a, const TableVi
 // =======================================================================================
 // sparse_pull_fused
 // =======================================================================================
+// kTiled: the staged row return (PullArgs::tile_rows > 0); one instantiation per form keeps the other form's code and
+// registers out of the loop.
+template <bool kTiled>
 __global__ void __launch_bounds__(kThreads, 1) sparse_pull_fused_kernel(const __grid_constant__ PullArgs a) {
   const SparseCommView& c = a.c;
   // The table's arrays are read through a descriptor in device memory when the caller has one: the shard can then
@@ -290,223 +276,243 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_pull_fused_kernel(const __
       }
     }
   }
+  gs.arrive();       // this CTA no longer reads the dedup scratch; phase C waits for all of them before clearing it
   prof_mark(c, 2);
 
-  // ---- phase B1: as owner, probe / insert every requested sign ------------------------------------
-  // Two passes: this GPU's own segment first (nothing to wait for), then the segments of all other senders as
-  // ONE flat index space, so that with many GPUs no thread idles on a short per-sender segment.
-  // s_pre[k] = ids of senders R+1 .. R+k (mod W) that precede sender R+1+k in that space.
-  for (int part = 0; part < (W > 1 ? 2 : 1); ++part) {
-    __syncthreads();
-    if (part == 0 && threadIdx.x == 0) {
-      const int v = min(__ldcg(&c.cnt[R]), capo);
-      s_n[R] = v;
-      if (blockIdx.x == 0) c.req_n[R] = v;
-      s_flag = (unsigned long long)v;
-    }
-    if (part == 1 && threadIdx.x < 32) {
-      // one lane per sender: the W-1 flags are polled side by side, the counts they carry are turned into the
-      // flat index space with a warp scan
-      const int k = threadIdx.x;
-      const int sk = (R + 1 + k) % W;
-      unsigned long long f = 0;
-      bool ok = true;
-      if (k + 1 < W) ok = wait_flag_ge(sig_word(c.sig[R], kSigPullReq, sk), epoch, &f, c.wait_ns, c.status, 3, sk);
-      const bool all_ok = __all_sync(0xffffffffu, ok);
-      const int n_k = (k + 1 < W && all_ok) ? (int)(f & 0xffffffffull) : 0;
-      int incl = n_k;
+  // ---- phase B: as owner, probe / insert every requested sign and return its row ----------------------
+  // A warp takes 32 requests at a time: every lane probes (or inserts) one sign, then the warp's lane groups
+  // return the 32 rows.  No grid barrier separates probing from the row return, so the row stores of one warp
+  // cross NVLink while other warps still wait on their probes.  Two passes: this GPU's own segment first
+  // (nothing to wait for), then the segments of all other senders as ONE flat space of units, so that with many
+  // GPUs no warp idles on a short per-sender segment.  A unit is one shared-memory tile of the staged return
+  // (tile_rows consecutive requests of one sender) or, without staging, a single request.
+  // s_pre[k] = units of the senders that precede the k-th sender of the pass.
+  {
+    const int G = a.lanes;
+    const int gl = threadIdx.x % G, sub = lane / G, rpp = 32 / G;
+    const int ustride = c.ustride, uchunks = ustride >> 2;
+    const int TR = kTiled ? a.tile_rows : 0;
+    const int urows = kTiled ? TR : 1;
+    const int upw = 32 / urows;                        // units per warp step
+    extern __shared__ float4 s_tiles[];
+    float* tile = reinterpret_cast<float*>(s_tiles) + (size_t)(threadIdx.x >> 5) * TR * ustride;
+    const int n_warps = nth >> 5;
+    for (int part = 0; part < (W > 1 ? 2 : 1); ++part) {
+      __syncthreads();
+      if (part == 0 && threadIdx.x == 0) {
+        const int v = min(__ldcg(&c.cnt[R]), capo);
+        s_n[R] = v;
+        if (blockIdx.x == 0) c.req_n[R] = v;
+        s_pre[0] = 0;
+        s_pre[1] = (v + urows - 1) / urows;
+        s_flag = (unsigned long long)s_pre[1];
+      }
+      if (part == 1 && threadIdx.x < 32) {
+        // one lane per sender: the W-1 flags are polled side by side, the counts they carry are turned into the
+        // flat unit space with a warp scan
+        const int k = threadIdx.x;
+        const int sk = (R + 1 + k) % W;
+        unsigned long long f = 0;
+        bool ok = true;
+        if (k + 1 < W) ok = wait_flag_ge(sig_word(c.sig[R], kSigPullReq, sk), epoch, &f, c.wait_ns, c.status, 3, sk);
+        const bool all_ok = __all_sync(0xffffffffu, ok);
+        const int n_k = (k + 1 < W && all_ok) ? (int)(f & 0xffffffffull) : 0;
+        int incl = (n_k + urows - 1) / urows;
 #pragma unroll
-      for (int o = 1; o < kMaxWorld; o <<= 1) {
-        const int up = __shfl_up_sync(0xffffffffu, incl, o);
-        if (k >= o) incl += up;
+        for (int o = 1; o < kMaxWorld; o <<= 1) {
+          const int up = __shfl_up_sync(0xffffffffu, incl, o);
+          if (k >= o) incl += up;
+        }
+        if (k + 1 < W) {
+          s_n[sk] = n_k;
+          if (blockIdx.x == 0) c.req_n[sk] = n_k;
+          s_pre[k + 1] = incl;
+        }
+        if (k == 0) s_pre[0] = 0;
+        const int total = __shfl_sync(0xffffffffu, incl, W - 2);
+        if (k == 0) s_flag = all_ok ? (unsigned long long)total : ~0ull;
       }
-      if (k + 1 < W) {
-        s_n[sk] = n_k;
-        if (blockIdx.x == 0) c.req_n[sk] = n_k;
-        s_pre[k + 1] = incl;
-      }
-      if (k == 0) s_pre[0] = 0;
-      const int total = __shfl_sync(0xffffffffu, incl, W - 2);
-      if (k == 0) s_flag = all_ok ? (unsigned long long)total : ~0ull;
-    }
-    __syncthreads();
-    if (s_flag == ~0ull) { gs.failed = true; break; }
-    const int n_part = (int)(s_flag & 0xffffffffull);
-    for (int base = tid - lane; base < n_part; base += nth) {
-      const int jj = base + lane;
-      const bool valid = jj < n_part;
-      int s = R, j = jj;
-      if (part == 1 && valid) {
-        int k = 0;
-        while (jj >= s_pre[k + 1]) ++k;
-        s = (R + 1 + k) % W;
-        j = jj - s_pre[k];
-      }
-      const unsigned long long* src = (s == R) ? c.stage_ids + (size_t)R * capo : c.inbox_ids[R] + (size_t)s * capo;
-      int rr = kReqNone, ou = -1;
-      bool is_new = false, need_claim = false;
-      unsigned hnew = 0;
-      int r_exist = -1;
-      unsigned long long tag_seen = 0, key = 0;
-      if (valid) {
-        key = __ldcg(&src[j]);
-        unsigned h = table_home(t, key);
-        bool placed = false;
-        for (unsigned probes = 0; probes <= t.cap_mask; ++probes) {
-          unsigned long long k = __ldcg(&t.keys[h]);
-          if (k == kEmptyKey) {
-            if (a.lookup_only) { placed = true; break; }        // read-only table (serving): an unknown sign pulls zeros
-            k = atomicCAS(&t.keys[h], kEmptyKey, key);
-            if (k == kEmptyKey) { is_new = true; hnew = h; placed = true; break; }
-          }
-          if (k == key) {
-            const int r = ld_volatile_s32(&t.slots[h]);
-            if (r == -1) {          // inserter has not published the row yet: resolve after the barrier
-              rr = kReqPending;
-              ou = (int)h;
-            } else if (r >= 0) {
-              rr = r;
-              if (W > 1) {
-                const unsigned long long tg = *((volatile unsigned long long*)&t.row_tag[r]);
-                if ((tg >> 32) == epoch) {
-                  if (tg & kTagNew) rr = r | kReqNewCopy;
-                  if (need_ou) ou = (int)(tg & 0x7fffffffull);
-                } else if (need_ou) {
-                  need_claim = true; r_exist = r; tag_seen = tg;
+      __syncthreads();
+      if (s_flag == ~0ull) { gs.failed = true; break; }
+      const int n_units = (int)(s_flag & 0xffffffffull);
+      const int first = part == 0 ? R : R + 1;
+      // units per warp step: all 32 lanes probe when there is enough work for every warp, fewer when a small batch
+      // would otherwise leave most warps idle while a few return 32 rows one after the other
+      int su = min(upw, (n_units + n_warps - 1) / n_warps);
+      if (!kTiled) su = min(32, (su + rpp - 1) / rpp * rpp);
+      if (su < 1) su = 1;
+      for (int wu = (tid >> 5) * su; wu < n_units; wu += n_warps * su) {
+        // -- probe: one request per lane
+        const int lu = lane / urows;
+        const int u = wu + lu;
+        int s = R, j = 0;
+        bool valid = false;
+        if (lu < su && u < n_units) {
+          int k = 0;
+          while (u >= s_pre[k + 1]) ++k;
+          s = (first + k) % W;
+          j = (u - s_pre[k]) * urows + lane % urows;
+          valid = j < s_n[s];
+        }
+        const unsigned long long* src = (s == R) ? c.stage_ids + (size_t)R * capo : c.inbox_ids[R] + (size_t)s * capo;
+        int rr = kReqNone, ou = -1;
+        bool is_new = false, need_claim = false;
+        unsigned hnew = 0;
+        int r_exist = -1;
+        unsigned long long tag_seen = 0, key = 0;
+        if (valid) {
+          key = __ldcg(&src[j]);
+          unsigned h = table_home(t, key);
+          bool placed = false;
+          for (unsigned probes = 0; probes <= t.cap_mask; ++probes) {
+            unsigned long long k = __ldcg(&t.keys[h]);
+            if (k == kEmptyKey) {
+              if (a.lookup_only) { placed = true; break; }        // read-only table (serving): an unknown sign pulls zeros
+              k = atomicCAS(&t.keys[h], kEmptyKey, key);
+              if (k == kEmptyKey) { is_new = true; hnew = h; placed = true; break; }
+            }
+            if (k == key) {
+              const int r = ld_volatile_s32(&t.slots[h]);
+              if (r == -1) {          // inserter has not published the row yet: resolved below, after this warp's own inserts
+                rr = kReqPending;
+                ou = (int)h;
+              } else if (r >= 0) {
+                rr = r;
+                if (W > 1) {
+                  const unsigned long long tg = *((volatile unsigned long long*)&t.row_tag[r]);
+                  if ((tg >> 32) == epoch) {
+                    if (tg & kTagNew) rr = r | kReqNewCopy;
+                    if (need_ou) ou = (int)(tg & 0x7fffffffull);
+                  } else if (need_ou) {
+                    need_claim = true; r_exist = r; tag_seen = tg;
+                  }
                 }
               }
+              placed = true;
+              break;
             }
-            placed = true;
-            break;
+            h = (h + 1) & t.cap_mask;
           }
-          h = (h + 1) & t.cap_mask;
+          if (!placed) set_status(c.status, kTableFull, 3, s);
         }
-        if (!placed) set_status(c.status, kTableFull, 3, s);
-      }
-      __syncwarp();
-      const unsigned nm = __ballot_sync(0xffffffffu, is_new);
-      const unsigned cm = __ballot_sync(0xffffffffu, need_claim);
-      const int r_new = warp_alloc(t.n_rows, nm);
-      int my_ou = -1;
-      if (need_ou) my_ou = warp_alloc(c.ocount, nm | cm);
-      if (is_new) {
-        if (r_new >= t.row_cap) {
-          atomicSub(t.n_rows, 1);
-          set_status(c.status, kTableFull, 3, s);
-          *((volatile int*)&t.slots[hnew]) = -3;
-          if (need_ou) c.ou_row[my_ou] = -1;
-        } else {
-          t.row_keys[r_new] = key;
-          unsigned long long tag = (epoch << 32) | kTagNew;
-          if (need_ou) { c.ou_row[my_ou] = r_new; tag |= (unsigned long long)my_ou; ou = my_ou; }
-          t.row_tag[r_new] = tag;
+        __syncwarp();
+        const unsigned nm = __ballot_sync(0xffffffffu, is_new);
+        const unsigned cm = __ballot_sync(0xffffffffu, need_claim);
+        const int r_new = warp_alloc(t.n_rows, nm);
+        int my_ou = -1;
+        if (need_ou) my_ou = warp_alloc(c.ocount, nm | cm);
+        if (is_new) {
+          if (r_new >= t.row_cap) {
+            atomicSub(t.n_rows, 1);
+            set_status(c.status, kTableFull, 3, s);
+            *((volatile int*)&t.slots[hnew]) = -3;
+            if (need_ou) c.ou_row[my_ou] = -1;
+          } else {
+            t.row_keys[r_new] = key;
+            unsigned long long tag = (epoch << 32) | kTagNew;
+            if (need_ou) { c.ou_row[my_ou] = r_new; tag |= (unsigned long long)my_ou; ou = my_ou; }
+            t.row_tag[r_new] = tag;
+            __threadfence();
+            *((volatile int*)&t.slots[hnew]) = r_new;
+            rr = r_new | kReqNewOwner;
+          }
+        } else if (need_claim) {
+          const unsigned long long old = atomicCAS(&t.row_tag[r_exist], tag_seen, (epoch << 32) | (unsigned long long)my_ou);
+          if (old == tag_seen) {
+            c.ou_row[my_ou] = r_exist;
+            ou = my_ou;
+          } else {                     // another sender claimed the row first: my index stays a hole
+            c.ou_row[my_ou] = -1;
+            ou = (int)(old & 0x7fffffffull);
+          }
+        }
+        __syncwarp();
+        if (rr == kReqPending) {
+          // Another thread won the insert of this sign in this very step and publishes the row index a few
+          // instructions after its CAS (a lane of this warp has done so above); wait for it, with a limit.
+          const int h = ou;
+          int r = ld_volatile_s32(&t.slots[h]);
+          const unsigned long long t0 = globaltimer_ns();
+          while (r == -1) {
+            if (globaltimer_ns() - t0 > c.wait_ns) { set_status(c.status, kGridBarrierTimeout, 4, s); break; }
+            r = ld_volatile_s32(&t.slots[h]);
+          }
           __threadfence();
-          *((volatile int*)&t.slots[hnew]) = r_new;
-          rr = r_new | kReqNewOwner;
+          rr = kReqNone;
+          ou = -1;
+          if (r >= 0) {
+            const unsigned long long tg = *((volatile unsigned long long*)&t.row_tag[r]);
+            const bool fresh = (tg >> 32) == epoch && (tg & kTagNew);
+            rr = fresh ? (r | kReqNewCopy) : r;
+            if (need_ou) ou = (int)(tg & 0x7fffffffull);
+          }
         }
-      } else if (need_claim) {
-        const unsigned long long old = atomicCAS(&t.row_tag[r_exist], tag_seen, (epoch << 32) | (unsigned long long)my_ou);
-        if (old == tag_seen) {
-          c.ou_row[my_ou] = r_exist;
-          ou = my_ou;
-        } else {                     // another sender claimed the row first: my index stays a hole
-          c.ou_row[my_ou] = -1;
-          ou = (int)(old & 0x7fffffffull);
+        if (valid) {
+          const int q = s * capo + j;
+          c.req_row[q] = rr;
+          c.req_ou[q] = ou;
+        }
+        __syncwarp();
+        // -- return: groups of G lanes take the warp's rows in turn
+        const unsigned vmask = __ballot_sync(0xffffffffu, valid);
+        if (kTiled) {
+          // Staged return: the warp gathers the rows of a tile into shared memory and then writes the tile out as
+          // one contiguous run of full 128-byte lines (16 bytes per lane, 512 per instruction).  Row-by-row stores
+          // of short rows (80 bytes for dim 16 + linear) reach a peer as partial lines and lose about a third of
+          // the NVLink write rate; the local case gains too.
+          for (int ti = 0; ti < su; ++ti) {
+            const unsigned tmask = (vmask >> (ti * TR)) & (TR >= 32 ? 0xffffffffu : ((1u << TR) - 1u));
+            if (tmask == 0) continue;
+            const int nrows = __popc(tmask);            // the valid requests of a tile are its first ones
+            const int s_t = __shfl_sync(0xffffffffu, s, ti * TR), j0 = __shfl_sync(0xffffffffu, j, ti * TR);
+            for (int p0 = 0; p0 < TR; p0 += rpp) {
+              const int jr = p0 + sub;
+              const int from = (ti * TR + jr) & 31;
+              const int rr_s = __shfl_sync(0xffffffffu, rr, from);
+              const unsigned long long key_s = __shfl_sync(0xffffffffu, key, from);
+              if (jr < nrows) pull_return_row(a, t, rr_s, key_s, tile + (size_t)jr * ustride, gl, G);
+            }
+            __syncwarp();
+            float4* d4 = reinterpret_cast<float4*>(c.U[s_t] + ((size_t)R * capo + j0) * ustride);
+            const float4* t4 = reinterpret_cast<const float4*>(tile);
+            const int n4 = nrows * uchunks;
+            for (int i = lane; i < n4; i += 32) d4[i] = t4[i];
+            __syncwarp();
+          }
+        } else {
+          for (int p0 = 0; p0 < su; p0 += rpp) {
+            const int from = p0 + sub;
+            const int rr_s = __shfl_sync(0xffffffffu, rr, from);
+            const unsigned long long key_s = __shfl_sync(0xffffffffu, key, from);
+            const int s_s = __shfl_sync(0xffffffffu, s, from), j_s = __shfl_sync(0xffffffffu, j, from);
+            if ((vmask >> from) & 1u)
+              pull_return_row(a, t, rr_s, key_s, c.U[s_s] + ((size_t)R * capo + j_s) * ustride, gl, G);
+          }
         }
       }
-      if (valid) {
-        const int q = s * capo + j;
-        c.req_row[q] = rr;
-        c.req_ou[q] = ou;
-      }
+      if (part == 0) prof_mark(c, 3);
     }
   }
   if (gs.failed) goto done;
-  if (!gs.sync(4, false)) goto done;
-  prof_mark(c, 3);
-
-  if (blockIdx.x == 0 && threadIdx.x < W) {  // counts of this step for pooling / push, then re-arm
-    c.cnt_saved[threadIdx.x] = min(c.cnt[threadIdx.x], capo);
-    c.cnt[threadIdx.x] = 0;
-  }
-
-  // ---- phase B2: initialise new rows, write rows straight into each requester's matrix -----------
-  {
-    const int G = a.lanes;
-    const int gl = threadIdx.x % G;
-    const int ustride = c.ustride, stride = t.stride;
-    const int uchunks = ustride >> 2;
-    // all requesters as one flat index space (own segment first)
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      s_pre[0] = 0;
-      if (a.tile_rows > 0) {     // s_pre[k] = tiles of requesters R .. R+k-1 (mod W)
-        for (int k = 0; k < W; ++k) s_pre[k + 1] = s_pre[k] + (s_n[(R + k) % W] + a.tile_rows - 1) / a.tile_rows;
-      } else {                   // s_pre[k] = rows of those requesters
-        for (int k = 0; k < W; ++k) s_pre[k + 1] = s_pre[k] + s_n[(R + k) % W];
-      }
-    }
-    __syncthreads();
-    const int n_all = s_pre[W];
-    if (a.tile_rows > 0) {
-      // Staged return: a warp gathers TR consecutive rows of one requester into shared memory and then writes
-      // the tile out as one contiguous run of full 128-byte lines (16 bytes per lane, 512 per instruction).
-      // Row-by-row stores of short rows (80 bytes for dim 16 + linear) reach a peer as partial lines and lose
-      // about a third of the NVLink write rate; the local case gains too (7 us instead of 10 for 144 K rows).
-      extern __shared__ float4 s_tiles[];
-      const int TR = a.tile_rows;
-      const int rpp = 32 / G;                                   // rows gathered per pass
-      const int sub = lane / G;
-      float* tile = reinterpret_cast<float*>(s_tiles) + (size_t)(threadIdx.x >> 5) * TR * ustride;
-      const int n_warps = nth >> 5;
-      for (int tl = tid >> 5; tl < n_all; tl += n_warps) {
-        int k = 0;
-        while (tl >= s_pre[k + 1]) ++k;
-        const int s = (R + k) % W, j0 = (tl - s_pre[k]) * TR;
-        const int nrows = min(TR, s_n[s] - j0);
-        const unsigned long long* src = (s == R) ? c.stage_ids + (size_t)R * capo : c.inbox_ids[R] + (size_t)s * capo;
-        for (int jr = sub; jr < nrows; jr += rpp)
-          pull_return_row(a, t, epoch, need_ou, s * capo + j0 + jr, __ldcg(&src[j0 + jr]), tile + (size_t)jr * ustride, gl, G);
-        __syncwarp();
-        float4* d4 = reinterpret_cast<float4*>(c.U[s] + ((size_t)R * capo + j0) * ustride);
-        const float4* t4 = reinterpret_cast<const float4*>(tile);
-        const int n4 = nrows * uchunks;
-        for (int i = lane; i < n4; i += 32) d4[i] = t4[i];
-        __syncwarp();
-      }
-    } else {
-      const int gid = tid / G, ngroups = nth / G;
-      for (int jj = gid; jj < n_all; jj += ngroups) {
-        int k = 0;
-        while (jj >= s_pre[k + 1]) ++k;
-        const int s = (R + k) % W, j = jj - s_pre[k];
-        const unsigned long long* src = (s == R) ? c.stage_ids + (size_t)R * capo : c.inbox_ids[R] + (size_t)s * capo;
-        if (jj + ngroups < n_all) {
-          const int j2 = jj + ngroups;
-          int k2 = k;
-          while (j2 >= s_pre[k2 + 1]) ++k2;
-          const int r2 = __ldcg(&c.req_row[((R + k2) % W) * capo + (j2 - s_pre[k2])]);
-          if (r2 >= 0 && !(r2 & (kReqNewOwner | kReqNewCopy))) prefetch_row_l2(t.rows + (size_t)r2 * stride, ustride, gl, G);
-        }
-        pull_return_row(a, t, epoch, need_ou, s * capo + j, __ldcg(&src[j]), c.U[s] + ((size_t)R * capo + j) * ustride, gl, G);
-      }
-    }
-  }
   if (c.prof != nullptr && threadIdx.x == 0) atomicMax(&c.prof[6], globaltimer_ns());   // slowest CTA's end of the row return
   prof_mark(c, 4);
 
-  // ---- phase C: clear the dedup scratch; tell the requesters their rows have landed ---------------
+  // ---- phase C: tell the requesters their rows have landed; clear the dedup scratch while the flags travel -----
   {
+    // The CTA that returns its rows last saves the per-owner counts of this step for pooling / push and re-arms
+    // them, and tells every requester that its matrix is complete; CTA 0 then keeps the kernel alive until the
+    // same word has arrived from every owner.
+    const bool last = last_cta_arrives(&c.bar[3], W > 1);
+    if (last && threadIdx.x < W) {
+      c.cnt_saved[threadIdx.x] = min(c.cnt[threadIdx.x], capo);
+      c.cnt[threadIdx.x] = 0;
+      if (threadIdx.x != R) st_release_sys_u64(sig_word(c.sig[threadIdx.x], kSigPullDone, R), epoch << 32);
+    }
+    if (!gs.wait(4)) goto done;      // every CTA has finished its inverse map (it arrived before phase B)
     ulonglong2* kk = reinterpret_cast<ulonglong2*>(c.dd_keys);
     const int n2 = (int)((c.dd_mask + 1u) >> 1);
     for (int i = tid; i < n2; i += nth) kk[i] = make_ulonglong2(kEmptyKey, kEmptyKey);
-  }
-  if (W > 1) {
-    // the CTA that returns its rows last tells every requester that its matrix is complete; CTA 0 then keeps
-    // the kernel alive until the same word has arrived from every owner
-    if (last_cta_arrives(&c.bar[3], true) && threadIdx.x < W && threadIdx.x != R)
-      st_release_sys_u64(sig_word(c.sig[threadIdx.x], kSigPullDone, R), epoch << 32);
-    if (blockIdx.x == 0 && threadIdx.x < W && threadIdx.x != R) {
+    if (W > 1 && blockIdx.x == 0 && threadIdx.x < W && threadIdx.x != R) {
       unsigned long long v;
       wait_flag_ge(sig_word(c.sig[R], kSigPullDone, threadIdx.x), epoch, &v, c.wait_ns, c.status, 6, threadIdx.x);
     }
@@ -885,21 +891,23 @@ static int coop_grid(const void* fn, int device) {
 cudaError_t launch_sparse_pull(const PullArgs& args, int work_items, cudaStream_t stream) {
   int dev = 0;
   cudaGetDevice(&dev);
-  static int grid_max[64] = {0};
-  if (grid_max[dev] == 0) grid_max[dev] = coop_grid((const void*)sparse_pull_fused_kernel, dev);
+  const bool tiled = args.tile_rows > 0;
+  const void* fn = tiled ? (const void*)sparse_pull_fused_kernel<true> : (const void*)sparse_pull_fused_kernel<false>;
+  static int grid_max[64][2] = {{0}};
+  if (grid_max[dev][tiled] == 0) grid_max[dev][tiled] = coop_grid(fn, dev);
   int grid = (work_items + kThreads - 1) / kThreads;
   if (grid < 1) grid = 1;
-  if (grid > grid_max[dev]) grid = grid_max[dev];
+  if (grid > grid_max[dev][tiled]) grid = grid_max[dev][tiled];
   const size_t smem = (size_t)args.tile_rows * args.c.ustride * sizeof(float) * (kThreads / 32);
   static bool attr_set[64] = {false};
   // static + dynamic shared memory beyond 48 KiB needs the opt-in; a 48 KiB tile buffer alone already crosses it
   if (smem > 32 * 1024 && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute((const void*)sparse_pull_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
   void* params[] = {(void*)&args};
-  return cudaLaunchCooperativeKernel((const void*)sparse_pull_fused_kernel, dim3(grid), dim3(kThreads), params, smem, stream);
+  return cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kThreads), params, smem, stream);
 }
 
 // `max_ctas` > 0 caps the grid below the SM count, leaving whole SMs to a kernel running on another stream.

@@ -118,6 +118,42 @@ struct GridSync {
     return ok;
   }
 
+  // The same barrier in two halves: `arrive` when this CTA's part of a phase is done, `wait` (much later, typically
+  // for free) before the first access that needs every CTA's part.  No other barrier of this object may be used in
+  // between.  What the CTAs wrote before `arrive` is visible after `wait`.
+  __device__ __forceinline__ void arrive() {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      gen += 1;
+      atomicAdd(&bar[0], 1u);
+    }
+  }
+  __device__ __forceinline__ bool wait(int phase) {
+    __shared__ int s_ok2;
+    if (threadIdx.x == 0) {
+      const unsigned target = gen * nblocks;
+      int ok = 1;
+      unsigned long long t0 = globaltimer_ns();
+      unsigned spins = 0;
+      while (ld_acquire_gpu_u32(&bar[0]) < target) {
+        if (((++spins) & 63u) == 0) {
+          if (globaltimer_ns() - t0 > budget_ns) { ok = 0; break; }
+          if (ld_volatile_s32(status) != 0) break;
+        }
+        __nanosleep(32);
+      }
+      if (!ok) set_status(status, kGridBarrierTimeout, phase, (int)blockIdx.x);
+      if (ld_volatile_s32(status) != 0) ok = 0;
+      s_ok2 = ok;
+    }
+    __syncthreads();
+    const bool ok = s_ok2 != 0;
+    __syncthreads();
+    if (!ok) failed = true;
+    return ok;
+  }
+
   // Call once per CTA on every exit path.
   __device__ __forceinline__ void leave() {
     __syncthreads();

@@ -363,15 +363,16 @@ class GpuSparseLink:
         self.arena.tensor("sig").zero_()
 
     def pull_phase_us(self):
-        """Durations (microseconds) of the last pull's phases as seen by CTA 0:
-        dedup, inverse+dispatch, owner probe/insert, row return, scratch clear + completion."""
+        """Durations (microseconds) of the last pull's phases as seen by CTA 0: dedup; id dispatch + inverse map;
+        probe and row return of this GPU's own segment; wait for the other GPUs' ids, their probe and row return;
+        completion flags + scratch clear."""
         t = self.prof.tolist()
         return [(t[i + 1] - t[i]) / 1e3 for i in range(5)]
 
     def push_phase_us(self):
-        """Durations (microseconds) of the last multi-GPU push's phases as seen by CTA 0: moving records into the
-        owners' inboxes, grid barrier + signal, owner-side accumulation (own records, then the wait for and the
-        sum over the peers' records), grid barrier, optimizer update."""
+        """Durations (microseconds) of the last multi-GPU push's phases as seen by CTA 0: flags to the owners,
+        (unused), owner-side accumulation (own records, then the wait for and the read of the peers' records over
+        NVLink), grid barrier, optimizer update."""
         t = self.prof.tolist()
         return [(t[i + 1] - t[i]) / 1e3 for i in range(8, 13)]
 
