@@ -32,7 +32,7 @@ CUDA_SOURCES = [
     "pooling.cu",
     "table_ops.cu",
     "gemm_tcgen05.cu",
-    "mlp_fused.cu",
+    "mlp_fused.cu", "gemm_2sm.cu",
     "dense_fused.cu",
     "elementwise.cu",
     "serving.cu",

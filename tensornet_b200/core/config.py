@@ -42,9 +42,11 @@ class Config:
     gate_first_gemm: bool = True   # multi-GPU: first MLP GEMM waits for the dense all-gather (no closing barrier)
     #: pull returns rows through shared-memory tiles: -1 = only with several GPUs, 0 = never, 1 = always
     staged_row_return: int = -1
-    #: multi-GPU: run the dense step beside the sparse push (small dense arrays only); measured at 2 GPUs on the
-    #: DeepFM step: 2 % slower than back to back (both kernels are latency-bound and lose CTAs), so off by default
-    overlap_dense_push: bool = False
+    #: multi-GPU: run the dense step beside the sparse push on a second stream, each on its own share of the SMs.
+    #: -1 = only for dense arrays above 4 M elements (smaller ones ride on the push kernel, see below; measured at
+    #: 2 GPUs on the DeepFM step, side by side was 2 % slower than back to back), 0 = never, 1 = always
+    overlap_dense_push: int = -1
+    overlap_dense_sms: int = 40    # SMs the push leaves to a large dense step
     #: multi-GPU, dense arrays up to 4 M elements: the dense step runs on a few CTAs of the last sparse push kernel of
     #: the step instead of in a kernel of its own behind it
     dense_rides_push: bool = True
@@ -82,7 +84,8 @@ class Config:
         c.gate_first_gemm = _env("TN_GATE_FIRST_GEMM", c.gate_first_gemm, bool)
         c.staged_row_return = _env("TN_STAGED_RETURN", c.staged_row_return, int)
         c.dense_small_grid = _env("TN_DENSE_SMALL_GRID", c.dense_small_grid, int)
-        c.overlap_dense_push = _env("TN_OVERLAP_DENSE_PUSH", c.overlap_dense_push, bool)
+        c.overlap_dense_push = _env("TN_OVERLAP_DENSE_PUSH", c.overlap_dense_push, int)
+        c.overlap_dense_sms = _env("TN_OVERLAP_DENSE_SMS", c.overlap_dense_sms, int)
         c.dense_rides_push = _env("TN_DENSE_RIDES_PUSH", c.dense_rides_push, bool)
         c.checkpoint_chunk_rows = _env("TN_CKPT_CHUNK_ROWS", c.checkpoint_chunk_rows, int)
         c.checkpoint_load_chunk_rows = _env("TN_CKPT_LOAD_CHUNK_ROWS", c.checkpoint_load_chunk_rows, int)

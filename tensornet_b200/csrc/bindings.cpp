@@ -418,6 +418,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("apply_fwd", &BnCtx::apply_fwd)
       .def("apply_bwd", &BnCtx::apply_bwd);
   py::class_<DenseCtx>(m, "DenseCtx").def(py::init<py::dict>()).def("step", &DenseCtx::step, py::arg("skip_open") = false).def("set_gated", &DenseCtx::set_gated).def("set_max_ctas", &DenseCtx::set_max_ctas);
+  m.def("dense_ctas_per_sm", [] { return tn::dense_step_ctas_per_sm(); });
   m.def("mlp_chain", [](bool backward, at::Tensor x, int in_cols, std::vector<at::Tensor> weights, std::vector<int> n_rows,
                         std::vector<int> k_cols, std::vector<at::Tensor> outs, std::vector<int> relu, std::vector<int> n_valid,
                         std::vector<c10::optional<at::Tensor>> masks, at::Tensor status, c10::optional<at::Tensor> gate_flags,

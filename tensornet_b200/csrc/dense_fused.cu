@@ -60,6 +60,12 @@ __global__ void __launch_bounds__(kDThreads) dense_fused_kernel(const __grid_con
 
 }  // namespace
 
+int dense_step_ctas_per_sm() {
+  int per_sm = 0;
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, dense_fused_kernel, kDThreads, 0);
+  return per_sm < 1 ? 1 : per_sm;
+}
+
 cudaError_t launch_dense_step(const DenseStepArgs& a, cudaStream_t st) {
   if (a.n % 4 || a.chunk % 4) return cudaErrorInvalidValue;
   if (a.world == 1) {

@@ -26,6 +26,7 @@
 #include <unordered_map>
 #include "gemm_tcgen05.h"
 #include "tc_primitives.cuh"
+#include "gemm_epilogue.cuh"
 
 namespace tn {
 
@@ -40,7 +41,7 @@ constexpr int kABytes = kBM * kBK * 2;   // 16 KiB
 constexpr int kEpiSubs = 4;               // epilogue warps per TMEM lane quarter
 constexpr int kEpiWarps = 4 * kEpiSubs;
 constexpr int kGemmThreads = 32 * (2 + kEpiWarps);   // warp0 TMA, warp1 MMA + TMEM owner, the rest epilogue
-constexpr int kEpiBytesPerWarp = 6144;   // out block + two auxiliary blocks of 32 rows x 64 B
+constexpr int kEpiBytesPerWarp = gemm_epi::kBytesPerWarp;
 
 template <int kStages, int kHalves>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -210,174 +211,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       // row segments, eight rows per store instruction.
       uint8_t* smem_gen = smem_raw + (base - smem_u32(smem_raw));
       uint8_t* sm_out = smem_gen + (warp - 2) * kEpiBytesPerWarp;
-      uint8_t* sm_a0 = sm_out + 2048;
-      uint8_t* sm_a1 = sm_out + 4096;
-      const int n_store = p.n_store;
 #pragma unroll 1
       for (int half = 0; half < halves; ++half) {
-      const int row_base = m0 + half * kBM + q * 32;
-      const uint32_t tm_lane = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * 256);
-      const int lrow = lane >> 2, lpc = lane & 3;          // line-wise mapping: 4 lanes per row
-      const bool has_aux = p.mask_aux != nullptr || p.had_x0 != nullptr || p.had_xl != nullptr;
-      const bool has_bias = p.bias != nullptr, relu = p.relu != 0;
-      const int my_off = lane * 64;
-      const int my_sw = (lane >> 1) & 3;
-      if (!p.out_f32) {
-        for (int c0 = 32 * sub; c0 < BN; c0 += 32 * kEpiSubs) {
-          if (n0 + c0 >= n_store) break;                   // warp-uniform
-          if (has_aux) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int r = 8 * i + lrow;
-              const int grow = row_base + r, gcol = n0 + c0 + lpc * 8;
-              uint4 va = make_uint4(0u, 0u, 0u, 0u), vb = va;
-              if (grow < p.M && gcol + 8 <= p.ld_aux) {
-                const size_t off = (size_t)grow * p.ld_aux + gcol;
-                if (p.mask_aux) va = *reinterpret_cast<const uint4*>(p.mask_aux + off);
-                else {
-                  if (p.had_x0) va = *reinterpret_cast<const uint4*>(p.had_x0 + off);
-                  vb = *reinterpret_cast<const uint4*>(p.had_xl + off);
-                }
-              }
-              const int so = r * 64 + ((lpc ^ ((r >> 1) & 3)) << 4);
-              *reinterpret_cast<uint4*>(sm_a0 + so) = va;
-              if (!p.mask_aux) *reinterpret_cast<uint4*>(sm_a1 + so) = vb;
-            }
-            __syncwarp();
-          }
-          uint32_t acc[32];
-          tmem_ld16_nowait(tm_lane + (uint32_t)c0, acc);
-          if (c0 + 16 < BN) tmem_ld16_nowait(tm_lane + (uint32_t)(c0 + 16), acc + 16);
-          else {
-#pragma unroll
-            for (int j = 16; j < 32; ++j) acc[j] = 0u;
-          }
-          tmem_ld_wait();
-#pragma unroll
-          for (int pc = 0; pc < 4; ++pc) {
-            const int nb = n0 + c0 + pc * 8;
-            float v[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(acc[pc * 8 + j]);
-            if (has_bias) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) if (nb + j < p.N) v[j] += __ldg(p.bias + nb + j);
-            }
-            if (relu) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) v[j] = fmaxf(v[j], 0.f);
-            }
-            const int so = my_off + ((pc ^ my_sw) << 4);
-            if (has_aux) {
-              const uint4 a0 = *reinterpret_cast<const uint4*>(sm_a0 + so);
-              const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&a0);
-              if (p.mask_aux) {   // backward of ReLU: keep the gradient where the forward activation was positive
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                  const float2 m2 = __bfloat1622float2(h0[k]);
-                  if (!(m2.x > 0.f)) v[2 * k] = 0.f;
-                  if (!(m2.y > 0.f)) v[2 * k + 1] = 0.f;
-                }
-              } else {            // DCN-v2: x0 * (acc + bias) + xl, or just + xl when there is no x0
-                const uint4 a1 = *reinterpret_cast<const uint4*>(sm_a1 + so);
-                const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&a1);
-                if (p.aux_out) {  // keep u = acc + bias for the backward pass; this lane owns the slot it just read
-                  *reinterpret_cast<uint4*>(sm_a1 + so) =
-                      make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
-                }
-                if (p.had_x0) {
-#pragma unroll
-                  for (int k = 0; k < 4; ++k) {
-                    const float2 x0 = __bfloat1622float2(h0[k]), xl = __bfloat1622float2(h1[k]);
-                    v[2 * k] = x0.x * v[2 * k] + xl.x;
-                    v[2 * k + 1] = x0.y * v[2 * k + 1] + xl.y;
-                  }
-                } else {
-#pragma unroll
-                  for (int k = 0; k < 4; ++k) {
-                    const float2 xl = __bfloat1622float2(h1[k]);
-                    v[2 * k] += xl.x;
-                    v[2 * k + 1] += xl.y;
-                  }
-                }
-              }
-            }
-            if (nb + 8 > p.N) {   // only the piece that straddles N pays for the ones / padding columns
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const int n = nb + j;
-                if (n >= p.N) v[j] = (n == p.ones_col) ? 1.f : 0.f;
-              }
-            }
-            *reinterpret_cast<uint4*>(sm_out + so) =
-                make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
-          }
-          __syncwarp();
-          const int gcol = n0 + c0 + lpc * 8;
-          const bool col_ok = gcol < n_store && c0 + lpc * 8 < BN;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int r = 8 * i + lrow;
-            const int grow = row_base + r;
-            if (grow < p.M && col_ok) {
-              const int sl = r * 64 + ((lpc ^ ((r >> 1) & 3)) << 4);
-              const uint4 o = *reinterpret_cast<const uint4*>(sm_out + sl);
-              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)grow * p.ldc + gcol;
-              if (gcol + 8 <= n_store) {
-                *reinterpret_cast<uint4*>(dst) = o;
-              } else {
-                const __nv_bfloat16* ob = reinterpret_cast<const __nv_bfloat16*>(&o);
-                for (int j = 0; j < n_store - gcol; ++j) dst[j] = ob[j];
-              }
-              if (p.aux_out && gcol + 8 <= p.ld_aux)
-                *reinterpret_cast<uint4*>(p.aux_out + (size_t)grow * p.ld_aux + gcol) = *reinterpret_cast<const uint4*>(sm_a1 + sl);
-            }
-          }
-          __syncwarp();
-        }
-      } else {
-        for (int c0 = 16 * sub; c0 < BN; c0 += 16 * kEpiSubs) {
-          if (n0 + c0 >= n_store) break;                   // warp-uniform
-          uint32_t acc[16];
-          tmem_ld16_nowait(tm_lane + (uint32_t)c0, acc);
-          tmem_ld_wait();
-#pragma unroll
-          for (int pc = 0; pc < 4; ++pc) {
-            const int nb = n0 + c0 + pc * 4;
-            float v[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              v[j] = __uint_as_float(acc[pc * 4 + j]);
-              if (has_bias && nb + j < p.N) v[j] += __ldg(p.bias + nb + j);
-              if (relu) v[j] = fmaxf(v[j], 0.f);
-              if (nb + j >= p.N) v[j] = (nb + j == p.ones_col) ? 1.f : 0.f;
-            }
-            *reinterpret_cast<float4*>(sm_out + my_off + ((pc ^ my_sw) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
-          }
-          __syncwarp();
-          const int gcol = n0 + c0 + lpc * 4;
-          const bool col_ok = gcol < n_store && c0 + lpc * 4 < BN;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int r = 8 * i + lrow;
-            const int grow = row_base + r;
-            if (grow < p.M && col_ok) {
-              const float4 o = *reinterpret_cast<const float4*>(sm_out + r * 64 + ((lpc ^ ((r >> 1) & 3)) << 4));
-              float* dst = reinterpret_cast<float*>(p.C) + (size_t)grow * p.ldc + gcol;
-              if (gcol + 4 <= n_store) {
-                if (p.accumulate) red_add_f32x4(dst, o); else *reinterpret_cast<float4*>(dst) = o;
-              } else {
-                const float ov[4] = {o.x, o.y, o.z, o.w};
-                for (int j = 0; j < n_store - gcol; ++j) {
-                  if (p.accumulate) atomicAdd(dst + j, ov[j]); else dst[j] = ov[j];
-                }
-              }
-            }
-          }
-          __syncwarp();
-        }
+        const int row_base = m0 + half * kBM + q * 32;
+        const uint32_t tm_lane = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * 256);
+        gemm_epi::store_rows(p, tm_lane, row_base, n0, BN, sub, kEpiSubs, lane, sm_out);
       }
-      }   // halves
     }
   }
 
@@ -459,6 +298,10 @@ bool get_tensor_map(const void* ptr, long long rows, long long cols, long long l
   return true;
 }
 
+// gemm_2sm.cu: the persistent kernel on pairs of CTAs
+bool gemm_pair_supported(const GemmDesc& d, int BN, int splits);
+const char* gemm_bf16_pair(const GemmDesc& d, const GemmParams& p, int raster_group, cudaStream_t stream);
+
 const char* gemm_bf16(const GemmDesc& d, cudaStream_t stream) {
   if (d.M <= 0 || d.N <= 0 || d.K <= 0) return "gemm_bf16: empty problem";
   if ((reinterpret_cast<uintptr_t>(d.A) & 15) || (reinterpret_cast<uintptr_t>(d.B) & 15)) return "gemm_bf16: operands must be 16-byte aligned";
@@ -487,7 +330,17 @@ const char* gemm_bf16(const GemmDesc& d, cudaStream_t stream) {
   const bool may_split = d.out_f32 && d.accumulate;
   if (d.split_k > 1 && !may_split) return "gemm_bf16: split-K needs an fp32 accumulate epilogue";
   int BN = d.BN, splits = d.split_k;
+  // Compute-sized problems (several waves of 256 x 512 tiles, a long contraction, no split-K) go to the persistent
+  // kernel on pairs of CTAs (gemm_2sm.cu); m_halves == 4 asks for it whatever the size.
+  bool pair = false;
   {
+    const int bn_pair = d.BN > 0 ? d.BN : 512;
+    const long long tiles = (long long)((d.M + 2 * kBM - 1) / (2 * kBM)) * ((n_cover + bn_pair - 1) / bn_pair);
+    const bool sized = tiles >= 2 * 74 && kt_total >= 16;
+    pair = (d.m_halves == 4 || (d.m_halves == 0 && sized)) && d.split_k <= 1 && gemm_pair_supported(d, bn_pair, 1);
+    if (pair) { BN = bn_pair; splits = 1; }
+  }
+  if (!pair) {
     const int gran = d.b_mn ? 64 : 16;
     double best_cost = 1e30;
     int best_bn = 0, best_sp = 1;
@@ -508,30 +361,33 @@ const char* gemm_bf16(const GemmDesc& d, cudaStream_t stream) {
     BN = best_bn;
     splits = best_sp;
   }
-  if (BN % 16 || BN < 16 || BN > 256 || (d.b_mn && BN % 64)) return "gemm_bf16: bad tile N";
+  if (!pair && (BN % 16 || BN < 16 || BN > 256 || (d.b_mn && BN % 64))) return "gemm_bf16: bad tile N";
   if (splits < 1) splits = 1;
   if (splits > kt_total) splits = kt_total;
   int ktps = (kt_total + splits - 1) / splits;
   splits = (kt_total + ktps - 1) / ktps;
 
   CUtensorMap tmA, tmB;
-  bool ok;
-  if (!d.a_mn) ok = get_tensor_map(d.A, d.M, d.K, d.lda, kBM, &tmA);          // [M, K]
-  else         ok = get_tensor_map(d.A, d.K, d.M, d.lda, kBK, &tmA);          // [K, M]
-  if (!ok) return "gemm_bf16: cuTensorMapEncodeTiled failed for A";
-  if (!d.b_mn) ok = get_tensor_map(d.B, d.N, d.K, d.ldb, BN, &tmB);           // [N, K]
-  else         ok = get_tensor_map(d.B, d.K, d.N, d.ldb, kBK, &tmB);          // [K, N]
-  if (!ok) return "gemm_bf16: cuTensorMapEncodeTiled failed for B";
+  if (!pair) {       // the pair kernel makes its own (other box sizes)
+    bool ok;
+    if (!d.a_mn) ok = get_tensor_map(d.A, d.M, d.K, d.lda, kBM, &tmA);          // [M, K]
+    else         ok = get_tensor_map(d.A, d.K, d.M, d.lda, kBK, &tmA);          // [K, M]
+    if (!ok) return "gemm_bf16: cuTensorMapEncodeTiled failed for A";
+    if (!d.b_mn) ok = get_tensor_map(d.B, d.N, d.K, d.ldb, BN, &tmB);           // [N, K]
+    else         ok = get_tensor_map(d.B, d.K, d.N, d.ldb, kBK, &tmB);          // [K, N]
+    if (!ok) return "gemm_bf16: cuTensorMapEncodeTiled failed for B";
+  }
 
   // 256-row tiles pay off when the problem is compute-sized: several waves of full-width tiles, no split-K
-  int halves = d.m_halves;
+  int halves = pair ? 2 : d.m_halves;
+  if (halves == 4) halves = 0;         // the pair kernel was asked for but does not take this problem
   if (halves == 0) {
     const long long tiles256 = (long long)((d.M + 2 * kBM - 1) / (2 * kBM)) * ((n_cover + BN - 1) / BN);
     // measured on 8192 x 6416 x 6416: (K,K) 1087 -> 1313 TFLOP/s, (K,MN) 1000 -> 1327, (MN,MN) 962 -> 1238
     halves = (BN >= 128 && splits == 1 && tiles256 >= 3 * 148 && kt_total >= 16) ? 2 : 1;
   }
   if (halves != 1 && halves != 2) return "gemm_bf16: m_halves must be 1 or 2";
-  if (halves == 2 && BN > 256) return "gemm_bf16: bad tile N";
+  if (!pair && halves == 2 && BN > 256) return "gemm_bf16: bad tile N";
 
   GemmParams p;
   p.m_halves = halves;
@@ -548,6 +404,8 @@ const char* gemm_bf16(const GemmDesc& d, cudaStream_t stream) {
   p.aux_out = reinterpret_cast<__nv_bfloat16*>(d.aux_out);
   p.ld_aux = d.ld_aux; p.ones_col = d.ones_col; p.n_store = n_cover; p.bias = d.bias; p.status = d.status; p.prof = d.prof;
   p.gate_flags = d.gate_flags; p.gate_epoch = d.gate_epoch; p.gate_world = d.gate_world; p.gate_wait_ns = d.gate_wait_ns;
+
+  if (pair) return gemm_bf16_pair(d, p, p.raster_group, stream);
 
   dim3 grid((n_cover + BN - 1) / BN, (d.M + kBM * halves - 1) / (kBM * halves), splits);
   const size_t b_bytes = (size_t)BN * kBK * 2;

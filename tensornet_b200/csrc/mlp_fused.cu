@@ -42,41 +42,6 @@ constexpr int kMaxStages = 4;
 
 __device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpiWarps) : "memory"); }
 
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-// address of the same shared-memory location in CTA `rank` of this cluster
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_local_cluster(uint32_t addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cta.b64 _, [%0];" ::"r"(addr) : "memory");
-}
-// bounded wait that also acquires what the other CTA of the pair released
-__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* s_abort) {
-  for (unsigned spins = 0; spins < kWaitSpins; ++spins) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (ok) return true;
-    if ((spins & 255u) == 255u && *s_abort) return false;
-    if (spins > 64) __nanosleep(40);
-  }
-  return false;
-}
-
 struct ChainMaps {
   CUtensorMap in;                       // chain input [M, cols]
   CUtensorMap w[kMlpMaxLayers][2];      // weights of step i, as seen by CTA 0 / CTA 1 of a pair (box heights differ)

@@ -116,6 +116,74 @@ __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t* r) {
       : "r"(taddr));
 }
 
+
+// ---- thread-block clusters: distributed shared memory and barriers of the peer CTA --------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// address of the same shared-memory location in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_local_cluster(uint32_t addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cta.b64 _, [%0];" ::"r"(addr) : "memory");
+}
+// bounded wait that also acquires what the other CTA of the pair released
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* s_abort) {
+  for (unsigned spins = 0; spins < kWaitSpins; ++spins) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((spins & 255u) == 255u && *s_abort) return false;
+    if (spins > 64) __nanosleep(40);
+  }
+  return false;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// ---- tcgen05 with cta_group::2: one MMA over the tensor cores of a pair of CTAs (cluster ranks 2i, 2i+1) ------------
+// The even CTA of the pair issues the instruction.  A: each CTA's shared memory holds its own 128 rows; B: each CTA
+// holds half of the N columns; D: each CTA's TMEM receives its 128 rows of all N columns.  Descriptors carry
+// CTA-local shared-memory offsets, so both CTAs use the same layout.
+__device__ __forceinline__ void umma_f16_2sm(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum)
+      : "memory");
+}
+// Arrives, once all MMAs issued so far have completed, on one barrier given by its shared::cluster address (this
+// CTA's or, through map_to_cta, the other CTA's of the pair).  To release both CTAs, commit once per barrier.
+__device__ __forceinline__ void umma_commit_2sm(uint32_t bar_cluster) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster) : "memory");
+}
+// Tile load into this CTA's shared memory whose bytes are counted on a barrier that may live in the other CTA of
+// the pair (`bar_cluster`: a shared::cluster address, see map_to_cta).  One CTA's data only; nothing is replicated.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar_cluster) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster), "r"(x), "r"(y)
+      : "memory");
+}
+
 }  // namespace tc
 
 // 2-D bf16 row-major tensor [rows, cols] with leading dimension `ld` elements as a TMA descriptor whose box is

@@ -156,6 +156,7 @@ struct BnSyncView {
 };
 
 cudaError_t launch_dense_step(const DenseStepArgs& a, cudaStream_t st);
+int dense_step_ctas_per_sm();      // resident CTAs of the multi-GPU dense kernel per SM
 cudaError_t launch_sparse_pull(const PullArgs& args, int work_items, cudaStream_t stream);
 cudaError_t launch_sparse_push(const PushArgs& args, int work_items, int max_ctas, const DenseStepArgs* dense, cudaStream_t stream);
 

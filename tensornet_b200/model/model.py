@@ -268,19 +268,24 @@ class Model(nn.Module):
             tower = getattr(self, "first_dense_tower", None)
             if tower is not None and rt.on_gpu and rt.world > 1 and core.config.gate_first_gemm:
                 tower().weight_gate = optimizer.table.enable_gate()
-            # Several GPUs, small dense array: the dense step and the sparse push both wait on their peers, so they
-            # may only share the GPU if each fits beside the other whatever order the hardware picks.  The push
-            # gives up 8 SMs, the dense kernel takes at most 32 small CTAs (they fit on those 8 SMs); then neither
-            # can block the other from becoming resident and the two run side by side.
-            self._overlap_dense = bool(rt.on_gpu and rt.world > 1 and core.config.overlap_dense_push and
-                                       optimizer.table.n <= (4 << 20) and self.sparse_layers())
-            if rt.on_gpu and rt.world > 1 and core.config.dense_small_grid > 0 and optimizer.table.n <= (4 << 20):
+            # Several GPUs: the dense step and the sparse push both wait on their peers, so they may only share the
+            # GPU if each fits beside the other whatever order the hardware picks.  The push gives up some SMs and
+            # the dense kernel takes no more CTAs than those SMs hold; then neither can keep the other from
+            # becoming resident and the two run side by side on two streams.  Small arrays (<= 4 M elements) ride
+            # on the push kernel instead unless asked otherwise; large ones (a DCN-v2 cross tower: 130 M) are
+            # bound by NVLink, which a quarter of the SMs saturates.
+            small = optimizer.table.n <= (4 << 20)
+            mode = int(core.config.overlap_dense_push)
+            self._overlap_dense = bool(rt.on_gpu and rt.world > 1 and self.sparse_layers() and
+                                       (mode == 1 or (mode < 0 and not small)))
+            if rt.on_gpu and rt.world > 1 and core.config.dense_small_grid > 0 and small:
                 optimizer.table.limit_grid(core.config.dense_small_grid)
             if self._overlap_dense:
-                optimizer.table.limit_grid(32)
+                dense_sms = 12 if small else int(core.config.overlap_dense_sms)
+                optimizer.table.limit_grid_to_sms(dense_sms)
                 for layer in self.sparse_layers():
                     for lk in getattr(layer, "links", None) or [layer.link]:
-                        lk.push_cta_cap = 140
+                        lk.push_cta_cap = torch.cuda.get_device_properties(rt.device).multi_processor_count - dense_sms
         return self
 
     def sparse_layers(self):

@@ -125,6 +125,12 @@ class DenseTable:
         if runtime().on_gpu and self.initialized:
             self.ctx.set_max_ctas(int(max_ctas))
 
+    def limit_grid_to_sms(self, n_sms: int):
+        """Cap the multi-GPU dense kernel's grid at what ``n_sms`` SMs hold, so that all of it is resident beside a
+        kernel that leaves that many SMs free."""
+        if runtime().on_gpu and self.initialized:
+            self.ctx.set_max_ctas(int(n_sms) * int(_build.cuda_ext().dense_ctas_per_sm()))
+
     def set_lr(self, lr: float):
         if lr != self.lr:
             self.lr = float(lr)

@@ -152,6 +152,60 @@ def test_two_accumulator_tile(tn_gpu, status_ok, layout):
     assert _rel_err(C, ref) < 2e-2
 
 
+@pytest.mark.parametrize("layout", ["kk", "k_mn", "mn_mn"])
+@pytest.mark.parametrize("BN", [512, 256, 128])
+def test_pair_kernel_walks_several_tiles_per_cluster(tn_gpu, status_ok, layout, BN):
+    """The persistent kernel on pairs of CTAs (one tcgen05.mma over two SMs, double-buffered accumulator) against an
+    fp32 reference: more tiles than clusters, so every cluster walks two or three tiles through both accumulator
+    stages and around the operand ring; ragged last row tile, ragged last column tile, contraction not a multiple
+    of the stage depth."""
+    dev = tn_gpu.core.runtime().device
+    M, N, K = 4096 + 40, {512: 5120, 256: 2560, 128: 1280}[BN] + 64, 1000
+    g = torch.Generator().manual_seed(21)
+    st = tn_gpu.core.runtime().status
+    if layout == "kk":
+        A = torch.randn(M, K, generator=g).bfloat16().to(dev)
+        B = (torch.randn(N, K, generator=g) * 0.05).bfloat16().to(dev)
+        C = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+        _ext().gemm(A, B, C, M, N, K, K, K, N, False, False, False, False, None, None, None, None, 0, -1, N, 1, BN, st, m_halves=4)
+        ref = A.float() @ B.float().t()
+    elif layout == "k_mn":
+        A = torch.randn(M, K, generator=g).bfloat16().to(dev)
+        B = (torch.randn(K, N, generator=g) * 0.05).bfloat16().to(dev)          # [K, N]: N contiguous
+        C = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+        _ext().gemm(A, B, C, M, N, K, K, N, N, False, True, False, False, None, None, None, None, 0, -1, N, 1, BN, st, m_halves=4)
+        ref = A.float() @ B.float()
+    else:
+        A = torch.randn(K, M, generator=g).bfloat16().to(dev)                  # [K, M]: M contiguous
+        B = (torch.randn(K, N, generator=g) * 0.05).bfloat16().to(dev)
+        C = torch.ones(M, N, dtype=torch.float32, device=dev)
+        _ext().gemm(A, B, C, M, N, K, M, N, N, True, True, True, False, None, None, None, None, 0, -1, N, 1, BN, st, m_halves=4)
+        ref = A.float().t() @ B.float() + 1.0
+    torch.cuda.synchronize()
+    tn_gpu.core.runtime().check_status()
+    assert _rel_err(C, ref) < 2e-2
+
+
+@pytest.mark.parametrize("BN", [512, 256])
+def test_pair_kernel_hadamard_epilogue(tn_gpu, status_ok, BN):
+    """The DCN-v2 cross-layer epilogue (bias, pre-activation kept, x0 * u + xl) through the pair kernel."""
+    dev = tn_gpu.core.runtime().device
+    M, N, K = 1024 + 24, 768 + 16, 448
+    g = torch.Generator(device="cpu").manual_seed(10)
+    A = torch.randn(M, K, generator=g).bfloat16().to(dev)
+    B = (torch.randn(N, K, generator=g) * 0.05).bfloat16().to(dev)
+    bias = torch.randn(N, generator=g).to(dev)
+    x0 = torch.randn(M, N, generator=g).bfloat16().to(dev)
+    xl = torch.randn(M, N, generator=g).bfloat16().to(dev)
+    st = tn_gpu.core.runtime().status
+    C = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    U = torch.full((M, N), 7.0, dtype=torch.bfloat16, device=dev)
+    _ext().gemm(A, B, C, M, N, K, K, K, N, False, False, False, False, bias, None, x0, xl, N, -1, N, 1, BN, st, m_halves=4, aux_out=U)
+    u_ref = A.float() @ B.float().t() + bias
+    assert _rel_err(U, u_ref) < 2e-2
+    assert _rel_err(C, x0.float() * u_ref + xl.float()) < 2e-2
+
+
 def test_hadamard_epilogue_keeps_pre_activation_and_residual_mode(tn_gpu, status_ok):
     """aux_out receives u = A . B^T + bias next to y = x0 * u + xl; without x0 the epilogue is a plain residual add."""
     dev = tn_gpu.core.runtime().device
