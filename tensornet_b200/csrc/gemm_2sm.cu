@@ -10,11 +10,11 @@
 //     drain tile i while the MMAs of tile i+1 run;
 //   * BN = 512: two MMAs per contraction step (columns 0-255 and 256-511) share each A tile and fill all 512 TMEM
 //     columns.  A 256 x 512 tile reads a quarter fewer operand bytes per FLOP than 256 x 256, and this kernel family is
-//     bound by the rate at which L2 feeds the SMs (8192 x 6416 x 6416: 5.5 GB of tile loads per launch at 256 x 256,
-//     about 10 TB/s whichever kernel runs it).  The epilogue (twelve warps) is then not overlapped, but the operand
-//     ring refills for the next tile while it runs.  Measured on that shape, forward / dgrad / wgrad: 486 / 484 /
-//     512 us against 497 / 504 / 535 for the one-CTA 256 x 256 tile and 551 / 550 / 597 for the pair's 256 x 256 tile
-//     (library GEMM: 456);
+//     bound by the rate at which one SM takes in operand tiles: on 8192 x 6416 x 6416 both tile shapes (and the one-CTA
+//     256 x 256 tile) settle at about 72 GB/s per SM, 10.6 TB/s over the chip, with the tensor pipe 77 % busy.  The
+//     epilogue is then not overlapped (8 us per tile), but the operand ring refills for the next tile while it runs.
+//     Measured on that shape, forward / dgrad / wgrad: 481 / 481 / 512 us against 497 / 504 / 535 for the one-CTA
+//     256 x 256 tile and 551 / 550 / 597 for the pair's 256 x 256 tile (library GEMM: 455);
 //   * the pair walks the tile list (static round-robin over the clusters, same L2-friendly raster as the one-CTA
 //     kernel), so barrier set-up, TMEM allocation and the pipeline fill are paid once per launch, not per tile.
 // Operand layouts, epilogues and error handling are those of gemm_tcgen05.cu (the epilogue code is shared).
@@ -42,6 +42,7 @@ constexpr int kNBlockBytes = 128 * kBK * 2;   // this CTA's half (128 columns) o
 
 struct PairTiles {
   int tiles_m, tiles_n, raster_group;
+  int epi_bytes_per_warp;      // 2 KiB (transpose block only) or gemm_epi::kBytesPerWarp (plus the auxiliary operand blocks)
 };
 
 __device__ __forceinline__ void tile_of(const PairTiles& g, int t, int* tile_m, int* tile_n) {
@@ -211,7 +212,7 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     // ------------------------------- epilogue (both CTAs, kEpiW / 4 warps per TMEM lane quarter) --
     const int q = warp & 3;
     const int sub = (warp - 2) >> 2;
-    uint8_t* sm_out = smem_raw + (base - smem_u32(smem_raw)) + epi_smem_off + (warp - 2) * gemm_epi::kBytesPerWarp;
+    uint8_t* sm_out = smem_raw + (base - smem_u32(smem_raw)) + epi_smem_off + (warp - 2) * g.epi_bytes_per_warp;
     const uint32_t acc_empty_even = map_to_cta(smem_u32(&s_acc_empty[0]), 0);
     uint32_t lt = 0;
     bool ok = true;
@@ -262,14 +263,14 @@ template <int kNB, int kStages, int kEpiW>
 cudaError_t launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, const PairTiles& g, int clusters,
                         cudaStream_t stream) {
   const int BN = p.BN;
-  const size_t smem = (size_t)kStages * (kABytes + (size_t)(BN / 2) * kBK * 2) + kEpiW * gemm_epi::kBytesPerWarp + 1024;
+  const size_t smem = (size_t)kStages * (kABytes + (size_t)(BN / 2) * kBK * 2) + (size_t)kEpiW * g.epi_bytes_per_warp + 1024;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_2sm_kernel<kNB, kStages, kEpiW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_2sm_kernel<kNB, kStages, kEpiW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  if (smem > 225 * 1024) return cudaErrorInvalidValue;
+  if (smem > 226 * 1024) return cudaErrorInvalidValue;
   static const bool use_pdl = []() { const char* e = getenv("TN_PDL"); return e == nullptr || atoi(e) != 0; }();
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(2 * clusters));
@@ -314,8 +315,14 @@ const char* gemm_bf16_pair(const GemmDesc& d, const GemmParams& p_in, int raster
   long long clusters = (long long)g.tiles_m * g.tiles_n;
   if (clusters > sms / 2) clusters = sms / 2;
   if (clusters < 1) clusters = 1;
-  const cudaError_t e = BN == 512 ? launch_pair<2, 3, 12>(tmA, tmB, p, g, (int)clusters, stream)
-                                  : launch_pair<1, 6, 4>(tmA, tmB, p, g, (int)clusters, stream);
+  // Epilogues that read auxiliary operands (ReLU mask, Hadamard / residual step) need 6 KiB of shared memory per
+  // epilogue warp, the others 2 KiB: those afford a fourth operand stage and four more epilogue warps at BN = 512.
+  const bool has_aux = d.mask_aux != nullptr || d.had_x0 != nullptr || d.had_xl != nullptr;
+  g.epi_bytes_per_warp = has_aux ? gemm_epi::kBytesPerWarp : 2048;
+  cudaError_t e;
+  if (BN == 512) e = has_aux ? launch_pair<2, 3, 12>(tmA, tmB, p, g, (int)clusters, stream)
+                             : launch_pair<2, 4, 16>(tmA, tmB, p, g, (int)clusters, stream);
+  else { g.epi_bytes_per_warp = gemm_epi::kBytesPerWarp; e = launch_pair<1, 6, 4>(tmA, tmB, p, g, (int)clusters, stream); }
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
 
