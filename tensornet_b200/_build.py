@@ -8,6 +8,11 @@ Two shared objects are produced under ``tensornet_b200/_ext``:
 * ``_tn_cpu``  - the plain C++ restatement of the reference's parameter-server algorithms
   (CPU oracle and CPU execution path) and the checkpoint reader/writer.
 
+With ``TN_CPU_SANITIZE=1`` the C++ runtime is built a second time as ``_tn_cpu_san`` with AddressSanitizer and
+UndefinedBehaviorSanitizer and used in place of ``_tn_cpu`` (run Python with the ASan runtime preloaded:
+``LD_PRELOAD=$(gcc -print-file-name=libasan.so) ASAN_OPTIONS=detect_leaks=0``); the CI job ``cpu-sanitizers`` runs the
+table, checkpoint and streaming tests that way.
+
 A built ``.so`` is loaded directly when the digest of the sources it was built from (kept next
 to it) still matches ``csrc``; otherwise it is rebuilt first, so an edited kernel can never run
 as its previous build.
@@ -74,10 +79,12 @@ def _build(name: str, sources, cuda: bool, verbose: bool = False):
     os.makedirs(os.path.join(_EXT, name), exist_ok=True)
     os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0a")
     os.environ.setdefault("MAX_JOBS", str(os.cpu_count() or 4))
+    sanitize = name.endswith("_san")
     kwargs = dict(
         name=name,
         sources=sources,
-        extra_cflags=["-O3", "-std=c++17"],
+        extra_cflags=(["-O1", "-g", "-std=c++17", "-fsanitize=address,undefined", "-fno-omit-frame-pointer"] if sanitize
+                      else ["-O3", "-std=c++17"]),
         extra_include_paths=[_CSRC],
         build_directory=os.path.join(_EXT, name),
         verbose=verbose,
@@ -87,7 +94,7 @@ def _build(name: str, sources, cuda: bool, verbose: bool = False):
         kwargs["with_cuda"] = True
         kwargs["extra_ldflags"] = ["-lcuda"] if _has_libcuda() else []
     else:
-        kwargs["extra_ldflags"] = ["-lz"]
+        kwargs["extra_ldflags"] = ["-lz"] + (["-fsanitize=address,undefined"] if sanitize else [])
     mod = cpp_extension.load(**kwargs)
     with open(_digest_path(name), "w") as f:
         f.write(_digest(sources))
@@ -163,4 +170,6 @@ def cuda_ext():
 
 
 def cpu_ext():
+    if os.environ.get("TN_CPU_SANITIZE", "") not in ("", "0"):
+        return load("_tn_cpu_san")
     return load("_tn_cpu")

@@ -71,3 +71,44 @@ def start_as_current_span(name: str):
     finally:
         if nvtx is not None:
             nvtx.range_pop()
+
+
+class _NoRange:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_RANGE = _NoRange()
+
+
+class _NvtxRange:
+    def __init__(self, name):
+        self.name = name
+
+    def __enter__(self):
+        import torch
+
+        torch.cuda.nvtx.range_push(self.name)
+
+    def __exit__(self, *exc):
+        import torch
+
+        torch.cuda.nvtx.range_pop()
+        return False
+
+
+def phase(name: str):
+    """NVTX range around one phase of a training step (sparse pull, forward, backward, sparse push, dense step) when
+    ``TN_NVTX_PHASES=1``; a no-op object otherwise, so the hot loop pays one attribute test.  The ranges show in a
+    timeline of the eager steps (the first steps of a run, ``cuda_graph=False``, or ``ProfileBatches``); a replayed
+    CUDA graph is one launch and has no host-side phases."""
+    from .core import config
+
+    if not config.nvtx_phases:
+        return _NO_RANGE
+    import torch
+
+    return _NvtxRange(name) if torch.cuda.is_available() else _NO_RANGE

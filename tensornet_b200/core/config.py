@@ -47,6 +47,7 @@ class Config:
     #: 2 GPUs on the DeepFM step, side by side was 2 % slower than back to back), 0 = never, 1 = always
     overlap_dense_push: int = -1
     overlap_dense_sms: int = 40    # SMs the push leaves to a large dense step
+    nvtx_phases: bool = False      # NVTX ranges around the phases of an eager training step
     #: multi-GPU, dense arrays up to 4 M elements: the dense step runs on a few CTAs of the last sparse push kernel of
     #: the step instead of in a kernel of its own behind it
     dense_rides_push: bool = True
@@ -86,6 +87,7 @@ class Config:
         c.dense_small_grid = _env("TN_DENSE_SMALL_GRID", c.dense_small_grid, int)
         c.overlap_dense_push = _env("TN_OVERLAP_DENSE_PUSH", c.overlap_dense_push, int)
         c.overlap_dense_sms = _env("TN_OVERLAP_DENSE_SMS", c.overlap_dense_sms, int)
+        c.nvtx_phases = _env("TN_NVTX_PHASES", c.nvtx_phases, bool)
         c.dense_rides_push = _env("TN_DENSE_RIDES_PUSH", c.dense_rides_push, bool)
         c.checkpoint_chunk_rows = _env("TN_CKPT_CHUNK_ROWS", c.checkpoint_chunk_rows, int)
         c.checkpoint_load_chunk_rows = _env("TN_CKPT_LOAD_CHUNK_ROWS", c.checkpoint_load_chunk_rows, int)

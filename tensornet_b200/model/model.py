@@ -23,7 +23,7 @@ import torch
 from torch import nn
 
 from .. import core, metric as _metric
-from .._opentelemetry import start_as_current_span
+from .._opentelemetry import phase, start_as_current_span
 from ..data.features import PackedFeatures, Ragged
 from ..ops import functional as F
 from ..parallel.symm import verify_all_arenas
@@ -310,15 +310,17 @@ class Model(nn.Module):
             if loss is not None:
                 self._loss_steps += 1
         if loss is None:
-            logits = self(features)
-            loss, pred = self._loss(logits, labels)
+            with phase("tn.forward"):
+                logits = self(features)
+                loss, pred = self._loss(logits, labels)
             for m in self._host_metrics:
                 m.update_state(labels, pred)
         rt = core.runtime()
-        if rt.on_gpu and loss.dim() == 0 and loss.dtype == torch.float32:
-            loss.backward(self._unit_grad)      # a resident 1.0: autograd would otherwise launch a fill kernel for it
-        else:
-            loss.backward()
+        with phase("tn.backward"):
+            if rt.on_gpu and loss.dim() == 0 and loss.dtype == torch.float32:
+                loss.backward(self._unit_grad)      # a resident 1.0: autograd would otherwise launch a fill kernel for it
+            else:
+                loss.backward()
         if rt.on_gpu and rt.world == 1 and self.optimizer is not None:
             # one GPU: the sparse push and the dense update touch disjoint state and neither waits on other
             # CTAs, so they run side by side

@@ -17,6 +17,7 @@ import torch
 import torch.distributed as dist
 
 from .. import _build
+from .._opentelemetry import phase
 from ..core.config import config
 from ..core.optimizers import KIND_ADAGRAD, KIND_ADAM, OptimizerBase
 from ..core.runtime import runtime
@@ -143,7 +144,8 @@ class DenseTable:
         rt = runtime()
         self.step_count += 1
         if rt.on_gpu:
-            self.ctx.step(bool(peers_past_backward and self.world > 1))
+            with phase("tn.dense_step"):
+                self.ctx.step(bool(peers_past_backward and self.world > 1))
             return
         with torch.no_grad():
             if self.world > 1:

@@ -17,6 +17,7 @@ import numpy as np
 import torch
 
 from .. import _build
+from .._opentelemetry import phase
 from ..core.config import config
 from ..core.optimizers import KIND_ADAGRAD, KIND_ADAM, KIND_FTRL, OptimizerBase
 from ..core.runtime import runtime
@@ -339,13 +340,15 @@ class GpuSparseLink:
         if inverse is None:
             inverse = torch.empty(n, dtype=torch.int32, device=self.dev)
         self._last_n_ids = n
-        self.ctx.pull(ids.reshape(-1), inverse, labels, int(label_mod), bool(training), bool(lookup_only))
+        with phase("tn.sparse_pull"):
+            self.ctx.pull(ids.reshape(-1), inverse, labels, int(label_mod), bool(training), bool(lookup_only))
         return inverse
 
     def push(self):
         """Apply the accumulated unique-row gradients (``self.gU``) on the owning GPUs."""
         rider, self.dense_rider = self.dense_rider, None
-        self.ctx.push(max(self._last_n_ids, 1), int(self.push_cta_cap), rider.ctx if rider is not None else None)
+        with phase("tn.sparse_push+dense_step" if rider is not None else "tn.sparse_push"):
+            self.ctx.push(max(self._last_n_ids, 1), int(self.push_cta_cap), rider.ctx if rider is not None else None)
         if self.table.world > 1:
             runtime().peer_synced_pushes += 1      # this kernel waited for every peer's gradient records
 
