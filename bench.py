@@ -280,9 +280,14 @@ def main():
         return {tn.data.PACKED_KEY: tn.data.PackedFeatures(slots, ids=ids), "dense": dense}
 
     # ---------------- warm-up (eager steps, graph capture, a few replays) ----------------
-    for k in range(args.warmup + 4):
+    def dev_step(k):
+        # the step on batch k; naming batch k+1 lets the captured step start that batch's dedup and id dispatch ahead
         i, d, l = dev_batch(k)
-        model.train_on_batch(feats(i, d), l)
+        i2, d2, l2 = dev_batch(k + 1)
+        return model.train_on_batch(feats(i, d), l, next_batch=(feats(i2, d2), l2))
+
+    for k in range(args.warmup + 4):
+        dev_step(k)
     # the end-to-end path (Model.fit: overlapped input copies, pinned loss buffers) gets its warm-up too
     model.fit(((feats(*host_batch(k)[:2]), host_batch(k)[2]) for k in range(args.warmup)), epochs=1, record_step_loss=True)
     torch.cuda.synchronize()
@@ -292,8 +297,7 @@ def main():
         per_step_launches = model._launches_per_step
     else:
         c0 = ext.launch_count()
-        i, d, l = dev_batch(0)
-        model.train_on_batch(feats(i, d), l)
+        dev_step(0)
         per_step_launches = ext.launch_count() - c0
     torch.cuda.synchronize()
 
@@ -309,13 +313,12 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX, group=rt.host_group)
         return t.tolist()
 
-    step_no = [0]
+    step_no = [args.warmup + 4]
 
     def device_block():
         for _ in range(K):
-            i, d, l = dev_batch(step_no[0])
+            dev_step(step_no[0])
             step_no[0] += 1
-            model.train_on_batch(feats(i, d), l)
 
     # calibration block (also warm-up): how many blocks make up the minimum timed duration
     rt.barrier()
@@ -421,7 +424,7 @@ def main():
                        "table_rows_resident": rows_all, "table_rows_this_gpu": rows_here,
                        "key_array_load_factor": rows_here / table.keys.numel(), "table_fill_seconds": t_fill,
                        "l2": f"no flush: every step draws fresh ids (pool of {pool} batches) against {rows_here * table.stride * 4 / 1e9:.1f} GB of rows per GPU, far beyond L2",
-                       "cuda_graph": graphed, "linear_weights": "stored in the embedding rows (one table)" if model.share_linear_table else "separate dim-1 table", "last_loss": last,
+                       "cuda_graph": graphed, "pull_front_ahead": bool(getattr(model, "_rings", None)), "linear_weights": "stored in the embedding rows (one table)" if model.share_linear_table else "separate dim-1 table", "last_loss": last,
                        "dense_multimem": bool(getattr(model.optimizer.table, "uses_multimem", False))},
             "clocks": clocks,
             "e2e": {"value": e2e, "unit": "examples/s", "ms_per_step": e2e_med / K, "h2d_bytes_per_step": h2d,

@@ -48,6 +48,12 @@ class Config:
     overlap_dense_push: int = -1
     overlap_dense_sms: int = 40    # SMs the push leaves to a large dense step
     nvtx_phases: bool = False      # NVTX ranges around the phases of an eager training step
+    #: replayed steps stage their inputs and read their loss back through one native call each instead of Python-level
+    #: stream / event / copy calls
+    native_step_path: bool = True
+    #: when the caller names the batch of the following step (`fit` does), its dedup and id dispatch run on a second
+    #: stream under the current step's forward / backward, and the pull of that step only probes and returns rows
+    pull_front_ahead: bool = True
     #: multi-GPU, dense arrays up to 4 M elements: the dense step runs on a few CTAs of the last sparse push kernel of
     #: the step instead of in a kernel of its own behind it
     dense_rides_push: bool = True
@@ -88,6 +94,8 @@ class Config:
         c.overlap_dense_push = _env("TN_OVERLAP_DENSE_PUSH", c.overlap_dense_push, int)
         c.overlap_dense_sms = _env("TN_OVERLAP_DENSE_SMS", c.overlap_dense_sms, int)
         c.nvtx_phases = _env("TN_NVTX_PHASES", c.nvtx_phases, bool)
+        c.native_step_path = _env("TN_NATIVE_STEP_PATH", c.native_step_path, bool)
+        c.pull_front_ahead = _env("TN_PULL_FRONT_AHEAD", c.pull_front_ahead, bool)
         c.dense_rides_push = _env("TN_DENSE_RIDES_PUSH", c.dense_rides_push, bool)
         c.checkpoint_chunk_rows = _env("TN_CKPT_CHUNK_ROWS", c.checkpoint_chunk_rows, int)
         c.checkpoint_load_chunk_rows = _env("TN_CKPT_LOAD_CHUNK_ROWS", c.checkpoint_load_chunk_rows, int)

@@ -2,6 +2,7 @@
 // Storage is owned by torch tensors created on the Python side; the objects here only keep
 // raw device pointers (plus a reference to the tensors) so a kernel launch costs one call.
 #include <torch/extension.h>
+#include <ATen/cuda/CachingHostAllocator.h>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <cuda_runtime.h>
@@ -161,7 +162,23 @@ struct SparseCtx {
   // The shard's arrays were replaced (growth, compaction): launches already recorded in CUDA graphs pick the new ones up.
   void set_table(py::dict table) { keep["table"] = table; t = table_from_dict(table); upload_table(); }
 
-  void pull(at::Tensor ids, at::Tensor inverse, c10::optional<at::Tensor> labels, int label_mod, bool training, bool lookup_only) {
+  // Dedup, id dispatch and inverse map of a batch ahead of its pull (plain kernels on the current stream).
+  void front(at::Tensor ids, at::Tensor inverse) {
+    TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous(), "ids: contiguous int64 CUDA tensor");
+    TORCH_CHECK(inverse.scalar_type() == at::kInt && inverse.numel() >= ids.numel(), "inverse: int32, one per id");
+    c10::cuda::CUDAGuard guard(ids.device());
+    tn::PullArgs a{};
+    a.c = c; a.tbl = t; a.opt = o;
+    a.ids = ptr_of<const long long>(ids);
+    a.n_ids = (int)ids.numel();
+    a.inverse = ptr_of<int>(inverse);
+    a.training = 1;
+    check(tn::launch_sparse_pull_front(a, cur_stream()), "sparse_pull_front launch");
+    g_launches.fetch_add(1, std::memory_order_relaxed);      // two kernels
+  }
+
+  void pull(at::Tensor ids, at::Tensor inverse, c10::optional<at::Tensor> labels, int label_mod, bool training, bool lookup_only,
+            bool front_done) {
     TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous(), "ids: contiguous int64 CUDA tensor");
     TORCH_CHECK(inverse.scalar_type() == at::kInt && inverse.numel() >= ids.numel(), "inverse: int32, one per id");
     c10::cuda::CUDAGuard guard(ids.device());
@@ -176,6 +193,7 @@ struct SparseCtx {
     a.training = training ? 1 : 0;
     a.lookup_only = lookup_only ? 1 : 0;
     TORCH_CHECK(!(training && lookup_only), "a training pull creates rows; lookup_only is for inference");
+    a.front_done = front_done ? 1 : 0;
     a.lanes = pull_lanes;
     a.tile_rows = tile_rows;
     long long work = (long long)a.n_ids * (pull_lanes > 4 ? pull_lanes / 2 : 2);
@@ -403,12 +421,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("set_opt", &SparseCtx::set_opt)
       .def("set_table", &SparseCtx::set_table)
       .def("pull", &SparseCtx::pull, py::arg("ids"), py::arg("inverse"), py::arg("labels"), py::arg("label_mod"), py::arg("training"),
-           py::arg("lookup_only") = false)
+           py::arg("lookup_only") = false, py::arg("front_done") = false)
       .def("push", [](SparseCtx& self, int64_t work_hint, int max_ctas, py::object dense) {
         if (dense.is_none()) { self.push(work_hint, max_ctas, nullptr); return; }
         const tn::DenseStepArgs d = dense.cast<DenseCtx&>().rider_args();
         self.push(work_hint, max_ctas, &d);
-      }, py::arg("work_hint"), py::arg("max_ctas") = 0, py::arg("dense") = py::none());
+      }, py::arg("work_hint"), py::arg("max_ctas") = 0, py::arg("dense") = py::none())
+      .def("front", &SparseCtx::front, py::arg("ids"), py::arg("inverse"));
   py::class_<BnCtx>(m, "BnCtx")
       .def(py::init<py::dict>())
       .def("push", &BnCtx::push)
@@ -455,6 +474,45 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("gate_flags") = py::none(), py::arg("gate_epoch") = py::none(), py::arg("gate_world") = 0, py::arg("gate_wait_ns") = 0,
         py::arg("m_halves") = 0, py::arg("aux_out") = py::none());
   m.def("launch_count", []() { return g_launches.load(); });
+
+  // ---- per-step host path of a replayed training step --------------------------------------------
+  // One call instead of a dozen Python-level stream / event / copy calls: wait (on the copy stream) until the replay
+  // that last read these input buffers is over, copy the step's inputs host -> device, record their arrival and make
+  // the compute stream wait for it.  Streams and events come as the handles torch exposes (cuda_stream, cuda_event).
+  m.def("stage_inputs", [](std::vector<at::Tensor> dsts, std::vector<at::Tensor> srcs, int64_t copy_stream, int64_t main_stream,
+                           int64_t done_event, int64_t copied_event, int64_t read_event) {
+    TORCH_CHECK(dsts.size() == srcs.size(), "stage_inputs: one source per destination");
+    cudaStream_t cs = reinterpret_cast<cudaStream_t>(copy_stream), ms = reinterpret_cast<cudaStream_t>(main_stream);
+    if (done_event) check(cudaStreamWaitEvent(cs, reinterpret_cast<cudaEvent_t>(done_event), 0), "cudaStreamWaitEvent");
+    // the loss of the step that last used this buffer set has been read back (it lives in the same captured memory)
+    if (read_event) check(cudaStreamWaitEvent(cs, reinterpret_cast<cudaEvent_t>(read_event), 0), "cudaStreamWaitEvent");
+    for (size_t i = 0; i < dsts.size(); ++i) {
+      const at::Tensor& d = dsts[i];
+      const at::Tensor& h = srcs[i];
+      TORCH_CHECK(d.is_cuda() && !h.is_cuda() && d.is_contiguous() && h.is_contiguous() && d.nbytes() == h.nbytes() &&
+                      d.scalar_type() == h.scalar_type(),
+                  "stage_inputs: leaf ", i, " must be a contiguous host tensor of the static buffer's type and size");
+      check(cudaMemcpyAsync(d.data_ptr(), h.data_ptr(), d.nbytes(), cudaMemcpyHostToDevice, cs), "cudaMemcpyAsync");
+      // a page-locked source from torch's host allocator must not be handed out again before the copy has run
+      // (what Tensor.copy_(non_blocking=True) does behind the scenes); a no-op for other host memory
+      if (h.is_pinned())
+        at::getHostAllocator(at::kCUDA)->record_event(h.data_ptr(), h.storage().data_ptr().get_context(),
+                                                      c10::cuda::getStreamFromExternal(cs, d.device().index()).unwrap());
+    }
+    check(cudaEventRecord(reinterpret_cast<cudaEvent_t>(copied_event), cs), "cudaEventRecord");
+    check(cudaStreamWaitEvent(ms, reinterpret_cast<cudaEvent_t>(copied_event), 0), "cudaStreamWaitEvent");
+  });
+  // 4-byte device scalar -> slot of a pinned ring, then an event behind it (the loss of a step on its way to the host)
+  // `wait_event` != 0: the copy runs on a stream of its own behind that event (the end of the step), so the compute
+  // stream carries nothing between two replayed steps.
+  m.def("read_scalar_async", [](at::Tensor pinned, int64_t slot, at::Tensor src, int64_t stream, int64_t event, int64_t wait_event) {
+    TORCH_CHECK(!pinned.is_cuda() && pinned.scalar_type() == at::kFloat && slot >= 0 && slot < pinned.numel(), "bad ring slot");
+    TORCH_CHECK(src.is_cuda() && src.scalar_type() == at::kFloat && src.numel() == 1, "source: one float on the device");
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    if (wait_event) check(cudaStreamWaitEvent(st, reinterpret_cast<cudaEvent_t>(wait_event), 0), "cudaStreamWaitEvent");
+    check(cudaMemcpyAsync(pinned.data_ptr<float>() + slot, src.data_ptr(), sizeof(float), cudaMemcpyDeviceToHost, st), "cudaMemcpyAsync");
+    check(cudaEventRecord(reinterpret_cast<cudaEvent_t>(event), st), "cudaEventRecord");
+  });
 
   // ---- CUDA IPC peer memory (fallback transport for the symmetric heap) --------------------------
   m.def("ipc_alloc", [](int64_t nbytes) {

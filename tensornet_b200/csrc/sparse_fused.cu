@@ -174,9 +174,32 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_pull_fused_kernel(const __
   const int dim = t.dim;
   const bool need_ou = a.training && W > 1;
 
-  if (tid == 0) *c.ocount = 0;
+  const bool front_done = a.front_done != 0;     // dedup, id dispatch and inverse map already ran (pull_front_*)
+  if (tid == 0 && !front_done) *c.ocount = 0;    // (with the front ahead, the push of the previous step re-armed it)
   prof_mark(c, 0);
 
+  if (front_done) {
+    // show / click counts of the batch into the gradient records (the front runs while the previous step's records
+    // are still in use, so it leaves them alone)
+    if (a.training) {
+      for (int base = tid - lane; base < a.n_ids; base += nth) {
+        const int i = base + lane;
+        const bool valid = i < a.n_ids;
+        const int v = valid ? a.inverse[i] : -1;
+        const unsigned same = __match_any_sync(0xffffffffu, (valid && v >= 0) ? v : -2 - lane);
+        if (valid && v >= 0) {
+          float* rec = c.cnts + 2 * (size_t)v;
+          if (lane == __ffs(same) - 1) atomicAdd(rec, (float)__popc(same));
+          if (a.labels != nullptr) {
+            float y = a.label_mod > 0 ? a.labels[i % a.label_mod] : a.labels[i];
+            if (y != 0.f) atomicAdd(rec + 1, y);
+          }
+        }
+      }
+    }
+    prof_mark(c, 1);
+    prof_mark(c, 2);
+  } else {
   // ---- phase A: dedup; first occurrence of a sign allocates a slot in its owner's segment --------
   for (int base = tid - lane; base < a.n_ids; base += nth) {
     const int i = base + lane;
@@ -278,6 +301,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_pull_fused_kernel(const __
   }
   gs.arrive();       // this CTA no longer reads the dedup scratch; phase C waits for all of them before clearing it
   prof_mark(c, 2);
+  }
 
   // ---- phase B: as owner, probe / insert every requested sign and return its row ----------------------
   // A warp takes 32 requests at a time: every lane probes (or inserts) one sign, then the warp's lane groups
@@ -508,10 +532,12 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_pull_fused_kernel(const __
       c.cnt[threadIdx.x] = 0;
       if (threadIdx.x != R) st_release_sys_u64(sig_word(c.sig[threadIdx.x], kSigPullDone, R), epoch << 32);
     }
-    if (!gs.wait(4)) goto done;      // every CTA has finished its inverse map (it arrived before phase B)
-    ulonglong2* kk = reinterpret_cast<ulonglong2*>(c.dd_keys);
-    const int n2 = (int)((c.dd_mask + 1u) >> 1);
-    for (int i = tid; i < n2; i += nth) kk[i] = make_ulonglong2(kEmptyKey, kEmptyKey);
+    if (!front_done) {
+      if (!gs.wait(4)) goto done;      // every CTA has finished its inverse map (it arrived before phase B)
+      ulonglong2* kk = reinterpret_cast<ulonglong2*>(c.dd_keys);
+      const int n2 = (int)((c.dd_mask + 1u) >> 1);
+      for (int i = tid; i < n2; i += nth) kk[i] = make_ulonglong2(kEmptyKey, kEmptyKey);
+    }
     if (W > 1 && blockIdx.x == 0 && threadIdx.x < W && threadIdx.x != R) {
       unsigned long long v;
       wait_flag_ge(sig_word(c.sig[R], kSigPullDone, threadIdx.x), epoch, &v, c.wait_ns, c.status, 6, threadIdx.x);
@@ -523,6 +549,116 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_pull_fused_kernel(const __
 
 done:
   gs.leave();
+}
+
+// =======================================================================================
+// pull front: phases A and A2 of the pull (without the show / click counts) as two ordinary kernels.  They need
+// only the ids of a batch, so they can run on a second stream while the previous step's forward and backward
+// passes run; their CTAs are small and fit beside the GEMM CTAs.  `c.bar[4]` counts the CTAs of the second kernel
+// (the cooperative kernels of the same link use bar[0..3] and may run at the same time).
+// =======================================================================================
+constexpr int kFrontThreads = 256;
+
+__global__ void __launch_bounds__(kFrontThreads) pull_front_dedup_kernel(const __grid_constant__ PullArgs a) {
+  const SparseCommView& c = a.c;
+  if (ld_volatile_s32(c.status) != 0) return;
+  const int tid = blockIdx.x * blockDim.x + threadIdx.x;
+  const int nth = gridDim.x * blockDim.x;
+  const int lane = threadIdx.x & 31;
+  const int W = c.world, capo = c.capo;
+  for (int base = tid - lane; base < a.n_ids; base += nth) {
+    const int i = base + lane;
+    bool winner = false;
+    unsigned hw = 0;
+    unsigned long long key = kEmptyKey;
+    if (i < a.n_ids) key = canon_key((unsigned long long)a.ids[i]);
+    const unsigned same = __match_any_sync(0xffffffffu, key);
+    if (i < a.n_ids && lane == __ffs(same) - 1) {
+      unsigned h = (unsigned)mix64(key ^ 0x2545F4914F6CDD1Dull) & c.dd_mask;
+      bool done = false;
+      for (unsigned probes = 0; probes <= c.dd_mask; ++probes) {
+        unsigned long long old = __ldcg(&c.dd_keys[h]);
+        if (old == kEmptyKey) old = atomicCAS(&c.dd_keys[h], kEmptyKey, key);
+        if (old == kEmptyKey) { winner = true; hw = h; done = true; break; }
+        if (old == key) { done = true; break; }
+        h = (h + 1) & c.dd_mask;
+      }
+      if (!done) set_status(c.status, kDedupOverflow, 1, 0);
+    }
+    __syncwarp();
+    int owner = 0, pos = 0;
+    if (W == 1) {
+      pos = warp_alloc(&c.cnt[0], __ballot_sync(0xffffffffu, winner));
+    } else {
+      owner = winner ? owner_of(key, W) : -1;
+      const unsigned peers = __match_any_sync(0xffffffffu, owner);
+      if (winner) {
+        const int leader = __ffs(peers) - 1;
+        int b = 0;
+        if (lane == leader) b = atomicAdd(&c.cnt[owner], __popc(peers));
+        b = __shfl_sync(peers, b, leader);
+        pos = b + __popc(peers & lanemask_lt());
+      }
+    }
+    if (winner) {
+      if (pos >= capo) {
+        set_status(c.status, kOwnerSegOverflow, 1, owner);
+        c.dd_vals[hw] = -1;
+      } else {
+        c.stage_ids[owner * capo + pos] = key;
+        c.dd_vals[hw] = owner * capo + pos;
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kFrontThreads) pull_front_ship_kernel(const __grid_constant__ PullArgs a) {
+  const SparseCommView& c = a.c;
+  if (ld_volatile_s32(c.status) != 0) return;
+  const int tid = blockIdx.x * blockDim.x + threadIdx.x;
+  const int nth = gridDim.x * blockDim.x;
+  const int lane = threadIdx.x & 31;
+  const int W = c.world, R = c.rank, capo = c.capo;
+  const unsigned long long epoch = __ldcg(c.epoch) + 1ull;
+  if (W > 1) {
+    for (int p = 0; p < W; ++p) {
+      if (p == R) continue;
+      int n = __ldcg(&c.cnt[p]);
+      if (n > capo) n = capo;
+      const ulonglong2* src = reinterpret_cast<const ulonglong2*>(c.stage_ids + (size_t)p * capo);
+      ulonglong2* dst = reinterpret_cast<ulonglong2*>(c.inbox_ids[p] + (size_t)R * capo);
+      const int n2 = (n + 1) >> 1;
+      for (int j = tid; j < n2; j += nth) dst[j] = __ldcg(&src[j]);
+    }
+    // the CTA that finishes shipping last tells the owners their segments are complete and re-arms the counter
+    if (last_cta_arrives(&c.bar[4], true)) {
+      if (threadIdx.x < W && threadIdx.x != R) {
+        const int p = threadIdx.x;
+        const int n = min(__ldcg(&c.cnt[p]), capo);
+        st_release_sys_u64(sig_word(c.sig[p], kSigPullReq, R), (epoch << 32) | (unsigned long long)n);
+      }
+      if (threadIdx.x == 0) c.bar[4] = 0;
+    }
+  }
+  for (int base = tid - lane; base < a.n_ids; base += nth) {
+    const int i = base + lane;
+    const bool valid = i < a.n_ids;
+    const unsigned long long key = valid ? canon_key((unsigned long long)a.ids[i]) : kEmptyKey;
+    const unsigned same = __match_any_sync(0xffffffffu, key);
+    const int leader = __ffs(same) - 1;
+    int v = -1;
+    if (valid && lane == leader) {
+      unsigned h = (unsigned)mix64(key ^ 0x2545F4914F6CDD1Dull) & c.dd_mask;
+      for (unsigned probes = 0; probes <= c.dd_mask; ++probes) {
+        unsigned long long k = __ldcg(&c.dd_keys[h]);
+        if (k == key) { v = __ldcg(&c.dd_vals[h]); break; }
+        if (k == kEmptyKey) break;
+        h = (h + 1) & c.dd_mask;
+      }
+    }
+    v = __shfl_sync(same, v, leader);
+    if (valid) a.inverse[i] = v;
+  }
 }
 
 // =======================================================================================
@@ -847,6 +983,8 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_push_fused_kernel(const __
     }
   }
   prof_mark(c, 13);
+  // every CTA is past its row updates: re-arm the owner-unique counter for a pull whose front ran ahead
+  if (last_cta_arrives(&c.bar[3], false, (unsigned)nb) && threadIdx.x == 0) *c.ocount = 0;
 
   // ---- tail: once every owner has read this GPU's records, clear them for the next backward pass (the owners' reads
   // finished while this GPU updated its rows, so the wait is short)
@@ -908,6 +1046,21 @@ cudaError_t launch_sparse_pull(const PullArgs& args, int work_items, cudaStream_
   }
   void* params[] = {(void*)&args};
   return cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kThreads), params, smem, stream);
+}
+
+cudaError_t launch_sparse_pull_front(const PullArgs& args, cudaStream_t stream) {
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int grid = (args.n_ids + kFrontThreads - 1) / kFrontThreads;
+  if (grid < 1) grid = 1;
+  if (grid > 4 * sms) grid = 4 * sms;
+  pull_front_dedup_kernel<<<grid, kFrontThreads, 0, stream>>>(args);
+  pull_front_ship_kernel<<<grid, kFrontThreads, 0, stream>>>(args);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  // the inverse map is complete: the dedup scratch goes back to all-empty (kEmptyKey is all ones)
+  return cudaMemsetAsync(args.c.dd_keys, 0xFF, ((size_t)args.c.dd_mask + 1u) * sizeof(unsigned long long), stream);
 }
 
 // `max_ctas` > 0 caps the grid below the SM count, leaving whole SMs to a kernel running on another stream.

@@ -77,6 +77,7 @@ struct PullArgs {
   int lookup_only;        // never insert: signs the table does not hold come back as zero rows (serving)
   int lanes;              // lanes per row in the row-copy phase
   int tile_rows;          // > 0: rows per shared-memory tile of the staged row return; capo is a multiple of it
+  int front_done;         // dedup, id dispatch and inverse map of this batch already ran (launch_sparse_pull_front)
 };
 
 struct PushArgs {
@@ -155,6 +156,9 @@ struct BnSyncView {
   unsigned long long wait_ns;
 };
 
+// Dedup, id dispatch to the owners and inverse map of a batch as plain (non-cooperative) kernels, to be run on a
+// second stream under the previous step's forward / backward; the pull of that batch then runs with front_done = 1.
+cudaError_t launch_sparse_pull_front(const PullArgs& args, cudaStream_t stream);
 cudaError_t launch_dense_step(const DenseStepArgs& a, cudaStream_t st);
 int dense_step_ctas_per_sm();      // resident CTAs of the multi-GPU dense kernel per SM
 cudaError_t launch_sparse_pull(const PullArgs& args, int work_items, cudaStream_t stream);

@@ -18,7 +18,7 @@ import torch
 from torch import nn
 
 from .. import core
-from ..data.features import gather_columns
+from ..data.features import PACKED_KEY, gather_columns
 from ..feature_column import EmbeddingColumn
 from ..ops.embedding import pull_pool
 
@@ -99,6 +99,21 @@ class EmbeddingFeatures(nn.Module):
         self.table.set_training(training)
         self._pending_push = training and self.trainable
         return ids, B
+
+    def ids_pulled_for(self, features: Dict):
+        """The id tensor this layer's next training pull will receive for ``features``, when that is known ahead
+        without any work: the packed single-hot ids of exactly this layer's slots, already on the device (the
+        tensor the pull gets is then a view of it, same address).  None otherwise, and for layers whose table
+        serves several links (their pulls share one step counter)."""
+        rt = core.runtime()
+        if not (rt.on_gpu and self.trainable and isinstance(features, dict)) or not hasattr(self.link, "prefetch"):
+            return None
+        if len(getattr(self.table, "links", ())) != 1:
+            return None
+        packed = features.get(PACKED_KEY)
+        if packed is None or list(packed.keys) != list(self._keys) or packed.ids is None or not packed.ids.is_cuda:
+            return None
+        return packed.ids.reshape(-1)
 
     def backwards(self, grads_and_vars=None):
         """Push this step's sparse gradients to the owning shards and apply the sparse optimizer."""

@@ -128,7 +128,7 @@ def _is_static(spec) -> bool:
     return True
 
 
-_LOSS_RING = 8      # pinned slots for per-step losses on their way to the host
+_LOSS_RING = 32     # pinned slots for per-step losses on their way to the host: how far the host may run ahead
 
 
 def graph_decision(world: int, known: bool, static: bool, n_graphs: int, max_graphs: int, eager_steps: int,
@@ -151,6 +151,17 @@ def graph_decision(world: int, known: bool, static: bool, n_graphs: int, max_gra
     return "capture"
 
 
+def _with_next(it):
+    """(item, following item or None) for every item of ``it``."""
+    prev = _with_next        # sentinel
+    for b in it:
+        if prev is not _with_next:
+            yield prev, b
+        prev = b
+    if prev is not _with_next:
+        yield prev, None
+
+
 class _GraphPair:
     """Two captures of the same step that take turns.  Each has its own static input buffers, so the inputs of the
     next step land (on the copy stream) while the previous replay still reads the other set."""
@@ -161,7 +172,37 @@ class _GraphPair:
         self.loss: List[torch.Tensor] = []
         self.done = [torch.cuda.Event(), torch.cuda.Event()]        # replay that last read set p has finished
         self.copied = [torch.cuda.Event(), torch.cuda.Event()]      # inputs of set p have landed
+        self.done_recorded = [False, False]
+        for e in self.copied:
+            e.record()               # events get their CUDA handle at the first record
         self.turn = 0
+
+
+_FRONT_IN_GRAPH = ("front pending in a replayed graph",)      # marks a link whose device state holds a run-ahead front
+
+
+class _GraphRing:
+    """Captured steps for callers that name the batch of the FOLLOWING step: three sets of static input buffers
+    take turns.  The graph of set i runs the step on set i with the probe-only pull (the front for set i ran in
+    the previous graph) and, on a second stream, the pull front for set i+1.  A fourth capture on set 0 does the
+    whole pull itself; it starts the ring, and restarts it after anything else touched the tables."""
+
+    SETS = 3
+
+    def __init__(self):
+        self.cold = None
+        self.cold_loss = None
+        self.warm: List[Any] = []
+        self.leaves: List[List[torch.Tensor]] = []
+        self.loss: List[torch.Tensor] = []
+        self.done = [torch.cuda.Event() for _ in range(self.SETS)]       # the graph that ran set i as its step is over
+        self.copied = [torch.cuda.Event() for _ in range(self.SETS)]     # inputs of set i have landed
+        self.done_recorded = [False] * self.SETS
+        for e in self.copied:
+            e.record()
+        self.sig: List[Any] = [None] * self.SETS                        # which batch (leaf addresses) set i holds
+        self.turn = 0
+        self.links: List[Any] = []
 
 
 class _StatusPoll:
@@ -218,6 +259,9 @@ class Model(nn.Module):
         self._host_metrics: List[Any] = []    # metrics that need (labels, predictions) tensors every step
         self._graph = None
         self._graphs: Dict[Any, _GraphPair] = {}     # batch signature -> the two captures of the step
+        self._rings: Dict[Any, _GraphRing] = {}      # same, for callers that name the following batch
+        self._ring_refused = False
+        self._last_done = None                       # event behind the last replayed step (None after an eager one)
         self._max_graphs = 8
         self._graph_key = None
         self._static_leaves: List[torch.Tensor] = []
@@ -302,7 +346,36 @@ class Model(nn.Module):
         for layer in self.sparse_layers():
             layer.backwards(grads_and_vars)
 
-    def _step_impl(self, features, labels):
+    def _front_layers(self, next_features):
+        """(layer, ids) for every sparse layer whose next pull can be started ahead for ``next_features``; empty
+        unless ALL trainable sparse layers of the model qualify (a step either runs every front ahead or none)."""
+        if next_features is None or not core.config.pull_front_ahead or not core.runtime().on_gpu:
+            return []
+        out = []
+        for layer in self.sparse_layers():
+            if not getattr(layer, "trainable", True):
+                continue
+            ids = layer.ids_pulled_for(next_features) if hasattr(layer, "ids_pulled_for") else None
+            if ids is None:
+                return []
+            out.append((layer, ids))
+        return out
+
+    def _step_impl(self, features, labels, next_features=None):
+        fronts = self._front_layers(next_features) if self.training else []
+        for layer, ids in fronts:
+            layer.link.next_ids = ids          # the link forks the front of the next batch right behind its pull
+        loss = self._step_body(features, labels)
+        for layer, _ in fronts:
+            lk = layer.link
+            lk.next_ids = None
+            if lk.front_in_flight:             # join the side stream: the step (and a captured graph) ends after the front
+                from ..ops.sparse_table_gpu import front_stream
+                torch.cuda.current_stream().wait_stream(front_stream(lk.dev))
+                lk.front_in_flight = False
+        return loss
+
+    def _step_body(self, features, labels):
         loss = None
         fused = getattr(self, "fused_train_loss", None)
         if fused is not None and not callable(self.loss_fn) and self.use_fused and not self._host_metrics:
@@ -372,13 +445,23 @@ class Model(nn.Module):
         return _unflatten(spec, iter(moved)), spec, leaves
 
     def _eager_step(self, features, labels):
+        self._last_done = None
         (f, y), _, _ = self._to_device((features, labels))
         return self._step_impl(f, y)
 
-    def train_step(self, data):
-        """One optimisation step on ``data = (features, labels)``; returns the loss (device tensor)."""
+    def train_step(self, data, next_data=None):
+        """One optimisation step on ``data = (features, labels)``; returns the loss (device tensor).
+
+        ``next_data``: the batch that will be passed as ``data`` at the next call (same tensors, unchanged).  On the
+        captured path its sparse ids are deduplicated and sent to their owners on a second stream while this step
+        runs, so the next step's pull only probes and returns rows.  ``fit`` passes it by itself."""
+        if next_data is not None and self._use_graph and core.config.pull_front_ahead and core.runtime().on_gpu:
+            loss = self._ring_step(data, next_data)
+            if loss is not None:
+                return loss
         features, labels = data
-        self.train()
+        if not self.training:
+            self.train()
         if self._status_poll is not None:
             self._status_poll.tick()
         if not self._use_graph:
@@ -413,6 +496,11 @@ class Model(nn.Module):
         if any(t.is_cuda for t in leaves):
             # inputs produced on the device come with the stream order of whatever produced them
             torch._foreach_copy_(gp.leaves[p], [t if t.is_cuda else t.to(rt.device, non_blocking=True) for t in leaves])
+        elif core.config.native_step_path and all(t.is_contiguous() for t in leaves):
+            # one native call: copy stream waits for the replay that last read this input set, the leaves go host ->
+            # device, their arrival is recorded and the compute stream waits for it
+            self._ext.stage_inputs(gp.leaves[p], leaves, self._copy_stream.cuda_stream, main.cuda_stream,
+                                   gp.done[p].cuda_event if gp.done_recorded[p] else 0, gp.copied[p].cuda_event, 0)
         else:
             copy = self._copy_stream
             copy.wait_event(gp.done[p])          # the replay that last read this input set is over
@@ -425,6 +513,8 @@ class Model(nn.Module):
             self.optimizer.table.set_lr(self.optimizer._lr())
         gp.graphs[p].replay()
         gp.done[p].record(main)
+        gp.done_recorded[p] = True
+        self._last_done = gp.done[p]
         if self.optimizer is not None:
             self.optimizer.iterations += 1
             self.optimizer.table.step_count += 1
@@ -432,12 +522,143 @@ class Model(nn.Module):
         self._graph, self._graph_key, self._static_leaves, self._static_loss = gp.graphs[p], key, gp.leaves[p], gp.loss[p]
         return gp.loss[p]
 
+    # ---- captured steps with the next batch's pull front run ahead -------------------------------------------
+    @staticmethod
+    def _sig(leaves):
+        return tuple((t.data_ptr(), tuple(t.shape)) for t in leaves)
+
+    def _stage(self, ring, i, leaves):
+        """Inputs ``leaves`` into static set i of the ring (host leaves: native staged copy on the copy stream; device
+        leaves: one foreach copy in stream order)."""
+        main = torch.cuda.current_stream()
+        if any(t.is_cuda for t in leaves):
+            dev = core.runtime().device
+            torch._foreach_copy_(ring.leaves[i], [t if t.is_cuda else t.to(dev, non_blocking=True) for t in leaves])
+        else:
+            srcs = [t if t.is_contiguous() else t.contiguous() for t in leaves]
+            self._ext.stage_inputs(ring.leaves[i], srcs, self._copy_stream.cuda_stream, main.cuda_stream,
+                                   ring.done[i].cuda_event if ring.done_recorded[i] else 0, ring.copied[i].cuda_event,
+                                   0)
+        ring.sig[i] = self._sig(leaves)
+
+    def _ring_step(self, data, next_data):
+        """The step through the three-set ring, or None when this batch does not take that path."""
+        rt = core.runtime()
+        leaves: List[torch.Tensor] = []
+        spec = _flatten(data, leaves)
+        if not _is_static(spec):
+            return None
+        nleaves: List[torch.Tensor] = []
+        if _flatten(next_data, nleaves) != spec or [(t.shape, t.dtype) for t in nleaves] != [(t.shape, t.dtype) for t in leaves]:
+            return None          # the following batch has another shape (a shorter last batch): no run-ahead for it
+        key = (spec, tuple((t.shape, t.dtype) for t in leaves))
+        ring = self._rings.get(key)
+        if ring is None:
+            if self._rings or self._ring_refused or self._eager_steps < self._graph_warmup or key in self._graphs:
+                return None      # one ring per model, captured right after the warm-up steps on every rank alike
+            if not self.training:
+                self.train()
+            ring = self._capture_ring(spec, leaves, nleaves, key)
+            if ring is None:
+                self._ring_refused = True
+                return None
+        if not self.training:
+            self.train()
+        if self._status_poll is not None:
+            self._status_poll.tick()
+        main = torch.cuda.current_stream()
+        cur = ring.turn
+        warm = ring.sig[cur] == self._sig(leaves) and all(lk._front is _FRONT_IN_GRAPH for lk in ring.links)
+        if not warm:
+            # (re)start: whatever front is pending belongs to another batch
+            for lk in ring.links:
+                if lk._front is not None:
+                    lk.discard_front()
+            cur = ring.turn = 0
+            self._stage(ring, 0, leaves)
+        nxt = (cur + 1) % ring.SETS
+        self._stage(ring, nxt, nleaves)
+        if self.optimizer is not None:
+            self.optimizer.table.set_lr(self.optimizer._lr())
+        (ring.warm[cur] if warm else ring.cold).replay()
+        ring.done[cur].record(main)
+        ring.done_recorded[cur] = True
+        for lk in ring.links:
+            lk._front = _FRONT_IN_GRAPH
+        ring.turn = nxt
+        if self.optimizer is not None:
+            self.optimizer.iterations += 1
+            self.optimizer.table.step_count += 1
+        self._loss_steps += self._graph_loss_steps
+        loss = ring.loss[cur] if warm else ring.cold_loss
+        self._graph, self._graph_key, self._static_leaves, self._static_loss = (ring.warm[cur] if warm else ring.cold), key, ring.leaves[cur], loss
+        self._last_done = ring.done[cur]
+        return loss
+
+    def _capture_ring(self, spec, leaves, nleaves, key):
+        """Capture the cold graph (set 0, whole pull) and the three warm graphs; None when the model's sparse layers
+        cannot start their pulls ahead for this kind of batch."""
+        rt = core.runtime()
+        dev = rt.device
+        from .. import _build
+        ext = self._ext = _build.cuda_ext()
+        ring = _GraphRing()
+        for i in range(ring.SETS):
+            src = nleaves if i == 1 else leaves
+            st = [torch.empty(t.shape, dtype=t.dtype, device=dev) for t in src]
+            for d, h in zip(st, src):
+                d.copy_(h, non_blocking=True)
+            ring.leaves.append(st)
+        feats = [_unflatten(spec, iter(st)) for st in ring.leaves]
+        fronts = self._front_layers(feats[1][0])
+        if not fronts:
+            return None
+        ring.links = [layer.link for layer, _ in fronts]
+        for lk in ring.links:
+            if lk._front is not None:
+                lk.discard_front()
+        iters = self.optimizer.iterations if self.optimizer is not None else 0
+        steps0 = self.optimizer.table.step_count if self.optimizer is not None else 0
+        loss_steps0 = self._loss_steps
+        pool = None
+        order = [(0, True), (1, False), (2, False), (0, False)]          # (set, cold): every warm capture follows the
+        ring.warm = [None] * ring.SETS                                    # capture that ran the front for its set
+        ring.loss = [None] * ring.SETS
+        for i, cold in order:
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            c0 = ext.launch_count()
+            f, y = feats[i]
+            with torch.cuda.graph(g, pool=pool):
+                static_loss = self._step_impl(f, y, next_features=feats[(i + 1) % ring.SETS][0])
+            if pool is None:
+                self._launches_per_step = ext.launch_count() - c0
+                self._graph_loss_steps = self._loss_steps - loss_steps0
+                pool = g.pool()
+            if cold:
+                ring.cold, ring.cold_loss = g, static_loss
+            else:
+                ring.warm[i], ring.loss[i] = g, static_loss
+        if self.optimizer is not None:      # capture only records work, it does not run a step
+            self.optimizer.iterations = iters
+            self.optimizer.table.step_count = steps0
+        self._loss_steps = loss_steps0
+        for lk in ring.links:
+            lk._front = None                # nothing ran: no front is pending on the device
+        self._rings[key] = ring
+        rt.barrier()                        # captures take a different time on every rank; line the ranks up again
+        return ring
+
     def _capture(self, spec, leaves, key):
         """Capture the step twice (two sets of static inputs that take turns) into one memory pool."""
         dev = core.runtime().device
         gp = _GraphPair()
         from .. import _build
-        ext = _build.cuda_ext()
+        ext = self._ext = _build.cuda_ext()
+        for layer in self.sparse_layers():      # a pull front that ran ahead for another batch must not leak into the capture
+            lk = getattr(layer, "link", None)
+            if lk is not None and getattr(lk, "_front", None) is not None:
+                lk.discard_front()
         iters = self.optimizer.iterations if self.optimizer is not None else 0
         steps0 = self.optimizer.table.step_count if self.optimizer is not None else 0
         loss_steps0 = self._loss_steps
@@ -470,9 +691,11 @@ class Model(nn.Module):
         # device with a finite budget, so line the ranks up on the host first.
         core.runtime().barrier()
 
-    def train_on_batch(self, x, y=None, return_dict: bool = False):
+    def train_on_batch(self, x, y=None, return_dict: bool = False, next_batch=None):
+        """One training step.  ``next_batch = (x, y)`` of the following call, when known, lets the captured step start
+        that batch's sparse pull ahead (see :meth:`train_step`)."""
         with start_as_current_span("train_on_batch"):
-            loss = self.train_step((x, y))
+            loss = self.train_step((x, y), next_batch)
         return {"loss": loss} if return_dict else loss
 
     def test_step(self, data):
@@ -622,6 +845,11 @@ class Model(nn.Module):
                 if getattr(self, "_pinned_loss", None) is None:      # page-locked allocation is slow: once per model
                     self._pinned_loss = torch.zeros(_LOSS_RING, dtype=torch.float32).pin_memory()
                     self._loss_events = [torch.cuda.Event() for _ in range(_LOSS_RING)]
+                    for e in self._loss_events:
+                        e.record()           # events get their CUDA handle at the first record
+                    from .. import _build
+                    self._ext = _build.cuda_ext()
+                    self._read_stream = torch.cuda.Stream(device=rt.device)
                 pinned = self._pinned_loss
                 events = self._loss_events
             for cb in callbacks:
@@ -635,17 +863,29 @@ class Model(nn.Module):
                     self.reset_metrics()
                 last = None
                 issued = collected = 0       # losses copied to / read from the pinned ring (the host runs up to _LOSS_RING - 1 steps ahead)
-                for i, batch in enumerate(self._batch_source(dataset, prefetch)):
+                ahead = gpu and self._use_graph and core.config.pull_front_ahead
+                for i, (batch, nxt) in enumerate(_with_next(self._batch_source(dataset, prefetch))):
                     if steps_per_epoch is not None and i >= steps_per_epoch:
                         break
-                    last = self.train_step(batch)
+                    # the last batch of a pass names itself as its successor: the step stays on the same captured path
+                    last = self.train_step(batch, (nxt if nxt is not None else batch) if ahead else None)
                     if record_step_loss:
                         if pinned is None:
                             history["step_loss"].append(float(last))
                         else:
                             slot = issued % _LOSS_RING
-                            pinned[slot: slot + 1].copy_(last.detach().reshape(1), non_blocking=True)
-                            events[slot].record()
+                            if core.config.native_step_path and last.dtype == torch.float32 and last.numel() == 1:
+                                if self._last_done is not None:
+                                    # behind the step's end event on a stream of its own: the compute stream
+                                    # carries nothing between two replayed steps
+                                    self._ext.read_scalar_async(pinned, slot, last, self._read_stream.cuda_stream,
+                                                                events[slot].cuda_event, self._last_done.cuda_event)
+                                else:
+                                    self._ext.read_scalar_async(pinned, slot, last, torch.cuda.current_stream().cuda_stream,
+                                                                events[slot].cuda_event, 0)
+                            else:
+                                pinned[slot: slot + 1].copy_(last.detach().reshape(1), non_blocking=True)
+                                events[slot].record()
                             issued += 1
                             # read back what has arrived; wait only when the ring is about to wrap
                             while collected < issued and (issued - collected >= _LOSS_RING or events[collected % _LOSS_RING].query()):
@@ -835,7 +1075,7 @@ class PCGradModel(Model):
     back-propagated separately and the dense gradients are combined by PCGrad
     (tensornet/model/Model.py:259-293, tensornet/model/compile_utils.py:55-126)."""
 
-    def _step_impl(self, features, labels):
+    def _step_impl(self, features, labels, next_features=None):
         from ..optimizer import PCGrad
 
         logits = self(features)

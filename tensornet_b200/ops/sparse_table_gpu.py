@@ -261,6 +261,18 @@ class GpuSparseTable:
         return self.compact(keep)
 
 
+_FRONT_STREAMS = {}
+
+
+def front_stream(device) -> "torch.cuda.Stream":
+    """The stream the pull fronts of a device run on."""
+    key = str(device)
+    st = _FRONT_STREAMS.get(key)
+    if st is None:
+        st = _FRONT_STREAMS[key] = torch.cuda.Stream(device=device)
+    return st
+
+
 class GpuSparseLink:
     """Per-layer exchange state of a table: symmetric inboxes, the per-batch unique-row matrix
     ``U``, its gradient ``gU`` and the bookkeeping that ties one pull to the following push."""
@@ -310,7 +322,7 @@ class GpuSparseLink:
             acc=torch.zeros(n_seg * self.gstride if multi else 4, dtype=torch.float32, device=d),
             dd_keys=torch.full((dd_cap,), -1, dtype=torch.int64, device=d),
             dd_vals=torch.zeros(dd_cap, dtype=torch.int32, device=d),
-            bar=torch.zeros(4, dtype=torch.int32, device=d),
+            bar=torch.zeros(8, dtype=torch.int32, device=d),
             prof=torch.zeros(16, dtype=torch.int64, device=d),
         )
         self.arena = arena
@@ -328,6 +340,12 @@ class GpuSparseLink:
         self._last_n_ids = 0
         self.push_cta_cap = 0        # > 0: the push kernel leaves the remaining SMs to a kernel on another stream
         self.dense_rider = None      # a DenseTable whose step the next push carries on a few of its CTAs (several GPUs)
+        # pull front run ahead of its step (see prefetch): (ids data pointer, count, inverse buffer) of the batch it ran for
+        self._front = None
+        self.next_ids = None         # set by the model before a step: the ids this link will pull at the NEXT step
+        self.front_in_flight = False # a front was forked onto the side stream during this step (the model joins it)
+        self._fork = torch.cuda.Event() if runtime().on_gpu else None
+        self._front_inverse = {}     # inverse buffers of the fronts, one per id buffer (stable addresses for CUDA graphs)
         if multi:
             rt.barrier()
 
@@ -337,12 +355,52 @@ class GpuSparseLink:
         return ``inverse``: the row of ``self.U`` holding each id's embedding.  ``lookup_only`` (inference)
         never creates rows: signs no shard holds come back as zeros."""
         n = ids.numel()
+        front, self._front = self._front, None
+        front_done = False
+        if front is not None:
+            if front[0] == ids.data_ptr() and front[1] == n and training and not lookup_only and inverse is None:
+                inverse, front_done = front[2], True
+            else:
+                self.discard_front()
         if inverse is None:
             inverse = torch.empty(n, dtype=torch.int32, device=self.dev)
         self._last_n_ids = n
         with phase("tn.sparse_pull"):
-            self.ctx.pull(ids.reshape(-1), inverse, labels, int(label_mod), bool(training), bool(lookup_only))
+            self.ctx.pull(ids.reshape(-1), inverse, labels, int(label_mod), bool(training), bool(lookup_only), front_done)
+        nxt, self.next_ids = self.next_ids, None
+        if nxt is not None and training:
+            # the batch of the following step is known: its dedup and id dispatch run on a second stream from here on,
+            # under this step's forward and backward passes
+            self._fork.record()
+            side = front_stream(self.dev)
+            side.wait_event(self._fork)
+            with torch.cuda.stream(side):
+                self.prefetch(nxt)
+            self.front_in_flight = True
         return inverse
+
+    def prefetch(self, ids: torch.Tensor):
+        """Run the front of the pull (dedup, id dispatch to the owners, inverse map) for the batch ``ids`` on the
+        current stream.  The next :meth:`pull` must be a training pull of this very tensor; it then only probes and
+        returns rows.  Anything else discards the front (:meth:`discard_front`)."""
+        n = ids.numel()
+        key = (ids.data_ptr(), n)
+        inverse = self._front_inverse.get(key)
+        if inverse is None:
+            if len(self._front_inverse) >= 8:
+                self._front_inverse.pop(next(iter(self._front_inverse)))
+            inverse = self._front_inverse[key] = torch.empty(n, dtype=torch.int32, device=self.dev)
+        with phase("tn.sparse_pull_front"):
+            self.ctx.front(ids.reshape(-1), inverse)
+        self._front = (ids.data_ptr(), n, inverse)
+
+    def discard_front(self):
+        """Forget a front that ran for a batch which is not pulled next: the per-owner counters it built are
+        cleared and the step counter moves on by one, so the id segments and flags it sent can never be taken for
+        those of the pull that follows.  Every rank must do this at the same point (they do: same program)."""
+        self._front = None
+        self._loc["cnt"].zero_()
+        self.table.epoch.add_(1)
 
     def push(self):
         """Apply the accumulated unique-row gradients (``self.gU``) on the owning GPUs."""

@@ -32,9 +32,14 @@ def main():
         lo, hi = rt.rank * B, (rt.rank + 1) * B
         data.append(({tn.data.PACKED_KEY: tn.data.PackedFeatures(slots, ids=ids[:, lo:hi].contiguous()), "dense": dense[lo:hi]}, label[lo:hi]))
     losses = []
-    for epoch in range(5):
-        for f, y in data:
-            l = model.train_on_batch(f, y)
+    # every step names the batch of the following one, as `fit` does: after the warm-up the captured steps run that
+    # batch's dedup and id dispatch ahead on a second stream (the last step names a batch that never comes: its
+    # front is discarded by whatever touches the tables next)
+    order = [data[k % len(data)] for k in range(5 * len(data) + 1)]
+    for k in range(5 * len(data)):
+        if True:
+            f, y = order[k]
+            l = model.train_on_batch(f, y, next_batch=order[k + 1])
             t = l.detach().clone()
             if rt.world > 1:
                 torch.distributed.all_reduce(t, group=rt.device_group)

@@ -195,3 +195,66 @@ def test_training_through_table_growth_matches_a_large_table(tn_gpu):
     assert graphed and grown >= 2 and grown_big == 0
     assert dropped_s == dropped_b and dropped_s > 0
     assert torch.allclose(p_small, p_big, atol=1e-6), float((p_small - p_big).abs().max())
+
+
+def test_fit_from_pinned_batches_native_step_path_matches_torch_calls(tn_gpu):
+    """`fit` on page-locked host batches: inputs staged and losses read back through the native per-step calls
+    against the same run issued with torch stream / event / copy calls; every step's loss reaches the host, and a
+    page-locked batch released right after its step is not handed out again before its copy has run."""
+    tn = tn_gpu
+    B = 512
+    runs = []
+    for native in (True, False):
+        tn.core.config.native_step_path = native
+        try:
+            m, slots = _make(tn, graph=True, seed=5)
+            data = _batches(tn, slots, B, 6, seed=8)
+
+            def stream():
+                for epoch in range(5):
+                    for f, y in data:
+                        # fresh page-locked copies every step, dropped as soon as the step is issued
+                        pf = {tn.data.PACKED_KEY: tn.data.PackedFeatures(slots, ids=f[tn.data.PACKED_KEY].ids.clone().pin_memory()),
+                              "dense": f["dense"].clone().pin_memory()}
+                        yield pf, y.clone().pin_memory()
+
+            hist = m.fit(stream(), epochs=1, record_step_loss=True)
+            torch.cuda.synchronize()
+            tn.core.runtime().check_status()
+            assert m._graph is not None
+            assert len(hist["step_loss"]) == 30
+            runs.append(hist["step_loss"])
+        finally:
+            tn.core.config.native_step_path = True
+    for a, b in zip(*runs):
+        assert abs(a - b) < 5e-2 * max(1.0, abs(a)), (a, b)
+    assert runs[0][-1] < runs[0][0]
+
+
+@pytest.mark.parametrize("share", [False, True])
+def test_pull_front_run_ahead_in_the_captured_ring_matches_the_plain_path(tn_gpu, share):
+    """`fit` names the following batch, so the captured steps run the next batch's dedup and id dispatch ahead (three
+    input sets, cold + warm graphs); the trajectory equals the one without run-ahead, also across an evaluation in the
+    middle of training (which discards the pending front) and a second `fit`."""
+    tn = tn_gpu
+    B = 512
+    runs = []
+    for ahead in (True, False):
+        tn.core.config.pull_front_ahead = ahead
+        try:
+            m, slots = _make(tn, graph=True, seed=7, share=share)
+            data = _batches(tn, slots, B, 7, seed=9)
+            h1 = m.fit(data * 3, epochs=1, record_step_loss=True)
+            ev = m.evaluate(data[:2])
+            h2 = m.fit(data * 2, epochs=1, record_step_loss=True)
+            torch.cuda.synchronize()
+            tn.core.runtime().check_status()
+            assert bool(m._rings) == ahead, "the ring of captured steps was %sused" % ("not " if ahead else "")
+            runs.append((h1["step_loss"] + h2["step_loss"], ev))
+        finally:
+            tn.core.config.pull_front_ahead = True
+    (la, ea), (lb, eb) = runs
+    assert len(la) == len(lb) == 35
+    for a, b in zip(la, lb):
+        assert abs(a - b) < 5e-2 * max(1.0, abs(a)), (la, lb)
+    assert la[-1] < 0.8 * la[0]

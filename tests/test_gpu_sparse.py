@@ -272,3 +272,58 @@ def test_shard_grows_and_compacts_on_the_device(tn_gpu, status_ok):
     inv = lks.pull(dropped_keys[:200].contiguous(), training=False)      # the freed part of the slab takes new signs
     torch.cuda.synchronize()
     assert small.n_rows == kept_keys.numel() + 200
+
+
+@pytest.mark.parametrize("dim", [8, 64])
+def test_pull_front_run_ahead_matches_the_one_kernel_pull(tn_gpu, status_ok, dim):
+    """The front of a pull (dedup, id dispatch, inverse map) run ahead as plain kernels, followed by the probe-only
+    pull, against the pull that does everything in one kernel: same rows per id, same show / click counts, same
+    table after the pushes; a front that is not followed by its pull is discarded cleanly."""
+    tn = tn_gpu
+    opt = tn.core.AdaGrad(learning_rate=0.05, initial_g2sum=0.1, initial_scale=0.3)
+    g = torch.Generator().manual_seed(11)
+    batches = [(torch.randint(0, 700, (3000,), generator=g, dtype=torch.int64) * 104729 + 5) for _ in range(4)]
+    labels = [(torch.rand(3000, generator=g) < 0.3).float() for _ in range(4)]
+    tables = []
+    for ahead in (False, True):
+        t, lk = _mk(tn, opt, dim)
+        dev = t.dev
+        ids_d = [b.to(dev) for b in batches]
+        lab_d = [l.to(dev) for l in labels]
+        seen = []
+        for k in range(4):
+            inv = lk.pull(ids_d[k], labels=lab_d[k], label_mod=0, training=True)
+            if ahead and k > 0:
+                assert inv.data_ptr() == lk._front_inverse[(ids_d[k].data_ptr(), 3000)].data_ptr()
+            if ahead and k + 1 < 4:
+                lk.prefetch(ids_d[k + 1])                 # same stream here; the model forks it onto a side stream
+            torch.cuda.synchronize()
+            tn.core.runtime().check_status()
+            inv_l = inv.long()
+            assert int(inv_l.min()) >= 0
+            seen.append((lk.U[inv_l, :dim].cpu(), lk.cnts[inv_l].cpu()))
+            # a gradient that depends only on the sign, so both runs push the same thing whatever the virtual order
+            gid = (ids_d[k] % 97).float().unsqueeze(1) * 0.01 + torch.arange(dim, device=dev).float() * 1e-3
+            lk.gU[:, :dim].index_put_((inv_l,), gid, accumulate=False)
+            lk.push()
+        torch.cuda.synchronize()
+        tn.core.runtime().check_status()
+        tables.append((_host_rows(t), seen))
+        if ahead:
+            # a front whose pull never comes: the next pull is for other ids and must still be right
+            lk.prefetch(ids_d[0])
+            inv = lk.pull(ids_d[2], labels=lab_d[2], label_mod=0, training=True)
+            torch.cuda.synchronize()
+            tn.core.runtime().check_status()
+            rows = _host_rows(t)
+            U = lk.U[inv.long(), :dim].cpu().numpy()
+            for i, s in enumerate(batches[2].tolist()[:200]):
+                assert np.allclose(U[i], rows[s][:dim])
+            lk.push()
+    (rows_a, seen_a), (rows_b, seen_b) = tables
+    for (Ua, ca), (Ub, cb) in zip(seen_a, seen_b):
+        assert torch.allclose(Ua, Ub, rtol=1e-6, atol=1e-7)
+        assert torch.equal(ca, cb)
+    assert rows_a.keys() == rows_b.keys()
+    for k in rows_a:
+        assert np.allclose(rows_a[k], rows_b[k], rtol=1e-5, atol=1e-6)
