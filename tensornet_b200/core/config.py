@@ -54,6 +54,9 @@ class Config:
     #: when the caller names the batch of the following step (`fit` does), its dedup and id dispatch run on a second
     #: stream under the current step's forward / backward, and the pull of that step only probes and returns rows
     pull_front_ahead: bool = True
+    #: several GPUs: bind each process to the CPU cores closest to its GPU (NVML's affinity mask) before it allocates
+    #: page-locked buffers
+    bind_cpu_affinity: bool = True
     #: multi-GPU, dense arrays up to 4 M elements: the dense step runs on a few CTAs of the last sparse push kernel of
     #: the step instead of in a kernel of its own behind it
     dense_rides_push: bool = True
@@ -96,6 +99,7 @@ class Config:
         c.nvtx_phases = _env("TN_NVTX_PHASES", c.nvtx_phases, bool)
         c.native_step_path = _env("TN_NATIVE_STEP_PATH", c.native_step_path, bool)
         c.pull_front_ahead = _env("TN_PULL_FRONT_AHEAD", c.pull_front_ahead, bool)
+        c.bind_cpu_affinity = _env("TN_BIND_CPU_AFFINITY", c.bind_cpu_affinity, bool)
         c.dense_rides_push = _env("TN_DENSE_RIDES_PUSH", c.dense_rides_push, bool)
         c.checkpoint_chunk_rows = _env("TN_CKPT_CHUNK_ROWS", c.checkpoint_chunk_rows, int)
         c.checkpoint_load_chunk_rows = _env("TN_CKPT_LOAD_CHUNK_ROWS", c.checkpoint_load_chunk_rows, int)

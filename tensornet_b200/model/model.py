@@ -1075,6 +1075,9 @@ class PCGradModel(Model):
     back-propagated separately and the dense gradients are combined by PCGrad
     (tensornet/model/Model.py:259-293, tensornet/model/compile_utils.py:55-126)."""
 
+    def _front_layers(self, next_features):
+        return []          # this step runs several backward passes per pull; it does not start pulls ahead
+
     def _step_impl(self, features, labels, next_features=None):
         from ..optimizer import PCGrad
 

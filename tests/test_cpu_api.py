@@ -292,3 +292,30 @@ def test_ps_strategy_scope_and_checkpoint_callback_cycle(tmp_path):
         cb2.on_predict_begin()
         got = torch.as_tensor(m2.predict_on_batch(data[0][0])).reshape(-1)
     assert torch.allclose(got, want, atol=1e-5)
+
+
+def test_cpu_affinity_follows_the_mask_nvml_gives(monkeypatch):
+    """The per-GPU CPU binding against a fake NVML: the process keeps the cores NVML names that it is allowed to use,
+    and is left alone when there is no overlap or no NVML."""
+    import os
+    import sys
+    import types
+    import importlib
+    rtmod = importlib.import_module("tensornet_b200.core.runtime")
+
+    allowed = set(range(8))
+    calls = []
+    monkeypatch.setattr(os, "sched_getaffinity", lambda pid: set(allowed), raising=False)
+    monkeypatch.setattr(os, "sched_setaffinity", lambda pid, cpus: calls.append(set(cpus)), raising=False)
+    fake = types.SimpleNamespace(nvmlInit=lambda: None, nvmlDeviceGetHandleByIndex=lambda i: ("h", i),
+                                 nvmlDeviceGetHandleByUUID=lambda u: (_ for _ in ()).throw(RuntimeError("no such GPU")),
+                                 nvmlDeviceGetCpuAffinity=lambda h, n: [0b00111100] + [0] * (n - 1))
+    monkeypatch.setitem(sys.modules, "pynvml", fake)
+    rtmod._bind_cpus_near(0)
+    assert calls == [{2, 3, 4, 5}]
+    fake.nvmlDeviceGetCpuAffinity = lambda h, n: [1 << 40] + [0] * (n - 1)      # cores this process may not use
+    rtmod._bind_cpus_near(0)
+    assert len(calls) == 1
+    monkeypatch.setitem(sys.modules, "pynvml", None)                              # import fails: nothing happens
+    rtmod._bind_cpus_near(0)
+    assert len(calls) == 1
