@@ -261,6 +261,7 @@ class Model(nn.Module):
         self._graphs: Dict[Any, _GraphPair] = {}     # batch signature -> the two captures of the step
         self._rings: Dict[Any, _GraphRing] = {}      # same, for callers that name the following batch
         self._ring_refused = False
+        self._flat_cache = None                      # (batch object, its flattened form) of the batch named as next
         self._last_done = None                       # event behind the last replayed step (None after an eager one)
         self._max_graphs = 8
         self._graph_key = None
@@ -527,10 +528,9 @@ class Model(nn.Module):
     def _sig(leaves):
         return tuple((t.data_ptr(), tuple(t.shape)) for t in leaves)
 
-    def _stage(self, ring, i, leaves):
+    def _stage(self, ring, i, leaves, sig, main):
         """Inputs ``leaves`` into static set i of the ring (host leaves: native staged copy on the copy stream; device
         leaves: one foreach copy in stream order)."""
-        main = torch.cuda.current_stream()
         if any(t.is_cuda for t in leaves):
             dev = core.runtime().device
             torch._foreach_copy_(ring.leaves[i], [t if t.is_cuda else t.to(dev, non_blocking=True) for t in leaves])
@@ -539,19 +539,30 @@ class Model(nn.Module):
             self._ext.stage_inputs(ring.leaves[i], srcs, self._copy_stream.cuda_stream, main.cuda_stream,
                                    ring.done[i].cuda_event if ring.done_recorded[i] else 0, ring.copied[i].cuda_event,
                                    0)
-        ring.sig[i] = self._sig(leaves)
+        ring.sig[i] = sig
+
+    def _flat(self, batch):
+        """(spec, leaves, shapes, addresses) of a batch; the batch named as ``next_data`` at the previous call is
+        looked up instead of being walked again."""
+        c = self._flat_cache
+        if c is not None and c[0] is batch:
+            return c[1]
+        leaves: List[torch.Tensor] = []
+        spec = _flatten(batch, leaves)
+        return spec, leaves, tuple((t.shape, t.dtype) for t in leaves), self._sig(leaves)
 
     def _ring_step(self, data, next_data):
         """The step through the three-set ring, or None when this batch does not take that path."""
-        rt = core.runtime()
-        leaves: List[torch.Tensor] = []
-        spec = _flatten(data, leaves)
+        setattr_ = object.__setattr__          # plain attributes: nn.Module's bookkeeping costs microseconds per write
+        spec, leaves, shapes, sig = self._flat(data)
         if not _is_static(spec):
             return None
-        nleaves: List[torch.Tensor] = []
-        if _flatten(next_data, nleaves) != spec or [(t.shape, t.dtype) for t in nleaves] != [(t.shape, t.dtype) for t in leaves]:
+        nflat = self._flat(next_data)
+        nspec, nleaves, nshapes, nsig = nflat
+        if nspec != spec or nshapes != shapes:
             return None          # the following batch has another shape (a shorter last batch): no run-ahead for it
-        key = (spec, tuple((t.shape, t.dtype) for t in leaves))
+        setattr_(self, "_flat_cache", (next_data, nflat))
+        key = (spec, shapes)
         ring = self._rings.get(key)
         if ring is None:
             if self._rings or self._ring_refused or self._eager_steps < self._graph_warmup or key in self._graphs:
@@ -568,31 +579,36 @@ class Model(nn.Module):
             self._status_poll.tick()
         main = torch.cuda.current_stream()
         cur = ring.turn
-        warm = ring.sig[cur] == self._sig(leaves) and all(lk._front is _FRONT_IN_GRAPH for lk in ring.links)
+        warm = ring.sig[cur] == sig and all(lk._front is _FRONT_IN_GRAPH for lk in ring.links)
         if not warm:
             # (re)start: whatever front is pending belongs to another batch
             for lk in ring.links:
                 if lk._front is not None:
                     lk.discard_front()
             cur = ring.turn = 0
-            self._stage(ring, 0, leaves)
+            self._stage(ring, 0, leaves, sig, main)
         nxt = (cur + 1) % ring.SETS
-        self._stage(ring, nxt, nleaves)
-        if self.optimizer is not None:
-            self.optimizer.table.set_lr(self.optimizer._lr())
-        (ring.warm[cur] if warm else ring.cold).replay()
+        self._stage(ring, nxt, nleaves, nsig, main)
+        opt = self.optimizer
+        if opt is not None:
+            opt.table.set_lr(opt._lr())
+        graph = ring.warm[cur] if warm else ring.cold
+        graph.replay()
         ring.done[cur].record(main)
         ring.done_recorded[cur] = True
         for lk in ring.links:
             lk._front = _FRONT_IN_GRAPH
         ring.turn = nxt
-        if self.optimizer is not None:
-            self.optimizer.iterations += 1
-            self.optimizer.table.step_count += 1
-        self._loss_steps += self._graph_loss_steps
+        if opt is not None:
+            opt.iterations += 1
+            opt.table.step_count += 1
         loss = ring.loss[cur] if warm else ring.cold_loss
-        self._graph, self._graph_key, self._static_leaves, self._static_loss = (ring.warm[cur] if warm else ring.cold), key, ring.leaves[cur], loss
-        self._last_done = ring.done[cur]
+        setattr_(self, "_loss_steps", self._loss_steps + self._graph_loss_steps)
+        setattr_(self, "_graph", graph)
+        setattr_(self, "_graph_key", key)
+        setattr_(self, "_static_leaves", ring.leaves[cur])
+        setattr_(self, "_static_loss", loss)
+        setattr_(self, "_last_done", ring.done[cur])
         return loss
 
     def _capture_ring(self, spec, leaves, nleaves, key):
