@@ -44,7 +44,7 @@ def peaks():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm_fwd", "gemm_dgrad", "gemm_wgrad", "gemm_big", "sparse", "deepfm", "deepfm_head", "mlp_chain", "dense", "small_ops"])
+    ap.add_argument("case", choices=["gemm_fwd", "gemm_dgrad", "gemm_wgrad", "gemm_big", "sparse", "sparse_front", "deepfm", "deepfm_head", "mlp_chain", "dense", "small_ops"])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--batch", type=int, default=8192)
     a = ap.parse_args()
@@ -182,6 +182,30 @@ def main():
         flops = 2.0 * B * 400 * (430 + 401 + 401)
         res = {"chain_fwd": timed(fwd, a.iters), "chain_bwd": timed(bwd, a.iters), "three_gemm_launches_fwd": timed(layers_fwd, a.iters)}
         out.update(us=res, tflops={k: flops / v / 1e6 for k, v in res.items()}, shape=[B, 429, 400, 400, 400])
+    elif a.case == "sparse_front":
+        # the pull split in two: front (dedup, id dispatch, inverse map; plain kernels that run ahead under the previous
+        # step) and the probe-only pull that follows it, on the DeepFM batch
+        import bench
+        from tensornet_b200.ops.sparse_table_gpu import GpuSparseTable
+        B, S, dim = a.batch, 26, 20
+        data = [b[0].reshape(-1) for b in bench.make_batches(8, B, 3846154, dev, 5)]
+        t = GpuSparseTable(tn.core.Adam(learning_rate=1e-3, initial_scale=0.1), dim, rows=1 << 22)
+        lk = t.link(B * S)
+        for ids in data + data:
+            lk.pull(ids, training=True); lk.push()
+        k = [0]
+        def front():
+            lk.prefetch(data[k[0] % 8])
+        def back():
+            lk.pull(data[k[0] % 8], training=True); lk.push(); k[0] += 1
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        tf, tb = [], []
+        for _ in range(a.iters + 3):
+            ev[0].record(); front(); ev[1].record(); back(); ev[2].record()
+            torch.cuda.synchronize()
+            tf.append(ev[0].elapsed_time(ev[1]) * 1e3); tb.append(ev[1].elapsed_time(ev[2]) * 1e3)
+        tf, tb = sorted(tf[3:]), sorted(tb[3:])
+        out.update(front_us=tf[len(tf) // 2], probe_only_pull_plus_push_us=tb[len(tb) // 2], phases_us=[round(x, 1) for x in lk.pull_phase_us()])
     elif a.case == "deepfm":
         import bench
         slots = [str(i) for i in range(1, 27)]

@@ -319,3 +319,20 @@ def test_cpu_affinity_follows_the_mask_nvml_gives(monkeypatch):
     monkeypatch.setitem(sys.modules, "pynvml", None)                              # import fails: nothing happens
     rtmod._bind_cpus_near(0)
     assert len(calls) == 1
+
+
+def test_lookahead_pairs_every_batch_with_its_successor():
+    from tensornet_b200.model.model import _with_next
+
+    assert list(_with_next(iter([]))) == []
+    assert list(_with_next(iter([7]))) == [(7, None)]
+    assert list(_with_next(iter("abc"))) == [("a", "b"), ("b", "c"), ("c", None)]
+    seen = []
+
+    def gen():
+        for k in range(4):
+            seen.append(k)
+            yield k
+
+    it = _with_next(gen())
+    assert next(it) == (0, 1) and seen == [0, 1]          # exactly one batch ahead of the consumer
