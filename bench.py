@@ -230,6 +230,9 @@ def main():
     if args.gpus > 1 and "RANK" not in os.environ:
         raise SystemExit("for --gpus N > 1 launch with: python -m torch.distributed.run --nproc-per-node N bench.py --gpus N ...")
     tn.core.init()
+    # every rank draws batches of one shape at every step, so the captured steps may start the next batch's pull
+    # (dedup + id dispatch) ahead on several GPUs too; one GPU does so by default
+    tn.core.config.pull_front_ahead = 1
     rt = tn.core.runtime()
     assert rt.on_gpu, "bench.py needs a CUDA device"
     assert rt.world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE is {rt.world}"

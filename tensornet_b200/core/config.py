@@ -52,8 +52,10 @@ class Config:
     #: stream / event / copy calls
     native_step_path: bool = True
     #: when the caller names the batch of the following step (`fit` does), its dedup and id dispatch run on a second
-    #: stream under the current step's forward / backward, and the pull of that step only probes and returns rows
-    pull_front_ahead: bool = True
+    #: stream under the current step's forward / backward, and the pull of that step only probes and returns rows.
+    #: -1 = on one GPU only; 1 = also on several GPUs, where the caller then guarantees that all ranks change batch
+    #: shape (a shorter last batch) at the same step: a rank cannot leave the two-step pull protocol alone; 0 = never
+    pull_front_ahead: int = -1
     #: several GPUs: bind each process to the CPU cores closest to its GPU (NVML's affinity mask) before it allocates
     #: page-locked buffers
     bind_cpu_affinity: bool = True
@@ -98,7 +100,7 @@ class Config:
         c.overlap_dense_sms = _env("TN_OVERLAP_DENSE_SMS", c.overlap_dense_sms, int)
         c.nvtx_phases = _env("TN_NVTX_PHASES", c.nvtx_phases, bool)
         c.native_step_path = _env("TN_NATIVE_STEP_PATH", c.native_step_path, bool)
-        c.pull_front_ahead = _env("TN_PULL_FRONT_AHEAD", c.pull_front_ahead, bool)
+        c.pull_front_ahead = _env("TN_PULL_FRONT_AHEAD", c.pull_front_ahead, int)
         c.bind_cpu_affinity = _env("TN_BIND_CPU_AFFINITY", c.bind_cpu_affinity, bool)
         c.dense_rides_push = _env("TN_DENSE_RIDES_PUSH", c.dense_rides_push, bool)
         c.checkpoint_chunk_rows = _env("TN_CKPT_CHUNK_ROWS", c.checkpoint_chunk_rows, int)

@@ -347,10 +347,16 @@ class Model(nn.Module):
         for layer in self.sparse_layers():
             layer.backwards(grads_and_vars)
 
+    @staticmethod
+    def _front_ahead_on() -> bool:
+        rt = core.runtime()
+        mode = int(core.config.pull_front_ahead)
+        return bool(rt.on_gpu and (mode > 0 or (mode < 0 and rt.world == 1)))
+
     def _front_layers(self, next_features):
         """(layer, ids) for every sparse layer whose next pull can be started ahead for ``next_features``; empty
         unless ALL trainable sparse layers of the model qualify (a step either runs every front ahead or none)."""
-        if next_features is None or not core.config.pull_front_ahead or not core.runtime().on_gpu:
+        if next_features is None or not self._front_ahead_on():
             return []
         out = []
         for layer in self.sparse_layers():
@@ -456,7 +462,7 @@ class Model(nn.Module):
         ``next_data``: the batch that will be passed as ``data`` at the next call (same tensors, unchanged).  On the
         captured path its sparse ids are deduplicated and sent to their owners on a second stream while this step
         runs, so the next step's pull only probes and returns rows.  ``fit`` passes it by itself."""
-        if next_data is not None and self._use_graph and core.config.pull_front_ahead and core.runtime().on_gpu:
+        if next_data is not None and self._use_graph and self._front_ahead_on():
             loss = self._ring_step(data, next_data)
             if loss is not None:
                 return loss
@@ -471,7 +477,7 @@ class Model(nn.Module):
         leaves: List[torch.Tensor] = []
         spec = _flatten((features, labels), leaves)
         key = (spec, tuple((t.shape, t.dtype) for t in leaves))
-        what = graph_decision(rt.world, key in self._graphs, _is_static(spec), len(self._graphs), self._max_graphs,
+        what = graph_decision(rt.world, key in self._graphs, _is_static(spec), len(self._graphs) + len(self._rings), self._max_graphs,
                               self._eager_steps, self._graph_warmup)
         if what == "eager":
             self._eager_steps += 1
@@ -879,7 +885,7 @@ class Model(nn.Module):
                     self.reset_metrics()
                 last = None
                 issued = collected = 0       # losses copied to / read from the pinned ring (the host runs up to _LOSS_RING - 1 steps ahead)
-                ahead = gpu and self._use_graph and core.config.pull_front_ahead
+                ahead = gpu and self._use_graph and self._front_ahead_on()
                 for i, (batch, nxt) in enumerate(_with_next(self._batch_source(dataset, prefetch))):
                     if steps_per_epoch is not None and i >= steps_per_epoch:
                         break

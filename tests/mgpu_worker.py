@@ -35,6 +35,7 @@ def main():
     # every step names the batch of the following one, as `fit` does: after the warm-up the captured steps run that
     # batch's dedup and id dispatch ahead on a second stream (the last step names a batch that never comes: its
     # front is discarded by whatever touches the tables next)
+    tn.core.config.pull_front_ahead = 1      # every rank feeds batches of one shape at every step
     order = [data[k % len(data)] for k in range(5 * len(data) + 1)]
     for k in range(5 * len(data)):
         if True:

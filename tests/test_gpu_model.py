@@ -240,7 +240,7 @@ def test_pull_front_run_ahead_in_the_captured_ring_matches_the_plain_path(tn_gpu
     B = 512
     runs = []
     for ahead in (True, False):
-        tn.core.config.pull_front_ahead = ahead
+        tn.core.config.pull_front_ahead = 1 if ahead else 0
         try:
             m, slots = _make(tn, graph=True, seed=7, share=share)
             data = _batches(tn, slots, B, 7, seed=9)
@@ -252,7 +252,7 @@ def test_pull_front_run_ahead_in_the_captured_ring_matches_the_plain_path(tn_gpu
             assert bool(m._rings) == ahead, "the ring of captured steps was %sused" % ("not " if ahead else "")
             runs.append((h1["step_loss"] + h2["step_loss"], ev))
         finally:
-            tn.core.config.pull_front_ahead = True
+            tn.core.config.pull_front_ahead = -1
     (la, ea), (lb, eb) = runs
     assert len(la) == len(lb) == 35
     for a, b in zip(la, lb):
