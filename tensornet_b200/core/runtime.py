@@ -185,6 +185,29 @@ class Runtime:
                     w.wait()
         return recv
 
+    def exchange_bytes_many(self, exchanges):
+        """Several :meth:`exchange_bytes` at once: ``exchanges`` is a list of ``(send, recv_sizes)``; all messages are
+        posted together and waited for together, so N independent all-to-alls cost one round trip instead of N.
+        Messages between one pair of ranks are matched in posting order, which is the same on every rank."""
+        recvs = []
+        for send, recv_sizes in exchanges:
+            recv = [torch.empty(int(n), dtype=torch.uint8) for n in recv_sizes]
+            recv[self.rank] = send[self.rank]
+            recvs.append(recv)
+        if self.world > 1:
+            ops = []
+            for (send, _), recv in zip(exchanges, recvs):
+                for k in range(1, self.world):
+                    dst, src = (self.rank + k) % self.world, (self.rank - k) % self.world
+                    if send[dst].numel():
+                        ops.append(dist.P2POp(dist.isend, send[dst].contiguous(), dst, group=self.host_group))
+                    if recv[src].numel():
+                        ops.append(dist.P2POp(dist.irecv, recv[src], src, group=self.host_group))
+            if ops:
+                for w in dist.batch_isend_irecv(ops):
+                    w.wait()
+        return recvs
+
     def broadcast_object(self, obj, src: int = 0):
         if self.world == 1:
             return obj

@@ -1038,6 +1038,49 @@ py::array_t<float> init_weights(uint64_t seed, py::array_t<uint64_t, py::array::
 #define TORCH_EXTENSION_NAME _tn_cpu
 #endif
 
+// One dense optimizer step over a flat fp32 array in a single pass (the CPU path's counterpart of the fused dense
+// kernel): Adam as in core/ps/optimizer/adam_kernel.cc:46-55 (alpha carries both beta powers, no bias correction of
+// the moments themselves), AdaGrad with decayed statistics and momentum as in ada_grad_kernel.cc:42-48.  The
+// gradient is zeroed on the way.  All arrays are contiguous float32 numpy views of the table's tensors.
+void dense_step(int kind, py::array_t<float> w_, py::array_t<float> g_, py::array_t<float> s0_, py::array_t<float> s1_,
+                py::array_t<float> s2_, double lr, double alpha, double beta1, double beta2, double eps,
+                double grad_decay, double mom_decay) {
+  float* w = w_.mutable_data();
+  float* g = g_.mutable_data();
+  float* s0 = s0_.mutable_data();
+  float* s1 = s1_.mutable_data();
+  float* s2 = s2_.size() ? s2_.mutable_data() : nullptr;
+  const ssize_t n = w_.size();
+  if (g_.size() != n || s0_.size() != n || s1_.size() != n) throw std::runtime_error("dense_step: array sizes differ");
+  py::gil_scoped_release rel;
+  if (kind == tn::kAdam) {
+    const float a = (float)alpha, b1 = (float)beta1, b2 = (float)beta2, e = (float)eps;
+    for (ssize_t i = 0; i < n; ++i) {
+      const float x = g[i];
+      const float m = s0[i] + (x - s0[i]) * (1.f - b1);
+      const float v = s1[i] + (x * x - s1[i]) * (1.f - b2);
+      s0[i] = m;
+      s1[i] = v;
+      w[i] -= m * a / (std::sqrt(v) + e);
+      g[i] = 0.f;
+    }
+  } else {
+    if (!s2 || s2_.size() != n) throw std::runtime_error("dense_step: AdaGrad needs the momentum array");
+    const float gd = (float)grad_decay, md = (float)mom_decay, l = (float)lr, e = (float)eps;
+    for (ssize_t i = 0; i < n; ++i) {
+      const float x = g[i];
+      const float c = s0[i] * gd + 1.f;
+      const float q = s1[i] * gd + x * x;
+      const float m = s2[i] + (x - s2[i]) * (1.f - md);
+      s0[i] = c;
+      s1[i] = q;
+      s2[i] = m;
+      w[i] -= l * m / (std::sqrt(q) / std::sqrt(c) + e);
+      g[i] = 0.f;
+    }
+  }
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   py::class_<CpuSparseTable>(m, "CpuSparseTable")
       .def(py::init<py::dict, int, bool, int, int>())
@@ -1061,6 +1104,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   py::class_<DictionaryReader>(m, "DictionaryReader")
       .def(py::init<const std::string&>())
       .def("next", &DictionaryReader::next, py::arg("max_rows"));
+  m.def("dense_step", &dense_step);
   m.def("list_block_files", &list_block_files);
   m.def("unique_first_occurrence", &unique_first_occurrence);
   m.def("write_sparse_dir", &write_sparse_dir);

@@ -57,18 +57,21 @@ class EmbeddingFeatures(nn.Module):
         self.out_dim = dim + (2 if self.use_cvm else 0)
         self._anchor = torch.zeros(1, requires_grad=True, device=core.runtime().device)
         self._pending_push = False
+        self._args_cache = None
 
     # --------------------------------------------------------------------------------
     @property
     def feature_columns(self):
         return self._feature_columns
 
-    def forward(self, features: Dict, training: Optional[bool] = None):
-        if not isinstance(features, dict):
-            raise ValueError("We expected a dictionary here. Instead we got: ", features)
-        training = self.training if training is None else bool(training)
+    def _pull_args(self, features: Dict, training: bool):
+        """What this layer's pull needs from a batch: ``(ids, offsets, B, labels, label_mod, count)``.  A model that
+        runs several layers' pulls with shared round trips asks for them first; the ``forward`` of the same batch
+        then finds them here (once) instead of gathering the columns again."""
+        c, self._args_cache = self._args_cache, None
+        if c is not None and c[0] is features and c[1] == training:
+            return c[2]
         dev = core.runtime().device
-        self.table.set_training(training)
         ids, offsets, B = gather_columns(features, self._keys, dev)
         S = len(self._keys)
         labels, label_mod = None, 0
@@ -79,7 +82,20 @@ class EmbeddingFeatures(nn.Module):
             else:
                 lens = (offsets[1:] - offsets[:-1]).long()
                 labels = torch.repeat_interleave(y.repeat(S), lens, output_size=int(ids.numel()))
-        count = training and self.trainable
+        return ids, offsets, B, labels, label_mod, training and self.trainable
+
+    def stash_pull_args(self, features: Dict, training: bool):
+        args = self._pull_args(features, training)
+        self._args_cache = (features, training, args)
+        return args
+
+    def forward(self, features: Dict, training: Optional[bool] = None):
+        if not isinstance(features, dict):
+            raise ValueError("We expected a dictionary here. Instead we got: ", features)
+        training = self.training if training is None else bool(training)
+        self.table.set_training(training)
+        ids, offsets, B, labels, label_mod, count = self._pull_args(features, training)
+        S = len(self._keys)
         out = pull_pool(self._anchor, self.link, ids, offsets, B, S, self.combiner, labels, label_mod, count)
         self._pending_push = count
         if self.is_concat:

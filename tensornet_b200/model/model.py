@@ -344,8 +344,40 @@ class Model(nn.Module):
         return F.bce_with_logits(logits, labels, self._sums)
 
     def backwards(self, grads_and_vars=None):
-        for layer in self.sparse_layers():
+        layers = self.sparse_layers()
+        rt = core.runtime()
+        if not rt.on_gpu and rt.world > 1:
+            # CPU ranks: the gradient records of all embedding layers travel in one round trip
+            from ..ops.sparse_table_cpu import CpuSparseLink
+            pend = [l for l in layers if getattr(l, "_pending_push", False) and isinstance(getattr(l, "link", None), CpuSparseLink)]
+            # with a handful of ranks the dense gradient rides in the same round: everybody sends its gradient to
+            # everybody and takes the mean itself (an all-gather; beyond four ranks the all-reduce is the cheaper form)
+            dense = None
+            if (pend and rt.world <= 4 and self.optimizer is not None and self.optimizer.table.initialized
+                    and grads_and_vars is None and not getattr(self, "_dense_exchange_off", False)):
+                dense = self.optimizer.table
+            if len(pend) > 1 or dense is not None:
+                CpuSparseLink.push_many([l.link for l in pend], dense)
+                for l in pend:
+                    l._pending_push = False
+        for layer in layers:
             layer.backwards(grads_and_vars)
+
+    def _cpu_pulls_together(self, features):
+        """CPU ranks: run the pulls of all embedding layers of a step with shared round trips (ids of every layer in
+        one exchange, rows in a second one) before the forward pass asks for them layer by layer."""
+        rt = core.runtime()
+        if rt.on_gpu or rt.world == 1 or not isinstance(features, dict):
+            return
+        from ..ops.sparse_table_cpu import CpuSparseLink
+        calls = []
+        for layer in self.sparse_layers():
+            if hasattr(layer, "stash_pull_args") and isinstance(getattr(layer, "link", None), CpuSparseLink):
+                layer.table.set_training(True)
+                ids, _, _, labels, label_mod, count = layer.stash_pull_args(features, True)
+                calls.append((layer.link, ids, labels, label_mod, count))
+        if len(calls) > 1:
+            CpuSparseLink.pull_many(calls)
 
     @staticmethod
     def _front_ahead_on() -> bool:
@@ -391,6 +423,8 @@ class Model(nn.Module):
                 self._loss_steps += 1
         if loss is None:
             with phase("tn.forward"):
+                if self.training:
+                    self._cpu_pulls_together(features)
                 logits = self(features)
                 loss, pred = self._loss(logits, labels)
             for m in self._host_metrics:
@@ -1096,6 +1130,8 @@ class PCGradModel(Model):
     """Multi-task variant: ``forward`` returns one logit column per task; every task loss is
     back-propagated separately and the dense gradients are combined by PCGrad
     (tensornet/model/Model.py:259-293, tensornet/model/compile_utils.py:55-126)."""
+
+    _dense_exchange_off = True      # the projected gradient is written after the sparse pushes: it travels by itself
 
     def _front_layers(self, next_features):
         return []          # this step runs several backward passes per pull; it does not start pulls ahead

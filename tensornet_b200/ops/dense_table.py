@@ -36,6 +36,7 @@ class DenseTable:
                              "core/ps/optimizer/ftrl_kernel.cc:24-32)")
         self.opt = opt
         self.initialized = False
+        self.grad_pre_reduced = False      # CPU ranks: the next step finds the mean gradient in G already
         self.step_count = 0
         self.names: List[str] = []
         self.offsets: List[int] = []
@@ -148,11 +149,26 @@ class DenseTable:
                 self.ctx.step(bool(peers_past_backward and self.world > 1))
             return
         with torch.no_grad():
-            if self.world > 1:
+            reduced, self.grad_pre_reduced = self.grad_pre_reduced, False
+            if self.world > 1 and not reduced:        # (a caller that exchanged the gradient itself left the mean in G)
                 dist.all_reduce(self.G, group=rt.host_group)
                 self.G.div_(self.world)
             g, w = self.G, self.W
             o = self.opt
+            if all(t.is_contiguous() and t.dtype == torch.float32 for t in (g, w, self.s0, self.s1)):
+                # one native pass over the flat arrays instead of a dozen tensor-op passes
+                import numpy as np
+                alpha = 0.0
+                if o.kind == KIND_ADAM:
+                    self.state[0] *= o.beta1
+                    self.state[1] *= o.beta2
+                    alpha = float(self.lr * torch.sqrt(1 - self.state[1]) / (1 - self.state[0]))
+                s2 = self.s2.numpy() if self.s2 is not None else np.zeros(0, np.float32)
+                _build.cpu_ext().dense_step(int(o.kind), w.detach().numpy().reshape(-1), g.numpy().reshape(-1), self.s0.numpy(),
+                                            self.s1.numpy(), s2, float(self.lr), alpha, float(getattr(o, "beta1", 0.0)),
+                                            float(getattr(o, "beta2", 0.0)), float(o.epsilon),
+                                            float(getattr(o, "grad_decay_rate", 1.0)), float(getattr(o, "mom_decay_rate", 1.0)))
+                return
             if o.kind == KIND_ADAM:   # core/ps/optimizer/adam_kernel.cc:46-55
                 self.state[0] *= o.beta1
                 self.state[1] *= o.beta2
