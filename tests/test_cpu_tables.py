@@ -99,3 +99,36 @@ def test_unknown_hyper_parameter_is_rejected():
         tn.core.Adam(learnin_rate=0.1)
     with pytest.raises(ValueError):
         tn.core.AdaGrad(elimination_logic=2)
+
+
+@pytest.mark.parametrize("kind", ["Adam", "AdaGrad"])
+def test_native_dense_step_matches_the_reference_formulas(kind):
+    """The one-pass dense optimizer step of the CPU path against the update rules written out in numpy
+    (core/ps/optimizer/adam_kernel.cc:46-55, ada_grad_kernel.cc:42-48); the gradient is zeroed on the way."""
+    from tensornet_b200 import _build
+
+    ext = _build.cpu_ext()
+    rng = np.random.default_rng(4)
+    n = 1003
+    w = rng.standard_normal(n).astype(np.float32)
+    g = rng.standard_normal(n).astype(np.float32)
+    s0 = np.abs(rng.standard_normal(n)).astype(np.float32)
+    s1 = np.abs(rng.standard_normal(n)).astype(np.float32) + 0.1
+    s2 = rng.standard_normal(n).astype(np.float32)
+    lr, b1, b2, eps, gd, md = 0.01, 0.9, 0.999, 1e-8, 0.98, 0.95
+    w0, g0, a0, a1, a2 = w.copy(), g.copy(), s0.copy(), s1.copy(), s2.copy()
+    if kind == "Adam":
+        alpha = lr * np.sqrt(1 - b2 ** 3) / (1 - b1 ** 3)
+        ext.dense_step(1, w, g, s0, s1, np.zeros(0, np.float32), lr, alpha, b1, b2, eps, 1.0, 1.0)
+        m = a0 + (g0 - a0) * (1 - b1)
+        v = a1 + (g0 * g0 - a1) * (1 - b2)
+        assert np.allclose(s0, m, rtol=1e-5, atol=1e-6) and np.allclose(s1, v, rtol=1e-5, atol=1e-6)
+        assert np.allclose(w, w0 - m * alpha / (np.sqrt(v) + eps), rtol=1e-5, atol=1e-6)
+    else:
+        ext.dense_step(0, w, g, s0, s1, s2, lr, 0.0, 0.0, 0.0, eps, gd, md)
+        c = a0 * gd + 1
+        q = a1 * gd + g0 * g0
+        m = a2 + (g0 - a2) * (1 - md)
+        assert np.allclose(s0, c, rtol=1e-5) and np.allclose(s1, q, rtol=1e-5) and np.allclose(s2, m, rtol=1e-5, atol=1e-6)
+        assert np.allclose(w, w0 - lr * m / (np.sqrt(q) / np.sqrt(c) + eps), rtol=1e-5, atol=1e-6)
+    assert not g.any()
