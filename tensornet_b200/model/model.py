@@ -920,9 +920,11 @@ class Model(nn.Module):
                 last = None
                 issued = collected = 0       # losses copied to / read from the pinned ring (the host runs up to _LOSS_RING - 1 steps ahead)
                 ahead = gpu and self._use_graph and self._front_ahead_on()
-                for i, (batch, nxt) in enumerate(_with_next(self._batch_source(dataset, prefetch))):
-                    if steps_per_epoch is not None and i >= steps_per_epoch:
-                        break
+                source = self._batch_source(dataset, prefetch)
+                if steps_per_epoch is not None:
+                    import itertools
+                    source = itertools.islice(source, int(steps_per_epoch))      # the look-ahead stays inside the pass
+                for i, (batch, nxt) in enumerate(_with_next(source)):
                     # the last batch of a pass names itself as its successor: the step stays on the same captured path
                     last = self.train_step(batch, (nxt if nxt is not None else batch) if ahead else None)
                     if record_step_loss:

@@ -422,6 +422,7 @@ class GpuSparseLink:
         for k in ("req_row", "req_ou", "ou_row"):
             l[k].fill_(-1)
         self.arena.tensor("sig").zero_()
+        self._front = None           # a pull front that ran ahead is gone with the counters it built
 
     def pull_phase_us(self):
         """Durations (microseconds) of the last pull's phases as seen by CTA 0: dedup; id dispatch + inverse map;

@@ -177,3 +177,20 @@ def test_profile_batches_writes_a_trace(tmp_path):
     assert cb.trace_path and os.path.getsize(cb.trace_path) > 0
     with open(cb.trace_path) as f:
         assert "traceEvents" in json.load(f)
+
+
+def test_steps_per_epoch_consumes_exactly_that_many_batches_of_a_shared_iterator():
+    """`fit` looks one batch ahead; with `steps_per_epoch` the look-ahead must not eat a batch of the next pass."""
+    data = _data(n_batches=10)
+    taken = []
+
+    def gen():
+        for k, b in enumerate(data):
+            taken.append(k)
+            yield b
+
+    it = gen()
+    m = _model([])
+    h = m.fit(it, epochs=3, steps_per_epoch=3, record_step_loss=True)
+    assert len(h["step_loss"]) == 9
+    assert taken == list(range(9))
