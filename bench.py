@@ -268,16 +268,22 @@ def main():
 
     pool = max(args.pool, args.warmup + K)
     drawn = make_batches(pool, B, ranks_per_slot, dev, seed=1000 + rt.rank)
-    # ids, dense features and labels cycle with different periods (pool, pool-3, pool-5; pairwise coprime for the
-    # default pool), so no (ids, labels) pairing comes back within a run and the random labels cannot be memorised
-    per = (pool, max(pool - 3, 1), max(pool - 5, 1))
-    host_drawn = [tuple(t.cpu().pin_memory() for t in b) for b in drawn]
+    # Ids and dense features cycle with different periods (pool, pool-3); the labels come from a pool of their own with
+    # a prime number of batches (32 KB each), so that no (ids, labels) pairing returns within a run: with only a few
+    # dozen label batches a one-GPU run sees each pairing twice and the embeddings of rare ids learn the random labels
+    # by heart, which says nothing about speed but makes the reported loss meaningless.
+    per = (pool, max(pool - 3, 1))
+    n_lab = 4099
+    lab_gen = torch.Generator(device=dev).manual_seed(77 + rt.rank)
+    label_pool = (torch.rand((n_lab, B), generator=lab_gen, device=dev) < 0.25).float()
+    host_drawn = [tuple(t.cpu().pin_memory() for t in b[:2]) for b in drawn]
+    host_labels = label_pool.cpu().pin_memory()
 
     def dev_batch(k):
-        return drawn[k % per[0]][0], drawn[k % per[1]][1], drawn[k % per[2]][2]
+        return drawn[k % per[0]][0], drawn[k % per[1]][1], label_pool[k % n_lab]
 
     def host_batch(k):
-        return host_drawn[k % per[0]][0], host_drawn[k % per[1]][1], host_drawn[k % per[2]][2]
+        return host_drawn[k % per[0]][0], host_drawn[k % per[1]][1], host_labels[k % n_lab]
 
     def feats(ids, dense):
         return {tn.data.PACKED_KEY: tn.data.PackedFeatures(slots, ids=ids), "dense": dense}
@@ -389,7 +395,7 @@ def main():
     med, e2e_med = statistics.median(blocks), statistics.median(e2e_blocks)
     value = G * K / (med / 1e3)
     e2e = G * K / (e2e_med / 1e3)
-    h2d = sum(t.numel() * t.element_size() for t in host_drawn[0])
+    h2d = sum(t.numel() * t.element_size() for t in host_batch(0))
 
     # ---------------- context arms (not the reference; for orientation) -------------------
     context = {}

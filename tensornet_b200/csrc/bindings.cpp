@@ -496,7 +496,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       // a page-locked source from torch's host allocator must not be handed out again before the copy has run
       // (what Tensor.copy_(non_blocking=True) does behind the scenes); a no-op for other host memory
       if (h.is_pinned())
-        at::getHostAllocator(at::kCUDA)->record_event(h.data_ptr(), h.storage().data_ptr().get_context(),
+        at::getHostAllocator(at::kCUDA)->record_event(const_cast<void*>(h.storage().data()), h.storage().data_ptr().get_context(),
                                                       c10::cuda::getStreamFromExternal(cs, d.device().index()).unwrap());
     }
     check(cudaEventRecord(reinterpret_cast<cudaEvent_t>(copied_event), cs), "cudaEventRecord");
