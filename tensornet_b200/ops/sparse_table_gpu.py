@@ -382,7 +382,8 @@ class GpuSparseLink:
     def prefetch(self, ids: torch.Tensor):
         """Run the front of the pull (dedup, id dispatch to the owners, inverse map) for the batch ``ids`` on the
         current stream.  The next :meth:`pull` must be a training pull of this very tensor; it then only probes and
-        returns rows.  Anything else discards the front (:meth:`discard_front`)."""
+        returns rows.  Anything else discards the front (:meth:`discard_front`).  ``ids`` must not live in the
+        buffer of a batch whose backward pass is still to come: the inverse map of a front is kept per id buffer."""
         n = ids.numel()
         key = (ids.data_ptr(), n)
         inverse = self._front_inverse.get(key)
