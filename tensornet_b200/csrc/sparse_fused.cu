@@ -561,7 +561,11 @@ constexpr int kFrontThreads = 256;
 
 __global__ void __launch_bounds__(kFrontThreads) pull_front_dedup_kernel(const __grid_constant__ PullArgs a) {
   const SparseCommView& c = a.c;
-  if (ld_volatile_s32(c.status) != 0) return;
+  // one read per CTA: all its threads take the same way out (a CTA barrier follows in the shipping kernel)
+  __shared__ int s_bad;
+  if (threadIdx.x == 0) s_bad = ld_volatile_s32(c.status);
+  __syncthreads();
+  if (s_bad != 0) return;
   const int tid = blockIdx.x * blockDim.x + threadIdx.x;
   const int nth = gridDim.x * blockDim.x;
   const int lane = threadIdx.x & 31;
@@ -614,7 +618,11 @@ __global__ void __launch_bounds__(kFrontThreads) pull_front_dedup_kernel(const _
 
 __global__ void __launch_bounds__(kFrontThreads) pull_front_ship_kernel(const __grid_constant__ PullArgs a) {
   const SparseCommView& c = a.c;
-  if (ld_volatile_s32(c.status) != 0) return;
+  // one read per CTA: all its threads take the same way out (a CTA barrier follows in the shipping kernel)
+  __shared__ int s_bad;
+  if (threadIdx.x == 0) s_bad = ld_volatile_s32(c.status);
+  __syncthreads();
+  if (s_bad != 0) return;
   const int tid = blockIdx.x * blockDim.x + threadIdx.x;
   const int nth = gridDim.x * blockDim.x;
   const int lane = threadIdx.x & 31;
