@@ -570,6 +570,7 @@ __global__ void __launch_bounds__(kFrontThreads) pull_front_dedup_kernel(const _
   const int nth = gridDim.x * blockDim.x;
   const int lane = threadIdx.x & 31;
   const int W = c.world, capo = c.capo;
+  if (c.prof != nullptr && tid == 0) c.prof[16] = globaltimer_ns();
   for (int base = tid - lane; base < a.n_ids; base += nth) {
     const int i = base + lane;
     bool winner = false;
@@ -614,6 +615,7 @@ __global__ void __launch_bounds__(kFrontThreads) pull_front_dedup_kernel(const _
       }
     }
   }
+  if (c.prof != nullptr && threadIdx.x == 0) atomicMax(&c.prof[17], globaltimer_ns());      // last CTA's end
 }
 
 __global__ void __launch_bounds__(kFrontThreads) pull_front_ship_kernel(const __grid_constant__ PullArgs a) {
@@ -667,6 +669,7 @@ __global__ void __launch_bounds__(kFrontThreads) pull_front_ship_kernel(const __
     v = __shfl_sync(same, v, leader);
     if (valid) a.inverse[i] = v;
   }
+  if (c.prof != nullptr && threadIdx.x == 0) atomicMax(&c.prof[18], globaltimer_ns());      // last CTA's end
 }
 
 // =======================================================================================

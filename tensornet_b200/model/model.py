@@ -262,6 +262,7 @@ class Model(nn.Module):
         self._rings: Dict[Any, _GraphRing] = {}      # same, for callers that name the following batch
         self._ring_refused = False
         self._flat_cache = None                      # (batch object, its flattened form) of the batch named as next
+        self._fronts_now = ()                        # (layer, next ids) of the step being issued
         self._last_done = None                       # event behind the last replayed step (None after an eager one)
         self._max_graphs = 8
         self._graph_key = None
@@ -403,8 +404,10 @@ class Model(nn.Module):
     def _step_impl(self, features, labels, next_features=None):
         fronts = self._front_layers(next_features) if self.training else []
         for layer, ids in fronts:
-            layer.link.next_ids = ids          # the link forks the front of the next batch right behind its pull
+            layer.link.next_ids = ids
+        object.__setattr__(self, "_fronts_now", fronts)
         loss = self._step_body(features, labels)
+        object.__setattr__(self, "_fronts_now", ())
         for layer, _ in fronts:
             lk = layer.link
             lk.next_ids = None
@@ -430,6 +433,8 @@ class Model(nn.Module):
             for m in self._host_metrics:
                 m.update_state(labels, pred)
         rt = core.runtime()
+        for layer, _ in self._fronts_now:          # forward pass issued: the next batch's pull fronts start here
+            layer.link.fork_front()
         with phase("tn.backward"):
             if rt.on_gpu and loss.dim() == 0 and loss.dtype == torch.float32:
                 loss.backward(self._unit_grad)      # a resident 1.0: autograd would otherwise launch a fill kernel for it

@@ -323,7 +323,7 @@ class GpuSparseLink:
             dd_keys=torch.full((dd_cap,), -1, dtype=torch.int64, device=d),
             dd_vals=torch.zeros(dd_cap, dtype=torch.int32, device=d),
             bar=torch.zeros(8, dtype=torch.int32, device=d),
-            prof=torch.zeros(16, dtype=torch.int64, device=d),
+            prof=torch.zeros(24, dtype=torch.int64, device=d),
         )
         self.arena = arena
         self._loc = loc
@@ -367,17 +367,21 @@ class GpuSparseLink:
         self._last_n_ids = n
         with phase("tn.sparse_pull"):
             self.ctx.pull(ids.reshape(-1), inverse, labels, int(label_mod), bool(training), bool(lookup_only), front_done)
-        nxt, self.next_ids = self.next_ids, None
-        if nxt is not None and training:
-            # the batch of the following step is known: its dedup and id dispatch run on a second stream from here on,
-            # under this step's forward and backward passes
-            self._fork.record()
-            side = front_stream(self.dev)
-            side.wait_event(self._fork)
-            with torch.cuda.stream(side):
-                self.prefetch(nxt)
-            self.front_in_flight = True
         return inverse
+
+    def fork_front(self):
+        """The batch of the following step is known (``next_ids``): run its dedup and id dispatch on the side stream
+        from this point of the current stream on.  The model calls this once the forward pass is issued, so the
+        front's atomics share the GPU with the backward GEMMs rather than with the gather of this step's rows."""
+        nxt, self.next_ids = self.next_ids, None
+        if nxt is None:
+            return
+        self._fork.record()
+        side = front_stream(self.dev)
+        side.wait_event(self._fork)
+        with torch.cuda.stream(side):
+            self.prefetch(nxt)
+        self.front_in_flight = True
 
     def prefetch(self, ids: torch.Tensor):
         """Run the front of the pull (dedup, id dispatch to the owners, inverse map) for the batch ``ids`` on the
@@ -431,6 +435,13 @@ class GpuSparseLink:
         completion flags + scratch clear."""
         t = self.prof.tolist()
         return [(t[i + 1] - t[i]) / 1e3 for i in range(5)]
+
+    def front_timeline_us(self):
+        """Where the last run-ahead pull front sat in time, in microseconds relative to the start of the last pull
+        kernel: (front start, end of its dedup kernel, end of its shipping / inverse kernel, end of the pull, start of
+        the last push, end of that push's row updates)."""
+        t = self.prof.tolist()
+        return [(t[i] - t[0]) / 1e3 for i in (16, 17, 18, 5, 8, 13)]
 
     def push_phase_us(self):
         """Durations (microseconds) of the last multi-GPU push's phases as seen by CTA 0: flags to the owners,
