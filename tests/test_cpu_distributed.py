@@ -120,3 +120,67 @@ tn.core.shutdown()
     for row in got["arrival"]:
         assert row == pytest.approx([w_arr, w_arr], rel=1e-5)
     assert abs(w_sum - w_arr) > 1e-3
+
+
+@pytest.mark.timeout(900)
+def test_shared_round_trips_give_what_one_by_one_exchanges_give(tmp_path):
+    """Two ranks, two tables: the pulls run together (`pull_many`: ids of both tables in one round, rows in a second)
+    and the pushes with the dense gradient riding along (`push_many`), against the same calls made one by one and a
+    plain all-reduce; pulled rows, tables after the push and the mean dense gradient must be identical."""
+    script = tmp_path / "w.py"
+    script.write_text('''
+import json, numpy as np, torch
+import torch.distributed as dist
+import tensornet_b200 as tn
+from tensornet_b200.ops.sparse_table_cpu import CpuSparseTable, CpuSparseLink
+from tensornet_b200.ops.dense_table import DenseTable
+tn.core.init()
+rt = tn.core.runtime()
+res = {}
+g = torch.Generator().manual_seed(5 + rt.rank)
+ids_a = torch.randint(1, 200, (96,), generator=g)
+ids_b = torch.randint(1, 50, (64,), generator=g)
+for mode in ("single", "many"):
+    ta = CpuSparseTable(tn.core.AdaGrad(learning_rate=0.1, initial_g2sum=0.5, initial_scale=0.3), 4)
+    tb = CpuSparseTable(tn.core.Adam(learning_rate=0.05, initial_scale=0.3), 2)
+    la, lb = ta.link(256), tb.link(256)
+    p = torch.nn.Parameter(torch.arange(16, dtype=torch.float32))
+    dt = DenseTable(tn.core.Adam(learning_rate=0.01)); dt.init([("p", p)])
+    for step in range(2):
+        if mode == "single":
+            ia, ib = la.pull(ids_a, training=True), lb.pull(ids_b, training=True)
+        else:
+            CpuSparseLink.pull_many([(la, ids_a, None, 0, True), (lb, ids_b, None, 0, True)])
+            ia, ib = la.pull(ids_a, training=True), lb.pull(ids_b, training=True)      # picked up, no exchange
+        Ua, Ub = la.U[ia.long()].clone(), lb.U[ib.long()].clone()
+        la.gU = (la.U[:, :4] * 0.5 + 0.1 * (rt.rank + 1)).clone()
+        lb.gU = (lb.U[:, :2] * 0.25 - 0.2 * (rt.rank + 1)).clone()
+        dt.G.copy_(torch.arange(dt.G.numel(), dtype=torch.float32) * (rt.rank + 1))
+        if mode == "single":
+            la.push(); lb.push()
+        else:
+            CpuSparseLink.push_many([la, lb], dt)
+            assert dt.grad_pre_reduced
+        mean_g = dt.G.clone()
+        if mode == "single":
+            dist.all_reduce(mean_g, group=rt.host_group); mean_g /= rt.world
+        dt.step()
+        rt.barrier()
+    ka, ra = ta.dump(); kb, rb = tb.dump()
+    oa, ob = np.argsort(ka), np.argsort(kb)
+    res[mode] = dict(Ua=Ua.tolist(), Ub=Ub.tolist(), ka=ka[oa].tolist(), ra=ra[oa].tolist(), kb=kb[ob].tolist(), rb=rb[ob].tolist(),
+                     g=mean_g.tolist(), w=dt.W.tolist())
+ok = all(np.allclose(np.array(res["single"][k], dtype=np.float64), np.array(res["many"][k], dtype=np.float64), rtol=1e-6, atol=1e-7)
+         for k in res["single"])
+oks = rt.all_gather_object(bool(ok))
+if rt.rank == 0:
+    print(json.dumps({"ok": all(oks), "rows_a": len(res["many"]["ka"])}))
+tn.core.shutdown()
+''')
+    env = dict(os.environ, TN_FORCE_CPU="1", OMP_NUM_THREADS="1", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), str(script)]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    got = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
+    assert got["ok"] and got["rows_a"] > 0
