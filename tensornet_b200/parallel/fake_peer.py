@@ -6,7 +6,11 @@ word with a wall-time budget and, when the budget runs out, records ``{code, pha
 skips the rest of its work and returns (csrc/tn_device.cuh ``wait_flag_ge``; csrc/sparse_fused.cu phases A2, B1, B2, C
 of the pull and A, B, C and the tail of the push).  In the push the payload does not move: a sender only raises
 "my records are complete", every owner reads its segment out of the sender's memory, answers "read", and the sender
-clears its records once every owner has answered.  This module restates that protocol with ``W`` ranks as threads of one process
+clears its records once every owner has answered.  The pull may also run in two steps: its front (dedup and id
+dispatch, flags carrying the NEXT step counter) one training step ahead, and the probe-only rest when the batch is
+due; a front that is not followed by its pull is discarded by moving the step counter on by one on every rank, so
+that the ids and flags it sent can never be taken for current ones (csrc/sparse_fused.cu ``pull_front_*``,
+``GpuSparseLink.prefetch`` / ``discard_front``).  This module restates that protocol with ``W`` ranks as threads of one process
 and numpy arrays as the "symmetric heap", on top of the CPU tables, so that the hand-shake order and the failure
 behaviour can be exercised without a GPU: a test may drop or delay any single flag and must see every rank return
 within the budget with the right peer named.  The reference's counterpart is the brpc retry loop that ends in
@@ -69,7 +73,7 @@ class FakeHeap:
         while True:
             with self._lock:
                 v = int(self.sig[receiver, kind, sender])
-            if (v >> 32) == epoch:
+            if (v >> 32) >= epoch:                                          # wait_flag_ge: this step's flag or a later one
                 return v & 0xFFFFFFFF
             if self.status[receiver, 0] != OK:                              # an earlier phase already failed
                 return None
@@ -88,23 +92,51 @@ class FakeRank:
         self.heap, self.rank, self.table, self.ext, self.dim = heap, rank, table, ext, dim
         self.epoch = 0
         self._route = None
+        self._front = None           # (ids, dedup results) of a pull front that ran ahead
 
     @property
     def failed(self) -> bool:
         return self.heap.status[self.rank, 0] != OK
 
-    def pull(self, ids: np.ndarray, labels: Optional[np.ndarray] = None):
-        """Returns ``(rows_of_unique_signs, inverse)`` or None when a wait ran out (status words say which)."""
+    def _dedup_and_dispatch(self, ids, labels, ep):
+        """Phases A and A2: dedup, split by owner, ids into the owners' inboxes, then the flags of step ``ep``."""
         h, R, W = self.heap, self.rank, self.heap.world
-        self.epoch += 1
-        ep = self.epoch
-        uniq, inv, show, click = self.ext.unique_first_occurrence(np.ascontiguousarray(ids, np.uint64), labels)   # phase A
+        uniq, inv, show, click = self.ext.unique_first_occurrence(np.ascontiguousarray(ids, np.uint64), labels)
         owner = (uniq % np.uint64(W)).astype(np.int64)
         order = np.argsort(owner, kind="stable")
         counts = np.bincount(owner, minlength=W)
         segs = np.split(uniq[order], np.cumsum(counts)[:-1])
-        for p in range(W):                                                   # phase A2: ids first, then the flag
+        for p in range(W):                                                   # ids first, then the flag
             h.post(K_PULL_REQ, R, p, segs[p], ep, len(segs[p]))
+        return uniq, inv, order, counts, show, click
+
+    def pull_front(self, ids: np.ndarray):
+        """The front of the NEXT step's pull, run while the current step computes: its flags carry the next step
+        counter; the counter itself moves when that pull runs."""
+        self._front = (np.array(ids, copy=True), self._dedup_and_dispatch(ids, None, self.epoch + 1))
+
+    def discard_front(self):
+        """The pull the front ran for is not coming: move the step counter past the flags it sent.  Every rank must
+        do this at the same point of the program."""
+        self._front = None
+        self.epoch += 1
+
+    def pull(self, ids: np.ndarray, labels: Optional[np.ndarray] = None):
+        """Returns ``(rows_of_unique_signs, inverse)`` or None when a wait ran out (status words say which)."""
+        h, R, W = self.heap, self.rank, self.heap.world
+        front, self._front = self._front, None
+        if front is not None and not np.array_equal(front[0], ids):
+            self._front = front
+            self.discard_front()
+            front = None
+        self.epoch += 1
+        ep = self.epoch
+        if front is not None:
+            uniq, inv, order, counts, show, click = front[1]                 # ids and flags of this step are out already
+            if labels is not None:                                           # show / click are counted by the probe-only pull
+                _, _, show, click = self.ext.unique_first_occurrence(np.ascontiguousarray(ids, np.uint64), labels)
+        else:
+            uniq, inv, order, counts, show, click = self._dedup_and_dispatch(ids, labels, ep)
         self._route = (uniq, order, counts, show, click)
         def serve(s):
             want = np.ascontiguousarray(h.box[R][(K_PULL_REQ, s)], np.uint64)
