@@ -678,6 +678,7 @@ class Model(nn.Module):
         for lk in ring.links:
             if lk._front is not None:
                 lk.discard_front()
+        hits0 = {id(lk): lk.front_hits for lk in ring.links}
         iters = self.optimizer.iterations if self.optimizer is not None else 0
         steps0 = self.optimizer.table.step_count if self.optimizer is not None else 0
         loss_steps0 = self._loss_steps
@@ -706,6 +707,11 @@ class Model(nn.Module):
         self._loss_steps = loss_steps0
         for lk in ring.links:
             lk._front = None                # nothing ran: no front is pending on the device
+        if any(lk.front_hits - hits0[id(lk)] < ring.SETS for lk in ring.links):
+            # a layer whose front ran but whose pull never came in the step (an embedding the forward pass does not
+            # use): its fronts would pile up unconsumed; such a model keeps the one-kernel pull
+            rt.barrier()
+            return None
         self._rings[key] = ring
         rt.barrier()                        # captures take a different time on every rank; line the ranks up again
         return ring

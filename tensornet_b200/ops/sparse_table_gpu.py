@@ -344,6 +344,7 @@ class GpuSparseLink:
         self._front = None
         self.next_ids = None         # set by the model before a step: the ids this link will pull at the NEXT step
         self.front_in_flight = False # a front was forked onto the side stream during this step (the model joins it)
+        self.front_hits = 0          # pulls that found their front done (a model checks that its layers really pull)
         self._fork = torch.cuda.Event() if runtime().on_gpu else None
         self._front_inverse = {}     # inverse buffers of the fronts, one per id buffer (stable addresses for CUDA graphs)
         if multi:
@@ -360,6 +361,7 @@ class GpuSparseLink:
         if front is not None:
             if front[0] == ids.data_ptr() and front[1] == n and training and not lookup_only and inverse is None:
                 inverse, front_done = front[2], True
+                self.front_hits += 1
             else:
                 self.discard_front()
         if inverse is None:
