@@ -4,6 +4,7 @@ Reports p50 / p99 latency (host wall clock per request batch incl. H2D of the id
 probabilities) and request batches / s.
 
     python benchmarks/serving_bench.py --requests 500
+    TN_FORCE_CPU=1 python benchmarks/serving_bench.py --requests 40          # CPU baseline: dictionary lookup + fp32 towers on the host
     torchrun --nproc-per-node 8 --master-addr 127.0.0.1 benchmarks/serving_bench.py --sharded     # dictionary sharded over the GPUs
 
 With ``--sharded`` every rank serves its own request batches while the lookups cross NVLink inside the fused pull
@@ -54,7 +55,8 @@ def main():
         u = rng.random((a.slots, a.batch))
         x = np.floor(((float(2 ** 40) ** (1 - s) - 1) * u + 1) ** (1 / (1 - s))).astype(np.int64)
         pick = signs[(x % len(signs))].view(np.int64)          # most requests hit the dictionary
-        return torch.from_numpy(np.where(rng.random((a.slots, a.batch)) < 0.9, pick, x)).pin_memory()
+        t = torch.from_numpy(np.where(rng.random((a.slots, a.batch)) < 0.9, pick, x))
+        return t.pin_memory() if rt.on_gpu else t          # TN_FORCE_CPU=1: the same requests through the CPU path (the baseline)
     reqs = [req() for _ in range(16)]
     for r in reqs[:4]:
         eng.infer(r).cpu()
