@@ -8,6 +8,7 @@ against full tables.  Ragged inputs run eagerly (no CUDA graph).  Prints one JSO
 
     python benchmarks/dcn_bench.py --steps 10
     torchrun --nproc-per-node 8 --master-addr 127.0.0.1 benchmarks/dcn_bench.py --steps 10 --universe 1000000000
+    TN_FORCE_CPU=1 python benchmarks/dcn_bench.py --steps 2 --warmup 1 --batch 512 --universe 200000     # CPU baseline (wall clock)
 """
 from __future__ import annotations
 
@@ -44,9 +45,10 @@ def make_batch(rng, B, S, mean_len, n_dense, ranks_per_slot):
     x = np.where(x > R, folded, x)
     slot = np.repeat(np.arange(S, dtype=np.uint64), lens.sum(axis=1))
     h = slot_signs(x, slot)
-    return (torch.from_numpy(h.view(np.int64)).pin_memory(), torch.from_numpy(offs).pin_memory(),
-            torch.from_numpy(np.log1p(rng.exponential(1.0, (B, n_dense))).astype(np.float32)).pin_memory(),
-            torch.from_numpy((rng.random(B) < 0.25).astype(np.float32)).pin_memory())
+    pin = (lambda t: t.pin_memory()) if torch.cuda.is_available() and tn.core.runtime().on_gpu else (lambda t: t)
+    return (pin(torch.from_numpy(h.view(np.int64))), pin(torch.from_numpy(offs)),
+            pin(torch.from_numpy(np.log1p(rng.exponential(1.0, (B, n_dense))).astype(np.float32))),
+            pin(torch.from_numpy((rng.random(B) < 0.25).astype(np.float32))))
 
 
 def main():
@@ -61,6 +63,11 @@ def main():
     a = ap.parse_args()
     tn.core.init()
     rt = tn.core.runtime()
+
+    def sync():
+        if rt.on_gpu:
+            torch.cuda.synchronize()
+
     universe = a.universe or 24_000_000 * rt.world
     ranks_per_slot = max(1, universe // a.slots)
     a.rows = int(ranks_per_slot * a.slots / rt.world * 1.1) + (1 << 16)      # this GPU's share of the universe plus head-room
@@ -83,7 +90,7 @@ def main():
         s_, c = jobs[min(k * rt.world + rt.rank, len(jobs) - 1)]
         x = (torch.arange(c * piece, (c + 1) * piece, device=rt.device, dtype=torch.int64) + 1).clamp_(max=ranks_per_slot)
         link.pull((x + ((s_ + 1) << 42)) * -7046029254386353131, training=False)
-    torch.cuda.synchronize(); rt.check_status(); rt.barrier()
+    sync(); rt.check_status(); rt.barrier()
     rows_here = link.table.n_rows
     rows_all = sum(rt.all_gather_object(rows_here))
     t_fill = time.time() - t_fill
@@ -97,13 +104,20 @@ def main():
 
     for k in range(a.warmup):
         step(k)
-    torch.cuda.synchronize(); rt.check_status(); rt.barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for k in range(a.steps):
-        loss = step(k)
-    e1.record(); torch.cuda.synchronize(); rt.barrier(); rt.check_status()
-    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64)
+    sync(); rt.check_status(); rt.barrier()
+    if rt.on_gpu:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for k in range(a.steps):
+            loss = step(k)
+        e1.record(); sync(); rt.barrier(); rt.check_status()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64)
+    else:                      # TN_FORCE_CPU=1: the same steps on the CPU path, wall clock (the CPU baseline of this config)
+        t0 = time.perf_counter()
+        for k in range(a.steps):
+            loss = step(k)
+        rt.barrier()
+        t = torch.tensor([(time.perf_counter() - t0) * 1e3], dtype=torch.float64)
     if rt.world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=rt.host_group)
     ms = float(t) / a.steps
@@ -114,7 +128,7 @@ def main():
                           "value": a.batch * rt.world / ms * 1e3, "ms_per_step": ms, "n_gpus": rt.world, "loss": float(loss),
                           "dense_tflops_per_gpu": flops / ms / 1e9, "ids_per_gpu_per_step": int(data[0][0].numel()),
                           "config": {"slots": a.slots, "dim": a.dim, "cross_width": D, "batch_per_gpu": a.batch, "table_rows_resident": rows_all,
-                                     "table_rows_this_gpu": rows_here, "table_GB_this_gpu": rows_here * link.table.stride * 4 / 1e9,
+                                     "table_rows_this_gpu": rows_here, "table_GB_this_gpu": rows_here * getattr(link.table, "stride", 0) * 4 / 1e9, "device": str(rt.device),
                                      "table_fill_seconds": t_fill, "gate_first_gemm": bool(tn.core.config.gate_first_gemm)}}),
               flush=True)
     tn.core.shutdown()
