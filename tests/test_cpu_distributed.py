@@ -123,7 +123,8 @@ tn.core.shutdown()
 
 
 @pytest.mark.timeout(900)
-def test_shared_round_trips_give_what_one_by_one_exchanges_give(tmp_path):
+@pytest.mark.parametrize("nproc", [2, 3])
+def test_shared_round_trips_give_what_one_by_one_exchanges_give(tmp_path, nproc):
     """Two ranks, two tables: the pulls run together (`pull_many`: ids of both tables in one round, rows in a second)
     and the pushes with the dense gradient riding along (`push_many`), against the same calls made one by one and a
     plain all-reduce; pulled rows, tables after the push and the mean dense gradient must be identical."""
@@ -178,7 +179,7 @@ if rt.rank == 0:
 tn.core.shutdown()
 ''')
     env = dict(os.environ, TN_FORCE_CPU="1", OMP_NUM_THREADS="1", PYTHONPATH=ROOT)
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
            "--master-port", str(_free_port()), str(script)]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
