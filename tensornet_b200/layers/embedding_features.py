@@ -12,7 +12,7 @@ embedding_features.py:288-295, core/ps/optimizer/ada_grad_kernel.cc:121-128).
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, Optional, Sequence
 
 import torch
 from torch import nn

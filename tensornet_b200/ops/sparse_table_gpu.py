@@ -19,7 +19,7 @@ import torch
 from .. import _build
 from .._opentelemetry import phase
 from ..core.config import config
-from ..core.optimizers import KIND_ADAGRAD, KIND_ADAM, KIND_FTRL, OptimizerBase
+from ..core.optimizers import KIND_ADAGRAD, OptimizerBase
 from ..core.runtime import runtime
 from ..parallel.symm import SymmArena
 

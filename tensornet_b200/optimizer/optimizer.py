@@ -8,7 +8,7 @@ conflicting per-task gradients before the update (tensornet/optimizer/optimizer.
 from __future__ import annotations
 
 import random
-from typing import Iterable, List, Sequence, Tuple
+from typing import Iterable, Sequence, Tuple
 
 import torch
 

@@ -1,8 +1,7 @@
 from __future__ import annotations
 
-import gzip
 import os
-from typing import Optional, Sequence
+from typing import Optional
 
 import numpy as np
 import torch

@@ -2,7 +2,6 @@
 the rule that decides when a training step is captured into a CUDA graph keeps several ranks in agreement.
 Reference behaviour: tensornet/model/Model.py:79-85,114-115, tensornet/callbacks/callbacks.py:78-91,
 examples/main.py:63-74."""
-import numpy as np
 import pytest
 import torch
 

@@ -3,7 +3,6 @@ reader), the tools re-shard without holding a table, a large shard loads with th
 path with a URL scheme goes through a file-system object, and the serving dictionary is parsed natively.
 Reference: core/ps/optimizer/optimizer_kernel.h:366-420,488-538, core/utility/file_io.cc:47-50,132,
 tensornet_tools/python/resize_sparse.py:35-54."""
-import gzip
 import os
 import resource
 import shutil

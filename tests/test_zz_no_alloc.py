@@ -9,7 +9,6 @@ ordinary (allocating) ``unique_assign`` entry point.  Virtual indices depend on 
 an insert race, so the two outputs are compared after ordering the distinct signs.
 """
 import ctypes
-import os
 
 import numpy as np
 import pytest
