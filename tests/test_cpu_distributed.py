@@ -73,6 +73,24 @@ def test_other_model_families_on_two_ranks(tmp_path, model):
     assert sorted(os.listdir(os.path.join(cp, "sparse_table", "deep_input"))) == ["rank_0", "rank_1"]
 
 
+@pytest.mark.timeout(600)
+def test_integration_script_prepares_trains_and_checks_on_two_ranks(tmp_path):
+    """The user-runnable end-to-end check (examples/integration-test.py in the reference): rank 0 writes the missing
+    days and clears an old model directory while rank 1 waits in the rendezvous, both train, rank 0 verifies."""
+    data, model_dir = str(tmp_path / "data"), str(tmp_path / "model")
+    os.makedirs(os.path.join(model_dir, "stale"))                # an old model directory must go
+    env = dict(os.environ, TN_FORCE_CPU="1", OMP_NUM_THREADS="1", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), os.path.join(ROOT, "examples", "integration_test.py"), "--data", data,
+           "--model-dir", model_dir, "--files-per-day", "2", "--examples-per-file", "640", "--max-steps", "8",
+           "--hidden", "32", "16"]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=500)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    assert "integration test passed" in out.stdout
+    assert not os.path.exists(os.path.join(model_dir, "stale"))
+    assert sorted(os.listdir(data)) == ["2020-05-10", "2020-05-11"]
+
+
 @pytest.mark.timeout(300)
 def test_apply_on_arrival_differs_from_one_summed_update(tmp_path):
     """What changes when two workers push the same sign in one step.  ``apply_mode="sum"`` (this framework's
