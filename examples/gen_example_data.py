@@ -2,17 +2,23 @@
 day, ``slots`` categorical features drawn from small id pools so ids repeat, one multi-valued slot,
 a slot that is missing for negative examples, dense features and a label correlated with the ids.
 
-Files are ``torch.save``d dicts of tensors: {"ids": {slot: (values, offsets)}, "dense": [N, D], "label": [N]}.
+Files are ``torch.save``d dicts of tensors: {"ids": {slot: (values, offsets)}, "dense": [N, D], "label": [N]}, or with
+``--format tfrecord`` TFRecord files of ``tf.train.Example`` records named ``tf-part.NNNNN`` with the features the
+reference's generator writes: int64 ``label``, bytes ``uniq_id``, one int64 list per slot (absent where the slot is
+missing) and, when asked for, a float list ``dense``.
 """
 from __future__ import annotations
 
 import argparse
 import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 import torch
 
 
-def make_file(path: str, n: int, slots, dense_dim: int, seed: int, pool: int = 1000):
+def make_file(path: str, n: int, slots, dense_dim: int, seed: int, pool: int = 1000, fmt: str = "pt"):
     g = torch.Generator().manual_seed(seed)
     label = (torch.rand(n, generator=g) < 0.3)
     ids = {}
@@ -31,7 +37,19 @@ def make_file(path: str, n: int, slots, dense_dim: int, seed: int, pool: int = 1
             ids[s] = (sign, torch.arange(n + 1))
     dense = torch.randn(n, dense_dim, generator=g)
     os.makedirs(os.path.dirname(path), exist_ok=True)
-    torch.save({"ids": ids, "dense": dense, "label": label.float()}, path)
+    if fmt == "pt":
+        torch.save({"ids": ids, "dense": dense, "label": label.float()}, path)
+        return
+    import tensornet_b200 as tn
+    cols = {s: (v.numpy(), o.numpy()) for s, (v, o) in ids.items()}
+    with tn.data.TFRecordWriter(path) as w:
+        for i in range(n):
+            ints = {"label": [int(label[i])]}
+            for s, (v, o) in cols.items():
+                if o[i + 1] > o[i]:
+                    ints[s] = v[o[i]:o[i + 1]]
+            floats = {"dense": dense[i].numpy()} if dense_dim else {}
+            w.write(tn.data.encode_example(ints, floats, {"uniq_id": b"%08d" % i}))
 
 
 def main():
@@ -42,11 +60,13 @@ def main():
     ap.add_argument("--examples-per-file", type=int, default=12000)
     ap.add_argument("--slots", type=int, default=4)
     ap.add_argument("--dense-dim", type=int, default=0)
+    ap.add_argument("--format", default="pt", choices=["pt", "tfrecord"])
     a = ap.parse_args()
     slots = [str(i + 1) for i in range(a.slots)]
     for d, day in enumerate(a.days):
         for f in range(a.files_per_day):
-            make_file(os.path.join(a.out, day, f"part-{f:05d}.pt"), a.examples_per_file, slots, a.dense_dim, d * 100 + f)
+            name = f"part-{f:05d}.pt" if a.format == "pt" else f"tf-part.{f:05d}"
+            make_file(os.path.join(a.out, day, name), a.examples_per_file, slots, a.dense_dim, d * 100 + f, fmt=a.format)
     print("wrote", a.out)
 
 

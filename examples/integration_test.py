@@ -30,16 +30,18 @@ def prepare(argv):
     ap.add_argument("--dense-dim", type=int, default=0)
     ap.add_argument("--files-per-day", type=int, default=4)
     ap.add_argument("--examples-per-file", type=int, default=12000)
+    ap.add_argument("--format", default="pt", choices=["pt", "tfrecord"], help="input files: torch-saved tensors or TFRecord")
     a, rest = ap.parse_known_args(argv)
     if int(os.environ.get("RANK", "0")) == 0:
         slots = [str(i + 1) for i in range(a.slots)]
         for d, day in enumerate(a.days):
             if not os.path.isdir(os.path.join(a.data, day)):
                 for f in range(a.files_per_day):
-                    gen_example_data.make_file(os.path.join(a.data, day, f"part-{f:05d}.pt"), a.examples_per_file, slots,
-                                               a.dense_dim, d * 100 + f)
+                    name = f"part-{f:05d}.pt" if a.format == "pt" else f"tf-part.{f:05d}"
+                    gen_example_data.make_file(os.path.join(a.data, day, name), a.examples_per_file, slots, a.dense_dim,
+                                               d * 100 + f, fmt=a.format)
         shutil.rmtree(a.model_dir, ignore_errors=True)
-    # what the driver understands: everything but the two generator-only flags
+    # what the driver understands: everything but the generator-only flags
     fwd = ["--data", a.data, "--model-dir", a.model_dir, "--days", *a.days, "--slots", str(a.slots),
            "--dense-dim", str(a.dense_dim)] + rest
     return a, fwd

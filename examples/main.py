@@ -22,7 +22,13 @@ import tensornet_b200 as tn
 
 
 def read_dataset(files, batch_size, slots, dense_dim, rank, world):
-    """Shard files by rank, cut them into batches, balance the number of batches between ranks."""
+    """Shard files by rank, cut them into batches, balance the number of batches between ranks.  TFRecord files
+    (``tf-*``, the reference's input format) go through the native reader; ``.pt`` files are sliced here."""
+    mine = files[rank::world] if len(files) >= world else files
+    if mine and os.path.basename(mine[0]).startswith("tf-"):
+        return tn.data.BalanceDataset(tn.data.TFRecordDataset(mine, batch_size, slots, dense_keys={"dense": dense_dim} if dense_dim else None,
+                                                              label_key="label", drop_remainder=True))
+
     def gen():
         for f in files[rank::world] if len(files) >= world else files:
             d = torch.load(f)
@@ -39,6 +45,14 @@ def read_dataset(files, batch_size, slots, dense_dim, rank, world):
                 feats["label"] = d["label"][lo:hi]
                 yield feats, d["label"][lo:hi]
     return tn.data.BalanceDataset(gen())
+
+
+def list_day_files(data, days):
+    """``part-*.pt`` files of the days, or their ``tf-*`` TFRecord files when there are none."""
+    try:
+        return tn.data.list_files(data, days, "part-*")
+    except FileNotFoundError:
+        return tn.data.list_files(data, days, "tf-*")
 
 
 def build_model(name, slots, dense_dim, hidden, emb_dim):
@@ -87,7 +101,7 @@ def main():
     for day in a.days:
         if last_dt is not None and day <= last_dt:       # already trained (resume after a restart)
             continue
-        files = tn.data.list_files(a.data, [day], "part-*")
+        files = list_day_files(a.data, [day])
         ds = read_dataset(files, a.batch_size, slots, a.dense_dim, rt.rank, rt.world)
         cb = tn.callbacks.PsWeightCheckpoint(a.model_dir, need_save_model=True, dt=day, delta_days=1, save_mode=a.save_mode)
         t0 = time.time()
@@ -105,7 +119,7 @@ def main():
         os.makedirs(a.model_dir, exist_ok=True)
         torch.save(model.sub_model.state_dict(), os.path.join(a.model_dir, "sub_model.pt"))
     if a.predict:
-        files = tn.data.list_files(a.data, a.days[-1:], "part-*")
+        files = list_day_files(a.data, a.days[-1:])
         ds = read_dataset(files, a.batch_size, slots, a.dense_dim, rt.rank, rt.world)
         y, p = model.predict(ds, steps=a.max_steps or None)
         out = os.path.join(a.model_dir, "predict")

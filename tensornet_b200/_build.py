@@ -46,7 +46,7 @@ CUDA_SOURCES = [
     "deepfm_fused.cu",
     "no_alloc.cu",
 ]
-CPU_SOURCES = ["cpu_ref.cpp"]
+CPU_SOURCES = ["cpu_ref.cpp", "tfrecord.cpp"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

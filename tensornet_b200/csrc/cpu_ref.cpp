@@ -1081,7 +1081,10 @@ void dense_step(int kind, py::array_t<float> w_, py::array_t<float> g_, py::arra
   }
 }
 
+void bind_tfrecord(py::module_& m);   // tfrecord.cpp: TFRecord / tf.train.Example input pipeline
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  bind_tfrecord(m);
   py::class_<CpuSparseTable>(m, "CpuSparseTable")
       .def(py::init<py::dict, int, bool, int, int>())
       .def("set_opt", &CpuSparseTable::set_opt)

@@ -1,0 +1,134 @@
+"""TFRecord files of ``tf.train.Example`` records as training input, without TensorFlow.
+
+The reference reads its input through ``tf.data``: files sharded by rank, an interleave of ``TFRecordDataset``
+readers, ``batch`` and a parallel ``parse_example`` with one ``VarLenFeature(int64)`` per slot
+(examples/common/util.py:23-39, examples/models/wide_deep.py parse function); its example data holds an int64
+``label``, a bytes ``uniq_id`` and one int64 list per slot, where a slot may be missing from a record
+(examples/gen_example_data.py:20-60).  :class:`TFRecordDataset` reads the same files through the native reader of
+``csrc/tfrecord.cpp`` (worker threads, plain or gzip files, checksums verified) and yields ``(features, labels)``
+batches in the containers the embedding layers take:
+
+* default: ``{slot: Ragged(values, offsets)}``, any number of ids per example, none when the record lacks the slot;
+* ``packed=True``: additionally one :class:`PackedFeatures` under ``PACKED_KEY`` holding all slots in one buffer
+  (one host-to-device copy per batch; picked up by a layer whose slot list is exactly ``sparse_keys``);
+* ``single_hot=True``: every slot has one id per example (``default_id`` when missing, the first of several), so
+  batches have fixed shapes and replay from CUDA graphs: ``{slot: int64 [B]}`` or packed ``ids [S, B]``.
+
+``TFRecordWriter`` and ``encode_example`` write such files (the example data generator and the tests use them).
+"""
+from __future__ import annotations
+
+from typing import Dict, Iterator, Mapping, Optional, Sequence, Tuple, Union
+
+import numpy as np
+import torch
+
+from .. import _build
+from .features import PACKED_KEY, PackedFeatures, Ragged
+
+
+def encode_example(ints: Optional[Mapping[str, Sequence[int]]] = None, floats: Optional[Mapping[str, Sequence[float]]] = None,
+                   raw: Optional[Mapping[str, bytes]] = None) -> bytes:
+    """Serialized ``tf.train.Example`` with int64-list, float-list and (single-value) bytes-list features."""
+    ext = _build.cpu_ext()
+    return ext.tf_example_encode({k: np.asarray(v, dtype=np.int64).reshape(-1) for k, v in (ints or {}).items()},
+                                 {k: np.asarray(v, dtype=np.float32).reshape(-1) for k, v in (floats or {}).items()},
+                                 dict(raw or {}))
+
+
+class TFRecordWriter:
+    """Writes records in TensorFlow's record framing (length, masked crc32c, data, masked crc32c); ``gzip=True``
+    compresses the whole file the way ``TFRecordOptions(compression_type="GZIP")`` does."""
+
+    def __init__(self, path: str, gzip: bool = False):
+        self._w = _build.cpu_ext().TFRecordWriter(str(path), bool(gzip))
+
+    def write(self, record: bytes) -> None:
+        self._w.write(record)
+
+    def close(self) -> None:
+        self._w.close()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+        return False
+
+
+class TFRecordDataset:
+    """Iterable of ``(features, labels)`` batches read from TFRecord files.
+
+    ``files``: the files THIS rank reads (``tn.data.list_files(...)[rank::world]``).  ``sparse_keys``: int64 features
+    (slots).  ``dense_keys``: ``{name: width}`` of float features (shorter lists are zero-filled, int64 lists are
+    converted) returned as one ``float32 [B, sum(widths)]`` tensor under ``dense_name``.  ``label_key``: int64 or
+    float feature whose first value is the label (also copied into ``features[label_key]``).  ``bytes_keys``: bytes
+    features returned as Python lists (for prediction dumps).
+
+    ``num_workers`` threads each own every ``num_workers``-th file, keep ``cycle_length`` of them open and take
+    ``block_length`` records from each in turn; batches are handed out worker after worker, so their order depends
+    only on these arguments.  Every iteration starts from the first file again.
+    """
+
+    def __init__(self, files: Sequence[str], batch_size: int, sparse_keys: Sequence[str],
+                 dense_keys: Optional[Union[Mapping[str, int], Sequence[Tuple[str, int]]]] = None, label_key: Optional[str] = "label",
+                 bytes_keys: Sequence[str] = (), *, dense_name: str = "dense", packed: bool = False, single_hot: bool = False,
+                 default_id: int = 0, drop_remainder: bool = False, verify_checksums: bool = True, num_workers: int = 4,
+                 cycle_length: int = 4, block_length: int = 8, queue_depth: int = 4, pin_memory: Optional[bool] = None):
+        self.files = [str(f) for f in files]
+        self.batch_size = int(batch_size)
+        self.sparse_keys = [str(k) for k in sparse_keys]
+        items = list(dense_keys.items()) if isinstance(dense_keys, Mapping) else list(dense_keys or [])
+        self.dense_keys = [(str(k), int(w)) for k, w in items]
+        self.label_key = label_key or ""
+        self.bytes_keys = [str(k) for k in bytes_keys]
+        self.dense_name, self.packed, self.single_hot, self.default_id = dense_name, bool(packed), bool(single_hot), int(default_id)
+        self.drop_remainder, self.verify = bool(drop_remainder), bool(verify_checksums)
+        self.num_workers, self.cycle_length, self.block_length, self.queue_depth = int(num_workers), int(cycle_length), int(block_length), int(queue_depth)
+        self.pin_memory = torch.cuda.is_available() if pin_memory is None else bool(pin_memory)
+
+    def _tensor(self, a: np.ndarray) -> torch.Tensor:
+        t = torch.from_numpy(a)
+        return t.pin_memory() if self.pin_memory and t.numel() else t
+
+    def _convert(self, raw: Dict) -> Tuple[Dict, Optional[torch.Tensor]]:
+        n, keys = int(raw["n"]), self.sparse_keys
+        feats: Dict = {}
+        if self.single_hot:
+            ids = self._tensor(raw["ids"])
+            if self.packed:
+                feats[PACKED_KEY] = PackedFeatures(keys, ids=ids)
+            for s, k in enumerate(keys):
+                feats[k] = ids[s]
+        else:
+            values, base = self._tensor(raw["values"]), raw["slot_base"]
+            local = torch.from_numpy(raw["local_offsets"])
+            if self.packed:
+                feats[PACKED_KEY] = PackedFeatures(keys, values=values, offsets=self._tensor(raw["offsets"]), batch_size=n)
+            for s, k in enumerate(keys):
+                feats[k] = Ragged(values[int(base[s]):int(base[s + 1])], local[s])
+        if self.dense_keys:
+            feats[self.dense_name] = self._tensor(raw["dense"])
+        labels = None
+        if self.label_key:
+            labels = self._tensor(raw["label"])
+            feats[self.label_key] = labels
+        for k in self.bytes_keys:
+            feats[k] = raw[k]
+        return feats, labels
+
+    def __iter__(self) -> Iterator[Tuple[Dict, Optional[torch.Tensor]]]:
+        ext = _build.cpu_ext()
+        b = ext.TFRecordBatcher(self.files, self.batch_size, self.sparse_keys, [k for k, _ in self.dense_keys],
+                                [w for _, w in self.dense_keys], self.label_key, self.bytes_keys, self.single_hot,
+                                self.default_id, self.drop_remainder, self.verify, self.num_workers, self.cycle_length,
+                                self.block_length, self.queue_depth)
+        try:
+            while True:
+                raw = b.next()
+                if raw is None:
+                    return
+                yield self._convert(raw)
+        finally:
+            b.close()

@@ -83,12 +83,13 @@ def test_integration_script_prepares_trains_and_checks_on_two_ranks(tmp_path):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
            "--master-port", str(_free_port()), os.path.join(ROOT, "examples", "integration_test.py"), "--data", data,
            "--model-dir", model_dir, "--files-per-day", "2", "--examples-per-file", "640", "--max-steps", "8",
-           "--hidden", "32", "16"]
+           "--hidden", "32", "16", "--format", "tfrecord"]        # the reference's input format, through the native reader
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=500)
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
     assert "integration test passed" in out.stdout
     assert not os.path.exists(os.path.join(model_dir, "stale"))
     assert sorted(os.listdir(data)) == ["2020-05-10", "2020-05-11"]
+    assert sorted(os.listdir(os.path.join(data, "2020-05-10"))) == ["tf-part.00000", "tf-part.00001"]
 
 
 @pytest.mark.timeout(300)

@@ -1,0 +1,213 @@
+"""TFRecord / tf.train.Example input without TensorFlow: the native reader against records serialized by the protobuf
+library from a schema written out here (independent of this package's own encoder), the framing against the known
+crc32c check value, interleave order, gzip files, damaged files, and a model trained from such files.
+
+Reference: examples/common/util.py:23-39 (input pipeline), examples/gen_example_data.py:20-60 (record contents)."""
+import gzip
+import struct
+
+import numpy as np
+import pytest
+import torch
+
+import tensornet_b200 as tn
+from tensornet_b200 import _build
+
+
+def _example_class():
+    """tf.train.Example rebuilt from its published schema with the protobuf runtime."""
+    from google.protobuf import descriptor_pb2, descriptor_pool, message_factory
+    fd = descriptor_pb2.FileDescriptorProto(name="example_for_test.proto", package="tnt", syntax="proto3")
+    F = descriptor_pb2.FieldDescriptorProto
+
+    def msg(name):
+        m = fd.message_type.add()
+        m.name = name
+        return m
+
+    for name, typ in (("BytesList", F.TYPE_BYTES), ("FloatList", F.TYPE_FLOAT), ("Int64List", F.TYPE_INT64)):
+        msg(name).field.add(name="value", number=1, label=F.LABEL_REPEATED, type=typ)
+    m = msg("Feature")
+    m.oneof_decl.add(name="kind")
+    for i, (n, t) in enumerate((("bytes_list", "BytesList"), ("float_list", "FloatList"), ("int64_list", "Int64List"))):
+        m.field.add(name=n, number=i + 1, label=F.LABEL_OPTIONAL, type=F.TYPE_MESSAGE, type_name=".tnt." + t, oneof_index=0)
+    m = msg("Features")
+    e = m.nested_type.add(name="FeatureEntry")
+    e.options.map_entry = True
+    e.field.add(name="key", number=1, label=F.LABEL_OPTIONAL, type=F.TYPE_STRING)
+    e.field.add(name="value", number=2, label=F.LABEL_OPTIONAL, type=F.TYPE_MESSAGE, type_name=".tnt.Feature")
+    m.field.add(name="feature", number=1, label=F.LABEL_REPEATED, type=F.TYPE_MESSAGE, type_name=".tnt.Features.FeatureEntry")
+    msg("Example").field.add(name="features", number=1, label=F.LABEL_OPTIONAL, type=F.TYPE_MESSAGE, type_name=".tnt.Features")
+    pool = descriptor_pool.DescriptorPool()
+    pool.Add(fd)
+    return message_factory.GetMessageClass(pool.FindMessageTypeByName("tnt.Example"))
+
+
+def _frame(data: bytes) -> bytes:
+    ext = _build.cpu_ext()
+    head = struct.pack("<Q", len(data))
+    return head + struct.pack("<I", ext.tf_masked_crc32c(head)) + data + struct.pack("<I", ext.tf_masked_crc32c(data))
+
+
+def _make_examples(n, seed=0):
+    rng = np.random.default_rng(seed)
+    Example = _example_class()
+    rows, blobs = [], []
+    for i in range(n):
+        label = int(rng.random() < 0.4)
+        row = {"label": label, "uniq_id": b"id%05d" % i, "1": [int(rng.integers(1, 50))],
+               "2": [int(x) for x in rng.integers(-2 ** 62, 2 ** 62, size=int(rng.integers(0, 4)))],
+               "4": None if label == 0 else [int(x) for x in rng.integers(1, 1000, size=3)],
+               "dense": [float(x) for x in rng.standard_normal(3).astype(np.float32)]}
+        ex = Example()
+        ex.features.feature["label"].int64_list.value.append(label)
+        ex.features.feature["uniq_id"].bytes_list.value.append(row["uniq_id"])
+        ex.features.feature["1"].int64_list.value.extend(row["1"])
+        ex.features.feature["2"].int64_list.value.extend(row["2"])          # may be an empty list
+        if row["4"] is not None:                                             # missing for negatives
+            ex.features.feature["4"].int64_list.value.extend(row["4"])
+        ex.features.feature["dense"].float_list.value.extend(row["dense"])
+        ex.features.feature["ignored"].float_list.value.append(1.0)
+        rows.append(row)
+        blobs.append(ex.SerializeToString())
+    return rows, blobs
+
+
+def test_crc32c_check_value_on_both_code_paths():
+    ext = _build.cpu_ext()
+    assert ext.crc32c(b"123456789", True) == 0xE3069283 and ext.crc32c(b"123456789", False) == 0xE3069283
+    blob = bytes(range(256)) * 37 + b"tail"
+    assert ext.crc32c(blob, True) == ext.crc32c(blob, False)
+    assert ext.crc32c(b"", False) == 0
+
+
+@pytest.mark.parametrize("compressed", [False, True])
+def test_reader_matches_records_written_by_the_protobuf_library(tmp_path, compressed):
+    rows, blobs = _make_examples(37)
+    path = str(tmp_path / "tf-part.00001")
+    payload = b"".join(_frame(b) for b in blobs)
+    with (gzip.open(path, "wb") if compressed else open(path, "wb")) as f:
+        f.write(payload)
+    ds = tn.data.TFRecordDataset([path], 16, ["1", "2", "4"], dense_keys={"dense": 3}, bytes_keys=["uniq_id"], packed=True,
+                                 num_workers=1, pin_memory=False)
+    got = list(ds)
+    assert [int(y.numel()) for _, y in got] == [16, 16, 5]
+    i = 0
+    for feats, y in got:
+        n = int(y.numel())
+        packed = feats[tn.data.PACKED_KEY]
+        assert packed.keys == ["1", "2", "4"] and packed.batch_size == n and packed.offsets.numel() == 3 * n + 1
+        for b in range(n):
+            row = rows[i + b]
+            assert float(y[b]) == row["label"] and feats["uniq_id"][b] == row["uniq_id"]
+            np.testing.assert_array_equal(feats["dense"][b].numpy(), np.asarray(row["dense"], np.float32))
+            for s, k in enumerate(["1", "2", "4"]):
+                want = row[k] or []
+                v, o = feats[k]
+                assert v[int(o[b]):int(o[b + 1])].tolist() == want
+                lo, hi = int(packed.offsets[s * n + b]), int(packed.offsets[s * n + b + 1])
+                assert packed.values[lo:hi].tolist() == want
+        i += n
+    assert i == 37
+    # fixed shapes: one id per slot, the default where the record has none, the first of several
+    one = list(tn.data.TFRecordDataset([path], 64, ["1", "2", "4"], single_hot=True, default_id=7, packed=True, num_workers=1,
+                                       pin_memory=False))
+    (feats, y), = one
+    assert feats[tn.data.PACKED_KEY].ids.shape == (3, 37)
+    for b, row in enumerate(rows):
+        assert int(feats["1"][b]) == row["1"][0]
+        assert int(feats["2"][b]) == (row["2"][0] if row["2"] else 7)
+        assert int(feats["4"][b]) == (row["4"][0] if row["4"] else 7)
+
+
+def test_own_writer_round_trips_and_unpacked_lists_are_read(tmp_path):
+    path = str(tmp_path / "w.tfrecord.gz")
+    with tn.data.TFRecordWriter(path, gzip=True) as w:
+        w.write(tn.data.encode_example({"a": [1, -2, 3], "label": [1]}, {"x": [0.5, 0.25]}, {"u": b"k"}))
+        # hand-made record: the int64 list with one element per tag (not packed), as old writers emit it
+        lst = b"\x08\x05\x08\x06"
+        feat = b"\x1a" + bytes([len(lst)]) + lst
+        entry = b"\x0a\x01a\x12" + bytes([len(feat)]) + feat
+        feats = b"\x0a" + bytes([len(entry)]) + entry
+        w.write(b"\x0a" + bytes([len(feats)]) + feats)
+    (f, y), = list(tn.data.TFRecordDataset([path], 8, ["a"], dense_keys={"x": 4}, bytes_keys=["u"], pin_memory=False))
+    assert f["a"].values.tolist() == [1, -2, 3, 5, 6] and f["a"].offsets.tolist() == [0, 3, 5]
+    assert y.tolist() == [1.0, 0.0] and f["dense"].tolist() == [[0.5, 0.25, 0, 0], [0, 0, 0, 0]] and f["u"] == [b"k", b""]
+
+
+def test_interleave_order_and_worker_split_are_deterministic(tmp_path):
+    files = []
+    for k in range(5):                                   # file k holds ids 100k .. 100k + 19 + k (unequal lengths)
+        p = str(tmp_path / f"tf-{k}")
+        with tn.data.TFRecordWriter(p) as w:
+            for j in range(20 + k):
+                w.write(tn.data.encode_example({"s": [100 * k + j]}))
+        files.append(p)
+
+    def run(**kw):
+        ds = tn.data.TFRecordDataset(files, 4, ["s"], label_key=None, single_hot=True, pin_memory=False, **kw)
+        return [f["s"].tolist() for f, _ in ds]
+
+    one = run(num_workers=1, cycle_length=2, block_length=3)
+    flat = [x for b in one for x in b]
+    assert flat[:12] == [0, 1, 2, 100, 101, 102, 3, 4, 5, 103, 104, 105]       # blocks of 3 from two open files in turn
+    assert sorted(flat) == sorted(100 * k + j for k in range(5) for j in range(20 + k))
+    assert len(one[-1]) == len(flat) % 4 or len(one[-1]) == 4
+    a, b = run(num_workers=3), run(num_workers=3)
+    assert a == b                                                               # thread timing does not show
+    assert sorted(x for bb in a for x in bb) == sorted(flat)
+    assert all(len({x // 100 % 3 for x in bb}) == 1 for bb in a)                # a batch never mixes two workers' files
+    assert sum(len(bb) for bb in run(num_workers=2, drop_remainder=True)) % 4 == 0
+
+
+def test_damaged_files_are_reported(tmp_path):
+    good = _frame(tn.data.encode_example({"s": [1]}))
+    cases = {"cut": good + good[:-3], "flip": good[:14] + bytes([good[14] ^ 1]) + good[15:], "head": b"\x01" + good[1:]}
+    for name, payload in cases.items():
+        p = str(tmp_path / name)
+        with open(p, "wb") as f:
+            f.write(payload)
+        with pytest.raises(RuntimeError, match=name == "cut" and "ends inside" or name == "flip" and "checksum" or "corrupt"):
+            list(tn.data.TFRecordDataset([p], 2, ["s"], label_key=None, pin_memory=False))
+    p = str(tmp_path / "junk")
+    with open(p, "wb") as f:
+        f.write(_frame(b"\x0a\x05\x0a\x03\x0a\x7f"))                          # lengths that run past the record
+    with pytest.raises(RuntimeError, match="well-formed"):
+        list(tn.data.TFRecordDataset([p], 2, ["s"], label_key=None, pin_memory=False))
+    # a reader abandoned in mid-file shuts its threads down
+    p = str(tmp_path / "many")
+    with tn.data.TFRecordWriter(p) as w:
+        for j in range(2000):
+            w.write(tn.data.encode_example({"s": [j]}))
+    it = iter(tn.data.TFRecordDataset([p], 4, ["s"], label_key=None, pin_memory=False, queue_depth=1))
+    next(it)
+    it.close()
+
+
+def test_wide_deep_trains_from_tfrecord_files(tmp_path):
+    """The reference's example records (slots 1-3 one id, slot 4 three ids or missing, int64 label) through fit."""
+    rng = np.random.default_rng(3)
+    pools = {s: rng.integers(1, 2 ** 62, size=10) for s in "1234"}
+    files = []
+    for k in range(2):
+        p = str(tmp_path / f"tf-part.{k:05d}")
+        with tn.data.TFRecordWriter(p) as w:
+            for _ in range(640):
+                first = int(rng.integers(0, 10))
+                label = int(first % 2 == 0)
+                ints = {"label": [label], "1": [int(pools["1"][first])], "2": [int(rng.choice(pools["2"]))],
+                        "3": [int(rng.choice(pools["3"]))]}
+                if label:
+                    ints["4"] = [int(x) for x in rng.choice(pools["4"], size=3)]
+                w.write(tn.data.encode_example(ints, raw={"uniq_id": b"xxxxx"}))
+        files.append(p)
+    tn.core.init()
+    slots = ["1", "2", "3", "4"]
+    torch.manual_seed(0)
+    model = tn.models.WideDeep(slots, slots, dnn_hidden_units=(32, 16), embedding_dim=8, bucket_size=2048,
+                               sparse_opt=tn.core.AdaGrad(learning_rate=0.05, initial_g2sum=0.1, initial_scale=0.1))
+    model.compile(optimizer=tn.optimizer.Optimizer(tn.core.Adam(learning_rate=5e-3)), loss="binary_crossentropy",
+                  metrics=[tn.metric.AUC()])
+    ds = tn.data.TFRecordDataset(files, 64, slots, num_workers=2)
+    hist = model.fit(ds, epochs=3)
+    assert hist["loss"][-1] < 0.2 and hist["auc"][-1] > 0.98, hist
