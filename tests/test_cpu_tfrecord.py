@@ -211,3 +211,31 @@ def test_wide_deep_trains_from_tfrecord_files(tmp_path):
     ds = tn.data.TFRecordDataset(files, 64, slots, num_workers=2)
     hist = model.fit(ds, epochs=3)
     assert hist["loss"][-1] < 0.2 and hist["auc"][-1] > 0.98, hist
+
+
+def test_arbitrary_record_bytes_parse_or_are_refused(tmp_path):
+    """Records are untrusted input: random bytes and damaged valid records either parse or raise, and what parses
+    stays inside the batch's bounds (run under the sanitizer build this is a fuzz test of the wire parser)."""
+    from hypothesis import given, settings, strategies as st
+    good = tn.data.encode_example({"a": [1, 2, 3], "b": [], "label": [1]}, {"x": [1.0, 2.0]}, {"u": b"abc"})
+    path = str(tmp_path / "fuzz")
+
+    @settings(max_examples=300, deadline=None)
+    @given(st.one_of(st.binary(max_size=64),
+                     st.tuples(st.integers(0, len(good) - 1), st.integers(0, 255)).map(
+                         lambda t: good[:t[0]] + bytes([t[1]]) + good[t[0] + 1:]),
+                     st.integers(0, len(good)).map(lambda n: good[:n])))
+    def check(blob):
+        with open(path, "wb") as f:
+            f.write(_frame(blob) + _frame(good))
+        ds = tn.data.TFRecordDataset([path], 4, ["a", "b"], dense_keys={"x": 2}, bytes_keys=["u"], num_workers=1, pin_memory=False)
+        try:
+            (feats, y), = list(ds)
+        except RuntimeError as e:
+            assert "well-formed" in str(e)
+            return
+        assert y.numel() == 2 and feats["a"].offsets.numel() == 3 and feats["dense"].shape == (2, 2)
+        assert int(feats["a"].offsets[-1]) == feats["a"].values.numel()
+        assert feats["a"].values[int(feats["a"].offsets[1]):].tolist() == [1, 2, 3]      # the good record behind it
+
+    check()
