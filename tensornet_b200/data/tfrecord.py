@@ -9,8 +9,9 @@ readers, ``batch`` and a parallel ``parse_example`` with one ``VarLenFeature(int
 batches in the containers the embedding layers take:
 
 * default: ``{slot: Ragged(values, offsets)}``, any number of ids per example, none when the record lacks the slot;
-* ``packed=True``: additionally one :class:`PackedFeatures` under ``PACKED_KEY`` holding all slots in one buffer
-  (one host-to-device copy per batch; picked up by a layer whose slot list is exactly ``sparse_keys``);
+* ``packed=True``: instead one :class:`PackedFeatures` under ``PACKED_KEY`` holding all slots in one buffer (one
+  host-to-device copy per batch); for models whose embedding layers all take exactly ``sparse_keys``, in that
+  order (with ``single_hot=True`` a layer may also take a subset);
 * ``single_hot=True``: every slot has one id per example (``default_id`` when missing, the first of several), so
   batches have fixed shapes and replay from CUDA graphs: ``{slot: int64 [B]}`` or packed ``ids [S, B]``.
 
@@ -99,15 +100,17 @@ class TFRecordDataset:
             ids = self._tensor(raw["ids"])
             if self.packed:
                 feats[PACKED_KEY] = PackedFeatures(keys, ids=ids)
-            for s, k in enumerate(keys):
-                feats[k] = ids[s]
+            else:
+                for s, k in enumerate(keys):
+                    feats[k] = ids[s]
         else:
-            values, base = self._tensor(raw["values"]), raw["slot_base"]
-            local = torch.from_numpy(raw["local_offsets"])
+            values = self._tensor(raw["values"])
             if self.packed:
                 feats[PACKED_KEY] = PackedFeatures(keys, values=values, offsets=self._tensor(raw["offsets"]), batch_size=n)
-            for s, k in enumerate(keys):
-                feats[k] = Ragged(values[int(base[s]):int(base[s + 1])], local[s])
+            else:
+                base, local = raw["slot_base"], self._tensor(raw["local_offsets"])
+                for s, k in enumerate(keys):
+                    feats[k] = Ragged(values[int(base[s]):int(base[s + 1])], local[s])
         if self.dense_keys:
             feats[self.dense_name] = self._tensor(raw["dense"])
         labels = None

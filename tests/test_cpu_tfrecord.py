@@ -88,14 +88,15 @@ def test_reader_matches_records_written_by_the_protobuf_library(tmp_path, compre
     payload = b"".join(_frame(b) for b in blobs)
     with (gzip.open(path, "wb") if compressed else open(path, "wb")) as f:
         f.write(payload)
-    ds = tn.data.TFRecordDataset([path], 16, ["1", "2", "4"], dense_keys={"dense": 3}, bytes_keys=["uniq_id"], packed=True,
-                                 num_workers=1, pin_memory=False)
-    got = list(ds)
-    assert [int(y.numel()) for _, y in got] == [16, 16, 5]
+    kw = dict(dense_keys={"dense": 3}, bytes_keys=["uniq_id"], num_workers=1, pin_memory=False)
+    got = list(tn.data.TFRecordDataset([path], 16, ["1", "2", "4"], **kw))
+    got_packed = list(tn.data.TFRecordDataset([path], 16, ["1", "2", "4"], packed=True, **kw))
+    assert [int(y.numel()) for _, y in got] == [16, 16, 5] == [int(y.numel()) for _, y in got_packed]
     i = 0
-    for feats, y in got:
+    for (feats, y), (pf, _) in zip(got, got_packed):
         n = int(y.numel())
-        packed = feats[tn.data.PACKED_KEY]
+        packed = pf[tn.data.PACKED_KEY]
+        assert "1" not in pf and tn.data.PACKED_KEY not in feats
         assert packed.keys == ["1", "2", "4"] and packed.batch_size == n and packed.offsets.numel() == 3 * n + 1
         for b in range(n):
             row = rows[i + b]
@@ -110,10 +111,11 @@ def test_reader_matches_records_written_by_the_protobuf_library(tmp_path, compre
         i += n
     assert i == 37
     # fixed shapes: one id per slot, the default where the record has none, the first of several
-    one = list(tn.data.TFRecordDataset([path], 64, ["1", "2", "4"], single_hot=True, default_id=7, packed=True, num_workers=1,
-                                       pin_memory=False))
-    (feats, y), = one
-    assert feats[tn.data.PACKED_KEY].ids.shape == (3, 37)
+    (pf, _), = list(tn.data.TFRecordDataset([path], 64, ["1", "2", "4"], single_hot=True, default_id=7, packed=True,
+                                            num_workers=1, pin_memory=False))
+    (feats, y), = list(tn.data.TFRecordDataset([path], 64, ["1", "2", "4"], single_hot=True, default_id=7, num_workers=1,
+                                               pin_memory=False))
+    assert pf[tn.data.PACKED_KEY].ids.shape == (3, 37) and pf[tn.data.PACKED_KEY].ids[0].tolist() == feats["1"].tolist()
     for b, row in enumerate(rows):
         assert int(feats["1"][b]) == row["1"][0]
         assert int(feats["2"][b]) == (row["2"][0] if row["2"] else 7)
