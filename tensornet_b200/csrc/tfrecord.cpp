@@ -102,53 +102,71 @@ static inline uint32_t masked(uint32_t crc) { return ((crc >> 15) | (crc << 17))
 // ---------------------------------------------------------------------------------------------- record files
 class RecordFile {
  public:
-  explicit RecordFile(const std::string& path) : path_(path) {
+  explicit RecordFile(const std::string& path) : path_(path), buf_(kChunk) {
     f_ = gzopen(path.c_str(), "rb");
     if (!f_) throw std::runtime_error("cannot open " + path);
-    gzbuffer(f_, 1 << 20);
+    gzbuffer(f_, 1 << 18);
   }
   ~RecordFile() { if (f_) gzclose(f_); }
   RecordFile(const RecordFile&) = delete;
   RecordFile& operator=(const RecordFile&) = delete;
 
-  // One record into `buf`; false at a clean end of file.  A file that ends inside a record, or a checksum that does
-  // not match, raises.
-  bool next(std::vector<uint8_t>& buf, bool verify) {
-    uint8_t head[12];
-    const int got = read_some(head, 12);
-    if (got == 0) return false;
-    if (got != 12) fail("ends inside a record header");
+  // The next record, in place: `data` points into this reader's chunk buffer and stays valid until the next call.
+  // False at a clean end of file.  A file that ends inside a record, or a checksum that does not match, raises.
+  bool next(const uint8_t*& data, size_t& len_out, bool verify) {
+    if (!want(12)) {
+      if (end_ == pos_) return false;
+      fail("ends inside a record header");
+    }
+    const uint8_t* head = buf_.data() + pos_;
     uint64_t len;
     uint32_t crc;
     std::memcpy(&len, head, 8);
     std::memcpy(&crc, head + 8, 4);
     if (masked(crc32c(head, 8)) != crc) fail("has a corrupt record length");
     if (len > (1ull << 31)) fail("has a record longer than 2 GiB");
-    buf.resize(len + 4);
-    if (read_some(buf.data(), (unsigned)(len + 4)) != (int)(len + 4)) fail("ends inside a record");
+    if (!want(12 + len + 4)) fail("ends inside a record");
+    const uint8_t* rec = buf_.data() + pos_ + 12;
     if (verify) {
       uint32_t dcrc;
-      std::memcpy(&dcrc, buf.data() + len, 4);
-      if (masked(crc32c(buf.data(), len)) != dcrc) fail("has a record whose checksum does not match");
+      std::memcpy(&dcrc, rec + len, 4);
+      if (masked(crc32c(rec, len)) != dcrc) fail("has a record whose checksum does not match");
     }
-    buf.resize(len);
+    pos_ += 12 + len + 4;
+    data = rec;
+    len_out = len;
     return true;
   }
 
  private:
-  int read_some(uint8_t* dst, unsigned n) {
-    unsigned have = 0;
-    while (have < n) {
-      const int r = gzread(f_, dst + have, n - have);
-      if (r < 0) fail("cannot be read (zlib error)");
-      if (r == 0) break;
-      have += (unsigned)r;
+  static constexpr size_t kChunk = 1 << 20;
+
+  // Makes `n` bytes available at pos_ (moving the unread tail to the front and reading on); false at end of file.
+  bool want(size_t n) {
+    if (end_ - pos_ >= n) return true;
+    if (eof_) return false;
+    if (pos_) {
+      std::memmove(buf_.data(), buf_.data() + pos_, end_ - pos_);
+      end_ -= pos_;
+      pos_ = 0;
     }
-    return (int)have;
+    if (buf_.size() < n) buf_.resize(std::max(n, buf_.size() * 2));
+    while (end_ < n || end_ < buf_.size()) {
+      const size_t room = std::min<size_t>(buf_.size() - end_, 1u << 30);
+      if (!room) break;
+      const int r = gzread(f_, buf_.data() + end_, (unsigned)room);
+      if (r < 0) fail("cannot be read (zlib error)");
+      if (r == 0) { eof_ = true; break; }
+      end_ += (size_t)r;
+    }
+    return end_ - pos_ >= n;
   }
   [[noreturn]] void fail(const char* what) { throw std::runtime_error("TFRecord file " + path_ + " " + what); }
   std::string path_;
   gzFile f_ = nullptr;
+  std::vector<uint8_t> buf_;
+  size_t pos_ = 0, end_ = 0;
+  bool eof_ = false;
 };
 
 // ---------------------------------------------------------------------------------------------- protobuf wire format
@@ -159,6 +177,25 @@ struct Cursor {
 };
 
 static inline bool varint(Cursor& c, uint64_t& v) {
+  if (c.p < c.e && !(*c.p & 0x80)) {      // tags and short lengths: one byte
+    v = *c.p++;
+    return true;
+  }
+  if (c.e - c.p >= 10) {                  // ids: up to ten bytes, no bounds check per byte
+    const uint8_t* p = c.p;
+    uint64_t r = 0;
+#pragma GCC unroll 10
+    for (int i = 0; i < 10; ++i) {
+      const uint64_t b = p[i];
+      r |= (b & 0x7F) << (7 * i);
+      if (!(b & 0x80)) {
+        c.p = p + i + 1;
+        v = r;
+        return true;
+      }
+    }
+    return false;
+  }
   v = 0;
   for (int shift = 0; shift < 64 && c.p < c.e; shift += 7) {
     const uint8_t b = *c.p++;
@@ -219,8 +256,11 @@ struct Spec {
 
 struct Batch {
   int n = 0;
-  std::vector<std::vector<int64_t>> vals;   // per sparse slot, examples one after the other
-  std::vector<std::vector<int32_t>> lens;   // per sparse slot: ids per example
+  size_t S;
+  // While records arrive: ids in arrival order and, per (example, slot), where its ids start and how many there are.
+  std::vector<int64_t> ids;
+  std::vector<uint32_t> pos;
+  std::vector<int32_t> len;
   std::vector<float> dense, label;
   std::vector<std::vector<std::string>> bytes;
   // filled by seal(): the arrays handed to Python
@@ -229,36 +269,56 @@ struct Batch {
   std::vector<int32_t> local_offsets;       // [S, n + 1], every slot counted from 0
   std::vector<int64_t> slot_base;           // [S + 1] where each slot starts in `values`
 
-  explicit Batch(const Spec& sp) : vals(sp.sparse.size()), lens(sp.sparse.size()), bytes(sp.bytes.size()) {}
+  explicit Batch(const Spec& sp, int expect) : S(sp.sparse.size()), bytes(sp.bytes.size()) {
+    ids.reserve((size_t)expect * S);
+    pos.reserve((size_t)expect * S);
+    len.reserve((size_t)expect * S);
+    dense.reserve((size_t)expect * sp.dense_total);
+  }
 
   void seal(const Spec& sp) {
-    const size_t S = sp.sparse.size();
-    size_t total = 0;
-    for (auto& v : vals) total += v.size();
-    values.reserve(total);
     slot_base.assign(S + 1, 0);
+    if (ids.size() > (size_t)INT32_MAX) throw std::runtime_error("a batch holds more than 2^31 ids");
     if (sp.single_hot) {
-      for (size_t s = 0; s < S; ++s) { values.insert(values.end(), vals[s].begin(), vals[s].end()); slot_base[s + 1] = (int64_t)values.size(); }
-      return;
-    }
-    offsets.resize(S * (size_t)n + 1);
-    local_offsets.resize(S * (size_t)(n + 1));
-    int64_t run = 0;
-    for (size_t s = 0; s < S; ++s) {
-      int32_t loc = 0;
-      for (int b = 0; b < n; ++b) {
-        offsets[s * n + b] = (int32_t)run;
-        local_offsets[s * (n + 1) + b] = loc;
-        run += lens[s][b];
-        loc += lens[s][b];
+      values.resize(S * (size_t)n);
+      for (size_t s = 0; s < S; ++s) {
+        for (int b = 0; b < n; ++b) values[s * n + b] = ids[pos[(size_t)b * S + s]];
+        slot_base[s + 1] = (int64_t)((s + 1) * (size_t)n);
       }
-      local_offsets[s * (n + 1) + n] = loc;
-      values.insert(values.end(), vals[s].begin(), vals[s].end());
-      slot_base[s + 1] = run;
+    } else {
+      size_t total = 0;
+      for (int32_t l : len) total += (size_t)l;
+      values.resize(total);
+      offsets.resize(S * (size_t)n + 1);
+      local_offsets.resize(S * (size_t)(n + 1));
+      size_t run = 0;
+      for (size_t s = 0; s < S; ++s) {
+        const size_t begin = run;
+        for (int b = 0; b < n; ++b) {
+          const size_t at = (size_t)b * S + s;
+          offsets[s * n + b] = (int32_t)run;
+          local_offsets[s * (n + 1) + b] = (int32_t)(run - begin);
+          const int32_t l = len[at];
+          const int64_t* src = ids.data() + pos[at];
+          for (int32_t k = 0; k < l; ++k) values[run + k] = src[k];
+          run += (size_t)l;
+        }
+        local_offsets[s * (n + 1) + n] = (int32_t)(run - begin);
+        slot_base[s + 1] = (int64_t)run;
+      }
+      offsets[S * (size_t)n] = (int32_t)run;
     }
-    if (run > INT32_MAX) throw std::runtime_error("a batch holds more than 2^31 ids");
-    offsets[S * (size_t)n] = (int32_t)run;
+    std::vector<int64_t>().swap(ids);
+    std::vector<uint32_t>().swap(pos);
+    std::vector<int32_t>().swap(len);
   }
+};
+
+// What a worker remembers between records: writers emit the features of every record in the same order, so the
+// name at position i of the previous record predicts the name at position i of this one and most look-ups are one
+// short comparison instead of a hash.
+struct ParseState {
+  std::vector<std::pair<std::string, int>> order;
 };
 
 // ---------------------------------------------------------------------------------------------- one Example
@@ -345,17 +405,18 @@ static bool first_bytes(Cursor list, std::string& out) {
 
 // Adds one serialized Example to the batch.  Features that the record does not carry keep their defaults (no ids,
 // zeros, label 0, empty bytes); when a name occurs twice the later entry wins, as in a protobuf map.
-static void parse_example(const uint8_t* data, size_t len, const Spec& sp, Batch& b) {
+static void parse_example(const uint8_t* data, size_t len, const Spec& sp, Batch& b, ParseState& st) {
   const size_t S = sp.sparse.size(), D = sp.dense.size();
-  static thread_local std::vector<size_t> start;
-  start.resize(S);
-  for (size_t s = 0; s < S; ++s) { start[s] = b.vals[s].size(); b.lens[s].push_back(0); }
+  const size_t row = b.pos.size();
+  b.pos.resize(row + S, 0u);
+  b.len.resize(row + S, 0);
   const size_t drow = b.dense.size();
   b.dense.resize(drow + sp.dense_total, 0.f);
   if (!sp.label.empty()) b.label.push_back(0.f);
   for (auto& col : b.bytes) col.emplace_back();
 
   auto bad = []() { throw std::runtime_error("a record is not a well-formed tf.train.Example"); };
+  size_t nth = 0;
   Cursor ex{data, data + len};
   while (!ex.done()) {
     uint64_t tag;
@@ -381,27 +442,40 @@ static void parse_example(const uint8_t* data, size_t len, const Spec& sp, Batch
           bad();
         }
       }
-      const auto it = sp.index.find(key);
-      if (it == sp.index.end()) continue;
-      const size_t code = (size_t)it->second;
+      int found;
+      if (nth < st.order.size() && st.order[nth].first.size() == key.size() &&
+          std::memcmp(st.order[nth].first.data(), key.data(), key.size()) == 0) {
+        found = st.order[nth].second;
+      } else {
+        const auto it = sp.index.find(key);
+        found = it == sp.index.end() ? -1 : it->second;
+        if (nth < 4096) {                       // remember the order of ordinary records only
+          if (st.order.size() <= nth) st.order.resize(nth + 1);
+          st.order[nth].first.assign(key.data(), key.size());
+          st.order[nth].second = found;
+        }
+      }
+      ++nth;
+      if (found < 0) continue;
+      const size_t code = (size_t)found;
       bool ok = true;
       if (code < S) {
-        auto& v = b.vals[code];
-        v.resize(start[code]);
+        const size_t at = b.ids.size();
         ok = for_each_list(feat, [&](int kind, Cursor list) {
           if (kind != 3) return true;
-          return for_each_int64(list, [&](int64_t x) { v.push_back(x); });
+          return for_each_int64(list, [&](int64_t x) { b.ids.push_back(x); });
         });
-        b.lens[code].back() = (int32_t)(v.size() - start[code]);
+        b.pos[row + code] = (uint32_t)at;
+        b.len[row + code] = (int32_t)(b.ids.size() - at);
       } else if (code < S + D) {
         const size_t j = code - S;
-        float* row = b.dense.data() + drow + sp.dense_off[j];
+        float* out = b.dense.data() + drow + sp.dense_off[j];
         const int w = sp.dense_width[j];
         int k = 0;
-        std::fill(row, row + w, 0.f);
+        std::fill(out, out + w, 0.f);
         ok = for_each_list(feat, [&](int kind, Cursor list) {
-          if (kind == 2) return for_each_float(list, [&](float x) { if (k < w) row[k++] = x; });
-          if (kind == 3) return for_each_int64(list, [&](int64_t x) { if (k < w) row[k++] = (float)x; });
+          if (kind == 2) return for_each_float(list, [&](float x) { if (k < w) out[k++] = x; });
+          if (kind == 3) return for_each_int64(list, [&](int64_t x) { if (k < w) out[k++] = (float)x; });
           return true;
         });
       } else if (code == S + D) {
@@ -421,8 +495,11 @@ static void parse_example(const uint8_t* data, size_t len, const Spec& sp, Batch
   }
   if (sp.single_hot) {
     for (size_t s = 0; s < S; ++s) {
-      b.vals[s].resize(start[s] + 1, sp.default_id);     // none -> the default id; several -> the first
-      b.lens[s].back() = 1;
+      if (b.len[row + s] == 0) {                 // none -> the default id; several -> the first
+        b.pos[row + s] = (uint32_t)b.ids.size();
+        b.ids.push_back(sp.default_id);
+      }
+      b.len[row + s] = 1;
     }
   }
   ++b.n;
@@ -526,22 +603,24 @@ class Batcher {
         while ((int)open.size() < cycle_ && next_file < w->files.size()) open.emplace_back(new RecordFile(w->files[next_file++]));
       };
       refill();
-      std::vector<uint8_t> rec;
-      auto batch = std::make_unique<Batch>(spec_);
+      const uint8_t* rec = nullptr;
+      size_t rec_len = 0;
+      auto batch = std::make_unique<Batch>(spec_, batch_size_);
+      ParseState state;
       size_t cur = 0;
       int in_block = 0;
       while (!open.empty() && !stop_.load()) {
         if (cur >= open.size()) cur = 0;
-        if (!open[cur]->next(rec, verify_)) {          // this file is done: the next unopened one takes its place
+        if (!open[cur]->next(rec, rec_len, verify_)) {          // this file is done: the next unopened one takes its place
           if (next_file < w->files.size()) open[cur].reset(new RecordFile(w->files[next_file++]));
           else open.erase(open.begin() + (long)cur);
           in_block = 0;
           continue;
         }
-        parse_example(rec.data(), rec.size(), spec_, *batch);
+        parse_example(rec, rec_len, spec_, *batch, state);
         if (batch->n == batch_size_) {
           if (!put(w, std::move(batch))) return;
-          batch = std::make_unique<Batch>(spec_);
+          batch = std::make_unique<Batch>(spec_, batch_size_);
         }
         if (++in_block == block_) { in_block = 0; ++cur; }
       }
