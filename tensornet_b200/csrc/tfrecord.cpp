@@ -102,9 +102,10 @@ static inline uint32_t masked(uint32_t crc) { return ((crc >> 15) | (crc << 17))
 // ---------------------------------------------------------------------------------------------- record files
 class RecordFile {
  public:
-  explicit RecordFile(const std::string& path) : path_(path), buf_(kChunk) {
+  // `path` is opened; `name` is what error messages call the file (the remote name of a fetched copy).
+  explicit RecordFile(const std::string& path, const std::string& name) : path_(name), buf_(kChunk) {
     f_ = gzopen(path.c_str(), "rb");
-    if (!f_) throw std::runtime_error("cannot open " + path);
+    if (!f_) throw std::runtime_error("cannot open " + name);
     gzbuffer(f_, 1 << 18);
   }
   ~RecordFile() { if (f_) gzclose(f_); }
@@ -524,9 +525,11 @@ class Batcher {
  public:
   Batcher(std::vector<std::string> files, int batch_size, std::vector<std::string> sparse, std::vector<std::string> dense,
           std::vector<int> dense_width, std::string label, std::vector<std::string> bytes, bool single_hot,
-          int64_t default_id, bool drop_remainder, bool verify, int workers, int cycle, int block, int depth)
+          int64_t default_id, bool drop_remainder, bool verify, int workers, int cycle, int block, int depth,
+          py::object localize, py::object release)
       : batch_size_(batch_size), drop_remainder_(drop_remainder), verify_(verify), cycle_(std::max(1, cycle)),
-        block_(std::max(1, block)), depth_(std::max(1, depth)) {
+        block_(std::max(1, block)), depth_(std::max(1, depth)), localize_(std::move(localize)), release_(std::move(release)) {
+    hooks_ = !localize_.is_none();
     if (batch_size <= 0) throw std::invalid_argument("batch_size must be positive");
     if (dense.size() != dense_width.size()) throw std::invalid_argument("one width per dense feature");
     for (int w : dense_width) if (w <= 0) throw std::invalid_argument("dense widths must be positive");
@@ -547,7 +550,15 @@ class Batcher {
     }
   }
 
-  ~Batcher() { close(); }
+  ~Batcher() {
+    // Workers may be waiting for the interpreter lock to call a hook: let go of it while they wind down.
+    if (hooks_ && PyGILState_Check()) {
+      py::gil_scoped_release nogil;
+      close();
+    } else {
+      close();
+    }
+  }
 
   void close() {
     stop_.store(true);
@@ -599,10 +610,15 @@ class Batcher {
     try {
       std::vector<std::unique_ptr<RecordFile>> open;
       size_t next_file = 0;
-      auto refill = [&] {
-        while ((int)open.size() < cycle_ && next_file < w->files.size()) open.emplace_back(new RecordFile(w->files[next_file++]));
+      auto open_next = [&]() {
+        const std::string& name = w->files[next_file++];
+        return std::unique_ptr<RecordFile>(new RecordFile(hooks_ ? hook(localize_, name) : name, name));
       };
-      refill();
+      std::vector<std::string> names;      // of the open files, for the release hook
+      while ((int)open.size() < cycle_ && next_file < w->files.size()) {
+        names.push_back(w->files[next_file]);
+        open.push_back(open_next());
+      }
       const uint8_t* rec = nullptr;
       size_t rec_len = 0;
       auto batch = std::make_unique<Batch>(spec_, batch_size_);
@@ -612,8 +628,15 @@ class Batcher {
       while (!open.empty() && !stop_.load()) {
         if (cur >= open.size()) cur = 0;
         if (!open[cur]->next(rec, rec_len, verify_)) {          // this file is done: the next unopened one takes its place
-          if (next_file < w->files.size()) open[cur].reset(new RecordFile(w->files[next_file++]));
-          else open.erase(open.begin() + (long)cur);
+          open[cur].reset();
+          if (hooks_) hook(release_, names[cur]);
+          if (next_file < w->files.size()) {
+            names[cur] = w->files[next_file];
+            open[cur] = open_next();
+          } else {
+            open.erase(open.begin() + (long)cur);
+            names.erase(names.begin() + (long)cur);
+          }
           in_block = 0;
           continue;
         }
@@ -636,10 +659,27 @@ class Batcher {
     w->can_get.notify_all();
   }
 
+  // Calls a Python hook from a worker thread; what it raises travels on as this worker's error.
+  static std::string hook(const py::object& fn, const std::string& name) {
+    py::gil_scoped_acquire gil;
+    try {
+      if (fn.is_none()) return name;
+      py::object r = fn(name);
+      return r.is_none() ? name : py::cast<std::string>(r);
+    } catch (py::error_already_set& e) {
+      const std::string what = e.what();
+      e.restore();
+      PyErr_Clear();
+      throw std::runtime_error(what);
+    }
+  }
+
   Spec spec_;
   int batch_size_;
   bool drop_remainder_, verify_;
   int cycle_, block_, depth_;
+  py::object localize_, release_;
+  bool hooks_ = false;
   std::vector<std::unique_ptr<Worker>> workers_;
   std::atomic<bool> stop_{false};
   size_t turn_ = 0;
@@ -774,10 +814,11 @@ void bind_tfrecord(py::module_& m) {
   using namespace tfrec;
   py::class_<Batcher>(m, "TFRecordBatcher")
       .def(py::init<std::vector<std::string>, int, std::vector<std::string>, std::vector<std::string>, std::vector<int>,
-                    std::string, std::vector<std::string>, bool, int64_t, bool, bool, int, int, int, int>(),
+                    std::string, std::vector<std::string>, bool, int64_t, bool, bool, int, int, int, int, py::object, py::object>(),
            py::arg("files"), py::arg("batch_size"), py::arg("sparse"), py::arg("dense"), py::arg("dense_width"),
            py::arg("label"), py::arg("bytes"), py::arg("single_hot"), py::arg("default_id"), py::arg("drop_remainder"),
-           py::arg("verify"), py::arg("workers"), py::arg("cycle"), py::arg("block"), py::arg("depth"))
+           py::arg("verify"), py::arg("workers"), py::arg("cycle"), py::arg("block"), py::arg("depth"),
+           py::arg("localize") = py::none(), py::arg("release") = py::none())
       .def("next", &next_batch)
       .def("close", [](Batcher& b) { py::gil_scoped_release nogil; b.close(); });
   py::class_<Writer>(m, "TFRecordWriter")

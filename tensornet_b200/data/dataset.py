@@ -19,10 +19,24 @@ _balance_epoch = 0
 
 
 def list_files(datapath: str, days: Sequence[str], match_pattern: str) -> List[str]:
+    """Files ``datapath/<day>/<match_pattern>`` of the given days, sorted within a day.  ``datapath`` may carry a URL
+    scheme (``hdfs://...``): the day directories are then listed through the remote file-system layer and the
+    names come back as URLs, which :class:`TFRecordDataset` fetches as it reads."""
+    from ..utils.checkpoint import _fs_for, is_remote
     patterns = [os.path.join(datapath, str(day), match_pattern) for day in days]
     files: List[str] = []
-    for p in patterns:
-        files.extend(sorted(glob.glob(p)))
+    if is_remote(datapath):
+        import fnmatch
+        for day in days:
+            url = datapath.rstrip("/") + "/" + str(day)
+            fs, rpath = _fs_for(url)
+            if not fs.exists(rpath):
+                continue
+            names = sorted(os.path.basename(str(e).rstrip("/")) for e in fs.ls(rpath, detail=False))
+            files.extend(url + "/" + n for n in names if fnmatch.fnmatch(n, match_pattern))
+    else:
+        for p in patterns:
+            files.extend(sorted(glob.glob(p)))
     if not files:
         raise FileNotFoundError("No files matched pattern: " + ", ".join(patterns))
     return files

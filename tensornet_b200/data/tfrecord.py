@@ -19,12 +19,17 @@ batches in the containers the embedding layers take:
 """
 from __future__ import annotations
 
+import os
+import shutil
+import tempfile
+import threading
 from typing import Dict, Iterator, Mapping, Optional, Sequence, Tuple, Union
 
 import numpy as np
 import torch
 
 from .. import _build
+from ..utils.checkpoint import _fs_for, is_remote
 from .features import PACKED_KEY, PackedFeatures, Ragged
 
 
@@ -61,7 +66,8 @@ class TFRecordWriter:
 class TFRecordDataset:
     """Iterable of ``(features, labels)`` batches read from TFRecord files.
 
-    ``files``: the files THIS rank reads (``tn.data.list_files(...)[rank::world]``).  ``sparse_keys``: int64 features
+    ``files``: the files THIS rank reads (``tn.data.list_files(...)[rank::world]``); names with a URL scheme
+    (``hdfs://...``) are fetched to a scratch directory one by one as the readers get to them.  ``sparse_keys``: int64 features
     (slots).  ``dense_keys``: ``{name: width}`` of float features (shorter lists are zero-filled, int64 lists are
     converted) returned as one ``float32 [B, sum(widths)]`` tensor under ``dense_name``.  ``label_key``: int64 or
     float feature whose first value is the label (also copied into ``features[label_key]``).  ``bytes_keys``: bytes
@@ -123,10 +129,12 @@ class TFRecordDataset:
 
     def __iter__(self) -> Iterator[Tuple[Dict, Optional[torch.Tensor]]]:
         ext = _build.cpu_ext()
+        scratch = _Scratch() if any(is_remote(f) for f in self.files) else None
         b = ext.TFRecordBatcher(self.files, self.batch_size, self.sparse_keys, [k for k, _ in self.dense_keys],
                                 [w for _, w in self.dense_keys], self.label_key, self.bytes_keys, self.single_hot,
                                 self.default_id, self.drop_remainder, self.verify, self.num_workers, self.cycle_length,
-                                self.block_length, self.queue_depth)
+                                self.block_length, self.queue_depth, scratch.localize if scratch else None,
+                                scratch.release if scratch else None)
         try:
             while True:
                 raw = b.next()
@@ -135,3 +143,39 @@ class TFRecordDataset:
                 yield self._convert(raw)
         finally:
             b.close()
+            if scratch:
+                scratch.close()
+
+
+class _Scratch:
+    """Local copies of remote input files (``hdfs://...``, any scheme the installed file-system layer knows): a reader
+    thread asks for a file when its turn comes and gives it back when it has read it, so at most
+    ``num_workers x cycle_length`` copies exist at a time.  The reference reaches such files through TensorFlow's
+    file-system layer (core/utility/file_io.cc:47-50); here they come through fsspec or an installed client
+    (``tn.utils.checkpoint.set_remote_fs``)."""
+
+    def __init__(self):
+        self.dir = tempfile.mkdtemp(prefix="tn_input_")
+        self._lock = threading.Lock()
+        self._local: Dict[str, str] = {}
+        self._count = 0
+
+    def localize(self, name: str) -> str:
+        if not is_remote(name):
+            return name[7:] if name.startswith("file://") else name
+        fs, rpath = _fs_for(name)
+        with self._lock:
+            dst = os.path.join(self.dir, "%06d_%s" % (self._count, os.path.basename(rpath.rstrip("/"))))
+            self._count += 1
+            self._local[name] = dst
+        fs.get(rpath, dst)
+        return dst
+
+    def release(self, name: str) -> None:
+        with self._lock:
+            dst = self._local.pop(name, None)
+        if dst and os.path.exists(dst):
+            os.remove(dst)
+
+    def close(self) -> None:
+        shutil.rmtree(self.dir, ignore_errors=True)

@@ -4,6 +4,7 @@ crc32c check value, interleave order, gzip files, damaged files, and a model tra
 
 Reference: examples/common/util.py:23-39 (input pipeline), examples/gen_example_data.py:20-60 (record contents)."""
 import gzip
+import os
 import struct
 
 import numpy as np
@@ -241,3 +242,58 @@ def test_arbitrary_record_bytes_parse_or_are_refused(tmp_path):
         assert feats["a"].values[int(feats["a"].offsets[1]):].tolist() == [1, 2, 3]      # the good record behind it
 
     check()
+
+
+def test_input_files_on_a_remote_file_system_are_fetched_as_they_are_read(tmp_path):
+    """Day directories under a URL (``hdfs://`` for the reference's users; a local stand-in here) are listed through
+    the file-system layer and every file is copied to scratch space only while a reader works on it."""
+    import shutil
+    from tensornet_b200.utils import checkpoint
+
+    class DirFS:
+        def __init__(self, root):
+            self.root, self.gets, self.live_max = root, [], 0
+
+        def _p(self, path):
+            return os.path.join(self.root, path.lstrip("/"))
+
+        def exists(self, path):
+            return os.path.exists(self._p(path))
+
+        def ls(self, path, detail=False):
+            return [os.path.join(path, n) for n in os.listdir(self._p(path))]
+
+        def get(self, src, dst, recursive=True):
+            self.gets.append(src)
+            shutil.copy(self._p(src), dst)
+            self.live_max = max(self.live_max, len(os.listdir(os.path.dirname(dst))))
+
+    root = tmp_path / "remote"
+    want = []
+    for day in ("2020-05-10", "2020-05-11"):
+        os.makedirs(root / "bucket" / "data" / day)
+        for k in range(3):
+            with tn.data.TFRecordWriter(str(root / "bucket" / "data" / day / f"tf-part.{k:05d}")) as w:
+                for j in range(10):
+                    x = int(day[-2:]) * 1000 + k * 100 + j
+                    want.append(x)
+                    w.write(tn.data.encode_example({"s": [x], "label": [j & 1]}))
+        (root / "bucket" / "data" / day / "_SUCCESS").write_text("")
+    fs = DirFS(str(root))
+    checkpoint.set_remote_fs(lambda url: (fs, url.split("://", 1)[1]))
+    try:
+        files = tn.data.list_files("mem://bucket/data", ["2020-05-10", "2020-05-11"], "tf-*")
+        assert files[0] == "mem://bucket/data/2020-05-10/tf-part.00000" and len(files) == 6
+        with pytest.raises(FileNotFoundError):
+            tn.data.list_files("mem://bucket/data", ["2020-05-12"], "tf-*")
+        ds = tn.data.TFRecordDataset(files, 4, ["s"], single_hot=True, num_workers=2, cycle_length=1, pin_memory=False)
+        got = [x for f, _ in ds for x in f["s"].tolist()]
+        assert sorted(got) == sorted(want)
+        assert sorted(fs.gets) == sorted(f.split("://", 1)[1] for f in files)
+        assert fs.live_max <= 2                               # two readers, one open file each
+        # a file that cannot be fetched is reported with its remote name
+        bad = tn.data.TFRecordDataset(files[:1] + ["mem://bucket/data/2020-05-10/missing"], 4, ["s"], num_workers=1, pin_memory=False)
+        with pytest.raises(RuntimeError, match="missing|No such file"):
+            list(bad)
+    finally:
+        checkpoint.set_remote_fs(None)
