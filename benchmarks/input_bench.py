@@ -4,8 +4,10 @@
     python benchmarks/input_bench.py --records 200000 --workers 1 2 4 8
 
 Writes ``--files`` TFRecord files under ``--dir`` once (kept between runs), then reads them with each worker count and
-prints one JSON line per run: records / s, MB / s of file data and batches / s at ``--batch``.  Host-only: no GPU is
-touched; page-locked output buffers are off so that the figure is the reader's own.
+prints one JSON line per run: records / s, MB / s of file data and batches / s at ``--batch``.  Then the same pass is
+written once as a batch cache (``tn.data.write_batch_cache``) and read back (``tn.data.BatchCacheDataset``): no
+parsing, one contiguous read per batch.  Host-only: no GPU is touched; page-locked output buffers are off so that
+the figures are the readers' own.
 """
 from __future__ import annotations
 
@@ -66,6 +68,24 @@ def main():
             print(json.dumps({"workers": nw, "single_hot": single_hot, "gzip": a.gzip, "records": n,
                               "records_per_s": round(n / best), "file_mb_per_s": round(size / best / 1e6, 1),
                               "batches_per_s": round(nb / best, 1), "host_cores": os.cpu_count()}), flush=True)
+
+    cache = os.path.join(a.dir, "pass.tnbc")
+    if not os.path.exists(cache):
+        src = tn.data.TFRecordDataset(files, a.batch, slots, dense_keys={"dense": 13}, num_workers=max(a.workers), single_hot=True,
+                                      packed=True, pin_memory=False)
+        tn.data.write_batch_cache(cache, src, slots, dense_name="dense")
+    best = None
+    for _ in range(a.repeat):
+        t0 = time.perf_counter()
+        n = nb = 0
+        for _, y in tn.data.BatchCacheDataset(cache, pin_memory=False):
+            n += int(y.numel())
+            nb += 1
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    print(json.dumps({"reader": "batch_cache", "records": n, "records_per_s": round(n / best),
+                      "file_mb_per_s": round(os.path.getsize(cache) / best / 1e6, 1), "batches_per_s": round(nb / best, 1),
+                      "host_cores": os.cpu_count()}), flush=True)
 
 
 if __name__ == "__main__":
