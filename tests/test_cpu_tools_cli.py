@@ -58,3 +58,22 @@ def test_cli_merge_and_resize(tmp_path):
     parts = [ext.read_dense_file(str(tmp_path / "dense3" / str(r)), 1) for r in range(3)]
     wkey = [k for k in whole if isinstance(whole[k], np.ndarray) and whole[k].ndim == 1 and len(whole[k]) == n][0]
     assert np.allclose(np.concatenate([p[wkey] for p in parts])[:n], whole[wkey])
+
+
+def test_cli_batch_cache(tmp_path):
+    """TFRecord files parsed once into a cache of ready-made batches from the command line."""
+    files = []
+    for k in range(2):
+        p = str(tmp_path / f"tf-{k}")
+        with tn.data.TFRecordWriter(p) as w:
+            for j in range(50):
+                w.write(tn.data.encode_example({"1": [k * 100 + j], "2": [7], "label": [j & 1]}, {"d": [0.5, 1.5]}))
+        files.append(p)
+    out = str(tmp_path / "pass.tnbc")
+    assert int(_tool("batch-cache", out, *files, "--batch-size", "32", "--slots", "1", "2", "--dense", "d", "2", "--single-hot",
+                     "--workers", "1")) == 100
+    got = list(tn.data.BatchCacheDataset(out, pin_memory=False))
+    assert [int(y.numel()) for _, y in got] == [32, 32, 32, 4]
+    ids = torch.cat([f[tn.data.PACKED_KEY].ids for f, _ in got], dim=1)
+    assert sorted(ids[0].tolist()) == sorted(k * 100 + j for k in range(2) for j in range(50)) and set(ids[1].tolist()) == {7}
+    assert got[0][0]["dense"].shape == (32, 2) and float(got[0][0]["dense"][0, 1]) == 1.5
