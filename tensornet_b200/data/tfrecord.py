@@ -75,14 +75,16 @@ class TFRecordDataset:
 
     ``num_workers`` threads each own every ``num_workers``-th file, keep ``cycle_length`` of them open and take
     ``block_length`` records from each in turn; batches are handed out worker after worker, so their order depends
-    only on these arguments.  Every iteration starts from the first file again.
+    only on these arguments.  Every iteration starts from the first file again; ``shuffle_files=True`` reads the files in
+    another order in every pass (determined by ``seed`` and the number of the pass).
     """
 
     def __init__(self, files: Sequence[str], batch_size: int, sparse_keys: Sequence[str],
                  dense_keys: Optional[Union[Mapping[str, int], Sequence[Tuple[str, int]]]] = None, label_key: Optional[str] = "label",
                  bytes_keys: Sequence[str] = (), *, dense_name: str = "dense", packed: bool = False, single_hot: bool = False,
                  default_id: int = 0, drop_remainder: bool = False, verify_checksums: bool = True, num_workers: int = 4,
-                 cycle_length: int = 4, block_length: int = 8, queue_depth: int = 4, pin_memory: Optional[bool] = None):
+                 cycle_length: int = 4, block_length: int = 8, queue_depth: int = 4, pin_memory: Optional[bool] = None,
+                 shuffle_files: bool = False, seed: int = 0):
         self.files = [str(f) for f in files]
         self.batch_size = int(batch_size)
         self.sparse_keys = [str(k) for k in sparse_keys]
@@ -94,6 +96,7 @@ class TFRecordDataset:
         self.drop_remainder, self.verify = bool(drop_remainder), bool(verify_checksums)
         self.num_workers, self.cycle_length, self.block_length, self.queue_depth = int(num_workers), int(cycle_length), int(block_length), int(queue_depth)
         self.pin_memory = torch.cuda.is_available() if pin_memory is None else bool(pin_memory)
+        self.shuffle_files, self.seed, self._passes = bool(shuffle_files), int(seed), 0
 
     def _tensor(self, a: np.ndarray) -> torch.Tensor:
         t = torch.from_numpy(a)
@@ -130,7 +133,12 @@ class TFRecordDataset:
     def __iter__(self) -> Iterator[Tuple[Dict, Optional[torch.Tensor]]]:
         ext = _build.cpu_ext()
         scratch = _Scratch() if any(is_remote(f) for f in self.files) else None
-        b = ext.TFRecordBatcher(self.files, self.batch_size, self.sparse_keys, [k for k, _ in self.dense_keys],
+        files = self.files
+        if self.shuffle_files:                 # another order in every pass, the same on every run with this seed
+            order = np.random.default_rng([self.seed, self._passes]).permutation(len(files))
+            files = [files[i] for i in order]
+        self._passes += 1
+        b = ext.TFRecordBatcher(files, self.batch_size, self.sparse_keys, [k for k, _ in self.dense_keys],
                                 [w for _, w in self.dense_keys], self.label_key, self.bytes_keys, self.single_hot,
                                 self.default_id, self.drop_remainder, self.verify, self.num_workers, self.cycle_length,
                                 self.block_length, self.queue_depth, scratch.localize if scratch else None,

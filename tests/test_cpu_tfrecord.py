@@ -161,6 +161,22 @@ def test_interleave_order_and_worker_split_are_deterministic(tmp_path):
     assert sorted(x for bb in a for x in bb) == sorted(flat)
     assert all(len({x // 100 % 3 for x in bb}) == 1 for bb in a)                # a batch never mixes two workers' files
     assert sum(len(bb) for bb in run(num_workers=2, drop_remainder=True)) % 4 == 0
+    ds = tn.data.TFRecordDataset(files, 4, ["s"], label_key=None, single_hot=True, pin_memory=False, num_workers=1, cycle_length=1,
+                                 shuffle_files=True, seed=5)
+
+    def file_order(d):
+        seen = []
+        for f, _ in d:
+            for x in f["s"].tolist():
+                if x // 100 not in seen:
+                    seen.append(x // 100)
+        return seen
+
+    first = [file_order(ds) for _ in range(3)]                     # three passes over one dataset object
+    again = tn.data.TFRecordDataset(files, 4, ["s"], label_key=None, single_hot=True, pin_memory=False, num_workers=1,
+                                    cycle_length=1, shuffle_files=True, seed=5)
+    assert len({tuple(o) for o in first}) > 1 and all(sorted(o) == [0, 1, 2, 3, 4] for o in first)
+    assert file_order(again) == first[0]
 
 
 def test_damaged_files_are_reported(tmp_path):
