@@ -270,11 +270,14 @@ struct Batch {
   std::vector<int32_t> local_offsets;       // [S, n + 1], every slot counted from 0
   std::vector<int64_t> slot_base;           // [S + 1] where each slot starts in `values`
 
-  explicit Batch(const Spec& sp, int expect) : S(sp.sparse.size()), bytes(sp.bytes.size()) {
-    ids.reserve((size_t)expect * S);
-    pos.reserve((size_t)expect * S);
-    len.reserve((size_t)expect * S);
+  Batch(const Spec& sp, int expect, bool own_buffers = true) : S(sp.sparse.size()), bytes(sp.bytes.size()) {
+    if (own_buffers) {                       // otherwise hand_down() of the previous batch provides them
+      ids.reserve((size_t)expect * S);
+      pos.reserve((size_t)expect * S);
+      len.reserve((size_t)expect * S);
+    }
     dense.reserve((size_t)expect * sp.dense_total);
+    label.reserve(sp.label.empty() ? 0 : (size_t)expect);
   }
 
   void seal(const Spec& sp) {
@@ -309,9 +312,16 @@ struct Batch {
       }
       offsets[S * (size_t)n] = (int32_t)run;
     }
-    std::vector<int64_t>().swap(ids);
-    std::vector<uint32_t>().swap(pos);
-    std::vector<int32_t>().swap(len);
+  }
+
+  // The accumulation buffers of a sealed batch go on to the next one (their pages are already mapped).
+  void hand_down(Batch& next) {
+    ids.clear();
+    pos.clear();
+    len.clear();
+    next.ids.swap(ids);
+    next.pos.swap(pos);
+    next.len.swap(len);
   }
 };
 
@@ -596,7 +606,6 @@ class Batcher {
 
  private:
   bool put(Worker* w, std::unique_ptr<Batch> b) {
-    b->seal(spec_);
     std::unique_lock<std::mutex> lk(w->mu);
     w->can_put.wait(lk, [&] { return (int)w->q.size() < depth_ || stop_.load(); });
     if (stop_.load()) return false;
@@ -642,12 +651,18 @@ class Batcher {
         }
         parse_example(rec, rec_len, spec_, *batch, state);
         if (batch->n == batch_size_) {
+          auto fresh = std::make_unique<Batch>(spec_, batch_size_, false);
+          batch->seal(spec_);
+          batch->hand_down(*fresh);
           if (!put(w, std::move(batch))) return;
-          batch = std::make_unique<Batch>(spec_, batch_size_);
+          batch = std::move(fresh);
         }
         if (++in_block == block_) { in_block = 0; ++cur; }
       }
-      if (batch->n > 0 && !drop_remainder_ && !stop_.load()) put(w, std::move(batch));
+      if (batch->n > 0 && !drop_remainder_ && !stop_.load()) {
+        batch->seal(spec_);
+        put(w, std::move(batch));
+      }
     } catch (const std::exception& e) {
       std::lock_guard<std::mutex> g(w->mu);
       w->error = e.what();
