@@ -414,6 +414,104 @@ static bool first_bytes(Cursor list, std::string& out) {
   return true;
 }
 
+// Fast path for a map entry of the usual shape: every length fits one byte, the name is the one the previous record
+// had at this position, and the feature holds one list whose values sit in a single `value = 1` field (packed
+// numbers, or one bytes value), or no values at all.  `p` points at the entry's length byte.  On success `kind` is
+// the list (1 bytes, 2 float, 3 int64; 0 = feature without a list), [pay, pay + paylen) its value bytes and `total`
+// the size of the entry including its length byte.  Anything else is left to the general parser.
+static inline bool quick_entry(const uint8_t* p, const uint8_t* end, const std::string& key, int& kind,
+                               const uint8_t*& pay, size_t& paylen, size_t& total) {
+  const size_t kl = key.size();
+  if (end - p < 1 || (p[0] & 0x80) || kl > 100) return false;
+  const size_t L = p[0];
+  if ((size_t)(end - p) < 1 + L || L < kl + 4) return false;
+  const uint8_t* q = p + 1;
+  if (q[0] != 0x0A || q[1] != kl || std::memcmp(q + 2, key.data(), kl) != 0) return false;
+  const uint8_t* f = q + 2 + kl;
+  const size_t F = L - kl - 4;                         // bytes of the Feature message
+  if (f[0] != 0x12 || f[1] != F) return false;
+  total = 1 + L;
+  if (F == 0) { kind = 0; pay = f + 2; paylen = 0; return true; }
+  if (F < 2 || f[3] != F - 2) return false;
+  kind = f[2] == 0x0A ? 1 : f[2] == 0x12 ? 2 : f[2] == 0x1A ? 3 : 0;
+  if (!kind) return false;
+  if (F == 2) { pay = f + 4; paylen = 0; return true; }  // a list without values
+  if (F < 4 || f[4] != 0x0A || f[5] != F - 4) return false;
+  pay = f + 6;
+  paylen = F - 4;
+  return true;
+}
+
+// Varints filling [p, e) exactly; false when one runs past the end.
+template <class F>
+static inline bool packed_varints(const uint8_t* p, const uint8_t* e, F&& fn) {
+  while (p < e) {
+    uint64_t v = 0;
+    int shift = 0;
+    for (;;) {
+      if (p >= e || shift > 63) return false;
+      const uint64_t b = *p++;
+      v |= (b & 0x7F) << shift;
+      if (!(b & 0x80)) break;
+      shift += 7;
+    }
+    fn((int64_t)v);
+  }
+  return true;
+}
+
+// Stores the values of an entry that quick_entry() recognised; false (nothing stored) when they are not of a form
+// this path handles, so that the general parser takes the entry.
+static inline bool take_quick(const Spec& sp, Batch& b, int found, int kind, const uint8_t* pay, size_t paylen, size_t row,
+                              size_t drow) {
+  if (found < 0) return true;                            // a feature nobody asked for
+  const size_t S = sp.sparse.size(), D = sp.dense.size(), code = (size_t)found;
+  if (code < S) {
+    const size_t at = b.ids.size();
+    if (kind == 3 && !packed_varints(pay, pay + paylen, [&](int64_t x) { b.ids.push_back(x); })) {
+      b.ids.resize(at);
+      return false;
+    }
+    b.pos[row + code] = (uint32_t)at;
+    b.len[row + code] = (int32_t)(b.ids.size() - at);
+    return true;
+  }
+  if (code < S + D) {
+    const size_t j = code - S;
+    float* out = b.dense.data() + drow + sp.dense_off[j];
+    const int w = sp.dense_width[j];
+    float tmp[64];
+    if (w > 64) return false;
+    int k = 0;
+    if (kind == 2) {
+      if (paylen % 4) return false;
+      k = (int)std::min<size_t>((size_t)w, paylen / 4);
+      std::memcpy(tmp, pay, (size_t)k * 4);
+    } else if (kind == 3) {
+      if (!packed_varints(pay, pay + paylen, [&](int64_t x) { if (k < w) tmp[k++] = (float)x; })) return false;
+    }
+    std::fill(out, out + w, 0.f);
+    std::copy(tmp, tmp + k, out);
+    return true;
+  }
+  if (code == S + D) {
+    float y = 0.f;
+    bool have = false;
+    if (kind == 2) {
+      if (paylen % 4) return false;
+      if (paylen) { std::memcpy(&y, pay, 4); have = true; }
+    } else if (kind == 3) {
+      if (!packed_varints(pay, pay + paylen, [&](int64_t x) { if (!have) { y = (float)x; have = true; } })) return false;
+    }
+    if (have) b.label.back() = y;
+    return true;
+  }
+  std::string& dst = b.bytes[code - S - D - 1].back();
+  if (kind == 1 && paylen) dst.assign(reinterpret_cast<const char*>(pay), paylen);
+  else if (kind == 1) return false;                      // an empty value or none: the general parser knows which
+  return true;
+}
+
 // Adds one serialized Example to the batch.  Features that the record does not carry keep their defaults (no ids,
 // zeros, label 0, empty bytes); when a name occurs twice the later entry wins, as in a protobuf map.
 static void parse_example(const uint8_t* data, size_t len, const Spec& sp, Batch& b, ParseState& st) {
@@ -438,6 +536,17 @@ static void parse_example(const uint8_t* data, size_t len, const Spec& sp, Batch
     while (!feats.done()) {
       if (!varint(feats, tag)) bad();
       if ((tag >> 3) != 1 || (tag & 7) != 2) { if (!skip(feats, (uint32_t)(tag & 7))) bad(); continue; }
+      if (nth < st.order.size()) {
+        int kind;
+        const uint8_t* pay;
+        size_t paylen, total;
+        if (quick_entry(feats.p, feats.e, st.order[nth].first, kind, pay, paylen, total) &&
+            take_quick(sp, b, st.order[nth].second, kind, pay, paylen, row, drow)) {
+          feats.p += total;
+          ++nth;
+          continue;
+        }
+      }
       Cursor entry;
       if (!sub(feats, entry)) bad();
       std::string_view key;

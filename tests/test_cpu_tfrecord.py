@@ -313,3 +313,95 @@ def test_input_files_on_a_remote_file_system_are_fetched_as_they_are_read(tmp_pa
             list(bad)
     finally:
         checkpoint.set_remote_fs(None)
+
+
+def _py_example(row, long_len=False, unpacked=False):
+    """Plain-Python tf.train.Example encoder with two knobs that keep a record valid but off the reader's fast path:
+    every length as a two-byte varint, and number lists with one element per tag."""
+    def varint(v):
+        v &= (1 << 64) - 1
+        out = bytearray()
+        while v >= 0x80:
+            out.append((v & 0x7F) | 0x80)
+            v >>= 7
+        out.append(v)
+        return bytes(out)
+
+    def length(n):
+        return bytes([(n & 0x7F) | 0x80, n >> 7]) if long_len else varint(n)
+
+    def field(num, body):
+        return varint(num << 3 | 2) + length(len(body)) + body
+
+    feats = b""
+    for key, (kind, vals) in row.items():
+        if kind == "int":
+            lst = b"".join(b"\x08" + varint(v) for v in vals) if unpacked else (field(1, b"".join(varint(v) for v in vals)) if vals else b"")
+            feature = field(3, lst)
+        elif kind == "float":
+            raw = [struct.pack("<f", v) for v in vals]
+            lst = b"".join(b"\x0d" + r for r in raw) if unpacked else (field(1, b"".join(raw)) if vals else b"")
+            feature = field(2, lst)
+        elif kind == "bytes":
+            feature = field(1, b"".join(field(1, v) for v in vals))
+        else:
+            feature = b""                                              # a feature with no list at all
+        feats += field(1, field(1, key.encode()) + field(2, feature))
+    return field(1, feats)
+
+
+def test_fast_path_and_general_parser_agree(tmp_path):
+    """Records of the usual shape take a shortcut in the reader; the same contents encoded so that the shortcut does
+    not apply (long length prefixes, unpacked lists) must give the same batches."""
+    rng = np.random.default_rng(11)
+    rows = []
+    for i in range(300):
+        row = {}
+        if rng.random() < 0.9:
+            row["a"] = ("int", [int(x) for x in rng.integers(-2 ** 63, 2 ** 63 - 1, size=int(rng.integers(0, 5)))])
+        if rng.random() < 0.8:
+            row["b"] = ("int", [int(rng.integers(0, 200))])
+        row["c"] = [("int", [3]), ("float", [1.0]), ("none", []), ("bytes", [b"z"])][int(rng.integers(0, 4))]   # a slot of the wrong type
+        row["x"] = ("float", [float(np.float32(v)) for v in rng.standard_normal(int(rng.integers(0, 6)))])
+        row["n"] = ("int", [int(v) for v in rng.integers(-5, 5, size=int(rng.integers(0, 3)))])                  # ints into the dense block
+        row["label"] = ("int", [int(rng.integers(0, 2))]) if rng.random() < 0.5 else ("float", [float(rng.integers(0, 2))])
+        if rng.random() < 0.7:
+            row["u"] = ("bytes", [bytes(rng.integers(0, 256, size=int(rng.integers(0, 9)), dtype=np.uint8))])
+        keys = list(row)
+        if i % 7 == 0:
+            rng.shuffle(keys)                                           # another order: the predicted names miss
+        rows.append({k: row[k] for k in keys})
+    outs = []
+    for name, kw in (("plain", {}), ("long", {"long_len": True}), ("unpacked", {"unpacked": True})):
+        p = str(tmp_path / name)
+        with tn.data.TFRecordWriter(p) as w:
+            for row in rows:
+                w.write(_py_example(row, **kw))
+        ds = tn.data.TFRecordDataset([p], 64, ["a", "b", "c"], dense_keys={"x": 4, "n": 2}, bytes_keys=["u"], packed=True, num_workers=1,
+                                     pin_memory=False)
+        outs.append(list(ds))
+    ref = outs[0]
+    assert sum(int(y.numel()) for _, y in ref) == 300
+    i = 0
+    for f, y in ref:                                                    # and the plain file against the rows themselves
+        pk = f[tn.data.PACKED_KEY]
+        n = pk.batch_size
+        for b in range(n):
+            row = rows[i + b]
+            want_a = row["a"][1] if "a" in row else []
+            lo, hi = int(pk.offsets[b]), int(pk.offsets[b + 1])
+            assert pk.values[lo:hi].tolist() == want_a
+            want_c = row["c"][1] if row["c"][0] == "int" else []
+            lo, hi = int(pk.offsets[2 * n + b]), int(pk.offsets[2 * n + b + 1])
+            assert pk.values[lo:hi].tolist() == want_c
+            xs = (row["x"][1] + [0.0] * 4)[:4] + ([float(v) for v in row["n"][1]] + [0.0, 0.0])[:2]
+            assert f["dense"][b].tolist() == xs
+            assert float(y[b]) == float(row["label"][1][0])
+            assert f["u"][b] == (row["u"][1][0] if "u" in row else b"")
+        i += n
+    for other in outs[1:]:
+        assert len(other) == len(ref)
+        for (f0, y0), (f1, y1) in zip(ref, other):
+            assert torch.equal(f0[tn.data.PACKED_KEY].values, f1[tn.data.PACKED_KEY].values)
+            assert torch.equal(f0[tn.data.PACKED_KEY].offsets, f1[tn.data.PACKED_KEY].offsets)
+            assert torch.equal(f0["dense"], f1["dense"]) and torch.equal(y0, y1) and f0["u"] == f1["u"]
