@@ -1,7 +1,7 @@
 """Batches stored the way the device takes them.
 
-Parsing records costs the host about a microsecond per example (``benchmarks/input_bench.py``), two orders of
-magnitude more than a B200 needs to train on it; the reference has the same imbalance between its TensorFlow input
+Parsing records costs the host about a microsecond per example (``benchmarks/input_bench.py``), thirty
+times what a B200 needs to train on it; the reference has the same imbalance between its TensorFlow input
 pipeline and its parameter servers and hides it behind ``prefetch``.  A batch cache removes the parsing from the
 training run: a pass over the input (``TFRecordDataset`` or any iterable of ``(features, labels)``) is written once as
 whole batches, each one blob holding exactly the arrays a step copies to the GPU (ids of all slots slot-major, bag
