@@ -11,7 +11,9 @@ Two shared objects are produced under ``tensornet_b200/_ext``:
 With ``TN_CPU_SANITIZE=1`` the C++ runtime is built a second time as ``_tn_cpu_san`` with AddressSanitizer and
 UndefinedBehaviorSanitizer and used in place of ``_tn_cpu`` (run Python with the ASan runtime preloaded:
 ``LD_PRELOAD=$(gcc -print-file-name=libasan.so) ASAN_OPTIONS=detect_leaks=0``); the CI job ``cpu-sanitizers`` runs the
-table, checkpoint and streaming tests that way.
+table, checkpoint and streaming tests that way.  ``TN_CPU_SANITIZE=thread`` does the same with ThreadSanitizer
+(``_tn_cpu_tsan``, ``LD_PRELOAD=$(gcc -print-file-name=libtsan.so)``) for the code that runs its own threads: the
+TFRecord reader's workers, the lock-striped tables, the parallel block readers.
 
 A built ``.so`` is loaded directly when the digest of the sources it was built from (kept next
 to it) still matches ``csrc``; otherwise it is rebuilt first, so an edited kernel can never run
@@ -80,10 +82,12 @@ def _build(name: str, sources, cuda: bool, verbose: bool = False):
     os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0a")
     os.environ.setdefault("MAX_JOBS", str(os.cpu_count() or 4))
     sanitize = name.endswith("_san")
+    tsan = name.endswith("_tsan")
     kwargs = dict(
         name=name,
         sources=sources,
         extra_cflags=(["-O1", "-g", "-std=c++17", "-fsanitize=address,undefined", "-fno-omit-frame-pointer"] if sanitize
+                      else ["-O1", "-g", "-std=c++17", "-fsanitize=thread", "-fno-omit-frame-pointer"] if tsan
                       else ["-O3", "-std=c++17"]),
         extra_include_paths=[_CSRC],
         build_directory=os.path.join(_EXT, name),
@@ -94,8 +98,14 @@ def _build(name: str, sources, cuda: bool, verbose: bool = False):
         kwargs["with_cuda"] = True
         kwargs["extra_ldflags"] = ["-lcuda"] if _has_libcuda() else []
     else:
-        kwargs["extra_ldflags"] = ["-lz"] + (["-fsanitize=address,undefined"] if sanitize else [])
-    mod = cpp_extension.load(**kwargs)
+        kwargs["extra_ldflags"] = ["-lz"] + (["-fsanitize=address,undefined"] if sanitize else ["-fsanitize=thread"] if tsan else [])
+    # The compiler and ninja must not inherit a preloaded sanitizer runtime (this process keeps its own copy).
+    preload = os.environ.pop("LD_PRELOAD", None) if (sanitize or tsan) else None
+    try:
+        mod = cpp_extension.load(**kwargs)
+    finally:
+        if preload is not None:
+            os.environ["LD_PRELOAD"] = preload
     with open(_digest_path(name), "w") as f:
         f.write(_digest(sources))
     return mod
@@ -170,6 +180,9 @@ def cuda_ext():
 
 
 def cpu_ext():
-    if os.environ.get("TN_CPU_SANITIZE", "") not in ("", "0"):
+    mode = os.environ.get("TN_CPU_SANITIZE", "")
+    if mode == "thread":
+        return load("_tn_cpu_tsan")
+    if mode not in ("", "0"):
         return load("_tn_cpu_san")
     return load("_tn_cpu")
