@@ -29,6 +29,7 @@ def main():
     ap.add_argument("--hidden", type=int, nargs="+", default=[512, 256, 256])
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--requests", type=int, default=100)
+    ap.add_argument("--export-tower", default="", help="also write the dense tower to this file for examples/native_serving/serve.cpp")
     a = ap.parse_args()
     tn.core.init()
     rt = tn.core.runtime()
@@ -45,6 +46,8 @@ def main():
         for k, v in sd.items():
             if k.startswith("mlp.weights.") and v.shape == mlp.weights[int(k.split(".")[-1])].shape:
                 mlp.weights[int(k.split(".")[-1])].copy_(v)
+    if a.export_tower:
+        tn.serving.export_tower(mlp, head, a.export_tower)
     eng = InferenceEngine(d, mlp, head, a.slots, combiner="mean")
     g = torch.Generator().manual_seed(0)
     signs = torch.from_numpy(d.signs.view("int64")) if not rt.on_gpu else d.row_keys[: d.n].cpu()

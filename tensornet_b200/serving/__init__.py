@@ -8,5 +8,6 @@ sub-graph" (README.md:42-44): the dictionary is ``sign -> w[0..dim)`` cut out of
 (examples/online_serving/main.cc:76-81).  Here the lookup is real.
 """
 from .engine import EmbeddingDictionary, InferenceEngine, ShardedInferenceEngine, export_sparse_dictionary
+from .export import export_tower
 
-__all__ = ["EmbeddingDictionary", "InferenceEngine", "ShardedInferenceEngine", "export_sparse_dictionary"]
+__all__ = ["EmbeddingDictionary", "InferenceEngine", "ShardedInferenceEngine", "export_sparse_dictionary", "export_tower"]
