@@ -187,14 +187,93 @@ class AUC(Metric):
         return float(torch.trapz(torch.flip(tpr, [0]), torch.flip(fpr, [0])))
 
 
-_BY_NAME = {"auc": AUC, "ctr": CTR, "pctr": PCTR, "copc": COPC, "loss": MeanLoss}
+class _PerExample(Metric):
+    """Mean over the examples of a value computed from (label, prediction): the metrics Keras knows by name, which
+    the reference's example compiles as ``"acc", "mse", "mae", "mape"`` (examples/main.py:64-69).  They need the
+    predictions of every step, so a model that compiles one runs its steps without CUDA graphs; sums are kept as
+    tensors on the predictions' device and read when ``result()`` is called."""
+
+    def __init__(self, name):
+        super().__init__(name)
+        self.reset_state()
+
+    def reset_state(self):
+        self._total, self._count = None, None
+
+    def _value(self, y: torch.Tensor, p: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+    def update_state(self, y_true, y_pred, sample_weight=None):
+        p = y_pred.detach().float().reshape(-1)
+        y = y_true.detach().float().reshape(-1).to(p.device)
+        v = self._value(y, p)
+        if sample_weight is not None:
+            w = sample_weight.detach().float().reshape(-1).to(p.device)
+            s, c = (v * w).sum(), w.sum()
+        else:
+            s, c = v.sum(), torch.tensor(float(v.numel()), device=p.device)
+        self._total = s if self._total is None else self._total + s
+        self._count = c if self._count is None else self._count + c
+
+    def result(self) -> float:
+        if self._total is None:
+            return 0.0
+        c = float(self._count)
+        return float(self._total) / c if c else 0.0
+
+
+class BinaryAccuracy(_PerExample):
+    """Share of examples whose prediction falls on the label's side of ``threshold``."""
+
+    def __init__(self, name="acc", threshold: float = 0.5):
+        super().__init__(name)
+        self.threshold = threshold
+
+    def _value(self, y, p):
+        return ((p > self.threshold) == (y > 0.5)).float()
+
+
+class MeanSquaredError(_PerExample):
+    def __init__(self, name="mse"):
+        super().__init__(name)
+
+    def _value(self, y, p):
+        return (y - p) ** 2
+
+
+class MeanAbsoluteError(_PerExample):
+    def __init__(self, name="mae"):
+        super().__init__(name)
+
+    def _value(self, y, p):
+        return (y - p).abs()
+
+
+class MeanAbsolutePercentageError(_PerExample):
+    """``100 * |y - p| / max(|y|, 1e-7)``, as Keras defines it (large when labels are 0)."""
+
+    def __init__(self, name="mape"):
+        super().__init__(name)
+
+    def _value(self, y, p):
+        return 100.0 * (y - p).abs() / y.abs().clamp(min=1e-7)
+
+
+_BY_NAME = {"auc": AUC, "ctr": CTR, "pctr": PCTR, "copc": COPC, "loss": MeanLoss,
+            "acc": BinaryAccuracy, "accuracy": BinaryAccuracy, "binary_accuracy": BinaryAccuracy,
+            "mse": MeanSquaredError, "mean_squared_error": MeanSquaredError,
+            "mae": MeanAbsoluteError, "mean_absolute_error": MeanAbsoluteError,
+            "mape": MeanAbsolutePercentageError, "mean_absolute_percentage_error": MeanAbsolutePercentageError}
 
 
 def get(spec) -> Metric:
-    """A metric object from an instance or one of the names ``auc / ctr / pctr / copc / loss``."""
+    """A metric object from an instance or one of the names ``auc / ctr / pctr / copc / loss`` (fed from the loss
+    kernels' sums) and ``acc / mse / mae / mape`` with their long Keras names (computed from every step's
+    predictions).  A name keeps its spelling as the metric's name."""
     if isinstance(spec, str):
         try:
-            return _BY_NAME[spec.lower()]()
+            cls = _BY_NAME[spec.lower()]
+            return cls(spec) if issubclass(cls, _PerExample) else cls()
         except KeyError:
             raise ValueError(f"unknown metric {spec!r}; pass an object with update_state / result") from None
     if not (hasattr(spec, "update_state") and hasattr(spec, "result")):
@@ -202,4 +281,5 @@ def get(spec) -> Metric:
     return spec
 
 
-__all__ = ["Metric", "BatchStats", "CTR", "PCTR", "COPC", "AUC", "MeanLoss", "get", "AUC_BINS"]
+__all__ = ["Metric", "BatchStats", "CTR", "PCTR", "COPC", "AUC", "MeanLoss", "BinaryAccuracy", "MeanSquaredError",
+           "MeanAbsoluteError", "MeanAbsolutePercentageError", "get", "AUC_BINS"]

@@ -282,9 +282,10 @@ class Model(nn.Module):
 
     def compile(self, optimizer=None, loss="binary_crossentropy", metrics: Optional[Sequence] = None,
                 cuda_graph: Optional[bool] = None, graph_warmup: int = 3):
-        """``metrics``: objects with ``update_state / result`` or the names ``auc, ctr, pctr, copc, loss``.  The metrics
-        of ``tn.metric`` are fed from sums the loss kernel keeps on the device (no per-step cost); any other metric
-        object gets ``update_state(labels, predictions)`` after every step, which reads the predictions back."""
+        """``metrics``: objects with ``update_state / result`` or names.  ``auc, ctr, pctr, copc, loss`` (the classes of
+        ``tn.metric``) are fed from sums the loss kernel keeps on the device (no per-step cost).  The Keras names
+        ``acc, mse, mae, mape`` and any other metric object get ``update_state(labels, predictions)`` after every
+        step; such a model runs its steps without CUDA graphs."""
         rt = core.runtime()
         self.to(rt.device)
         self.optimizer = optimizer
@@ -300,7 +301,8 @@ class Model(nn.Module):
         self._sums_seen = None
         self._steps_seen = self._loss_steps = 0
         self._unit_grad = torch.ones((), dtype=torch.float32, device=rt.device)
-        self._use_graph = rt.on_gpu and (core.config.cuda_graph if cuda_graph is None else cuda_graph)
+        # metrics that read every step's predictions on the host cannot run inside a captured step
+        self._use_graph = rt.on_gpu and (core.config.cuda_graph if cuda_graph is None else cuda_graph) and not self._host_metrics
         self._graph_warmup = graph_warmup
         if rt.on_gpu:
             tables = {id(l.table): l.table for l in self.sparse_layers() if hasattr(l, "table")}

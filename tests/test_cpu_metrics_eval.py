@@ -193,3 +193,27 @@ def test_steps_per_epoch_consumes_exactly_that_many_batches_of_a_shared_iterator
     h = m.fit(it, epochs=3, steps_per_epoch=3, record_step_loss=True)
     assert len(h["step_loss"]) == 9
     assert taken == list(range(9))
+
+
+def test_keras_metric_names_of_the_reference_example():
+    """compile(metrics=["acc", "mse", "mae", "mape", AUC, CTR, PCTR, COPC]) as in the reference's examples/main.py."""
+    data = _data(4)
+    m = _model(["acc", "mse", "mae", "mape", tn.metric.AUC(), tn.metric.CTR(), tn.metric.PCTR(), tn.metric.COPC()])
+    assert [x.name for x in m._host_metrics] == ["acc", "mse", "mae", "mape"] and not m._use_graph
+    hist = m.fit(iter(data * 5), epochs=1)
+    assert set(hist) >= {"loss", "acc", "mse", "mae", "mape", "auc", "CTR", "PCTR", "COPC"}
+    # against the definitions, on one batch
+    y = torch.tensor([1.0, 0.0, 1.0, 1.0])
+    p = torch.tensor([0.9, 0.4, 0.2, 0.6])
+    want = {"acc": 0.75, "mse": float(((y - p) ** 2).mean()), "mae": float((y - p).abs().mean()),
+            "mape": float((100 * (y - p).abs() / y.abs().clamp(min=1e-7)).mean())}
+    for name, v in want.items():
+        met = tn.metric.get(name)
+        met.update_state(y, p)
+        met.update_state(y[:2], p[:2], sample_weight=torch.tensor([0.0, 0.0]))       # weightless examples change nothing
+        assert met.name == name and abs(met.result() - v) <= 1e-6 * max(1.0, abs(v))
+        met.reset_state()
+        assert met.result() == 0.0
+    assert tn.metric.get("binary_accuracy").name == "binary_accuracy"
+    with pytest.raises(ValueError):
+        tn.metric.get("top_k")
