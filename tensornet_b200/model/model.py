@@ -793,10 +793,11 @@ class Model(nn.Module):
         with start_as_current_span("predict_on_batch"):
             return self.predict_step((x, None))[1]
 
-    def predict(self, dataset: Iterable, steps: Optional[int] = None, callbacks: Sequence = ()):
+    def predict(self, dataset: Iterable, steps: Optional[int] = None, callbacks: Sequence = (), verbose: int = 0):
         """``(labels, predictions)`` over ``dataset``.  ``callbacks`` get ``on_predict_begin`` (where
         ``PsWeightCheckpoint`` loads the checkpoint and re-arms the balanced dataset) and ``on_predict_end``
-        (tensornet/model/Model.py:79-81, tensornet/callbacks/callbacks.py:78-84)."""
+        (tensornet/model/Model.py:79-81, tensornet/callbacks/callbacks.py:78-84).  ``verbose``: rank 0 prints the
+        number of batches scored when the pass ends (the reference's example passes ``verbose=1``)."""
         with start_as_current_span("predict"):
             for cb in callbacks:
                 cb.set_model(self)
@@ -812,9 +813,12 @@ class Model(nn.Module):
             core.runtime().check_status()
             for cb in callbacks:
                 cb.on_predict_end()
+            if verbose and core.runtime().rank == 0:
+                print(f"predict: {len(ps)} batches", flush=True)
             return (torch.cat(ys) if ys else None), (torch.cat(ps) if ps else None)
 
-    def evaluate(self, dataset: Iterable, steps: Optional[int] = None, callbacks: Sequence = (), return_dict: bool = True):
+    def evaluate(self, dataset: Iterable, steps: Optional[int] = None, callbacks: Sequence = (), return_dict: bool = True,
+                 verbose: int = 0):
         """Loss and every compiled metric over ``dataset`` with the parameters left untouched (rows of unseen signs
         are created as zeros, as in the reference's inference mode).  ``callbacks`` get ``on_test_begin`` /
         ``on_test_end`` (tensornet/callbacks/callbacks.py:86-91).  Metric state is reset first, as Keras does."""
@@ -838,6 +842,8 @@ class Model(nn.Module):
             out.update(self.metric_results())
             for cb in callbacks:
                 cb.on_test_end(out)
+            if verbose and core.runtime().rank == 0:
+                print("evaluate: " + " ".join(f"{k} {v:.5f}" for k, v in out.items()), flush=True)
             return out if return_dict else [out["loss"]] + [out[m.name] for m in self.metrics]
 
     def _prefetched(self, dataset: Iterable):

@@ -215,5 +215,8 @@ def test_keras_metric_names_of_the_reference_example():
         met.reset_state()
         assert met.result() == 0.0
     assert tn.metric.get("binary_accuracy").name == "binary_accuracy"
+    # the calls of the reference's driver: verbose is accepted by fit, predict and evaluate
+    y_all, p_all = m.predict(iter(data), verbose=1, callbacks=[])
+    assert y_all.shape == p_all.reshape(-1).shape and "loss" in m.evaluate(iter(data), verbose=1)
     with pytest.raises(ValueError):
         tn.metric.get("top_k")
