@@ -1061,6 +1061,20 @@ class Model(nn.Module):
             elif hasattr(m, "save_bn_table"):
                 yield "bn", m
 
+    def save(self, filepath: str) -> str:
+        """Export the dense part for serving: ``<filepath>/sub_model.pt`` holds the ``state_dict`` of ``self.sub_model``
+        (of the whole module when there is no such attribute).  The role of ``sub_model.save(...)`` in the reference's
+        driver (examples/main.py:100-104), which writes a TensorFlow SavedModel; the sparse part is exported separately
+        (``tn.serving.export_sparse_dictionary``).  Rank 0 writes; every rank returns the file's path."""
+        rt = core.runtime()
+        path = os.path.join(filepath, "sub_model.pt")
+        if rt.rank == 0:
+            os.makedirs(filepath, exist_ok=True)
+            module = getattr(self, "sub_model", None) or self
+            torch.save({k: v.detach().cpu() for k, v in module.state_dict().items()}, path)
+        core.barrier()
+        return path
+
     def save_weights(self, filepath: str, dt: str = "", mode: str = "txt", **kwargs):
         """<filepath>/<dt>/{sparse_table,dense_table,bn_table,torch_checkpoint.pt}; ``_checkpoint`` last."""
         rt = core.runtime()

@@ -215,6 +215,12 @@ def test_keras_metric_names_of_the_reference_example():
         met.reset_state()
         assert met.result() == 0.0
     assert tn.metric.get("binary_accuracy").name == "binary_accuracy"
+    # the dense part for serving, as sub_model.save(...) in the reference's driver
+    import os, tempfile
+    with tempfile.TemporaryDirectory() as d:
+        path = m.save(os.path.join(d, "saved_model"))
+        sd = torch.load(path)
+        assert os.path.basename(path) == "sub_model.pt" and set(sd) == set(m.sub_model.state_dict())
     # the calls of the reference's driver: verbose is accepted by fit, predict and evaluate
     y_all, p_all = m.predict(iter(data), verbose=1, callbacks=[])
     assert y_all.shape == p_all.reshape(-1).shape and "loss" in m.evaluate(iter(data), verbose=1)
