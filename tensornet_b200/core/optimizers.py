@@ -52,6 +52,11 @@ class OptimizerBase:
     def current_lr(self, step: int) -> float:
         return float(self.schedule(step)) if self.schedule is not None else self.learning_rate
 
+    def get_config(self) -> Dict[str, Any]:
+        """Name and hyper-parameters, enough for :func:`optimizer_from_config` to build the same optimizer again
+        (a learning-rate schedule is code and is not part of it: the current base rate stands in)."""
+        return {"name": self.name, "learning_rate": self.learning_rate, **{k: getattr(self, k) for k in self._defaults}}
+
     def __repr__(self):
         kv = ", ".join(f"{k}={getattr(self, k)!r}" for k in ["learning_rate", *self._defaults])
         return f"{self.name}({kv})"
@@ -80,3 +85,13 @@ class Adam(OptimizerBase):
 class Ftrl(OptimizerBase):
     name, kind = "Ftrl", KIND_FTRL
     _defaults = dict(show_decay_rate=0.98, show_threshold=0.0, beta=1.0, lambda1=0.1, lambda2=1.0, initial_scale=1.0)
+
+
+def optimizer_from_config(config: Dict[str, Any]) -> OptimizerBase:
+    """The optimizer :meth:`OptimizerBase.get_config` described."""
+    kw = dict(config)
+    name = kw.pop("name")
+    for cls in OptimizerBase.__subclasses__():
+        if cls.name == name:
+            return cls(**kw)
+    raise ValueError(f"unknown optimizer {name!r}")

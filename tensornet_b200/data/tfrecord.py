@@ -98,6 +98,18 @@ class TFRecordDataset:
         self.pin_memory = torch.cuda.is_available() if pin_memory is None else bool(pin_memory)
         self.shuffle_files, self.seed, self._passes = bool(shuffle_files), int(seed), 0
 
+    @classmethod
+    def from_columns(cls, files: Sequence[str], batch_size: int, feature_columns: Sequence, **kwargs) -> "TFRecordDataset":
+        """The dataset that reads what ``feature_columns`` (category, sequence or embedding columns, e.g. the list an
+        ``EmbeddingFeatures`` layer was built from) declare in their ``parse_example_spec``: one int64 list per
+        column key, in the columns' order.  Other arguments as for the constructor."""
+        keys = []
+        for c in feature_columns:
+            for k in c.parse_example_spec:
+                if k not in keys:
+                    keys.append(k)
+        return cls(files, batch_size, keys, **kwargs)
+
     def _tensor(self, a: np.ndarray) -> torch.Tensor:
         t = torch.from_numpy(a)
         return t.pin_memory() if self.pin_memory and t.numel() else t

@@ -22,6 +22,23 @@ class CategoryColumn:
     def num_buckets(self) -> int:
         return self.bucket_size
 
+    @property
+    def parse_example_spec(self) -> dict:
+        """What an input parser has to extract for this column: a variable-length int64 list under ``key``
+        (category_column.py:52-54; ``tn.data.TFRecordDataset.from_columns`` reads it)."""
+        return {self.key: ("varlen", "int64")}
+
+    @property
+    def parents(self) -> list:
+        return [self.key]
+
+    def get_config(self) -> dict:
+        return {"key": self.key, "bucket_size": self.bucket_size}
+
+    @classmethod
+    def from_config(cls, config: dict) -> "CategoryColumn":
+        return cls(config["key"], config.get("bucket_size", 1024))
+
     def __repr__(self):
         return f"CategoryColumn(key={self.key!r}, bucket_size={self.bucket_size})"
 
@@ -50,6 +67,25 @@ class SequenceCategoryColumn:
     def bucket_size(self):
         return self.categorical_column.bucket_size
 
+    @property
+    def num_buckets(self):
+        return self.categorical_column.num_buckets
+
+    @property
+    def parse_example_spec(self) -> dict:
+        return self.categorical_column.parse_example_spec
+
+    @property
+    def parents(self) -> list:
+        return [self.categorical_column]
+
+    def get_config(self) -> dict:
+        return {"categorical_column": self.categorical_column.get_config(), "max_length": self.max_length}
+
+    @classmethod
+    def from_config(cls, config: dict) -> "SequenceCategoryColumn":
+        return cls(CategoryColumn.from_config(config["categorical_column"]), config.get("max_length", 0))
+
 
 def sequence_category_column(categorical_column: CategoryColumn, max_length: int = 0) -> SequenceCategoryColumn:
     return SequenceCategoryColumn(categorical_column, max_length)
@@ -66,6 +102,20 @@ class EmbeddingColumn:
     @property
     def name(self):
         return self.categorical_column.name + "_embedding"
+
+    @property
+    def parse_example_spec(self) -> dict:
+        return self.categorical_column.parse_example_spec
+
+    def get_config(self) -> dict:
+        cat = self.categorical_column
+        return {"categorical_column": cat.get_config(), "sequence": isinstance(cat, SequenceCategoryColumn),
+                "dimension": self.dimension, "combiner": self.combiner}
+
+    @classmethod
+    def from_config(cls, config: dict) -> "EmbeddingColumn":
+        kind = SequenceCategoryColumn if config.get("sequence") else CategoryColumn
+        return cls(kind.from_config(config["categorical_column"]), config["dimension"], config.get("combiner", "mean"))
 
     def __repr__(self):
         return f"EmbeddingColumn({self.categorical_column!r}, dimension={self.dimension}, combiner={self.combiner!r})"

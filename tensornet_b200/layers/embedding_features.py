@@ -64,6 +64,39 @@ class EmbeddingFeatures(nn.Module):
     def feature_columns(self):
         return self._feature_columns
 
+    def filter_not_used_features(self, features: Dict) -> Dict:
+        """The entries of ``features`` that this layer's columns read (embedding_features.py:314-319)."""
+        return {k: features[k] for k in self._keys}
+
+    def get_sparse_pulling_feature(self, features: Dict):
+        """``(pulled, targets)``: the id features of ``features`` split into those whose signs are looked up and the
+        target columns that only feed the show / click counters (embedding_features.py:321-334)."""
+        pulled, targets = {}, {}
+        for k, v in features.items():
+            if self._target_columns and k in self._target_columns:
+                targets[k] = v
+            elif k in self._keys:
+                pulled[k] = v
+        return pulled, targets
+
+    def get_config(self) -> Dict:
+        """Constructor arguments as plain data (embedding_features.py:369-379); ``from_config`` builds the layer again."""
+        return {"name": self.layer_name, "trainable": self.trainable, "is_concat": self.is_concat,
+                "target_columns": self._target_columns, "embedding_share": self.embedding_share,
+                "feature_columns": [c.get_config() for c in self._feature_columns], "sparse_opt": self._sparse_opt.get_config()}
+
+    @classmethod
+    def from_config(cls, config: Dict, sparse_opt=None):
+        """``sparse_opt`` overrides the optimizer described in ``config`` (a learning-rate schedule is not part of a
+        configuration)."""
+        from ..core.optimizers import optimizer_from_config
+        from ..feature_column import EmbeddingColumn
+        cfg = dict(config)
+        cols = [EmbeddingColumn.from_config(c) for c in cfg.pop("feature_columns")]
+        opt = sparse_opt or optimizer_from_config(cfg.pop("sparse_opt"))
+        cfg.pop("sparse_opt", None)
+        return cls(cols, opt, **cfg)
+
     def _pull_args(self, features: Dict, training: bool):
         """What this layer's pull needs from a batch: ``(ids, offsets, B, labels, label_mod, count)``.  A model that
         runs several layers' pulls with shared round trips asks for them first; the ``forward`` of the same batch

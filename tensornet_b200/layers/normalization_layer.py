@@ -162,6 +162,12 @@ class TNBatchNormalizationBase(nn.Module):
         core.load_bn_table(self.bn_table_handle, filepath)
         self.update_moments()
 
+    def get_config(self) -> dict:
+        """Constructor arguments as plain data (normalization_layer.py:185-198)."""
+        return {"name": self.layer_name, "center": self.center, "scale": self.scale, "epsilon": self.epsilon,
+                "momentum": self.momentum, "synchronized": self.synchronized, "sync_freq": self.sync_freq,
+                "max_count": self.max_count}
+
 
 class TNBatchNormalization(TNBatchNormalizationBase):
     """var = squared_sum / count - (sum / count)^2"""

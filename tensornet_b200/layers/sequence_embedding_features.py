@@ -23,6 +23,8 @@ class SequenceEmbeddingFeatures(nn.Module):
         for c in feature_columns:
             assert c.dimension == dim, "currently we only support feature_columns with same dimension"
         self.layer_name = name or ""
+        self._sparse_opt = sparse_opt
+        self.is_concat = is_concat
         self.trainable = trainable
         self._feature_columns = list(feature_columns)
         self._keys = [c.categorical_column.name for c in feature_columns]
@@ -36,6 +38,30 @@ class SequenceEmbeddingFeatures(nn.Module):
         self.links = [self.table.link(c.categorical_column.bucket_size) for c in feature_columns]
         self._anchor = torch.zeros(1, requires_grad=True, device=core.runtime().device)
         self._pending = []
+
+    def filter_not_used_features(self, features: Dict) -> Dict:
+        """The entries of ``features`` that this layer's columns read (sequence_embedding_features.py:147-152)."""
+        return {k: features[k] for k in self._keys}
+
+    def get_sparse_pulling_feature(self, features: Dict) -> Dict:
+        """The id features whose signs this layer looks up (sequence_embedding_features.py:154-162)."""
+        return {k: v for k, v in features.items() if k in self._keys}
+
+    def get_config(self) -> Dict:
+        return {"name": self.layer_name, "trainable": self.trainable, "is_concat": self.is_concat,
+                "embedding_share": self.embedding_share, "need_stop_gradient": self._need_stop_gradient,
+                "max_length": self.max_length, "feature_columns": [c.get_config() for c in self._feature_columns],
+                "sparse_opt": self._sparse_opt.get_config()}
+
+    @classmethod
+    def from_config(cls, config: Dict, sparse_opt=None):
+        from ..core.optimizers import optimizer_from_config
+        from ..feature_column import EmbeddingColumn
+        cfg = dict(config)
+        cols = [EmbeddingColumn.from_config(c) for c in cfg.pop("feature_columns")]
+        opt = sparse_opt or optimizer_from_config(cfg.pop("sparse_opt"))
+        cfg.pop("sparse_opt", None)
+        return cls(cols, opt, **cfg)
 
     def forward(self, features: Dict, training: Optional[bool] = None):
         if not isinstance(features, dict):

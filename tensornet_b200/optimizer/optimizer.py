@@ -50,6 +50,10 @@ class Optimizer:
         if self.table.initialized:
             self.table.G.zero_()
 
+    def get_config(self) -> dict:
+        """Name and the dense optimizer's hyper-parameters (optimizer.py:80-82)."""
+        return {"name": self.name, "dense_opt": self.dense_opt.get_config()}
+
     def save_dense_table(self, filepath: str):
         return core.save_dense_table(self.dense_table_handle, filepath)
 
@@ -80,13 +84,20 @@ class PCGrad(Optimizer):
             out.append(g)
         return torch.stack(out).sum(dim=0)
 
-    def step_multi(self, losses: Sequence[torch.Tensor]):
-        """Backward every task loss separately, project, write the result into the flat gradient, step."""
+    def compute_gradients(self, loss: Sequence[torch.Tensor], var_list=None, tape=None, grad_loss=None) -> torch.Tensor:
+        """One backward pass per task loss over the attached dense parameters, then the projection; the result is
+        left in the flat gradient that ``step()`` applies and is returned (optimizer.py:91-130 in the reference, whose
+        ``var_list`` / ``tape`` / ``grad_loss`` arguments have no meaning here and are accepted for the call's shape)."""
         G = self.table.G
         grads = []
-        for k, loss in enumerate(losses):
+        for k, task_loss in enumerate(loss):
             G.zero_()
-            loss.backward(retain_graph=k < len(losses) - 1)
+            task_loss.backward(retain_graph=k < len(loss) - 1)
             grads.append(G.clone())
         G.copy_(self.project(grads))
+        return G
+
+    def step_multi(self, losses: Sequence[torch.Tensor]):
+        """Backward every task loss separately, project, write the result into the flat gradient, step."""
+        self.compute_gradients(losses)
         self.step()

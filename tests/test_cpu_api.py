@@ -336,3 +336,49 @@ def test_lookahead_pairs_every_batch_with_its_successor():
 
     it = _with_next(gen())
     assert next(it) == (0, 1) and seen == [0, 1]          # exactly one batch ahead of the consumer
+
+
+def test_configuration_and_helper_methods_of_the_reference_surface():
+    """get_config / from_config of columns, layers and optimizers, the feature filters of the embedding layers, the
+    parse spec of a column and PCGrad.compute_gradients (names of tensornet/layers/embedding_features.py:309-392,
+    feature_column/category_column.py:52-58, optimizer/optimizer.py:80-130)."""
+    tn.core.init()
+    cat = tn.feature_column.category_column("7", bucket_size=64)
+    assert cat.parse_example_spec == {"7": ("varlen", "int64")} and cat.parents == ["7"]
+    emb = tn.feature_column.embedding_column(cat, 4, "sum")
+    again = type(emb).from_config(emb.get_config())
+    assert repr(again) == repr(emb)
+    seq = tn.feature_column.embedding_column(tn.feature_column.sequence_category_column(tn.feature_column.category_column("s", 32), 5), 4)
+    assert type(seq).from_config(seq.get_config()).categorical_column.max_length == 5
+
+    opt = tn.core.AdaGrad(learning_rate=0.05, initial_g2sum=0.2)
+    layer = tn.layers.EmbeddingFeatures([emb], opt, name="cfg_layer", is_concat=True, target_columns=["label"])
+    cfg = layer.get_config()
+    assert cfg["name"] == "cfg_layer" and cfg["sparse_opt"]["name"] == "AdaGrad" and cfg["sparse_opt"]["initial_g2sum"] == 0.2
+    cfg["name"] = "cfg_layer_2"
+    twin = tn.layers.EmbeddingFeatures.from_config(cfg)
+    assert twin.layer_name == "cfg_layer_2" and twin.use_cvm and twin._sparse_opt.initial_g2sum == 0.2
+    feats = {"7": torch.tensor([1, 2]), "other": torch.tensor([3, 4]), "label": torch.tensor([1.0, 0.0])}
+    assert list(layer.filter_not_used_features(feats)) == ["7"]
+    pulled, targets = layer.get_sparse_pulling_feature(feats)
+    assert list(pulled) == ["7"] and list(targets) == ["label"]
+
+    slayer = tn.layers.SequenceEmbeddingFeatures([seq], opt, name="cfg_seq")
+    scfg = slayer.get_config()
+    assert scfg["max_length"] == 5 and list(slayer.get_sparse_pulling_feature({"s": 1, "x": 2})) == ["s"]
+    scfg["name"] = "cfg_seq_2"
+    assert tn.layers.SequenceEmbeddingFeatures.from_config(scfg).max_length == 5
+
+    bn = tn.layers.TNBatchNormalization(synchronized=True, sync_freq=4, max_count=1000)
+    assert bn.get_config()["sync_freq"] == 4 and tn.layers.TNBatchNormalization(**bn.get_config()).max_count == 1000
+
+    dense = tn.optimizer.PCGrad(tn.core.Adam(learning_rate=0.01))
+    assert dense.get_config()["dense_opt"]["name"] == "Adam"
+    w = torch.nn.Parameter(torch.tensor([1.0, 0.0]))
+    dense.attach([("w", w)])
+    w = dict(dense.table.named_views())["w"] if hasattr(dense.table, "named_views") else w
+    g = dense.compute_gradients([(w * torch.tensor([1.0, 1.0])).sum(), (w * torch.tensor([-1.0, 0.5])).sum()])
+    # task gradients (1, 1) and (-1, 0.5) conflict: each loses its component along the other before they are summed
+    g1 = torch.tensor([1.0, 1.0]) - (-0.5 / 1.25) * torch.tensor([-1.0, 0.5])
+    g2 = torch.tensor([-1.0, 0.5]) - (-0.5 / 2.0) * torch.tensor([1.0, 1.0])
+    assert torch.allclose(g[:2].cpu(), g1 + g2, atol=1e-6)
