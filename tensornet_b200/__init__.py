@@ -15,7 +15,9 @@ from . import metric
 from . import callbacks
 from . import distribute
 from . import utils
+from . import tools
+from . import serving
 from .version import VERSION as __version__
 
 __all__ = ["core", "feature_column", "layers", "optimizer", "model", "models", "data", "metric", "callbacks",
-           "distribute", "__version__"]
+           "distribute", "utils", "tools", "serving", "__version__"]
