@@ -258,7 +258,9 @@ struct Spec {
 struct Batch {
   int n = 0;
   size_t S;
-  // While records arrive: ids in arrival order and, per (example, slot), where its ids start and how many there are.
+  size_t cap;                               // examples a full batch holds
+  // While records arrive: ids in arrival order and, per (example, slot), where its ids start and how many there are
+  // (with one id per slot the ids go straight to their place in `values` [S, cap] instead).
   std::vector<int64_t> ids;
   std::vector<uint32_t> pos;
   std::vector<int32_t> len;
@@ -270,8 +272,10 @@ struct Batch {
   std::vector<int32_t> local_offsets;       // [S, n + 1], every slot counted from 0
   std::vector<int64_t> slot_base;           // [S + 1] where each slot starts in `values`
 
-  Batch(const Spec& sp, int expect, bool own_buffers = true) : S(sp.sparse.size()), bytes(sp.bytes.size()) {
-    if (own_buffers) {                       // otherwise hand_down() of the previous batch provides them
+  Batch(const Spec& sp, int expect, bool own_buffers = true) : S(sp.sparse.size()), cap((size_t)expect), bytes(sp.bytes.size()) {
+    if (sp.single_hot) {
+      values.assign(S * cap, sp.default_id);
+    } else if (own_buffers) {                // otherwise hand_down() of the previous batch provides them
       ids.reserve((size_t)expect * S);
       pos.reserve((size_t)expect * S);
       len.reserve((size_t)expect * S);
@@ -284,11 +288,10 @@ struct Batch {
     slot_base.assign(S + 1, 0);
     if (ids.size() > (size_t)INT32_MAX) throw std::runtime_error("a batch holds more than 2^31 ids");
     if (sp.single_hot) {
+      if ((size_t)n < cap)                     // a short last batch: close the gaps between the slots' rows
+        for (size_t s = 1; s < S; ++s) std::memmove(values.data() + s * (size_t)n, values.data() + s * cap, (size_t)n * sizeof(int64_t));
       values.resize(S * (size_t)n);
-      for (size_t s = 0; s < S; ++s) {
-        for (int b = 0; b < n; ++b) values[s * n + b] = ids[pos[(size_t)b * S + s]];
-        slot_base[s + 1] = (int64_t)((s + 1) * (size_t)n);
-      }
+      for (size_t s = 0; s < S; ++s) slot_base[s + 1] = (int64_t)((s + 1) * (size_t)n);
     } else {
       size_t total = 0;
       for (int32_t l : len) total += (size_t)l;
@@ -466,6 +469,13 @@ static inline bool take_quick(const Spec& sp, Batch& b, int found, int kind, con
                               size_t drow) {
   if (found < 0) return true;                            // a feature nobody asked for
   const size_t S = sp.sparse.size(), D = sp.dense.size(), code = (size_t)found;
+  if (code < S && sp.single_hot) {                       // the first id, or the default when the list is empty
+    int64_t first = sp.default_id;
+    bool have = false;
+    if (kind == 3 && !packed_varints(pay, pay + paylen, [&](int64_t x) { if (!have) { first = x; have = true; } })) return false;
+    b.values[code * b.cap + (size_t)b.n] = first;
+    return true;
+  }
   if (code < S) {
     const size_t at = b.ids.size();
     if (kind == 3 && !packed_varints(pay, pay + paylen, [&](int64_t x) { b.ids.push_back(x); })) {
@@ -517,8 +527,10 @@ static inline bool take_quick(const Spec& sp, Batch& b, int found, int kind, con
 static void parse_example(const uint8_t* data, size_t len, const Spec& sp, Batch& b, ParseState& st) {
   const size_t S = sp.sparse.size(), D = sp.dense.size();
   const size_t row = b.pos.size();
-  b.pos.resize(row + S, 0u);
-  b.len.resize(row + S, 0);
+  if (!sp.single_hot) {
+    b.pos.resize(row + S, 0u);
+    b.len.resize(row + S, 0);
+  }
   const size_t drow = b.dense.size();
   b.dense.resize(drow + sp.dense_total, 0.f);
   if (!sp.label.empty()) b.label.push_back(0.f);
@@ -579,7 +591,15 @@ static void parse_example(const uint8_t* data, size_t len, const Spec& sp, Batch
       if (found < 0) continue;
       const size_t code = (size_t)found;
       bool ok = true;
-      if (code < S) {
+      if (code < S && sp.single_hot) {
+        int64_t first = sp.default_id;
+        bool have = false;
+        ok = for_each_list(feat, [&](int kind, Cursor list) {
+          if (kind != 3) return true;
+          return for_each_int64(list, [&](int64_t x) { if (!have) { first = x; have = true; } });
+        });
+        b.values[code * b.cap + (size_t)b.n] = first;
+      } else if (code < S) {
         const size_t at = b.ids.size();
         ok = for_each_list(feat, [&](int kind, Cursor list) {
           if (kind != 3) return true;
@@ -611,15 +631,6 @@ static void parse_example(const uint8_t* data, size_t len, const Spec& sp, Batch
         ok = for_each_list(feat, [&](int kind, Cursor list) { return kind != 1 || first_bytes(list, dst); });
       }
       if (!ok) bad();
-    }
-  }
-  if (sp.single_hot) {
-    for (size_t s = 0; s < S; ++s) {
-      if (b.len[row + s] == 0) {                 // none -> the default id; several -> the first
-        b.pos[row + s] = (uint32_t)b.ids.size();
-        b.ids.push_back(sp.default_id);
-      }
-      b.len[row + s] = 1;
     }
   }
   ++b.n;

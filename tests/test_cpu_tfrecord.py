@@ -373,7 +373,7 @@ def test_fast_path_and_general_parser_agree(tmp_path):
         if i % 7 == 0:
             rng.shuffle(keys)                                           # another order: the predicted names miss
         rows.append({k: row[k] for k in keys})
-    outs = []
+    outs, singles = [], []
     for name, kw in (("plain", {}), ("long", {"long_len": True}), ("unpacked", {"unpacked": True})):
         p = str(tmp_path / name)
         with tn.data.TFRecordWriter(p) as w:
@@ -382,8 +382,21 @@ def test_fast_path_and_general_parser_agree(tmp_path):
         ds = tn.data.TFRecordDataset([p], 64, ["a", "b", "c"], dense_keys={"x": 4, "n": 2}, bytes_keys=["u"], packed=True, num_workers=1,
                                      pin_memory=False)
         outs.append(list(ds))
+        singles.append(list(tn.data.TFRecordDataset([p], 64, ["a", "b", "c"], single_hot=True, default_id=-7, packed=True,
+                                                    num_workers=1, pin_memory=False)))
     ref = outs[0]
     assert sum(int(y.numel()) for _, y in ref) == 300
+    i = 0
+    for f, _ in singles[0]:                                             # one id per slot: the first, or the default
+        ids = f[tn.data.PACKED_KEY].ids
+        for b in range(ids.shape[1]):
+            row = rows[i + b]
+            want = [(row[k][1][0] if k in row and row[k][0] == "int" and row[k][1] else -7) for k in ("a", "b", "c")]
+            assert ids[:, b].tolist() == want
+        i += ids.shape[1]
+    assert i == 300
+    for other in singles[1:]:
+        assert all(torch.equal(f0[tn.data.PACKED_KEY].ids, f1[tn.data.PACKED_KEY].ids) for (f0, _), (f1, _) in zip(singles[0], other))
     i = 0
     for f, y in ref:                                                    # and the plain file against the rows themselves
         pk = f[tn.data.PACKED_KEY]
