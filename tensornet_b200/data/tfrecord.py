@@ -85,7 +85,7 @@ class TFRecordDataset:
                  default_id: int = 0, drop_remainder: bool = False, verify_checksums: bool = True, num_workers: int = 4,
                  cycle_length: int = 4, block_length: int = 8, queue_depth: int = 4, pin_memory: Optional[bool] = None,
                  shuffle_files: bool = False, seed: int = 0):
-        self.files = [str(f) for f in files]
+        self.files = [str(files)] if isinstance(files, (str, os.PathLike)) else [str(f) for f in files]
         self.batch_size = int(batch_size)
         self.sparse_keys = [str(k) for k in sparse_keys]
         items = list(dense_keys.items()) if isinstance(dense_keys, Mapping) else list(dense_keys or [])

@@ -135,6 +135,7 @@ def test_own_writer_round_trips_and_unpacked_lists_are_read(tmp_path):
         w.write(b"\x0a" + bytes([len(feats)]) + feats)
     (f, y), = list(tn.data.TFRecordDataset([path], 8, ["a"], dense_keys={"x": 4}, bytes_keys=["u"], pin_memory=False))
     assert f["a"].values.tolist() == [1, -2, 3, 5, 6] and f["a"].offsets.tolist() == [0, 3, 5]
+    assert tn.data.TFRecordDataset(path, 8, ["a"], pin_memory=False).files == [path]           # one path, not its characters
     cols = [tn.feature_column.embedding_column(tn.feature_column.category_column(k), 4) for k in ("a", "zz")]
     assert tn.data.TFRecordDataset.from_columns([path], 8, cols, pin_memory=False).sparse_keys == ["a", "zz"]
     assert y.tolist() == [1.0, 0.0] and f["dense"].tolist() == [[0.5, 0.25, 0, 0], [0, 0, 0, 0]] and f["u"] == [b"k", b""]
