@@ -105,3 +105,44 @@ def test_training_from_the_cache_follows_training_from_the_records(tmp_path):
 
     a, b = train(ds), train(tn.data.BatchCacheDataset(cache, pin_memory=False))
     assert a == b and a[-1] < a[0]
+
+
+def test_any_mix_of_ragged_and_fixed_slots_survives_the_cache(tmp_path):
+    """Property: whatever per-slot features go in (fixed [B], fixed [B, L], ragged with empty bags, any batch sizes),
+    what comes back packs to the same ids and offsets."""
+    from hypothesis import given, settings, strategies as st
+    from tensornet_b200.data.features import gather_columns
+    path = str(tmp_path / "p.tnbc")
+
+    @settings(max_examples=40, deadline=None)
+    @given(st.lists(st.tuples(st.integers(1, 9), st.integers(0, 2 ** 31)), min_size=1, max_size=4), st.integers(1, 3))
+    def check(batches, S):
+        keys = [f"k{s}" for s in range(S)]
+        fed = []
+        with tn.data.BatchCacheWriter(path, keys, label=False) as w:
+            for B, seed in batches:
+                g = torch.Generator().manual_seed(seed)
+                f = {}
+                for s, k in enumerate(keys):
+                    kind = (seed + s) % 3
+                    if kind == 0:
+                        f[k] = torch.randint(-2 ** 62, 2 ** 62, (B,), generator=g)
+                    elif kind == 1:
+                        f[k] = torch.randint(0, 100, (B, 2), generator=g)
+                    else:
+                        lens = torch.randint(0, 4, (B,), generator=g)
+                        offs = torch.cat([torch.zeros(1, dtype=torch.long), lens.cumsum(0)])
+                        f[k] = tn.data.Ragged(torch.randint(0, 100, (int(offs[-1]),), generator=g), offs.int())
+                w.append(f)
+                fed.append(f)
+        back = list(tn.data.BatchCacheDataset(path, pin_memory=False, threads=1))
+        assert len(back) == len(fed)
+        for f, (fb, yb) in zip(fed, back):
+            assert yb is None
+            ids, offs, B = gather_columns(f, keys, torch.device("cpu"))
+            ids2, offs2, B2 = gather_columns(fb, keys, torch.device("cpu"))
+            assert B == B2 and torch.equal(ids, ids2) and (offs is None) == (offs2 is None)
+            if offs is not None:
+                assert torch.equal(offs.int(), offs2.int())
+
+    check()
