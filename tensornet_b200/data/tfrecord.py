@@ -76,7 +76,8 @@ class TFRecordDataset:
     ``num_workers`` threads each own every ``num_workers``-th file, keep ``cycle_length`` of them open and take
     ``block_length`` records from each in turn; batches are handed out worker after worker, so their order depends
     only on these arguments.  Every iteration starts from the first file again; ``shuffle_files=True`` reads the files in
-    another order in every pass (determined by ``seed`` and the number of the pass).
+    another order in every pass (determined by ``seed`` and the number of the pass).  Batches never mix records
+    of two workers, so a pass ends with at most one short batch per worker (none with ``drop_remainder=True``).
     """
 
     def __init__(self, files: Sequence[str], batch_size: int, sparse_keys: Sequence[str],
